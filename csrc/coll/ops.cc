@@ -1,0 +1,640 @@
+// ops.cc - operator front end.
+//
+// Flow of one operator (compare HcclAllReduceInner -> ExecOp in the reference,
+// framework/op_base/src/op_base_host.cc:62-184, hccl_communicator_host.cc:4574-4810):
+//   validate arguments -> (group mode: queue) -> lock communicator -> check state -> select
+//   strategy + engine -> run on the engine (splitting into passes that fit the CCL buffer)
+//   -> record the operator in the diagnostics ring.
+#include "ops.h"
+
+#include <time.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../core/dtype.h"
+#include "../core/env.h"
+#include "../core/log.h"
+#include "../device/coll_kernels.h"
+#include "../device/emu_launch.h"
+#include "exec.h"
+
+namespace hc {
+
+namespace {
+
+uint64_t NowNs()
+{
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (uint64_t)ts.tv_sec * 1000000000ull + (uint64_t)ts.tv_nsec;
+}
+
+std::mutex g_algoMu;
+std::map<std::string, AlgoConfig> g_algoCfg;
+
+struct GroupJob {
+    std::function<HcclResult()> fn;
+    uint64_t volume;
+    bool p2p;
+    bool variable;
+    Comm *comm;
+    OpDesc desc;
+    size_t order;
+};
+thread_local int t_groupDepth = 0;
+thread_local std::vector<GroupJob> t_groupJobs;
+
+void Record(Comm *c, const OpDesc &d, const Selection &sel, uint64_t t0)
+{
+    std::lock_guard<std::mutex> lk(c->diagMu);
+    HcclOpRecord &r = c->opRing[c->opRingNext % c->opRing.size()];
+    memset(&r, 0, sizeof(r));
+    r.seq = c->opSeq;
+    r.cmdType = d.cmd; r.dataType = d.dtype; r.count = d.count; r.reduceOp = d.op; r.root = d.root;
+    snprintf(r.algName, sizeof(r.algName), "%s", sel.name.c_str());
+    r.hostStartNs = t0;
+    r.hostEndNs = NowNs();
+    ++c->opRingNext;
+}
+
+int PickCtas(Comm *c, const Selection &sel, uint64_t bytesPerRank)
+{
+    int forced = EnvConfig::Get().maxCtas.value;
+    int ctas = sel.ctas ? (int)sel.ctas : (int)std::min<uint64_t>(32, std::max<uint64_t>(1, (bytesPerRank + (64 << 10) - 1) / (64 << 10)));
+    if (bytesPerRank >= (64ull << 20)) ctas = std::max(ctas, 48);
+    if (forced > 0) ctas = std::min(ctas, forced);
+    if (c->emuSameDevice) ctas = std::min(ctas, 4);
+    return std::max(1, std::min(ctas, HC_MAX_CTAS));
+}
+
+void FillBase(Comm *c, const OpDesc &d, CollArgs &a)
+{
+    memset(&a, 0, sizeof(a));
+    a.dev = c->devStruct;
+    a.dtype = d.dtype;
+    a.op = d.op;
+    a.root = (int32_t)d.root;
+    a.scale = d.scale;
+    a.useScale = d.useScale ? 1 : 0;
+    a.elemSize = DtypeSize(d.dtype);
+    a.p2pOffset = c->p2pOffset;
+    a.p2pSlotBytes = c->p2pSlotBytes;
+}
+
+HcclResult Launch(Comm *c, int kind, CollArgs &a, int ctas, Stream stream)
+{
+    FastLaunch l;
+    memset(&l, 0, sizeof(l));
+    l.kind = kind;
+    a.preBarrier = (c->lastOpOnHost && kind != FK_SEND && kind != FK_RECV) ? 1 : 0;
+    l.args = a;
+    l.ctas = ctas;
+    l.threads = 512;
+    l.stream = stream;
+    HcclResult r = LaunchForRank(c, l);
+    if (r == HCCL_SUCCESS && kind != FK_SEND && kind != FK_RECV) c->lastOpOnHost = false;
+    return r;
+}
+
+uint64_t AlignDownElems(uint64_t elems, uint32_t esz)
+{
+    uint64_t q = esz >= 16 ? 1 : 16 / esz;
+    return elems / q * q;
+}
+
+// -------------------------------------------------------------------------- fast-kernel drivers
+
+HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    int kind = sel.engine == Engine::NVLS ? FK_ALLREDUCE_NVLS : (sel.algo == Algo::MESH_ONESHOT ? FK_ALLREDUCE_ONESHOT : FK_ALLREDUCE_TWOSHOT);
+    uint64_t maxPerLaunch, oneShotCap = AlignDownElems(c->halfBytes / n / esz, esz);
+    if (kind == FK_ALLREDUCE_ONESHOT && d.count > oneShotCap) kind = FK_ALLREDUCE_TWOSHOT;
+    if (kind == FK_ALLREDUCE_ONESHOT) maxPerLaunch = oneShotCap;
+    else if (kind == FK_ALLREDUCE_TWOSHOT) maxPerLaunch = AlignDownElems(c->halfBytes / (n + 1) / esz, esz) * n;
+    else maxPerLaunch = AlignDownElems(c->halfBytes / esz, esz);
+    for (uint64_t off = 0; off < d.count; off += maxPerLaunch) {
+        uint64_t cnt = std::min(maxPerLaunch, d.count - off);
+        a.in = (const char *)d.in + off * esz;
+        a.out = (char *)d.out + off * esz;
+        a.count = cnt;
+        a.sliceElems = kind == FK_ALLREDUCE_ONESHOT ? oneShotCap : AlignedSliceCount(cnt, n, esz);
+        uint64_t perRank = kind == FK_ALLREDUCE_ONESHOT ? cnt * esz : cnt * esz / n * 2;
+        CHK_RET(Launch(c, kind, a, PickCtas(c, sel, perRank), d.stream));
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult FastReduce(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    uint64_t maxPerLaunch = AlignDownElems(c->halfBytes / (n + 1) / esz, esz) * n;
+    for (uint64_t off = 0; off < d.count; off += maxPerLaunch) {
+        uint64_t cnt = std::min(maxPerLaunch, d.count - off);
+        a.in = (const char *)d.in + off * esz;
+        a.out = d.out ? (char *)d.out + off * esz : nullptr;
+        a.count = cnt;
+        a.sliceElems = AlignedSliceCount(cnt, n, esz);
+        CHK_RET(Launch(c, FK_REDUCE, a, PickCtas(c, sel, cnt * esz / n), d.stream));
+    }
+    return HCCL_SUCCESS;
+}
+
+// ReduceScatter and its V form: block q = sendCounts[q] elements at sendDispls[q].
+HcclResult FastReduceScatter(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    std::vector<uint64_t> cnt(n), dsp(n);
+    uint64_t maxCnt = 0;
+    for (uint32_t q = 0; q < n; ++q) {
+        cnt[q] = d.sendCounts.empty() ? d.count : d.sendCounts[q];
+        dsp[q] = d.sendCounts.empty() ? (uint64_t)q * d.count : d.sendDispls[q];
+        maxCnt = std::max(maxCnt, cnt[q]);
+    }
+    uint64_t cap = AlignDownElems(c->halfBytes / n / esz, esz);
+    a.sliceElems = cap;
+    a.in = d.in;
+    for (uint64_t c0 = 0; c0 < maxCnt; c0 += cap) {
+        for (uint32_t q = 0; q < n; ++q) {
+            uint64_t hi = std::min(cnt[q], c0 + cap);
+            a.sendCounts[q] = hi > c0 ? hi - c0 : 0;
+            a.sendDispls[q] = dsp[q] + c0;
+        }
+        a.out = (char *)d.out + c0 * esz;
+        CHK_RET(Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz), d.stream));
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult FastAllGather(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    std::vector<uint64_t> cnt(n), dsp(n);
+    uint64_t maxCnt = 0;
+    for (uint32_t q = 0; q < n; ++q) {
+        cnt[q] = d.recvCounts.empty() ? d.count : d.recvCounts[q];
+        dsp[q] = d.recvCounts.empty() ? (uint64_t)q * d.count : d.recvDispls[q];
+        maxCnt = std::max(maxCnt, cnt[q]);
+    }
+    uint64_t cap = AlignDownElems(c->halfBytes / esz, esz);
+    a.out = d.out;
+    for (uint64_t c0 = 0; c0 < maxCnt; c0 += cap) {
+        for (uint32_t q = 0; q < n; ++q) {
+            uint64_t hi = std::min(cnt[q], c0 + cap);
+            a.recvCounts[q] = hi > c0 ? hi - c0 : 0;
+            a.recvDispls[q] = dsp[q] + c0;
+        }
+        a.in = (const char *)d.in + c0 * esz;
+        CHK_RET(Launch(c, FK_ALLGATHER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz), d.stream));
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult FastAlltoAll(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    uint64_t maxCnt = 0;
+    for (uint32_t q = 0; q < n; ++q) {
+        a.sendCounts[q] = d.sendCounts.empty() ? d.count : d.sendCounts[q];
+        a.sendDispls[q] = d.sendCounts.empty() ? (uint64_t)q * d.count : d.sendDispls[q];
+        a.recvCounts[q] = d.recvCounts.empty() ? d.count : d.recvCounts[q];
+        a.recvDispls[q] = d.recvCounts.empty() ? (uint64_t)q * d.count : d.recvDispls[q];
+        maxCnt = std::max(maxCnt, std::max(a.sendCounts[q], a.recvCounts[q]));
+    }
+    uint64_t cap = AlignDownElems(c->halfBytes / n / esz, esz);
+    a.sliceElems = cap;
+    a.in = d.in;
+    a.out = d.out;
+    a.count = maxCnt;                                  // this rank's longest block
+    a.root = d.sendCounts.empty() ? 0 : 1;             // variable counts: agree on the job-wide maximum in the kernel
+    return Launch(c, FK_ALLTOALL, a, PickCtas(c, sel, std::min(cap, maxCnt) * esz * (n - 1)), d.stream);
+}
+
+HcclResult FastBroadcast(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    int kind = sel.engine == Engine::NVLS ? FK_BROADCAST_NVLS : (sel.algo == Algo::MESH_ONESHOT ? FK_BROADCAST_PUSH : FK_BROADCAST_TWOSHOT);
+    uint64_t cap = AlignDownElems(c->halfBytes / esz, esz);
+    for (uint64_t off = 0; off < d.count; off += cap) {
+        uint64_t cnt = std::min(cap, d.count - off);
+        a.in = (const char *)d.in + off * esz;
+        a.out = (char *)d.out + off * esz;
+        a.count = cnt;
+        a.sliceElems = AlignedSliceCount(cnt, n, esz);
+        CHK_RET(Launch(c, kind, a, PickCtas(c, sel, cnt * esz), d.stream));
+    }
+    return HCCL_SUCCESS;
+}
+
+HcclResult FastScatterGather(Comm *c, const OpDesc &d, const Selection &sel, bool scatter)
+{
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    uint64_t cap = AlignDownElems(c->halfBytes / (scatter ? 1 : n) / esz, esz);
+    if (d.count > cap) {
+        RPT_ERR("EI0003", "%s of %llu elements per rank exceeds what one CCL half holds (%llu); raise HCCL_BUFFSIZE", scatter ? "scatter" : "gather",
+                (unsigned long long)d.count, (unsigned long long)cap);
+        return HCCL_E_MEMORY;
+    }
+    a.in = d.in; a.out = d.out; a.count = d.count; a.sliceElems = cap;
+    return Launch(c, scatter ? FK_SCATTER : FK_GATHER, a, PickCtas(c, sel, d.count * esz), d.stream);
+}
+
+HcclResult FastSendRecv(Comm *c, const OpDesc &d, bool send, Stream stream)
+{
+    if (c->emuSameDevice) {
+        RPT_ERR("EI0003", "send/recv kernels of two ranks cannot share one GPU; use one GPU per rank or the simulator");
+        return HCCL_E_NOT_SUPPORT;
+    }
+    const uint32_t esz = DtypeSize(d.dtype);
+    CollArgs a;
+    FillBase(c, d, a);
+    a.peer = (int32_t)d.peer;
+    a.count = d.count;
+    uint64_t bytes = d.count * esz, sub = c->p2pSlotBytes / 2, chunks = (bytes + sub - 1) / sub;
+    if (send) { a.in = d.in; a.p2pDataBase = c->p2pSent[d.peer]; c->p2pSent[d.peer] += chunks; }
+    else { a.out = d.out; a.p2pDataBase = c->p2pRecvd[d.peer]; c->p2pRecvd[d.peer] += chunks; }
+    int ctas = (int)std::min<uint64_t>(16, std::max<uint64_t>(1, bytes >> 18));
+    return Launch(c, send ? FK_SEND : FK_RECV, a, ctas, stream);
+}
+
+// ------------------------------------------------------------------------------- host drivers
+
+HcclResult HostCollective(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    CollShape sh;
+    sh.cmd = d.cmd;
+    sh.nRanks = c->nRanks;
+    sh.root = d.root;
+    sh.count = d.count;
+    sh.elemSize = DtypeSize(d.dtype);
+    sh.onlyRank = (int)c->rank;
+    std::string key;
+    bool cacheable = d.sendCounts.empty() && d.recvCounts.empty();
+    switch (d.cmd) {
+        case HCCL_CMD_REDUCE_SCATTER_V:
+            sh.sendCounts = {d.sendCounts}; sh.sendDispls = {d.sendDispls};
+            break;
+        case HCCL_CMD_ALLGATHER_V:
+            sh.recvCounts = {d.recvCounts}; sh.recvDispls = {d.recvDispls};
+            break;
+        case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC:
+            sh.sendCounts.assign(c->nRanks, {}); sh.sendDispls.assign(c->nRanks, {});
+            sh.recvCounts.assign(c->nRanks, {}); sh.recvDispls.assign(c->nRanks, {});
+            sh.sendCounts[c->rank] = d.sendCounts; sh.sendDispls[c->rank] = d.sendDispls;
+            sh.recvCounts[c->rank] = d.recvCounts; sh.recvDispls[c->rank] = d.recvDispls;
+            break;
+        case HCCL_CMD_SEND: sh.p2pSrc = c->rank; sh.p2pDst = d.peer; break;
+        case HCCL_CMD_RECEIVE: sh.p2pSrc = d.peer; sh.p2pDst = c->rank; break;
+        default: break;
+    }
+    std::shared_ptr<Schedule> sched;
+    if (cacheable) {
+        key = std::string(CmdName(d.cmd)) + "/" + AlgoName(sel.algo) + "/" + std::to_string(d.count) + "/" + std::to_string(sh.elemSize) + "/" +
+              std::to_string(d.root) + "/" + std::to_string(d.peer);
+        auto it = c->schedCache.find(key);
+        if (it != c->schedCache.end()) sched = it->second;
+    }
+    if (!sched) {
+        sched = std::make_shared<Schedule>();
+        std::string why;
+        if (!BuildSchedule(sh, sel.algo, sched.get(), &why)) {
+            RPT_ERR("EI0003", "cannot build %s with algorithm %s: %s", CmdName(d.cmd), AlgoName(sel.algo), why.c_str());
+            return HCCL_E_NOT_SUPPORT;
+        }
+        HCCL_DEBUG_CAT(CAT_ALG, "built %s: %zu primitives for rank %u", sched->name.c_str(), sched->ranks[c->rank].prims.size(), c->rank);
+        if (cacheable) {
+            if (c->schedCache.size() > 512) c->schedCache.clear();
+            c->schedCache[key] = sched;
+        }
+    }
+    // All-to-all with per-rank counts: every rank must walk the same number of passes, so the ranks agree on
+    // the longest block of the job over the control plane (the reference gathers the whole count matrix
+    // for the same reason before it stages AlltoAllV).
+    if (d.cmd == HCCL_CMD_ALLTOALLV || d.cmd == HCCL_CMD_ALLTOALLVC) {
+        uint64_t localMax = 0;
+        for (auto v : d.sendCounts) localMax = std::max(localMax, v);
+        for (auto v : d.recvCounts) localMax = std::max(localMax, v);
+        Blob mine((uint8_t *)&localMax, (uint8_t *)&localMax + 8);
+        std::vector<Blob> all;
+        CHK_RET(c->boot->AllGather(c->group, mine, &all));
+        uint64_t gmax = 0;
+        for (auto &b : all) { uint64_t v = 0; if (b.size() == 8) memcpy(&v, b.data(), 8); gmax = std::max(gmax, v); }
+        for (auto &L : sched->input) L.sliceCount = std::max(L.sliceCount, gmax);
+        for (auto &L : sched->output) L.sliceCount = std::max(L.sliceCount, gmax);
+        sched->scratch.sliceCount = std::max(sched->scratch.sliceCount, gmax);
+    }
+    ExecArgs ea;
+    ea.in = d.in; ea.out = d.out; ea.dtype = d.dtype; ea.op = d.op;
+    ea.stream = c->plat->kind() == PlatKind::SIM ? nullptr : d.stream;
+    CHK_RET(ExecuteOnHost(c, *sched, ea));
+    c->lastOpOnHost = true;
+    if (d.useScale) {
+        RPT_ERR("EI0003", "the fused scale is served by the SM kernels only");
+        return HCCL_E_NOT_SUPPORT;
+    }
+    return HCCL_SUCCESS;
+}
+
+// Batch of sends and receives executed on the host engine in three phases so that no pairing of
+// sends and receives can deadlock: announce all receives, perform all sends, complete all receives.
+HcclResult HostBatchSendRecv(Comm *c, const OpDesc &d)
+{
+    Platform *P = c->plat;
+    Stream st = P->kind() == PlatKind::SIM ? nullptr : d.stream;
+    const uint32_t n = c->nRanks;
+    const uint64_t slotBytes = (c->halfBytes / n) & ~255ull;
+    auto notify = [&](uint32_t owner, uint32_t from, uint32_t idx) {
+        return (uint64_t *)(c->PeerHeap(owner) + HC_OFF_CHAN_NOTIFY) + (uint64_t)from * HC_CHAN_NOTIFY + idx;
+    };
+    auto slot = [&](uint32_t owner, uint32_t from) { return c->PeerHeap(owner) + HC_CTRL_BYTES + (uint64_t)from * slotBytes; };
+    auto wait = [&](uint32_t peer, uint32_t idx) -> HcclResult {
+        uint64_t &w = c->chanWaited[(size_t)peer * HC_CHAN_NOTIFY + idx];
+        ++w;
+        WaitReport rep;
+        rep.status = c->waitStatus; rep.abortWord = c->abortWord; rep.rank = c->rank; rep.peer = peer; rep.kind = HC_WAIT_CHAN_NOTIFY; rep.slot = idx; rep.seq = c->opSeq;
+        return P->FlagWaitGeAsync(notify(c->rank, peer, idx), w, c->TimeoutMs(), rep, st);
+    };
+    // items between the same ordered pair are served in successive rounds
+    std::vector<uint64_t> progress(d.batch.size(), 0);
+    for (;;) {
+        std::vector<bool> sendBusy(n, false), recvBusy(n, false);
+        std::vector<size_t> round;
+        for (size_t i = 0; i < d.batch.size(); ++i) {
+            const HcclSendRecvItem &it = d.batch[i];
+            uint64_t bytes = it.count * DtypeSize(it.dataType);
+            if (progress[i] >= bytes && !(bytes == 0 && progress[i] == 0)) continue;
+            std::vector<bool> &busy = it.sendRecvType == HCCL_SEND ? sendBusy : recvBusy;
+            if (busy[it.remoteRank]) continue;
+            busy[it.remoteRank] = true;
+            round.push_back(i);
+        }
+        if (round.empty()) break;
+        for (size_t i : round)
+            if (d.batch[i].sendRecvType == HCCL_RECV) CHK_RET(P->FlagAddAsync(notify(d.batch[i].remoteRank, c->rank, N_READY), 1, st));
+        for (size_t i : round) {
+            const HcclSendRecvItem &it = d.batch[i];
+            if (it.sendRecvType != HCCL_SEND) continue;
+            uint64_t bytes = it.count * DtypeSize(it.dataType), len = std::min(slotBytes, bytes - progress[i]);
+            CHK_RET(wait(it.remoteRank, N_READY));
+            if (len) CHK_RET(P->MemcpyAsync(slot(it.remoteRank, c->rank), (char *)it.buf + progress[i], len, st));
+            CHK_RET(P->FlagAddAsync(notify(it.remoteRank, c->rank, N_DATA), 1, st));
+        }
+        for (size_t i : round) {
+            const HcclSendRecvItem &it = d.batch[i];
+            uint64_t bytes = it.count * DtypeSize(it.dataType), len = std::min(slotBytes, bytes - progress[i]);
+            if (it.sendRecvType == HCCL_RECV) {
+                CHK_RET(wait(it.remoteRank, N_DATA));
+                if (len) CHK_RET(P->MemcpyAsync((char *)it.buf + progress[i], slot(c->rank, it.remoteRank), len, st));
+            }
+            progress[i] += len;
+            if (bytes == 0) progress[i] = 1;
+        }
+    }
+    c->lastOpOnHost = true;
+    return HCCL_SUCCESS;
+}
+
+HcclResult FastBatchSendRecv(Comm *c, const OpDesc &d)
+{
+    Platform *P = c->plat;
+    while (c->auxStreams.size() < 2) {
+        Stream s;
+        CHK_RET(P->StreamCreate(&s));
+        c->auxStreams.push_back(s);
+    }
+    Stream sendSt = c->auxStreams[0], recvSt = c->auxStreams[1];
+    CHK_RET(P->StreamOrder(d.stream, sendSt));
+    CHK_RET(P->StreamOrder(d.stream, recvSt));
+    for (auto &it : d.batch) {
+        OpDesc one;
+        one.cmd = it.sendRecvType == HCCL_SEND ? HCCL_CMD_SEND : HCCL_CMD_RECEIVE;
+        one.in = it.buf; one.out = it.buf; one.count = it.count; one.dtype = it.dataType; one.peer = it.remoteRank;
+        CHK_RET(FastSendRecv(c, one, it.sendRecvType == HCCL_SEND, it.sendRecvType == HCCL_SEND ? sendSt : recvSt));
+    }
+    CHK_RET(P->StreamOrder(sendSt, d.stream));
+    CHK_RET(P->StreamOrder(recvSt, d.stream));
+    return HCCL_SUCCESS;
+}
+
+}  // namespace
+
+const AlgoConfig &AlgoConfigOf(Comm *c)
+{
+    std::lock_guard<std::mutex> lk(g_algoMu);
+    auto it = g_algoCfg.find(c->cfg.algo);
+    if (it != g_algoCfg.end()) return it->second;
+    AlgoConfig cfg;
+    std::string err;
+    if (!cfg.Parse(c->cfg.algo, &err)) {
+        HCCL_WARNING("algorithm configuration \"%s\" ignored: %s", c->cfg.algo.c_str(), err.c_str());
+        cfg.perCmd.clear();
+    }
+    return g_algoCfg[c->cfg.algo] = cfg;
+}
+
+HcclResult LaunchForRank(Comm *c, FastLaunch &l)
+{
+    if (c->emuSameDevice && c->nRanks > 1) return EmuLaunch(c->identifier + "#" + std::to_string(c->group.id), c->nRanks, c->rank, l);
+    return LaunchFastKernel(l);
+}
+
+uint64_t OpDataVolume(const Comm *c, const OpDesc &d)
+{
+    uint64_t esz = DtypeSize(d.dtype);
+    switch (d.cmd) {
+        case HCCL_CMD_ALLGATHER: case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_ALLTOALL: case HCCL_CMD_SCATTER: case HCCL_CMD_GATHER:
+            return d.count * esz * c->nRanks;
+        default: return d.count * esz;
+    }
+}
+
+bool GroupActive() { return t_groupDepth > 0; }
+
+HcclResult RunOp(Comm *c, const OpDesc &d)
+{
+    std::lock_guard<std::mutex> lk(c->opMu);
+    int st = c->state.load();
+    if (st == (int)CommState::SUSPENDING || st == (int)CommState::SUSPENDED) return HCCL_E_SUSPENDING;
+    if (st == (int)CommState::DESTROYED) return HCCL_E_PARA;
+    if (c->asyncError.load() != 0) return (HcclResult)c->asyncError.load();
+    uint64_t t0 = NowNs();
+    ++c->opSeq;
+    const bool cuda = c->plat->kind() == PlatKind::CUDA;
+    const uint32_t esz = DtypeSize(d.dtype);
+
+    SelectInput si;
+    si.cmd = d.cmd; si.nRanks = c->nRanks; si.dtype = d.dtype; si.op = d.op;
+    si.bytes = d.count * esz;
+    si.opExpansionMode = c->cfg.opExpansionMode;
+    si.deterministic = c->cfg.deterministic;
+    si.cuda = cuda;
+    si.singleDomain = c->nRanks <= HC_KERNEL_MAX_RANKS && c->graph.SingleNvlinkDomain();
+    si.nvlsAvailable = c->mcBase != nullptr;
+    si.variableCounts = !d.sendCounts.empty() || !d.recvCounts.empty();
+    Selection sel;
+    if (d.cmd == HCCL_CMD_BATCH_SEND_RECV || d.cmd == HCCL_CMD_BARRIER) {
+        bool hostOnly = !cuda || c->cfg.opExpansionMode == 1 || c->cfg.opExpansionMode == 2 || (c->emuSameDevice && d.cmd == HCCL_CMD_BATCH_SEND_RECV);
+        sel.engine = hostOnly ? Engine::HOST : Engine::SM_FAST;
+        sel.algo = d.cmd == HCCL_CMD_BARRIER ? Algo::MESH_ONESHOT : Algo::MESH;
+        sel.name = std::string(CmdName(d.cmd)) + "@" + EngineName(sel.engine);
+    } else {
+        CHK_RET(SelectAlgorithm(si, AlgoConfigOf(c), &sel));
+    }
+    if (d.useScale && sel.engine == Engine::HOST && c->nRanks > 1) {
+        // the scale is a kernel feature; on the host engines apply it as a separate pass is not offered
+        RPT_ERR("EI0003", "HcclAllReduceScaled needs the SM or NVLS engine (op expansion mode %u selects the host engine)", c->cfg.opExpansionMode);
+        return HCCL_E_NOT_SUPPORT;
+    }
+    static thread_local std::string lastLogged;
+    if (lastLogged != sel.name) {
+        HCCL_DEBUG_CAT(CAT_ALG, "%s: %llu elements of %s -> %s (%s)", CmdName(d.cmd), (unsigned long long)d.count, DtypeName(d.dtype), sel.name.c_str(), sel.reason.c_str());
+        lastLogged = sel.name;
+    }
+
+    HcclResult r = HCCL_SUCCESS;
+    if (sel.engine == Engine::SM_IR) sel.engine = Engine::HOST;   // the stream engine runs every template
+    if (sel.engine == Engine::HOST) {
+        if (cuda && c->emuSameDevice && c->nRanks > 1) {
+            RPT_ERR("EI0003", "the stream engine cannot run ranks that share one GPU; use the SM kernels or the simulator");
+            return HCCL_E_NOT_SUPPORT;
+        }
+        if (d.cmd == HCCL_CMD_BATCH_SEND_RECV) r = HostBatchSendRecv(c, d);
+        else if (d.cmd == HCCL_CMD_BARRIER) {
+            OpDesc b = d;
+            b.cmd = HCCL_CMD_ALLREDUCE; b.count = 1; b.dtype = HCCL_DATA_TYPE_FP32; b.op = HCCL_REDUCE_SUM;
+            void *scratch = c->LocalHeap() + HC_OFF_ONESIDED;   // internal one-element buffer, as the reference uses
+            b.in = scratch; b.out = (char *)scratch + 64;
+            Selection s2 = sel;
+            s2.algo = Algo::MESH_ONESHOT;
+            r = HostCollective(c, b, s2);
+        } else r = HostCollective(c, d, sel);
+        if (r == HCCL_SUCCESS && c->plat->kind() == PlatKind::SIM) r = CommPollDeviceStatus(c);
+    } else {
+        switch (d.cmd) {
+            case HCCL_CMD_ALLREDUCE: r = FastAllReduce(c, d, sel); break;
+            case HCCL_CMD_REDUCE: r = FastReduce(c, d, sel); break;
+            case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_REDUCE_SCATTER_V: r = FastReduceScatter(c, d, sel); break;
+            case HCCL_CMD_ALLGATHER: case HCCL_CMD_ALLGATHER_V: r = FastAllGather(c, d, sel); break;
+            case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: r = FastAlltoAll(c, d, sel); break;
+            case HCCL_CMD_BROADCAST: r = FastBroadcast(c, d, sel); break;
+            case HCCL_CMD_SCATTER: r = FastScatterGather(c, d, sel, true); break;
+            case HCCL_CMD_GATHER: r = FastScatterGather(c, d, sel, false); break;
+            case HCCL_CMD_SEND: r = FastSendRecv(c, d, true, d.stream); break;
+            case HCCL_CMD_RECEIVE: r = FastSendRecv(c, d, false, d.stream); break;
+            case HCCL_CMD_BATCH_SEND_RECV: r = FastBatchSendRecv(c, d); break;
+            case HCCL_CMD_BARRIER: {
+                CollArgs a;
+                FillBase(c, d, a);
+                r = Launch(c, FK_BARRIER, a, 1, d.stream);
+                break;
+            }
+            default: r = HCCL_E_NOT_SUPPORT;
+        }
+    }
+    Record(c, d, sel, t0);
+    return r;
+}
+
+void GroupQueue(std::function<HcclResult()> job, uint64_t volume, bool isP2p, Comm *c, const OpDesc *p2p)
+{
+    GroupJob j;
+    j.fn = std::move(job);
+    j.volume = volume;
+    j.p2p = isP2p;
+    j.variable = false;
+    j.comm = c;
+    if (p2p) j.desc = *p2p;
+    j.order = t_groupJobs.size();
+    t_groupJobs.push_back(std::move(j));
+}
+
+HcclResult SubmitOp(Comm *c, const OpDesc &d)
+{
+    if (GroupActive()) {
+        bool p2p = d.cmd == HCCL_CMD_SEND || d.cmd == HCCL_CMD_RECEIVE;
+        OpDesc copy = d;
+        GroupQueue([c, copy] { return RunOp(c, copy); }, OpDataVolume(c, d), p2p, c, &copy);
+        t_groupJobs.back().variable = !d.sendCounts.empty() || !d.recvCounts.empty();
+        return HCCL_SUCCESS;
+    }
+    return RunOp(c, d);
+}
+
+}  // namespace hc
+
+// -------------------------------------------------------------------------------- group C API
+
+using namespace hc;
+
+extern "C" HcclResult HcclGroupStart(void)
+{
+    ++t_groupDepth;
+    return HCCL_SUCCESS;
+}
+
+extern "C" HcclResult HcclGroupStatusGet(bool *isGroupEnabled)
+{
+    CHK_PTR_NULL(isGroupEnabled);
+    *isGroupEnabled = t_groupDepth > 0;
+    return HCCL_SUCCESS;
+}
+
+// Launch order at the outermost End (reference: framework/group/hccl_group.cc:181-230): queued
+// communicator initialisations first, then all sends/receives of a communicator fused into one batch,
+// then fixed-count collectives by descending data volume, variable-count ones last in issue order.
+extern "C" HcclResult HcclGroupEnd(void)
+{
+    if (t_groupDepth == 0) {
+        RPT_ERR("EI0003", "HcclGroupEnd without a matching HcclGroupStart");
+        return HCCL_E_PARA;
+    }
+    if (--t_groupDepth > 0) return HCCL_SUCCESS;
+    std::vector<GroupJob> jobs;
+    jobs.swap(t_groupJobs);
+    HcclResult first = HCCL_SUCCESS;
+    auto keep = [&](HcclResult r) { if (r != HCCL_SUCCESS && first == HCCL_SUCCESS) first = r; };
+    for (auto &j : jobs)
+        if (!j.comm) keep(j.fn());   // communicator bring-up jobs
+    std::map<Comm *, OpDesc> batches;
+    std::vector<Comm *> batchOrder;
+    for (auto &j : jobs) {
+        if (!j.comm || !j.p2p) continue;
+        if (!batches.count(j.comm)) {
+            batchOrder.push_back(j.comm);
+            batches[j.comm].cmd = HCCL_CMD_BATCH_SEND_RECV;
+            batches[j.comm].stream = j.desc.stream;
+        }
+        HcclSendRecvItem it;
+        it.sendRecvType = j.desc.cmd == HCCL_CMD_SEND ? HCCL_SEND : HCCL_RECV;
+        it.buf = j.desc.cmd == HCCL_CMD_SEND ? const_cast<void *>(j.desc.in) : j.desc.out;
+        it.count = j.desc.count;
+        it.dataType = j.desc.dtype;
+        it.remoteRank = j.desc.peer;
+        batches[j.comm].batch.push_back(it);
+    }
+    for (Comm *c : batchOrder) keep(RunOp(c, batches[c]));
+    std::vector<GroupJob *> fixed, variable;
+    for (auto &j : jobs) {
+        if (!j.comm || j.p2p) continue;
+        (j.variable ? variable : fixed).push_back(&j);
+    }
+    std::stable_sort(fixed.begin(), fixed.end(), [](const GroupJob *a, const GroupJob *b) { return a->volume > b->volume; });
+    for (auto *j : fixed) keep(j->fn());
+    for (auto *j : variable) keep(j->fn());
+    return first;
+}

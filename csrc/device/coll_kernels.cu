@@ -1,0 +1,645 @@
+// coll_kernels.cu - the specialised collective kernels of the SM and NVLS engines (sm_100a).
+//
+// Design (all kernels):
+//   * CTA b of rank r only ever depends on CTA b of the other ranks: data is partitioned among CTAs
+//     by interleaved 16-byte vectors with the same (gridDim, blockDim) on every rank, and phases are
+//     separated by CrossRankBarrier between same-index CTAs.  CTAs therefore pipeline naturally:
+//     one CTA may be gathering while another still reduces.
+//   * Staging lives in this operator's half of the CCL buffer (launch parity), every kernel contains
+//     at least one barrier that all ranks wait on, so a rank can be at most one operator ahead of a
+//     peer and never overwrites staging that is still being read.
+//   * Traffic pattern: "push" (remote stores, posted, one NVLink traversal) for scatter phases,
+//     "pull" (remote loads straight into the caller's output) for gather phases, so neither input
+//     nor output has to be registered and no extra copy pass over HBM is needed.
+//   * Reductions add the ranks' contributions in ascending rank order with fp32 accumulation for
+//     16-bit floats: every rank computes bit-identical results and results do not depend on timing
+//     (what the reference calls deterministic mode, aiv_all_reduce_deter_910b_*.h).
+//   * A scale factor and the narrowing cast are applied in the reduce phase (fused scale/cast).
+//
+// Kernel inventory and the reference kernels they replace (alg_aiv_template/...):
+//   AllReduceOneShot    aiv_all_reduce_910b_smalldata.h, A5 aiv_all_reduce_mesh_1d_oneshot.h
+//   AllReduceTwoShot    aiv_all_reduce_910b_middata.h / bigdata.h, A5 mesh_1D_twoshot
+//   AllReduceNvls       (no AIV analogue; replaces the CCU in-fabric reduce programs)
+//   ReduceScatter(V)    aiv_reduce_scatter_910b_{small,mid,big}data.h, aiv_reduce_scatter_v_910b_*.h
+//   AllGather(V)        aiv_all_gather_910b_{small,big}data.h, aiv_all_gather_v_910b_*.h
+//   AlltoAll(V/VC)      aiv_all_to_all_910b_smalldata.h, aiv_all_to_all_v_910b.h, ..._vc_910b_*.h
+//   Broadcast*          aiv_broadcast_910b_{small,big}data.h
+//   Reduce / Scatter / Gather   A5 aiv_reduce_mesh_1d.h, aiv_scatter_mesh_1d.h (+ gather)
+//   Send / Recv         A5 aiv_send_mesh_1D.h / aiv_recv_mesh_1D.h
+#include <cooperative_groups.h>
+#include <cuda_runtime.h>
+
+#include "../core/log.h"
+#include "coll_kernels.h"
+#include "hcomm_device.cuh"
+
+namespace hc {
+using namespace hcdev;
+
+#define HC_ARGS const CollArgs &a = (emu != nullptr) ? emu[blockIdx.y] : byval; const CommDev *d = a.dev
+
+namespace {
+
+template <typename T, bool VEC> struct Chunk;
+template <typename T> struct Chunk<T, true> {
+    static constexpr int N = 16 / sizeof(T);
+    union { uint4 v; T e[N]; };
+    __device__ __forceinline__ void Load(const char *p) { v = Ld16Volatile(p); }
+    __device__ __forceinline__ void Store(char *p) const { St16(p, v); }
+};
+template <typename T> struct Chunk<T, false> {
+    static constexpr int N = 1;
+    T e[1];
+    __device__ __forceinline__ void Load(const char *p) { e[0] = *(volatile const T *)p; }
+    __device__ __forceinline__ void Store(char *p) const { *(T *)p = e[0]; }
+};
+template <> struct Chunk<__half, false> {
+    static constexpr int N = 1;
+    __half e[1];
+    __device__ __forceinline__ void Load(const char *p) { unsigned short u = *(volatile const unsigned short *)p; e[0] = __ushort_as_half(u); }
+    __device__ __forceinline__ void Store(char *p) const { *(__half *)p = e[0]; }
+};
+template <> struct Chunk<__nv_bfloat16, false> {
+    static constexpr int N = 1;
+    __nv_bfloat16 e[1];
+    __device__ __forceinline__ void Load(const char *p) { unsigned short u = *(volatile const unsigned short *)p; e[0] = __ushort_as_bfloat16(u); }
+    __device__ __forceinline__ void Store(char *p) const { *(__nv_bfloat16 *)p = e[0]; }
+};
+
+// dst1[i] (and dst2[i] when non-null) = scale * (src[0][i] op src[1][i] op ... op src[n-1][i]) for nElems
+// elements, contributions combined in index order.  Grid-interleaved by chunks of Chunk::N elements.
+template <typename T, bool VEC>
+__device__ __forceinline__ void ReduceSources(const char *const *src, int n, char *dst1, char *dst2, uint64_t nElems, int op, int useScale,
+                                              float scale)
+{
+    using A = typename AccOf<T>::type;
+    using C = Chunk<T, VEC>;
+    constexpr int N = C::N;
+    const uint64_t nChunks = nElems / N;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nChunks; i += stride) {
+        const uint64_t off = i * (uint64_t)(N * sizeof(T));
+        A acc[N];
+        for (int base = 0; base < n; base += 8) {
+            C buf[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (base + k < n) buf[k].Load(src[base + k] + off);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (base + k < n) {
+                    if (base + k == 0) {
+#pragma unroll
+                        for (int j = 0; j < N; ++j) acc[j] = Widen<T>(buf[k].e[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < N; ++j) acc[j] = Combine<A>(op, acc[j], Widen<T>(buf[k].e[j]));
+                    }
+                }
+            }
+        }
+        C out;
+#pragma unroll
+        for (int j = 0; j < N; ++j) out.e[j] = Narrow<T>(useScale ? ScaleAcc<A>(acc[j], scale) : acc[j]);
+        out.Store(dst1 + off);
+        if (dst2) out.Store(dst2 + off);
+    }
+    if (VEC && blockIdx.x == 0) {   // ragged end of a vectorised range
+        for (uint64_t e = nChunks * N + threadIdx.x; e < nElems; e += blockDim.x) {
+            const uint64_t off = e * sizeof(T);
+            A acc = Widen<T>(*(volatile const T *)(src[0] + off));
+            for (int r = 1; r < n; ++r) acc = Combine<A>(op, acc, Widen<T>(*(volatile const T *)(src[r] + off)));
+            T v = Narrow<T>(useScale ? ScaleAcc<A>(acc, scale) : acc);
+            *(T *)(dst1 + off) = v;
+            if (dst2) *(T *)(dst2 + off) = v;
+        }
+    }
+}
+
+template <typename T>
+__device__ __forceinline__ void ReduceAuto(const char *const *src, int n, char *dst1, char *dst2, uint64_t nElems, int op, int useScale, float scale)
+{
+    uintptr_t bits = (uintptr_t)dst1 | (uintptr_t)dst2;
+    for (int r = 0; r < n; ++r) bits |= (uintptr_t)src[r];
+    if ((bits & 15) == 0) ReduceSources<T, true>(src, n, dst1, dst2, nElems, op, useScale, scale);
+    else ReduceSources<T, false>(src, n, dst1, dst2, nElems, op, useScale, scale);
+}
+
+// Element range of slice q when `count` elements are cut into slices of `S`.
+__device__ __forceinline__ void SliceRange(uint64_t count, uint64_t S, int q, uint64_t *beg, uint64_t *len)
+{
+    uint64_t b = (uint64_t)q * S;
+    *beg = b < count ? b : count;
+    uint64_t e = b + S < count ? b + S : count;
+    *len = e > *beg ? e - *beg : 0;
+}
+
+__device__ __forceinline__ uint32_t MaybePreBarrier(const CommDev *d, const CollArgs &a, const LaunchState &ls)
+{
+    if (!a.preBarrier) return 0;
+    CrossRankBarrier(d, ls.epoch0 + 1);
+    return 1;
+}
+
+// ------------------------------------------------------------------------------------ AllReduce
+
+// count <= sliceElems; staging: n slots of sliceElems elements.
+template <typename T>
+__global__ void __launch_bounds__(512) KAllReduceOneShot(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t bytes = a.count * sizeof(T), slotBytes = a.sliceElems * sizeof(T);
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        GridCopy(CclHalf(d, q, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in, bytes, sizeof(T));
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    const char *src[HC_KERNEL_MAX_RANKS];
+    for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in : CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes;
+    ReduceAuto<T>(src, n, (char *)a.out, nullptr, a.count, a.op, a.useScale, a.scale);
+    KernelEnd(d, ls, used);
+}
+
+// Staging: n slots + 1 result slice, each sliceElems elements; count <= n * sliceElems.
+template <typename T>
+__global__ void __launch_bounds__(512) KAllReduceTwoShot(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t S = a.sliceElems, slotBytes = S * sizeof(T);
+    uint64_t beg, len;
+    // scatter: my copy of slice q goes to slot `me` of rank q
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        SliceRange(a.count, S, q, &beg, &len);
+        GridCopy(CclHalf(d, q, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in + beg * sizeof(T), len * sizeof(T), sizeof(T));
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    // reduce my slice in rank order into the result slice and my part of the output
+    SliceRange(a.count, S, me, &beg, &len);
+    char *red = CclHalf(d, me, ls.half) + (uint64_t)n * slotBytes;
+    {
+        const char *src[HC_KERNEL_MAX_RANKS];
+        for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + beg * sizeof(T) : CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes;
+        ReduceAuto<T>(src, n, red, (char *)a.out + beg * sizeof(T), len, a.op, a.useScale, a.scale);
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    // gather: read the other result slices where they were reduced
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        SliceRange(a.count, S, q, &beg, &len);
+        GridCopy((char *)a.out + beg * sizeof(T), CclHalf(d, q, ls.half) + (uint64_t)n * slotBytes, len * sizeof(T), sizeof(T));
+    }
+    KernelEnd(d, ls, used);
+}
+
+// In-switch reduction.  count*sizeof(T) <= halfBytes; the vector lives in the symmetric half,
+// multimem.ld_reduce pulls the sum of all ranks' copies, multimem.st replicates it to all of them.
+template <typename T>
+__global__ void __launch_bounds__(512) KAllReduceNvls(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    // pad to whole 16-byte vectors: the padding bytes are whatever the half held, harmless
+    const uint64_t bytes = a.count * sizeof(T);
+    char *mine = CclHalf(d, me, ls.half);
+    GridCopy(mine, (const char *)a.in, bytes, sizeof(T));
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    {
+        const uint64_t nvec = (bytes + 15) >> 4;
+        const uint64_t per = (nvec + n - 1) / n;
+        const uint64_t v0 = per * me < nvec ? per * me : nvec, v1 = (v0 + per < nvec) ? v0 + per : nvec;
+        char *mc = d->mcBase + d->bufOffset + (uint64_t)ls.half * d->halfBytes;
+        const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+        for (uint64_t i = v0 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
+            uint4 v = Multimem<T>::LdReduceAdd(mc + (i << 4));
+            if (a.useScale) {
+                Pack<T> p; p.v = v;
+#pragma unroll
+                for (int j = 0; j < Pack<T>::N; ++j) p.e[j] = Narrow<T>(Widen<T>(p.e[j]) * a.scale);
+                v = p.v;
+            }
+            MultimemSt16(mc + (i << 4), v);
+        }
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    GridCopy((char *)a.out, mine, bytes, sizeof(T));
+    KernelEnd(d, ls, used);
+}
+
+// -------------------------------------------------------------------------------- ReduceScatter
+
+// Input: n blocks; block q has sendCounts[q] elements at sendDispls[q]; output recvCounts[me] elements.
+// Staging: n slots of sliceElems elements.
+template <typename T>
+__global__ void __launch_bounds__(512) KReduceScatter(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t slotBytes = a.sliceElems * sizeof(T);
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        GridCopy(CclHalf(d, q, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in + a.sendDispls[q] * sizeof(T), a.sendCounts[q] * sizeof(T), sizeof(T));
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    const char *src[HC_KERNEL_MAX_RANKS];
+    for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + a.sendDispls[me] * sizeof(T) : CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes;
+    ReduceAuto<T>(src, n, (char *)a.out, nullptr, a.sendCounts[me], a.op, a.useScale, a.scale);
+    KernelEnd(d, ls, used);
+}
+
+// --------------------------------------------------------------------------------------- Reduce
+
+template <typename T>
+__global__ void __launch_bounds__(512) KReduce(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t S = a.sliceElems, slotBytes = S * sizeof(T);
+    uint64_t beg, len;
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        SliceRange(a.count, S, q, &beg, &len);
+        GridCopy(CclHalf(d, q, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in + beg * sizeof(T), len * sizeof(T), sizeof(T));
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    SliceRange(a.count, S, me, &beg, &len);
+    char *red = CclHalf(d, me, ls.half) + (uint64_t)n * slotBytes;
+    {
+        const char *src[HC_KERNEL_MAX_RANKS];
+        for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + beg * sizeof(T) : CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes;
+        ReduceAuto<T>(src, n, red, me == a.root ? (char *)a.out + beg * sizeof(T) : nullptr, len, a.op, a.useScale, a.scale);
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    if (me == a.root) {
+        for (int i = 1; i < n; ++i) {
+            int q = (me + i) % n;
+            SliceRange(a.count, S, q, &beg, &len);
+            GridCopy((char *)a.out + beg * sizeof(T), CclHalf(d, q, ls.half) + (uint64_t)n * slotBytes, len * sizeof(T), sizeof(T));
+        }
+    }
+    KernelEnd(d, ls, used);
+}
+
+// ------------------------------------------------------------------------- byte-moving kernels
+
+// AllGather(V): rank r contributes sendCounts[0] elements... expressed in bytes via elemSize:
+// my block has recvCounts[me] elements and lands at recvDispls[q] of everyone's output.
+__global__ void __launch_bounds__(512) KAllGather(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t es = a.elemSize;
+    GridCopy(CclHalf(d, me, ls.half), (const char *)a.in, a.recvCounts[me] * es, a.elemSize);
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    GridCopy((char *)a.out + a.recvDispls[me] * es, (const char *)a.in, a.recvCounts[me] * es, a.elemSize);
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        GridCopy((char *)a.out + a.recvDispls[q] * es, CclHalf(d, q, ls.half), a.recvCounts[q] * es, a.elemSize);
+    }
+    KernelEnd(d, ls, used);
+}
+
+// AlltoAll(V/VC): block for rank q has sendCounts[q] elements at sendDispls[q]; block from rank r has
+// recvCounts[r] elements at recvDispls[r].  Blocks longer than a staging slot (sliceElems) travel in
+// column windows; consecutive windows alternate between the two CCL halves.  With variable counts
+// (a.root != 0) no rank knows the longest block of the job, so the ranks first agree on it in-kernel:
+// everyone publishes its own maximum (a.count) in every peer's meta slot, one barrier, take the max.
+__global__ void __launch_bounds__(512) KAlltoAll(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t es = a.elemSize, cap = a.sliceElems, slotBytes = cap * es;
+    uint64_t gmax = a.count;
+    if (a.root != 0) {
+        if ((int)threadIdx.x < n) ((volatile uint64_t *)(HcPeerHeap(d, threadIdx.x) + HC_OFF_META))[me] = a.count;
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        const volatile uint64_t *meta = (const volatile uint64_t *)(HcPeerHeap(d, me) + HC_OFF_META);
+        for (int r = 0; r < n; ++r) { uint64_t v = meta[r]; gmax = v > gmax ? v : gmax; }
+    }
+    uint32_t nWin = (uint32_t)((gmax + cap - 1) / cap);
+    if (nWin == 0) nWin = 1;
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const uint32_t half = (ls.half + w) & 1u;
+        const uint64_t col0 = (uint64_t)w * cap, col1 = col0 + cap;
+        auto window = [&](uint64_t cnt) { uint64_t hi = cnt < col1 ? cnt : col1; return hi > col0 ? hi - col0 : (uint64_t)0; };
+        for (int i = 1; i < n; ++i) {
+            int q = (me + i) % n;
+            GridCopy(CclHalf(d, q, half) + (uint64_t)me * slotBytes, (const char *)a.in + (a.sendDispls[q] + col0) * es, window(a.sendCounts[q]) * es, a.elemSize);
+        }
+        GridCopy((char *)a.out + (a.recvDispls[me] + col0) * es, (const char *)a.in + (a.sendDispls[me] + col0) * es, window(a.sendCounts[me]) * es, a.elemSize);
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        for (int i = 1; i < n; ++i) {
+            int r = (me + n - i) % n;
+            GridCopy((char *)a.out + (a.recvDispls[r] + col0) * es, CclHalf(d, me, half) + (uint64_t)r * slotBytes, window(a.recvCounts[r]) * es, a.elemSize);
+        }
+    }
+    KernelEnd(d, ls, used, nWin);
+}
+
+// Broadcast, root pushes the whole buffer to every peer's staging.
+__global__ void __launch_bounds__(512) KBroadcastPush(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t bytes = a.count * a.elemSize;
+    if (me == a.root) {
+        for (int i = 1; i < n; ++i) GridCopy(CclHalf(d, (me + i) % n, ls.half), (const char *)a.in, bytes, a.elemSize);
+        GridCopy((char *)a.out, (const char *)a.in, bytes, a.elemSize);
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    if (me != a.root) GridCopy((char *)a.out, CclHalf(d, me, ls.half), bytes, a.elemSize);
+    KernelEnd(d, ls, used);
+}
+
+// Broadcast as scatter + all-gather: the root sends slice q to rank q only; everyone then pulls
+// slice q from rank q.  The root's outbound traffic is one buffer instead of n-1.
+__global__ void __launch_bounds__(512) KBroadcastTwoShot(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t es = a.elemSize, S = a.sliceElems;
+    uint64_t beg, len;
+    if (me == a.root) {
+        for (int i = 0; i < n; ++i) {
+            int q = (me + i) % n;
+            SliceRange(a.count, S, q, &beg, &len);
+            GridCopy(CclHalf(d, q, ls.half), (const char *)a.in + beg * es, len * es, a.elemSize);
+        }
+        GridCopy((char *)a.out, (const char *)a.in, a.count * es, a.elemSize);
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    if (me != a.root) {
+        for (int i = 0; i < n; ++i) {
+            int q = (me + i) % n;
+            SliceRange(a.count, S, q, &beg, &len);
+            GridCopy((char *)a.out + beg * es, CclHalf(d, q, ls.half), len * es, a.elemSize);
+        }
+    }
+    KernelEnd(d, ls, used);
+}
+
+// Broadcast through the switch: the root stores once to the multicast alias, the switch replicates.
+__global__ void __launch_bounds__(512) KBroadcastNvls(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int me = d->rank;
+    const uint64_t bytes = a.count * a.elemSize;
+    CrossRankBarrier(d, ls.epoch0 + (++used));   // everyone has left the previous use of this half
+    if (me == a.root) {
+        char *mc = d->mcBase + d->bufOffset + (uint64_t)ls.half * d->halfBytes;
+        const char *src = (const char *)a.in;
+        const uint64_t nvec = bytes >> 4, stride = (uint64_t)gridDim.x * blockDim.x;
+        if (((uintptr_t)src & 15) == 0) {
+            for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) MultimemSt16(mc + (i << 4), Ld16(src + (i << 4)));
+            if (blockIdx.x == 0 && threadIdx.x == 0 && (bytes & 15)) {   // last partial vector: zero-padded
+                Pack<char> p; p.v = make_uint4(0, 0, 0, 0);
+                for (uint64_t b = 0; b < (bytes & 15); ++b) p.e[b] = src[(nvec << 4) + b];
+                MultimemSt16(mc + (nvec << 4), p.v);
+            }
+        } else {
+            for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < ((bytes + 15) >> 4); i += stride) {
+                Pack<char> p; p.v = make_uint4(0, 0, 0, 0);
+                for (int b = 0; b < 16; ++b) if ((i << 4) + b < bytes) p.e[b] = src[(i << 4) + b];
+                MultimemSt16(mc + (i << 4), p.v);
+            }
+        }
+        GridCopy((char *)a.out, src, bytes, a.elemSize);
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    if (me != a.root) GridCopy((char *)a.out, CclHalf(d, me, ls.half), bytes, a.elemSize);
+    KernelEnd(d, ls, used);
+}
+
+// Scatter: root's block q (count elements each) goes to rank q.
+__global__ void __launch_bounds__(512) KScatter(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t bytes = a.count * a.elemSize;
+    if (me == a.root) {
+        for (int i = 1; i < n; ++i) {
+            int q = (me + i) % n;
+            GridCopy(CclHalf(d, q, ls.half), (const char *)a.in + (uint64_t)q * bytes, bytes, a.elemSize);
+        }
+        GridCopy((char *)a.out, (const char *)a.in + (uint64_t)me * bytes, bytes, a.elemSize);
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    if (me != a.root) GridCopy((char *)a.out, CclHalf(d, me, ls.half), bytes, a.elemSize);
+    KernelEnd(d, ls, used);
+}
+
+// Gather: every rank pushes its block into slot `me` of the root.
+__global__ void __launch_bounds__(512) KGather(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t bytes = a.count * a.elemSize, slotBytes = a.sliceElems * a.elemSize;
+    if (me != a.root) GridCopy(CclHalf(d, a.root, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in, bytes, a.elemSize);
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    if (me == a.root) {
+        GridCopy((char *)a.out + (uint64_t)me * bytes, (const char *)a.in, bytes, a.elemSize);
+        for (int i = 1; i < n; ++i) {
+            int r = (me + i) % n;
+            GridCopy((char *)a.out + (uint64_t)r * bytes, CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes, bytes, a.elemSize);
+        }
+    }
+    KernelEnd(d, ls, used);
+}
+
+__global__ void __launch_bounds__(512) KBarrier(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    CrossRankBarrier(d, ls.epoch0 + 1);
+    KernelEnd(d, ls, 1);
+}
+
+// ---------------------------------------------------------------------------------- Send / Recv
+//
+// The landing area of (receiver, sender) is two sub-slots; chunk k uses sub-slot k%2.  Two 64-bit
+// counters per ordered pair live in the receiver's / sender's control region:
+//   data[receiver][sender]   chunks written so far (sender increments, release)
+//   ack [sender][receiver]   chunks consumed so far (receiver increments, release)
+// Both only grow over the life of the communicator; the host passes their values before this call.
+// These kernels involve two ranks only, so they touch neither the barrier epoch nor the CCL halves.
+
+__device__ __forceinline__ uint64_t *P2pWord(const CommDev *d, int owner, int other, int which)
+{
+    return (uint64_t *)(HcPeerHeap(d, owner) + HC_OFF_P2P) + (uint64_t)other * 8 + which;
+}
+
+__global__ void __launch_bounds__(512) KSend(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const int me = d->rank, dst = a.peer;
+    const uint64_t bytes = a.count * a.elemSize, sub = a.p2pSlotBytes / 2;
+    const uint64_t nChunks = bytes == 0 ? 0 : (bytes + sub - 1) / sub;
+    char *land = HcPeerHeap(d, dst) + a.p2pOffset + (uint64_t)me * a.p2pSlotBytes;
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    for (uint64_t k = 0; k < nChunks; ++k) {
+        const uint64_t global = a.p2pDataBase + k;            // ordinal of this chunk on the pair
+        if (global >= 2) {                                     // sub-slot reuse: chunk global-2 must be consumed
+            if (threadIdx.x == 0) WaitFlagGe64(d, P2pWord(d, me, dst, 1), global - 1, (uint32_t)dst, HC_WAIT_CHAN_NOTIFY, 1);
+            __syncthreads();
+        }
+        const uint64_t off = k * sub, len = (bytes - off < sub) ? bytes - off : sub;
+        GridCopy(land + (global & 1) * sub, (const char *)a.in + off, len, a.elemSize);
+        __threadfence_system();
+        grid.sync();
+        if (blockIdx.x == 0 && threadIdx.x == 0) RedReleaseSysAdd64(P2pWord(d, dst, me, 0), 1);
+    }
+}
+
+__global__ void __launch_bounds__(512) KRecv(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const int me = d->rank, src = a.peer;
+    const uint64_t bytes = a.count * a.elemSize, sub = a.p2pSlotBytes / 2;
+    const uint64_t nChunks = bytes == 0 ? 0 : (bytes + sub - 1) / sub;
+    const char *land = HcPeerHeap(d, me) + a.p2pOffset + (uint64_t)src * a.p2pSlotBytes;
+    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+    for (uint64_t k = 0; k < nChunks; ++k) {
+        const uint64_t global = a.p2pDataBase + k;
+        if (threadIdx.x == 0) WaitFlagGe64(d, P2pWord(d, me, src, 0), global + 1, (uint32_t)src, HC_WAIT_CHAN_NOTIFY, 0);
+        __syncthreads();
+        const uint64_t off = k * sub, len = (bytes - off < sub) ? bytes - off : sub;
+        GridCopy((char *)a.out + off, land + (global & 1) * sub, len, a.elemSize);
+        grid.sync();
+        if (blockIdx.x == 0 && threadIdx.x == 0) RedReleaseSysAdd64(P2pWord(d, src, me, 1), 1);
+    }
+}
+
+template <typename K> struct KernelOf { K fn; };
+
+template <template <typename> class Dummy = AccOf>
+void *ReduceKernelFor(int kind, int dtype)
+{
+#define HC_PICK(KERNEL)                                                                                             \
+    switch (dtype) {                                                                                                \
+        case HCCL_DATA_TYPE_FP32: return (void *)KERNEL<float>; case HCCL_DATA_TYPE_FP16: return (void *)KERNEL<__half>;                   \
+        case HCCL_DATA_TYPE_BFP16: return (void *)KERNEL<__nv_bfloat16>; case HCCL_DATA_TYPE_FP64: return (void *)KERNEL<double>;          \
+        case HCCL_DATA_TYPE_INT8: return (void *)KERNEL<int8_t>; case HCCL_DATA_TYPE_INT16: return (void *)KERNEL<int16_t>;                \
+        case HCCL_DATA_TYPE_INT32: return (void *)KERNEL<int32_t>; case HCCL_DATA_TYPE_INT64: return (void *)KERNEL<long long>;            \
+        case HCCL_DATA_TYPE_UINT8: return (void *)KERNEL<uint8_t>; case HCCL_DATA_TYPE_UINT16: return (void *)KERNEL<uint16_t>;            \
+        case HCCL_DATA_TYPE_UINT32: return (void *)KERNEL<uint32_t>; case HCCL_DATA_TYPE_UINT64: return (void *)KERNEL<unsigned long long>; \
+        default: return nullptr;                                                                                    \
+    }
+    switch (kind) {
+        case FK_ALLREDUCE_ONESHOT: HC_PICK(KAllReduceOneShot)
+        case FK_ALLREDUCE_TWOSHOT: HC_PICK(KAllReduceTwoShot)
+        case FK_REDUCE_SCATTER: HC_PICK(KReduceScatter)
+        case FK_REDUCE: HC_PICK(KReduce)
+        case FK_ALLREDUCE_NVLS:
+            switch (dtype) {
+                case HCCL_DATA_TYPE_FP32: return (void *)KAllReduceNvls<float>;
+                case HCCL_DATA_TYPE_FP16: return (void *)KAllReduceNvls<__half>;
+                case HCCL_DATA_TYPE_BFP16: return (void *)KAllReduceNvls<__nv_bfloat16>;
+                default: return nullptr;
+            }
+        default: return nullptr;
+    }
+#undef HC_PICK
+}
+
+void *KernelFor(int kind, int dtype)
+{
+    switch (kind) {
+        case FK_ALLGATHER: return (void *)KAllGather;
+        case FK_ALLTOALL: return (void *)KAlltoAll;
+        case FK_BROADCAST_PUSH: return (void *)KBroadcastPush;
+        case FK_BROADCAST_TWOSHOT: return (void *)KBroadcastTwoShot;
+        case FK_BROADCAST_NVLS: return (void *)KBroadcastNvls;
+        case FK_SCATTER: return (void *)KScatter;
+        case FK_GATHER: return (void *)KGather;
+        case FK_SEND: return (void *)KSend;
+        case FK_RECV: return (void *)KRecv;
+        case FK_BARRIER: return (void *)KBarrier;
+        default: return ReduceKernelFor<>(kind, dtype);
+    }
+}
+
+}  // namespace
+
+const char *FastKindName(int32_t k)
+{
+    static const char *names[] = {"AllReduceOneShot", "AllReduceTwoShot", "AllReduceNvls", "ReduceScatter", "AllGather", "AlltoAll",
+                                  "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier"};
+    return (k >= 0 && k < FK_COUNT) ? names[k] : "?";
+}
+
+uint32_t FastKindBarriers(int32_t kind, int preBarrier)
+{
+    uint32_t k = 1;
+    switch (kind) {
+        case FK_ALLREDUCE_TWOSHOT: case FK_ALLREDUCE_NVLS: case FK_REDUCE: case FK_BROADCAST_NVLS: k = 2; break;
+        case FK_SEND: case FK_RECV: return 0;
+        default: k = 1;
+    }
+    return k + (preBarrier ? 1 : 0);
+}
+
+int FastMaxCoResidentCtas(int32_t kind, int threads, int ranksOnDevice)
+{
+    void *fn = KernelFor(kind, HCCL_DATA_TYPE_FP32);
+    if (!fn) return 0;
+    int perSm = 0, dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, fn, threads, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    int total = perSm * sms;
+    return ranksOnDevice > 0 ? total / ranksOnDevice : total;
+}
+
+HcclResult LaunchFastKernel(const FastLaunch &l)
+{
+    void *fn = KernelFor(l.kind, l.args.dtype);
+    if (!fn) {
+        HCCL_ERROR("no %s kernel for data type %d", FastKindName(l.kind), l.args.dtype);
+        return HCCL_E_NOT_SUPPORT;
+    }
+    dim3 grid((unsigned)l.ctas, (unsigned)(l.emuTable ? l.emuRanks : 1), 1), block((unsigned)l.threads, 1, 1);
+    CollArgs args = l.args;
+    const CollArgs *emu = l.emuTable;
+    void *params[] = {(void *)&args, (void *)&emu};
+    cudaError_t e;
+    // Cooperative launch guarantees that all CTAs are resident at once: required whenever CTAs wait
+    // for CTAs of the same launch (shared-GPU emulation, grid.sync in send/recv).
+    bool coop = l.emuTable != nullptr || l.kind == FK_SEND || l.kind == FK_RECV;
+    if (coop) e = cudaLaunchCooperativeKernel(fn, grid, block, params, 0, (cudaStream_t)l.stream);
+    else e = cudaLaunchKernel(fn, grid, block, params, 0, (cudaStream_t)l.stream);
+    if (e != cudaSuccess) {
+        HCCL_ERROR("launch of %s (%d CTAs x %d threads, %d ranks) failed: %s", FastKindName(l.kind), l.ctas, l.threads, grid.y, cudaGetErrorString(e));
+        return HCCL_E_RUNTIME;
+    }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace hc

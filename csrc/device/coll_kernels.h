@@ -1,0 +1,78 @@
+// coll_kernels.h - host-side interface of the specialised collective kernels (engine "sm" / "nvls").
+//
+// One kernel per (collective, regime); all share the argument block below.  A launch normally has
+// gridDim.y == 1 and takes its arguments by value.  When several ranks of one process share a GPU
+// (tests on a single device) the ranks' argument blocks are placed in a device table and ONE
+// cooperative launch with gridDim.y == nRanks runs all of them, because kernels that wait on each
+// other must never be separate launches on one GPU.
+#pragma once
+#include <stdint.h>
+
+#include "comm_dev.h"
+#include "hccl/hccl_types.h"
+
+namespace hc {
+
+enum FastKind : int32_t {
+    FK_ALLREDUCE_ONESHOT = 0,
+    FK_ALLREDUCE_TWOSHOT,
+    FK_ALLREDUCE_NVLS,
+    FK_REDUCE_SCATTER,
+    FK_ALLGATHER,
+    FK_ALLTOALL,
+    FK_BROADCAST_PUSH,
+    FK_BROADCAST_TWOSHOT,
+    FK_BROADCAST_NVLS,
+    FK_REDUCE,
+    FK_SCATTER,
+    FK_GATHER,
+    FK_SEND,
+    FK_RECV,
+    FK_BARRIER,
+    FK_COUNT
+};
+const char *FastKindName(int32_t k);
+
+struct CollArgs {
+    CommDev *dev;
+    const void *in;
+    void *out;
+    uint64_t count;          // elements; meaning depends on the collective (see coll_kernels.cu)
+    uint64_t sliceElems;     // elements per slot / slice (host-computed, 16-byte multiple)
+    int32_t dtype;
+    int32_t op;
+    int32_t root;
+    int32_t peer;            // send / recv partner
+    float scale;             // applied to the reduced value when useScale != 0
+    int32_t useScale;
+    int32_t preBarrier;      // 1: synchronise all ranks before touching peer memory
+    uint32_t elemSize;
+    // variable-count collectives (elements); unused entries are zero
+    uint64_t sendCounts[HC_KERNEL_MAX_RANKS], sendDispls[HC_KERNEL_MAX_RANKS];
+    uint64_t recvCounts[HC_KERNEL_MAX_RANKS], recvDispls[HC_KERNEL_MAX_RANKS];
+    uint64_t col0, col1;     // column window of this launch for chunked all-to-all style ops
+    // point-to-point bookkeeping (values before this operator)
+    uint64_t p2pDataBase, p2pAckBase;
+    uint64_t p2pOffset;      // offset of the point-to-point landing area in the heap
+    uint64_t p2pSlotBytes;   // bytes per source rank in that area (two sub-slots)
+};
+
+struct FastLaunch {
+    int32_t kind;
+    CollArgs args;
+    int ctas;                // CTAs per rank
+    int threads;
+    void *stream;
+    // shared-GPU emulation
+    const CollArgs *emuTable;   // device pointer to nRanks argument blocks, or NULL
+    int emuRanks;
+};
+
+// Returns HCCL_E_NOT_SUPPORT for a (kind, dtype) pair without a kernel.
+HcclResult LaunchFastKernel(const FastLaunch &l);
+// Barriers a kernel of this kind consumes (the epoch advance), so callers can reason about it.
+uint32_t FastKindBarriers(int32_t kind, int preBarrier);
+// Upper bound of CTAs per rank for which all CTAs of `ranksOnDevice` ranks are co-resident.
+int FastMaxCoResidentCtas(int32_t kind, int threads, int ranksOnDevice);
+
+}  // namespace hc

@@ -1,0 +1,270 @@
+// hcomm_device.cuh - device-side primitive library of the SM engine.
+//
+// These are the __device__ forms of the verbs in hcomm_primitives.h, written against peer pointers
+// into the symmetric heap: system-scope release/acquire flag accesses, bounded waits that record
+// where they gave up instead of hanging, a cross-rank barrier between same-index CTAs, vectorised
+// copy / reduce loops, and the NVLS multimem wrappers.  Every collective kernel, the schedule
+// interpreter and the fused GEMM kernels are built from them.
+//
+// Reference counterpart: the AscendC base class of the AIV kernels
+// (algorithm/base/alg_aiv_template/aiv_communication_base.h:696-1137: CpGM2GM, Record/Wait,
+// Record1vN/WaitNv1, head/tail counters) - with the difference that no wait here is unbounded.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "comm_dev.h"
+#include "hccl/hccl_types.h"
+
+namespace hcdev {
+
+// ------------------------------------------------------------------------------ flag accesses
+
+__device__ __forceinline__ void StReleaseSys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t LdAcquireSys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void StReleaseSys64(uint64_t *p, uint64_t v)
+{
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t LdAcquireSys64(const uint64_t *p)
+{
+    uint64_t v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void RedReleaseSysAdd64(uint64_t *p, uint64_t v)
+{
+    asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t GlobalTimerNs()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool Aborted(const CommDev *d) { return *(volatile uint32_t *)d->abortWord != 0; }
+
+// Records the first expired wait of the communicator and raises the abort word.
+__device__ __noinline__ void ReportTimeout(const CommDev *d, uint32_t peer, uint32_t kind, uint32_t slot, uint64_t expected,
+                                           uint64_t seen)
+{
+    if (atomicExch_system(&d->status->valid, 1u) == 0u) {
+        d->status->rank = (uint32_t)d->rank; d->status->peer = peer; d->status->kind = kind; d->status->slot = slot;
+        d->status->block = blockIdx.x; d->status->expected = expected; d->status->seen = seen; d->status->seq = d->opCounters[0];
+    }
+    *(volatile uint32_t *)d->abortWord = 1u;
+    __threadfence_system();
+}
+
+// Spins until *flag reaches `target` (wrap-safe), the abort word is raised, or the time budget ends.
+__device__ __forceinline__ bool WaitFlagGe32(const CommDev *d, const uint32_t *flag, uint32_t target, uint32_t peer, uint32_t kind,
+                                             uint32_t slot)
+{
+    uint32_t seen = LdAcquireSys(flag);
+    if ((int32_t)(seen - target) >= 0) return true;
+    uint64_t start = GlobalTimerNs();
+    for (uint32_t it = 1;; ++it) {
+        seen = LdAcquireSys(flag);
+        if ((int32_t)(seen - target) >= 0) return true;
+        if ((it & 63) == 0) {
+            if (Aborted(d)) return false;
+            if (GlobalTimerNs() - start > d->timeoutNs) { ReportTimeout(d, peer, kind, slot, target, seen); return false; }
+        }
+    }
+}
+__device__ __forceinline__ bool WaitFlagGe64(const CommDev *d, const uint64_t *flag, uint64_t target, uint32_t peer, uint32_t kind,
+                                             uint32_t slot)
+{
+    uint64_t seen = LdAcquireSys64(flag);
+    if (seen >= target) return true;
+    uint64_t start = GlobalTimerNs();
+    for (uint32_t it = 1;; ++it) {
+        seen = LdAcquireSys64(flag);
+        if (seen >= target) return true;
+        if ((it & 63) == 0) {
+            if (Aborted(d)) return false;
+            if (GlobalTimerNs() - start > d->timeoutNs) { ReportTimeout(d, peer, kind, slot, target, seen); return false; }
+        }
+    }
+}
+
+// Barrier between CTA `blockIdx.x` of every rank.  Writes issued by any thread of the CTA before the
+// call are visible to the peers' CTAs after they leave it (bar.sync orders them before the
+// signalling threads' system-scope release stores).
+__device__ __forceinline__ void CrossRankBarrier(const CommDev *d, uint32_t epoch)
+{
+    __syncthreads();
+    const int t = threadIdx.x;
+    if (t < d->nRanks) {
+        uint32_t *theirs = (uint32_t *)(HcPeerHeap(d, t) + HC_OFF_BARRIER) + (uint64_t)blockIdx.x * HC_MAX_RANKS + d->rank;
+        StReleaseSys(theirs, epoch);
+        const uint32_t *mine = (const uint32_t *)(HcPeerHeap(d, d->rank) + HC_OFF_BARRIER) + (uint64_t)blockIdx.x * HC_MAX_RANKS + t;
+        WaitFlagGe32(d, mine, epoch, (uint32_t)t, HC_WAIT_BARRIER, blockIdx.x);
+    }
+    __syncthreads();
+}
+
+// Kernel prologue / epilogue: read the epoch and CCL half, count the launch when the last CTA ends.
+struct LaunchState {
+    uint32_t epoch0;
+    uint32_t half;
+};
+__device__ __forceinline__ LaunchState KernelBegin(const CommDev *d)
+{
+    LaunchState s;
+    s.epoch0 = *(volatile uint32_t *)d->epoch;
+    s.half = *(volatile uint32_t *)d->launches & 1u;
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd_system((unsigned long long *)&d->opCounters[0], 1ull);
+    return s;
+}
+__device__ __forceinline__ void KernelEnd(const CommDev *d, const LaunchState &s, uint32_t barriersUsed, uint32_t halvesUsed = 1)
+{
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        uint32_t done = atomicAdd(d->blocksDone, 1u);
+        if (done == gridDim.x - 1) {
+            *(volatile uint32_t *)d->epoch = s.epoch0 + barriersUsed;
+            *(volatile uint32_t *)d->launches = *(volatile uint32_t *)d->launches + halvesUsed;
+            *(volatile uint32_t *)d->blocksDone = 0u;
+            __threadfence();
+            atomicAdd_system((unsigned long long *)&d->opCounters[1], 1ull);
+        }
+    }
+}
+__device__ __forceinline__ char *CclHalf(const CommDev *d, int rank, uint32_t half)
+{
+    return HcPeerHeap(d, rank) + d->bufOffset + (uint64_t)half * d->halfBytes;
+}
+
+// ----------------------------------------------------------------------------- element algebra
+
+template <typename T> struct AccOf { using type = T; };
+template <> struct AccOf<__half> { using type = float; };
+template <> struct AccOf<__nv_bfloat16> { using type = float; };
+
+template <typename A> __device__ __forceinline__ A Combine(int op, A a, A b)
+{
+    switch (op) {
+        case HCCL_REDUCE_SUM: return a + b;
+        case HCCL_REDUCE_PROD: return a * b;
+        case HCCL_REDUCE_MAX: return a > b ? a : b;
+        default: return a < b ? a : b;
+    }
+}
+template <typename T> __device__ __forceinline__ typename AccOf<T>::type Widen(T v) { return (typename AccOf<T>::type)v; }
+template <> __device__ __forceinline__ float Widen<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float Widen<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T Narrow(typename AccOf<T>::type v) { return (T)v; }
+template <> __device__ __forceinline__ __half Narrow<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 Narrow<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <typename A> __device__ __forceinline__ A ScaleAcc(A a, float) { return a; }
+template <> __device__ __forceinline__ float ScaleAcc<float>(float a, float s) { return a * s; }
+template <> __device__ __forceinline__ double ScaleAcc<double>(double a, float s) { return a * (double)s; }
+
+// 16 bytes of T.
+template <typename T> struct Pack {
+    static constexpr int N = 16 / sizeof(T);
+    union { uint4 v; T e[N]; };
+};
+
+__device__ __forceinline__ uint4 Ld16(const void *p) { return *(const uint4 *)p; }
+__device__ __forceinline__ void St16(void *p, uint4 v) { *(uint4 *)p = v; }
+// Loads that bypass L1: data written by another GPU must not be served from a stale line.
+__device__ __forceinline__ uint4 Ld16Volatile(const void *p)
+{
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Copies n bytes dst <- src with all CTAs of the grid taking interleaved 16-byte vectors.  Both
+// pointers must be 16-byte aligned; the (n % 16) tail is moved bytewise by CTA 0.
+__device__ __forceinline__ void GridCopy16(char *dst, const char *src, uint64_t n)
+{
+    const uint64_t nvec = n >> 4;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+        uint4 a = Ld16Volatile(src + (i << 4)), b = Ld16Volatile(src + ((i + stride) << 4));
+        uint4 c = Ld16Volatile(src + ((i + 2 * stride) << 4)), e = Ld16Volatile(src + ((i + 3 * stride) << 4));
+        St16(dst + (i << 4), a); St16(dst + ((i + stride) << 4), b);
+        St16(dst + ((i + 2 * stride) << 4), c); St16(dst + ((i + 3 * stride) << 4), e);
+    }
+    for (; i < nvec; i += stride) St16(dst + (i << 4), Ld16Volatile(src + (i << 4)));
+    if (blockIdx.x == 0) {
+        const uint64_t tail0 = nvec << 4;
+        for (uint64_t b = tail0 + threadIdx.x; b < n; b += blockDim.x) dst[b] = *(volatile const char *)(src + b);
+    }
+}
+// Same partition, any alignment: moves elements of `esz` bytes (1, 2, 4 or 8).
+__device__ __forceinline__ void GridCopyElems(char *dst, const char *src, uint64_t n, uint32_t esz)
+{
+    const uint64_t cnt = n / esz;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < cnt; i += stride) {
+        switch (esz) {
+            case 8: ((uint64_t *)dst)[i] = ((volatile const uint64_t *)src)[i]; break;
+            case 4: ((uint32_t *)dst)[i] = ((volatile const uint32_t *)src)[i]; break;
+            case 2: ((uint16_t *)dst)[i] = ((volatile const uint16_t *)src)[i]; break;
+            default: dst[i] = ((volatile const char *)src)[i]; break;
+        }
+    }
+}
+// Picks the widest legal path.
+__device__ __forceinline__ void GridCopy(char *dst, const char *src, uint64_t n, uint32_t esz)
+{
+    if (n == 0 || dst == src) return;
+    if ((((uintptr_t)dst | (uintptr_t)src) & 15) == 0) GridCopy16(dst, src, n);
+    else {
+        uint32_t w = esz;
+        while (w < 8 && ((((uintptr_t)dst | (uintptr_t)src | n) & (2 * w - 1)) == 0)) w *= 2;
+        GridCopyElems(dst, src, n, w);
+    }
+}
+
+// ------------------------------------------------------------------------------ NVLS multimem
+
+template <typename T> struct Multimem;
+template <> struct Multimem<float> {
+    __device__ static __forceinline__ uint4 LdReduceAdd(const void *mc)
+    {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+template <> struct Multimem<__nv_bfloat16> {
+    __device__ static __forceinline__ uint4 LdReduceAdd(const void *mc)
+    {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+template <> struct Multimem<__half> {
+    __device__ static __forceinline__ uint4 LdReduceAdd(const void *mc)
+    {
+        uint4 v;
+        asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+                     : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+        return v;
+    }
+};
+__device__ __forceinline__ void MultimemSt16(void *mc, uint4 v)
+{
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+}  // namespace hcdev

@@ -1,0 +1,167 @@
+"""In-tree build of the native parts.
+
+Produces, under ``hcomm_b200/lib``:
+
+* ``libhcomm.so``  - the communication library (C ABI of ``include/``): host runtime compiled with
+  g++, every ``.cu`` compiled by nvcc for ``sm_100a`` only, CUDA runtime linked statically, no link
+  against libcuda (driver entry points are resolved at run time) so the library also loads on a host
+  without a GPU, where only the simulator platform is available.
+* ``_hcomm_torch.so`` - the PyTorch extension (c10d backend and the fused operators), built on demand
+  by :func:`build_torch_extension`.
+
+Objects are cached in ``build/`` and recompiled when a source or any header is newer.
+Run ``python -m hcomm_b200.build`` to build everything.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+CSRC = ROOT / "csrc"
+INCLUDE = ROOT / "include"
+BUILD = ROOT / "build"
+LIBDIR = ROOT / "hcomm_b200" / "lib"
+CUDA_HOME = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda"))
+NVCC = str(CUDA_HOME / "bin" / "nvcc")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+CXX_FLAGS = ["-std=c++17", "-O2", "-fPIC", "-Wall", "-Wno-unused-function", "-fvisibility=default",
+             f"-I{INCLUDE}", f"-I{CUDA_HOME / 'include'}", "-pthread"]
+NVCC_FLAGS = ARCH_FLAGS + ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", f"-I{INCLUDE}",
+                           "--expt-relaxed-constexpr", "-Xcudafe", "--diag_suppress=177"]
+
+# Sources that belong to the torch extension rather than to libhcomm.so.
+TORCH_DIR = CSRC / "torch"
+
+
+def _headers_mtime() -> float:
+    newest = 0.0
+    for pattern in ("*.h", "*.cuh", "*.hpp"):
+        for base in (CSRC, INCLUDE):
+            for p in base.rglob(pattern):
+                newest = max(newest, p.stat().st_mtime)
+    return newest
+
+
+def _core_sources():
+    srcs = []
+    for p in sorted(CSRC.rglob("*.cc")) + sorted(CSRC.rglob("*.cu")):
+        if TORCH_DIR in p.parents:
+            continue
+        srcs.append(p)
+    return srcs
+
+
+def _obj_for(src: Path) -> Path:
+    rel = src.relative_to(CSRC)
+    return BUILD / "obj" / (str(rel).replace("/", "__") + ".o")
+
+
+def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=()) -> Path:
+    obj = _obj_for(src)
+    obj.parent.mkdir(parents=True, exist_ok=True)
+    if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_mtime):
+        return obj
+    if src.suffix == ".cu":
+        cmd = [NVCC, *NVCC_FLAGS, *extra_nvcc, "-c", str(src), "-o", str(obj)]
+    else:
+        cmd = ["g++", *CXX_FLAGS, "-c", str(src), "-o", str(obj)]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"compiling {src} failed:\n{res.stdout}\n{res.stderr}")
+    if verbose and res.stderr.strip():
+        print(res.stderr, file=sys.stderr)
+    return obj
+
+
+def build_core(verbose: bool = False, jobs: int | None = None) -> Path:
+    """Builds ``libhcomm.so`` and returns its path."""
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    out = LIBDIR / "libhcomm.so"
+    srcs = _core_sources()
+    hdr = _headers_mtime()
+    jobs = jobs or min(8, os.cpu_count() or 4)
+    with ThreadPoolExecutor(max_workers=jobs) as ex:
+        objs = list(ex.map(lambda s: _compile(s, hdr, verbose), srcs))
+    newest_obj = max(o.stat().st_mtime for o in objs)
+    if out.exists() and out.stat().st_mtime >= newest_obj:
+        return out
+    link = ["g++", "-shared", "-o", str(out), *map(str, objs), f"-L{CUDA_HOME / 'lib64'}", "-lcudart_static",
+            "-lpthread", "-ldl", "-lrt", "-Wl,--no-undefined"]
+    if verbose:
+        print(" ".join(link), flush=True)
+    res = subprocess.run(link, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"linking libhcomm.so failed:\n{res.stdout}\n{res.stderr}")
+    return out
+
+
+def build_torch_extension(verbose: bool = False) -> Path:
+    """Builds the PyTorch extension against the installed torch and links it to libhcomm.so."""
+    import torch
+    from torch.utils import cpp_extension as ce
+
+    core = build_core(verbose)
+    out = LIBDIR / "_hcomm_torch.so"
+    srcs = sorted(TORCH_DIR.glob("*.cpp")) + sorted(TORCH_DIR.glob("*.cu"))
+    if not srcs:
+        raise RuntimeError("no sources under csrc/torch")
+    hdr = _headers_mtime()
+    newest = max([s.stat().st_mtime for s in srcs] + [hdr, core.stat().st_mtime])
+    if out.exists() and out.stat().st_mtime >= newest:
+        return out
+    inc = [f"-I{p}" for p in ce.include_paths(device_type="cuda")] + [f"-I{INCLUDE}", f"-I{CSRC}"]
+    import sysconfig
+    inc.append(f"-I{sysconfig.get_paths()['include']}")
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    common = [f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_hcomm_torch", "-DTORCH_API_INCLUDE_EXTENSION_H"]
+    objs = []
+
+    def one(src: Path) -> Path:
+        obj = BUILD / "obj_torch" / (src.name + ".o")
+        obj.parent.mkdir(parents=True, exist_ok=True)
+        if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr):
+            return obj
+        if src.suffix == ".cu":
+            cmd = [NVCC, *ARCH_FLAGS, "-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC",
+                   *inc, *common, "-c", str(src), "-o", str(obj)]
+        else:
+            cmd = ["g++", "-std=c++17", "-O2", "-fPIC", *inc, *common, "-c", str(src), "-o", str(obj)]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"compiling {src} failed:\n{res.stdout[-4000:]}\n{res.stderr[-8000:]}")
+        return obj
+
+    with ThreadPoolExecutor(max_workers=4) as ex:
+        objs = list(ex.map(one, srcs))
+    torch_lib = Path(torch.__file__).parent / "lib"
+    link = ["g++", "-shared", "-o", str(out), *map(str, objs), f"-L{LIBDIR}", "-lhcomm", f"-L{torch_lib}", "-ltorch", "-ltorch_cpu",
+            "-lc10", "-ltorch_python", f"-L{CUDA_HOME / 'lib64'}", "-lcudart_static", "-lpthread", "-ldl", "-lrt",
+            "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    if (torch_lib / "libtorch_cuda.so").exists():
+        link += ["-ltorch_cuda", "-lc10_cuda"]
+    if verbose:
+        print(" ".join(link), flush=True)
+    res = subprocess.run(link, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"linking _hcomm_torch.so failed:\n{res.stdout}\n{res.stderr}")
+    return out
+
+
+def build_all(verbose: bool = False) -> None:
+    build_core(verbose)
+    if any(TORCH_DIR.glob("*.cpp")) or any(TORCH_DIR.glob("*.cu")):
+        build_torch_extension(verbose)
+
+
+if __name__ == "__main__":
+    build_all(verbose="-v" in sys.argv)
+    print("built:", *sorted(p.name for p in LIBDIR.glob("*.so")))

@@ -1,0 +1,75 @@
+/*
+ * hcom.h - named-group ("graph mode") API used by the python `hccl` package and by frameworks
+ * that address communicators by group name (reference: pkg_inc/legacy/hccl/hcom.h:167-352).
+ * The world group is called "hccl_world_group".
+ */
+#ifndef HCOM_H_
+#define HCOM_H_
+
+#include "hccl_rank_graph.h"
+#include "hccl_types.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HCCL_WORLD_GROUP "hccl_world_group"
+
+HcclResult HcomInitByRankTable(const char *rankTable, uint32_t rankId);
+/* Adopt an existing communicator as the world group (for processes bootstrapped by root info). */
+HcclResult HcomInitByComm(HcclComm comm);
+HcclResult HcomDestroy(void);
+HcclResult HcomGetInitStatus(bool *initiated);
+HcclResult HcomCreateGroup(const char *group, uint32_t rankNum, uint32_t *rankIds);
+HcclResult HcomDestroyGroup(const char *group);
+HcclResult HcomGetCommHandleByGroup(const char *group, HcclComm *commHandle);
+HcclResult HcomGetRankSize(const char *group, uint32_t *rankSize);
+HcclResult HcomGetRankId(const char *group, uint32_t *rankId);
+HcclResult HcomGetLocalRankSize(const char *group, uint32_t *localRankSize);
+HcclResult HcomGetLocalRankId(const char *group, uint32_t *localRankId);
+HcclResult HcomGetWorldRankFromGroupRank(const char *group, uint32_t groupRank, uint32_t *worldRank);
+HcclResult HcomGetGroupRankFromWorldRank(uint32_t worldRank, const char *group, uint32_t *groupRank);
+
+/* Gradient fusion split: boundaries by gradient index, or by cumulative size percentage. */
+HcclResult HcomSetGradFusionByIndex(const char *group, uint32_t segmentNum, const uint32_t *idxList);
+HcclResult HcomSetGradFusionBySize(const char *group, uint32_t segmentNum, const float *sizeList);
+/* Resolve the stored strategy for a model with gradNum gradients of the given byte sizes into
+ * segment end indices (inclusive).  segIdx must hold gradNum entries; *segNum receives the count. */
+HcclResult HcomGetSplitStrategy(const char *group, uint32_t gradNum, const uint64_t *gradBytes, uint32_t *segIdx,
+                                uint32_t *segNum);
+
+HcclResult HcomGetInCCLbuffer(const char *group, void **buffer, uint64_t *size);
+HcclResult HcomGetOutCCLbuffer(const char *group, void **buffer, uint64_t *size);
+HcclResult HcomGetCommCCLBufferSize(const char *group, uint64_t *size);
+HcclResult HcomGetBandWidthPerNPU(uint32_t level, float *bandWidthGBs);
+HcclResult HcomGetServerNumAndDeviceNumPerServer(uint32_t *serverNum, uint32_t *deviceNumPerServer,
+                                                 uint32_t *deviceNumPerAggregation);
+HcclResult HcomGetAlgorithm(uint32_t level, char **algo);
+HcclResult HcomGetL0TopoTypeEx(const char *group, CommTopo *topoType, uint32_t flag);
+HcclResult HcomSupportDeterministicOptim(const char *group, bool *isDeterministicOptim);
+
+HcclResult HcomAllReduce(const char *tag, void *in, void *out, uint64_t count, HcclDataType dataType, HcclReduceOp op,
+                         const char *group, aclrtStream stream);
+HcclResult HcomAllGather(const char *tag, void *in, void *out, uint64_t inCount, HcclDataType dataType,
+                         const char *group, aclrtStream stream);
+HcclResult HcomReduceScatter(const char *tag, void *in, void *out, uint64_t outCount, HcclDataType dataType,
+                             HcclReduceOp op, const char *group, aclrtStream stream);
+HcclResult HcomBroadcast(const char *tag, void *ptr, uint64_t count, HcclDataType dataType, uint32_t root,
+                         const char *group, aclrtStream stream);
+HcclResult HcomReduce(const char *tag, void *in, void *out, uint64_t count, HcclDataType dataType, HcclReduceOp op,
+                      uint32_t root, const char *group, aclrtStream stream);
+HcclResult HcomSend(const char *tag, void *in, uint64_t count, HcclDataType dataType, uint32_t destRank,
+                    uint32_t srTag, const char *group, aclrtStream stream);
+HcclResult HcomReceive(const char *tag, void *out, uint64_t count, HcclDataType dataType, uint32_t srcRank,
+                       uint32_t srTag, const char *group, aclrtStream stream);
+HcclResult HcomAllToAll(const void *in, uint64_t sendCount, HcclDataType sendType, const void *out,
+                        uint64_t recvCount, HcclDataType recvType, const char *group, aclrtStream stream,
+                        const char *tag);
+HcclResult HcomAlltoAllV(const void *in, const void *sendCounts, const void *sdispls, HcclDataType sendType,
+                         const void *out, const void *recvCounts, const void *rdispls, HcclDataType recvType,
+                         const char *group, aclrtStream stream, const char *tag);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HCOM_H_ */
