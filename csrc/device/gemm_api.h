@@ -1,0 +1,17 @@
+// gemm_api.h - host entry points of the tcgen05 GEMM family.
+#pragma once
+#include <cuda.h>
+#include <stdint.h>
+
+#include "hccl/hccl_types.h"
+
+namespace hc {
+
+// Tiled, 128-byte swizzled tensor map over a row-major bf16 matrix (cols contiguous, pitch ldElems).
+HcclResult MakeTensorMap2dBf16(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ldElems, uint32_t boxRows, uint32_t boxCols);
+// C[M,N] = A[M,K] * B[N,K]^T, bf16 in / bf16 out, fp32 accumulation in tensor memory.
+HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream);
+int GemmSmCount();
+uint32_t *GemmErrorFlag();
+
+}  // namespace hc

@@ -1,0 +1,133 @@
+// gemm_sm100.cu - the plain bf16 GEMM on the tcgen05 main loop, and the host-side tensor-map helper
+// used by every kernel that loads tiles with TMA.
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "../core/log.h"
+#include "gemm_api.h"
+#include "gemm_sm100.cuh"
+
+namespace hc {
+
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encodeOnce;
+
+template <int BN>
+__global__ void __launch_bounds__(hcgemm::kThreads, 1)
+GemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16 epi)
+{
+    hcgemm::GemmMainLoop<BN>(&tmA, &tmB, shape, hcgemm::RowMajorOrder(), hcgemm::NoGate(), epi);
+}
+}  // namespace
+
+HcclResult MakeTensorMap2dBf16(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols, uint64_t ldElems, uint32_t boxRows, uint32_t boxCols)
+{
+    std::call_once(g_encodeOnce, [] {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess) g_encode = (EncodeTiledFn)fn;
+        cudaGetLastError();
+    });
+    if (!g_encode) {
+        HCCL_ERROR("cuTensorMapEncodeTiled is not available from this driver");
+        return HCCL_E_DRV;
+    }
+    if (((uintptr_t)base & 15) != 0 || (ldElems * 2) % 16 != 0) {
+        HCCL_ERROR("TMA needs a 16-byte aligned base and row pitch (base %p, pitch %llu bytes)", base, (unsigned long long)(ldElems * 2));
+        return HCCL_E_PARA;
+    }
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ldElems * 2};
+    cuuint32_t box[2] = {boxCols, boxRows};
+    cuuint32_t elemStrides[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims, strides, box, elemStrides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        HCCL_ERROR("cuTensorMapEncodeTiled failed with %d (rows %llu cols %llu ld %llu box %ux%u)", (int)r, (unsigned long long)rows,
+                   (unsigned long long)cols, (unsigned long long)ldElems, boxRows, boxCols);
+        return HCCL_E_DRV;
+    }
+    return HCCL_SUCCESS;
+}
+
+int GemmSmCount()
+{
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+uint32_t *GemmErrorFlag()
+{
+    static thread_local uint32_t *flag[16] = {nullptr};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 16) dev = 0;
+    if (!flag[dev]) {
+        cudaMalloc(&flag[dev], sizeof(uint32_t));
+        cudaMemset(flag[dev], 0, sizeof(uint32_t));
+    }
+    return flag[dev];
+}
+
+HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream)
+{
+    if (M <= 0 || N <= 0 || K <= 0) return HCCL_SUCCESS;
+    if (N % 8 != 0 || K % 8 != 0 || ((uintptr_t)C & 15) != 0 || (ldc % 8) != 0) {
+        HCCL_ERROR("GemmBf16: N, K and ldc must be multiples of 8 and C 16-byte aligned (N=%d K=%d ldc=%d)", N, K, ldc);
+        return HCCL_E_PARA;
+    }
+    const int BN = (N % 256 == 0 || N >= 2048) ? 256 : 128;
+    CUtensorMap tmA, tmB;
+    CHK_RET(MakeTensorMap2dBf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, hcgemm::kBlockM, hcgemm::kBlockK));
+    CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN, hcgemm::kBlockK));
+    hcgemm::GemmShape shape;
+    shape.M = M; shape.N = N; shape.K = K;
+    shape.tilesM = (M + hcgemm::kBlockM - 1) / hcgemm::kBlockM;
+    shape.tilesN = (N + BN - 1) / BN;
+    shape.errFlag = GemmErrorFlag();
+    hcgemm::StoreBf16 epi{(__nv_bfloat16 *)C, ldc, M, N};
+    int grid = std::min(GemmSmCount(), shape.tilesM * shape.tilesN);
+    cudaError_t e;
+    if (BN == 256) {
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(GemmBf16Kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config<256>::kSmemBytes); attr = true; }
+        GemmBf16Kernel<256><<<grid, hcgemm::kThreads, hcgemm::Config<256>::kSmemBytes, (cudaStream_t)stream>>>(tmA, tmB, shape, epi);
+    } else {
+        static bool attr = false;
+        if (!attr) { cudaFuncSetAttribute(GemmBf16Kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config<128>::kSmemBytes); attr = true; }
+        GemmBf16Kernel<128><<<grid, hcgemm::kThreads, hcgemm::Config<128>::kSmemBytes, (cudaStream_t)stream>>>(tmA, tmB, shape, epi);
+    }
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        HCCL_ERROR("GemmBf16 launch failed: %s", cudaGetErrorString(e));
+        return HCCL_E_RUNTIME;
+    }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace hc
+
+// C entry points (used from Python through ctypes).
+extern "C" int HcommGemmBf16(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream)
+{
+    return (int)hc::GemmBf16(A, B, C, M, N, K, lda, ldb, ldc, stream);
+}
+// Reads and clears the "a bounded wait expired inside a GEMM kernel" flag of the current device.
+extern "C" int HcommGemmTakeError(void)
+{
+    uint32_t v = 0, zero = 0;
+    uint32_t *f = hc::GemmErrorFlag();
+    if (cudaMemcpy(&v, f, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) cudaMemcpy(f, &zero, sizeof(zero), cudaMemcpyHostToDevice);
+    return (int)v;
+}

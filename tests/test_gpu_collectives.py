@@ -1,0 +1,131 @@
+"""The SM-engine collective kernels, several ranks sharing one GPU in one cooperative launch,
+checked against plain PyTorch fp32 (or exact integer) references."""
+import os
+
+import pytest
+import torch
+
+from helpers import run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def _make(n, **kw):
+    import hcomm_b200 as hb
+    info = hb.get_root_info()
+
+    def init(r):
+        torch.cuda.set_device(0)
+        return hb.Communicator(n, info, r, buffer_mb=kw.get("buffer_mb", 8), **{k: v for k, v in kw.items() if k != "buffer_mb"})
+    return run_ranks(n, init)
+
+
+def _destroy(comms):
+    run_ranks(len(comms), lambda r: comms[r].destroy())
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16, torch.int32])
+def test_allreduce_small_and_large(n, dtype):
+    comms = _make(n)
+    try:
+        for count in (1, 7, 1000, 65536, 1_000_003):
+            gen = torch.Generator(device="cuda").manual_seed(count)
+            if dtype.is_floating_point:
+                xs = [torch.randn(count, device="cuda", generator=gen).to(dtype) for _ in range(n)]
+            else:
+                xs = [torch.randint(-1000, 1000, (count,), device="cuda", generator=gen, dtype=dtype) for _ in range(n)]
+            outs = [torch.empty_like(x) for x in xs]
+
+            def op(r):
+                torch.cuda.set_device(0)
+                comms[r].all_reduce(xs[r], outs[r])
+                torch.cuda.synchronize()
+            run_ranks(n, op)
+            ref = sum(x.double() for x in xs)
+            for r in range(n):
+                assert torch.equal(outs[r], outs[0]), "ranks disagree"
+            if dtype.is_floating_point:
+                tol = {torch.float32: 1e-5, torch.bfloat16: 4e-2, torch.float16: 4e-3}[dtype] * (n ** 0.5) * 4
+                assert (outs[0].double() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+            else:
+                assert torch.equal(outs[0].double(), ref)
+    finally:
+        _destroy(comms)
+
+
+@pytest.mark.parametrize("n", [2, 3, 8])
+def test_reduce_scatter_allgather_alltoall_broadcast(n):
+    comms = _make(n)
+    try:
+        per = 4099
+        xs = [torch.randn(per * n, device="cuda") for _ in range(n)]
+        rs = [torch.empty(per, device="cuda") for _ in range(n)]
+        ag_in = [torch.randn(per, device="cuda").to(torch.bfloat16) for _ in range(n)]
+        ag_out = [torch.empty(per * n, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+        a2a_in = [torch.arange(per * n, device="cuda", dtype=torch.int32) + 1_000_000 * r for r in range(n)]
+        a2a_out = [torch.empty(per * n, device="cuda", dtype=torch.int32) for _ in range(n)]
+        bc = [torch.full((123457,), float(r), device="cuda") for r in range(n)]
+        red_out = [torch.empty(per * n, device="cuda") for _ in range(n)]
+
+        def op(r):
+            torch.cuda.set_device(0)
+            c = comms[r]
+            c.reduce_scatter(xs[r], rs[r])
+            c.all_gather(ag_in[r], ag_out[r])
+            c.all_to_all(a2a_in[r], a2a_out[r])
+            c.broadcast(bc[r], root=n - 1)
+            c.reduce(xs[r], red_out[r], root=0, op="max")
+            c.barrier()
+            torch.cuda.synchronize()
+        run_ranks(n, op)
+        total = sum(x.double() for x in xs)
+        for r in range(n):
+            assert (rs[r].double() - total[r * per:(r + 1) * per]).abs().max().item() < 1e-4
+            assert torch.equal(ag_out[r], torch.cat(ag_in))
+            assert torch.equal(a2a_out[r], torch.cat([a2a_in[q][r * per:(r + 1) * per] for q in range(n)]))
+            assert (bc[r] == n - 1).all()
+        assert torch.equal(red_out[0], torch.stack(xs).max(dim=0).values)
+    finally:
+        _destroy(comms)
+
+
+def test_chunked_allreduce_and_scaled(n=4):
+    comms = _make(n, buffer_mb=1)     # 1 MB halves force several launches per operator
+    try:
+        count = 3_000_001
+        xs = [torch.randn(count, device="cuda").to(torch.bfloat16) for _ in range(n)]
+        outs = [torch.empty_like(x) for x in xs]
+
+        def op(r):
+            torch.cuda.set_device(0)
+            comms[r].all_reduce_scaled(xs[r], outs[r], scale=1.0 / n)
+            torch.cuda.synchronize()
+        run_ranks(n, op)
+        ref = sum(x.float() for x in xs) / n
+        assert torch.equal(outs[1], outs[0])
+        assert (outs[0].float() - ref).abs().max().item() <= 2e-2 * max(1.0, ref.abs().max().item())
+    finally:
+        _destroy(comms)
+
+
+def test_alltoallv_variable_counts(n=4):
+    comms = _make(n)
+    try:
+        sc = [[(r * 3 + q * 5) % 7 * 1000 + 17 for q in range(n)] for r in range(n)]
+        rc = [[sc[q][r] for q in range(n)] for r in range(n)]
+        sd = [[sum(sc[r][:q]) for q in range(n)] for r in range(n)]
+        rd = [[sum(rc[r][:q]) for q in range(n)] for r in range(n)]
+        send = [torch.arange(sum(sc[r]), device="cuda", dtype=torch.float32) + 1e6 * r for r in range(n)]
+        recv = [torch.empty(sum(rc[r]), device="cuda") for r in range(n)]
+
+        def op(r):
+            torch.cuda.set_device(0)
+            comms[r].all_to_all_v(send[r], sc[r], sd[r], recv[r], rc[r], rd[r])
+            torch.cuda.synchronize()
+        run_ranks(n, op)
+        for r in range(n):
+            exp = torch.cat([send[q][sd[q][r]:sd[q][r] + sc[q][r]] for q in range(n)])
+            assert torch.equal(recv[r], exp)
+    finally:
+        _destroy(comms)
