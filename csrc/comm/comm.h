@@ -98,6 +98,12 @@ struct ChannelRes {
     std::vector<std::string> remoteTags;
     std::vector<char *> tagPtrs;
     void *devView = nullptr;
+    // where records go and where they arrive; filled from the heap for communicator channels and from
+    // exchanged descriptors for base-level channels
+    uint64_t *remoteNotify = nullptr, *localNotify = nullptr;
+    Platform *plat = nullptr;
+    int sock = -1;                   // base-level channels keep their control socket
+    std::vector<void *> importedBases;
 };
 
 enum class CommState { READY = 0, SUSPENDING = 1, SUSPENDED = 2, DESTROYED = 3 };

@@ -79,17 +79,12 @@ uint32_t TimeoutMs(const Op &op)
     return c ? c->TimeoutMs() : 1836000u;
 }
 
-uint64_t *ChanWord(ChannelRes *ch, bool remoteSide, uint32_t idx)
-{
-    Comm *c = ch->comm;
-    uint32_t owner = remoteSide ? ch->remoteRank : c->rank, from = remoteSide ? c->rank : ch->remoteRank;
-    return (uint64_t *)(c->PeerHeap(owner) + HC_OFF_CHAN_NOTIFY) + (uint64_t)from * HC_CHAN_NOTIFY + ch->notifyBase + idx;
-}
+uint64_t *ChanWord(ChannelRes *ch, bool remoteSide, uint32_t idx) { return (remoteSide ? ch->remoteNotify : ch->localNotify) + idx; }
 
 HcclResult Submit(const Op &op)
 {
     ThreadRes *t = op.thread;
-    Platform *P = t ? t->plat : (op.chan ? op.chan->comm->plat : nullptr);
+    Platform *P = t ? t->plat : (op.chan ? op.chan->plat : nullptr);
     if (!P) return HCCL_E_PTR;
     Stream s = t ? t->stream : nullptr;
     Comm *c = t && t->comm ? t->comm : (op.chan ? op.chan->comm : nullptr);
