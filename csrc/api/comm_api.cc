@@ -456,7 +456,7 @@ HcclResult HcclCommResume(HcclComm comm)
     Platform *P = c->plat;
     CHK_RET(c->boot->Barrier(c->group));            // everyone is quiescent
     CHK_RET(P->MemsetSync(c->LocalHeap(), 0, HC_CTRL_BYTES));
-    CHK_RET(P->MemsetSync(c->devCounters, 0, 64 * sizeof(uint32_t)));
+    CHK_RET(P->MemsetSync(c->devCounters, 0, 128 * sizeof(uint32_t)));
     CHK_RET(P->MemsetSync(c->devIrCounters, 0, 2ull * HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY * sizeof(uint64_t)));
     std::fill(c->chanWaited.begin(), c->chanWaited.end(), 0);
     std::fill(c->p2pSent.begin(), c->p2pSent.end(), 0);
@@ -468,6 +468,7 @@ HcclResult HcclCommResume(HcclComm comm)
     }
     c->hostLaunches = 0;
     c->lastOpOnHost = true;
+    c->fusedRsSeq = c->fusedAgSeq = 0;
     memset(c->waitStatus, 0, sizeof(HcclDeviceWaitStatus));
     __atomic_store_n(c->abortWord, 0u, __ATOMIC_RELEASE);
     c->asyncError.store(0);

@@ -433,6 +433,17 @@ HcclResult FastBatchSendRecv(Comm *c, const OpDesc &d)
 
 }  // namespace
 
+// A specialised kernel that follows a host-engine operator must not touch peer staging before every rank has
+// left that operator; fused kernels (which have no barrier of their own) call this first.
+HcclResult LaunchBarrierIfNeeded(Comm *c, void *stream)
+{
+    if (!c->lastOpOnHost || c->nRanks == 1) { c->lastOpOnHost = false; return HCCL_SUCCESS; }
+    OpDesc d;
+    CollArgs a;
+    FillBase(c, d, a);
+    return Launch(c, FK_BARRIER, a, 1, stream);
+}
+
 const AlgoConfig &AlgoConfigOf(Comm *c)
 {
     std::lock_guard<std::mutex> lk(g_algoMu);

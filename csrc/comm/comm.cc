@@ -8,6 +8,7 @@
 
 #include "../core/env.h"
 #include "../core/log.h"
+#include "../device/coll_kernels.h"
 #include "../topo/nvml_topo.h"
 
 namespace hc {
@@ -243,9 +244,9 @@ static HcclResult SetupDeviceState(Comm *c)
 {
     Platform *P = c->plat;
     void *p = nullptr;
-    CHK_RET(P->DevAlloc(64 * sizeof(uint32_t), &p));
+    CHK_RET(P->DevAlloc(128 * sizeof(uint32_t), &p));
     c->devCounters = (uint32_t *)p;
-    CHK_RET(P->MemsetSync(p, 0, 64 * sizeof(uint32_t)));
+    CHK_RET(P->MemsetSync(p, 0, 128 * sizeof(uint32_t)));
     size_t irBytes = 2ull * HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY * sizeof(uint64_t);
     CHK_RET(P->DevAlloc(irBytes, &p));
     c->devIrCounters = (uint64_t *)p;
@@ -343,6 +344,7 @@ HcclResult CommCreate(const CommInitArgs &args, Comm **out)
     c->chanWaited.assign((size_t)HC_MAX_RANKS * HC_CHAN_NOTIFY, 0);
     c->opRing.resize(256);
 
+    if (c->plat->kind() == PlatKind::CUDA) { PreloadFastKernels(); PreloadPlatformKernels(); }
     CHK_RET(SetupHeap(c.get()));
     SetupMulticast(c.get());
     CHK_RET(SetupDeviceState(c.get()));
@@ -392,6 +394,7 @@ Comm::~Comm()
         plat->VaFree(heapBase, heapStride * nRanks);
     }
     if (heapPhys.bytes) plat->PhysRelease(&heapPhys);
+    if (fusedParamRing) plat->DevFree(fusedParamRing);
     if (devStruct) plat->DevFree(devStruct);
     if (devCounters) plat->DevFree(devCounters);
     if (devIrCounters) plat->DevFree(devIrCounters);

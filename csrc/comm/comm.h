@@ -130,6 +130,9 @@ struct Comm {
     uint64_t heapStride = 0, heapBytes = 0, halfBytes = 0;
     uint64_t p2pOffset = 0, p2pSlotBytes = 0;    // landing area of the send/recv kernels: one slot per source rank
     std::vector<uint64_t> p2pSent, p2pRecvd;     // chunks exchanged so far with each peer
+    uint32_t fusedRsSeq = 0, fusedAgSeq = 0;     // calls of the fused GEMM kernels so far (arrival counters only grow)
+    void *fusedParamRing = nullptr;              // device ring of kernel parameter blocks
+    int fusedParamNext = 0;
     bool lastOpOnHost = true;                    // the next specialised kernel must start with a barrier
     PhysMem mcPhys;
     char *mcBase = nullptr;

@@ -26,7 +26,6 @@
 //   Broadcast*          aiv_broadcast_910b_{small,big}data.h
 //   Reduce / Scatter / Gather   A5 aiv_reduce_mesh_1d.h, aiv_scatter_mesh_1d.h (+ gather)
 //   Send / Recv         A5 aiv_send_mesh_1D.h / aiv_recv_mesh_1D.h
-#include <cooperative_groups.h>
 #include <cuda_runtime.h>
 
 #include "../core/log.h"
@@ -228,8 +227,11 @@ __global__ void __launch_bounds__(512) KAllReduceNvls(const __grid_constant__ Co
             }
             MultimemSt16(mc + (i << 4), v);
         }
+        // Multicast stores travel through the switch; the barrier's release by another thread of the CTA does not
+        // cover them, so every thread fences its own before the CTA signals.
+        __threadfence_system();
     }
-    CrossRankBarrier(d, ls.epoch0 + (++used));
+    CrossRankBarrierMc(d, ls.epoch0 + (++used));
     GridCopy((char *)a.out, mine, bytes, sizeof(T));
     KernelEnd(d, ls, used);
 }
@@ -426,8 +428,9 @@ __global__ void __launch_bounds__(512) KBroadcastNvls(const __grid_constant__ Co
             }
         }
         GridCopy((char *)a.out, src, bytes, a.elemSize);
+        __threadfence_system();   // multicast stores are fenced by the thread that issued them
     }
-    CrossRankBarrier(d, ls.epoch0 + (++used));
+    CrossRankBarrierMc(d, ls.epoch0 + (++used));
     if (me != a.root) GridCopy((char *)a.out, CclHalf(d, me, ls.half), bytes, a.elemSize);
     KernelEnd(d, ls, used);
 }
@@ -494,6 +497,31 @@ __device__ __forceinline__ uint64_t *P2pWord(const CommDev *d, int owner, int ot
     return (uint64_t *)(HcPeerHeap(d, owner) + HC_OFF_P2P) + (uint64_t)other * 8 + which;
 }
 
+// Chunk completion inside one kernel is tracked with a device-local counter per (direction, peer) instead of a
+// grid-wide barrier, so these kernels are ordinary launches: a send and a receive kernel of the same rank must be
+// able to run side by side (each waits for the other GPU), which cooperative launches do not promise.
+// CTAs of one kernel can be at most one chunk apart from each other (chunk k+2 reuses the sub-slot of chunk k and
+// needs its acknowledgement, which needs every CTA to have finished chunk k), so two counters per (direction, peer),
+// selected by chunk parity, are enough; the last CTA to finish a chunk resets the counter and signals the peer.
+__device__ __forceinline__ uint32_t *P2pDone(const CommDev *d, int dir, int peer, uint64_t chunk)
+{
+    return d->blocksDone + 6 + ((dir * HC_KERNEL_MAX_RANKS + peer) * 2 + (int)(chunk & 1));
+}
+
+__device__ __forceinline__ bool LastCtaOfChunk(uint32_t *counter)
+{
+    __shared__ uint32_t isLast;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        uint32_t old = atomicAdd(counter, 1u);
+        isLast = (old == gridDim.x - 1) ? 1u : 0u;
+        if (isLast) { *(volatile uint32_t *)counter = 0u; __threadfence(); }
+    }
+    __syncthreads();
+    return isLast != 0;
+}
+
 __global__ void __launch_bounds__(512) KSend(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
     HC_ARGS;
@@ -501,7 +529,6 @@ __global__ void __launch_bounds__(512) KSend(const __grid_constant__ CollArgs by
     const uint64_t bytes = a.count * a.elemSize, sub = a.p2pSlotBytes / 2;
     const uint64_t nChunks = bytes == 0 ? 0 : (bytes + sub - 1) / sub;
     char *land = HcPeerHeap(d, dst) + a.p2pOffset + (uint64_t)me * a.p2pSlotBytes;
-    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
     for (uint64_t k = 0; k < nChunks; ++k) {
         const uint64_t global = a.p2pDataBase + k;            // ordinal of this chunk on the pair
         if (global >= 2) {                                     // sub-slot reuse: chunk global-2 must be consumed
@@ -510,9 +537,7 @@ __global__ void __launch_bounds__(512) KSend(const __grid_constant__ CollArgs by
         }
         const uint64_t off = k * sub, len = (bytes - off < sub) ? bytes - off : sub;
         GridCopy(land + (global & 1) * sub, (const char *)a.in + off, len, a.elemSize);
-        __threadfence_system();
-        grid.sync();
-        if (blockIdx.x == 0 && threadIdx.x == 0) RedReleaseSysAdd64(P2pWord(d, dst, me, 0), 1);
+        if (LastCtaOfChunk(P2pDone(d, 0, dst, global)) && threadIdx.x == 0) RedReleaseSysAdd64(P2pWord(d, dst, me, 0), 1);
     }
 }
 
@@ -523,15 +548,13 @@ __global__ void __launch_bounds__(512) KRecv(const __grid_constant__ CollArgs by
     const uint64_t bytes = a.count * a.elemSize, sub = a.p2pSlotBytes / 2;
     const uint64_t nChunks = bytes == 0 ? 0 : (bytes + sub - 1) / sub;
     const char *land = HcPeerHeap(d, me) + a.p2pOffset + (uint64_t)src * a.p2pSlotBytes;
-    cooperative_groups::grid_group grid = cooperative_groups::this_grid();
     for (uint64_t k = 0; k < nChunks; ++k) {
         const uint64_t global = a.p2pDataBase + k;
         if (threadIdx.x == 0) WaitFlagGe64(d, P2pWord(d, me, src, 0), global + 1, (uint32_t)src, HC_WAIT_CHAN_NOTIFY, 0);
         __syncthreads();
         const uint64_t off = k * sub, len = (bytes - off < sub) ? bytes - off : sub;
         GridCopy((char *)a.out + off, land + (global & 1) * sub, len, a.elemSize);
-        grid.sync();
-        if (blockIdx.x == 0 && threadIdx.x == 0) RedReleaseSysAdd64(P2pWord(d, src, me, 1), 1);
+        if (LastCtaOfChunk(P2pDone(d, 1, src, global)) && threadIdx.x == 0) RedReleaseSysAdd64(P2pWord(d, src, me, 1), 1);
     }
 }
 
@@ -586,6 +609,22 @@ void *KernelFor(int kind, int dtype)
 
 }  // namespace
 
+// With lazy module loading the first launch of a kernel may have to wait for running kernels; a kernel that spins
+// on a peer which in turn waits for a not-yet-loaded kernel of this process would stall until its time budget ends.
+// Loading every kernel up front (function attributes force the load) removes that dependency.
+void PreloadFastKernels()
+{
+    static const int dtypes[] = {HCCL_DATA_TYPE_FP32, HCCL_DATA_TYPE_FP16, HCCL_DATA_TYPE_BFP16, HCCL_DATA_TYPE_FP64, HCCL_DATA_TYPE_INT8, HCCL_DATA_TYPE_INT16,
+                                 HCCL_DATA_TYPE_INT32, HCCL_DATA_TYPE_INT64, HCCL_DATA_TYPE_UINT8, HCCL_DATA_TYPE_UINT16, HCCL_DATA_TYPE_UINT32, HCCL_DATA_TYPE_UINT64};
+    for (int k = 0; k < FK_COUNT; ++k)
+        for (int dt : dtypes) {
+            void *fn = KernelFor(k, dt);
+            cudaFuncAttributes attr;
+            if (fn) cudaFuncGetAttributes(&attr, fn);
+        }
+    cudaGetLastError();
+}
+
 const char *FastKindName(int32_t k)
 {
     static const char *names[] = {"AllReduceOneShot", "AllReduceTwoShot", "AllReduceNvls", "ReduceScatter", "AllGather", "AlltoAll",
@@ -632,7 +671,7 @@ HcclResult LaunchFastKernel(const FastLaunch &l)
     cudaError_t e;
     // Cooperative launch guarantees that all CTAs are resident at once: required whenever CTAs wait
     // for CTAs of the same launch (shared-GPU emulation, grid.sync in send/recv).
-    bool coop = l.emuTable != nullptr || l.kind == FK_SEND || l.kind == FK_RECV;
+    bool coop = l.emuTable != nullptr;
     if (coop) e = cudaLaunchCooperativeKernel(fn, grid, block, params, 0, (cudaStream_t)l.stream);
     else e = cudaLaunchKernel(fn, grid, block, params, 0, (cudaStream_t)l.stream);
     if (e != cudaSuccess) {

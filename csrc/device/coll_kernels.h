@@ -68,6 +68,8 @@ struct FastLaunch {
     int emuRanks;
 };
 
+// Forces every kernel of this file to be loaded on the current device (call once per device before any launch).
+void PreloadFastKernels();
 // Returns HCCL_E_NOT_SUPPORT for a (kind, dtype) pair without a kernel.
 HcclResult LaunchFastKernel(const FastLaunch &l);
 // Barriers a kernel of this kind consumes (the epoch advance), so callers can reason about it.

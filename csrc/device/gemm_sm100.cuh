@@ -53,9 +53,15 @@ struct SharedState {
     volatile uint32_t abort;
 };
 
-template <int BN, typename TileOrder, typename Gate, typename Epilogue>
+struct NoExtra {
+    __device__ __forceinline__ void operator()(int, int, volatile uint32_t *) const {}
+};
+
+// tmA2: optional second tensor map for A; the Gate policy decides per tile which one the producer reads
+// (the all-gather fusion reads the caller's own shard in place and the peers' shards from staging).
+template <int BN, typename TileOrder, typename Gate, typename Epilogue, typename Extra = NoExtra>
 __device__ __forceinline__ void GemmMainLoop(const CUtensorMap *tmA, const CUtensorMap *tmB, const GemmShape &g, TileOrder order, Gate gate,
-                                             Epilogue epi)
+                                             Epilogue epi, const CUtensorMap *tmA2 = nullptr, Extra extra = Extra())
 {
     using Cfg = Config<BN>;
     extern __shared__ uint8_t smemRaw[];
@@ -94,14 +100,16 @@ __device__ __forceinline__ void GemmMainLoop(const CUtensorMap *tmA, const CUten
             for (int t = blockIdx.x; t < numTiles && alive; t += gridDim.x) {
                 int mb, nb;
                 order(t, g, &mb, &nb);
-                if (!gate(mb, nb, &st->abort)) { alive = false; break; }
+                int aRow = mb * kBlockM;
+                const CUtensorMap *mapA = tmA;
+                if (!gate(mb, nb, &st->abort, &aRow, tmA, tmA2, &mapA)) { alive = false; break; }
                 for (int kb = 0; kb < kBlocks; ++kb, ++it) {
                     const int s = it % Cfg::kStages;
                     const uint32_t ph = (it / Cfg::kStages) & 1;
                     if (!MbarWait(&st->empty[s], ph ^ 1, &st->abort)) { alive = false; break; }
                     uint8_t *sa = smem + s * Cfg::kStageBytes, *sb = sa + Cfg::kABytes;
                     MbarExpectTx(&st->full[s], Cfg::kStageBytes);
-                    TmaLoad2d(sa, tmA, &st->full[s], kb * kBlockK, mb * kBlockM);
+                    TmaLoad2d(sa, mapA, &st->full[s], kb * kBlockK, aRow);
                     TmaLoad2d(sb, tmB, &st->full[s], kb * kBlockK, nb * BN);
                     issued[s] = true;
                     lastPhase[s] = ph;
@@ -144,6 +152,9 @@ __device__ __forceinline__ void GemmMainLoop(const CUtensorMap *tmA, const CUten
                 if (alive) MmaCommit(&st->tmemFull[acc]);
             }
         }
+    } else if (warp >= 6) {
+        // -------------------------------------------------- extra warps (communication roles of fused kernels)
+        extra(warp - 6, lane, &st->abort);
     } else {
         // ---------------------------------------------------------------------- epilogue
         const int q = warp & 3;                 // TMEM lane quarter this warp may read
@@ -183,7 +194,7 @@ struct RowMajorOrder {
     __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const { *mb = t / g.tilesN; *nb = t % g.tilesN; }
 };
 struct NoGate {
-    __device__ __forceinline__ bool operator()(int, int, volatile uint32_t *) const { return true; }
+    __device__ __forceinline__ bool operator()(int, int, volatile uint32_t *, int *, const CUtensorMap *, const CUtensorMap *, const CUtensorMap **) const { return true; }
 };
 
 // Writes bf16 rows of C; each thread stores its 32 columns as four 16-byte vectors.

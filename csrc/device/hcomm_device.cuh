@@ -54,7 +54,7 @@ __device__ __forceinline__ uint64_t GlobalTimerNs()
 __device__ __forceinline__ bool Aborted(const CommDev *d) { return *(volatile uint32_t *)d->abortWord != 0; }
 
 // Records the first expired wait of the communicator and raises the abort word.
-__device__ __noinline__ void ReportTimeout(const CommDev *d, uint32_t peer, uint32_t kind, uint32_t slot, uint64_t expected,
+static __device__ __noinline__ void ReportTimeout(const CommDev *d, uint32_t peer, uint32_t kind, uint32_t slot, uint64_t expected,
                                            uint64_t seen)
 {
     if (atomicExch_system(&d->status->valid, 1u) == 0u) {
@@ -107,6 +107,24 @@ __device__ __forceinline__ void CrossRankBarrier(const CommDev *d, uint32_t epoc
     if (t < d->nRanks) {
         uint32_t *theirs = (uint32_t *)(HcPeerHeap(d, t) + HC_OFF_BARRIER) + (uint64_t)blockIdx.x * HC_MAX_RANKS + d->rank;
         StReleaseSys(theirs, epoch);
+        const uint32_t *mine = (const uint32_t *)(HcPeerHeap(d, d->rank) + HC_OFF_BARRIER) + (uint64_t)blockIdx.x * HC_MAX_RANKS + t;
+        WaitFlagGe32(d, mine, epoch, (uint32_t)t, HC_WAIT_BARRIER, blockIdx.x);
+    }
+    __syncthreads();
+}
+
+// Same barrier, arrival announced through the NVLS multicast alias: one multimem.st lands in every rank's slot.
+// Used after multimem data stores - a unicast flag write takes another route through the fabric and may overtake
+// multicast data, a multicast flag write from the same SM follows it.
+__device__ __forceinline__ void CrossRankBarrierMc(const CommDev *d, uint32_t epoch)
+{
+    __syncthreads();
+    const int t = threadIdx.x;
+    if (t == 0) {
+        uint32_t *slot = (uint32_t *)(d->mcBase + HC_OFF_BARRIER) + (uint64_t)blockIdx.x * HC_MAX_RANKS + d->rank;
+        asm volatile("multimem.st.release.sys.global.u32 [%0], %1;" ::"l"(slot), "r"(epoch) : "memory");
+    }
+    if (t < d->nRanks) {
         const uint32_t *mine = (const uint32_t *)(HcPeerHeap(d, d->rank) + HC_OFF_BARRIER) + (uint64_t)blockIdx.x * HC_MAX_RANKS + t;
         WaitFlagGe32(d, mine, epoch, (uint32_t)t, HC_WAIT_BARRIER, blockIdx.x);
     }

@@ -1,0 +1,431 @@
+// moe_kernels.cu - expert-parallel all-to-all for mixture-of-experts layers: dispatch (tokens to the
+// ranks that own their experts, quantised on the fly to fp8 e4m3 with one fp32 scale per 128 values) and
+// combine (expert outputs back to the token's rank with the gate-weighted sum fused).  One kernel each;
+// all traffic is remote stores into symmetric buffers.  The reference only offers AlltoAll(V/VC) for this
+// (pkg_inc/legacy/hccl/hccl_inner.h:55-66); routing, quantisation and the weighted sum are fused here.
+//
+// Dispatch, rank r:
+//   1. histogram of the experts its tokens chose                                  (all CTAs, grid barrier)
+//   2. publish the counts to the rank that owns each expert                       (CTA 0, cross-rank barrier)
+//   3. every CTA reads the owners' count tables and derives, for each expert, where this rank's rows start
+//      in the owner's receive buffer: rows are grouped by expert, inside an expert by source rank
+//   4. one warp per token: load 7168 bf16, per 128-value block absmax -> scale -> e4m3, then for each of
+//      the token's k experts claim a row (local atomic) and store row, scales and origin to the owner
+//   5. cross-rank barrier; the owner writes the per-expert offsets for its grouped GEMM
+// Combine, rank r (owner of experts):
+//   1. one warp per received row: send the bf16 expert output to slot (token, k) of the token's rank
+//   2. cross-rank barrier
+//   3. one warp per local token: out = sum_k gate[k] * slot(token, k), fp32 accumulation
+//
+// Device scratch (beyond inputs and outputs): per call, 2 * numExperts u32 counters (histogram and row
+// cursors) that the kernel leaves zeroed for the next call.
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <map>
+
+#include "../comm/comm.h"
+#include "../core/log.h"
+#include "emu_launch.h"
+#include "hccl/hccl_sym_win.h"
+#include "hcomm_res.h"
+#include "hcomm_device.cuh"
+#include "moe_api.h"
+
+namespace hc {
+namespace {
+
+namespace cg = cooperative_groups;
+using namespace hcdev;
+
+constexpr int kMaxExperts = 1024;
+constexpr int kBlock = 128;            // quantisation block
+
+struct MoeParams {
+    CommDev *dev;
+    char *peerBuf[HC_KERNEL_MAX_RANKS];   // symmetric buffer of every rank as mapped here
+    MoeLayout lay;
+    // dispatch
+    const __nv_bfloat16 *x;
+    const int32_t *topkIdx;
+    int numTokens;
+    uint32_t *scratch;                    // [2 * numExperts]: histogram, row cursors (zero between calls)
+    // combine
+    const __nv_bfloat16 *y;
+    const float *gates;
+    __nv_bfloat16 *out;
+    uint32_t *overflow;                   // device word: rows that did not fit the receive capacity
+};
+
+__device__ __forceinline__ uint32_t *Counts(const MoeParams &p, int rank) { return (uint32_t *)(p.peerBuf[rank] + p.lay.offCounts); }
+__device__ __forceinline__ uint8_t *Rows(const MoeParams &p, int rank) { return (uint8_t *)(p.peerBuf[rank] + p.lay.offRows); }
+__device__ __forceinline__ float *Scales(const MoeParams &p, int rank) { return (float *)(p.peerBuf[rank] + p.lay.offScales); }
+__device__ __forceinline__ uint64_t *Origin(const MoeParams &p, int rank) { return (uint64_t *)(p.peerBuf[rank] + p.lay.offOrigin); }
+__device__ __forceinline__ uint32_t *ExpertOffsets(const MoeParams &p, int rank) { return (uint32_t *)(p.peerBuf[rank] + p.lay.offExpertOffsets); }
+__device__ __forceinline__ __nv_bfloat16 *Comb(const MoeParams &p, int rank) { return (__nv_bfloat16 *)(p.peerBuf[rank] + p.lay.offCombine); }
+
+__global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
+{
+    const MoeParams &p = table[blockIdx.y];
+    const CommDev *d = p.dev;
+    cg::grid_group grid = cg::this_grid();
+    const LaunchState ls = KernelBegin(d);
+    const int n = d->nRanks, me = d->rank;
+    const int E = p.lay.numExperts, El = E / n, K = p.lay.topk, H = p.lay.hidden;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int warpsPerCta = blockDim.x >> 5;
+    __shared__ uint32_t sBase[kMaxExperts];
+    uint32_t *hist = p.scratch, *cursor = p.scratch + E;
+
+    // 1. histogram
+    for (int e = tid; e < E; e += blockDim.x) sBase[e] = 0;
+    __syncthreads();
+    for (int i = blockIdx.x * blockDim.x + tid; i < p.numTokens * K; i += gridDim.x * blockDim.x) {
+        int e = p.topkIdx[i];
+        if (e >= 0 && e < E) atomicAdd(&sBase[e], 1u);
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x)
+        if (sBase[e]) atomicAdd(&hist[e], sBase[e]);
+    grid.sync();
+
+    // 2. publish my counts to the owners; CTA 0 of every rank meets, then releases the rest of its grid
+    uint32_t used = 0;
+    ++used;
+    if (blockIdx.x == 0) {
+        for (int e = tid; e < E; e += blockDim.x) Counts(p, e / El)[me * El + (e % El)] = hist[e];
+        CrossRankBarrier(d, ls.epoch0 + used);
+        // the offsets of my own experts for the grouped GEMM that follows (the table may be overwritten by a
+        // peer's next dispatch as soon as this kernel's last barrier is passed, so derive them now)
+        if (tid == 0) {
+            const volatile uint32_t *c = Counts(p, me);
+            uint32_t acc = 0;
+            uint32_t *off = ExpertOffsets(p, me);
+            for (int el = 0; el < El; ++el) {
+                off[el] = acc;
+                for (int s = 0; s < n; ++s) acc += c[s * El + el];
+            }
+            off[El] = acc < (uint32_t)p.lay.maxRecvRows ? acc : (uint32_t)p.lay.maxRecvRows;
+        }
+    }
+    grid.sync();
+
+    // 3. where do my rows of expert e start at its owner?  before them: all rows of the owner's earlier experts,
+    //    and the rows of this expert that come from lower ranks
+    for (int e = tid; e < E; e += blockDim.x) {
+        const int owner = e / El, el = e % El;
+        const volatile uint32_t *c = Counts(p, owner);
+        uint32_t base = 0;
+        for (int e2 = 0; e2 < el; ++e2)
+            for (int s = 0; s < n; ++s) base += c[s * El + e2];
+        for (int s = 0; s < me; ++s) base += c[s * El + el];
+        sBase[e] = base;
+    }
+    __syncthreads();
+
+    // 4. quantise and send, one warp per token
+    const int chunks = H / 16;                       // 16 values (32 bytes in, 16 bytes out) per lane step
+    const int blocksPerRow = H / kBlock;
+    for (int t = blockIdx.x * warpsPerCta + warp; t < p.numTokens; t += gridDim.x * warpsPerCta) {
+        const __nv_bfloat16 *src = p.x + (size_t)t * H;
+        uint4 q[16];                                 // up to 16 chunks per lane: hidden <= 8192
+        float sc[16];
+        int nq = 0;
+        for (int c = lane; c < chunks; c += 32, ++nq) {
+            const uint4 a = *(const uint4 *)(src + c * 16), b = *(const uint4 *)(src + c * 16 + 8);
+            float v[16];
+            const __nv_bfloat162 *pa = (const __nv_bfloat162 *)&a, *pb = (const __nv_bfloat162 *)&b;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 fa = __bfloat1622float2(pa[j]), fb = __bfloat1622float2(pb[j]);
+                v[2 * j] = fa.x; v[2 * j + 1] = fa.y; v[8 + 2 * j] = fb.x; v[8 + 2 * j + 1] = fb.y;
+            }
+            float amax = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) amax = fmaxf(amax, fabsf(v[j]));
+            // the 8 lanes that share a 128-value block sit next to each other
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+            const float scale = fmaxf(amax, 1e-4f) / 448.0f, inv = 1.0f / scale;
+            sc[nq] = scale;
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * inv, v[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+                __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * inv, v[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                w[j] = (uint32_t)lo | ((uint32_t)hi << 16);
+            }
+            q[nq] = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        for (int k = 0; k < K; ++k) {
+            const int e = p.topkIdx[t * K + k];
+            if (e < 0 || e >= E) continue;
+            const int owner = e / El;
+            uint32_t slot = 0;
+            if (lane == 0) slot = sBase[e] + atomicAdd(&cursor[e], 1u);
+            slot = __shfl_sync(0xffffffffu, slot, 0);
+            if (slot >= (uint32_t)p.lay.maxRecvRows) {
+                if (lane == 0) atomicAdd(p.overflow, 1u);
+                continue;
+            }
+            uint8_t *row = Rows(p, owner) + (size_t)slot * H;
+            float *srow = Scales(p, owner) + (size_t)slot * blocksPerRow;
+            int i = 0;
+            for (int c = lane; c < chunks; c += 32, ++i) {
+                *(uint4 *)(row + c * 16) = q[i];
+                if ((lane & 7) == 0) srow[c / 8] = sc[i];
+            }
+            if (lane == 0) Origin(p, owner)[slot] = ((uint64_t)me << 32) | (uint32_t)(t * K + k);
+        }
+    }
+
+    // 5. all rows have landed everywhere; scratch back to zero for the next call
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    grid.sync();
+    if (blockIdx.x == 0)
+        for (int e = tid; e < 2 * E; e += blockDim.x) p.scratch[e] = 0;
+    KernelEnd(d, ls, used);
+}
+
+__global__ void __launch_bounds__(512) MoeCombineKernel(const MoeParams *table)
+{
+    const MoeParams &p = table[blockIdx.y];
+    const CommDev *d = p.dev;
+    const LaunchState ls = KernelBegin(d);
+    const int n = d->nRanks, me = d->rank;
+    const int El = p.lay.numExperts / n, K = p.lay.topk, H = p.lay.hidden;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warpsPerCta = blockDim.x >> 5;
+    const int rows = (int)ExpertOffsets(p, me)[El];
+    const int vecs = H / 8;                          // 16-byte vectors of bf16 per row
+
+    // 1. send every expert output row home
+    for (int r = blockIdx.x * warpsPerCta + warp; r < rows; r += gridDim.x * warpsPerCta) {
+        const uint64_t o = Origin(p, me)[r];
+        const int src = (int)(o >> 32);
+        const uint32_t tk = (uint32_t)o;
+        const uint4 *in = (const uint4 *)(p.y + (size_t)r * H);
+        uint4 *dst = (uint4 *)(Comb(p, src) + (size_t)tk * H);
+        for (int v = lane; v < vecs; v += 32) dst[v] = in[v];
+    }
+    uint32_t used = 0;
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+
+    // 2. gate-weighted sum per local token
+    for (int t = blockIdx.x * warpsPerCta + warp; t < p.numTokens; t += gridDim.x * warpsPerCta) {
+        float g[16];
+        for (int k = 0; k < K; ++k) g[k] = p.gates[t * K + k];
+        for (int v = lane; v < vecs; v += 32) {
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int k = 0; k < K; ++k) {
+                const uint4 pk = Ld16Volatile((const char *)(Comb(p, me) + ((size_t)t * K + k) * H) + (size_t)v * 16);
+                const __nv_bfloat162 *ph = (const __nv_bfloat162 *)&pk;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float2 f = __bfloat1622float2(ph[j]);
+                    acc[2 * j] += g[k] * f.x;
+                    acc[2 * j + 1] += g[k] * f.y;
+                }
+            }
+            uint4 outv;
+            uint32_t *pw = (uint32_t *)&outv;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+                pw[j] = *(uint32_t *)&h;
+            }
+            *(uint4 *)((char *)(p.out + (size_t)t * H) + (size_t)v * 16) = outv;
+        }
+    }
+    KernelEnd(d, ls, used);
+}
+
+struct MoeCtx {
+    Comm *comm;
+    MoeLayout lay;
+    void *buf = nullptr;          // local symmetric buffer
+    HcclCommSymWindow win = nullptr;
+    char *peer[HC_KERNEL_MAX_RANKS] = {nullptr};
+    uint32_t *scratch = nullptr;
+    uint32_t *overflow = nullptr;
+    MoeParams *devParams = nullptr;
+    int nextParam = 0;
+};
+std::mutex g_mu;
+std::map<void *, MoeCtx *> g_ctx;
+
+uint64_t Align256(uint64_t v) { return (v + 255) & ~255ull; }
+
+HcclResult LaunchMoe(MoeCtx *m, void *kernel, const MoeParams &hp, int id, void *stream)
+{
+    Comm *c = m->comm;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (c->emuSameDevice && c->nRanks > 1) {
+        const int ctas = std::max(1, sms / (int)c->nRanks);
+        return EmuLaunchGeneric(c->identifier + "#moe" + std::to_string(c->group.id), c->nRanks, c->rank, id, &hp, sizeof(hp), stream,
+                                [=](const void *devTable, uint32_t n, void *st) {
+                                    void *args[] = {(void *)&devTable};
+                                    cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(ctas, n, 1), dim3(512, 1, 1), args, 0, (cudaStream_t)st);
+                                    if (e != cudaSuccess) { HCCL_ERROR("MoE launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+                                    return HCCL_SUCCESS;
+                                });
+    }
+    MoeParams *slot = m->devParams + m->nextParam;
+    m->nextParam = (m->nextParam + 1) % 32;
+    if (cudaMemcpyAsync(slot, &hp, sizeof(hp), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess) return HCCL_E_RUNTIME;
+    void *args[] = {(void *)&slot};
+    cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(sms, 1, 1), dim3(512, 1, 1), args, 0, (cudaStream_t)stream);
+    if (e != cudaSuccess) { HCCL_ERROR("MoE launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
+}  // namespace
+
+HcclResult LaunchBarrierIfNeeded(Comm *c, void *stream);
+
+}  // namespace hc
+
+using namespace hc;
+
+extern "C" {
+
+// Collective: every rank allocates the same symmetric buffer and maps its peers'.
+int HcommMoeCreate(HcclComm comm, int numExperts, int topk, int hidden, int maxTokens, float capacityFactor, void **handle, MoeLayout *layoutOut)
+{
+    Comm *c = AsComm(comm);
+    if (!c || !handle) return HCCL_E_PTR;
+    if (c->plat->kind() != PlatKind::CUDA || c->nRanks > HC_KERNEL_MAX_RANKS) return HCCL_E_NOT_SUPPORT;
+    const int n = (int)c->nRanks;
+    if (numExperts <= 0 || numExperts > kMaxExperts || numExperts % n || topk <= 0 || topk > 16 || hidden % 512 || hidden > 8192 || maxTokens <= 0) {
+        RPT_ERR("EI0003", "MoE geometry not supported: experts %d (multiple of %d, <= %d), top-k %d (<= 16), hidden %d (multiple of 512, <= 8192)", numExperts, n, kMaxExperts, topk, hidden);
+        return HCCL_E_PARA;
+    }
+    MoeCtx *m = new MoeCtx();
+    m->comm = c;
+    MoeLayout &L = m->lay;
+    L.numExperts = numExperts; L.topk = topk; L.hidden = hidden; L.maxTokens = maxTokens;
+    L.maxRecvRows = (int)std::max<int64_t>(1, (int64_t)((double)maxTokens * topk * (capacityFactor > 0 ? capacityFactor : 2.0)));
+    uint64_t off = 0;
+    L.offCounts = off; off = Align256(off + (uint64_t)n * (numExperts / n) * 4);
+    L.offExpertOffsets = off; off = Align256(off + (uint64_t)(numExperts / n + 1) * 4);
+    L.offOrigin = off; off = Align256(off + (uint64_t)L.maxRecvRows * 8);
+    L.offScales = off; off = Align256(off + (uint64_t)L.maxRecvRows * (hidden / 128) * 4);
+    L.offRows = off; off = Align256(off + (uint64_t)L.maxRecvRows * hidden);
+    L.offCombine = off; off = Align256(off + (uint64_t)maxTokens * topk * hidden * 2);
+    L.totalBytes = off;
+    HcclResult r = (HcclResult)HcommMemAlloc(&m->buf, L.totalBytes);
+    if (r != HCCL_SUCCESS) { delete m; return r; }
+    cudaMemset(m->buf, 0, L.offOrigin);
+    r = HcclCommSymWinRegister(comm, m->buf, L.totalBytes, &m->win, 0);
+    if (r != HCCL_SUCCESS) { HcommMemFree(m->buf); delete m; return r; }
+    for (int q = 0; q < n; ++q) {
+        void *pp = nullptr;
+        HcclSymWinGetPeerPointer(m->win, 0, (uint32_t)q, &pp);
+        m->peer[q] = (char *)pp;
+    }
+    cudaMalloc(&m->scratch, sizeof(uint32_t) * 2 * numExperts);
+    cudaMemset(m->scratch, 0, sizeof(uint32_t) * 2 * numExperts);
+    cudaMalloc(&m->overflow, sizeof(uint32_t));
+    cudaMemset(m->overflow, 0, sizeof(uint32_t));
+    cudaMalloc(&m->devParams, sizeof(MoeParams) * 32);
+    cudaFuncAttributes fa;
+    cudaFuncGetAttributes(&fa, MoeDispatchKernel);
+    cudaFuncGetAttributes(&fa, MoeCombineKernel);
+    cudaDeviceSynchronize();
+    *handle = m;
+    if (layoutOut) *layoutOut = L;
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_ctx[m] = m;
+    return HCCL_SUCCESS;
+}
+
+int HcommMoeDestroy(void *handle)
+{
+    MoeCtx *m = (MoeCtx *)handle;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (!g_ctx.erase(handle)) return HCCL_E_NOT_FOUND;
+    }
+    cudaDeviceSynchronize();
+    HcclCommSymWinDeregister(m->win);
+    HcommMemFree(m->buf);
+    cudaFree(m->scratch); cudaFree(m->overflow); cudaFree(m->devParams);
+    delete m;
+    return HCCL_SUCCESS;
+}
+
+// Local addresses of the receive-side arrays (valid after a dispatch on the same stream).
+int HcommMoeGetBuffers(void *handle, void **rows, void **scales, void **origin, void **expertOffsets, void **combine)
+{
+    MoeCtx *m = (MoeCtx *)handle;
+    if (!m) return HCCL_E_PTR;
+    char *b = (char *)m->buf;
+    if (rows) *rows = b + m->lay.offRows;
+    if (scales) *scales = b + m->lay.offScales;
+    if (origin) *origin = b + m->lay.offOrigin;
+    if (expertOffsets) *expertOffsets = b + m->lay.offExpertOffsets;
+    if (combine) *combine = b + m->lay.offCombine;
+    return HCCL_SUCCESS;
+}
+
+static void FillCommon(MoeCtx *m, MoeParams &hp)
+{
+    memset(&hp, 0, sizeof(hp));
+    hp.dev = m->comm->devStruct;
+    for (uint32_t q = 0; q < m->comm->nRanks; ++q) hp.peerBuf[q] = m->peer[q];
+    hp.lay = m->lay;
+    hp.scratch = m->scratch;
+    hp.overflow = m->overflow;
+}
+
+int HcommMoeDispatch(void *handle, const void *x, const int32_t *topkIdx, int numTokens, void *stream)
+{
+    MoeCtx *m = (MoeCtx *)handle;
+    if (!m || !x || !topkIdx) return HCCL_E_PTR;
+    if (numTokens < 0 || numTokens > m->lay.maxTokens) return HCCL_E_PARA;
+    Comm *c = m->comm;
+    std::lock_guard<std::mutex> lk(c->opMu);
+    int st = c->state.load();
+    if (st == (int)CommState::SUSPENDING || st == (int)CommState::SUSPENDED) return HCCL_E_SUSPENDING;
+    CHK_RET(LaunchBarrierIfNeeded(c, stream));
+    MoeParams hp;
+    FillCommon(m, hp);
+    hp.x = (const __nv_bfloat16 *)x; hp.topkIdx = topkIdx; hp.numTokens = numTokens;
+    ++c->opSeq;
+    return LaunchMoe(m, (void *)MoeDispatchKernel, hp, 9101, stream);
+}
+
+int HcommMoeCombine(void *handle, const void *y, const float *gates, void *out, int numTokens, void *stream)
+{
+    MoeCtx *m = (MoeCtx *)handle;
+    if (!m || !y || !gates || !out) return HCCL_E_PTR;
+    if (numTokens < 0 || numTokens > m->lay.maxTokens) return HCCL_E_PARA;
+    Comm *c = m->comm;
+    std::lock_guard<std::mutex> lk(c->opMu);
+    int st = c->state.load();
+    if (st == (int)CommState::SUSPENDING || st == (int)CommState::SUSPENDED) return HCCL_E_SUSPENDING;
+    CHK_RET(LaunchBarrierIfNeeded(c, stream));
+    MoeParams hp;
+    FillCommon(m, hp);
+    hp.y = (const __nv_bfloat16 *)y; hp.gates = gates; hp.out = (__nv_bfloat16 *)out; hp.numTokens = numTokens;
+    ++c->opSeq;
+    return LaunchMoe(m, (void *)MoeCombineKernel, hp, 9102, stream);
+}
+
+// Rows dropped because a rank received more than its capacity since the last call (clears the counter).
+int HcommMoeTakeOverflow(void *handle)
+{
+    MoeCtx *m = (MoeCtx *)handle;
+    if (!m) return -1;
+    uint32_t v = 0, zero = 0;
+    cudaMemcpy(&v, m->overflow, 4, cudaMemcpyDeviceToHost);
+    if (v) cudaMemcpy(m->overflow, &zero, 4, cudaMemcpyHostToDevice);
+    return (int)v;
+}
+
+}  // extern "C"

@@ -380,6 +380,21 @@ private:
 
 }  // namespace
 
+// Forces the helper kernels of the stream engine to be loaded on the current device.  A wait kernel may be spinning
+// when the host issues the first reduce; with lazy loading that first launch could have to wait for the spinning
+// kernel, whose partner may be stuck the same way on the other side.
+void PreloadPlatformKernels()
+{
+    cudaFuncAttributes a;
+    cudaFuncGetAttributes(&a, FlagAddKernel);
+    cudaFuncGetAttributes(&a, FlagWaitGeKernel);
+#define HC_PRELOAD(T) cudaFuncGetAttributes(&a, HostTsReduceKernel<T>);
+    HC_PRELOAD(int8_t) HC_PRELOAD(int16_t) HC_PRELOAD(int32_t) HC_PRELOAD(long long) HC_PRELOAD(uint8_t) HC_PRELOAD(uint16_t) HC_PRELOAD(uint32_t)
+    HC_PRELOAD(unsigned long long) HC_PRELOAD(float) HC_PRELOAD(double) HC_PRELOAD(__half) HC_PRELOAD(__nv_bfloat16)
+#undef HC_PRELOAD
+    cudaGetLastError();
+}
+
 Platform *CudaInstance()
 {
     static std::once_flag once;

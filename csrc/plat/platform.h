@@ -108,5 +108,7 @@ Platform *SimInstance();
 Platform *CudaInstance();
 // Applies HCCL_SIM: 1 -> simulator, 0 -> CUDA or failure, unset -> CUDA when available else simulator.
 Platform *DefaultPlatform();
+// CUDA only: load the stream-engine helper kernels on the current device (see cuda_platform.cu).
+void PreloadPlatformKernels();
 
 }  // namespace hc

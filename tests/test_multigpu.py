@@ -1,0 +1,22 @@
+"""Real multi-GPU runs: one process per GPU, peer memory mapped through exported VMM handles."""
+import pytest
+
+from conftest import cuda_device_count
+from mp_launch import launch
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_collectives_across_gpus(world):
+    if cuda_device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    codes, outs = launch("collectives", world, {"HCOMM_TEST_BUFFER_MB": "16", "HCCL_EXEC_TIMEOUT": "20"}, timeout=150)
+    assert codes == [0] * world, "\n".join(outs)
+
+
+def test_peer_exit_between_steps_is_seen_on_the_host():
+    if cuda_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    codes, outs = launch("peer_exit", 2, {"HCOMM_TEST_BUFFER_MB": "8", "HCCL_NVLS_ENABLE": "0", "NCCL_NVLS_ENABLE": "0", "HCCL_EXEC_TIMEOUT": "20"}, timeout=90)
+    assert codes[0] == 0, "\n".join(outs)

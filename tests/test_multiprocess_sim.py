@@ -1,0 +1,21 @@
+"""Ranks as separate processes on the host simulator: rendezvous over TCP, shared memory passed as file
+descriptors over Unix sockets, and the failure paths of the control plane (a rank that never joins, a
+rank that exits between steps)."""
+from mp_launch import launch
+
+
+def test_four_processes_allreduce_allgather():
+    codes, outs = launch("collectives", 4, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "2"})
+    assert codes == [0, 0, 0, 0], "\n".join(outs)
+
+
+def test_rank_that_never_joins_times_out_with_a_report():
+    codes, outs = launch("never_join", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCCL_CONNECT_TIMEOUT": "2"}, timeout=60)
+    assert codes[2] == 0
+    assert codes[0] == 40 + 9 and codes[1] == 40 + 9, "\n".join(outs)     # HCCL_E_TIMEOUT
+    assert "EI0015" in outs[0] and "missing ranks: 2" in outs[0], outs[0]
+
+
+def test_peer_exit_is_reported_as_remote_error():
+    codes, outs = launch("peer_exit", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=90)
+    assert codes[0] == 0 and codes[1] == 0, "\n".join(outs)
