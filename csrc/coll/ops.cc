@@ -58,12 +58,20 @@ void Record(Comm *c, const OpDesc &d, const Selection &sel, uint64_t t0)
     ++c->opRingNext;
 }
 
+// CTAs per rank.  Small transfers are latency bound (few CTAs keep the barrier cheap); large ones need many CTAs
+// to keep enough 16-byte accesses in flight for NVLink: measured on B200, a 256 MB all-reduce runs at 275 GB/s bus
+// bandwidth with 32 CTAs, 413 with 64 and 520 with 128.
 int PickCtas(Comm *c, const Selection &sel, uint64_t bytesPerRank)
 {
-    int forced = EnvConfig::Get().maxCtas.value;
-    int ctas = sel.ctas ? (int)sel.ctas : (int)std::min<uint64_t>(32, std::max<uint64_t>(1, (bytesPerRank + (64 << 10) - 1) / (64 << 10)));
-    if (bytesPerRank >= (64ull << 20)) ctas = std::max(ctas, 48);
-    if (forced > 0) ctas = std::min(ctas, forced);
+    const int cap = EnvConfig::Get().maxCtas.value, forced = EnvConfig::Get().forceCtas.value;
+    int ctas;
+    if (sel.ctas) ctas = (int)sel.ctas;
+    else if (bytesPerRank >= (32ull << 20)) ctas = 144;
+    else if (bytesPerRank >= (8ull << 20)) ctas = 96;
+    else if (bytesPerRank >= (2ull << 20)) ctas = 48;
+    else ctas = (int)std::min<uint64_t>(24, std::max<uint64_t>(1, (bytesPerRank + (64 << 10) - 1) / (64 << 10)));
+    if (cap > 0) ctas = std::min(ctas, cap);
+    if (forced > 0) ctas = forced;
     if (c->emuSameDevice) ctas = std::min(ctas, 4);
     return std::max(1, std::min(ctas, HC_MAX_CTAS));
 }
@@ -114,7 +122,7 @@ HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
     uint64_t maxPerLaunch, oneShotCap = AlignDownElems(c->halfBytes / n / esz, esz);
     if (kind == FK_ALLREDUCE_ONESHOT && d.count > oneShotCap) kind = FK_ALLREDUCE_TWOSHOT;
     if (kind == FK_ALLREDUCE_ONESHOT) maxPerLaunch = oneShotCap;
-    else if (kind == FK_ALLREDUCE_TWOSHOT) maxPerLaunch = AlignDownElems(c->halfBytes / (n + 1) / esz, esz) * n;
+    else if (kind == FK_ALLREDUCE_TWOSHOT) maxPerLaunch = AlignDownElems(c->halfBytes / (2 * n) / esz, esz) * n;
     else maxPerLaunch = AlignDownElems(c->halfBytes / esz, esz);
     for (uint64_t off = 0; off < d.count; off += maxPerLaunch) {
         uint64_t cnt = std::min(maxPerLaunch, d.count - off);

@@ -108,6 +108,7 @@ void EnvConfig::LoadAll()
     simulate.Load(ParseInt);
     nvlsEnable.Load(ParseInt);
     maxCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
+    forceCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
     tuneFile.Load(ParseStr);
     symStrideGB.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 4096; });
 }

@@ -45,7 +45,8 @@ struct EnvConfig {
     // B200-specific knobs
     EnvField<int32_t> simulate{"HCCL_SIM", -1};             // 1 force host simulator, 0 force CUDA, -1 auto
     EnvField<int32_t> nvlsEnable{"HCCL_NVLS_ENABLE", 1};
-    EnvField<int32_t> maxCtas{"HCCL_MAX_CTAS", 0};          // 0 = selector decides
+    EnvField<int32_t> maxCtas{"HCCL_MAX_CTAS", 0};          // upper bound of CTAs per collective kernel; 0 = selector decides
+    EnvField<int32_t> forceCtas{"HCCL_FORCE_CTAS", 0};      // exact CTA count (tuning runs); 0 = off
     EnvField<std::string> tuneFile{"HCCL_TUNE_FILE", ""};   // measured bus-bandwidth table (JSON)
     EnvField<int32_t> symStrideGB{"HCCL_SYM_STRIDE_GB", 0};
 

@@ -124,6 +124,61 @@ __device__ __forceinline__ void ReduceAuto(const char *const *src, int n, char *
     else ReduceSources<T, false>(src, n, dst1, dst2, nElems, op, useScale, scale);
 }
 
+// Like ReduceAuto with any number of destinations (local and remote): every reduced chunk is stored to all of them.
+template <typename T, bool VEC>
+__device__ __forceinline__ void ReduceFanOutImpl(const char *const *src, int n, char *const *dst, int nd, uint64_t nElems, int op, int useScale, float scale)
+{
+    using A = typename AccOf<T>::type;
+    using C = Chunk<T, VEC>;
+    constexpr int N = C::N;
+    const uint64_t nChunks = nElems / N;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nChunks; i += stride) {
+        const uint64_t off = i * (uint64_t)(N * sizeof(T));
+        A acc[N];
+        for (int base = 0; base < n; base += 8) {
+            C buf[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                if (base + k < n) buf[k].Load(src[base + k] + off);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (base + k < n) {
+                    if (base + k == 0) {
+#pragma unroll
+                        for (int j = 0; j < N; ++j) acc[j] = Widen<T>(buf[k].e[j]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < N; ++j) acc[j] = Combine<A>(op, acc[j], Widen<T>(buf[k].e[j]));
+                    }
+                }
+            }
+        }
+        C out;
+#pragma unroll
+        for (int j = 0; j < N; ++j) out.e[j] = Narrow<T>(useScale ? ScaleAcc<A>(acc[j], scale) : acc[j]);
+        for (int k = 0; k < nd; ++k) out.Store(dst[k] + off);
+    }
+    if (VEC && blockIdx.x == 0) {
+        for (uint64_t e = nChunks * N + threadIdx.x; e < nElems; e += blockDim.x) {
+            const uint64_t off = e * sizeof(T);
+            A acc = Widen<T>(*(volatile const T *)(src[0] + off));
+            for (int r = 1; r < n; ++r) acc = Combine<A>(op, acc, Widen<T>(*(volatile const T *)(src[r] + off)));
+            T v = Narrow<T>(useScale ? ScaleAcc<A>(acc, scale) : acc);
+            for (int k = 0; k < nd; ++k) *(T *)(dst[k] + off) = v;
+        }
+    }
+}
+template <typename T>
+__device__ __forceinline__ void ReduceFanOut(const char *const *src, int n, char *const *dst, int nd, uint64_t nElems, int op, int useScale, float scale)
+{
+    uintptr_t bits = 0;
+    for (int r = 0; r < n; ++r) bits |= (uintptr_t)src[r];
+    for (int k = 0; k < nd; ++k) bits |= (uintptr_t)dst[k];
+    if ((bits & 15) == 0) ReduceFanOutImpl<T, true>(src, n, dst, nd, nElems, op, useScale, scale);
+    else ReduceFanOutImpl<T, false>(src, n, dst, nd, nElems, op, useScale, scale);
+}
+
 // Element range of slice q when `count` elements are cut into slices of `S`.
 __device__ __forceinline__ void SliceRange(uint64_t count, uint64_t S, int q, uint64_t *beg, uint64_t *len)
 {
@@ -162,7 +217,9 @@ __global__ void __launch_bounds__(512) KAllReduceOneShot(const __grid_constant__
     KernelEnd(d, ls, used);
 }
 
-// Staging: n slots + 1 result slice, each sliceElems elements; count <= n * sliceElems.
+// Staging: 2n slots of sliceElems elements: [0,n) partial slices arriving from the peers, [n,2n) reduced slices
+// arriving from their owners.  count <= n * sliceElems.  NVLink carries data in the first two phases (partials
+// out, then reduced slices out while they are being computed); the last phase is a local copy.
 template <typename T>
 __global__ void __launch_bounds__(512) KAllReduceTwoShot(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
@@ -179,20 +236,23 @@ __global__ void __launch_bounds__(512) KAllReduceTwoShot(const __grid_constant__
         GridCopy(CclHalf(d, q, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in + beg * sizeof(T), len * sizeof(T), sizeof(T));
     }
     CrossRankBarrier(d, ls.epoch0 + (++used));
-    // reduce my slice in rank order into the result slice and my part of the output
+    // reduce my slice in rank order; the result goes to my output and to slot n+me of every peer
     SliceRange(a.count, S, me, &beg, &len);
-    char *red = CclHalf(d, me, ls.half) + (uint64_t)n * slotBytes;
     {
         const char *src[HC_KERNEL_MAX_RANKS];
+        char *dst[HC_KERNEL_MAX_RANKS];
         for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + beg * sizeof(T) : CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes;
-        ReduceAuto<T>(src, n, red, (char *)a.out + beg * sizeof(T), len, a.op, a.useScale, a.scale);
+        int nd = 0;
+        dst[nd++] = (char *)a.out + beg * sizeof(T);
+        for (int i = 1; i < n; ++i) dst[nd++] = CclHalf(d, (me + i) % n, ls.half) + (uint64_t)(n + me) * slotBytes;
+        ReduceFanOut<T>(src, n, dst, nd, len, a.op, a.useScale, a.scale);
     }
     CrossRankBarrier(d, ls.epoch0 + (++used));
-    // gather: read the other result slices where they were reduced
+    // the other slices have landed in my staging: copy them out
     for (int i = 1; i < n; ++i) {
         int q = (me + i) % n;
         SliceRange(a.count, S, q, &beg, &len);
-        GridCopy((char *)a.out + beg * sizeof(T), CclHalf(d, q, ls.half) + (uint64_t)n * slotBytes, len * sizeof(T), sizeof(T));
+        GridCopy((char *)a.out + beg * sizeof(T), CclHalf(d, me, ls.half) + (uint64_t)(n + q) * slotBytes, len * sizeof(T), sizeof(T));
     }
     KernelEnd(d, ls, used);
 }
@@ -217,7 +277,25 @@ __global__ void __launch_bounds__(512) KAllReduceNvls(const __grid_constant__ Co
         const uint64_t v0 = per * me < nvec ? per * me : nvec, v1 = (v0 + per < nvec) ? v0 + per : nvec;
         char *mc = d->mcBase + d->bufOffset + (uint64_t)ls.half * d->halfBytes;
         const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-        for (uint64_t i = v0 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < v1; i += stride) {
+        // A switch round trip takes microseconds: four independent 16-byte reductions per thread are kept in flight.
+        constexpr int kUnroll = 4;
+        uint64_t i = v0 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+        for (; i + (kUnroll - 1) * stride < v1; i += kUnroll * stride) {
+            uint4 v[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) v[u] = Multimem<T>::LdReduceAdd(mc + ((i + u * stride) << 4));
+#pragma unroll
+            for (int u = 0; u < kUnroll; ++u) {
+                if (a.useScale) {
+                    Pack<T> p; p.v = v[u];
+#pragma unroll
+                    for (int j = 0; j < Pack<T>::N; ++j) p.e[j] = Narrow<T>(Widen<T>(p.e[j]) * a.scale);
+                    v[u] = p.v;
+                }
+                MultimemSt16(mc + ((i + u * stride) << 4), v[u]);
+            }
+        }
+        for (; i < v1; i += stride) {
             uint4 v = Multimem<T>::LdReduceAdd(mc + (i << 4));
             if (a.useScale) {
                 Pack<T> p; p.v = v;

@@ -76,8 +76,8 @@ struct RsOrder {
         const int perDest = mbPer * g.tilesN;
         const int i = t / perDest, local = t % perDest;
         const int q = (rank + 1 + i) % nRanks;
-        *mb = q * mbPer + local / g.tilesN;
-        *nb = local % g.tilesN;
+        *mb = q * mbPer + local % mbPer;      // column by column inside a destination: its row blocks share B panels
+        *nb = local / mbPer;
     }
 };
 
@@ -190,8 +190,8 @@ struct AgOrder {
         const int perSrc = mbPer * g.tilesN;
         const int j = t / perSrc, local = t % perSrc;
         const int src = (rank - j + nRanks) % nRanks;
-        *mb = src * mbPer + local / g.tilesN;
-        *nb = local % g.tilesN;
+        *mb = src * mbPer + local % mbPer;
+        *nb = local / mbPer;
     }
 };
 

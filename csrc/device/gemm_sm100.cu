@@ -20,7 +20,7 @@ template <int BN>
 __global__ void __launch_bounds__(hcgemm::kThreads, 1)
 GemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16 epi)
 {
-    hcgemm::GemmMainLoop<BN>(&tmA, &tmB, shape, hcgemm::RowMajorOrder(), hcgemm::NoGate(), epi);
+    hcgemm::GemmMainLoop<BN>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < 16 ? shape.tilesM : 16}, hcgemm::NoGate(), epi);
 }
 }  // namespace
 

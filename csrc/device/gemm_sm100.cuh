@@ -189,9 +189,21 @@ __device__ __forceinline__ void GemmMainLoop(const CUtensorMap *tmA, const CUten
 
 // ------------------------------------------------------------------------------ stock policies
 
-struct RowMajorOrder {
-    // n fastest: CTAs of one wave share A panels and sweep B, which stays resident in L2
-    __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const { *mb = t / g.tilesN; *nb = t % g.tilesN; }
+// L2-aware rasterisation: tiles are walked in groups of `gm` row blocks, column by column inside a group, so the
+// CTAs of one wave (148 tiles) cover about gm x 148/gm tiles and share gm A panels and 148/gm B panels.  With
+// B panels twice as tall as A panels the traffic per wave, gm*a + (148/gm)*2a, is smallest near gm = 16; walking
+// rows first instead would fetch every B panel once per row block and make large problems HBM bound.
+struct GroupedOrder {
+    int gm;
+    __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
+    {
+        const int perGroup = gm * g.tilesN;
+        const int group = t / perGroup, rem = t % perGroup;
+        const int rowsLeft = g.tilesM - group * gm;
+        const int rowsHere = rowsLeft < gm ? rowsLeft : gm;
+        *nb = rem / rowsHere;
+        *mb = group * gm + rem % rowsHere;
+    }
 };
 struct NoGate {
     __device__ __forceinline__ bool operator()(int, int, volatile uint32_t *, int *, const CUtensorMap *, const CUtensorMap *, const CUtensorMap **) const { return true; }

@@ -150,13 +150,13 @@ __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
             amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-            const float scale = fmaxf(amax, 1e-4f) / 448.0f, inv = 1.0f / scale;
+            const float scale = fmaxf(amax, 1e-4f) / 448.0f;   // values are divided (not multiplied by a reciprocal): bit-exact with x / scale
             sc[nq] = scale;
             uint32_t w[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] * inv, v[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-                __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] * inv, v[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+                __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j] / scale, v[4 * j + 1] / scale), __NV_SATFINITE, __NV_E4M3);
+                __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(v[4 * j + 2] / scale, v[4 * j + 3] / scale), __NV_SATFINITE, __NV_E4M3);
                 w[j] = (uint32_t)lo | ((uint32_t)hi << 16);
             }
             q[nq] = make_uint4(w[0], w[1], w[2], w[3]);
@@ -213,6 +213,9 @@ __global__ void __launch_bounds__(512) MoeCombineKernel(const MoeParams *table)
     }
     uint32_t used = 0;
     CrossRankBarrier(d, ls.epoch0 + (++used));
+    // A CTA's barrier only pairs it with the same-index CTA of the other ranks, but the rows of one token come from
+    // arbitrary CTAs of their owners: once ALL local CTAs have passed their barrier, all CTAs of all ranks have sent.
+    cg::this_grid().sync();
 
     // 2. gate-weighted sum per local token
     for (int t = blockIdx.x * warpsPerCta + warp; t < p.numTokens; t += gridDim.x * warpsPerCta) {

@@ -106,6 +106,7 @@ def quantize_e4m3_1x128(x: torch.Tensor):
     """Reference quantiser with the kernel's rule: scale = max(|block|, 1e-4) / 448."""
     t, h = x.shape
     xb = x.float().view(t, h // 128, 128)
-    scale = xb.abs().amax(dim=-1).clamp_min(1e-4) / 448.0
-    q = (xb / scale.unsqueeze(-1)).to(torch.float8_e4m3fn)
+    amax = xb.abs().amax(dim=-1).clamp_min(1e-4)
+    scale = amax / torch.full_like(amax, 448.0)     # tensor / tensor is a true division; tensor / python scalar multiplies by a rounded reciprocal
+    q = (xb / scale.unsqueeze(-1)).clamp(-448.0, 448.0).to(torch.float8_e4m3fn)   # saturate like the kernel does
     return q.view(t, h), scale

@@ -93,7 +93,13 @@ def main():
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    info = exchange_root_info(rank, world)
+    if world > 1:
+        from ..comm import get_root_info
+        box = [get_root_info() if rank == 0 else None]
+        dist.broadcast_object_list(box, src=0)
+        info = box[0]
+    else:
+        info = exchange_root_info(rank, world)
     comm = Communicator(world, info, rank, buffer_mb=a.buffer_mb, algo=a.algo)
     sizes, s = [], parse_size(a.min)
     while s <= parse_size(a.max):

@@ -100,6 +100,58 @@ def main():
             g = np.zeros(7 * world, np.int32)
             comm.all_gather(np.full(7, rank, np.int32), g)
             assert np.array_equal(g, np.repeat(np.arange(world), 7))
+    elif scenario == "fused":
+        import torch
+        from hcomm_b200.ops.fused import all_gather_gemm, gemm_reduce_scatter
+        from hcomm_b200.ops.gemm import take_kernel_error
+        from hcomm_b200.ops.moe import MoeExchange, quantize_e4m3_1x128
+        import torch.distributed as dist
+        dist.init_process_group("gloo", init_method=f"file://{os.environ['HCOMM_ROOT_FILE']}.gloo", rank=rank, world_size=world)
+        m, n_, k = 128 * world * 2, 512, 1024
+        g = torch.Generator(device="cuda").manual_seed(5 + rank)
+        a = torch.randn(m, k, device="cuda", generator=g).to(torch.bfloat16)
+        b = (torch.randn(n_, k, device="cuda", generator=g) * 0.1).to(torch.bfloat16)
+        for rep in range(3):
+            y = gemm_reduce_scatter(comm, a, b)
+            torch.cuda.synchronize()
+            part = (a.float() @ b.float().t()).cpu()
+            dist.all_reduce(part)
+            rows = m // world
+            err = (y.float().cpu() - part[rank * rows:(rank + 1) * rows]).abs().max().item()
+            assert err <= 2e-2 * max(1.0, part.abs().max().item()), ("gemm_rs", rep, err)
+        stage("gemm_reduce_scatter ok")
+        xs = torch.randn(256, k, device="cuda", generator=g).to(torch.bfloat16)
+        for rep in range(3):
+            y2 = all_gather_gemm(comm, xs, b)
+            torch.cuda.synchronize()
+            gathered = [torch.empty(256, k, dtype=torch.bfloat16) for _ in range(world)]
+            dist.all_gather(gathered, xs.cpu())
+            ref = torch.cat(gathered).float() @ b.float().cpu().t()
+            err = (y2.float().cpu() - ref).abs().max().item()
+            assert err <= 2e-2 * max(1.0, ref.abs().max().item()), ("ag_gemm", rep, err)
+        stage("all_gather_gemm ok")
+        assert take_kernel_error() == 0 and comm.async_error() == 0
+        experts, topk, hidden, tokens = 8 * world, 4, 1024, 200
+        moe = MoeExchange(comm, experts, topk, hidden, tokens)
+        x = torch.randn(tokens, hidden, device="cuda", generator=g).to(torch.bfloat16)
+        idx = torch.stack([torch.randperm(experts, device="cuda", generator=g)[:topk] for _ in range(tokens)]).to(torch.int32).contiguous()
+        gates = torch.rand(tokens, topk, device="cuda", generator=g).float().contiguous()
+        for rep in range(2):
+            rec = moe.dispatch(x, idx)
+            torch.cuda.synchronize()
+            nrows = rec.num_rows
+            yexp = (rec.dequantized(nrows) * 3).to(torch.bfloat16)
+            out = moe.combine(yexp, gates)
+            torch.cuda.synchronize()
+            q, sc = quantize_e4m3_1x128(x)
+            deq = (q.float().view(tokens, -1, 128) * sc.unsqueeze(-1)).view(tokens, hidden)
+            ref = (deq * 3).to(torch.bfloat16).float() * gates.sum(dim=1, keepdim=True)
+            err = (out.float() - ref).abs().max().item()
+            assert err <= 3e-2 * max(1.0, ref.abs().max().item()), ("moe", rep, err)
+            assert moe.overflow() == 0
+        stage("moe dispatch/combine ok")
+        moe.destroy()
+        dist.destroy_process_group()
     elif scenario == "forced_algos":
         import torch
         for algo in ("level0:ring", "level0:H-D_R"):

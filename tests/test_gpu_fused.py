@@ -77,6 +77,7 @@ def test_fused_ops_interleave_with_collectives(n=2):
     try:
         a = [torch.randn(256, 128, device="cuda").to(torch.bfloat16) for _ in range(n)]
         b = [torch.randn(256, 128, device="cuda").to(torch.bfloat16) for _ in range(n)]
+        w2 = [torch.randn(128, 256, device="cuda").to(torch.bfloat16) for _ in range(n)]
         v = [torch.full((1000,), float(r + 1), device="cuda") for r in range(n)]
         res = [None] * n
 
@@ -85,7 +86,7 @@ def test_fused_ops_interleave_with_collectives(n=2):
             c = comms[r]
             y1 = gemm_reduce_scatter(c, a[r], b[r])
             c.all_reduce(v[r])
-            y2 = all_gather_gemm(c, y1, b[r])
+            y2 = all_gather_gemm(c, y1, w2[r])
             c.all_reduce(v[r])
             torch.cuda.synchronize()
             res[r] = (y1, y2)

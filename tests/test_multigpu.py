@@ -20,3 +20,11 @@ def test_peer_exit_between_steps_is_seen_on_the_host():
         pytest.skip("needs 2 GPUs")
     codes, outs = launch("peer_exit", 2, {"HCOMM_TEST_BUFFER_MB": "8", "HCCL_NVLS_ENABLE": "0", "NCCL_NVLS_ENABLE": "0", "HCCL_EXEC_TIMEOUT": "20"}, timeout=90)
     assert codes[0] == 0, "\n".join(outs)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_fused_kernels_across_gpus(world):
+    if cuda_device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    codes, outs = launch("fused", world, {"HCOMM_TEST_BUFFER_MB": "32", "HCCL_EXEC_TIMEOUT": "20"}, timeout=200)
+    assert codes == [0] * world, "\n".join(outs)
