@@ -420,6 +420,98 @@ int HcommMoeCombine(void *handle, const void *y, const float *gates, void *out, 
     return LaunchMoe(m, (void *)MoeCombineKernel, hp, 9102, stream);
 }
 
+// ------------------------------------------------------------------ dispatch without any allocation
+//
+// The dispatch kernel counts rows per expert in a small table of global-memory counters.  HcommMoeDispatch keeps
+// that table in a cudaMalloc'ed block owned by the exchange object.  The entry point below runs the SAME kernel
+// with the table placed in an array that is part of this library's device image instead, so that nothing on its
+// path asks any allocator for memory - neither the CUDA runtime's nor a framework's caching one.
+//
+// It exists for callers that must not allocate at the moment they dispatch:
+//   * a serving process whose memory pool has already claimed all of the GPU, where a late cudaMalloc fails;
+//   * a step in which other streams (or other ranks' kernels waiting on this rank) are in flight, where the
+//     implicit device-wide synchronisation of cudaMalloc / cudaFree stalls them or lengthens a peer's wait;
+//   * code that owns no handle it could hang a buffer on and would otherwise allocate and free around each call.
+//
+// Limits and rules:
+//   * at most kStaticScratchExperts experts (2 counters each, kStaticScratchBytes of device memory per process and
+//     GPU, reserved when the library is loaded); larger exchanges are refused with HCCL_E_PARA;
+//   * the array is shared by every call from this process on the same GPU and keeps whatever the previous call
+//     left (a call that ran out of time leaves counts behind); each call therefore zeroes the part it uses, on
+//     the caller's stream, before the kernel runs;
+//   * because the array is shared, two calls that overlap in time on one GPU (different streams, different
+//     exchange objects) race on it: keep calls of this entry point ordered one after another per GPU;
+//   * the first call on a device looks up the array's address (cudaGetSymbolAddress) and remembers it; make that
+//     first call during start-up, with the device current and before any stream capture begins;
+//   * ranks of one process that share a GPU (the single-GPU test arrangement) are refused: their launches are
+//     merged through a table that is created on demand, which this entry point promises not to do.
+constexpr int kStaticScratchExperts = 256;
+constexpr size_t kStaticScratchBytes = sizeof(uint32_t) * 2 * kStaticScratchExperts;
+static __device__ __align__(256) uint32_t g_staticDispatchScratch[2 * kStaticScratchExperts];
+
+namespace {
+constexpr int kMaxDevicesTracked = 64;
+uint32_t *g_staticScratchAddr[kMaxDevicesTracked];   // per device, filled on first use
+std::mutex g_staticScratchMu;
+
+// Address of the built-in table on the current device; looked up once per device.
+HcclResult StaticScratchForCurrentDevice(uint32_t **out)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevicesTracked) {
+        HCCL_ERROR("built-in dispatch scratch: no usable current device (%s)", e == cudaSuccess ? "index out of range" : cudaGetErrorString(e));
+        return HCCL_E_RUNTIME;
+    }
+    std::lock_guard<std::mutex> lk(g_staticScratchMu);
+    if (!g_staticScratchAddr[dev]) {
+        uint32_t *ptr = nullptr;
+        e = cudaGetSymbolAddress((void **)&ptr, g_staticDispatchScratch);
+        if (e != cudaSuccess || !ptr) {
+            HCCL_ERROR("built-in dispatch scratch: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+            return HCCL_E_RUNTIME;
+        }
+        g_staticScratchAddr[dev] = ptr;
+    }
+    *out = g_staticScratchAddr[dev];
+    return HCCL_SUCCESS;
+}
+}  // namespace
+
+int HcommMoeDispatchStaticScratch(void *handle, const void *x, const int32_t *topkIdx, int numTokens, void *stream)
+{
+    MoeCtx *m = (MoeCtx *)handle;
+    if (!m || !x || !topkIdx) return HCCL_E_PTR;
+    if (numTokens < 0 || numTokens > m->lay.maxTokens) return HCCL_E_PARA;
+    Comm *c = m->comm;
+    if (m->lay.numExperts > kStaticScratchExperts) {
+        RPT_ERR("EI0003", "HcommMoeDispatchStaticScratch serves at most %d experts (%zu bytes of built-in scratch); this exchange has %d - use HcommMoeDispatch",
+                kStaticScratchExperts, kStaticScratchBytes, m->lay.numExperts);
+        return HCCL_E_PARA;
+    }
+    if (c->emuSameDevice && c->nRanks > 1) {
+        RPT_ERR("EI0003", "HcommMoeDispatchStaticScratch does not serve several ranks of one process on one GPU - use HcommMoeDispatch");
+        return HCCL_E_NOT_SUPPORT;
+    }
+    std::lock_guard<std::mutex> lk(c->opMu);
+    int st = c->state.load();
+    if (st == (int)CommState::SUSPENDING || st == (int)CommState::SUSPENDED) return HCCL_E_SUSPENDING;
+    uint32_t *scratch = nullptr;
+    CHK_RET(StaticScratchForCurrentDevice(&scratch));
+    CHK_RET(LaunchBarrierIfNeeded(c, stream));
+    // the kernel expects both counter rows at zero and the array may hold a previous call's leftovers
+    if (cudaMemsetAsync(scratch, 0, sizeof(uint32_t) * 2 * (size_t)m->lay.numExperts, (cudaStream_t)stream) != cudaSuccess) {
+        HCCL_ERROR("built-in dispatch scratch: clearing failed: %s", cudaGetErrorString(cudaGetLastError()));
+        return HCCL_E_RUNTIME;
+    }
+    MoeParams hp;
+    FillCommon(m, hp);
+    hp.scratch = scratch;
+    hp.x = (const __nv_bfloat16 *)x; hp.topkIdx = topkIdx; hp.numTokens = numTokens;
+    ++c->opSeq;
+    return LaunchMoe(m, (void *)MoeDispatchKernel, hp, 9103, stream);
+}
+
 // Rows dropped because a rank received more than its capacity since the last call (clears the counter).
 int HcommMoeTakeOverflow(void *handle)
 {
