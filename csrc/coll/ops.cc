@@ -351,10 +351,6 @@ HcclResult HostCollective(Comm *c, const OpDesc &d, const Selection &sel)
     ea.stream = c->plat->kind() == PlatKind::SIM ? nullptr : d.stream;
     CHK_RET(ExecuteOnHost(c, *sched, ea));
     c->lastOpOnHost = true;
-    if (d.useScale) {
-        RPT_ERR("EI0003", "the fused scale is served by the SM kernels only");
-        return HCCL_E_NOT_SUPPORT;
-    }
     return HCCL_SUCCESS;
 }
 
@@ -514,11 +510,6 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
     } else {
         CHK_RET(SelectAlgorithm(si, AlgoConfigOf(c), &sel));
     }
-    if (d.useScale && sel.engine == Engine::HOST && c->nRanks > 1) {
-        // the scale is a kernel feature; on the host engines apply it as a separate pass is not offered
-        RPT_ERR("EI0003", "HcclAllReduceScaled needs the SM or NVLS engine (op expansion mode %u selects the host engine)", c->cfg.opExpansionMode);
-        return HCCL_E_NOT_SUPPORT;
-    }
     static thread_local std::string lastLogged;
     if (lastLogged != sel.name) {
         HCCL_DEBUG_CAT(CAT_ALG, "%s: %llu elements of %s -> %s (%s)", CmdName(d.cmd), (unsigned long long)d.count, DtypeName(d.dtype), sel.name.c_str(), sel.reason.c_str());
@@ -542,6 +533,8 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
             s2.algo = Algo::MESH_ONESHOT;
             r = HostCollective(c, b, s2);
         } else r = HostCollective(c, d, sel);
+        // the stream engine has no fused scale: a second pass over the result applies it
+        if (r == HCCL_SUCCESS && d.useScale) r = c->plat->ScaleAsync(d.out, d.count, d.dtype, d.scale, c->plat->kind() == PlatKind::SIM ? nullptr : d.stream);
         if (r == HCCL_SUCCESS && c->plat->kind() == PlatKind::SIM) r = CommPollDeviceStatus(c);
     } else {
         switch (d.cmd) {

@@ -115,6 +115,14 @@ __global__ void HostTsReduceKernel(T *__restrict__ dst, const T *__restrict__ sr
     for (; i < count; i += stride) dst[i] = (T)OpApply<A>(op, (A)dst[i], (A)src[i]);
 }
 
+template <typename T>
+__global__ void HostTsScaleKernel(T *__restrict__ buf, uint64_t count, float scale)
+{
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    for (; i < count; i += stride) buf[i] = (T)((typename Acc<T>::type)buf[i] * (typename Acc<T>::type)scale);
+}
+
 __global__ void FlagAddKernel(uint64_t *flag, uint64_t v)
 {
     __threadfence_system();
@@ -338,6 +346,23 @@ public:
         CUDA_CHK(cudaGetLastError());
         return HCCL_SUCCESS;
     }
+    HcclResult ScaleAsync(void *buf, uint64_t count, HcclDataType t, float scale, Stream s) override
+    {
+        if (count == 0) return HCCL_SUCCESS;
+        const int threads = 256;
+        uint64_t want = (count + threads - 1) / threads;
+        int blocks = (int)(want > 1184 ? 1184 : want);
+        cudaStream_t st = (cudaStream_t)s;
+        switch (t) {
+            case HCCL_DATA_TYPE_FP32: HostTsScaleKernel<float><<<blocks, threads, 0, st>>>((float *)buf, count, scale); break;
+            case HCCL_DATA_TYPE_FP64: HostTsScaleKernel<double><<<blocks, threads, 0, st>>>((double *)buf, count, scale); break;
+            case HCCL_DATA_TYPE_FP16: HostTsScaleKernel<__half><<<blocks, threads, 0, st>>>((__half *)buf, count, scale); break;
+            case HCCL_DATA_TYPE_BFP16: HostTsScaleKernel<__nv_bfloat16><<<blocks, threads, 0, st>>>((__nv_bfloat16 *)buf, count, scale); break;
+            default: return HCCL_E_NOT_SUPPORT;
+        }
+        CUDA_CHK(cudaGetLastError());
+        return HCCL_SUCCESS;
+    }
     HcclResult FlagAddAsync(uint64_t *flag, uint64_t v, Stream s) override
     {
         FlagAddKernel<<<1, 1, 0, (cudaStream_t)s>>>(flag, v);
@@ -388,6 +413,8 @@ void PreloadPlatformKernels()
     cudaFuncAttributes a;
     cudaFuncGetAttributes(&a, FlagAddKernel);
     cudaFuncGetAttributes(&a, FlagWaitGeKernel);
+    cudaFuncGetAttributes(&a, HostTsScaleKernel<float>); cudaFuncGetAttributes(&a, HostTsScaleKernel<double>);
+    cudaFuncGetAttributes(&a, HostTsScaleKernel<__half>); cudaFuncGetAttributes(&a, HostTsScaleKernel<__nv_bfloat16>);
 #define HC_PRELOAD(T) cudaFuncGetAttributes(&a, HostTsReduceKernel<T>);
     HC_PRELOAD(int8_t) HC_PRELOAD(int16_t) HC_PRELOAD(int32_t) HC_PRELOAD(long long) HC_PRELOAD(uint8_t) HC_PRELOAD(uint16_t) HC_PRELOAD(uint32_t)
     HC_PRELOAD(unsigned long long) HC_PRELOAD(float) HC_PRELOAD(double) HC_PRELOAD(__half) HC_PRELOAD(__nv_bfloat16)

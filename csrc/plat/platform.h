@@ -96,6 +96,8 @@ public:
     virtual HcclResult ReduceAsync(void *dst, const void *src, uint64_t count, HcclDataType t, HcclReduceOp op,
                                    Stream s) = 0;
     // *flag += v with release semantics visible to every GPU and the host.
+    // buf[i] = buf[i] * scale for floating-point element types (fp16 / bf16 are scaled in fp32).
+    virtual HcclResult ScaleAsync(void *buf, uint64_t count, HcclDataType t, float scale, Stream s) = 0;
     virtual HcclResult FlagAddAsync(uint64_t *flag, uint64_t v, Stream s) = 0;
     // Blocks the stream until *flag >= expected, or timeoutMs elapses (then fills `rep`).
     virtual HcclResult FlagWaitGeAsync(uint64_t *flag, uint64_t expected, uint32_t timeoutMs, const WaitReport &rep,

@@ -225,6 +225,21 @@ public:
         Run(s, [=] { HostReduce(dst, src, count, t, op); });
         return HCCL_SUCCESS;
     }
+    HcclResult ScaleAsync(void *buf, uint64_t count, HcclDataType t, float scale, Stream s) override
+    {
+        if (t != HCCL_DATA_TYPE_FP32 && t != HCCL_DATA_TYPE_FP64 && t != HCCL_DATA_TYPE_FP16 && t != HCCL_DATA_TYPE_BFP16) return HCCL_E_NOT_SUPPORT;
+        Run(s, [=] {
+            for (uint64_t i = 0; i < count; ++i) {
+                switch (t) {
+                    case HCCL_DATA_TYPE_FP32: ((float *)buf)[i] *= scale; break;
+                    case HCCL_DATA_TYPE_FP64: ((double *)buf)[i] *= (double)scale; break;
+                    case HCCL_DATA_TYPE_FP16: ((uint16_t *)buf)[i] = FloatToHalf(HalfToFloat(((uint16_t *)buf)[i]) * scale); break;
+                    default: ((uint16_t *)buf)[i] = FloatToBf16(Bf16ToFloat(((uint16_t *)buf)[i]) * scale); break;
+                }
+            }
+        });
+        return HCCL_SUCCESS;
+    }
     HcclResult FlagAddAsync(uint64_t *flag, uint64_t v, Stream s) override
     {
         Run(s, [=] { __atomic_fetch_add(flag, v, __ATOMIC_RELEASE); });

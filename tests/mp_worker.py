@@ -30,6 +30,119 @@ def root_info(rank):
     return path.read_bytes()
 
 
+def torch_scenario(scenario, rank, world, local, use_cuda):
+    """torch.distributed over the "hccl" backend: every c10d operator against values computable locally."""
+    import torch
+    import torch.distributed as dist
+    import hcomm_b200.parallel.backend  # noqa: F401  (registers the backend)
+    dev = torch.device("cuda", local) if use_cuda else torch.device("cpu")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    dist.init_process_group("hccl", rank=rank, world_size=world)
+
+    def val(r, n, dtype=torch.float32):
+        return (torch.arange(n, dtype=torch.float32) * 0.25 + r + 1).to(dtype).to(dev)
+
+    if scenario == "torch_ops":
+        n = 1000
+        t = val(rank, n)
+        dist.all_reduce(t)
+        want = sum(val(r, n) for r in range(world))
+        assert torch.allclose(t, want), "all_reduce"
+        t = val(rank, n)
+        dist.all_reduce(t, op=dist.ReduceOp.AVG)
+        assert torch.allclose(t, want / world, rtol=1e-5), "all_reduce avg"
+        t = val(rank, n)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        assert torch.equal(t, val(world - 1, n)), "all_reduce max"
+        t = val(rank, n, torch.int64)
+        dist.all_reduce(t)
+        assert torch.equal(t, sum(val(r, n, torch.int64) for r in range(world))), "all_reduce int64"
+        t = val(rank, n)
+        dist.broadcast(t, src=1)
+        assert torch.equal(t, val(1, n)), "broadcast"
+        outs = [torch.empty(n, device=dev) for _ in range(world)]
+        dist.all_gather(outs, val(rank, n))
+        assert all(torch.equal(outs[r], val(r, n)) for r in range(world)), "all_gather"
+        flat = torch.empty(world * n, device=dev)
+        dist.all_gather_into_tensor(flat, val(rank, n))
+        assert torch.equal(flat, torch.cat([val(r, n) for r in range(world)])), "all_gather_into_tensor"
+        out = torch.empty(n, device=dev)
+        dist.reduce_scatter_tensor(out, torch.cat([val(rank, n) * (q + 1) for q in range(world)]))
+        assert torch.allclose(out, want * (rank + 1)), "reduce_scatter_tensor"
+        out = torch.empty(n, device=dev)
+        dist.reduce_scatter(out, [val(rank, n) * (q + 1) for q in range(world)])
+        assert torch.allclose(out, want * (rank + 1)), "reduce_scatter"
+        t = val(rank, n)
+        dist.reduce(t, dst=0)
+        if rank == 0:
+            assert torch.allclose(t, want), "reduce"
+        send = torch.cat([val(rank, 8) + 100 * q for q in range(world)])
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        assert torch.equal(recv, torch.cat([val(q, 8) + 100 * rank for q in range(world)])), "all_to_all_single"
+        # uneven splits: rank r sends (q + 1) rows of 4 to rank q
+        rows_out = [q + 1 for q in range(world)]
+        rows_in = [rank + 1] * world
+        send = torch.cat([torch.full((q + 1, 4), float(10 * rank + q), device=dev) for q in range(world)])
+        recv = torch.empty(sum(rows_in), 4, device=dev)
+        dist.all_to_all_single(recv, send, output_split_sizes=rows_in, input_split_sizes=rows_out)
+        assert torch.equal(recv, torch.cat([torch.full((rank + 1, 4), float(10 * q + rank), device=dev) for q in range(world)])), "all_to_all_single splits"
+        outs = [torch.empty(q + 2, device=dev) for q in range(world)]
+        outs = [torch.empty(rank + 2, device=dev) for _ in range(world)]
+        dist.all_to_all(outs, [torch.full((q + 2,), float(rank), device=dev) for q in range(world)])
+        assert all(torch.equal(outs[q], torch.full((rank + 2,), float(q), device=dev)) for q in range(world)), "all_to_all"
+        gl = [torch.empty(n, device=dev) for _ in range(world)] if rank == 0 else None
+        dist.gather(val(rank, n), gl, dst=0)
+        if rank == 0:
+            assert all(torch.equal(gl[r], val(r, n)) for r in range(world)), "gather"
+        out = torch.empty(n, device=dev)
+        dist.scatter(out, [val(q, n) * 3 for q in range(world)] if rank == 0 else None, src=0)
+        assert torch.equal(out, val(rank, n) * 3), "scatter"
+        if world >= 2:
+            if rank == 0:
+                dist.send(val(7, n), dst=1)
+            elif rank == 1:
+                t = torch.empty(n, device=dev)
+                dist.recv(t, src=0)
+                assert torch.equal(t, val(7, n)), "send/recv"
+        dist.barrier()
+        work = dist.all_reduce(val(rank, n), async_op=True)
+        work.wait()
+        assert work.is_completed() or use_cuda
+        print(f"rank {rank}: torch operators ok", flush=True)
+    elif scenario == "torch_ddp":
+        from hcomm_b200.parallel.ddp import wrap
+        torch.manual_seed(1234)
+        dtype = torch.bfloat16 if use_cuda else torch.float32
+        net = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.GELU(), torch.nn.Linear(128, 32)).to(dev).to(dtype)
+        ref = torch.nn.Sequential(torch.nn.Linear(64, 128), torch.nn.GELU(), torch.nn.Linear(128, 32)).to(dev).to(dtype)
+        ref.load_state_dict(net.state_dict())
+        ddp = wrap(net, bucket_cap_mb=1)
+        g = torch.Generator().manual_seed(99)
+        xs = torch.randn(world, 16, 64, generator=g).to(dtype)
+        ys = torch.randn(world, 16, 32, generator=g).to(dtype)
+        opt = torch.optim.SGD(ddp.parameters(), lr=0.05)
+        ropt = torch.optim.SGD(ref.parameters(), lr=0.05)
+        for step in range(3):
+            opt.zero_grad(set_to_none=True)
+            loss = torch.nn.functional.mse_loss(ddp(xs[rank].to(dev)).float(), ys[rank].to(dev).float())
+            loss.backward()
+            opt.step()
+            # reference: the mean over ranks of the per-rank gradients, computed locally
+            ropt.zero_grad(set_to_none=True)
+            total = sum(torch.nn.functional.mse_loss(ref(xs[r].to(dev)).float(), ys[r].to(dev).float()) for r in range(world)) / world
+            total.backward()
+            ropt.step()
+        tol = 3e-2 if use_cuda else 1e-5
+        for a, b in zip(net.parameters(), ref.parameters()):
+            assert torch.allclose(a.float(), b.float(), rtol=tol, atol=tol), (step, (a.float() - b.float()).abs().max().item())
+        print(f"rank {rank}: ddp ok", flush=True)
+    if use_cuda:
+        torch.cuda.synchronize()
+    dist.destroy_process_group()
+    return 0
+
+
 def main():
     scenario = sys.argv[1]
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", os.environ["RANK"]))
@@ -41,6 +154,8 @@ def main():
 
     if scenario == "never_join" and rank == world - 1:
         return 0   # this rank never joins the rendezvous
+    if scenario.startswith("torch_"):
+        return torch_scenario(scenario, rank, world, local, use_cuda)
     kw = {}
     if os.environ.get("HCOMM_TEST_BUFFER_MB"):
         kw["buffer_mb"] = int(os.environ["HCOMM_TEST_BUFFER_MB"])

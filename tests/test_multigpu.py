@@ -28,3 +28,12 @@ def test_fused_kernels_across_gpus(world):
         pytest.skip(f"needs {world} GPUs")
     codes, outs = launch("fused", world, {"HCOMM_TEST_BUFFER_MB": "32", "HCCL_EXEC_TIMEOUT": "20"}, timeout=200)
     assert codes == [0] * world, "\n".join(outs)
+
+
+@pytest.mark.parametrize("scenario", ["torch_ops", "torch_ddp"])
+def test_torch_backend_across_gpus(scenario):
+    if cuda_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    env = {"HCOMM_TORCH_BUFFER_MB": "16", "HCCL_EXEC_TIMEOUT": "20", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29651"}
+    codes, outs = launch(scenario, 2, env, timeout=200)
+    assert codes == [0, 0], "\n".join(outs)

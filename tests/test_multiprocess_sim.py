@@ -19,3 +19,13 @@ def test_rank_that_never_joins_times_out_with_a_report():
 def test_peer_exit_is_reported_as_remote_error():
     codes, outs = launch("peer_exit", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=90)
     assert codes[0] == 0 and codes[1] == 0, "\n".join(outs)
+
+
+def test_torch_backend_operators_on_the_simulator():
+    codes, outs = launch("torch_ops", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "2", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29641"}, timeout=240)
+    assert codes == [0, 0, 0], "\n".join(outs)
+
+
+def test_ddp_with_fused_scale_hook_matches_local_mean_gradient():
+    codes, outs = launch("torch_ddp", 2, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "2", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29642"}, timeout=240)
+    assert codes == [0, 0], "\n".join(outs)
