@@ -31,8 +31,10 @@ HcclResult HcclDiagGetOpCounters(HcclComm comm, uint64_t *launched, uint64_t *he
     Comm *c = AsComm(comm);
     CHK_PTR_NULL(c);
     if (launched) *launched = c->opSeq;
-    if (headCount) *headCount = __atomic_load_n(&c->opCounters[0], __ATOMIC_ACQUIRE);
-    if (tailCount) *tailCount = __atomic_load_n(&c->opCounters[1], __ATOMIC_ACQUIRE);
+    uint64_t ht[2] = {0, 0};
+    if (c->opCounters) CHK_RET(c->plat->PeekSync(ht, c->opCounters, sizeof(ht)));
+    if (headCount) *headCount = ht[0];
+    if (tailCount) *tailCount = ht[1];
     return HCCL_SUCCESS;
 }
 
@@ -83,7 +85,9 @@ HcclResult HcclDiagDump(HcclComm comm, char *buf, uint32_t bufLen)
     std::ostringstream os;
     os << "communicator " << c->cfg.name << " rank " << c->rank << "/" << c->nRanks << " platform " << c->plat->name() << " state " << c->state.load()
        << " asyncError " << c->asyncError.load() << "\n" << c->graph.Describe() << "\n";
-    os << "operators launched " << c->opSeq << " kernel head " << c->opCounters[0] << " tail " << c->opCounters[1] << "\n";
+    uint64_t ht[2] = {0, 0};
+    if (c->opCounters) c->plat->PeekSync(ht, c->opCounters, sizeof(ht));
+    os << "operators launched " << c->opSeq << " kernel head " << ht[0] << " tail " << ht[1] << "\n";
     const HcclDeviceWaitStatus &s = *c->waitStatus;
     if (s.valid) os << "expired wait: rank " << s.rank << " on rank " << s.peer << " kind " << s.kind << " slot " << s.slot << " block " << s.block << " expected " << s.expected << " saw " << s.seen << " op #" << s.seq << "\n";
     {

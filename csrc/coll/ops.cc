@@ -69,7 +69,7 @@ int PickCtas(Comm *c, const Selection &sel, uint64_t bytesPerRank)
     else if (bytesPerRank >= (32ull << 20)) ctas = 144;
     else if (bytesPerRank >= (8ull << 20)) ctas = 96;
     else if (bytesPerRank >= (2ull << 20)) ctas = 48;
-    else ctas = (int)std::min<uint64_t>(24, std::max<uint64_t>(1, (bytesPerRank + (64 << 10) - 1) / (64 << 10)));
+    else ctas = (int)std::min<uint64_t>(32, std::max<uint64_t>(1, (bytesPerRank + (16 << 10) - 1) / (16 << 10)));
     if (cap > 0) ctas = std::min(ctas, cap);
     if (forced > 0) ctas = forced;
     if (c->emuSameDevice) ctas = std::min(ctas, 4);

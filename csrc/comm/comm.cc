@@ -244,9 +244,12 @@ static HcclResult SetupDeviceState(Comm *c)
 {
     Platform *P = c->plat;
     void *p = nullptr;
-    CHK_RET(P->DevAlloc(128 * sizeof(uint32_t), &p));
-    c->devCounters = (uint32_t *)p;
-    CHK_RET(P->MemsetSync(p, 0, 128 * sizeof(uint32_t)));
+    // one block: [CommDev | launch counters | head/tail counters], see comm_dev.h
+    CHK_RET(P->DevAlloc(HC_DEV_BLOCK_BYTES, &p));
+    CHK_RET(P->MemsetSync(p, 0, HC_DEV_BLOCK_BYTES));
+    c->devStruct = (CommDev *)p;
+    c->devCounters = (uint32_t *)((char *)p + HC_DEV_COUNTERS_OFFSET);
+    c->opCounters = (uint64_t *)((char *)p + HC_DEV_OPCOUNTERS_OFFSET);
     size_t irBytes = 2ull * HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY * sizeof(uint64_t);
     CHK_RET(P->DevAlloc(irBytes, &p));
     c->devIrCounters = (uint64_t *)p;
@@ -255,7 +258,6 @@ static HcclResult SetupDeviceState(Comm *c)
     memset(p, 0, 4096);
     c->abortWord = (uint32_t *)p;
     c->waitStatus = (HcclDeviceWaitStatus *)((char *)p + 64);
-    c->opCounters = (uint64_t *)((char *)p + 256);
 
     CommDev &d = c->hostDev;
     d.rank = (int32_t)c->rank;
@@ -274,8 +276,7 @@ static HcclResult SetupDeviceState(Comm *c)
     d.status = c->waitStatus;
     d.opCounters = c->opCounters;
     d.timeoutNs = (uint64_t)c->TimeoutMs() * 1000000ull;
-    CHK_RET(P->DevAlloc(sizeof(CommDev), &p));
-    c->devStruct = (CommDev *)p;
+    static_assert(sizeof(CommDev) <= HC_DEV_COUNTERS_OFFSET, "CommDev outgrew its slot");
     CHK_RET(P->MemcpySync(c->devStruct, &d, sizeof(CommDev)));
     return HCCL_SUCCESS;
 }
@@ -396,7 +397,6 @@ Comm::~Comm()
     if (heapPhys.bytes) plat->PhysRelease(&heapPhys);
     if (fusedParamRing) plat->DevFree(fusedParamRing);
     if (devStruct) plat->DevFree(devStruct);
-    if (devCounters) plat->DevFree(devCounters);
     if (devIrCounters) plat->DevFree(devIrCounters);
     if (abortWord) plat->HostFree(abortWord);
 }

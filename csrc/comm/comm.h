@@ -146,7 +146,7 @@ struct Comm {
     uint64_t *devIrCounters = nullptr;       // irSent + irConsumed
     uint32_t *abortWord = nullptr;           // pinned host
     HcclDeviceWaitStatus *waitStatus = nullptr;
-    uint64_t *opCounters = nullptr;          // pinned host {head, tail}
+    uint64_t *opCounters = nullptr;          // device {head, tail} (inside the devStruct block); read with Platform::PeekSync
 
     // ---- execution state
     std::mutex opMu;                         // operators of one communicator are issued one at a time

@@ -65,101 +65,55 @@ template <> struct Chunk<__nv_bfloat16, false> {
     __device__ __forceinline__ void Store(char *p) const { *(__nv_bfloat16 *)p = e[0]; }
 };
 
-// dst1[i] (and dst2[i] when non-null) = scale * (src[0][i] op src[1][i] op ... op src[n-1][i]) for nElems
-// elements, contributions combined in index order.  Grid-interleaved by chunks of Chunk::N elements.
-template <typename T, bool VEC>
-__device__ __forceinline__ void ReduceSources(const char *const *src, int n, char *dst1, char *dst2, uint64_t nElems, int op, int useScale,
-                                              float scale)
+// dst[k][i] = scale * (src[0][i] op src[1][i] op ... op src[n-1][i]) for every destination k (local or remote) and
+// nElems elements, contributions combined in index order (the same order on every rank: results are bit-identical).
+// Grid-interleaved by chunks of Chunk::N elements.  A thread keeps M x U 16-byte loads in flight: M sources of U
+// chunks; with few ranks U grows so that the bytes in flight per thread stay the same (NVLink and HBM latency are
+// hidden by memory-level parallelism, not by occupancy: these kernels run with few CTAs next to compute kernels).
+template <typename T, bool VEC, int M, int U>
+__device__ __forceinline__ void ReduceLoop(const char *const *src, int n, char *const *dst, int nd, uint64_t nElems, int op, int useScale, float scale)
 {
     using A = typename AccOf<T>::type;
     using C = Chunk<T, VEC>;
     constexpr int N = C::N;
+    constexpr uint64_t CB = (uint64_t)N * sizeof(T);
     const uint64_t nChunks = nElems / N;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nChunks; i += stride) {
-        const uint64_t off = i * (uint64_t)(N * sizeof(T));
-        A acc[N];
-        for (int base = 0; base < n; base += 8) {
-            C buf[8];
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nChunks; i += U * stride) {
+        A acc[U][N];
+        for (int base = 0; base < n; base += M) {
+            C buf[U][M];
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (base + k < n) buf[k].Load(src[base + k] + off);
+            for (int u = 0; u < U; ++u)
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                if (base + k < n) {
-                    if (base + k == 0) {
+                for (int k = 0; k < M; ++k)
+                    if (base + k < n && i + u * stride < nChunks) buf[u][k].Load(src[base + k] + (i + u * stride) * CB);
 #pragma unroll
-                        for (int j = 0; j < N; ++j) acc[j] = Widen<T>(buf[k].e[j]);
-                    } else {
+            for (int u = 0; u < U; ++u)
 #pragma unroll
-                        for (int j = 0; j < N; ++j) acc[j] = Combine<A>(op, acc[j], Widen<T>(buf[k].e[j]));
+                for (int k = 0; k < M; ++k) {
+                    if (base + k < n) {
+                        if (base + k == 0) {
+#pragma unroll
+                            for (int j = 0; j < N; ++j) acc[u][j] = Widen<T>(buf[u][k].e[j]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < N; ++j) acc[u][j] = Combine<A>(op, acc[u][j], Widen<T>(buf[u][k].e[j]));
+                        }
                     }
                 }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            if (i + u * stride < nChunks) {
+                C out;
+#pragma unroll
+                for (int j = 0; j < N; ++j) out.e[j] = Narrow<T>(useScale ? ScaleAcc<A>(acc[u][j], scale) : acc[u][j]);
+                for (int k = 0; k < nd; ++k) out.Store(dst[k] + (i + u * stride) * CB);
             }
         }
-        C out;
-#pragma unroll
-        for (int j = 0; j < N; ++j) out.e[j] = Narrow<T>(useScale ? ScaleAcc<A>(acc[j], scale) : acc[j]);
-        out.Store(dst1 + off);
-        if (dst2) out.Store(dst2 + off);
     }
     if (VEC && blockIdx.x == 0) {   // ragged end of a vectorised range
-        for (uint64_t e = nChunks * N + threadIdx.x; e < nElems; e += blockDim.x) {
-            const uint64_t off = e * sizeof(T);
-            A acc = Widen<T>(*(volatile const T *)(src[0] + off));
-            for (int r = 1; r < n; ++r) acc = Combine<A>(op, acc, Widen<T>(*(volatile const T *)(src[r] + off)));
-            T v = Narrow<T>(useScale ? ScaleAcc<A>(acc, scale) : acc);
-            *(T *)(dst1 + off) = v;
-            if (dst2) *(T *)(dst2 + off) = v;
-        }
-    }
-}
-
-template <typename T>
-__device__ __forceinline__ void ReduceAuto(const char *const *src, int n, char *dst1, char *dst2, uint64_t nElems, int op, int useScale, float scale)
-{
-    uintptr_t bits = (uintptr_t)dst1 | (uintptr_t)dst2;
-    for (int r = 0; r < n; ++r) bits |= (uintptr_t)src[r];
-    if ((bits & 15) == 0) ReduceSources<T, true>(src, n, dst1, dst2, nElems, op, useScale, scale);
-    else ReduceSources<T, false>(src, n, dst1, dst2, nElems, op, useScale, scale);
-}
-
-// Like ReduceAuto with any number of destinations (local and remote): every reduced chunk is stored to all of them.
-template <typename T, bool VEC>
-__device__ __forceinline__ void ReduceFanOutImpl(const char *const *src, int n, char *const *dst, int nd, uint64_t nElems, int op, int useScale, float scale)
-{
-    using A = typename AccOf<T>::type;
-    using C = Chunk<T, VEC>;
-    constexpr int N = C::N;
-    const uint64_t nChunks = nElems / N;
-    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nChunks; i += stride) {
-        const uint64_t off = i * (uint64_t)(N * sizeof(T));
-        A acc[N];
-        for (int base = 0; base < n; base += 8) {
-            C buf[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k)
-                if (base + k < n) buf[k].Load(src[base + k] + off);
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-                if (base + k < n) {
-                    if (base + k == 0) {
-#pragma unroll
-                        for (int j = 0; j < N; ++j) acc[j] = Widen<T>(buf[k].e[j]);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < N; ++j) acc[j] = Combine<A>(op, acc[j], Widen<T>(buf[k].e[j]));
-                    }
-                }
-            }
-        }
-        C out;
-#pragma unroll
-        for (int j = 0; j < N; ++j) out.e[j] = Narrow<T>(useScale ? ScaleAcc<A>(acc[j], scale) : acc[j]);
-        for (int k = 0; k < nd; ++k) out.Store(dst[k] + off);
-    }
-    if (VEC && blockIdx.x == 0) {
         for (uint64_t e = nChunks * N + threadIdx.x; e < nElems; e += blockDim.x) {
             const uint64_t off = e * sizeof(T);
             A acc = Widen<T>(*(volatile const T *)(src[0] + off));
@@ -175,8 +129,20 @@ __device__ __forceinline__ void ReduceFanOut(const char *const *src, int n, char
     uintptr_t bits = 0;
     for (int r = 0; r < n; ++r) bits |= (uintptr_t)src[r];
     for (int k = 0; k < nd; ++k) bits |= (uintptr_t)dst[k];
-    if ((bits & 15) == 0) ReduceFanOutImpl<T, true>(src, n, dst, nd, nElems, op, useScale, scale);
-    else ReduceFanOutImpl<T, false>(src, n, dst, nd, nElems, op, useScale, scale);
+    if ((bits & 15) == 0) {
+        if (n <= 2) ReduceLoop<T, true, 2, 4>(src, n, dst, nd, nElems, op, useScale, scale);
+        else if (n <= 4) ReduceLoop<T, true, 4, 2>(src, n, dst, nd, nElems, op, useScale, scale);
+        else ReduceLoop<T, true, 8, 1>(src, n, dst, nd, nElems, op, useScale, scale);
+    } else {
+        ReduceLoop<T, false, 8, 1>(src, n, dst, nd, nElems, op, useScale, scale);
+    }
+}
+// One or two destinations (dst2 may be null).
+template <typename T>
+__device__ __forceinline__ void ReduceAuto(const char *const *src, int n, char *dst1, char *dst2, uint64_t nElems, int op, int useScale, float scale)
+{
+    char *dst[2] = {dst1, dst2};
+    ReduceFanOut<T>(src, n, dst, dst2 ? 2 : 1, nElems, op, useScale, scale);
 }
 
 // Element range of slice q when `count` elements are cut into slices of `S`.

@@ -54,9 +54,16 @@ struct CommDev {
     uint64_t *irConsumed;    /* device-local, same shape */
     uint32_t *abortWord;     /* host-pinned: non-zero makes every wait return immediately */
     HcclDeviceWaitStatus *status; /* host-pinned record of the first wait that expired */
-    uint64_t *opCounters;    /* host-pinned {head, tail}: bumped at kernel start / end */
+    uint64_t *opCounters;    /* device-local {head, tail}: bumped at kernel start / end (the host peeks at them to tell which operator hangs) */
     uint64_t timeoutNs;      /* budget of every device-side wait */
 };
+
+/* The structure, the launch counters and the head/tail counters share one device allocation so that a kernel
+ * finds its counters at a fixed distance from the structure (no dependent pointer load on the cold path):
+ *   [0, 128) CommDev   [128, 640) u32 counters[128]: 0 epoch, 1 launches, 2 blocksDone, ...   [640, 656) u64 {head, tail} */
+#define HC_DEV_COUNTERS_OFFSET 128
+#define HC_DEV_OPCOUNTERS_OFFSET 640
+#define HC_DEV_BLOCK_BYTES 1024
 
 #ifdef __CUDACC__
 #define HC_HD __host__ __device__ __forceinline__

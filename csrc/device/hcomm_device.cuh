@@ -136,26 +136,30 @@ struct LaunchState {
     uint32_t epoch0;
     uint32_t half;
 };
+static_assert(sizeof(CommDev) <= HC_DEV_COUNTERS_OFFSET, "CommDev outgrew its slot");
+__device__ __forceinline__ uint32_t *DevCounters(const CommDev *d) { return (uint32_t *)((char *)d + HC_DEV_COUNTERS_OFFSET); }
+__device__ __forceinline__ unsigned long long *DevOpCounters(const CommDev *d) { return (unsigned long long *)((char *)d + HC_DEV_OPCOUNTERS_OFFSET); }
 __device__ __forceinline__ LaunchState KernelBegin(const CommDev *d)
 {
     LaunchState s;
-    s.epoch0 = *(volatile uint32_t *)d->epoch;
-    s.half = *(volatile uint32_t *)d->launches & 1u;
-    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd_system((unsigned long long *)&d->opCounters[0], 1ull);
+    const uint32_t *ctr = DevCounters(d);
+    s.epoch0 = *(volatile const uint32_t *)&ctr[0];
+    s.half = *(volatile const uint32_t *)&ctr[1] & 1u;
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&DevOpCounters(d)[0], 1ull);
     return s;
 }
 __device__ __forceinline__ void KernelEnd(const CommDev *d, const LaunchState &s, uint32_t barriersUsed, uint32_t halvesUsed = 1)
 {
     __syncthreads();
     if (threadIdx.x == 0) {
+        uint32_t *ctr = DevCounters(d);
         __threadfence();
-        uint32_t done = atomicAdd(d->blocksDone, 1u);
+        uint32_t done = atomicAdd(&ctr[2], 1u);
         if (done == gridDim.x - 1) {
-            *(volatile uint32_t *)d->epoch = s.epoch0 + barriersUsed;
-            *(volatile uint32_t *)d->launches = *(volatile uint32_t *)d->launches + halvesUsed;
-            *(volatile uint32_t *)d->blocksDone = 0u;
-            __threadfence();
-            atomicAdd_system((unsigned long long *)&d->opCounters[1], 1ull);
+            *(volatile uint32_t *)&ctr[0] = s.epoch0 + barriersUsed;
+            *(volatile uint32_t *)&ctr[1] = *(volatile uint32_t *)&ctr[1] + halvesUsed;
+            *(volatile uint32_t *)&ctr[2] = 0u;
+            atomicAdd(&DevOpCounters(d)[1], 1ull);
         }
     }
 }
@@ -212,11 +216,13 @@ __device__ __forceinline__ void GridCopy16(char *dst, const char *src, uint64_t 
     const uint64_t nvec = n >> 4;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
     uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    for (; i + 3 * stride < nvec; i += 4 * stride) {
-        uint4 a = Ld16Volatile(src + (i << 4)), b = Ld16Volatile(src + ((i + stride) << 4));
-        uint4 c = Ld16Volatile(src + ((i + 2 * stride) << 4)), e = Ld16Volatile(src + ((i + 3 * stride) << 4));
-        St16(dst + (i << 4), a); St16(dst + ((i + stride) << 4), b);
-        St16(dst + ((i + 2 * stride) << 4), c); St16(dst + ((i + 3 * stride) << 4), e);
+    // eight independent 16-byte loads per thread in flight: the copy is latency bound with the few CTAs it gets
+    for (; i + 7 * stride < nvec; i += 8 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = Ld16Volatile(src + ((i + u * stride) << 4));
+#pragma unroll
+        for (int u = 0; u < 8; ++u) St16(dst + ((i + u * stride) << 4), v[u]);
     }
     for (; i < nvec; i += stride) St16(dst + (i << 4), Ld16Volatile(src + (i << 4)));
     if (blockIdx.x == 0) {

@@ -12,6 +12,7 @@
 #include <unistd.h>
 
 #include <cstring>
+#include <map>
 #include <mutex>
 
 #include "../core/dtype.h"
@@ -156,6 +157,9 @@ __global__ void FlagWaitGeKernel(const uint64_t *flag, uint64_t expected, uint64
 thread_local int t_dev = -1;
 
 class CudaPlatform : public Platform {
+    std::mutex peekMu_;
+    std::map<int, cudaStream_t> peekStreams_;
+
 public:
     PlatKind kind() const override { return PlatKind::CUDA; }
     const char *name() const override { return "cuda-sm100"; }
@@ -302,6 +306,15 @@ public:
     HcclResult MemsetSync(void *ptr, int v, size_t bytes) override { CUDA_CHK(cudaMemset(ptr, v, bytes)); CUDA_CHK(cudaDeviceSynchronize()); return HCCL_SUCCESS; }
     HcclResult MemcpySync(void *dst, const void *src, size_t bytes) override { CUDA_CHK(cudaMemcpy(dst, src, bytes, cudaMemcpyDefault)); return HCCL_SUCCESS; }
 
+    HcclResult PeekSync(void *hostDst, const void *devSrc, size_t bytes) override
+    {
+        std::lock_guard<std::mutex> lk(peekMu_);
+        cudaStream_t &st = peekStreams_[CurrentDevice()];
+        if (!st) CUDA_CHK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+        CUDA_CHK(cudaMemcpyAsync(hostDst, devSrc, bytes, cudaMemcpyDeviceToHost, st));
+        CUDA_CHK(cudaStreamSynchronize(st));
+        return HCCL_SUCCESS;
+    }
     HcclResult StreamCreate(Stream *s) override { cudaStream_t st; CUDA_CHK(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking)); *s = st; return HCCL_SUCCESS; }
     HcclResult StreamDestroy(Stream s) override { CUDA_CHK(cudaStreamDestroy((cudaStream_t)s)); return HCCL_SUCCESS; }
     HcclResult StreamSync(Stream s) override { CUDA_CHK(cudaStreamSynchronize((cudaStream_t)s)); return HCCL_SUCCESS; }

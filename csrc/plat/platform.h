@@ -84,6 +84,9 @@ public:
     virtual HcclResult MemcpySync(void *dst, const void *src, size_t bytes) = 0;
 
     // ---- ordered execution
+    // Copies a few bytes of device memory to the host without touching the streams of the application (works while
+    // a kernel of the communicator is still running or stuck).
+    virtual HcclResult PeekSync(void *hostDst, const void *devSrc, size_t bytes) = 0;
     virtual HcclResult StreamCreate(Stream *s) = 0;
     virtual HcclResult StreamDestroy(Stream s) = 0;
     virtual HcclResult StreamSync(Stream s) = 0;

@@ -198,6 +198,7 @@ public:
     HcclResult MemsetSync(void *ptr, int v, size_t bytes) override { memset(ptr, v, bytes); return HCCL_SUCCESS; }
     HcclResult MemcpySync(void *dst, const void *src, size_t bytes) override { memmove(dst, src, bytes); return HCCL_SUCCESS; }
 
+    HcclResult PeekSync(void *hostDst, const void *devSrc, size_t bytes) override { memcpy(hostDst, devSrc, bytes); return HCCL_SUCCESS; }
     HcclResult StreamCreate(Stream *s) override { *s = new SimStream(); return HCCL_SUCCESS; }
     HcclResult StreamDestroy(Stream s) override { delete (SimStream *)s; return HCCL_SUCCESS; }
     HcclResult StreamSync(Stream s) override { if (s) ((SimStream *)s)->Sync(); return HCCL_SUCCESS; }
