@@ -148,7 +148,7 @@ void Builtin(TuneTable &t)
     for (uint32_t p = 2; p <= 16u; ++p) {
         std::string n = std::to_string(p);
         t.buckets["allreduce/" + n] = {{(p <= 4 ? 512 : 256) * KB, Algo::MESH_ONESHOT, Engine::SM_FAST, 0},
-                                       {p <= 3 ? UINT64_MAX : 4 * MB, Algo::MESH, Engine::SM_FAST, 0},   // 2 GPUs: the switch saves no traffic, the mesh kernel measured faster
+                                       {p <= 4 ? UINT64_MAX : 4 * MB, Algo::MESH, Engine::SM_FAST, 0},   // up to 4 GPUs the mesh kernel measured faster than in-switch reduction
                                        {UINT64_MAX, Algo::NVLS, Engine::NVLS, 0}};
         t.buckets["broadcast/" + n] = {{1 * MB, Algo::MESH_ONESHOT, Engine::SM_FAST, 0}, {UINT64_MAX, Algo::NVLS, Engine::NVLS, 0}};
         t.buckets["allgather/" + n] = {{UINT64_MAX, Algo::MESH, Engine::SM_FAST, 0}};

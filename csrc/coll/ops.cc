@@ -176,7 +176,7 @@ HcclResult FastReduceScatter(Comm *c, const OpDesc &d, const Selection &sel)
             a.sendDispls[q] = dsp[q] + c0;
         }
         a.out = (char *)d.out + c0 * esz;
-        CHK_RET(Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz), d.stream));
+        CHK_RET(Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz * std::max(1u, n - 1)), d.stream));   // bytes this rank moves
     }
     return HCCL_SUCCESS;
 }
@@ -202,7 +202,7 @@ HcclResult FastAllGather(Comm *c, const OpDesc &d, const Selection &sel)
             a.recvDispls[q] = dsp[q] + c0;
         }
         a.in = (const char *)d.in + c0 * esz;
-        CHK_RET(Launch(c, FK_ALLGATHER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz), d.stream));
+        CHK_RET(Launch(c, FK_ALLGATHER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz * std::max(1u, n - 1)), d.stream));   // bytes this rank moves
     }
     return HCCL_SUCCESS;
 }

@@ -396,6 +396,7 @@ Comm::~Comm()
     }
     if (heapPhys.bytes) plat->PhysRelease(&heapPhys);
     if (fusedParamRing) plat->DevFree(fusedParamRing);
+    if (fusedExpectRing) plat->DevFree(fusedExpectRing);
     if (devStruct) plat->DevFree(devStruct);
     if (devIrCounters) plat->DevFree(devIrCounters);
     if (abortWord) plat->HostFree(abortWord);

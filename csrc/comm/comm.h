@@ -130,7 +130,12 @@ struct Comm {
     uint64_t heapStride = 0, heapBytes = 0, halfBytes = 0;
     uint64_t p2pOffset = 0, p2pSlotBytes = 0;    // landing area of the send/recv kernels: one slot per source rank
     std::vector<uint64_t> p2pSent, p2pRecvd;     // chunks exchanged so far with each peer
-    uint32_t fusedRsSeq = 0, fusedAgSeq = 0;     // calls of the fused GEMM kernels so far (arrival counters only grow)
+    // Fused GEMM kernels: arrival counters in the control region only grow; the host keeps, per counter, the value that
+    // means "complete" for the next call (all ranks issue the same calls, so the tables agree) and hands the
+    // kernel a device copy of the slice it uses - shapes may change from call to call.
+    std::vector<uint32_t> fusedExpect;           // [8192]
+    void *fusedExpectRing = nullptr;             // device ring: 16 tables of 8192 u32
+    int fusedExpectNext = 0;
     void *fusedParamRing = nullptr;              // device ring of kernel parameter blocks
     int fusedParamNext = 0;
     bool lastOpOnHost = true;                    // the next specialised kernel must start with a barrier

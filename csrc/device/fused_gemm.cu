@@ -11,14 +11,14 @@
 //
 // AllGather -> GEMM  (column-parallel linear:  Y_r[M,N_r] = concat_q(x_q)[M,K] * W_r[N_r,K]^T)
 //   Two extra warps per CTA push this rank's activation shard into every peer's staging (nearest consumer
-//   first, 32-row pieces, one arrival counter per 128-row block), while the GEMM starts on the local
+//   first, 32 KB chunks, one arrival counter per 128-row block), while the GEMM starts on the local
 //   shard.  The TMA producer of a tile whose rows come from rank q waits for that block's counter, then
 //   loads from the local staging copy - TMA never reads peer memory.  Blocks are consumed in the order
 //   own, r-1, r-2, ... which is the order in which peers send them.
 //
 // Both follow the CCL-buffer protocol of the collective kernels (launch parity selects the half, every
 // rank waits for every other rank once per call), so they interleave freely with other operators.
-// Arrival counters only grow: the value expected in call number s is s * (pieces per block).
+// Arrival counters only grow: the host keeps the value each counter reaches in the next call and passes the table.
 // With several ranks sharing one GPU (tests) all ranks run in one cooperative launch, gridDim.y = ranks.
 #include <cuda_runtime.h>
 
@@ -39,7 +39,8 @@ using namespace hcgemm;
 constexpr int kFusedThreads = 256;          // 6 GEMM warps + 2 communication warps
 constexpr int kRsFlagBase = 0;              // u32 indices inside HC_OFF_FUSED
 constexpr int kAgFlagBase = 4096;
-constexpr int kAgParts = 4;                 // 32-row pieces per 128-row block
+constexpr size_t kAgChunkBytes = 32 << 10;  // unit of the all-gather push: one warp moves one chunk, then bumps the block's counter
+constexpr int kFlagCount = 8192;
 
 struct FusedParams {
     CUtensorMap tmA, tmB, tmA2, tmA2b;   // tmA2 / tmA2b: staging copy of A in CCL half 0 / 1
@@ -49,7 +50,7 @@ struct FusedParams {
     const void *xLocal;       // AG: this rank's shard
     int ldOut;
     int mbPer;                // 128-row blocks per rank
-    uint32_t expected;        // arrival-counter value that means "complete" in this call
+    const uint32_t *expect;   // per arrival counter: the value that means "complete" in this call (indexed like the counters)
     int rowsPer;              // rows per rank
     int K;
 };
@@ -86,7 +87,8 @@ struct RsEpilogue {
     const CommDev *d;
     __nv_bfloat16 *out;
     int ldOut, N, mbPer, rowsPer, tilesN;
-    uint32_t half, expected;
+    uint32_t half;
+    const uint32_t *expect;
     volatile uint32_t *abortFlag;
 
     __device__ __forceinline__ char *Slot(int owner, int src) const
@@ -99,7 +101,7 @@ struct RsEpilogue {
         if (q != d->rank) return;
         // my own rows: every peer's partial of this tile must have landed
         const int idx = kRsFlagBase + (mb % mbPer) * tilesN + nb;
-        if ((threadIdx.x & 31) == 0) hcdev::WaitFlagGe32(d, FusedFlag(d, d->rank, idx), expected, 0, HC_WAIT_TILE_FLAG, (uint32_t)idx);
+        if ((threadIdx.x & 31) == 0) hcdev::WaitFlagGe32(d, FusedFlag(d, d->rank, idx), expect[idx], 0, HC_WAIT_TILE_FLAG, (uint32_t)idx);
         __syncwarp();
     }
     __device__ __forceinline__ void Fragment(int mb, int, int row, int col, const uint32_t (&f)[32]) const
@@ -121,28 +123,43 @@ struct RsEpilogue {
             }
             return;
         }
-        // reduce in ascending rank order, my own accumulator taking its place in the sequence
+        // reduce in ascending rank order, my own accumulator taking its place in the sequence; the partials of up to
+        // four peers are fetched together (16 loads in flight per thread) before they are added
         float acc[32];
         bool first = true;
-        for (int r = 0; r < d->nRanks; ++r) {
-            if (r == me) {
+        const int n = d->nRanks;
+        for (int base = 0; base < n; base += 4) {
+            uint4 pk[4][4];
 #pragma unroll
-                for (int j = 0; j < 32; ++j) acc[j] = first ? __uint_as_float(f[j]) : acc[j] + __uint_as_float(f[j]);
-            } else {
-                const char *src = Slot(me, r) + ((size_t)rowLocal * N + col) * sizeof(__nv_bfloat16);
+            for (int k = 0; k < 4; ++k) {
+                const int r = base + k;
+                if (r < n && r != me) {
+                    const char *src = Slot(me, r) + ((size_t)rowLocal * N + col) * sizeof(__nv_bfloat16);
 #pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    uint4 pk = hcdev::Ld16Volatile(src + v * 16);
-                    const __nv_bfloat162 *ph = (const __nv_bfloat162 *)&pk;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float2 x = __bfloat1622float2(ph[j]);
-                        acc[v * 8 + 2 * j] = first ? x.x : acc[v * 8 + 2 * j] + x.x;
-                        acc[v * 8 + 2 * j + 1] = first ? x.y : acc[v * 8 + 2 * j + 1] + x.y;
-                    }
+                    for (int v = 0; v < 4; ++v) pk[k][v] = hcdev::Ld16Volatile(src + v * 16);
                 }
             }
-            first = false;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int r = base + k;
+                if (r >= n) break;
+                if (r == me) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[j] = first ? __uint_as_float(f[j]) : acc[j] + __uint_as_float(f[j]);
+                } else {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const __nv_bfloat162 *ph = (const __nv_bfloat162 *)&pk[k][v];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            float2 x = __bfloat1622float2(ph[j]);
+                            acc[v * 8 + 2 * j] = first ? x.x : acc[v * 8 + 2 * j] + x.x;
+                            acc[v * 8 + 2 * j + 1] = first ? x.y : acc[v * 8 + 2 * j + 1] + x.y;
+                        }
+                    }
+                }
+                first = false;
+            }
         }
         __nv_bfloat16 *dst = out + (size_t)rowLocal * ldOut + col;
 #pragma unroll
@@ -176,7 +193,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(cons
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
-    RsEpilogue<BN> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, p.expected, nullptr};
+    RsEpilogue<BN> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, p.expect, nullptr};
     GemmMainLoop<BN>(&p.tmA, &p.tmB, p.shape, order, NoGate(), epi);
     hcdev::KernelEnd(d, ls, 0);
 }
@@ -198,7 +215,7 @@ struct AgOrder {
 struct AgGate {
     const CommDev *d;
     int mbPer;
-    uint32_t expected;
+    const uint32_t *expect;
     __device__ __forceinline__ bool operator()(int mb, int, volatile uint32_t *abortFlag, int *aRow, const CUtensorMap *own, const CUtensorMap *staged,
                                                const CUtensorMap **use) const
     {
@@ -211,7 +228,7 @@ struct AgGate {
         *use = staged;
         *aRow = mb * kBlockM;
         const int idx = kAgFlagBase + mb;
-        if (!hcdev::WaitFlagGe32(d, FusedFlag(d, d->rank, idx), expected, (uint32_t)src, HC_WAIT_TILE_FLAG, (uint32_t)idx)) {
+        if (!hcdev::WaitFlagGe32(d, FusedFlag(d, d->rank, idx), expect[idx], (uint32_t)src, HC_WAIT_TILE_FLAG, (uint32_t)idx)) {
             *abortFlag = 1;
             return false;
         }
@@ -230,27 +247,30 @@ struct AgPush {
     __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *) const
     {
         const int n = d->nRanks, me = d->rank;
-        const int items = (n - 1) * mbPer * kAgParts;
-        const int warps = gridDim.x * 2;
         const size_t rowBytes = (size_t)K * sizeof(__nv_bfloat16);
-        const size_t pieceBytes = (size_t)(kBlockM / kAgParts) * rowBytes;
+        const size_t blockBytes = (size_t)kBlockM * rowBytes;                     // a multiple of 2 KB (K is a multiple of 8)
+        const int chunksPerBlock = (int)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes);
+        const int perPeer = mbPer * chunksPerBlock;
+        const int items = (n - 1) * perPeer;
+        const int warps = gridDim.x * 2;
+        // peer-major order: everything for the nearest consumer first; consecutive warps take consecutive chunks
         for (int it = blockIdx.x * 2 + warpInRole; it < items; it += warps) {
-            const int peerIdx = it / (mbPer * kAgParts), rem = it % (mbPer * kAgParts);
-            const int blk = rem / kAgParts, part = rem % kAgParts;
+            const int peerIdx = it / perPeer, rem = it % perPeer;
+            const int blk = rem / chunksPerBlock, ch = rem % chunksPerBlock;
             const int peer = (me + 1 + peerIdx) % n;
-            const size_t off = ((size_t)blk * kBlockM + (size_t)part * (kBlockM / kAgParts)) * rowBytes;
+            const size_t off = (size_t)blk * blockBytes + (size_t)ch * kAgChunkBytes;
+            const size_t len = blockBytes - (size_t)ch * kAgChunkBytes < kAgChunkBytes ? blockBytes - (size_t)ch * kAgChunkBytes : kAgChunkBytes;
             const char *src = x + off;
-            char *dst = hcdev::CclHalf(d, peer, half) + (size_t)me * mbPer * kBlockM * rowBytes + off;
-            for (size_t b = (size_t)lane * 16; b < pieceBytes; b += 32 * 16 * 4) {
-                uint4 v0 = hcdev::Ld16(src + b), v1, v2, v3;
-                const bool h1 = b + 512 < pieceBytes, h2 = b + 1024 < pieceBytes, h3 = b + 1536 < pieceBytes;
-                if (h1) v1 = hcdev::Ld16(src + b + 512);
-                if (h2) v2 = hcdev::Ld16(src + b + 1024);
-                if (h3) v3 = hcdev::Ld16(src + b + 1536);
-                hcdev::St16(dst + b, v0);
-                if (h1) hcdev::St16(dst + b + 512, v1);
-                if (h2) hcdev::St16(dst + b + 1024, v2);
-                if (h3) hcdev::St16(dst + b + 1536, v3);
+            char *dst = hcdev::CclHalf(d, peer, half) + (size_t)me * mbPer * blockBytes + off;
+            // eight 16-byte loads per lane in flight (4 KB per warp and step)
+            for (size_t b = (size_t)lane * 16; b < len; b += 32 * 16 * 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (b + (size_t)u * 512 < len) v[u] = hcdev::Ld16(src + b + (size_t)u * 512);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (b + (size_t)u * 512 < len) hcdev::St16(dst + b + (size_t)u * 512, v[u]);
             }
             __syncwarp();
             if (lane == 0) {
@@ -268,7 +288,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) AllGatherGemmKernel(const Fu
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     AgOrder order{d->rank, d->nRanks, p.mbPer};
-    AgGate gate{d, p.mbPer, p.expected};
+    AgGate gate{d, p.mbPer, p.expect};
     AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
     GemmMainLoop<BN>(&p.tmA, &p.tmB, p.shape, order, gate, epi, ls.half ? &p.tmA2b : &p.tmA2, push);
@@ -285,6 +305,20 @@ FusedParams *ParamSlot(Comm *c)
     FusedParams *p = (FusedParams *)c->fusedParamRing + c->fusedParamNext;
     c->fusedParamNext = (c->fusedParamNext + 1) % 64;
     return p;
+}
+
+// Adds `units` to the expected value of counters [lo, hi) and returns a device table (indexed like the counters) that
+// holds the new values for that range; the copy is ordered on the operator's stream.
+const uint32_t *ExpectTable(Comm *c, int lo, int hi, uint32_t units, void *stream, int skipLo = 0, int skipHi = 0)
+{
+    if (c->fusedExpect.empty()) c->fusedExpect.assign(kFlagCount, 0u);
+    if (!c->fusedExpectRing && cudaMalloc(&c->fusedExpectRing, sizeof(uint32_t) * kFlagCount * 16) != cudaSuccess) return nullptr;
+    for (int i = lo; i < hi; ++i)
+        if (i < skipLo || i >= skipHi) c->fusedExpect[i] += units;      // [skipLo, skipHi): counters nobody bumps in this call
+    uint32_t *slot = (uint32_t *)c->fusedExpectRing + (size_t)c->fusedExpectNext * kFlagCount;
+    c->fusedExpectNext = (c->fusedExpectNext + 1) % 16;
+    if (cudaMemcpyAsync(slot + lo, c->fusedExpect.data() + lo, sizeof(uint32_t) * (size_t)(hi - lo), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess) return nullptr;
+    return slot;
 }
 
 template <typename KernelT>
@@ -354,7 +388,8 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     CHK_RET(MakeTensorMap2dBf16(&hp.tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN, kBlockK));
     hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / kBlockM; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / kBlockM; hp.rowsPer = rowsPer; hp.K = K;
-    hp.expected = ++c->fusedRsSeq * (uint32_t)(p - 1);
+    hp.expect = ExpectTable(c, kRsFlagBase, kRsFlagBase + (rowsPer / kBlockM) * (N / BN), (uint32_t)(p - 1), stream);
+    if (!hp.expect) return HCCL_E_RUNTIME;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
@@ -388,7 +423,10 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     CHK_RET(MakeTensorMap2dBf16(&hp.tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)BN, kBlockK));
     hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / kBlockM; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = Mshard / kBlockM; hp.rowsPer = Mshard; hp.K = K; hp.xLocal = x;
-    hp.expected = ++c->fusedAgSeq * (uint32_t)kAgParts;
+    const uint64_t blockBytes = (uint64_t)kBlockM * K * 2;
+    hp.expect = ExpectTable(c, kAgFlagBase, kAgFlagBase + M / kBlockM, (uint32_t)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes), stream,
+                            kAgFlagBase + (int)c->rank * (Mshard / kBlockM), kAgFlagBase + ((int)c->rank + 1) * (Mshard / kBlockM));   // my own blocks are not sent to me
+    if (!hp.expect) return HCCL_E_RUNTIME;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     if (BN == 256) return LaunchFused(c, AllGatherGemmKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9003, stream);

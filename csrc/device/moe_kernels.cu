@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
     const int E = p.lay.numExperts, El = E / n, K = p.lay.topk, H = p.lay.hidden;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int warpsPerCta = blockDim.x >> 5;
-    __shared__ uint32_t sBase[kMaxExperts];
+    __shared__ uint32_t sBase[kMaxExperts], sTot[kMaxExperts];
     uint32_t *hist = p.scratch, *cursor = p.scratch + E;
 
     // 1. histogram
@@ -99,30 +99,49 @@ __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
         for (int e = tid; e < E; e += blockDim.x) Counts(p, e / El)[me * El + (e % El)] = hist[e];
         CrossRankBarrier(d, ls.epoch0 + used);
         // the offsets of my own experts for the grouped GEMM that follows (the table may be overwritten by a
-        // peer's next dispatch as soon as this kernel's last barrier is passed, so derive them now)
-        if (tid == 0) {
+        // peer's next dispatch as soon as this kernel's last barrier is passed, so derive them now): one thread per
+        // local expert sums its column, thread 0 turns the sums into a prefix
+        for (int el = tid; el < El; el += blockDim.x) {
             const volatile uint32_t *c = Counts(p, me);
+            uint32_t sum = 0;
+            for (int s = 0; s < n; ++s) sum += c[s * El + el];
+            sTot[el] = sum;
+        }
+        __syncthreads();
+        if (tid == 0) {
             uint32_t acc = 0;
             uint32_t *off = ExpertOffsets(p, me);
             for (int el = 0; el < El; ++el) {
                 off[el] = acc;
-                for (int s = 0; s < n; ++s) acc += c[s * El + el];
+                acc += sTot[el];
             }
             off[El] = acc < (uint32_t)p.lay.maxRecvRows ? acc : (uint32_t)p.lay.maxRecvRows;
         }
+        __syncthreads();
     }
     grid.sync();
 
     // 3. where do my rows of expert e start at its owner?  before them: all rows of the owner's earlier experts,
-    //    and the rows of this expert that come from lower ranks
+    //    and the rows of this expert that come from lower ranks.  One thread per expert fetches that expert's n
+    //    counts from the owner (independent loads, one NVLink round trip), then the prefix runs on shared memory.
     for (int e = tid; e < E; e += blockDim.x) {
         const int owner = e / El, el = e % El;
         const volatile uint32_t *c = Counts(p, owner);
+        uint32_t total = 0, below = 0;
+        for (int s = 0; s < n; ++s) {
+            const uint32_t v = c[s * El + el];
+            total += v;
+            if (s < me) below += v;
+        }
+        sTot[e] = total;
+        sBase[e] = below;
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) {
+        const int first = (e / El) * El;
         uint32_t base = 0;
-        for (int e2 = 0; e2 < el; ++e2)
-            for (int s = 0; s < n; ++s) base += c[s * El + e2];
-        for (int s = 0; s < me; ++s) base += c[s * El + el];
-        sBase[e] = base;
+        for (int e2 = first; e2 < e; ++e2) base += sTot[e2];
+        sBase[e] += base;       // only this thread touches sBase[e]; sTot is read-only here
     }
     __syncthreads();
 

@@ -84,7 +84,7 @@ def main():
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--buffer-mb", type=int, default=200)
+    ap.add_argument("--buffer-mb", type=int, default=512)
     ap.add_argument("--algo", default=None)
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--out", default=None)

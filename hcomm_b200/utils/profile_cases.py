@@ -1,0 +1,122 @@
+"""Small, self-terminating workloads for kernel profilers (one GPU, one process).
+
+    python -m hcomm_b200.utils.profile_cases gemm            tcgen05 GEMM 8192^3 bf16 (operands larger than L2)
+    python -m hcomm_b200.utils.profile_cases fused           GEMM->ReduceScatter and AllGather->GEMM, two ranks sharing the GPU
+    python -m hcomm_b200.utils.profile_cases allreduce       one-shot, two-shot all-reduce and all-gather kernels, two ranks sharing the GPU
+    python -m hcomm_b200.utils.profile_cases moe             MoE dispatch + combine, one rank (256 experts, top-8, hidden 7168)
+
+Ranks that share the GPU run inside ONE cooperative launch (kernels that wait for each other are never separate
+launches on a GPU), so each case is a single process a profiler can wrap.  A few launches per kernel, a few hundred
+MB on the device at most.
+"""
+from __future__ import annotations
+
+import sys
+import threading
+
+import torch
+
+
+def _ranks(n, fn):
+    errs = []
+
+    def wrap(r):
+        try:
+            torch.cuda.set_device(0)
+            fn(r)
+        except BaseException as e:  # noqa: BLE001
+            errs.append(e)
+    ts = [threading.Thread(target=wrap, args=(r,)) for r in range(n)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    if errs:
+        raise errs[0]
+
+
+def case_gemm(reps=3):
+    from ..ops.gemm import gemm_bf16, take_kernel_error
+    a = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(8192, 8192, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(8192, 8192, device="cuda", dtype=torch.bfloat16)
+    for _ in range(reps):
+        gemm_bf16(a, w, out)
+    torch.cuda.synchronize()
+    assert take_kernel_error() == 0
+
+
+def _comms(n, buffer_mb):
+    import hcomm_b200 as hb
+    info = hb.get_root_info()
+    comms = [None] * n
+    _ranks(n, lambda r: comms.__setitem__(r, hb.Communicator(n, info, r, buffer_mb=buffer_mb)))
+    return comms
+
+
+def case_fused(reps=2):
+    from ..ops.fused import all_gather_gemm, gemm_reduce_scatter
+    from ..ops.gemm import take_kernel_error
+    n, m, nn, k = 2, 4096, 4096, 4096
+    comms = _comms(n, 96)
+    a = [torch.randn(m, k, device="cuda").to(torch.bfloat16) for _ in range(n)]
+    b = [(torch.randn(nn, k, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(n)]
+    x = [torch.randn(m // n, k, device="cuda").to(torch.bfloat16) for _ in range(n)]
+
+    def op(r):
+        for _ in range(reps):
+            gemm_reduce_scatter(comms[r], a[r], b[r])
+            all_gather_gemm(comms[r], x[r], b[r])
+        torch.cuda.synchronize()
+    _ranks(n, op)
+    assert take_kernel_error() == 0
+    _ranks(n, lambda r: comms[r].destroy())
+
+
+def case_allreduce(reps=2):
+    n = 2
+    comms = _comms(n, 64)
+    small = [torch.randn(16 << 10, device="cuda").to(torch.bfloat16) for _ in range(n)]       # 32 KB: one-shot
+    big = [torch.randn(32 << 20, device="cuda").to(torch.bfloat16) for _ in range(n)]         # 64 MB: two-shot
+    outs = [torch.empty_like(big[r]) for r in range(n)]
+    gathered = [torch.empty(n * (16 << 20), device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+
+    def op(r):
+        for _ in range(reps):
+            comms[r].all_reduce(small[r], outs[r][: small[r].numel()])
+            comms[r].all_reduce(big[r], outs[r])
+            comms[r].all_gather(big[r][: 16 << 20], gathered[r])
+        torch.cuda.synchronize()
+    _ranks(n, op)
+    _ranks(n, lambda r: comms[r].destroy())
+
+
+def case_moe(reps=2):
+    import hcomm_b200 as hb
+    from ..ops.moe import MoeExchange
+    comm = hb.Communicator(1, hb.get_root_info(), 0, buffer_mb=8)
+    e, k, h, t = 256, 8, 7168, 4096
+    moe = MoeExchange(comm, e, k, h, t)
+    x = torch.randn(t, h, device="cuda").to(torch.bfloat16)
+    top = torch.randn(t, e, device="cuda").topk(k, dim=1)
+    idx, gates = top.indices.to(torch.int32).contiguous(), torch.softmax(top.values, 1).float().contiguous()
+    for _ in range(reps):
+        rec = moe.dispatch(x, idx)
+        torch.cuda.synchronize()
+        y = torch.zeros(rec.num_rows, h, device="cuda", dtype=torch.bfloat16)
+        moe.combine(y, gates)
+    torch.cuda.synchronize()
+    assert moe.overflow() == 0
+    moe.destroy()
+    comm.destroy()
+
+
+def main():
+    torch.cuda.set_device(0)
+    which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    {"gemm": case_gemm, "fused": case_fused, "allreduce": case_allreduce, "moe": case_moe}[which]()
+    print(f"profile case {which}: done", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -25,16 +25,21 @@ def l2_flush(device=None):
 
 
 def time_cuda(fn, iters: int = 10, warmup: int = 3, flush: bool = True, barrier=None):
-    """Median and minimum milliseconds of fn() over `iters` runs."""
+    """Median and minimum milliseconds of fn() over `iters` runs.
+
+    Per iteration: ranks meet (host barrier), the L2 flush is queued, then start event, fn(), stop event.  The flush
+    keeps the GPU busy while the host enqueues fn, so the interval between the events is device time of fn, not the
+    host's launch path; it also makes every iteration start from a cold L2.
+    """
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     times = []
     for _ in range(iters):
-        if flush:
-            l2_flush()
         if barrier is not None:
             barrier()
+        if flush:
+            l2_flush()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         fn()

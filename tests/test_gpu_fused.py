@@ -98,3 +98,39 @@ def test_fused_ops_interleave_with_collectives(n=2):
             assert torch.allclose(res[r][0].float(), ref1[r * 128:(r + 1) * 128], atol=0.6, rtol=3e-2)
     finally:
         run_ranks(n, lambda r: comms[r].destroy())
+
+
+def test_fused_ops_with_changing_shapes():
+    """Arrival counters are shared by all calls on a communicator: shapes that change from call to call (other
+    numbers of tiles and row blocks) must not disturb each other."""
+    from hcomm_b200.ops.fused import all_gather_gemm, gemm_reduce_scatter
+    from hcomm_b200.ops.gemm import take_kernel_error
+    n = 2
+    comms = _make(n, 16)
+    try:
+        torch.manual_seed(5)
+        shapes = [(512, 512, 256), (256, 256, 128), (1024, 256, 192), (512, 512, 256), (256, 768, 64)]
+        for i, (m, nn, k) in enumerate(shapes):
+            a = [torch.randn(m, k, device="cuda").to(torch.bfloat16) for _ in range(n)]
+            b = [(torch.randn(nn, k, device="cuda") * 0.1).to(torch.bfloat16) for _ in range(n)]
+            x = [torch.randn(m // n, k, device="cuda").to(torch.bfloat16) for _ in range(n)]
+            outs, outs2 = [None] * n, [None] * n
+
+            def op(r):
+                torch.cuda.set_device(0)
+                outs[r] = gemm_reduce_scatter(comms[r], a[r], b[r])
+                outs2[r] = all_gather_gemm(comms[r], x[r], b[r])
+                torch.cuda.synchronize()
+            run_ranks(n, op)
+            assert take_kernel_error() == 0, i
+            ref = sum(a[r].float() @ b[r].float().t() for r in range(n))
+            rows = m // n
+            xa = torch.cat(x).float()
+            for r in range(n):
+                err = (outs[r].float() - ref[r * rows:(r + 1) * rows]).abs().max().item()
+                assert err <= 2e-2 * max(1.0, ref.abs().max().item()), ("rs", i, r, err)
+                ref2 = xa @ b[r].float().t()
+                err2 = (outs2[r].float() - ref2).abs().max().item()
+                assert err2 <= 2e-2 * max(1.0, ref2.abs().max().item()), ("ag", i, r, err2)
+    finally:
+        run_ranks(n, lambda r: comms[r].destroy())
