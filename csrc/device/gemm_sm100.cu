@@ -7,6 +7,7 @@
 #include "../core/log.h"
 #include "gemm_api.h"
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2sm.cuh"
 
 namespace hc {
 
@@ -21,6 +22,33 @@ __global__ void __launch_bounds__(hcgemm::kThreads, 1)
 GemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16 epi)
 {
     hcgemm::GemmMainLoop<BN>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < 16 ? shape.tilesM : 16}, hcgemm::NoGate(), epi);
+}
+// CTA-pair variant: 256 x 256 tiles, launched as clusters of two CTAs (see gemm_sm100_2sm.cuh).
+template <int BN>
+__global__ void __launch_bounds__(hcgemm::kThreads, 1)
+GemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16 epi)
+{
+    hcgemm::GemmMainLoopPair<BN>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < 8 ? shape.tilesM : 8}, epi);
+}
+
+// Clusters of two CTAs that can be resident at once (0 when the query fails).
+int PairClusterCapacity()
+{
+    static int cap = -1;
+    if (cap >= 0) return cap;
+    cudaFuncSetAttribute(GemmBf16PairKernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256>::kSmemBytes);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 148, 1, 1);
+    cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = hcgemm::Config2<256>::kSmemBytes;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, GemmBf16PairKernel<256>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    cap = n;
+    return cap;
 }
 }  // namespace
 
@@ -85,6 +113,34 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
     if (N % 8 != 0 || K % 8 != 0 || ((uintptr_t)C & 15) != 0 || (ldc % 8) != 0) {
         HCCL_ERROR("GemmBf16: N, K and ldc must be multiples of 8 and C 16-byte aligned (N=%d K=%d ldc=%d)", N, K, ldc);
         return HCCL_E_PARA;
+    }
+    static const bool pairEnabled = [] { const char *e = getenv("HCOMM_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    if (pairEnabled && M % hcgemm::kPairM == 0 && N % 256 == 0 && PairClusterCapacity() > 0) {
+        CUtensorMap tmA, tmB;
+        CHK_RET(MakeTensorMap2dBf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, hcgemm::kBlockM, hcgemm::kBlockK));
+        CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 128, hcgemm::kBlockK));
+        hcgemm::GemmShape shape;
+        shape.M = M; shape.N = N; shape.K = K;
+        shape.tilesM = M / hcgemm::kPairM;
+        shape.tilesN = N / 256;
+        shape.errFlag = GemmErrorFlag();
+        hcgemm::StoreBf16 epi{(__nv_bfloat16 *)C, ldc, M, N};
+        const int clusters = std::min(PairClusterCapacity(), shape.tilesM * shape.tilesN);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * clusters, 1, 1);
+        cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
+        cfg.dynamicSmemBytes = hcgemm::Config2<256>::kSmemBytes;
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256>, tmA, tmB, shape, epi);
+        if (e != cudaSuccess) {
+            HCCL_ERROR("GemmBf16 (CTA pairs) launch failed: %s", cudaGetErrorString(e));
+            return HCCL_E_RUNTIME;
+        }
+        return HCCL_SUCCESS;
     }
     const int BN = (N % 256 == 0 || N >= 2048) ? 256 : 128;
     CUtensorMap tmA, tmB;

@@ -1,0 +1,228 @@
+// gemm_sm100_2sm.cuh - the persistent bf16 GEMM main loop on CTA pairs (tcgen05 cta_group::2).
+//
+// Two CTAs on neighbouring SMs form a cluster and compute one 256 x 256 tile together:
+//   * CTA r of the pair loads rows [r*128, r*128+128) of the A tile and rows [r*128, r*128+128) of the B tile
+//     (half of the 256 output columns) - 32 KB per CTA and k-block instead of the 48 KB a lone CTA needs for a
+//     128 x 256 tile, so the operand traffic L2 -> shared memory per FLOP drops by a third and the ring holds six
+//     stages instead of four;
+//   * one thread of the leader CTA (cluster rank 0) issues tcgen05.mma.cta_group::2 with M = 256: each SM's tensor
+//     core produces its own 128 accumulator rows in its own tensor memory and reads the other half of B from the
+//     peer's shared memory;
+//   * all four TMA loads of a stage complete on the LEADER's "full" mbarrier (loads carry .cta_group::2, which
+//     allows the barrier to live in the peer CTA; no load carries a multicast qualifier);
+//   * tcgen05.commit with a two-CTA mask releases the stage ("empty") and publishes the accumulator
+//     ("tmemFull") in both CTAs at once; the epilogue warps of both CTAs hand the accumulator back on the
+//     leader's "tmemEmpty" barrier (remote mbarrier arrive for the peer).
+// Policies (TileOrder, Epilogue) are the ones of gemm_sm100.cuh; tile row blocks here are 256 rows tall.
+// Every wait is bounded; the CTAs of a pair always meet at the final cluster barrier before either exits.
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace hcgemm {
+
+constexpr int kPairM = 256;
+
+template <int BN> struct Config2 {
+    static_assert(BN == 256, "the pair kernel is built for 256 x 256 tiles");
+    static constexpr int kStages = 6;
+    static constexpr int kABytes = kBlockM * kBlockK * 2;          // 128 rows of A per CTA
+    static constexpr int kBBytes = (BN / 2) * kBlockK * 2;         // 128 of the 256 B rows per CTA
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+};
+
+namespace pair {
+
+__device__ __forceinline__ uint32_t ClusterCtaRank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t ClusterId()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t NumClusters()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void ClusterSync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `p` (a shared-memory object of this CTA) as seen in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t MapToCta(const void *p, uint32_t rank)
+{
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(SmemAddr(p)), "r"(rank));
+    return out;
+}
+__device__ __forceinline__ void RemoteArrive(uint32_t clusterAddr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+// 2-D tiled load into this CTA's shared memory; completion is signalled on `barClusterAddr`, which may be the
+// leader CTA's barrier.
+__device__ __forceinline__ void TmaLoad2dPair(void *smemDst, const CUtensorMap *m, uint32_t barClusterAddr, int32_t x, int32_t y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(SmemAddr(smemDst)), "l"(m), "r"(barClusterAddr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void TmemAlloc2(uint32_t *smemResult, uint32_t nCols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(SmemAddr(smemResult)), "r"(nCols) : "memory");
+}
+__device__ __forceinline__ void TmemRelinquish2() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void TmemDealloc2(uint32_t taddr, uint32_t nCols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(nCols) : "memory");
+}
+__device__ __forceinline__ void MmaBf16Pair(uint32_t tmemD, uint64_t descA, uint64_t descB, uint32_t idesc, bool accumulate)
+{
+    uint32_t acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmemD), "l"(descA), "l"(descB), "r"(idesc), "r"(acc) : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in BOTH CTAs once all MMAs issued so far have finished.
+__device__ __forceinline__ void MmaCommitPair(uint64_t *bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(SmemAddr(bar)), "h"(mask) : "memory");
+}
+
+}  // namespace pair
+
+// g.tilesM counts 256-row blocks here.  Launch with a cluster of two CTAs along x and an even grid.
+template <int BN, typename TileOrder, typename Epilogue>
+__device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const CUtensorMap *tmB, const GemmShape &g, TileOrder order, Epilogue epi)
+{
+    using Cfg = Config2<BN>;
+    using namespace pair;
+    extern __shared__ uint8_t smemRaw[];
+    uint8_t *smem = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
+    SharedState *st = (SharedState *)(smem + Cfg::kStages * Cfg::kStageBytes);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t ctaRank = ClusterCtaRank();
+    const bool leader = ctaRank == 0;
+    const int numTiles = g.tilesM * g.tilesN;
+    const int kBlocks = (g.K + kBlockK - 1) / kBlockK;
+    const int firstTile = (int)ClusterId(), tileStep = (int)NumClusters();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < Cfg::kStages; ++s) { MbarInit(&st->full[s], 1); MbarInit(&st->empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { MbarInit(&st->tmemFull[a], 1); MbarInit(&st->tmemEmpty[a], 8); }   // 4 epilogue warps x 2 CTAs
+        st->abort = 0;
+        MbarFenceInit();
+        TmaPrefetchDescriptor(tmA);
+        TmaPrefetchDescriptor(tmB);
+    }
+    if (warp == 1) {
+        TmemAlloc2(&st->tmemBase, Cfg::kTmemCols);
+        TmemRelinquish2();
+    }
+    TcFenceBefore();
+    __syncthreads();
+    ClusterSync();          // the peer's barriers are initialised before anything signals them
+    TcFenceAfter();
+    const uint32_t tmemBase = st->tmemBase;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (ElectOne()) {
+            uint32_t it = 0;
+            bool alive = true;
+            for (int t = firstTile; t < numTiles && alive; t += tileStep) {
+                int mb, nb;
+                order(t, g, &mb, &nb);
+                const int aRow = mb * kPairM + (int)ctaRank * kBlockM;
+                const int bRow = nb * BN + (int)ctaRank * (BN / 2);
+                for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const uint32_t ph = (it / Cfg::kStages) & 1;
+                    if (!MbarWait(&st->empty[s], ph ^ 1, &st->abort)) { alive = false; break; }
+                    uint8_t *sa = smem + s * Cfg::kStageBytes, *sb = sa + Cfg::kABytes;
+                    if (leader) MbarExpectTx(&st->full[s], 2 * Cfg::kStageBytes);      // both CTAs' loads land on this barrier
+                    const uint32_t bar = MapToCta(&st->full[s], 0);
+                    TmaLoad2dPair(sa, tmA, bar, kb * kBlockK, aRow);
+                    TmaLoad2dPair(sb, tmB, bar, kb * kBlockK, bRow);
+                }
+            }
+            // After a wait that ran out, copies already issued still write into this CTA's shared memory.  They take
+            // microseconds; the CTA stays for a fixed, much longer time before it goes on to the exit barrier.
+            if (!alive) __nanosleep(500000);
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (leader && ElectOne()) {
+            constexpr uint32_t idesc = InstrDescBf16(kPairM, BN);
+            uint32_t it = 0, tileIter = 0;
+            bool alive = true;
+            for (int t = firstTile; t < numTiles && alive; t += tileStep, ++tileIter) {
+                const uint32_t acc = tileIter & 1, accPh = (tileIter >> 1) & 1;
+                if (!MbarWait(&st->tmemEmpty[acc], accPh ^ 1, &st->abort)) { alive = false; break; }
+                TcFenceAfter();
+                const uint32_t tmemD = tmemBase + acc * BN;
+                for (int kb = 0; kb < kBlocks; ++kb, ++it) {
+                    const int s = it % Cfg::kStages;
+                    const uint32_t ph = (it / Cfg::kStages) & 1;
+                    if (!MbarWait(&st->full[s], ph, &st->abort)) { alive = false; break; }
+                    TcFenceAfter();
+                    uint8_t *sa = smem + s * Cfg::kStageBytes, *sb = sa + Cfg::kABytes;
+                    const uint64_t da = SmemDescKMajorSw128(sa), db = SmemDescKMajorSw128(sb);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / kUmmaK; ++k) MmaBf16Pair(tmemD, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb | k) != 0);
+                    MmaCommitPair(&st->empty[s]);
+                }
+                if (alive) MmaCommitPair(&st->tmemFull[acc]);
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------------- epilogue (both CTAs)
+        const int q = warp & 3;
+        uint32_t tileIter = 0;
+        bool alive = true;
+        for (int t = firstTile; t < numTiles && alive; t += tileStep, ++tileIter) {
+            int mb, nb;
+            order(t, g, &mb, &nb);
+            const uint32_t acc = tileIter & 1, accPh = (tileIter >> 1) & 1;
+            if (!MbarWait(&st->tmemFull[acc], accPh, &st->abort)) { alive = false; break; }
+            TcFenceAfter();
+            const int row = mb * kPairM + (int)ctaRank * kBlockM + q * 32 + lane;
+            epi.BeginTile(mb, nb, row);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t frag[32];
+                TmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + acc * BN + c, frag);
+                TmemLoadWait();
+                epi.Fragment(mb, nb, row, nb * BN + c, frag);
+            }
+            TcFenceBefore();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) MbarArrive(&st->tmemEmpty[acc]);
+                else RemoteArrive(MapToCta(&st->tmemEmpty[acc], 0));
+            }
+            epi.EndTile(mb, nb, row);
+        }
+    }
+    // Nobody leaves while the peer may still read this CTA's shared memory, signal its barriers or use its
+    // tensor memory: both CTAs meet here, also after a wait that ran out.
+    TcFenceBefore();
+    __syncthreads();
+    ClusterSync();
+    if (warp == 1) TmemDealloc2(tmemBase, Cfg::kTmemCols);
+    if (threadIdx.x == 0 && st->abort && g.errFlag) atomicExch(g.errFlag, 1u);
+}
+
+}  // namespace hcgemm
