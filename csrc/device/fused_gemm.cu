@@ -29,6 +29,7 @@
 #include "emu_launch.h"
 #include "gemm_api.h"
 #include "gemm_sm100.cuh"
+#include "gemm_sm100_2sm.cuh"
 #include "hcomm_device.cuh"
 
 namespace hc {
@@ -198,6 +199,19 @@ __global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(cons
     hcdev::KernelEnd(d, ls, 0);
 }
 
+// The same on CTA pairs (256 x 256 tiles): tile row blocks, blocks per rank and the epilogue's arrival counters are
+// per 256-row block; both CTAs of a pair write their half of a partial tile and each bumps the counter once.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) GemmReduceScatterPairKernel(const FusedParams *table)
+{
+    const FusedParams &p = table[blockIdx.y];
+    const CommDev *d = p.dev;
+    const hcdev::LaunchState ls = hcdev::KernelBegin(d);
+    RsOrder order{d->rank, d->nRanks, p.mbPer};
+    RsEpilogue<256> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, p.expect, nullptr};
+    GemmMainLoopPair<256, 7>(&p.tmA, &p.tmB, p.shape, order, epi);
+    hcdev::KernelEnd(d, ls, 0);
+}
+
 // -------------------------------------------------------------------------- AllGather -> GEMM
 
 struct AgOrder {
@@ -295,6 +309,21 @@ __global__ void __launch_bounds__(kFusedThreads, 1) AllGatherGemmKernel(const Fu
     hcdev::KernelEnd(d, ls, 0);
 }
 
+// CTA-pair variant: p.mbPer counts 128-row blocks (gate, push and counters keep that unit), the tile order works
+// on 256-row blocks.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) AllGatherGemmPairKernel(const FusedParams *table)
+{
+    const FusedParams &p = table[blockIdx.y];
+    const CommDev *d = p.dev;
+    const hcdev::LaunchState ls = hcdev::KernelBegin(d);
+    AgOrder order{d->rank, d->nRanks, p.mbPer / 2};
+    AgGate gate{d, p.mbPer, p.expect};
+    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half};
+    StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
+    GemmMainLoopPair<256, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
+    hcdev::KernelEnd(d, ls, 0);
+}
+
 // --------------------------------------------------------------------------------- host side
 
 std::mutex g_ringMu;
@@ -352,6 +381,49 @@ HcclResult LaunchFused(Comm *c, KernelT kernel, int smemBytes, const FusedParams
     return HCCL_SUCCESS;
 }
 
+bool PairKernelsEnabled()
+{
+    static const bool on = [] { const char *e = getenv("HCOMM_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+// Launches a CTA-pair kernel (compile-time cluster of two) on as many pairs as can be resident at once.
+template <typename KernelT>
+HcclResult LaunchFusedPair(Comm *c, KernelT kernel, const FusedParams &hp, int tiles, void *stream)
+{
+    constexpr int smemBytes = Config2<256, 7>::kSmemBytes;
+    static std::map<void *, int> capacity;
+    int cap;
+    {
+        std::lock_guard<std::mutex> lk(g_ringMu);
+        auto it = capacity.find((void *)kernel);
+        if (it == capacity.end()) {
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes);
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * GemmSmCount(), 1, 1);
+            cfg.blockDim = dim3(kFusedThreads, 1, 1);
+            cfg.dynamicSmemBytes = smemBytes;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+            HCCL_INFO("fused CTA-pair kernel %p: %d pairs can be resident", (void *)kernel, n);
+            it = capacity.emplace((void *)kernel, n).first;
+        }
+        cap = it->second;
+    }
+    if (cap <= 0) return HCCL_E_NOT_SUPPORT;
+    FusedParams *slot = ParamSlot(c);
+    if (cudaMemcpyAsync(slot, &hp, sizeof(hp), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess) return HCCL_E_RUNTIME;
+    const int pairs = std::min(cap, tiles);
+    kernel<<<dim3(2 * pairs, 1, 1), kFusedThreads, smemBytes, (cudaStream_t)stream>>>(slot);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) { HCCL_ERROR("fused launch (CTA pairs) failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
+    return HCCL_SUCCESS;
+}
+
 HcclResult CheckFusable(Comm *c, const char *what)
 {
     if (c->plat->kind() != PlatKind::CUDA) { RPT_ERR("EI0003", "%s runs on CUDA devices only", what); return HCCL_E_NOT_SUPPORT; }
@@ -384,14 +456,23 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     CHK_RET(LaunchBarrierIfNeeded(c, stream));
     FusedParams hp;
     memset(&hp, 0, sizeof(hp));
+    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && rowsPer % kPairM == 0 && N % 256 == 0;
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBlockM, kBlockK));
-    CHK_RET(MakeTensorMap2dBf16(&hp.tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)BN, kBlockK));
-    hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / kBlockM; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
-    hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / kBlockM; hp.rowsPer = rowsPer; hp.K = K;
-    hp.expect = ExpectTable(c, kRsFlagBase, kRsFlagBase + (rowsPer / kBlockM) * (N / BN), (uint32_t)(p - 1), stream);
+    CHK_RET(MakeTensorMap2dBf16(&hp.tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, usePair ? 128u : (uint32_t)BN, kBlockK));
+    const int blockRows = usePair ? kPairM : kBlockM;
+    hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / blockRows; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
+    hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / blockRows; hp.rowsPer = rowsPer; hp.K = K;
+    // every peer bumps a tile's counter once per CTA that wrote part of it (two CTAs share a tile in the pair kernel)
+    hp.expect = ExpectTable(c, kRsFlagBase, kRsFlagBase + hp.mbPer * hp.shape.tilesN, (uint32_t)(p - 1) * (usePair ? 2u : 1u), stream);
     if (!hp.expect) return HCCL_E_RUNTIME;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
+    if (usePair) {
+        HcclResult r = LaunchFusedPair(c, GemmReduceScatterPairKernel, hp, tiles, stream);
+        if (r != HCCL_E_NOT_SUPPORT) return r;
+        RPT_ERR("EI0003", "GEMM+ReduceScatter: CTA pairs cannot be scheduled on this device");
+        return r;
+    }
     if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
     return LaunchFused(c, GemmReduceScatterKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9002, stream);
 }
@@ -417,11 +498,12 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     memset(&hp, 0, sizeof(hp));
     // The staging copy of the gathered activations lives in this operator's CCL half; which half is only known on
     // the device (launch parity), so a map is built for each and the kernel picks.
+    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && Mshard % kPairM == 0 && N % 256 == 0;
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, x, (uint64_t)Mshard, (uint64_t)K, (uint64_t)ldx, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2, c->CclBuffer(), (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2b, c->CclBuffer() + c->halfBytes, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
-    CHK_RET(MakeTensorMap2dBf16(&hp.tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, (uint32_t)BN, kBlockK));
-    hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / kBlockM; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
+    CHK_RET(MakeTensorMap2dBf16(&hp.tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, usePair ? 128u : (uint32_t)BN, kBlockK));
+    hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / (usePair ? kPairM : kBlockM); hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = Mshard / kBlockM; hp.rowsPer = Mshard; hp.K = K; hp.xLocal = x;
     const uint64_t blockBytes = (uint64_t)kBlockM * K * 2;
     hp.expect = ExpectTable(c, kAgFlagBase, kAgFlagBase + M / kBlockM, (uint32_t)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes), stream,
@@ -429,6 +511,11 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     if (!hp.expect) return HCCL_E_RUNTIME;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
+    if (usePair) {
+        HcclResult r = LaunchFusedPair(c, AllGatherGemmPairKernel, hp, tiles, stream);
+        if (r == HCCL_E_NOT_SUPPORT) RPT_ERR("EI0003", "AllGather+GEMM: CTA pairs cannot be scheduled on this device");
+        return r;
+    }
     if (BN == 256) return LaunchFused(c, AllGatherGemmKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9003, stream);
     return LaunchFused(c, AllGatherGemmKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9004, stream);
 }

@@ -24,11 +24,11 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     hcgemm::GemmMainLoop<BN>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < 16 ? shape.tilesM : 16}, hcgemm::NoGate(), epi);
 }
 // CTA-pair variant: 256 x 256 tiles, launched as clusters of two CTAs (see gemm_sm100_2sm.cuh).
-template <int BN>
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(hcgemm::kThreads, 1)
-GemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16 epi)
+GemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16 epi, int gm)
 {
-    hcgemm::GemmMainLoopPair<BN>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < 8 ? shape.tilesM : 8}, epi);
+    hcgemm::GemmMainLoopPair<BN, STAGES>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < gm ? shape.tilesM : gm}, epi);
 }
 
 // Clusters of two CTAs that can be resident at once (0 when the query fails).
@@ -36,18 +36,20 @@ int PairClusterCapacity()
 {
     static int cap = -1;
     if (cap >= 0) return cap;
-    cudaFuncSetAttribute(GemmBf16PairKernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairKernel<256, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 6>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairKernel<256, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 7>::kSmemBytes);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148, 1, 1);
     cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = hcgemm::Config2<256>::kSmemBytes;
+    cfg.dynamicSmemBytes = hcgemm::Config2<256, 7>::kSmemBytes;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeClusterDimension;
     at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
     cfg.attrs = at; cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, GemmBf16PairKernel<256>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    if (cudaOccupancyMaxActiveClusters(&n, GemmBf16PairKernel<256, 7>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
     cap = n;
+    HCCL_INFO("GEMM CTA pairs resident at once: %d", cap);
     return cap;
 }
 }  // namespace
@@ -129,13 +131,16 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * clusters, 1, 1);
         cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
-        cfg.dynamicSmemBytes = hcgemm::Config2<256>::kSmemBytes;
+        static const int stages = [] { const char *e = getenv("HCOMM_GEMM_STAGES"); return e && atoi(e) == 6 ? 6 : 7; }();
+        static const int gm = [] { const char *e = getenv("HCOMM_GEMM_GM"); int v = e ? atoi(e) : 0; return v > 0 ? v : 16; }();
+        cfg.dynamicSmemBytes = stages == 7 ? hcgemm::Config2<256, 7>::kSmemBytes : hcgemm::Config2<256, 6>::kSmemBytes;
         cfg.stream = (cudaStream_t)stream;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
-        cudaError_t e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256>, tmA, tmB, shape, epi);
+        cudaError_t e = stages == 7 ? cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 7>, tmA, tmB, shape, epi, gm)
+                                    : cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 6>, tmA, tmB, shape, epi, gm);
         if (e != cudaSuccess) {
             HCCL_ERROR("GemmBf16 (CTA pairs) launch failed: %s", cudaGetErrorString(e));
             return HCCL_E_RUNTIME;

@@ -22,9 +22,10 @@ namespace hcgemm {
 
 constexpr int kPairM = 256;
 
-template <int BN> struct Config2 {
+template <int BN, int STAGES = 6> struct Config2 {
     static_assert(BN == 256, "the pair kernel is built for 256 x 256 tiles");
-    static constexpr int kStages = 6;
+    static_assert(STAGES >= 2 && STAGES <= 7, "the ring must fit 227 KB of shared memory and the 8-entry barrier arrays");
+    static constexpr int kStages = STAGES;
     static constexpr int kABytes = kBlockM * kBlockK * 2;          // 128 rows of A per CTA
     static constexpr int kBBytes = (BN / 2) * kBlockK * 2;         // 128 of the 256 B rows per CTA
     static constexpr int kStageBytes = kABytes + kBBytes;
@@ -103,10 +104,12 @@ __device__ __forceinline__ void MmaCommitPair(uint64_t *bar)
 }  // namespace pair
 
 // g.tilesM counts 256-row blocks here.  Launch with a cluster of two CTAs along x and an even grid.
-template <int BN, typename TileOrder, typename Epilogue>
-__device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const CUtensorMap *tmB, const GemmShape &g, TileOrder order, Epilogue epi)
+// The Gate policy is asked per CTA with the index of the 128-row block that CTA loads (2 * mb + cluster rank).
+template <int BN, int STAGES, typename TileOrder, typename Epilogue, typename Gate = NoGate, typename Extra = NoExtra>
+__device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const CUtensorMap *tmB, const GemmShape &g, TileOrder order, Epilogue epi,
+                                                 Gate gate = Gate(), const CUtensorMap *tmA2 = nullptr, Extra extra = Extra())
 {
-    using Cfg = Config2<BN>;
+    using Cfg = Config2<BN, STAGES>;
     using namespace pair;
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
@@ -145,7 +148,10 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
             for (int t = firstTile; t < numTiles && alive; t += tileStep) {
                 int mb, nb;
                 order(t, g, &mb, &nb);
-                const int aRow = mb * kPairM + (int)ctaRank * kBlockM;
+                const int mb128 = mb * 2 + (int)ctaRank;
+                int aRow = mb128 * kBlockM;
+                const CUtensorMap *mapA = tmA;
+                if (!gate(mb128, nb, &st->abort, &aRow, tmA, tmA2, &mapA)) { alive = false; break; }
                 const int bRow = nb * BN + (int)ctaRank * (BN / 2);
                 for (int kb = 0; kb < kBlocks; ++kb, ++it) {
                     const int s = it % Cfg::kStages;
@@ -154,7 +160,7 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
                     uint8_t *sa = smem + s * Cfg::kStageBytes, *sb = sa + Cfg::kABytes;
                     if (leader) MbarExpectTx(&st->full[s], 2 * Cfg::kStageBytes);      // both CTAs' loads land on this barrier
                     const uint32_t bar = MapToCta(&st->full[s], 0);
-                    TmaLoad2dPair(sa, tmA, bar, kb * kBlockK, aRow);
+                    TmaLoad2dPair(sa, mapA, bar, kb * kBlockK, aRow);
                     TmaLoad2dPair(sb, tmB, bar, kb * kBlockK, bRow);
                 }
             }
@@ -187,7 +193,10 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
                 if (alive) MmaCommitPair(&st->tmemFull[acc]);
             }
         }
-    } else if (warp < 6) {
+    } else if (warp >= 6) {
+        // -------------------------------------------------- extra warps (communication roles of fused kernels)
+        extra(warp - 6, lane, &st->abort);
+    } else {
         // ---------------------------------------------------------------------- epilogue (both CTAs)
         const int q = warp & 3;
         uint32_t tileIter = 0;
