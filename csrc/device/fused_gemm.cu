@@ -85,6 +85,7 @@ struct RsOrder {
 
 template <int BN>
 struct RsEpilogue {
+    static constexpr bool kStaged = true;      // the CTA-pair main loop sends partial tiles out as whole 256-byte row segments
     const CommDev *d;
     __nv_bfloat16 *out;
     int ldOut, N, mbPer, rowsPer, tilesN;
@@ -95,6 +96,14 @@ struct RsEpilogue {
     __device__ __forceinline__ char *Slot(int owner, int src) const
     {
         return hcdev::CclHalf(d, owner, half) + (size_t)src * rowsPer * N * sizeof(__nv_bfloat16);
+    }
+    __device__ __forceinline__ bool StagedTile(int mb) const { return mb / mbPer != d->rank; }
+    // 32 rows x 128 columns of a partial tile, parked in shared memory by the calling warp, go to the owner's staging
+    __device__ __forceinline__ void StoreStaged(int mb, int, int rowBase, int colBase, const uint8_t *slab, int lane) const
+    {
+        const int q = mb / mbPer;
+        char *dst = Slot(q, d->rank) + ((size_t)(rowBase - q * rowsPer) * N + colBase) * sizeof(__nv_bfloat16);
+        hcgemm::pair::StageFlushRows(slab, dst, (size_t)N * sizeof(__nv_bfloat16), lane);
     }
     __device__ __forceinline__ void BeginTile(int mb, int nb, int) const
     {
@@ -208,7 +217,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) Ge
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
     RsEpilogue<256> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, p.expect, nullptr};
-    GemmMainLoopPair<256, 7>(&p.tmA, &p.tmB, p.shape, order, epi);
+    GemmMainLoopPair<256, 6>(&p.tmA, &p.tmB, p.shape, order, epi);
     hcdev::KernelEnd(d, ls, 0);
 }
 
@@ -391,7 +400,8 @@ bool PairKernelsEnabled()
 template <typename KernelT>
 HcclResult LaunchFusedPair(Comm *c, KernelT kernel, const FusedParams &hp, int tiles, void *stream)
 {
-    constexpr int smemBytes = Config2<256, 7>::kSmemBytes;
+    constexpr int smemBytes = Config2<256, 7>::kSmemBytes;      // = Config2<256, 6, true>::kSmemBytes
+    static_assert(Config2<256, 7>::kSmemBytes == Config2<256, 6, true>::kSmemBytes, "both fused pair kernels use the same shared-memory size");
     static std::map<void *, int> capacity;
     int cap;
     {

@@ -211,6 +211,7 @@ struct NoGate {
 
 // Writes bf16 rows of C; each thread stores its 32 columns as four 16-byte vectors.
 struct StoreBf16 {
+    static constexpr bool kStaged = false;
     __nv_bfloat16 *C;
     int ldc, M, N;
     __device__ __forceinline__ void BeginTile(int, int, int) const {}

@@ -22,16 +22,24 @@ namespace hcgemm {
 
 constexpr int kPairM = 256;
 
-template <int BN, int STAGES = 6> struct Config2 {
+constexpr int kStagingBytesPerWarp = 32 * 128 * 2;      // 32 rows x 128 bf16 columns
+constexpr int kStagingBytes = 4 * kStagingBytesPerWarp;  // one slab per epilogue warp
+
+template <int BN, int STAGES = 6, bool STAGING = false> struct Config2 {
     static_assert(BN == 256, "the pair kernel is built for 256 x 256 tiles");
     static_assert(STAGES >= 2 && STAGES <= 7, "the ring must fit 227 KB of shared memory and the 8-entry barrier arrays");
+    static_assert(!STAGING || STAGES <= 6, "epilogue staging takes the room of the seventh stage");
     static constexpr int kStages = STAGES;
+    static constexpr int kStaging = STAGING ? kStagingBytes : 0;
     static constexpr int kABytes = kBlockM * kBlockK * 2;          // 128 rows of A per CTA
     static constexpr int kBBytes = (BN / 2) * kBlockK * 2;         // 128 of the 256 B rows per CTA
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN;
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 256;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + 1024 + 256;
 };
+
+// Epilogue policies without a staged path.
+struct NoStaging { static constexpr bool kStaged = false; };
 
 namespace pair {
 
@@ -101,6 +109,29 @@ __device__ __forceinline__ void MmaCommitPair(uint64_t *bar)
                  ::"r"(SmemAddr(bar)), "h"(mask) : "memory");
 }
 
+// Epilogue staging: a warp parks 32 rows x 128 bf16 columns (256 bytes per row) in shared memory so that the rows
+// can leave as whole 256-byte segments - two rows per warp store - instead of 16-byte pieces at a row stride.
+// 16-byte chunks are XOR-swizzled with the row so that neither the row-wise writes nor the segment-wise reads pile
+// up on the same banks.
+__device__ __forceinline__ void StagePut(uint8_t *slab, int row, int chunk, uint4 v)
+{
+    *(uint4 *)(slab + row * 256 + ((chunk ^ (row & 15)) << 4)) = v;
+}
+__device__ __forceinline__ uint4 StageGet(const uint8_t *slab, int row, int chunk)
+{
+    return *(const uint4 *)(slab + row * 256 + ((chunk ^ (row & 15)) << 4));
+}
+// Writes the slab to dst[row * pitchBytes + 0..255] for rows 0..31 (dst may be peer memory).
+__device__ __forceinline__ void StageFlushRows(const uint8_t *slab, char *dst, size_t pitchBytes, int lane)
+{
+    const int chunk = lane & 15, half = lane >> 4;
+#pragma unroll 4
+    for (int it = 0; it < 16; ++it) {
+        const int row = it * 2 + half;
+        *(uint4 *)(dst + (size_t)row * pitchBytes + (chunk << 4)) = StageGet(slab, row, chunk);
+    }
+}
+
 }  // namespace pair
 
 // g.tilesM counts 256-row blocks here.  Launch with a cluster of two CTAs along x and an even grid.
@@ -109,11 +140,12 @@ template <int BN, int STAGES, typename TileOrder, typename Epilogue, typename Ga
 __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const CUtensorMap *tmB, const GemmShape &g, TileOrder order, Epilogue epi,
                                                  Gate gate = Gate(), const CUtensorMap *tmA2 = nullptr, Extra extra = Extra())
 {
-    using Cfg = Config2<BN, STAGES>;
+    using Cfg = Config2<BN, STAGES, Epilogue::kStaged>;
     using namespace pair;
     extern __shared__ uint8_t smemRaw[];
     uint8_t *smem = (uint8_t *)(((uintptr_t)smemRaw + 1023) & ~(uintptr_t)1023);
-    SharedState *st = (SharedState *)(smem + Cfg::kStages * Cfg::kStageBytes);
+    uint8_t *staging = smem + Cfg::kStages * Cfg::kStageBytes;
+    SharedState *st = (SharedState *)(staging + Cfg::kStaging);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t ctaRank = ClusterCtaRank();
@@ -209,12 +241,43 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
             TcFenceAfter();
             const int row = mb * kPairM + (int)ctaRank * kBlockM + q * 32 + lane;
             epi.BeginTile(mb, nb, row);
+            bool staged = false;
+            if constexpr (Epilogue::kStaged) staged = epi.StagedTile(mb);
+            if (staged) {
+                if constexpr (Epilogue::kStaged) {
+                    uint8_t *slab = staging + q * kStagingBytesPerWarp;
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t frag[32];
-                TmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + acc * BN + c, frag);
-                TmemLoadWait();
-                epi.Fragment(mb, nb, row, nb * BN + c, frag);
+                    for (int c0 = 0; c0 < BN; c0 += 128) {
+#pragma unroll 1
+                        for (int c = 0; c < 128; c += 32) {
+                            uint32_t frag[32];
+                            TmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + acc * BN + c0 + c, frag);
+                            TmemLoadWait();
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                uint4 pk;
+                                uint32_t *pw = (uint32_t *)&pk;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(frag[v * 8 + 2 * j]), __uint_as_float(frag[v * 8 + 2 * j + 1]));
+                                    pw[j] = *(uint32_t *)&h;
+                                }
+                                StagePut(slab, lane, (c >> 3) + v, pk);
+                            }
+                        }
+                        __syncwarp();
+                        epi.StoreStaged(mb, nb, row - lane, nb * BN + c0, slab, lane);
+                        __syncwarp();
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t frag[32];
+                    TmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + acc * BN + c, frag);
+                    TmemLoadWait();
+                    epi.Fragment(mb, nb, row, nb * BN + c, frag);
+                }
             }
             TcFenceBefore();
             __syncwarp();
