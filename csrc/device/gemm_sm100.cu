@@ -24,6 +24,13 @@ GemmBf16Kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     hcgemm::GemmMainLoop<BN>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < 16 ? shape.tilesM : 16}, hcgemm::NoGate(), epi);
 }
 // CTA-pair variant: 256 x 256 tiles, launched as clusters of two CTAs (see gemm_sm100_2sm.cuh).
+template <int BN>
+__global__ void __launch_bounds__(hcgemm::kThreads, 1)
+GemmBf16PairStagedKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16Staged epi, int gm)
+{
+    hcgemm::GemmMainLoopPair<BN, 6>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < gm ? shape.tilesM : gm}, epi);
+}
+
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(hcgemm::kThreads, 1)
 GemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, hcgemm::GemmShape shape, hcgemm::StoreBf16 epi, int gm)
@@ -38,6 +45,7 @@ int PairClusterCapacity()
     if (cap >= 0) return cap;
     cudaFuncSetAttribute(GemmBf16PairKernel<256, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 6>::kSmemBytes);
     cudaFuncSetAttribute(GemmBf16PairKernel<256, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 7>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairStagedKernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 6, true>::kSmemBytes);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148, 1, 1);
     cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
@@ -139,6 +147,14 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
+        static const bool stagedEpilogue = [] { const char *e = getenv("HCOMM_GEMM_STAGED"); return e && e[0] == '1'; }();
+        if (stagedEpilogue && ldc % 8 == 0) {
+            cfg.dynamicSmemBytes = hcgemm::Config2<256, 6, true>::kSmemBytes;
+            hcgemm::StoreBf16Staged sepi{(__nv_bfloat16 *)C, ldc};
+            cudaError_t e2 = cudaLaunchKernelEx(&cfg, GemmBf16PairStagedKernel<256>, tmA, tmB, shape, sepi, gm);
+            if (e2 != cudaSuccess) { HCCL_ERROR("GemmBf16 (CTA pairs, staged epilogue) launch failed: %s", cudaGetErrorString(e2)); return HCCL_E_RUNTIME; }
+            return HCCL_SUCCESS;
+        }
         cudaError_t e = stages == 7 ? cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 7>, tmA, tmB, shape, epi, gm)
                                     : cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 6>, tmA, tmB, shape, epi, gm);
         if (e != cudaSuccess) {

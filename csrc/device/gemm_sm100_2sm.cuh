@@ -134,6 +134,22 @@ __device__ __forceinline__ void StageFlushRows(const uint8_t *slab, char *dst, s
 
 }  // namespace pair
 
+// Writes bf16 rows of C through the per-warp slab: every warp store covers two 256-byte row segments.
+// For shapes whose tiles are complete (M a multiple of 256, N a multiple of 256).
+struct StoreBf16Staged {
+    static constexpr bool kStaged = true;
+    __nv_bfloat16 *C;
+    int ldc;
+    __device__ __forceinline__ bool StagedTile(int) const { return true; }
+    __device__ __forceinline__ void BeginTile(int, int, int) const {}
+    __device__ __forceinline__ void EndTile(int, int, int) const {}
+    __device__ __forceinline__ void Fragment(int, int, int, int, const uint32_t (&)[32]) const {}
+    __device__ __forceinline__ void StoreStaged(int, int, int rowBase, int colBase, const uint8_t *slab, int lane) const
+    {
+        pair::StageFlushRows(slab, (char *)(C + (size_t)rowBase * ldc + colBase), (size_t)ldc * sizeof(__nv_bfloat16), lane);
+    }
+};
+
 // g.tilesM counts 256-row blocks here.  Launch with a cluster of two CTAs along x and an even grid.
 // The Gate policy is asked per CTA with the index of the 128-row block that CTA loads (2 * mb + cluster rank).
 template <int BN, int STAGES, typename TileOrder, typename Epilogue, typename Gate = NoGate, typename Extra = NoExtra>
