@@ -396,34 +396,39 @@ bool PairKernelsEnabled()
     return on;
 }
 
-// Launches a CTA-pair kernel (compile-time cluster of two) on as many pairs as can be resident at once.
+// CTA pairs of `kernel` (compile-time cluster of two) that can be resident at once; 0 when pairs cannot be scheduled.
 template <typename KernelT>
-HcclResult LaunchFusedPair(Comm *c, KernelT kernel, const FusedParams &hp, int tiles, void *stream)
+int PairCapacityOf(KernelT kernel)
 {
     constexpr int smemBytes = Config2<256, 7>::kSmemBytes;      // = Config2<256, 6, true>::kSmemBytes
     static_assert(Config2<256, 7>::kSmemBytes == Config2<256, 6, true>::kSmemBytes, "both fused pair kernels use the same shared-memory size");
     static std::map<void *, int> capacity;
-    int cap;
-    {
-        std::lock_guard<std::mutex> lk(g_ringMu);
-        auto it = capacity.find((void *)kernel);
-        if (it == capacity.end()) {
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes);
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(2 * GemmSmCount(), 1, 1);
-            cfg.blockDim = dim3(kFusedThreads, 1, 1);
-            cfg.dynamicSmemBytes = smemBytes;
-            cudaLaunchAttribute at[1];
-            at[0].id = cudaLaunchAttributeClusterDimension;
-            at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-            cfg.attrs = at; cfg.numAttrs = 1;
-            int n = 0;
-            if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
-            HCCL_INFO("fused CTA-pair kernel %p: %d pairs can be resident", (void *)kernel, n);
-            it = capacity.emplace((void *)kernel, n).first;
-        }
-        cap = it->second;
+    std::lock_guard<std::mutex> lk(g_ringMu);
+    auto it = capacity.find((void *)kernel);
+    if (it == capacity.end()) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * GemmSmCount(), 1, 1);
+        cfg.blockDim = dim3(kFusedThreads, 1, 1);
+        cfg.dynamicSmemBytes = smemBytes;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        HCCL_INFO("fused CTA-pair kernel %p: %d pairs can be resident", (void *)kernel, n);
+        it = capacity.emplace((void *)kernel, n).first;
     }
+    return it->second;
+}
+
+// Launches a CTA-pair kernel on as many pairs as can be resident at once.
+template <typename KernelT>
+HcclResult LaunchFusedPair(Comm *c, KernelT kernel, const FusedParams &hp, int tiles, void *stream)
+{
+    constexpr int smemBytes = Config2<256, 7>::kSmemBytes;
+    const int cap = PairCapacityOf(kernel);
     if (cap <= 0) return HCCL_E_NOT_SUPPORT;
     FusedParams *slot = ParamSlot(c);
     if (cudaMemcpyAsync(slot, &hp, sizeof(hp), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess) return HCCL_E_RUNTIME;
@@ -466,7 +471,8 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     CHK_RET(LaunchBarrierIfNeeded(c, stream));
     FusedParams hp;
     memset(&hp, 0, sizeof(hp));
-    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && rowsPer % kPairM == 0 && N % 256 == 0;
+    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && rowsPer % kPairM == 0 && N % 256 == 0 &&
+                         PairCapacityOf(GemmReduceScatterPairKernel) > 0;
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, usePair ? 128u : (uint32_t)BN, kBlockK));
     const int blockRows = usePair ? kPairM : kBlockM;
@@ -478,10 +484,7 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     if (usePair) {
-        HcclResult r = LaunchFusedPair(c, GemmReduceScatterPairKernel, hp, tiles, stream);
-        if (r != HCCL_E_NOT_SUPPORT) return r;
-        RPT_ERR("EI0003", "GEMM+ReduceScatter: CTA pairs cannot be scheduled on this device");
-        return r;
+        return LaunchFusedPair(c, GemmReduceScatterPairKernel, hp, tiles, stream);
     }
     if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
     return LaunchFused(c, GemmReduceScatterKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9002, stream);
@@ -508,7 +511,8 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     memset(&hp, 0, sizeof(hp));
     // The staging copy of the gathered activations lives in this operator's CCL half; which half is only known on
     // the device (launch parity), so a map is built for each and the kernel picks.
-    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && Mshard % kPairM == 0 && N % 256 == 0;
+    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && Mshard % kPairM == 0 && N % 256 == 0 &&
+                         PairCapacityOf(AllGatherGemmPairKernel) > 0;
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, x, (uint64_t)Mshard, (uint64_t)K, (uint64_t)ldx, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2, c->CclBuffer(), (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2b, c->CclBuffer() + c->halfBytes, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
@@ -522,9 +526,7 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     if (usePair) {
-        HcclResult r = LaunchFusedPair(c, AllGatherGemmPairKernel, hp, tiles, stream);
-        if (r == HCCL_E_NOT_SUPPORT) RPT_ERR("EI0003", "AllGather+GEMM: CTA pairs cannot be scheduled on this device");
-        return r;
+        return LaunchFusedPair(c, AllGatherGemmPairKernel, hp, tiles, stream);
     }
     if (BN == 256) return LaunchFused(c, AllGatherGemmKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9003, stream);
     return LaunchFused(c, AllGatherGemmKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9004, stream);
