@@ -320,7 +320,23 @@ HcclResult HcclCommMemUnreg(HcclComm comm, HcclMemHandle memHandle)
 
 // ----------------------------------------------------------------------------------- channels
 
-static HcclResult AcquireOne(Comm *c, CommEngine engine, const HcclChannelDesc &d, ChannelHandle *out)
+namespace {
+struct PendingChannel {
+    std::unique_ptr<ChannelRes> ch;     // null when an existing channel was reused
+    CheckFrame mine;
+    ChannelHandle reused = 0;
+};
+uint32_t &NotifyCursor(Comm *c, uint32_t peer)
+{
+    if (c->nextChanNotify.size() != c->nRanks) c->nextChanNotify.assign(c->nRanks, 8u);
+    return c->nextChanNotify[peer];
+}
+}  // namespace
+
+// First half of a channel acquisition: checks, slot allocation and the handshake frame on its way to the peer.
+// All frames of one HcclChannelAcquire call are sent before any answer is awaited, so ranks that acquire channels
+// to different peers in different orders (a ring: right neighbour first everywhere) cannot wait on each other in a cycle.
+static HcclResult AcquireBegin(Comm *c, CommEngine engine, const HcclChannelDesc &d, PendingChannel *pend)
 {
     if (d.header.magicWord != HCCL_CHANNEL_MAGIC_WORD || d.header.version == 0 || d.header.size < offsetof(HcclChannelDesc, memHandles)) {
         RPT_ERR("EI0003", "HcclChannelDesc was not initialised with HcclChannelDescInit (magic 0x%x version %u)", d.header.magicWord, d.header.version);
@@ -340,10 +356,10 @@ static HcclResult AcquireOne(Comm *c, CommEngine engine, const HcclChannelDesc &
         std::lock_guard<std::mutex> lk(c->resMu);
         for (auto &ch : c->channels)
             if (ch->engine == engine && ch->remoteRank == d.remoteRank && ch->notifyNum == d.notifyNum && ch->status.load() == HCOMM_CHANNEL_STATUS_READY) {
-                *out = (ChannelHandle)(uintptr_t)ch.get();
+                pend->reused = (ChannelHandle)(uintptr_t)ch.get();
                 return HCCL_SUCCESS;
             }
-        if (c->nextChanNotify + d.notifyNum > HC_CHAN_NOTIFY) {
+        if (NotifyCursor(c, d.remoteRank) + d.notifyNum > HC_CHAN_NOTIFY) {
             // out of notify slots: the caller may fall back to fewer notifies or release channels
             return HCCL_E_UNAVAIL;
         }
@@ -358,8 +374,8 @@ static HcclResult AcquireOne(Comm *c, CommEngine engine, const HcclChannelDesc &
     ch->plat = c->plat;
     {
         std::lock_guard<std::mutex> lk(c->resMu);
-        ch->notifyBase = c->nextChanNotify;
-        c->nextChanNotify += d.notifyNum;
+        ch->notifyBase = NotifyCursor(c, d.remoteRank);
+        NotifyCursor(c, d.remoteRank) += d.notifyNum;
     }
     ch->remoteNotify = (uint64_t *)(c->PeerHeap(d.remoteRank) + HC_OFF_CHAN_NOTIFY) + (uint64_t)c->rank * HC_CHAN_NOTIFY + ch->notifyBase;
     ch->localNotify = (uint64_t *)(c->LocalHeap() + HC_OFF_CHAN_NOTIFY) + (uint64_t)d.remoteRank * HC_CHAN_NOTIFY + ch->notifyBase;
@@ -388,6 +404,19 @@ static HcclResult AcquireOne(Comm *c, CommEngine engine, const HcclChannelDesc &
     ch->status.store(HCOMM_CHANNEL_STATUS_INIT);
     CHK_RET(c->boot->Send(c->worldRanks[d.remoteRank], tag, msg));
     ch->status.store(HCOMM_CHANNEL_STATUS_SOCKET_OK);
+    pend->mine = mine;
+    pend->ch = std::move(ch);
+    return HCCL_SUCCESS;
+}
+
+// Second half: the peer's frame is awaited and compared, the peer's memories are recorded.
+static HcclResult AcquireFinish(Comm *c, CommEngine engine, const HcclChannelDesc &d, PendingChannel *pend, ChannelHandle *out)
+{
+    if (pend->reused) { *out = pend->reused; return HCCL_SUCCESS; }
+    std::unique_ptr<ChannelRes> ch = std::move(pend->ch);
+    const CheckFrame mine = pend->mine;
+    const CommProtocol proto = ch->protocol;
+    const uint64_t tag = ((uint64_t)c->group.id << 32) | 0x43480000u | ((uint32_t)engine << 8);
     Blob theirs;
     HcclResult r = c->boot->Recv(c->worldRanks[d.remoteRank], tag, &theirs, EnvConfig::Get().connectTimeoutSec.value * 1000);
     if (r != HCCL_SUCCESS) {
@@ -448,24 +477,30 @@ HcclResult HcclChannelAcquire(HcclComm comm, CommEngine engine, const HcclChanne
     if (!EngineUsable(c, engine)) return HCCL_E_NOT_SUPPORT;
     if (!EngineMatchesMode(c, engine)) { RPT_ERR("EI0003", "engine %d contradicts op expansion mode %u", (int)engine, c->cfg.opExpansionMode); return HCCL_E_PARA; }
     size_t before;
-    uint32_t notifyBefore;
+    std::vector<uint32_t> notifyBefore;
     {
         std::lock_guard<std::mutex> lk(c->resMu);
         before = c->channels.size();
+        NotifyCursor(c, 0);
         notifyBefore = c->nextChanNotify;
     }
+    std::vector<PendingChannel> pending(channelNum);
     for (uint32_t i = 0; i < channelNum; ++i) {
-        HcclResult r = AcquireOne(c, engine, descs[i], &channels[i]);
+        HcclResult r = AcquireBegin(c, engine, descs[i], &pending[i]);
         if (r == HCCL_E_UNAVAIL) {
-            // roll back what this call created so the caller can retry with a smaller request
+            // Out of notify slots before anything of this request reached the peer beyond the frames of the earlier
+            // descriptors: finish those (the peers answer them), then roll the whole call back so the caller can
+            // retry with a smaller request.
+            for (uint32_t j = 0; j < i; ++j) { ChannelHandle h = 0; AcquireFinish(c, engine, descs[j], &pending[j], &h); }
             std::lock_guard<std::mutex> lk(c->resMu);
             c->channels.resize(before);
             c->nextChanNotify = notifyBefore;
-            for (uint32_t j = 0; j <= i; ++j) channels[j] = 0;
+            for (uint32_t j = 0; j < channelNum; ++j) channels[j] = 0;
             return r;
         }
         if (r != HCCL_SUCCESS) return r;
     }
+    for (uint32_t i = 0; i < channelNum; ++i) CHK_RET(AcquireFinish(c, engine, descs[i], &pending[i], &channels[i]));
     return HCCL_SUCCESS;
 }
 

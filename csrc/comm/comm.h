@@ -167,7 +167,9 @@ struct Comm {
     std::vector<std::unique_ptr<ThreadRes>> threads;
     std::map<int, ThreadRes *> dedicatedThreads;
     std::vector<std::unique_ptr<ChannelRes>> channels;
-    uint32_t nextChanNotify = 8;             // slots 0..7 of every peer belong to the library's own schedules
+    // Channel notify slots are numbered per peer (both ends of a pair acquire their k-th channel with the same
+    // base); slots 0..7 of every peer belong to the library's own schedules.
+    std::vector<uint32_t> nextChanNotify;    // [nRanks], starts at 8
     struct EngineCtx { void *ptr; uint64_t size; CommEngine engine; };
     std::map<std::string, EngineCtx> engineCtxs;
     std::vector<std::unique_ptr<RegMem>> regMems;

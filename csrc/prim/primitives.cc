@@ -404,6 +404,14 @@ int32_t HcommChannelNotifyWait(ChannelHandle channel, uint32_t localNotifyIdx, u
     return (int32_t)CommPollDeviceStatus(ch->comm);
 }
 
+int32_t HcommThreadSynchronize(ThreadHandle thread)
+{
+    NEED_THREAD(t, thread);
+    if (t->stream) CHK_RET(t->plat->StreamSync(t->stream));
+    if (t->comm) return CommPollDeviceStatus(t->comm);
+    return HCCL_SUCCESS;
+}
+
 int32_t HcommFenceOnThread(ThreadHandle thread)
 {
     NEED_THREAD(t, thread);

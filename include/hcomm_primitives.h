@@ -126,6 +126,9 @@ int32_t HcommChannelNotifyWait(ChannelHandle channel, uint32_t localNotifyIdx, u
 int32_t HcommChannelNotifyWaitOnThreadWithDefaultTimeout(ThreadHandle thread, ChannelHandle channel,
                                                          uint32_t localNotifyIdx);
 int32_t HcommFenceOnThread(ThreadHandle thread);
+/* B200 extension: blocks the caller until everything queued on the thread so far has run (the stream of the thread is
+ * synchronised) and reports an expired wait of the thread's communicator as HCCL_E_TIMEOUT. */
+int32_t HcommThreadSynchronize(ThreadHandle thread);
 int32_t HcommChannelFenceOnThread(ThreadHandle thread, ChannelHandle channel);
 int32_t HcommChannelFence(ChannelHandle channel);
 int32_t HcommChannelDrainOnThread(ThreadHandle thread, ChannelHandle channel);
