@@ -267,6 +267,89 @@ def main():
         stage("moe dispatch/combine ok")
         moe.destroy()
         dist.destroy_process_group()
+    elif scenario == "hcom":
+        # named groups, rank translation, gradient fusion split and group collectives (the python `hccl` package)
+        import ctypes
+        from hccl.manage import api as manage
+        from hccl.split import api as split
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+        manage.init_world_group(comm.handle)
+        assert manage.get_rank_size() == world and manage.get_rank_id() == rank
+        assert manage.get_local_rank_size() == world and manage.get_local_rank_id() == rank
+        evens = [r for r in range(world) if r % 2 == 0]
+        odds = [r for r in range(world) if r % 2 == 1]
+        mine = evens if rank % 2 == 0 else odds
+        name = "even_ranks" if rank % 2 == 0 else "odd_ranks"
+        manage.create_group(name, len(mine), mine)
+        assert manage.get_rank_size(name) == len(mine)
+        assert manage.get_rank_id(name) == mine.index(rank)
+        assert manage.get_world_rank_from_group_rank(name, len(mine) - 1) == mine[-1]
+        assert manage.get_group_rank_from_world_rank(mine[0], name) == 0
+        x = np.full(1000, rank + 1, np.float32)
+        y = np.zeros_like(x)
+        rc = lib.HcomAllReduce(b"grad0", x.ctypes.data_as(ctypes.c_void_p), y.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(1000), 4, 0,
+                               name.encode(), None)
+        assert rc == 0 and (y == sum(r + 1 for r in mine)).all(), (rc, y[:3])
+        rc = lib.HcomAllReduce(b"grad1", x.ctypes.data_as(ctypes.c_void_p), y.ctypes.data_as(ctypes.c_void_p), ctypes.c_uint64(1000), 4, 0,
+                               b"hccl_world_group", None)
+        assert rc == 0 and (y == world * (world + 1) / 2).all()
+        # gradient fusion: by index (segments end after gradient 1, 4, 9), then by size percentages
+        sizes = [4 << 20] * 10
+        split.set_split_strategy_by_idx([1, 4, 9])
+        assert split.get_split_strategy(sizes) == [1, 4, 9]
+        split.set_split_strategy_by_size([20.0, 30.0, 50.0])
+        assert split.get_split_strategy(sizes) == [1, 4, 9]
+        try:
+            split.set_split_strategy_by_size([50.0, 40.0])      # must add up to 100
+            raise AssertionError("a size list that does not add up to 100 was accepted")
+        except ValueError:
+            pass
+        manage.destroy_group(name)
+        manage.destroy_world_group()
+        stage("hcom ok")
+        return 0        # the world group adopted and released the communicator
+    elif scenario == "lifecycle":
+        # suspend / resume, snapshot, diagnostics
+        import ctypes
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+        x = np.full(4096, rank + 1, np.float32)
+        y = np.zeros_like(x)
+        comm.all_reduce(x, y)
+        comm.suspend()
+        try:
+            comm.all_reduce(x, y)
+            raise AssertionError("an operator ran on a suspended communicator")
+        except hb.HcclError as e:
+            assert e.code == 22, e.code                      # HCCL_E_SUSPENDING
+        comm.resume()
+        y[:] = 0
+        comm.all_reduce(x, y)
+        assert (y == world * (world + 1) / 2).all()
+        # snapshot: size, save, and what the blob says about itself
+        size = ctypes.c_uint64()
+        assert lib.HcclCommSnapshotSize(ctypes.c_void_p(comm.handle), ctypes.byref(size)) == 0 and size.value > 0
+        buf = ctypes.create_string_buffer(size.value)
+        written = ctypes.c_uint64()
+        assert lib.HcclCommSnapshotSave(ctypes.c_void_p(comm.handle), buf, ctypes.c_uint64(size.value), ctypes.byref(written)) == 0
+        rs, rk = ctypes.c_uint32(), ctypes.c_uint32()
+        name = ctypes.create_string_buffer(256)
+        ops = ctypes.c_uint64()
+        assert lib.HcclCommSnapshotInfo(buf, written, ctypes.byref(rs), ctypes.byref(rk), name, ctypes.byref(ops)) == 0
+        assert rs.value == world and rk.value == rank and name.value.decode() == comm.name and ops.value >= 2
+        # diagnostics: operator counter, heartbeat ages, text dump
+        launched, head, tail = ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+        assert lib.HcclDiagGetOpCounters(ctypes.c_void_p(comm.handle), ctypes.byref(launched), ctypes.byref(head), ctypes.byref(tail)) == 0
+        assert launched.value >= 2
+        ages = (ctypes.c_uint64 * world)()
+        lost = ctypes.c_uint64(123)
+        assert lib.HcclDiagGetHeartbeat(ctypes.c_void_p(comm.handle), ages, ctypes.c_uint32(world), ctypes.byref(lost)) == 0
+        assert lost.value == 0
+        text = ctypes.create_string_buffer(8192)
+        assert lib.HcclDiagDump(ctypes.c_void_p(comm.handle), text, ctypes.c_uint32(8192)) == 0
+        assert f"rank {rank}/{world}" in text.value.decode()
+        stage("lifecycle ok")
     elif scenario == "forced_algos":
         import torch
         for algo in ("level0:ring", "level0:H-D_R"):

@@ -29,3 +29,13 @@ def test_torch_backend_operators_on_the_simulator():
 def test_ddp_with_fused_scale_hook_matches_local_mean_gradient():
     codes, outs = launch("torch_ddp", 2, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "2", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29642"}, timeout=240)
     assert codes == [0, 0], "\n".join(outs)
+
+
+def test_named_groups_and_gradient_split_through_the_python_package():
+    codes, outs = launch("hcom", 4, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=120)
+    assert codes == [0, 0, 0, 0], "\n".join(outs)
+
+
+def test_suspend_resume_snapshot_and_diagnostics():
+    codes, outs = launch("lifecycle", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=120)
+    assert codes == [0, 0, 0], "\n".join(outs)
