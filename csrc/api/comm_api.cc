@@ -456,6 +456,7 @@ HcclResult HcclCommResume(HcclComm comm)
     Platform *P = c->plat;
     CHK_RET(c->boot->Barrier(c->group));            // everyone is quiescent
     CHK_RET(P->MemsetSync(c->LocalHeap(), 0, HC_CTRL_BYTES));
+    CHK_RET(P->MemsetSync(c->LocalHeap() + c->llOffset, 0, c->llBytes));
     CHK_RET(P->MemsetSync(c->devCounters, 0, 128 * sizeof(uint32_t)));
     CHK_RET(P->MemsetSync(c->devIrCounters, 0, 2ull * HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY * sizeof(uint64_t)));
     std::fill(c->chanWaited.begin(), c->chanWaited.end(), 0);

@@ -111,6 +111,44 @@ uint64_t AlignDownElems(uint64_t elems, uint32_t esz)
     return elems / q * q;
 }
 
+// Small all-reduce / all-gather / all-to-all / reduce-scatter: one flag-in-data kernel without any barrier.
+// Returns true (and the launch result in *res) when the operator was served here.
+bool TrySmallLL(Comm *c, const OpDesc &d, const Selection &sel, HcclResult *res)
+{
+    const int32_t limit = EnvConfig::Get().llMaxBytes.value;
+    if (limit <= 0 || c->nRanks < 2 || c->nRanks > HC_KERNEL_MAX_RANKS || c->lastOpOnHost) return false;
+    if (sel.reason == "forced by configuration" || (sel.engine != Engine::SM_FAST && sel.engine != Engine::NVLS)) return false;
+    if (!d.sendCounts.empty() || !d.recvCounts.empty()) return false;
+    int mode;
+    switch (d.cmd) {
+        case HCCL_CMD_ALLREDUCE: mode = LL_ALLREDUCE; break;
+        case HCCL_CMD_ALLGATHER: mode = LL_ALLGATHER; break;
+        case HCCL_CMD_ALLTOALL: mode = LL_ALLTOALL; break;
+        case HCCL_CMD_REDUCE_SCATTER: mode = LL_REDUCE_SCATTER; break;
+        default: return false;
+    }
+    const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
+    const uint64_t blockBytes = d.count * esz;
+    if (blockBytes == 0 || blockBytes % 16 != 0 || blockBytes > (uint64_t)limit || blockBytes > HC_LL_MAX_PAYLOAD) return false;
+    const bool reducing = mode == LL_ALLREDUCE || mode == LL_REDUCE_SCATTER;
+    if (reducing && !DtypeReducible(d.dtype)) return false;
+    const uint64_t inBytes = (mode == LL_ALLTOALL || mode == LL_REDUCE_SCATTER) ? blockBytes * n : blockBytes;
+    const uint64_t outBytes = (mode == LL_ALLGATHER || mode == LL_ALLTOALL) ? blockBytes * n : blockBytes;
+    const uintptr_t in = (uintptr_t)d.in, out = (uintptr_t)d.out;
+    if ((in | out) & 15) return false;
+    const bool overlap = in < out + outBytes && out < in + inBytes;
+    if (overlap && !(mode == LL_ALLREDUCE && in == out)) return false;     // in-place all-reduce reads and writes the same vector per thread
+    CollArgs a;
+    FillBase(c, d, a);
+    a.in = d.in; a.out = d.out; a.count = d.count; a.peer = mode;
+    OpDesc typed = d;
+    if (!reducing) typed.dtype = HCCL_DATA_TYPE_FP32;                        // byte movers share the fp32 instantiation
+    a.dtype = typed.dtype;
+    const int ctas = (int)std::min<uint64_t>(8, std::max<uint64_t>(1, blockBytes / 8192));
+    *res = Launch(c, FK_SMALL_LL, a, c->emuSameDevice ? std::min(ctas, 4) : ctas, d.stream);
+    return true;
+}
+
 // -------------------------------------------------------------------------- fast-kernel drivers
 
 HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
@@ -536,6 +574,8 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
         // the stream engine has no fused scale: a second pass over the result applies it
         if (r == HCCL_SUCCESS && d.useScale) r = c->plat->ScaleAsync(d.out, d.count, d.dtype, d.scale, c->plat->kind() == PlatKind::SIM ? nullptr : d.stream);
         if (r == HCCL_SUCCESS && c->plat->kind() == PlatKind::SIM) r = CommPollDeviceStatus(c);
+    } else if (TrySmallLL(c, d, sel, &r)) {
+        // served by the flag-in-data kernel
     } else {
         switch (d.cmd) {
             case HCCL_CMD_ALLREDUCE: r = FastAllReduce(c, d, sel); break;

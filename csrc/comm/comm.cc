@@ -152,7 +152,9 @@ static HcclResult SetupHeap(Comm *c)
     c->halfBytes = (uint64_t)c->cfg.bufferMB << 20;
     c->p2pSlotBytes = 4ull << 20;
     c->p2pOffset = HC_CTRL_BYTES + 2 * c->halfBytes;
-    c->heapBytes = AlignUp(c->p2pOffset + (uint64_t)n * c->p2pSlotBytes, gran);
+    c->llOffset = c->p2pOffset + (uint64_t)n * c->p2pSlotBytes;
+    c->llBytes = 2ull * HC_KERNEL_MAX_RANKS * HC_LL_SLOT_BYTES;
+    c->heapBytes = AlignUp(c->llOffset + c->llBytes, gran);
     c->p2pSent.assign(n, 0);
     c->p2pRecvd.assign(n, 0);
     c->heapStride = c->heapBytes;
@@ -163,6 +165,7 @@ static HcclResult SetupHeap(Comm *c)
     c->peerPhys.assign(n, PhysMem());
     CHK_RET(P->Map(c->heapBase + (uint64_t)me * c->heapStride, c->heapPhys, c->heapBytes));
     CHK_RET(P->MemsetSync(c->LocalHeap(), 0, HC_CTRL_BYTES));
+    CHK_RET(P->MemsetSync(c->LocalHeap() + c->llOffset, 0, c->llBytes));     // tags in this area only ever grow from zero
 
     // Hand my block to every peer, take theirs.  Tag = communicator group id and a fixed purpose code.
     const uint64_t tag = ((uint64_t)c->group.id << 32) | 0x48454150u;  // "HEAP"
@@ -276,6 +279,7 @@ static HcclResult SetupDeviceState(Comm *c)
     d.status = c->waitStatus;
     d.opCounters = c->opCounters;
     d.timeoutNs = (uint64_t)c->TimeoutMs() * 1000000ull;
+    d.llOffset = c->llOffset;
     static_assert(sizeof(CommDev) <= HC_DEV_COUNTERS_OFFSET, "CommDev outgrew its slot");
     CHK_RET(P->MemcpySync(c->devStruct, &d, sizeof(CommDev)));
     return HCCL_SUCCESS;

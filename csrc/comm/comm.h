@@ -129,6 +129,7 @@ struct Comm {
     char *heapBase = nullptr;
     uint64_t heapStride = 0, heapBytes = 0, halfBytes = 0;
     uint64_t p2pOffset = 0, p2pSlotBytes = 0;    // landing area of the send/recv kernels: one slot per source rank
+    uint64_t llOffset = 0, llBytes = 0;          // flag-in-data area of the small-message kernels
     std::vector<uint64_t> p2pSent, p2pRecvd;     // chunks exchanged so far with each peer
     // Fused GEMM kernels: arrival counters in the control region only grow; the host keeps, per counter, the value that
     // means "complete" for the next call (all ranks issue the same calls, so the tables agree) and hands the

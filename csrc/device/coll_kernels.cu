@@ -602,6 +602,110 @@ __global__ void __launch_bounds__(512) KRecv(const __grid_constant__ CollArgs by
     }
 }
 
+// ------------------------------------------------------------------------ small messages (LL)
+
+// Flag-in-data exchange: every 8 bytes written to a peer hold 4 bytes of payload and the 4-byte tag of this launch,
+// so the receiver needs no barrier - it polls the words themselves (8-byte writes are not torn).  The tag is the
+// communicator's launch count + 1: it is the same on all ranks, grows with every operator and the area is used for
+// nothing else, so a word can never show this launch's tag before this launch's sender wrote it.  Slots alternate
+// with the launch parity; a slot is rewritten two launches later, which a sender can only reach after the receiver
+// has sent - hence finished reading - in between (every rank receives from every rank in all four collectives).
+//
+// a.peer selects the collective; a.count = elements per block:
+//   LL_ALLREDUCE       every rank sends its whole vector to all peers, out = sum in rank order of in_r[0..count)
+//   LL_ALLGATHER       block = my contribution, out[r*count ..] = block of rank r
+//   LL_ALLTOALL        in[q*count ..] goes to rank q, out[r*count ..] comes from rank r
+//   LL_REDUCE_SCATTER  in[q*count ..] goes to rank q, out = sum in rank order of the blocks addressed to me
+// Blocks are whole 16-byte vectors (the host checks) of at most HC_LL_MAX_PAYLOAD bytes.
+__device__ __forceinline__ char *LlSlot(const CommDev *d, int owner, uint32_t parity, int src)
+{
+    return HcPeerHeap(d, owner) + d->llOffset + ((uint64_t)parity * HC_KERNEL_MAX_RANKS + (uint64_t)src) * HC_LL_SLOT_BYTES;
+}
+__device__ __forceinline__ void LlStore(char *slot, uint64_t vec, uint4 v, uint32_t tag)
+{
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(slot + vec * 32), "r"(v.x), "r"(tag), "r"(v.y), "r"(tag) : "memory");
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(slot + vec * 32 + 16), "r"(v.z), "r"(tag), "r"(v.w), "r"(tag) : "memory");
+}
+// Spins until both halves of vector `vec` carry `tag`; false when the wait was given up.
+__device__ __forceinline__ bool LlLoad(const CommDev *d, const char *slot, uint64_t vec, uint32_t tag, int src, uint4 *out)
+{
+    uint64_t start = 0;
+    for (uint32_t it = 0;; ++it) {
+        const uint4 a = Ld16Volatile(slot + vec * 32), b = Ld16Volatile(slot + vec * 32 + 16);
+        if (a.y == tag && a.w == tag && b.y == tag && b.w == tag) {
+            *out = make_uint4(a.x, a.z, b.x, b.z);
+            return true;
+        }
+        if ((it & 63) == 63) {
+            if (Aborted(d)) return false;
+            if (start == 0) start = GlobalTimerNs();
+            else if (GlobalTimerNs() - start > d->timeoutNs) { ReportTimeout(d, (uint32_t)src, HC_WAIT_TILE_FLAG, (uint32_t)vec, tag, a.y); return false; }
+        }
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    const uint32_t tag = *(volatile const uint32_t *)&DevCounters(d)[1] + 1u;
+    const int n = d->nRanks, me = d->rank, mode = a.peer;
+    const bool reducing = mode == LL_ALLREDUCE || mode == LL_REDUCE_SCATTER;
+    const uint64_t blockBytes = a.count * (reducing ? sizeof(T) : (uint64_t)a.elemSize);
+    const uint64_t nvec = blockBytes >> 4;
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const bool perPeerInput = mode == LL_ALLTOALL || mode == LL_REDUCE_SCATTER;
+    // send
+    for (int i = 1; i < n; ++i) {
+        const int q = (me + i) % n;
+        const char *src = (const char *)a.in + (perPeerInput ? (uint64_t)q * blockBytes : 0);
+        char *slot = LlSlot(d, q, ls.half, me);
+        for (uint64_t v = first; v < nvec; v += stride) LlStore(slot, v, Ld16(src + (v << 4)), tag);
+    }
+    // receive
+    const char *own = (const char *)a.in + (perPeerInput ? (uint64_t)me * blockBytes : 0);
+    if (reducing) {
+        using A = typename AccOf<T>::type;
+        constexpr int N = Pack<T>::N;
+        for (uint64_t v = first; v < nvec; v += stride) {
+            A acc[N];
+            bool ok = true;
+            for (int r = 0; r < n && ok; ++r) {
+                Pack<T> p;
+                if (r == me) p.v = Ld16(own + (v << 4));
+                else ok = LlLoad(d, LlSlot(d, me, ls.half, r), v, tag, r, &p.v);
+                if (r == 0) {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) acc[j] = Widen<T>(p.e[j]);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < N; ++j) acc[j] = Combine<A>(a.op, acc[j], Widen<T>(p.e[j]));
+                }
+            }
+            if (!ok) break;
+            Pack<T> o;
+#pragma unroll
+            for (int j = 0; j < N; ++j) o.e[j] = Narrow<T>(a.useScale ? ScaleAcc<A>(acc[j], a.scale) : acc[j]);
+            St16((char *)a.out + (v << 4), o.v);
+        }
+    } else {
+        for (uint64_t v = first; v < nvec; v += stride) St16((char *)a.out + (uint64_t)me * blockBytes + (v << 4), Ld16(own + (v << 4)));
+        for (int i = 1; i < n; ++i) {
+            const int r = (me + n - i) % n;
+            const char *slot = LlSlot(d, me, ls.half, r);
+            bool ok = true;
+            for (uint64_t v = first; v < nvec && ok; v += stride) {
+                uint4 val;
+                ok = LlLoad(d, slot, v, tag, r, &val);
+                if (ok) St16((char *)a.out + (uint64_t)r * blockBytes + (v << 4), val);
+            }
+            if (!ok) break;
+        }
+    }
+    KernelEnd(d, ls, 0);
+}
+
 template <typename K> struct KernelOf { K fn; };
 
 template <template <typename> class Dummy = AccOf>
@@ -622,6 +726,7 @@ void *ReduceKernelFor(int kind, int dtype)
         case FK_ALLREDUCE_TWOSHOT: HC_PICK(KAllReduceTwoShot)
         case FK_REDUCE_SCATTER: HC_PICK(KReduceScatter)
         case FK_REDUCE: HC_PICK(KReduce)
+        case FK_SMALL_LL: HC_PICK(KSmallLL)
         case FK_ALLREDUCE_NVLS:
             switch (dtype) {
                 case HCCL_DATA_TYPE_FP32: return (void *)KAllReduceNvls<float>;
@@ -672,7 +777,7 @@ void PreloadFastKernels()
 const char *FastKindName(int32_t k)
 {
     static const char *names[] = {"AllReduceOneShot", "AllReduceTwoShot", "AllReduceNvls", "ReduceScatter", "AllGather", "AlltoAll",
-                                  "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier"};
+                                  "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier", "SmallLL"};
     return (k >= 0 && k < FK_COUNT) ? names[k] : "?";
 }
 
@@ -681,7 +786,7 @@ uint32_t FastKindBarriers(int32_t kind, int preBarrier)
     uint32_t k = 1;
     switch (kind) {
         case FK_ALLREDUCE_TWOSHOT: case FK_ALLREDUCE_NVLS: case FK_REDUCE: case FK_BROADCAST_NVLS: k = 2; break;
-        case FK_SEND: case FK_RECV: return 0;
+        case FK_SEND: case FK_RECV: case FK_SMALL_LL: return 0;
         default: k = 1;
     }
     return k + (preBarrier ? 1 : 0);

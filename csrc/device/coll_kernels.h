@@ -29,9 +29,12 @@ enum FastKind : int32_t {
     FK_SEND,
     FK_RECV,
     FK_BARRIER,
+    FK_SMALL_LL,             // flag-in-data exchange for small all-reduce / all-gather / all-to-all / reduce-scatter
     FK_COUNT
 };
 const char *FastKindName(int32_t k);
+
+enum LlMode : int32_t { LL_ALLREDUCE = 0, LL_ALLGATHER = 1, LL_ALLTOALL = 2, LL_REDUCE_SCATTER = 3 };
 
 struct CollArgs {
     CommDev *dev;
@@ -42,7 +45,7 @@ struct CollArgs {
     int32_t dtype;
     int32_t op;
     int32_t root;
-    int32_t peer;            // send / recv partner
+    int32_t peer;            // send / recv partner; FK_SMALL_LL: which collective (LlMode)
     float scale;             // applied to the reduced value when useScale != 0
     int32_t useScale;
     int32_t preBarrier;      // 1: synchronise all ranks before touching peer memory

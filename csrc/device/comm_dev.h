@@ -56,11 +56,16 @@ struct CommDev {
     HcclDeviceWaitStatus *status; /* host-pinned record of the first wait that expired */
     uint64_t *opCounters;    /* device-local {head, tail}: bumped at kernel start / end (the host peeks at them to tell which operator hangs) */
     uint64_t timeoutNs;      /* budget of every device-side wait */
+    uint64_t llOffset;       /* heap offset of the flag-in-data (LL) area: [2 parities][HC_KERNEL_MAX_RANKS sources][HC_LL_SLOT_BYTES] */
 };
 
 /* The structure, the launch counters and the head/tail counters share one device allocation so that a kernel
  * finds its counters at a fixed distance from the structure (no dependent pointer load on the cold path):
  *   [0, 128) CommDev   [128, 640) u32 counters[128]: 0 epoch, 1 launches, 2 blocksDone, ...   [640, 656) u64 {head, tail} */
+/* LL area: every 8 bytes carry 4 bytes of payload and a 4-byte tag; a slot takes HC_LL_MAX_PAYLOAD payload bytes. */
+#define HC_LL_MAX_PAYLOAD (64ull << 10)
+#define HC_LL_SLOT_BYTES (2 * HC_LL_MAX_PAYLOAD)
+
 #define HC_DEV_COUNTERS_OFFSET 128
 #define HC_DEV_OPCOUNTERS_OFFSET 640
 #define HC_DEV_BLOCK_BYTES 1024

@@ -129,3 +129,47 @@ def test_alltoallv_variable_counts(n=4):
             assert torch.equal(recv[r], exp)
     finally:
         _destroy(comms)
+
+
+@pytest.mark.parametrize("n", [2, 4, 8])
+def test_small_message_flag_in_data_kernel(n):
+    """Blocks that are whole 16-byte vectors of at most 32 KB take the barrier-free kernel: repeated calls (the tag and
+    the slot parity advance), in-place all-reduce, and large operators in between."""
+    comms = _make(n)
+    try:
+        per = 2048                                   # 8 KB fp32 blocks
+        for rep in range(5):
+            g = torch.Generator(device="cuda").manual_seed(100 + rep)
+            xs = [torch.randn(per * n, device="cuda", generator=g) for _ in range(n)]
+            ar = [x[:per].clone() for x in xs]
+            rs = [torch.empty(per, device="cuda") for _ in range(n)]
+            ag_out = [torch.empty(per * n, device="cuda") for _ in range(n)]
+            a2a_out = [torch.empty(per * n, device="cuda") for _ in range(n)]
+            big = [torch.randn(300_000, device="cuda", generator=g) for _ in range(n)]
+            big_out = [torch.empty_like(b) for b in big]
+            half = [x[:per].to(torch.bfloat16) for x in xs]
+            half_out = [torch.empty_like(h) for h in half]
+
+            def op(r):
+                torch.cuda.set_device(0)
+                c = comms[r]
+                c.all_reduce(ar[r])                              # in place
+                c.reduce_scatter(xs[r], rs[r])
+                c.all_gather(xs[r][:per], ag_out[r])
+                if rep % 2:
+                    c.all_reduce(big[r], big_out[r])             # a barrier-based kernel between the small ones
+                c.all_to_all(xs[r], a2a_out[r])
+                c.all_reduce(half[r], half_out[r], op="max")
+                torch.cuda.synchronize()
+            run_ranks(n, op)
+            total = sum(x.double() for x in xs)
+            for r in range(n):
+                assert torch.equal(ar[r], ar[0])
+                assert (ar[r].double() - total[:per]).abs().max().item() < 1e-4
+                assert (rs[r].double() - total[r * per:(r + 1) * per]).abs().max().item() < 1e-4
+                assert torch.equal(ag_out[r], torch.cat([x[:per] for x in xs]))
+                assert torch.equal(a2a_out[r], torch.cat([xs[q][r * per:(r + 1) * per] for q in range(n)]))
+                assert torch.equal(half_out[r], torch.stack(half).max(dim=0).values)
+            assert all(c.async_error() == 0 for c in comms)
+    finally:
+        _destroy(comms)
