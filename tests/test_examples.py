@@ -13,6 +13,8 @@ EXAMPLES = [
     ("03_op_dev/mesh_send_recv.cc", ["2"]),
     ("04_team_one_sided/team_signal_put.cc", ["4"]),
     ("04_team_one_sided/team_signal_put.cc", ["2"]),
+    ("05_resources/reduce_scatter_primitives.cc", ["4"]),
+    ("05_resources/reduce_scatter_primitives.cc", ["3"]),
 ]
 
 
