@@ -109,7 +109,7 @@ void EnvConfig::LoadAll()
     nvlsEnable.Load(ParseInt);
     maxCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
     forceCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
-    llMaxBytes.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 65536; });
+    llMaxBytes.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 262144; });
     tuneFile.Load(ParseStr);
     symStrideGB.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 4096; });
 }
