@@ -130,7 +130,7 @@ bool TrySmallLL(Comm *c, const OpDesc &d, const Selection &sel, HcclResult *res)
     const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
     const uint64_t blockBytes = d.count * esz;
     if (blockBytes == 0 || blockBytes % 16 != 0 || blockBytes > (uint64_t)limit || blockBytes > HC_LL_MAX_PAYLOAD) return false;
-    if ((uint64_t)(n - 1) * blockBytes > (512ull << 10)) return false;      // what one rank receives: beyond this the two-phase kernels win
+    if ((uint64_t)(n - 1) * blockBytes > (uint64_t)EnvConfig::Get().llMaxRecvBytes.value) return false;      // what one rank receives: beyond this the two-phase kernels win
     const bool reducing = mode == LL_ALLREDUCE || mode == LL_REDUCE_SCATTER;
     if (reducing && !DtypeReducible(d.dtype)) return false;
     const uint64_t inBytes = (mode == LL_ALLTOALL || mode == LL_REDUCE_SCATTER) ? blockBytes * n : blockBytes;
@@ -145,7 +145,7 @@ bool TrySmallLL(Comm *c, const OpDesc &d, const Selection &sel, HcclResult *res)
     OpDesc typed = d;
     if (!reducing) typed.dtype = HCCL_DATA_TYPE_FP32;                        // byte movers share the fp32 instantiation
     a.dtype = typed.dtype;
-    const int ctas = (int)std::min<uint64_t>(16, std::max<uint64_t>(1, blockBytes / 8192));
+    const int ctas = (int)std::min<uint64_t>(32, std::max<uint64_t>(1, blockBytes / 8192));
     *res = Launch(c, FK_SMALL_LL, a, c->emuSameDevice ? std::min(ctas, 4) : ctas, d.stream);
     return true;
 }

@@ -109,7 +109,8 @@ void EnvConfig::LoadAll()
     nvlsEnable.Load(ParseInt);
     maxCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
     forceCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
-    llMaxBytes.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 262144; });
+    llMaxBytes.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1048576; });
+    llMaxRecvBytes.Load(ParseInt, [](const int32_t &v) { return v >= 0; });
     tuneFile.Load(ParseStr);
     symStrideGB.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 4096; });
 }

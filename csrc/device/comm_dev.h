@@ -63,7 +63,7 @@ struct CommDev {
  * finds its counters at a fixed distance from the structure (no dependent pointer load on the cold path):
  *   [0, 128) CommDev   [128, 640) u32 counters[128]: 0 epoch, 1 launches, 2 blocksDone, ...   [640, 656) u64 {head, tail} */
 /* LL area: every 8 bytes carry 4 bytes of payload and a 4-byte tag; a slot takes HC_LL_MAX_PAYLOAD payload bytes. */
-#define HC_LL_MAX_PAYLOAD (256ull << 10)
+#define HC_LL_MAX_PAYLOAD (1024ull << 10)
 #define HC_LL_SLOT_BYTES (2 * HC_LL_MAX_PAYLOAD)
 
 #define HC_DEV_COUNTERS_OFFSET 128
