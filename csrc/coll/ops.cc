@@ -163,18 +163,6 @@ HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
     if (kind == FK_ALLREDUCE_ONESHOT) maxPerLaunch = oneShotCap;
     else if (kind == FK_ALLREDUCE_TWOSHOT) maxPerLaunch = AlignDownElems(c->halfBytes / (2 * n) / esz, esz) * n;
     else maxPerLaunch = AlignDownElems(c->halfBytes / esz, esz);
-    const uint64_t pipeMin = (uint64_t)EnvConfig::Get().pipeMinMB.value << 20;
-    if (kind == FK_ALLREDUCE_TWOSHOT && n > 1 && pipeMin > 0 && (d.count * esz >= pipeMin || d.count > maxPerLaunch)) {
-        // one launch, chunks pipelined inside: about eight chunks, each slice at most what four-fold staging allows
-        uint64_t slice = AlignedSliceCount((d.count + 7) / 8, n, esz);
-        const uint64_t capSlice = AlignDownElems(c->halfBytes / (4 * n) / esz, esz);
-        const uint64_t minSlice = AlignDownElems(std::max<uint64_t>(16, (4ull << 20) / n / esz), esz);
-        slice = std::max(std::min(slice, capSlice), std::min(minSlice, capSlice));
-        if (slice > 0) {
-            a.in = d.in; a.out = d.out; a.count = d.count; a.sliceElems = slice;
-            return Launch(c, FK_ALLREDUCE_PIPE, a, PickCtas(c, sel, slice * esz * 4), d.stream);
-        }
-    }
     for (uint64_t off = 0; off < d.count; off += maxPerLaunch) {
         uint64_t cnt = std::min(maxPerLaunch, d.count - off);
         a.in = (const char *)d.in + off * esz;
@@ -218,19 +206,6 @@ HcclResult FastReduceScatter(Comm *c, const OpDesc &d, const Selection &sel)
         maxCnt = std::max(maxCnt, cnt[q]);
     }
     uint64_t cap = AlignDownElems(c->halfBytes / n / esz, esz);
-    const uint64_t pipeMin = (uint64_t)EnvConfig::Get().pipeMinMB.value << 20;
-    if (d.sendCounts.empty() && n > 1 && pipeMin > 0 && d.count % (16 / std::min<uint32_t>(esz, 16)) == 0 &&
-        (d.count * esz * n >= pipeMin || d.count > cap)) {
-        // equal blocks (a multiple of 16 bytes each): one launch, about eight pieces per block pipelined inside
-        uint64_t piece = AlignDownElems((d.count + 7) / 8 + (16 / std::min<uint32_t>(esz, 16)) - 1, esz);
-        const uint64_t capPiece = AlignDownElems(c->halfBytes / (2 * n) / esz, esz);
-        const uint64_t minPiece = AlignDownElems(std::max<uint64_t>(16, (4ull << 20) / n / esz), esz);
-        piece = std::max(std::min(piece, capPiece), std::min(minPiece, capPiece));
-        if (piece > 0) {
-            a.in = d.in; a.out = d.out; a.count = d.count; a.sliceElems = piece;
-            return Launch(c, FK_REDUCE_SCATTER_PIPE, a, PickCtas(c, sel, piece * esz * (n - 1) * 4), d.stream);
-        }
-    }
     a.sliceElems = cap;
     a.in = d.in;
     for (uint64_t c0 = 0; c0 < maxCnt; c0 += cap) {

@@ -110,7 +110,6 @@ void EnvConfig::LoadAll()
     maxCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
     forceCtas.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1024; });
     llMaxBytes.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 1048576; });
-    pipeMinMB.Load(ParseInt, [](const int32_t &v) { return v >= 0; });
     llMaxRecvBytes.Load(ParseInt, [](const int32_t &v) { return v >= 0; });
     tuneFile.Load(ParseStr);
     symStrideGB.Load(ParseInt, [](const int32_t &v) { return v >= 0 && v <= 4096; });

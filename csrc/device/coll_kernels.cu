@@ -602,99 +602,6 @@ __global__ void __launch_bounds__(512) KRecv(const __grid_constant__ CollArgs by
     }
 }
 
-// ------------------------------------------------------------- pipelined large all-reduce / reduce-scatter
-
-// The two-shot all-reduce over chunks of n slices, software-pipelined inside one launch: in step s every CTA
-//   * sends its copies of the slices of chunk s to their owners               (NVLink out),
-//   * reduces its own slice of chunk s-1 and fans the result out to the peers (local reads, NVLink out),
-//   * copies the reduced slices of chunk s-2 from its staging to the output   (local),
-// then meets its peers.  The link carries scatter and fan-out traffic of neighbouring chunks at the same time
-// instead of idling during the local phases, at the price of one barrier per chunk.
-// Staging: two buffers (chunk parity) of 2n slots of sliceElems elements: [0,n) partials from the peers, [n,2n)
-// reduced slices from their owners.  A buffer is rewritten two steps after it was read, with a barrier in between.
-// a.count = total elements, a.sliceElems = elements per slice and chunk (a 16-byte multiple).
-template <typename T>
-__global__ void __launch_bounds__(512) KAllReducePipe(const __grid_constant__ CollArgs byval, const CollArgs *emu)
-{
-    HC_ARGS;
-    const LaunchState ls = KernelBegin(d);
-    uint32_t used = MaybePreBarrier(d, a, ls);
-    const int n = d->nRanks, me = d->rank;
-    const uint64_t S = a.sliceElems, slotBytes = S * sizeof(T), chunkElems = S * (uint64_t)n;
-    const uint64_t nChunks = (a.count + chunkElems - 1) / chunkElems;
-    auto Buf = [&](int rank, uint64_t chunk) { return CclHalf(d, rank, ls.half) + (chunk & 1) * (2ull * n) * slotBytes; };
-    auto Range = [&](uint64_t chunk, int q, uint64_t *beg, uint64_t *len) {
-        const uint64_t c0 = chunk * chunkElems, cEnd = c0 + chunkElems < a.count ? c0 + chunkElems : a.count;
-        uint64_t b = c0 + (uint64_t)q * S;
-        b = b < cEnd ? b : cEnd;
-        const uint64_t e = b + S < cEnd ? b + S : cEnd;
-        *beg = b; *len = e - b;
-    };
-    uint64_t beg, len;
-    for (uint64_t step = 0; step < nChunks + 2; ++step) {
-        if (step < nChunks) {                       // scatter chunk `step`
-            for (int i = 1; i < n; ++i) {
-                const int q = (me + i) % n;
-                Range(step, q, &beg, &len);
-                GridCopy(Buf(q, step) + (uint64_t)me * slotBytes, (const char *)a.in + beg * sizeof(T), len * sizeof(T), sizeof(T));
-            }
-        }
-        if (step >= 1 && step <= nChunks) {         // reduce my slice of chunk step-1, fan out
-            const uint64_t c = step - 1;
-            Range(c, me, &beg, &len);
-            const char *src[HC_KERNEL_MAX_RANKS];
-            char *dst[HC_KERNEL_MAX_RANKS];
-            for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + beg * sizeof(T) : Buf(me, c) + (uint64_t)r * slotBytes;
-            int nd = 0;
-            dst[nd++] = (char *)a.out + beg * sizeof(T);
-            for (int i = 1; i < n; ++i) dst[nd++] = Buf((me + i) % n, c) + (uint64_t)(n + me) * slotBytes;
-            ReduceFanOut<T>(src, n, dst, nd, len, a.op, a.useScale, a.scale);
-        }
-        if (step >= 2) {                            // copy out chunk step-2
-            const uint64_t c = step - 2;
-            for (int i = 1; i < n; ++i) {
-                const int q = (me + i) % n;
-                Range(c, q, &beg, &len);
-                GridCopy((char *)a.out + beg * sizeof(T), Buf(me, c) + (uint64_t)(n + q) * slotBytes, len * sizeof(T), sizeof(T));
-            }
-        }
-        if (step + 1 < nChunks + 2) CrossRankBarrier(d, ls.epoch0 + (++used));
-    }
-    KernelEnd(d, ls, used);
-}
-
-// Reduce-scatter of equal blocks, pipelined the same way: step s sends the s-th piece of every block to its owner and
-// reduces the (s-1)-th piece of my block.  a.count = elements per block, a.sliceElems = elements per piece;
-// staging: two buffers of n slots of sliceElems elements.
-template <typename T>
-__global__ void __launch_bounds__(512) KReduceScatterPipe(const __grid_constant__ CollArgs byval, const CollArgs *emu)
-{
-    HC_ARGS;
-    const LaunchState ls = KernelBegin(d);
-    uint32_t used = MaybePreBarrier(d, a, ls);
-    const int n = d->nRanks, me = d->rank;
-    const uint64_t S = a.sliceElems, slotBytes = S * sizeof(T);
-    const uint64_t nPieces = (a.count + S - 1) / S;
-    auto Buf = [&](int rank, uint64_t piece) { return CclHalf(d, rank, ls.half) + (piece & 1) * (uint64_t)n * slotBytes; };
-    for (uint64_t step = 0; step < nPieces + 1; ++step) {
-        if (step < nPieces) {
-            const uint64_t off = step * S, len = off + S < a.count ? S : a.count - off;
-            for (int i = 1; i < n; ++i) {
-                const int q = (me + i) % n;
-                GridCopy(Buf(q, step) + (uint64_t)me * slotBytes, (const char *)a.in + ((uint64_t)q * a.count + off) * sizeof(T), len * sizeof(T), sizeof(T));
-            }
-        }
-        if (step >= 1) {
-            const uint64_t p = step - 1, off = p * S, len = off + S < a.count ? S : a.count - off;
-            const char *src[HC_KERNEL_MAX_RANKS];
-            for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + ((uint64_t)me * a.count + off) * sizeof(T) : Buf(me, p) + (uint64_t)r * slotBytes;
-            ReduceAuto<T>(src, n, (char *)a.out + off * sizeof(T), nullptr, len, a.op, a.useScale, a.scale);
-        }
-        if (step + 1 < nPieces + 1) CrossRankBarrier(d, ls.epoch0 + (++used));
-    }
-    KernelEnd(d, ls, used);
-}
-
 // ------------------------------------------------------------------------ small messages (LL)
 
 // Flag-in-data exchange: every 8 bytes written to a peer hold 4 bytes of payload and the 4-byte tag of this launch,
@@ -820,8 +727,6 @@ void *ReduceKernelFor(int kind, int dtype)
         case FK_REDUCE_SCATTER: HC_PICK(KReduceScatter)
         case FK_REDUCE: HC_PICK(KReduce)
         case FK_SMALL_LL: HC_PICK(KSmallLL)
-        case FK_ALLREDUCE_PIPE: HC_PICK(KAllReducePipe)
-        case FK_REDUCE_SCATTER_PIPE: HC_PICK(KReduceScatterPipe)
         case FK_ALLREDUCE_NVLS:
             switch (dtype) {
                 case HCCL_DATA_TYPE_FP32: return (void *)KAllReduceNvls<float>;
@@ -872,7 +777,7 @@ void PreloadFastKernels()
 const char *FastKindName(int32_t k)
 {
     static const char *names[] = {"AllReduceOneShot", "AllReduceTwoShot", "AllReduceNvls", "ReduceScatter", "AllGather", "AlltoAll",
-                                  "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier", "SmallLL", "AllReducePipe", "ReduceScatterPipe"};
+                                  "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier", "SmallLL"};
     return (k >= 0 && k < FK_COUNT) ? names[k] : "?";
 }
 

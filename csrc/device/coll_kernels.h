@@ -30,8 +30,6 @@ enum FastKind : int32_t {
     FK_RECV,
     FK_BARRIER,
     FK_SMALL_LL,             // flag-in-data exchange for small all-reduce / all-gather / all-to-all / reduce-scatter
-    FK_ALLREDUCE_PIPE,       // two-shot all-reduce, chunks software-pipelined inside one launch
-    FK_REDUCE_SCATTER_PIPE,  // reduce-scatter, chunks software-pipelined inside one launch
     FK_COUNT
 };
 const char *FastKindName(int32_t k);

@@ -173,43 +173,3 @@ def test_small_message_flag_in_data_kernel(n):
             assert all(c.async_error() == 0 for c in comms)
     finally:
         _destroy(comms)
-
-
-@pytest.mark.parametrize("n,dtype", [(2, torch.float32), (4, torch.bfloat16), (8, torch.float32)])
-def test_pipelined_allreduce_and_reduce_scatter(n, dtype, monkeypatch):
-    """Large all-reduce and reduce-scatter run chunk-pipelined inside one launch; a small buffer (1 MB halves) and a low
-    threshold make ordinary test sizes take that path with many chunks, ragged ends included."""
-    monkeypatch.setenv("HCCL_PIPE_MIN_MB", "1")
-    from hcomm_b200 import _lib
-    _lib.load().HcommToolReloadEnv()
-    comms = _make(n, buffer_mb=1)
-    try:
-        for count in (1_000_003, 4_500_001):
-            g = torch.Generator(device="cuda").manual_seed(count)
-            xs = [torch.randn(count, device="cuda", generator=g).to(dtype) for _ in range(n)]
-            outs = [torch.empty_like(x) for x in xs]
-            per = 262144 + 64
-            rs_in = [torch.randn(per * n, device="cuda", generator=g).to(dtype) for _ in range(n)]
-            rs_out = [torch.empty(per, device="cuda", dtype=dtype) for _ in range(n)]
-
-            def op(r):
-                torch.cuda.set_device(0)
-                comms[r].all_reduce(xs[r], outs[r])
-                comms[r].reduce_scatter(rs_in[r], rs_out[r])
-                comms[r].all_reduce_scaled(xs[r], outs[r], scale=0.5) if count > 2_000_000 else None
-                torch.cuda.synchronize()
-            run_ranks(n, op)
-            scale = 0.5 if count > 2_000_000 else 1.0
-            ref = sum(x.double() for x in xs) * scale
-            tol = (1e-5 if dtype == torch.float32 else 4e-2) * (n ** 0.5) * 4
-            for r in range(n):
-                assert torch.equal(outs[r], outs[0]), "ranks disagree"
-            assert (outs[0].double() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
-            total = sum(x.double() for x in rs_in)
-            for r in range(n):
-                assert (rs_out[r].double() - total[r * per:(r + 1) * per]).abs().max().item() <= tol * max(1.0, total.abs().max().item())
-            assert all(c.async_error() == 0 for c in comms)
-    finally:
-        _destroy(comms)
-        monkeypatch.delenv("HCCL_PIPE_MIN_MB")
-        _lib.load().HcommToolReloadEnv()
