@@ -68,7 +68,7 @@ def main():
         info = box[0]
     else:
         info = hb.get_root_info()
-    comm = hb.Communicator(world, info, rank, buffer_mb=200)
+    comm = hb.Communicator(world, info, rank, buffer_mb=512)
     mlp = TensorParallelMlp(comm, HIDDEN, INTER, device=dev, seed=1)
     rows = TOKENS // world
     g = torch.Generator(device=dev).manual_seed(100 + rank)
