@@ -47,8 +47,8 @@ struct EnvConfig {
     EnvField<int32_t> nvlsEnable{"HCCL_NVLS_ENABLE", 1};
     EnvField<int32_t> maxCtas{"HCCL_MAX_CTAS", 0};          // upper bound of CTAs per collective kernel; 0 = selector decides
     EnvField<int32_t> forceCtas{"HCCL_FORCE_CTAS", 0};      // exact CTA count (tuning runs); 0 = off
-    EnvField<int32_t> llMaxBytes{"HCCL_LL_MAX_BYTES", 1048576};
-    EnvField<int32_t> llMaxRecvBytes{"HCCL_LL_MAX_RECV_BYTES", 1048576};   // and the most one rank may receive that way, (ranks - 1) x block   // largest block (bytes per peer) the flag-in-data kernel serves; 0 = never
+    EnvField<int32_t> llMaxBytes{"HCCL_LL_MAX_BYTES", 1048576};            // largest block (bytes per peer) the flag-in-data kernel serves; 0 = never
+    EnvField<int32_t> llMaxRecvBytes{"HCCL_LL_MAX_RECV_BYTES", 1048576};   // and the most one rank may receive that way, (ranks - 1) x block
     EnvField<std::string> tuneFile{"HCCL_TUNE_FILE", ""};   // measured bus-bandwidth table (JSON)
     EnvField<int32_t> symStrideGB{"HCCL_SYM_STRIDE_GB", 0};
 
