@@ -132,6 +132,12 @@ class Communicator:
             cfg.hcclBufferSize = cfg_kw["buffer_mb"]
         if "name" in cfg_kw:
             cfg.hcclCommName = cfg_kw["name"].encode()
+        if "algo" in cfg_kw:
+            cfg.hcclAlgo = cfg_kw["algo"].encode()
+        if "deterministic" in cfg_kw:
+            cfg.hcclDeterministic = cfg_kw["deterministic"]
+        if "op_expansion_mode" in cfg_kw:
+            cfg.hcclOpExpansionMode = cfg_kw["op_expansion_mode"]
         ids = (ctypes.c_uint32 * len(rank_ids))(*rank_ids)
         sub = ctypes.c_void_p()
         check(self._lib.HcclCreateSubCommConfig(ctypes.byref(self._h), len(rank_ids), ids, ctypes.c_uint64(sub_id), list(rank_ids).index(self.rank),

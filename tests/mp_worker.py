@@ -351,14 +351,47 @@ def main():
         assert f"rank {rank}/{world}" in text.value.decode()
         stage("lifecycle ok")
     elif scenario == "forced_algos":
-        import torch
-        for algo in ("level0:ring", "level0:H-D_R"):
-            c2 = comm.split(list(range(world)), sub_id=hash(algo) % 1000, buffer_mb=8)
-            # algorithm forcing is a communicator property: build one per algorithm through the environment is not
-            # possible after start-up, so use the config field
+        # every forced algorithm family on its own sub-communicator; on GPUs the non-mesh ones run on the stream engine
+        if use_cuda:
+            import torch
+
+            def make(count, dtype, fill):
+                t = torch.full((count,), float(fill), device="cuda").to(dtype)
+                return t
+
+            def vals(t):
+                torch.cuda.synchronize()
+                return t.float().cpu().numpy()
+            f32, i32 = torch.float32, torch.int32
+        else:
+            def make(count, dtype, fill):
+                return np.full(count, fill, dtype)
+
+            def vals(t):
+                return t.astype(np.float64)
+            f32, i32 = np.float32, np.int32
+        for k, algo in enumerate(("level0:ring", "level0:H-D_R", "level0:pairwise", "level0:NB", "level0:fullmesh")):
+            c2 = comm.split(list(range(world)), sub_id=100 + k, buffer_mb=4, algo=algo)
+            count = 30_011
+            x, y = make(count, f32, rank + 1), make(count, f32, 0)
+            c2.all_reduce(x, y)
+            assert (vals(y) == world * (world + 1) / 2).all(), (algo, "all_reduce")
+            g = make(count * world, i32, -1)
+            c2.all_gather(make(count, i32, rank), g)
+            assert (vals(g).reshape(world, count) == np.arange(world).reshape(world, 1)).all(), (algo, "all_gather")
+            rs = make(count, f32, 0)
+            c2.reduce_scatter(make(count * world, f32, rank), rs)
+            assert (vals(rs) == world * (world - 1) / 2).all(), (algo, "reduce_scatter")
+            a_in, a_out = make(count * world, i32, rank), make(count * world, i32, -1)
+            c2.all_to_all(a_in, a_out)
+            assert (vals(a_out).reshape(world, count) == np.arange(world).reshape(world, 1)).all(), (algo, "all_to_all")
+            b = make(count, f32, rank)
+            c2.broadcast(b, root=world - 1)
+            assert (vals(b) == world - 1).all(), (algo, "broadcast")
+            assert c2.async_error() == 0
+            stage(f"{algo} ok")
             c2.destroy()
         comm.barrier()
-        torch.cuda.synchronize()
     elif scenario == "peer_exit":
         # One rank leaves between steps; the others learn it from the control plane before their next launch.
         x = np.ones(10, np.float32) if not use_cuda else None

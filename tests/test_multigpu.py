@@ -37,3 +37,10 @@ def test_torch_backend_across_gpus(scenario):
     env = {"HCOMM_TORCH_BUFFER_MB": "16", "HCCL_EXEC_TIMEOUT": "20", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29651"}
     codes, outs = launch(scenario, 2, env, timeout=200)
     assert codes == [0, 0], "\n".join(outs)
+
+
+def test_forced_algorithm_families_across_gpus():
+    if cuda_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    codes, outs = launch("forced_algos", 2, {"HCOMM_TEST_BUFFER_MB": "8", "HCCL_EXEC_TIMEOUT": "20"}, timeout=200)
+    assert codes == [0, 0], "\n".join(outs)

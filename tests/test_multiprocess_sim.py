@@ -39,3 +39,8 @@ def test_named_groups_and_gradient_split_through_the_python_package():
 def test_suspend_resume_snapshot_and_diagnostics():
     codes, outs = launch("lifecycle", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=120)
     assert codes == [0, 0, 0], "\n".join(outs)
+
+
+def test_forced_algorithm_families_on_sub_communicators():
+    codes, outs = launch("forced_algos", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=180)
+    assert codes == [0, 0, 0], "\n".join(outs)
