@@ -3,6 +3,7 @@
     python -m hcomm_b200.utils.profile_cases gemm            tcgen05 GEMM 8192^3 bf16 (operands larger than L2)
     python -m hcomm_b200.utils.profile_cases fused           GEMM->ReduceScatter and AllGather->GEMM, two ranks sharing the GPU
     python -m hcomm_b200.utils.profile_cases allreduce       one-shot, two-shot all-reduce and all-gather kernels, two ranks sharing the GPU
+    python -m hcomm_b200.utils.profile_cases fused_pair      the CTA-pair variants of the two fused kernels on a one-rank communicator
     python -m hcomm_b200.utils.profile_cases moe             MoE dispatch + combine, one rank (256 experts, top-8, hidden 7168)
 
 Ranks that share the GPU run inside ONE cooperative launch (kernels that wait for each other are never separate
@@ -73,10 +74,28 @@ def case_fused(reps=2):
     _ranks(n, lambda r: comms[r].destroy())
 
 
+def case_fused_pair(reps=2):
+    """One rank: every tile is the rank's own, nothing crosses NVLink; shows the tensor-core side of the pair kernels
+    (ranks that share a GPU use the single-CTA variants, so the two-rank case above cannot show them)."""
+    import hcomm_b200 as hb
+    from ..ops.fused import all_gather_gemm, gemm_reduce_scatter
+    from ..ops.gemm import take_kernel_error
+    comm = hb.Communicator(1, hb.get_root_info(), 0, buffer_mb=160)
+    m, nn, k = 8192, 4096, 8192
+    a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(nn, k, device="cuda") * 0.02).to(torch.bfloat16)
+    for _ in range(reps):
+        gemm_reduce_scatter(comm, a, b)
+        all_gather_gemm(comm, a, b)
+    torch.cuda.synchronize()
+    assert take_kernel_error() == 0
+    comm.destroy()
+
+
 def case_allreduce(reps=2):
     n = 2
     comms = _comms(n, 64)
-    small = [torch.randn(16 << 10, device="cuda").to(torch.bfloat16) for _ in range(n)]       # 32 KB: one-shot
+    small = [torch.randn(16 << 10, device="cuda").to(torch.bfloat16) for _ in range(n)]       # 32 KB: flag-in-data kernel
     big = [torch.randn(32 << 20, device="cuda").to(torch.bfloat16) for _ in range(n)]         # 64 MB: two-shot
     outs = [torch.empty_like(big[r]) for r in range(n)]
     gathered = [torch.empty(n * (16 << 20), device="cuda", dtype=torch.bfloat16) for _ in range(n)]
@@ -114,7 +133,7 @@ def case_moe(reps=2):
 def main():
     torch.cuda.set_device(0)
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": case_gemm, "fused": case_fused, "allreduce": case_allreduce, "moe": case_moe}[which]()
+    {"gemm": case_gemm, "fused": case_fused, "fused_pair": case_fused_pair, "allreduce": case_allreduce, "moe": case_moe}[which]()
     print(f"profile case {which}: done", flush=True)
 
 
