@@ -321,7 +321,8 @@ HcclResult FastSendRecv(Comm *c, const OpDesc &d, bool send, Stream stream)
 
 // ------------------------------------------------------------------------------- host drivers
 
-HcclResult HostCollective(Comm *c, const OpDesc &d, const Selection &sel)
+// Builds (or finds in the per-communicator cache) the schedule of an operator.
+static HcclResult GetSchedule(Comm *c, const OpDesc &d, const Selection &sel, std::shared_ptr<Schedule> *out)
 {
     CollShape sh;
     sh.cmd = d.cmd;
@@ -369,6 +370,14 @@ HcclResult HostCollective(Comm *c, const OpDesc &d, const Selection &sel)
             c->schedCache[key] = sched;
         }
     }
+    *out = sched;
+    return HCCL_SUCCESS;
+}
+
+HcclResult HostCollective(Comm *c, const OpDesc &d, const Selection &sel)
+{
+    std::shared_ptr<Schedule> sched;
+    CHK_RET(GetSchedule(c, d, sel, &sched));
     // All-to-all with per-rank counts: every rank must walk the same number of passes, so the ranks agree on
     // the longest block of the job over the control plane (the reference gathers the whole count matrix
     // for the same reason before it stages AlltoAllV).
@@ -476,6 +485,71 @@ HcclResult FastBatchSendRecv(Comm *c, const OpDesc &d)
 
 }  // namespace
 
+// Engine "sm-ir": the schedule of a forced (non-mesh) algorithm runs in the interpreter kernel, one launch per column
+// pass.  Operators with per-rank counts and programs longer than a ring slot stay on the stream engine.
+constexpr uint32_t kIrSlotPrims = 2048;
+HcclResult IrCollective(Comm *c, const OpDesc &d, const Selection &sel, bool *served)
+{
+    *served = false;
+    if (!d.sendCounts.empty() || !d.recvCounts.empty() || c->nRanks > HC_KERNEL_MAX_RANKS || !IrKernelFor(d.dtype)) return HCCL_SUCCESS;
+    switch (d.cmd) {
+        case HCCL_CMD_ALLREDUCE: case HCCL_CMD_ALLGATHER: case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_ALLTOALL: case HCCL_CMD_BROADCAST:
+        case HCCL_CMD_REDUCE: case HCCL_CMD_SCATTER: case HCCL_CMD_GATHER: break;
+        default: return HCCL_SUCCESS;
+    }
+    std::shared_ptr<Schedule> sched;
+    CHK_RET(GetSchedule(c, d, sel, &sched));
+    const Schedule &s = *sched;
+    const SliceLayout &in = s.In(c->rank), &out = s.Out(c->rank);
+    const RankProgram &prog = s.ranks[c->rank];
+    if (!in.displ.empty() || !in.count.empty() || !out.displ.empty() || !out.count.empty() || prog.prims.size() > kIrSlotPrims || s.nNotify > HC_IR_NOTIFY) return HCCL_SUCCESS;
+    const uint32_t esz = DtypeSize(d.dtype);
+    const uint64_t cap = ScratchCapacityElems(c, s, esz);
+    if (cap == 0) return HCCL_SUCCESS;
+    if (!c->irPrimRing) CHK_RET(c->plat->DevAlloc(sizeof(DevPrim) * kIrSlotPrims * 8, &c->irPrimRing));
+    std::vector<DevPrim> dev(prog.prims.size());
+    for (size_t i = 0; i < prog.prims.size(); ++i) {
+        const Prim &p = prog.prims[i];
+        DevPrim &q = dev[i];
+        memset(&q, 0, sizeof(q));
+        q.op = (uint8_t)p.op; q.thread = p.thread; q.srcBuf = (uint8_t)p.srcBuf; q.dstBuf = (uint8_t)p.dstBuf; q.peer = p.peer; q.notify = p.notify;
+        q.srcSlice = p.srcSlice; q.dstSlice = p.dstSlice; q.nSlices = p.nSlices; q.toThread = p.toThread; q.step = p.step; q.lenBuf = (uint8_t)p.lenBuf;
+        q.lenSlice = p.lenSlice;
+        if (p.op != PrimOp::POST && p.op != PrimOp::WAIT && p.op != PrimOp::NOP && (p.lenBuf == BufId::NONE || p.srcBuf == BufId::NONE || p.dstBuf == BufId::NONE)) return HCCL_SUCCESS;
+    }
+    DevPrim *slot = (DevPrim *)c->irPrimRing + (size_t)c->irPrimNext * kIrSlotPrims;
+    c->irPrimNext = (c->irPrimNext + 1) % 8;
+    // the source is pageable host memory: the runtime stages it before the call returns, so the vector may go away
+    if (!dev.empty()) CHK_RET(c->plat->MemcpyAsync(slot, dev.data(), sizeof(DevPrim) * dev.size(), d.stream));
+    uint64_t maxSlice = std::max(in.sliceCount, out.sliceCount);
+    for (auto &L : s.input) maxSlice = std::max(maxSlice, L.sliceCount);
+    for (auto &L : s.output) maxSlice = std::max(maxSlice, L.sliceCount);
+    const uint64_t q16 = esz >= 16 ? 1 : 16 / esz, chunk = cap / q16 * q16;
+    const uint64_t passes = maxSlice == 0 ? 1 : (maxSlice + chunk - 1) / chunk;
+    IrArgs a;
+    memset(&a, 0, sizeof(a));
+    a.dev = c->devStruct; a.prims = slot; a.nPrims = (uint32_t)dev.size(); a.dtype = d.dtype; a.op = d.op; a.elemSize = esz; a.in = d.in; a.out = d.out;
+    a.lay[0] = {in.sliceCount, in.total}; a.lay[1] = {out.sliceCount, out.total}; a.lay[2] = {s.scratch.sliceCount, s.scratch.total};
+    a.cap = cap;
+    int ctas = (int)std::min<uint64_t>(HC_IR_MAX_CTAS, std::max<uint64_t>(1, std::min(maxSlice, chunk) * esz / (64 << 10)));
+    if (c->emuSameDevice) ctas = std::min(ctas, 4);
+    for (uint64_t pass = 0; pass < passes; ++pass) {
+        a.col0 = pass * chunk; a.col1 = (pass + 1) * chunk;
+        a.preBarrier = c->lastOpOnHost ? 1 : 0;
+        HcclResult r;
+        if (c->emuSameDevice && c->nRanks > 1) {
+            r = EmuLaunchGeneric(c->identifier + "#ir" + std::to_string(c->group.id), c->nRanks, c->rank, 9200 + (int)d.cmd, &a, sizeof(a), d.stream,
+                                 [=](const void *devTable, uint32_t n, void *st) { return LaunchIrKernel(a, ctas, st, (const IrArgs *)devTable, (int)n); });
+        } else {
+            r = LaunchIrKernel(a, ctas, d.stream, nullptr, 0);
+        }
+        CHK_RET(r);
+        c->lastOpOnHost = false;
+    }
+    *served = true;
+    return HCCL_SUCCESS;
+}
+
 // A specialised kernel that follows a host-engine operator must not touch peer staging before every rank has
 // left that operator; fused kernels (which have no barrier of their own) call this first.
 HcclResult LaunchBarrierIfNeeded(Comm *c, void *stream)
@@ -556,8 +630,15 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
     }
 
     HcclResult r = HCCL_SUCCESS;
-    if (sel.engine == Engine::SM_IR) sel.engine = Engine::HOST;   // the stream engine runs every template
-    if (sel.engine == Engine::HOST) {
+    bool irServed = false;
+    if (sel.engine == Engine::SM_IR) {
+        r = IrCollective(c, d, sel, &irServed);
+        if (r != HCCL_SUCCESS) { Record(c, d, sel, t0); return r; }
+        if (!irServed) sel.engine = Engine::HOST;   // the stream engine runs every template
+    }
+    if (irServed) {
+        // done by the interpreter kernel
+    } else if (sel.engine == Engine::HOST) {
         if (cuda && c->emuSameDevice && c->nRanks > 1) {
             RPT_ERR("EI0003", "the stream engine cannot run ranks that share one GPU; use the SM kernels or the simulator");
             return HCCL_E_NOT_SUPPORT;

@@ -401,6 +401,7 @@ Comm::~Comm()
     if (heapPhys.bytes) plat->PhysRelease(&heapPhys);
     if (fusedParamRing) plat->DevFree(fusedParamRing);
     if (fusedExpectRing) plat->DevFree(fusedExpectRing);
+    if (irPrimRing) plat->DevFree(irPrimRing);
     if (devStruct) plat->DevFree(devStruct);
     if (devIrCounters) plat->DevFree(devIrCounters);
     if (abortWord) plat->HostFree(abortWord);

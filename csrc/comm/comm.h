@@ -138,6 +138,8 @@ struct Comm {
     void *fusedExpectRing = nullptr;             // device ring: 16 tables of 8192 u32
     int fusedExpectNext = 0;
     void *fusedParamRing = nullptr;              // device ring of kernel parameter blocks
+    void *irPrimRing = nullptr;                  // device ring of interpreter programs (8 slots of 2048 primitives)
+    int irPrimNext = 0;
     int fusedParamNext = 0;
     bool lastOpOnHost = true;                    // the next specialised kernel must start with a barrier
     PhysMem mcPhys;

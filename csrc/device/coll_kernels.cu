@@ -28,6 +28,7 @@
 //   Send / Recv         A5 aiv_send_mesh_1D.h / aiv_recv_mesh_1D.h
 #include <cuda_runtime.h>
 
+#include "../alg/ir.h"
 #include "../core/log.h"
 #include "coll_kernels.h"
 #include "hcomm_device.cuh"
@@ -706,6 +707,168 @@ __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs
     KernelEnd(d, ls, 0);
 }
 
+// ------------------------------------------------------------------- schedule interpreter (sm-ir)
+
+// Runs this rank's program of a Schedule (ring, halving-doubling, Bruck, pairwise, tree ... templates) in one launch.
+// Every CTA walks the whole program; of each slice it moves the 2048-element blocks b with b % gridDim.x == blockIdx.x,
+// counted from the start of the slice, so the same elements belong to the same CTA index on every rank whatever the
+// alignment of the buffers, and POST / WAIT can be per-CTA: CTA i signals CTA i of the peer through notify words
+// [cta][from][slot] in the control region and consumes posts with device-resident counters (they survive the launch,
+// a wait expects one more post than the previous wait on that word).  Primitives run in program order, which is the
+// order the host engine runs them in on one stream.
+template <typename T>
+__device__ __forceinline__ void IrMove(char *dst, const char *src, uint64_t n, bool reduce, int op)
+{
+    using A = typename AccOf<T>::type;
+    constexpr uint64_t kBlock = 2048;
+    constexpr int N = Pack<T>::N;
+    const uint64_t nBlocks = (n + kBlock - 1) / kBlock;
+    for (uint64_t b = blockIdx.x; b < nBlocks; b += gridDim.x) {
+        const uint64_t e0 = b * kBlock, cnt = n - e0 < kBlock ? n - e0 : kBlock;
+        const char *ps = src + e0 * sizeof(T);
+        char *pd = dst + e0 * sizeof(T);
+        uint64_t done = 0;
+        if ((((uintptr_t)ps | (uintptr_t)pd) & 15) == 0) {
+            const uint64_t nvec = cnt / N;
+            for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+                Pack<T> s;
+                s.v = Ld16Volatile(ps + (v << 4));
+                if (reduce) {
+                    Pack<T> t;
+                    t.v = Ld16Volatile(pd + (v << 4));
+#pragma unroll
+                    for (int j = 0; j < N; ++j) t.e[j] = Narrow<T>(Combine<A>(op, Widen<T>(t.e[j]), Widen<T>(s.e[j])));
+                    s = t;
+                }
+                St16(pd + (v << 4), s.v);
+            }
+            done = nvec * N;
+        }
+        for (uint64_t e = done + threadIdx.x; e < cnt; e += blockDim.x) {
+            T s = *(volatile const T *)(ps + e * sizeof(T));
+            if (reduce) s = Narrow<T>(Combine<A>(op, Widen<T>(*(volatile const T *)(pd + e * sizeof(T))), Widen<T>(s)));
+            *(T *)(pd + e * sizeof(T)) = s;
+        }
+    }
+}
+template <> __device__ __forceinline__ void IrMove<__half>(char *dst, const char *src, uint64_t n, bool reduce, int op);
+template <> __device__ __forceinline__ void IrMove<__nv_bfloat16>(char *dst, const char *src, uint64_t n, bool reduce, int op);
+
+// 16-bit floating types: the scalar tail goes through their bit patterns (volatile class-type loads do not compile)
+template <typename T>
+__device__ __forceinline__ void IrMoveHalfLike(char *dst, const char *src, uint64_t n, bool reduce, int op)
+{
+    constexpr uint64_t kBlock = 2048;
+    constexpr int N = 8;
+    const uint64_t nBlocks = (n + kBlock - 1) / kBlock;
+    for (uint64_t b = blockIdx.x; b < nBlocks; b += gridDim.x) {
+        const uint64_t e0 = b * kBlock, cnt = n - e0 < kBlock ? n - e0 : kBlock;
+        const char *ps = src + e0 * 2;
+        char *pd = dst + e0 * 2;
+        uint64_t done = 0;
+        if ((((uintptr_t)ps | (uintptr_t)pd) & 15) == 0) {
+            const uint64_t nvec = cnt / N;
+            for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
+                Pack<T> s;
+                s.v = Ld16Volatile(ps + (v << 4));
+                if (reduce) {
+                    Pack<T> t;
+                    t.v = Ld16Volatile(pd + (v << 4));
+#pragma unroll
+                    for (int j = 0; j < N; ++j) t.e[j] = Narrow<T>(Combine<float>(op, Widen<T>(t.e[j]), Widen<T>(s.e[j])));
+                    s = t;
+                }
+                St16(pd + (v << 4), s.v);
+            }
+            done = nvec * N;
+        }
+        for (uint64_t e = done + threadIdx.x; e < cnt; e += blockDim.x) {
+            unsigned short sb = *(volatile const unsigned short *)(ps + e * 2);
+            if (reduce) {
+                unsigned short db = *(volatile const unsigned short *)(pd + e * 2);
+                T sv, dv;
+                memcpy(&sv, &sb, 2); memcpy(&dv, &db, 2);
+                T r = Narrow<T>(Combine<float>(op, Widen<T>(dv), Widen<T>(sv)));
+                memcpy(&sb, &r, 2);
+            }
+            *(unsigned short *)(pd + e * 2) = sb;
+        }
+    }
+}
+template <> __device__ __forceinline__ void IrMove<__half>(char *dst, const char *src, uint64_t n, bool reduce, int op) { IrMoveHalfLike<__half>(dst, src, n, reduce, op); }
+template <> __device__ __forceinline__ void IrMove<__nv_bfloat16>(char *dst, const char *src, uint64_t n, bool reduce, int op) { IrMoveHalfLike<__nv_bfloat16>(dst, src, n, reduce, op); }
+
+template <typename T>
+__global__ void __launch_bounds__(512) KIrInterp(const __grid_constant__ IrArgs byval, const IrArgs *emu)
+{
+    const IrArgs &a = (emu != nullptr) ? emu[blockIdx.y] : byval;
+    const CommDev *d = a.dev;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = 0;
+    if (a.preBarrier) CrossRankBarrier(d, ls.epoch0 + (++used));
+    const int me = d->rank;
+    const DevPrim *prims = (const DevPrim *)a.prims;
+    const uint32_t esz = a.elemSize;
+    auto Word = [&](int owner, int from, uint32_t slot) {
+        return (uint64_t *)(HcPeerHeap(d, owner) + HC_OFF_IR_NOTIFY) + ((uint64_t)blockIdx.x * HC_MAX_RANKS + (uint64_t)from) * HC_IR_NOTIFY + slot;
+    };
+    auto Count = [&](uint32_t buf, uint32_t slice) -> uint64_t {      // elements of a slice inside the column window
+        const IrLayoutDev &L = a.lay[buf];
+        const uint64_t b0 = (uint64_t)slice * L.sliceCount;
+        uint64_t cnt = b0 >= L.total ? 0 : (L.total - b0 < L.sliceCount ? L.total - b0 : L.sliceCount);
+        if (cnt <= a.col0) return 0;
+        return (cnt < a.col1 ? cnt : a.col1) - a.col0;
+    };
+    auto Addr = [&](uint32_t buf, uint32_t slice, int rank) -> char * {
+        if (buf == 2) return CclHalf(d, rank, ls.half) + (uint64_t)slice * a.cap * esz;
+        char *base = buf == 0 ? (char *)a.in : (char *)a.out;
+        return base + ((uint64_t)slice * a.lay[buf].sliceCount + a.col0) * esz;
+    };
+    bool alive = true;
+    for (uint32_t i = 0; i < a.nPrims && alive; ++i) {
+        const DevPrim p = prims[i];
+        switch (p.op) {
+            case 6: {   // POST
+                __syncthreads();
+                if (threadIdx.x == 0) {
+                    __threadfence_system();
+                    RedReleaseSysAdd64(Word(p.peer, me, p.notify), 1ull);
+                }
+                break;
+            }
+            case 7: {   // WAIT
+                __shared__ int okFlag;
+                if (threadIdx.x == 0) {
+                    uint64_t *consumed = d->irConsumed + ((uint64_t)blockIdx.x * HC_MAX_RANKS + (uint64_t)p.peer) * HC_IR_NOTIFY + p.notify;
+                    const uint64_t expect = *consumed + 1;
+                    *consumed = expect;
+                    okFlag = WaitFlagGe64(d, Word(me, p.peer, p.notify), expect, (uint32_t)p.peer, HC_WAIT_CHAN_NOTIFY, p.notify) ? 1 : 0;
+                }
+                __syncthreads();
+                alive = okFlag != 0;
+                __syncthreads();
+                break;
+            }
+            case 8: break;   // NOP
+            default: {
+                const bool remoteDst = p.op == 2 || p.op == 3, remoteSrc = p.op == 4 || p.op == 5;
+                const bool reduce = p.op == 1 || p.op == 3 || p.op == 5;
+                const int srcRank = remoteSrc ? p.peer : me, dstRank = remoteDst ? p.peer : me;
+                for (uint32_t s = 0; s < p.nSlices; ++s) {
+                    const uint64_t n = Count(p.lenBuf, p.lenSlice + s);
+                    if (n == 0) continue;
+                    const char *src = Addr(p.srcBuf, p.srcSlice + s, srcRank);
+                    char *dst = Addr(p.dstBuf, p.dstSlice + s, dstRank);
+                    if (reduce || src != dst) IrMove<T>(dst, src, n, reduce, a.op);
+                }
+                // later primitives of this CTA may read what other threads of the CTA just wrote
+                __syncthreads();
+            }
+        }
+    }
+    KernelEnd(d, ls, used);
+}
+
 template <typename K> struct KernelOf { K fn; };
 
 template <template <typename> class Dummy = AccOf>
@@ -771,6 +934,11 @@ void PreloadFastKernels()
             cudaFuncAttributes attr;
             if (fn) cudaFuncGetAttributes(&attr, fn);
         }
+    for (int dt : dtypes) {
+        void *fn = IrKernelFor(dt);
+        cudaFuncAttributes attr;
+        if (fn) cudaFuncGetAttributes(&attr, fn);
+    }
     cudaGetLastError();
 }
 
@@ -825,6 +993,37 @@ HcclResult LaunchFastKernel(const FastLaunch &l)
     else e = cudaLaunchKernel(fn, grid, block, params, 0, (cudaStream_t)l.stream);
     if (e != cudaSuccess) {
         HCCL_ERROR("launch of %s (%d CTAs x %d threads, %d ranks) failed: %s", FastKindName(l.kind), l.ctas, l.threads, grid.y, cudaGetErrorString(e));
+        return HCCL_E_RUNTIME;
+    }
+    return HCCL_SUCCESS;
+}
+
+
+void *IrKernelFor(int dtype)
+{
+    switch (dtype) {
+        case HCCL_DATA_TYPE_FP32: return (void *)KIrInterp<float>; case HCCL_DATA_TYPE_FP16: return (void *)KIrInterp<__half>;
+        case HCCL_DATA_TYPE_BFP16: return (void *)KIrInterp<__nv_bfloat16>; case HCCL_DATA_TYPE_FP64: return (void *)KIrInterp<double>;
+        case HCCL_DATA_TYPE_INT8: return (void *)KIrInterp<int8_t>; case HCCL_DATA_TYPE_INT16: return (void *)KIrInterp<int16_t>;
+        case HCCL_DATA_TYPE_INT32: return (void *)KIrInterp<int32_t>; case HCCL_DATA_TYPE_INT64: return (void *)KIrInterp<long long>;
+        case HCCL_DATA_TYPE_UINT8: return (void *)KIrInterp<uint8_t>; case HCCL_DATA_TYPE_UINT16: return (void *)KIrInterp<uint16_t>;
+        case HCCL_DATA_TYPE_UINT32: return (void *)KIrInterp<uint32_t>; case HCCL_DATA_TYPE_UINT64: return (void *)KIrInterp<unsigned long long>;
+        default: return nullptr;
+    }
+}
+
+HcclResult LaunchIrKernel(const IrArgs &args, int ctas, void *stream, const IrArgs *emuTable, int emuRanks)
+{
+    void *fn = IrKernelFor(args.dtype);
+    if (!fn) return HCCL_E_NOT_SUPPORT;
+    dim3 grid((unsigned)ctas, (unsigned)(emuTable ? emuRanks : 1), 1), block(512, 1, 1);
+    IrArgs a = args;
+    const IrArgs *emu = emuTable;
+    void *params[] = {(void *)&a, (void *)&emu};
+    cudaError_t e = emuTable ? cudaLaunchCooperativeKernel(fn, grid, block, params, 0, (cudaStream_t)stream)
+                             : cudaLaunchKernel(fn, grid, block, params, 0, (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+        HCCL_ERROR("launch of the schedule interpreter (%d CTAs, %d ranks) failed: %s", ctas, grid.y, cudaGetErrorString(e));
         return HCCL_E_RUNTIME;
     }
     return HCCL_SUCCESS;

@@ -71,6 +71,25 @@ struct FastLaunch {
     int emuRanks;
 };
 
+// ---- schedule interpreter (engine "sm-ir"): one kernel runs this rank's program of a Schedule
+struct IrLayoutDev { uint64_t sliceCount, total; };       // uniform slice geometry of INPUT / OUTPUT / SCRATCH
+struct IrArgs {
+    CommDev *dev;
+    const void *prims;       // DevPrim[nPrims] in device memory
+    uint32_t nPrims;
+    int32_t dtype, op;
+    uint32_t elemSize;
+    const void *in;
+    void *out;
+    IrLayoutDev lay[3];
+    uint64_t cap;            // elements per scratch slot in this pass
+    uint64_t col0, col1;     // column window of this pass
+    int32_t preBarrier;
+};
+// Launches the interpreter for one pass; `emuTable` as in FastLaunch.  HCCL_E_NOT_SUPPORT for a data type without a kernel.
+HcclResult LaunchIrKernel(const IrArgs &args, int ctas, void *stream, const IrArgs *emuTable, int emuRanks);
+void *IrKernelFor(int dtype);
+
 // Forces every kernel of this file to be loaded on the current device (call once per device before any launch).
 void PreloadFastKernels();
 // Returns HCCL_E_NOT_SUPPORT for a (kind, dtype) pair without a kernel.

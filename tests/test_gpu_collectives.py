@@ -173,3 +173,46 @@ def test_small_message_flag_in_data_kernel(n):
             assert all(c.async_error() == 0 for c in comms)
     finally:
         _destroy(comms)
+
+
+@pytest.mark.parametrize("n,algo", [(2, "level0:ring"), (4, "level0:ring"), (4, "level0:H-D_R"), (3, "level0:H-D_R"), (4, "level0:pairwise"), (8, "level0:NB"),
+                                    (8, "level0:ring")])
+def test_forced_algorithms_run_in_the_schedule_interpreter(n, algo):
+    """Ring, halving-doubling (with a non-power-of-two fold), pairwise and Bruck schedules, executed by the interpreter
+    kernel; a 1 MB buffer forces several column passes for the larger vectors."""
+    comms = _make(n, buffer_mb=1, algo=algo)
+    try:
+        for count in (1000, 70_001, 1_200_007):
+            g = torch.Generator(device="cuda").manual_seed(count)
+            xs = [torch.randn(count, device="cuda", generator=g) for _ in range(n)]
+            outs = [torch.empty_like(x) for x in xs]
+            per = max(1, count // n)
+            ag_in = [torch.randint(0, 1 << 20, (per,), device="cuda", generator=g, dtype=torch.int32) for _ in range(n)]
+            ag_out = [torch.empty(per * n, device="cuda", dtype=torch.int32) for _ in range(n)]
+            rs_in = [torch.randn(per * n, device="cuda", generator=g).to(torch.bfloat16) for _ in range(n)]
+            rs_out = [torch.empty(per, device="cuda", dtype=torch.bfloat16) for _ in range(n)]
+            a2a_in = [torch.arange(per * n, device="cuda", dtype=torch.int32) + 10_000_000 * r for r in range(n)]
+            a2a_out = [torch.empty(per * n, device="cuda", dtype=torch.int32) for _ in range(n)]
+            bc = [torch.full((count,), float(r), device="cuda") for r in range(n)]
+
+            def op(r):
+                torch.cuda.set_device(0)
+                c = comms[r]
+                c.all_reduce(xs[r], outs[r])
+                c.all_gather(ag_in[r], ag_out[r])
+                c.reduce_scatter(rs_in[r], rs_out[r])
+                c.all_to_all(a2a_in[r], a2a_out[r])
+                c.broadcast(bc[r], root=1)
+                torch.cuda.synchronize()
+            run_ranks(n, op)
+            ref = sum(x.double() for x in xs)
+            total = sum(x.double() for x in rs_in)
+            for r in range(n):
+                assert (outs[r].double() - ref).abs().max().item() <= 1e-4 * max(1.0, ref.abs().max().item()), (algo, count, "all_reduce")
+                assert torch.equal(ag_out[r], torch.cat(ag_in)), (algo, count, "all_gather")
+                assert (rs_out[r].double() - total[r * per:(r + 1) * per]).abs().max().item() <= 0.1 * (n ** 0.5), (algo, count, "reduce_scatter")
+                assert torch.equal(a2a_out[r], torch.cat([a2a_in[q][r * per:(r + 1) * per] for q in range(n)])), (algo, count, "all_to_all")
+                assert (bc[r] == 1).all(), (algo, count, "broadcast")
+            assert all(c.async_error() == 0 for c in comms)
+    finally:
+        _destroy(comms)
