@@ -631,6 +631,18 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
 
     HcclResult r = HCCL_SUCCESS;
     bool irServed = false;
+    // The specialised kernels split a vector among CTAs by 16-byte vectors when the buffers allow it and by elements
+    // otherwise; with a user buffer that is not 16-byte aligned two phases of one kernel may pick different splits, and
+    // then a CTA would read what another CTA index of the peer wrote - which the per-CTA barriers do not order.  The
+    // interpreter assigns elements to CTAs by their index inside the slice, whatever the alignment: such calls go there.
+    if (cuda && (sel.engine == Engine::SM_FAST || sel.engine == Engine::NVLS) && ((((uintptr_t)d.in) | ((uintptr_t)d.out)) & 15) != 0 &&
+        d.sendCounts.empty() && d.recvCounts.empty() && !d.useScale && c->nRanks > 1 &&
+        (d.cmd == HCCL_CMD_ALLREDUCE || d.cmd == HCCL_CMD_ALLGATHER || d.cmd == HCCL_CMD_REDUCE_SCATTER || d.cmd == HCCL_CMD_ALLTOALL ||
+         d.cmd == HCCL_CMD_BROADCAST || d.cmd == HCCL_CMD_REDUCE)) {
+        sel.engine = Engine::SM_IR;
+        if (sel.algo != Algo::MESH_ONESHOT) sel.algo = Algo::MESH;
+        sel.reason = "buffers not 16-byte aligned";
+    }
     if (sel.engine == Engine::SM_IR) {
         r = IrCollective(c, d, sel, &irServed);
         if (r != HCCL_SUCCESS) { Record(c, d, sel, t0); return r; }

@@ -216,3 +216,38 @@ def test_forced_algorithms_run_in_the_schedule_interpreter(n, algo):
             assert all(c.async_error() == 0 for c in comms)
     finally:
         _destroy(comms)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_buffers_that_are_not_16_byte_aligned(n):
+    """Views that start one element into an allocation: the operators must not depend on vector alignment."""
+    comms = _make(n)
+    try:
+        for dtype, count in ((torch.bfloat16, 300_001), (torch.float32, 70_003)):
+            g = torch.Generator(device="cuda").manual_seed(count)
+            base_in = [torch.randn(count * n + 8, device="cuda", generator=g).to(dtype) for _ in range(n)]
+            base_out = [torch.zeros(count * n + 8, device="cuda", dtype=dtype) for _ in range(n)]
+            xs = [b[1:1 + count] for b in base_in]
+            outs = [b[3:3 + count] for b in base_out]
+            ag_out = [torch.zeros(count * n + 8, device="cuda", dtype=dtype) for _ in range(n)]
+            rs_in = [b[1:1 + count * n] for b in base_in]
+            rs_out = [torch.zeros(count + 8, device="cuda", dtype=dtype) for _ in range(n)]
+
+            def op(r):
+                torch.cuda.set_device(0)
+                comms[r].all_reduce(xs[r], outs[r])
+                comms[r].all_gather(xs[r], ag_out[r][1:1 + count * n])
+                comms[r].reduce_scatter(rs_in[r], rs_out[r][1:1 + count])
+                torch.cuda.synchronize()
+            run_ranks(n, op)
+            ref = sum(x.double() for x in xs)
+            total = sum(x.double() for x in rs_in)
+            tol = (1e-5 if dtype == torch.float32 else 4e-2) * (n ** 0.5) * 4
+            for r in range(n):
+                assert (outs[r].double() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+                assert torch.equal(ag_out[r][1:1 + count * n], torch.cat(xs))
+                assert (rs_out[r][1:1 + count].double() - total[r * count:(r + 1) * count]).abs().max().item() <= tol * max(1.0, total.abs().max().item())
+                assert base_out[r][0] == 0 and base_out[r][3 + count] == 0 and ag_out[r][0] == 0      # nothing outside the views was touched
+            assert all(c.async_error() == 0 for c in comms)
+    finally:
+        _destroy(comms)
