@@ -29,6 +29,8 @@ TOKENS, HIDDEN, INTER = 8192, 8192, 28672
 
 
 def reference_arm():
+    if int(os.environ.get("RANK", "0")) != 0:      # launched once per GPU: one line for the whole job
+        return 0
     print(json.dumps({"impl": "reference", "unavailable": "the reference is an Ascend CANN C++/AscendC project without setup.py or pyproject.toml: "
                       "pip cannot install it and it cannot build for CUDA"}))
     return 0
