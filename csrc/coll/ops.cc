@@ -129,19 +129,21 @@ bool TrySmallLL(Comm *c, const OpDesc &d, const Selection &sel, HcclResult *res)
     }
     const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
     const uint64_t blockBytes = d.count * esz;
-    if (blockBytes == 0 || blockBytes % 16 != 0 || blockBytes > (uint64_t)limit || blockBytes > HC_LL_MAX_PAYLOAD) return false;
+    if (blockBytes == 0 || blockBytes > (uint64_t)limit || blockBytes > HC_LL_MAX_PAYLOAD) return false;
     if ((uint64_t)(n - 1) * blockBytes > (uint64_t)EnvConfig::Get().llMaxRecvBytes.value) return false;      // what one rank receives: beyond this the two-phase kernels win
     const bool reducing = mode == LL_ALLREDUCE || mode == LL_REDUCE_SCATTER;
     if (reducing && !DtypeReducible(d.dtype)) return false;
     const uint64_t inBytes = (mode == LL_ALLTOALL || mode == LL_REDUCE_SCATTER) ? blockBytes * n : blockBytes;
     const uint64_t outBytes = (mode == LL_ALLGATHER || mode == LL_ALLTOALL) ? blockBytes * n : blockBytes;
     const uintptr_t in = (uintptr_t)d.in, out = (uintptr_t)d.out;
-    if ((in | out) & 15) return false;
+    // whole aligned vectors, or a tiny block of any shape that the kernel moves byte by byte
+    const bool bytewise = blockBytes % 16 != 0 || ((in | out) & 15) != 0;
+    if (bytewise && blockBytes > 256) return false;
     const bool overlap = in < out + outBytes && out < in + inBytes;
     if (overlap && !(mode == LL_ALLREDUCE && in == out)) return false;     // in-place all-reduce reads and writes the same vector per thread
     CollArgs a;
     FillBase(c, d, a);
-    a.in = d.in; a.out = d.out; a.count = d.count; a.peer = mode;
+    a.in = d.in; a.out = d.out; a.count = d.count; a.peer = mode; a.root = bytewise ? 1 : 0;
     OpDesc typed = d;
     if (!reducing) typed.dtype = HCCL_DATA_TYPE_FP32;                        // byte movers share the fp32 instantiation
     a.dtype = typed.dtype;
@@ -636,7 +638,7 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
     // then a CTA would read what another CTA index of the peer wrote - which the per-CTA barriers do not order.  The
     // interpreter assigns elements to CTAs by their index inside the slice, whatever the alignment: such calls go there.
     if (cuda && (sel.engine == Engine::SM_FAST || sel.engine == Engine::NVLS) && ((((uintptr_t)d.in) | ((uintptr_t)d.out)) & 15) != 0 &&
-        d.sendCounts.empty() && d.recvCounts.empty() && !d.useScale && c->nRanks > 1 &&
+        d.sendCounts.empty() && d.recvCounts.empty() && !d.useScale && c->nRanks > 1 && d.count * DtypeSize(d.dtype) > 256 &&
         (d.cmd == HCCL_CMD_ALLREDUCE || d.cmd == HCCL_CMD_ALLGATHER || d.cmd == HCCL_CMD_REDUCE_SCATTER || d.cmd == HCCL_CMD_ALLTOALL ||
          d.cmd == HCCL_CMD_BROADCAST || d.cmd == HCCL_CMD_REDUCE)) {
         sel.engine = Engine::SM_IR;

@@ -617,7 +617,8 @@ __global__ void __launch_bounds__(512) KRecv(const __grid_constant__ CollArgs by
 //   LL_ALLGATHER       block = my contribution, out[r*count ..] = block of rank r
 //   LL_ALLTOALL        in[q*count ..] goes to rank q, out[r*count ..] comes from rank r
 //   LL_REDUCE_SCATTER  in[q*count ..] goes to rank q, out = sum in rank order of the blocks addressed to me
-// Blocks are whole 16-byte vectors (the host checks) of at most HC_LL_MAX_PAYLOAD bytes.
+// Blocks are whole aligned 16-byte vectors of at most HC_LL_MAX_PAYLOAD bytes, or (a.root != 0) tiny blocks of any length
+// and alignment that are moved byte by byte.
 __device__ __forceinline__ char *LlSlot(const CommDev *d, int owner, uint32_t parity, int src)
 {
     return HcPeerHeap(d, owner) + d->llOffset + ((uint64_t)parity * HC_KERNEL_MAX_RANKS + (uint64_t)src) * HC_LL_SLOT_BYTES;
@@ -645,6 +646,28 @@ __device__ __forceinline__ bool LlLoad(const CommDev *d, const char *slot, uint6
     }
 }
 
+// 16 bytes of a block that may end inside the vector or start at any address: assembled from single bytes, missing
+// bytes read as zero (tiny messages only; whole aligned vectors use Ld16 / St16).
+__device__ __forceinline__ uint4 LlLoadBytes(const char *base, uint64_t vec, uint64_t blockBytes)
+{
+    union { uint4 v; unsigned char b[16]; } u;
+    u.v = make_uint4(0, 0, 0, 0);
+    const uint64_t off = vec << 4;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        if (off + j < blockBytes) u.b[j] = *(volatile const unsigned char *)(base + off + j);
+    return u.v;
+}
+__device__ __forceinline__ void LlStoreBytes(char *base, uint64_t vec, uint64_t blockBytes, uint4 val)
+{
+    union { uint4 v; unsigned char b[16]; } u;
+    u.v = val;
+    const uint64_t off = vec << 4;
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        if (off + j < blockBytes) base[off + j] = (char)u.b[j];
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
@@ -654,7 +677,9 @@ __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs
     const int n = d->nRanks, me = d->rank, mode = a.peer;
     const bool reducing = mode == LL_ALLREDUCE || mode == LL_REDUCE_SCATTER;
     const uint64_t blockBytes = a.count * (reducing ? sizeof(T) : (uint64_t)a.elemSize);
-    const uint64_t nvec = blockBytes >> 4;
+    const uint64_t nvec = (blockBytes + 15) >> 4;
+    // a.root != 0: the block is not made of whole aligned 16-byte vectors (the host sets it for tiny messages)
+    const bool bytewise = a.root != 0;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, first = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const bool perPeerInput = mode == LL_ALLTOALL || mode == LL_REDUCE_SCATTER;
     // send
@@ -662,7 +687,7 @@ __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs
         const int q = (me + i) % n;
         const char *src = (const char *)a.in + (perPeerInput ? (uint64_t)q * blockBytes : 0);
         char *slot = LlSlot(d, q, ls.half, me);
-        for (uint64_t v = first; v < nvec; v += stride) LlStore(slot, v, Ld16(src + (v << 4)), tag);
+        for (uint64_t v = first; v < nvec; v += stride) LlStore(slot, v, bytewise ? LlLoadBytes(src, v, blockBytes) : Ld16(src + (v << 4)), tag);
     }
     // receive
     const char *own = (const char *)a.in + (perPeerInput ? (uint64_t)me * blockBytes : 0);
@@ -674,7 +699,7 @@ __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs
             bool ok = true;
             for (int r = 0; r < n && ok; ++r) {
                 Pack<T> p;
-                if (r == me) p.v = Ld16(own + (v << 4));
+                if (r == me) p.v = bytewise ? LlLoadBytes(own, v, blockBytes) : Ld16(own + (v << 4));
                 else ok = LlLoad(d, LlSlot(d, me, ls.half, r), v, tag, r, &p.v);
                 if (r == 0) {
 #pragma unroll
@@ -688,10 +713,14 @@ __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs
             Pack<T> o;
 #pragma unroll
             for (int j = 0; j < N; ++j) o.e[j] = Narrow<T>(a.useScale ? ScaleAcc<A>(acc[j], a.scale) : acc[j]);
-            St16((char *)a.out + (v << 4), o.v);
+            if (bytewise) LlStoreBytes((char *)a.out, v, blockBytes, o.v);
+            else St16((char *)a.out + (v << 4), o.v);
         }
     } else {
-        for (uint64_t v = first; v < nvec; v += stride) St16((char *)a.out + (uint64_t)me * blockBytes + (v << 4), Ld16(own + (v << 4)));
+        for (uint64_t v = first; v < nvec; v += stride) {
+            if (bytewise) LlStoreBytes((char *)a.out + (uint64_t)me * blockBytes, v, blockBytes, LlLoadBytes(own, v, blockBytes));
+            else St16((char *)a.out + (uint64_t)me * blockBytes + (v << 4), Ld16(own + (v << 4)));
+        }
         for (int i = 1; i < n; ++i) {
             const int r = (me + n - i) % n;
             const char *slot = LlSlot(d, me, ls.half, r);
@@ -699,7 +728,10 @@ __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs
             for (uint64_t v = first; v < nvec && ok; v += stride) {
                 uint4 val;
                 ok = LlLoad(d, slot, v, tag, r, &val);
-                if (ok) St16((char *)a.out + (uint64_t)r * blockBytes + (v << 4), val);
+                if (ok) {
+                    if (bytewise) LlStoreBytes((char *)a.out + (uint64_t)r * blockBytes, v, blockBytes, val);
+                    else St16((char *)a.out + (uint64_t)r * blockBytes + (v << 4), val);
+                }
             }
             if (!ok) break;
         }
