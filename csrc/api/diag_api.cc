@@ -1,6 +1,8 @@
 // diag_api.cc - diagnostics (include/hccl/hccl_diag.h): operator record ring, exec counters, the
 // device wait-status block, heartbeat view, snapshots of a communicator and process-snapshot hooks.
+#include <cstddef>
 #include <cstring>
+#include <algorithm>
 #include <sstream>
 
 #include "../alg/selector.h"
@@ -35,6 +37,26 @@ HcclResult HcclDiagGetOpCounters(HcclComm comm, uint64_t *launched, uint64_t *he
     if (c->opCounters) CHK_RET(c->plat->PeekSync(ht, c->opCounters, sizeof(ht)));
     if (headCount) *headCount = ht[0];
     if (tailCount) *tailCount = ht[1];
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclDiagGetKernelTimes(HcclComm comm, uint64_t *startNs, uint64_t *endNs, uint32_t capacity, uint32_t *written)
+{
+    Comm *c = AsComm(comm);
+    CHK_PTR_NULL(c); CHK_PTR_NULL(written);
+    *written = 0;
+    if (!c->devStruct || c->plat->kind() != PlatKind::CUDA) return HCCL_SUCCESS;     // the simulator runs no kernels
+    uint64_t ht[2] = {0, 0}, ring[2 * HC_DEV_TIME_SLOTS];
+    CHK_RET(c->plat->PeekSync(ht, c->opCounters, sizeof(ht)));
+    CHK_RET(c->plat->PeekSync(ring, (char *)c->devStruct + HC_DEV_TIMES_OFFSET, sizeof(ring)));
+    // slots are written only while profiling is on: entries without a start time are skipped
+    const uint64_t have = std::min<uint64_t>(ht[0], HC_DEV_TIME_SLOTS);
+    for (uint64_t k = ht[0] - have; k < ht[0] && *written < capacity; ++k) {
+        if (ring[2 * (k % HC_DEV_TIME_SLOTS)] == 0) continue;
+        if (startNs) startNs[*written] = ring[2 * (k % HC_DEV_TIME_SLOTS)];
+        if (endNs) endNs[*written] = ring[2 * (k % HC_DEV_TIME_SLOTS) + 1];
+        ++*written;
+    }
     return HCCL_SUCCESS;
 }
 
@@ -75,6 +97,10 @@ HcclResult HcclDiagSetProfiling(HcclComm comm, int enable)
     Comm *c = AsComm(comm);
     CHK_PTR_NULL(c);
     c->profiling = enable != 0;
+    if (c->devStruct && c->plat->kind() == PlatKind::CUDA) {      // kernels start to time-stamp themselves
+        c->hostDev.profile = enable != 0 ? 1u : 0u;
+        CHK_RET(c->plat->MemcpySync((char *)c->devStruct + offsetof(CommDev, profile), &c->hostDev.profile, sizeof(uint32_t)));
+    }
     return HCCL_SUCCESS;
 }
 

@@ -633,10 +633,9 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
 
     HcclResult r = HCCL_SUCCESS;
     bool irServed = false;
-    // The specialised kernels split a vector among CTAs by 16-byte vectors when the buffers allow it and by elements
-    // otherwise; with a user buffer that is not 16-byte aligned two phases of one kernel may pick different splits, and
-    // then a CTA would read what another CTA index of the peer wrote - which the per-CTA barriers do not order.  The
-    // interpreter assigns elements to CTAs by their index inside the slice, whatever the alignment: such calls go there.
+    // The specialised kernels are written for 16-byte vector (and multimem) accesses to the user buffers and fall back to
+    // element accesses otherwise.  The interpreter assigns elements to CTAs by their index inside the slice and picks the
+    // access width block by block, so calls whose buffers do not start on a 16-byte boundary go there.
     if (cuda && (sel.engine == Engine::SM_FAST || sel.engine == Engine::NVLS) && ((((uintptr_t)d.in) | ((uintptr_t)d.out)) & 15) != 0 &&
         d.sendCounts.empty() && d.recvCounts.empty() && !d.useScale && c->nRanks > 1 && d.count * DtypeSize(d.dtype) > 256 &&
         (d.cmd == HCCL_CMD_ALLREDUCE || d.cmd == HCCL_CMD_ALLGATHER || d.cmd == HCCL_CMD_REDUCE_SCATTER || d.cmd == HCCL_CMD_ALLTOALL ||

@@ -273,7 +273,6 @@ static HcclResult SetupDeviceState(Comm *c)
     d.epoch = c->devCounters;
     d.launches = c->devCounters + 1;
     d.blocksDone = c->devCounters + 2;
-    d.irSent = c->devIrCounters;
     d.irConsumed = c->devIrCounters + (size_t)HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY;
     d.abortWord = c->abortWord;
     d.status = c->waitStatus;

@@ -47,23 +47,28 @@ template <typename T> struct Chunk<T, true> {
     __device__ __forceinline__ void Load(const char *p) { v = Ld16Volatile(p); }
     __device__ __forceinline__ void Store(char *p) const { St16(p, v); }
 };
+// Buffers that are not 16-byte aligned: the same 16-byte chunks (by offset from the start of the range), moved element
+// by element through the bit pattern.  Both forms give chunk i to the same thread, so two phases of a kernel agree on
+// which CTA owns which bytes even when only one of them can use vector accesses - the per-CTA barriers rely on that.
+template <int BYTES> struct BitsOf;
+template <> struct BitsOf<1> { using type = unsigned char; };
+template <> struct BitsOf<2> { using type = unsigned short; };
+template <> struct BitsOf<4> { using type = unsigned int; };
+template <> struct BitsOf<8> { using type = unsigned long long; };
 template <typename T> struct Chunk<T, false> {
-    static constexpr int N = 1;
-    T e[1];
-    __device__ __forceinline__ void Load(const char *p) { e[0] = *(volatile const T *)p; }
-    __device__ __forceinline__ void Store(char *p) const { *(T *)p = e[0]; }
-};
-template <> struct Chunk<__half, false> {
-    static constexpr int N = 1;
-    __half e[1];
-    __device__ __forceinline__ void Load(const char *p) { unsigned short u = *(volatile const unsigned short *)p; e[0] = __ushort_as_half(u); }
-    __device__ __forceinline__ void Store(char *p) const { *(__half *)p = e[0]; }
-};
-template <> struct Chunk<__nv_bfloat16, false> {
-    static constexpr int N = 1;
-    __nv_bfloat16 e[1];
-    __device__ __forceinline__ void Load(const char *p) { unsigned short u = *(volatile const unsigned short *)p; e[0] = __ushort_as_bfloat16(u); }
-    __device__ __forceinline__ void Store(char *p) const { *(__nv_bfloat16 *)p = e[0]; }
+    static constexpr int N = 16 / sizeof(T);
+    using B = typename BitsOf<sizeof(T)>::type;
+    union { uint4 v; T e[N]; B b[N]; };
+    __device__ __forceinline__ void Load(const char *p)
+    {
+#pragma unroll
+        for (int j = 0; j < N; ++j) b[j] = ((volatile const B *)p)[j];
+    }
+    __device__ __forceinline__ void Store(char *p) const
+    {
+#pragma unroll
+        for (int j = 0; j < N; ++j) ((B *)p)[j] = b[j];
+    }
 };
 
 // dst[k][i] = scale * (src[0][i] op src[1][i] op ... op src[n-1][i]) for every destination k (local or remote) and
@@ -114,7 +119,7 @@ __device__ __forceinline__ void ReduceLoop(const char *const *src, int n, char *
             }
         }
     }
-    if (VEC && blockIdx.x == 0) {   // ragged end of a vectorised range
+    if (blockIdx.x == 0) {   // ragged end: fewer elements than one chunk
         for (uint64_t e = nChunks * N + threadIdx.x; e < nElems; e += blockDim.x) {
             const uint64_t off = e * sizeof(T);
             A acc = Widen<T>(*(volatile const T *)(src[0] + off));

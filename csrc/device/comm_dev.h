@@ -50,8 +50,9 @@ struct CommDev {
     uint32_t *epoch;         /* device-local: last barrier epoch consumed */
     uint32_t *launches;      /* device-local: operators launched (parity picks the CCL half) */
     uint32_t *blocksDone;    /* device-local scratch counter */
-    uint64_t *irSent;        /* device-local [HC_IR_MAX_CTAS][HC_MAX_RANKS][HC_IR_NOTIFY] */
-    uint64_t *irConsumed;    /* device-local, same shape */
+    uint32_t profile;        /* non-zero: kernels record start / end timestamps in the ring at HC_DEV_TIMES_OFFSET */
+    uint32_t reservedDev;
+    uint64_t *irConsumed;    /* device-local [HC_IR_MAX_CTAS][HC_MAX_RANKS][HC_IR_NOTIFY]: posts consumed by the interpreter's waits */
     uint32_t *abortWord;     /* host-pinned: non-zero makes every wait return immediately */
     HcclDeviceWaitStatus *status; /* host-pinned record of the first wait that expired */
     uint64_t *opCounters;    /* device-local {head, tail}: bumped at kernel start / end (the host peeks at them to tell which operator hangs) */
@@ -68,6 +69,9 @@ struct CommDev {
 
 #define HC_DEV_COUNTERS_OFFSET 128
 #define HC_DEV_OPCOUNTERS_OFFSET 640
+/* [704, 960): ring of HC_DEV_TIME_SLOTS {start ns, end ns} pairs (GPU global timer) of the most recent kernels; slot = head count % slots */
+#define HC_DEV_TIMES_OFFSET 704
+#define HC_DEV_TIME_SLOTS 16
 #define HC_DEV_BLOCK_BYTES 1024
 
 #ifdef __CUDACC__

@@ -145,7 +145,18 @@ __device__ __forceinline__ LaunchState KernelBegin(const CommDev *d)
     const uint32_t *ctr = DevCounters(d);
     s.epoch0 = *(volatile const uint32_t *)&ctr[0];
     s.half = *(volatile const uint32_t *)&ctr[1] & 1u;
-    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&DevOpCounters(d)[0], 1ull);
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+        if (d->profile) {
+            // device-side timestamps of the last kernels, read by the host (HcclDiagGetKernelTimes); only when profiling
+            // is on, because the returning atomic sits on the first CTA's critical path
+            const unsigned long long seq = atomicAdd(&DevOpCounters(d)[0], 1ull);
+            unsigned long long *slot = (unsigned long long *)((char *)d + HC_DEV_TIMES_OFFSET) + 2 * (seq % HC_DEV_TIME_SLOTS);
+            slot[0] = GlobalTimerNs();
+            slot[1] = 0;
+        } else {
+            atomicAdd(&DevOpCounters(d)[0], 1ull);
+        }
+    }
     return s;
 }
 __device__ __forceinline__ void KernelEnd(const CommDev *d, const LaunchState &s, uint32_t barriersUsed, uint32_t halvesUsed = 1)
@@ -159,7 +170,12 @@ __device__ __forceinline__ void KernelEnd(const CommDev *d, const LaunchState &s
             *(volatile uint32_t *)&ctr[0] = s.epoch0 + barriersUsed;
             *(volatile uint32_t *)&ctr[1] = *(volatile uint32_t *)&ctr[1] + halvesUsed;
             *(volatile uint32_t *)&ctr[2] = 0u;
-            atomicAdd(&DevOpCounters(d)[1], 1ull);
+            if (d->profile) {
+                const unsigned long long seq = atomicAdd(&DevOpCounters(d)[1], 1ull);
+                ((unsigned long long *)((char *)d + HC_DEV_TIMES_OFFSET))[2 * (seq % HC_DEV_TIME_SLOTS) + 1] = GlobalTimerNs();
+            } else {
+                atomicAdd(&DevOpCounters(d)[1], 1ull);
+            }
         }
     }
 }
@@ -230,18 +246,55 @@ __device__ __forceinline__ void GridCopy16(char *dst, const char *src, uint64_t 
         for (uint64_t b = tail0 + threadIdx.x; b < n; b += blockDim.x) dst[b] = *(volatile const char *)(src + b);
     }
 }
-// Same partition, any alignment: moves elements of `esz` bytes (1, 2, 4 or 8).
+// The same partition for any alignment: thread i moves the 16 bytes at offset 16 i as elements of `esz` bytes (1, 2, 4
+// or 8), and CTA 0 the (n % 16) tail.  Two phases of one kernel therefore agree on which CTA owns which bytes even
+// when only one of them may use vector accesses (say staging -> user buffer at an odd displacement); the per-CTA
+// barriers between phases order nothing else.
 __device__ __forceinline__ void GridCopyElems(char *dst, const char *src, uint64_t n, uint32_t esz)
 {
-    const uint64_t cnt = n / esz;
+    const uint64_t nvec = n >> 4;
     const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < cnt; i += stride) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += stride) {
+        char *pd = dst + (i << 4);
+        const char *ps = src + (i << 4);
         switch (esz) {
-            case 8: ((uint64_t *)dst)[i] = ((volatile const uint64_t *)src)[i]; break;
-            case 4: ((uint32_t *)dst)[i] = ((volatile const uint32_t *)src)[i]; break;
-            case 2: ((uint16_t *)dst)[i] = ((volatile const uint16_t *)src)[i]; break;
-            default: dst[i] = ((volatile const char *)src)[i]; break;
+            case 8: {
+                uint64_t v[2];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) v[j] = ((volatile const uint64_t *)ps)[j];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) ((uint64_t *)pd)[j] = v[j];
+                break;
+            }
+            case 4: {
+                uint32_t v[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[j] = ((volatile const uint32_t *)ps)[j];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ((uint32_t *)pd)[j] = v[j];
+                break;
+            }
+            case 2: {
+                uint16_t v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = ((volatile const uint16_t *)ps)[j];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ((uint16_t *)pd)[j] = v[j];
+                break;
+            }
+            default: {
+                char v[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] = ((volatile const char *)ps)[j];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) pd[j] = v[j];
+                break;
+            }
         }
+    }
+    if (blockIdx.x == 0) {
+        const uint64_t tail0 = nvec << 4;
+        for (uint64_t b = tail0 + threadIdx.x; b < n; b += blockDim.x) dst[b] = *(volatile const char *)(src + b);
     }
 }
 // Picks the widest legal path.

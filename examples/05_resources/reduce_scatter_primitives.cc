@@ -99,7 +99,14 @@ int main(int argc, char **argv)
         if (n >= 2) {
             // everybody parks block `rank` of its input in its own staging slot n-1 ... reuse slot `rank`
             std::memcpy(staging + rank * block, in.data() + rank * block, block * sizeof(float));
-            EX_CHECK(HcclBarrier(comm, nullptr));
+            // The staging lives in the communication buffer, which the library's own operators (HcclBarrier among them)
+            // use as well: while it holds data, the ranks synchronise through the channels' notifies instead.
+            auto syncPeers = [&]() {
+                for (uint32_t i = 0; i < n - 1; ++i) EX_CHECK(HcommChannelNotifyRecordOnThread(thread, ch[i], 1));
+                for (uint32_t i = 0; i < n - 1; ++i) EX_CHECK(HcommChannelNotifyWaitOnThread(thread, ch[i], 1, 1800));
+                EX_CHECK(HcommThreadSynchronize(thread));
+            };
+            syncPeers();
             std::vector<float> acc(block, 0.0f);
             HcommBatchTransferDesc bt[2];
             std::memset(bt, 0, sizeof(bt));
@@ -118,7 +125,7 @@ int main(int argc, char **argv)
             EX_CHECK(HcommThreadSynchronize(thread));
             const uint32_t q = peers[0];
             for (uint64_t i = 0; i < block; ++i) EX_EXPECT(acc[i] == 2.0f * ((float)(q + 1) * 3.0f + (float)((q * block + i) % 5)));
-            EX_CHECK(HcclBarrier(comm, nullptr));
+            syncPeers();
         }
 
         // ---- batch mode + task cache: record a local copy chain once, replay it on other buffers

@@ -42,6 +42,9 @@ typedef struct {
 
 HcclResult HcclDiagGetOpRecords(HcclComm comm, HcclOpRecord *records, uint32_t capacity, uint32_t *written);
 HcclResult HcclDiagGetOpCounters(HcclComm comm, uint64_t *launched, uint64_t *headCount, uint64_t *tailCount);
+/* Device-side durations of the most recent kernels of the communicator (GPU global timer, nanoseconds), oldest first;
+ * at most 16 are kept, recorded while profiling is on (HcclDiagSetProfiling).  A kernel that is still running reports end = 0. */
+HcclResult HcclDiagGetKernelTimes(HcclComm comm, uint64_t *startNs, uint64_t *endNs, uint32_t capacity, uint32_t *written);
 HcclResult HcclDiagGetWaitStatus(HcclComm comm, HcclDeviceWaitStatus *status);
 HcclResult HcclDiagClearWaitStatus(HcclComm comm);
 /* rank -> milliseconds since its last heartbeat (UINT64_MAX: never seen); lostMask bit r = LOST. */

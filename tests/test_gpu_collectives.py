@@ -251,3 +251,66 @@ def test_buffers_that_are_not_16_byte_aligned(n):
             assert all(c.async_error() == 0 for c in comms)
     finally:
         _destroy(comms)
+
+
+@pytest.mark.parametrize("n", [2, 4])
+def test_blocks_at_displacements_that_are_not_16_byte_aligned(n):
+    """Aligned buffers whose per-rank blocks have an odd length: one phase of the specialised kernels can use vector
+    accesses and the other cannot, and both must still give the same bytes to the same CTA.  Repeated, with a small
+    staging buffer (several windows) and with the default one, because a wrong split shows as a race."""
+    for buffer_mb in (1, 64):
+        comms = _make(n, buffer_mb=buffer_mb)
+        try:
+            for dtype, per in ((torch.int32, 600_003), (torch.bfloat16, 300_001), (torch.int32, 70_001)):
+                ag_in = [(torch.arange(per, device="cuda", dtype=torch.int32) + 1_000_000 * r).to(dtype) for r in range(n)]
+                a2a_in = [(torch.arange(per * n, device="cuda", dtype=torch.int32) + 10_000_000 * r).to(dtype) for r in range(n)]
+                rs_in = [((torch.arange(per * n, device="cuda", dtype=torch.int32) + r) % 64).to(dtype) for r in range(n)]
+                for rep in range(4):
+                    ag_out = [torch.zeros(per * n, device="cuda", dtype=dtype) for _ in range(n)]
+                    a2a_out = [torch.zeros(per * n, device="cuda", dtype=dtype) for _ in range(n)]
+                    rs_out = [torch.zeros(per, device="cuda", dtype=dtype) for _ in range(n)]
+
+                    def op(r):
+                        torch.cuda.set_device(0)
+                        comms[r].all_gather(ag_in[r], ag_out[r])
+                        comms[r].all_to_all(a2a_in[r], a2a_out[r])
+                        comms[r].reduce_scatter(rs_in[r], rs_out[r])
+                        torch.cuda.synchronize()
+                    run_ranks(n, op)
+                    total = sum(x.double() for x in rs_in)     # sums of small integers: exact in bf16 too
+                    for r in range(n):
+                        assert torch.equal(ag_out[r], torch.cat(ag_in)), (buffer_mb, dtype, per, rep, "all_gather")
+                        assert torch.equal(a2a_out[r], torch.cat([a2a_in[q][r * per:(r + 1) * per] for q in range(n)])), (buffer_mb, dtype, per, rep, "all_to_all")
+                        assert torch.equal(rs_out[r].double(), total[r * per:(r + 1) * per]), (buffer_mb, dtype, per, rep, "reduce_scatter")
+            assert all(c.async_error() == 0 for c in comms)
+        finally:
+            _destroy(comms)
+
+
+def test_kernel_time_ring_reports_device_durations(n=2):
+    import ctypes
+    from hcomm_b200 import _lib
+    lib = _lib.load()
+    comms = _make(n)
+    try:
+        xs = [torch.randn(1 << 20, device="cuda") for _ in range(n)]
+        outs = [torch.empty_like(x) for x in xs]
+
+        def op(r):
+            torch.cuda.set_device(0)
+            comms[r].all_reduce(xs[r], outs[r])                      # before profiling is switched on: not recorded
+            torch.cuda.synchronize()
+            assert lib.HcclDiagSetProfiling(ctypes.c_void_p(comms[r].handle), 1) == 0
+            for _ in range(5):
+                comms[r].all_reduce(xs[r], outs[r])
+            torch.cuda.synchronize()
+        run_ranks(n, op)
+        start, end = (ctypes.c_uint64 * 16)(), (ctypes.c_uint64 * 16)()
+        written = ctypes.c_uint32()
+        assert lib.HcclDiagGetKernelTimes(ctypes.c_void_p(comms[0].handle), start, end, 16, ctypes.byref(written)) == 0
+        assert written.value == 5
+        for i in range(written.value):
+            assert start[i] > 0 and end[i] >= start[i] and end[i] - start[i] < 1_000_000_000
+        assert all(start[i] <= start[i + 1] for i in range(written.value - 1))
+    finally:
+        _destroy(comms)
