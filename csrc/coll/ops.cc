@@ -15,6 +15,7 @@
 #include "../core/dtype.h"
 #include "../core/env.h"
 #include "../core/log.h"
+#include "../core/nvtx_range.h"
 #include "../device/coll_kernels.h"
 #include "../device/emu_launch.h"
 #include "exec.h"
@@ -630,6 +631,10 @@ HcclResult RunOp(Comm *c, const OpDesc &d)
         HCCL_DEBUG_CAT(CAT_ALG, "%s: %llu elements of %s -> %s (%s)", CmdName(d.cmd), (unsigned long long)d.count, DtypeName(d.dtype), sel.name.c_str(), sel.reason.c_str());
         lastLogged = sel.name;
     }
+
+    char rangeName[128] = "";
+    if (c->profiling) snprintf(rangeName, sizeof(rangeName), "hccl:%s %llu x %s [%s]", CmdName(d.cmd), (unsigned long long)d.count, DtypeName(d.dtype), sel.name.c_str());
+    NvtxRange nvtxRange(c->profiling, rangeName);    // covers selection's outcome: every launch of this operator sits inside it
 
     HcclResult r = HCCL_SUCCESS;
     bool irServed = false;
