@@ -263,6 +263,26 @@ class Communicator:
     def barrier(self, stream=None):
         check(self._lib.HcclBarrier(self._h, self._stream(stream, None)), "HcclBarrier")
 
+    # ------------------------------------------------------------------ diagnostics
+    def set_profiling(self, enable: bool = True):
+        """Operator records, device timestamps of the kernels and one NVTX range per operator, from now on."""
+        check(self._lib.HcclDiagSetProfiling(self._h, 1 if enable else 0), "HcclDiagSetProfiling")
+
+    def kernel_times(self):
+        """[(start_ns, end_ns)] of the most recent kernels on the GPU's global timer, oldest first (profiling must be on;
+        at most 16 are kept; a kernel that still runs has end 0)."""
+        cap = 16
+        start, end = (ctypes.c_uint64 * cap)(), (ctypes.c_uint64 * cap)()
+        n = ctypes.c_uint32()
+        check(self._lib.HcclDiagGetKernelTimes(self._h, start, end, cap, ctypes.byref(n)), "HcclDiagGetKernelTimes")
+        return [(int(start[i]), int(end[i])) for i in range(n.value)]
+
+    def dump(self) -> str:
+        """The newest operator records and the device wait status, as text."""
+        buf = ctypes.create_string_buffer(16384)
+        check(self._lib.HcclDiagDump(self._h, buf, len(buf)), "HcclDiagDump")
+        return buf.value.decode(errors="replace")
+
     def suspend(self):
         check(self._lib.HcclCommSuspend(self._h), "HcclCommSuspend")
 

@@ -288,9 +288,6 @@ def test_blocks_at_displacements_that_are_not_16_byte_aligned(n):
 
 
 def test_kernel_time_ring_reports_device_durations(n=2):
-    import ctypes
-    from hcomm_b200 import _lib
-    lib = _lib.load()
     comms = _make(n)
     try:
         xs = [torch.randn(1 << 20, device="cuda") for _ in range(n)]
@@ -300,17 +297,16 @@ def test_kernel_time_ring_reports_device_durations(n=2):
             torch.cuda.set_device(0)
             comms[r].all_reduce(xs[r], outs[r])                      # before profiling is switched on: not recorded
             torch.cuda.synchronize()
-            assert lib.HcclDiagSetProfiling(ctypes.c_void_p(comms[r].handle), 1) == 0
+            comms[r].set_profiling(True)
             for _ in range(5):
                 comms[r].all_reduce(xs[r], outs[r])
             torch.cuda.synchronize()
         run_ranks(n, op)
-        start, end = (ctypes.c_uint64 * 16)(), (ctypes.c_uint64 * 16)()
-        written = ctypes.c_uint32()
-        assert lib.HcclDiagGetKernelTimes(ctypes.c_void_p(comms[0].handle), start, end, 16, ctypes.byref(written)) == 0
-        assert written.value == 5
-        for i in range(written.value):
-            assert start[i] > 0 and end[i] >= start[i] and end[i] - start[i] < 1_000_000_000
-        assert all(start[i] <= start[i + 1] for i in range(written.value - 1))
+        times = comms[0].kernel_times()
+        assert len(times) == 5
+        for start, end in times:
+            assert start > 0 and end >= start and end - start < 1_000_000_000
+        assert all(times[i][0] <= times[i + 1][0] for i in range(len(times) - 1))
+        assert "allreduce" in comms[0].dump().lower().replace("_", "")
     finally:
         _destroy(comms)

@@ -9,19 +9,19 @@ ROOT = Path(__file__).resolve().parent.parent
 CUDA_INCLUDE = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
 
 CHILD = """
-import ctypes, sys, torch
+import sys, torch
 sys.path.insert(0, %r)
 import hcomm_b200 as hb
-from hcomm_b200 import _lib
-lib = _lib.load()
 c = hb.Communicator(1, hb.get_root_info(), 0, buffer_mb=2)
 x = torch.arange(1000, dtype=torch.float32)
 y = torch.empty_like(x)
 c.all_reduce(x, y)                                            # profiling off: no range
-assert lib.HcclDiagSetProfiling(ctypes.c_void_p(c.handle), 1) == 0
+c.set_profiling(True)
 c.all_reduce(x, y)
 c.all_gather(x, y)
-assert lib.HcclDiagSetProfiling(ctypes.c_void_p(c.handle), 0) == 0
+c.set_profiling(False)
+assert c.kernel_times() == []                                 # the simulator runs no kernels
+assert "allreduce" in c.dump().lower().replace("_", ""), c.dump()
 c.all_reduce(x, y)
 c.destroy()
 """ % str(ROOT)
