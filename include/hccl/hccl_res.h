@@ -15,7 +15,10 @@ extern "C" {
 
 #define HCCL_RES_TAG_MAX_LEN 255u
 
-/* Local CCL buffer: in-half followed by out-half, each hcclBufferSize MB, peer-visible. */
+/* Local CCL buffer: in-half followed by out-half, each hcclBufferSize MB, peer-visible.
+ * The library's own operators stage their data in the same buffer (the stream engine's HcclBarrier included: it is a
+ * one-element all-reduce), so a custom operator that keeps data there must not run a built-in operator on this
+ * communicator until it has consumed the data; between its own steps it synchronises through channel notifies. */
 HcclResult HcclGetHcclBuffer(HcclComm comm, void **buffer, uint64_t *size);
 HcclResult HcclGetHcclBufferCleared(HcclComm comm, void **buffer, uint64_t *size);
 
