@@ -5,6 +5,7 @@
 #include <unistd.h>
 
 #include <algorithm>
+#include <cerrno>
 #include <cstring>
 
 #include "env.h"
@@ -397,10 +398,15 @@ void Bootstrap::Close()
 void Bootstrap::ReaderLoop()
 {
     while (!closing_.load()) {
+        // Wait for the first byte with a short timeout (to notice closing_), then read the whole message with a long one:
+        // a deadline that expires between the header and the payload would drop the header and leave the stream out of
+        // step - the rest of that message would be taken for the next header, and a reply would never be delivered.
+        struct pollfd pf = {sock_, POLLIN, 0};
+        int pr = poll(&pf, 1, 200);
+        if (pr == 0 || (pr < 0 && errno == EINTR)) continue;
         MsgHdr h;
         Blob pl;
-        HcclResult r = ReadMsg(sock_, &h, &pl, net::NowMs() + 200);
-        if (r == HCCL_E_TIMEOUT) continue;
+        HcclResult r = ReadMsg(sock_, &h, &pl, net::NowMs() + 30000);
         if (r != HCCL_SUCCESS) {
             if (!closing_.load()) {
                 hubGone_.store(true);
