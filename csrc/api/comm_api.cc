@@ -469,7 +469,7 @@ HcclResult HcclCommResume(HcclComm comm)
     }
     c->hostLaunches = 0;
     c->lastOpOnHost = true;
-    std::fill(c->fusedExpect.begin(), c->fusedExpect.end(), 0u);
+    FusedResetLocal(c);
     memset(c->waitStatus, 0, sizeof(HcclDeviceWaitStatus));
     __atomic_store_n(c->abortWord, 0u, __ATOMIC_RELEASE);
     c->asyncError.store(0);

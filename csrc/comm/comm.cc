@@ -398,8 +398,8 @@ Comm::~Comm()
         plat->VaFree(heapBase, heapStride * nRanks);
     }
     if (heapPhys.bytes) plat->PhysRelease(&heapPhys);
-    if (fusedParamRing) plat->DevFree(fusedParamRing);
-    if (fusedExpectRing) plat->DevFree(fusedExpectRing);
+    if (fusedLocal) plat->DevFree(fusedLocal);
+    if (fusedTemp) plat->DevFree(fusedTemp);
     if (irPrimRing) plat->DevFree(irPrimRing);
     if (devStruct) plat->DevFree(devStruct);
     if (devIrCounters) plat->DevFree(devIrCounters);

@@ -131,16 +131,15 @@ struct Comm {
     uint64_t p2pOffset = 0, p2pSlotBytes = 0;    // landing area of the send/recv kernels: one slot per source rank
     uint64_t llOffset = 0, llBytes = 0;          // flag-in-data area of the small-message kernels
     std::vector<uint64_t> p2pSent, p2pRecvd;     // chunks exchanged so far with each peer
-    // Fused GEMM kernels: arrival counters in the control region only grow; the host keeps, per counter, the value that
-    // means "complete" for the next call (all ranks issue the same calls, so the tables agree) and hands the
-    // kernel a device copy of the slice it uses - shapes may change from call to call.
-    std::vector<uint32_t> fusedExpect;           // [8192]
-    void *fusedExpectRing = nullptr;             // device ring: 16 tables of 8192 u32
-    int fusedExpectNext = 0;
-    void *fusedParamRing = nullptr;              // device ring of kernel parameter blocks
+    // Fused GEMM kernels: tile flags in the control region hold launch sequence numbers (kept on the device), so the
+    // host keeps no per-call state for them.
+    void *fusedLocal = nullptr;                  // device-local scratch: push chunk counters, phase clocks
+    bool fusedPhaseClocks = false;               // record per-CTA phase clocks in the CTA-pair fused kernels
+    int fusedLastCtas = 0;                       // CTAs of the most recent CTA-pair fused launch
+    void *fusedTemp = nullptr;                   // GEMM result of the split GEMM + reduce-scatter form
+    size_t fusedTempBytes = 0;
     void *irPrimRing = nullptr;                  // device ring of interpreter programs (8 slots of 2048 primitives)
     int irPrimNext = 0;
-    int fusedParamNext = 0;
     bool lastOpOnHost = true;                    // the next specialised kernel must start with a barrier
     PhysMem mcPhys;
     char *mcBase = nullptr;
@@ -225,6 +224,9 @@ HcclResult RegistryAdd(Comm *c);
 void RegistryRemove(Comm *c);
 Comm *RegistryFind(const std::string &name);
 void RegistryForEach(const std::function<void(Comm *)> &fn);
+
+// Clears the device-local scratch of the fused GEMM kernels (fused_gemm.cu) when a communicator resumes.
+void FusedResetLocal(Comm *c);
 
 // Records an asynchronous failure: stores it, tells the peers, logs the wait status.
 void CommSetAsyncError(Comm *c, HcclResult err);

@@ -3,27 +3,44 @@
 //
 // GEMM -> ReduceScatter  (row-parallel linear:  Y[M,N] = sum_r A_r[M,K_r] * B_r[N,K_r]^T, rank q keeps rows q*M/p ..)
 //   Rank r computes its partial tiles in destination order r+1, r+2, ..., r-1, r.  The epilogue of a
-//   tile owned by another rank converts the fp32 accumulator to bf16 and stores it straight into slot r of
-//   the owner's staging (remote stores), then bumps that tile's arrival counter on the owner.  Tiles of
-//   the rank's own rows come last: their epilogue waits until the p-1 partials have arrived, adds them
-//   to the accumulator still in registers in ascending rank order (fp32) and writes the final bf16 rows.
-//   There is no separate reduction pass and nothing goes through a library collective.
+//   tile owned by another rank converts the fp32 accumulator to bf16, stores it into slot r of the owner's
+//   staging (remote stores, whole 256-byte row segments) and then publishes it: every epilogue warp owns 32 rows
+//   of the tile and writes the operator's sequence number into the flag word of (source rank, tile, row group)
+//   on the owner.  Tiles of the rank's own rows come last: the warp that owns a row group waits for the p-1
+//   flags of that same row group (one lane per source), adds the partials to the accumulator still in registers
+//   in ascending rank order (fp32) and writes the final bf16 rows.  There is no separate reduction pass, no
+//   CTA-wide barrier on the way and nothing goes through a library collective.
 //
 // AllGather -> GEMM  (column-parallel linear:  Y_r[M,N_r] = concat_q(x_q)[M,K] * W_r[N_r,K]^T)
 //   Two extra warps per CTA push this rank's activation shard into every peer's staging (nearest consumer
-//   first, 32 KB chunks, one arrival counter per 128-row block), while the GEMM starts on the local
-//   shard.  The TMA producer of a tile whose rows come from rank q waits for that block's counter, then
-//   loads from the local staging copy - TMA never reads peer memory.  Blocks are consumed in the order
-//   own, r-1, r-2, ... which is the order in which peers send them.
+//   first, 32 KB chunks), while the GEMM starts on the local shard.  The warp that completes a 128-row block
+//   (counted on this GPU) writes the sequence number into the block's flag on the consumer.  The TMA producer of
+//   a tile whose rows come from rank q waits for that flag, then loads from the local staging copy - TMA never
+//   reads peer memory.  Blocks are consumed in the order own, r-1, r-2, ... which is the order in which peers
+//   send them.
+//
+// Flags hold the sequence number of the operator that wrote them (the communicator's launch count, the same on
+// every rank and kept on the device) and are compared with >=, so a flag names its call: a fast rank that is
+// already in the next call cannot complete a slower rank's wait of this one, nothing has to be reset, shapes may
+// change from call to call and a captured launch replays.  Waiting threads poll with relaxed loads and a sleep
+// between polls; each flag has one writer and is written once per call.
 //
 // Both follow the CCL-buffer protocol of the collective kernels (launch parity selects the half, every
 // rank waits for every other rank once per call), so they interleave freely with other operators.
-// Arrival counters only grow: the host keeps the value each counter reaches in the next call and passes the table.
 // With several ranks sharing one GPU (tests) all ranks run in one cooperative launch, gridDim.y = ranks.
+//
+// Either operator can also run split in two launches of this library's own kernels (all-gather push kernel, then
+// the GEMM reading the staging; GEMM, then the reduce-scatter kernel): the mode argument or HCOMM_FUSED_MODE
+// chooses, and shapes that do not fit the fused kernels' tables take the split form by themselves.
+//
+// Reference counterpart: the MC2 server (framework/device/aicpu_kfc/, framework/op_base/src/op_base_mc2.cc), where
+// a matmul kernel posts "tile ready" messages and a control CPU issues the transfers; here the handshake is a flag
+// word per tile and both sides live in one kernel.
 #include <cuda_runtime.h>
 
 #include <algorithm>
 
+#include "../coll/ops.h"
 #include "../comm/comm.h"
 #include "../core/log.h"
 #include "emu_launch.h"
@@ -31,6 +48,7 @@
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2sm.cuh"
 #include "hcomm_device.cuh"
+#include "hcomm_fused.h"
 
 namespace hc {
 namespace {
@@ -38,35 +56,36 @@ namespace {
 using namespace hcgemm;
 
 constexpr int kFusedThreads = 256;          // 6 GEMM warps + 2 communication warps
-constexpr int kRsFlagBase = 0;              // u32 indices inside HC_OFF_FUSED
-constexpr int kAgFlagBase = 4096;
-constexpr size_t kAgChunkBytes = 32 << 10;  // unit of the all-gather push: one warp moves one chunk, then bumps the block's counter
-constexpr int kFlagCount = 8192;
+constexpr size_t kAgChunkBytes = 32 << 10;  // unit of the all-gather push: one warp moves one chunk
+// Flag words (u32) inside the HC_OFF_FUSED region of every rank's heap:
+//   all-gather:      block b (128 rows of the gathered matrix)           -> kAgFlagBase + b * 8            (own 32-byte sector)
+//   reduce-scatter:  (source rank s, tile t of my rows, row group g < 8) -> kRsFlagBase + (s * tilesPer + t) * 8 + g
+constexpr int kAgFlagBase = 0;
+constexpr int kAgMaxBlocks = 1024;
+constexpr int kRsFlagBase = 16384;
+constexpr int kRsMaxSrcTiles = 8192;        // nRanks * tiles per rank
+static_assert((size_t)(kRsFlagBase + kRsMaxSrcTiles * 8) * 4 <= HC_OFF_TEAM_SYNC - HC_OFF_FUSED, "fused flags outgrew their region");
+// Device-local scratch of a communicator (Comm::fusedLocal): chunk counters of the push, then the phase clocks.
+constexpr size_t kLocalSentWords = kAgMaxBlocks;
+constexpr size_t kLocalPhaseWords = 2 * 160 * kPhaseSlots;     // u64, two CTAs per SM pair slot, up to 160 SMs
+constexpr size_t kLocalBytes = kLocalSentWords * 4 + kLocalPhaseWords * 8;
 
 struct FusedParams {
     CUtensorMap tmA, tmB, tmA2, tmA2b;   // tmA2 / tmA2b: staging copy of A in CCL half 0 / 1
     GemmShape shape;
     CommDev *dev;
     void *out;
-    const void *xLocal;       // AG: this rank's shard
+    const void *xLocal;       // AG: this rank's shard; NULL when a separate launch pushes it
     int ldOut;
-    int mbPer;                // 128-row blocks per rank
-    const uint32_t *expect;   // per arrival counter: the value that means "complete" in this call (indexed like the counters)
+    int mbPer;                // row blocks per rank (128 rows; 256 in the CTA-pair reduce-scatter)
     int rowsPer;              // rows per rank
     int K;
+    uint32_t *sent;           // AG: device-local chunk counters [peer index][block]
 };
 
 __device__ __forceinline__ uint32_t *FusedFlag(const CommDev *d, int rank, int idx)
 {
     return (uint32_t *)(HcPeerHeap(d, rank) + HC_OFF_FUSED) + idx;
-}
-__device__ __forceinline__ void RedReleaseSysAdd32(uint32_t *p, uint32_t v)
-{
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ void EpilogueBarrier()   // the four epilogue warps only
-{
-    asm volatile("bar.sync 1, 128;" ::: "memory");
 }
 
 // ------------------------------------------------------------------------ GEMM -> ReduceScatter
@@ -83,19 +102,23 @@ struct RsOrder {
     }
 };
 
-template <int BN>
+// TILE_ROWS: 128 (one CTA per tile) or 256 (CTA pair).  A row group is the 32 rows one epilogue warp owns.
+template <int BN, int TILE_ROWS>
 struct RsEpilogue {
     static constexpr bool kStaged = true;      // the CTA-pair main loop sends partial tiles out as whole 256-byte row segments
     const CommDev *d;
     __nv_bfloat16 *out;
     int ldOut, N, mbPer, rowsPer, tilesN;
-    uint32_t half;
-    const uint32_t *expect;
-    volatile uint32_t *abortFlag;
+    uint32_t half, seq;
+    uint64_t *phase;                           // this CTA's phase clocks or NULL
 
     __device__ __forceinline__ char *Slot(int owner, int src) const
     {
         return hcdev::CclHalf(d, owner, half) + (size_t)src * rowsPer * N * sizeof(__nv_bfloat16);
+    }
+    __device__ __forceinline__ uint32_t *TileFlag(int owner, int src, int mb, int nb, int group) const
+    {
+        return FusedFlag(d, owner, kRsFlagBase + ((src * mbPer + mb % mbPer) * tilesN + nb) * 8 + group);
     }
     __device__ __forceinline__ bool StagedTile(int mb) const { return mb / mbPer != d->rank; }
     // 32 rows x 128 columns of a partial tile, parked in shared memory by the calling warp, go to the owner's staging
@@ -105,13 +128,19 @@ struct RsEpilogue {
         char *dst = Slot(q, d->rank) + ((size_t)(rowBase - q * rowsPer) * N + colBase) * sizeof(__nv_bfloat16);
         hcgemm::pair::StageFlushRows(slab, dst, (size_t)N * sizeof(__nv_bfloat16), lane);
     }
-    __device__ __forceinline__ void BeginTile(int mb, int nb, int) const
+    // `row` is the calling thread's row; the warp's 32 rows form row group (row of lane 0 - tile start) / 32.
+    __device__ __forceinline__ void BeginTile(int mb, int nb, int row) const
     {
-        const int q = mb / mbPer;
-        if (q != d->rank) return;
-        // my own rows: every peer's partial of this tile must have landed
-        const int idx = kRsFlagBase + (mb % mbPer) * tilesN + nb;
-        if ((threadIdx.x & 31) == 0) hcdev::WaitFlagGe32(d, FusedFlag(d, d->rank, idx), expect[idx], 0, HC_WAIT_TILE_FLAG, (uint32_t)idx);
+        const int q = mb / mbPer, me = d->rank;
+        if (q != me) return;
+        // my own rows: every peer's partial of this row group must have landed; lane s waits for source s
+        const int lane = threadIdx.x & 31;
+        const int group = (row - lane - mb * TILE_ROWS) >> 5;
+        if (lane < d->nRanks && lane != me) {
+            uint64_t waited = 0;
+            hcdev::WaitFlagGe32Quiet(d, TileFlag(me, lane, mb, nb, group), seq, (uint32_t)lane, HC_WAIT_TILE_FLAG, (uint32_t)(mb * tilesN + nb), &waited);
+            if (phase && (threadIdx.x >> 5) == 2 && lane == (me == 0 ? 1 : 0)) phase[kPhaseTileWait] += waited;   // one lane speaks for the warp
+        }
         __syncwarp();
     }
     __device__ __forceinline__ void Fragment(int mb, int, int row, int col, const uint32_t (&f)[32]) const
@@ -184,39 +213,48 @@ struct RsEpilogue {
             *(uint4 *)(dst + v * 8) = pk;
         }
     }
-    __device__ __forceinline__ void EndTile(int mb, int nb, int) const
+    // The warp's rows of a partial tile are on their way: publish the row group.  The releasing store of lane 0
+    // orders the whole warp's stores before the flag (the lanes met at __syncwarp).
+    __device__ __forceinline__ void EndTile(int mb, int nb, int row) const
     {
         const int q = mb / mbPer;
         if (q == d->rank) return;
-        EpilogueBarrier();                       // all 128 epilogue threads have issued their stores
-        if (threadIdx.x == 64) {                 // first thread of the first epilogue warp
-            __threadfence_system();
-            RedReleaseSysAdd32(FusedFlag(d, q, kRsFlagBase + (mb % mbPer) * tilesN + nb), 1u);
+        __syncwarp();
+        const int lane = threadIdx.x & 31;
+        if (lane == 0) {
+            const int group = (row - mb * TILE_ROWS) >> 5;
+            const uint64_t t0 = phase ? GlobalTimer() : 0;
+            hcdev::StReleaseSys(TileFlag(q, d->rank, mb, nb, group), seq);
+            if (phase && (threadIdx.x >> 5) == 2) phase[kPhaseSignal] += GlobalTimer() - t0;
         }
     }
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(const FusedParams *table)
+__device__ __forceinline__ uint64_t *PhaseOfCta(const GemmShape &g)
 {
-    const FusedParams &p = table[blockIdx.y];
+    return g.phase ? g.phase + (size_t)blockIdx.x * kPhaseSlots : nullptr;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
+{
+    const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
-    RsEpilogue<BN> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, p.expect, nullptr};
+    RsEpilogue<BN, kBlockM> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, nullptr};
     GemmMainLoop<BN>(&p.tmA, &p.tmB, p.shape, order, NoGate(), epi);
     hcdev::KernelEnd(d, ls, 0);
 }
 
-// The same on CTA pairs (256 x 256 tiles): tile row blocks, blocks per rank and the epilogue's arrival counters are
-// per 256-row block; both CTAs of a pair write their half of a partial tile and each bumps the counter once.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) GemmReduceScatterPairKernel(const FusedParams *table)
+// The same on CTA pairs (256 x 256 tiles): row blocks and blocks per rank count 256 rows; a tile has eight row groups.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) GemmReduceScatterPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
-    const FusedParams &p = table[blockIdx.y];
+    const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
-    RsEpilogue<256> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, p.expect, nullptr};
+    RsEpilogue<256, kPairM> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, PhaseOfCta(p.shape)};
     GemmMainLoopPair<256, 6>(&p.tmA, &p.tmB, p.shape, order, epi);
     hcdev::KernelEnd(d, ls, 0);
 }
@@ -238,7 +276,8 @@ struct AgOrder {
 struct AgGate {
     const CommDev *d;
     int mbPer;
-    const uint32_t *expect;
+    uint32_t seq;
+    uint64_t *phase;
     __device__ __forceinline__ bool operator()(int mb, int, volatile uint32_t *abortFlag, int *aRow, const CUtensorMap *own, const CUtensorMap *staged,
                                                const CUtensorMap **use) const
     {
@@ -250,34 +289,41 @@ struct AgGate {
         }
         *use = staged;
         *aRow = mb * kBlockM;
-        const int idx = kAgFlagBase + mb;
-        if (!hcdev::WaitFlagGe32(d, FusedFlag(d, d->rank, idx), expect[idx], (uint32_t)src, HC_WAIT_TILE_FLAG, (uint32_t)idx)) {
+        uint64_t waited = 0;
+        if (!hcdev::WaitFlagGe32Quiet(d, FusedFlag(d, d->rank, kAgFlagBase + mb * 8), seq, (uint32_t)src, HC_WAIT_TILE_FLAG, (uint32_t)mb, &waited)) {
             *abortFlag = 1;
             return false;
         }
+        if (phase) phase[kPhaseGateWait] += waited;
         // the rows were written by another GPU's ordinary stores; TMA reads through the async proxy
         asm volatile("fence.proxy.async;" ::: "memory");
         return true;
     }
 };
 
-// Communication warps: push my shard to the peers' staging, nearest consumer first.
+// Communication warps: push my shard to the peers' staging, nearest consumer first.  `warps` warps share the work,
+// this one is number `w`.
 struct AgPush {
     const CommDev *d;
-    const char *x;         // my shard [rowsPer, K] bf16
+    const char *x;         // my shard [rowsPer, K] bf16; NULL: nothing to push from this launch
     int mbPer, K;
-    uint32_t half;
-    __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *) const
+    uint32_t half, seq;
+    uint32_t *sent;
+    uint64_t *phase;
+    __device__ __forceinline__ void Run(int w, int warps, int lane) const
     {
+        if (!x) return;
         const int n = d->nRanks, me = d->rank;
         const size_t rowBytes = (size_t)K * sizeof(__nv_bfloat16);
         const size_t blockBytes = (size_t)kBlockM * rowBytes;                     // a multiple of 2 KB (K is a multiple of 8)
         const int chunksPerBlock = (int)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes);
         const int perPeer = mbPer * chunksPerBlock;
         const int items = (n - 1) * perPeer;
-        const int warps = gridDim.x * 2;
+        const bool clocked = phase && w == (int)blockIdx.x * 2;                  // the CTA's first communication warp
+        const uint64_t tStart = clocked ? GlobalTimer() : 0;
+        uint64_t tSignal = 0;
         // peer-major order: everything for the nearest consumer first; consecutive warps take consecutive chunks
-        for (int it = blockIdx.x * 2 + warpInRole; it < items; it += warps) {
+        for (int it = w; it < items; it += warps) {
             const int peerIdx = it / perPeer, rem = it % perPeer;
             const int blk = rem / chunksPerBlock, ch = rem % chunksPerBlock;
             const int peer = (me + 1 + peerIdx) % n;
@@ -297,95 +343,129 @@ struct AgPush {
             }
             __syncwarp();
             if (lane == 0) {
-                __threadfence_system();
-                RedReleaseSysAdd32(FusedFlag(d, peer, kAgFlagBase + me * mbPer + blk), 1u);
+                const uint64_t t0 = clocked ? GlobalTimer() : 0;
+                // The chunk is ordered before the count; the warp whose count completes the block has therefore
+                // seen every chunk of it ordered (fence, atomic on one side - atomic, fence on the other) and names it.
+                hcdev::FenceAcqRelSys();
+                uint32_t *ctr = sent + peerIdx * mbPer + blk;
+                if (atomicAdd(ctr, 1u) + 1u == (uint32_t)chunksPerBlock) {
+                    *(volatile uint32_t *)ctr = 0u;                               // next used by a later launch
+                    hcdev::FenceAcqRelSys();
+                    hcdev::StRelaxedSys(FusedFlag(d, peer, kAgFlagBase + (me * mbPer + blk) * 8), seq);
+                }
+                if (clocked) tSignal += GlobalTimer() - t0;
             }
         }
+        if (clocked && lane == 0) {
+            const uint64_t now = GlobalTimer();
+            phase[kPhasePushBusy] = now - tStart;
+            phase[kPhasePushEnd] = now;
+            phase[kPhaseSignal] = tSignal;
+        }
+    }
+    __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *) const
+    {
+        Run((int)blockIdx.x * 2 + warpInRole, (int)gridDim.x * 2, lane);
     }
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kFusedThreads, 1) AllGatherGemmKernel(const FusedParams *table)
+__global__ void __launch_bounds__(kFusedThreads, 1) AllGatherGemmKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
-    const FusedParams &p = table[blockIdx.y];
+    const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     AgOrder order{d->rank, d->nRanks, p.mbPer};
-    AgGate gate{d, p.mbPer, p.expect};
-    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half};
+    AgGate gate{d, p.mbPer, ls.seq, nullptr};
+    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
     GemmMainLoop<BN>(&p.tmA, &p.tmB, p.shape, order, gate, epi, ls.half ? &p.tmA2b : &p.tmA2, push);
     hcdev::KernelEnd(d, ls, 0);
 }
 
-// CTA-pair variant: p.mbPer counts 128-row blocks (gate, push and counters keep that unit), the tile order works
-// on 256-row blocks.
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) AllGatherGemmPairKernel(const FusedParams *table)
+// CTA-pair variant: p.mbPer counts 128-row blocks (gate, push and flags keep that unit), the tile order works
+// on 256-row blocks.  BN: tile width (see Config2).
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) AllGatherGemmPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
-    const FusedParams &p = table[blockIdx.y];
+    const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     AgOrder order{d->rank, d->nRanks, p.mbPer / 2};
-    AgGate gate{d, p.mbPer, p.expect};
-    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half};
+    AgGate gate{d, p.mbPer, ls.seq, PhaseOfCta(p.shape)};
+    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape)};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
-    GemmMainLoopPair<256, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
+    GemmMainLoopPair<BN, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
     hcdev::KernelEnd(d, ls, 0);
+}
+
+// The push alone, on every warp of the grid: first launch of the split form.  It leaves the launch count alone so that
+// the GEMM launched next sees the same sequence number and CCL half.
+__global__ void __launch_bounds__(512, 1) AllGatherPushKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
+{
+    const FusedParams &p = table ? table[blockIdx.y] : own;
+    const CommDev *d = p.dev;
+    const hcdev::LaunchState ls = hcdev::KernelBegin(d);
+    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr};
+    const int warpsPerCta = blockDim.x >> 5;
+    push.Run((int)blockIdx.x * warpsPerCta + (int)(threadIdx.x >> 5), (int)gridDim.x * warpsPerCta, threadIdx.x & 31);
+    hcdev::KernelEnd(d, ls, 0, 0);
 }
 
 // --------------------------------------------------------------------------------- host side
 
 std::mutex g_ringMu;
 
-FusedParams *ParamSlot(Comm *c)
+// Device-local scratch of the fused kernels, zeroed once (the push counters return to zero by themselves).
+char *FusedLocal(Comm *c)
 {
-    if (!c->fusedParamRing) cudaMalloc(&c->fusedParamRing, sizeof(FusedParams) * 64);
-    FusedParams *p = (FusedParams *)c->fusedParamRing + c->fusedParamNext;
-    c->fusedParamNext = (c->fusedParamNext + 1) % 64;
-    return p;
+    if (!c->fusedLocal) {
+        if (cudaMalloc(&c->fusedLocal, kLocalBytes) != cudaSuccess) { cudaGetLastError(); c->fusedLocal = nullptr; return nullptr; }
+        cudaMemset(c->fusedLocal, 0, kLocalBytes);
+    }
+    return (char *)c->fusedLocal;
+}
+uint64_t *PhaseBuffer(Comm *c, void *stream)
+{
+    if (!c->fusedPhaseClocks) return nullptr;
+    char *base = FusedLocal(c);
+    if (!base) return nullptr;
+    uint64_t *ph = (uint64_t *)(base + kLocalSentWords * 4);
+    cudaMemsetAsync(ph, 0, kLocalPhaseWords * 8, (cudaStream_t)stream);
+    return ph;
 }
 
-// Adds `units` to the expected value of counters [lo, hi) and returns a device table (indexed like the counters) that
-// holds the new values for that range; the copy is ordered on the operator's stream.
-const uint32_t *ExpectTable(Comm *c, int lo, int hi, uint32_t units, void *stream, int skipLo = 0, int skipHi = 0)
+template <typename KernelT>
+void SetSmemOnce(KernelT kernel, int smemBytes)
 {
-    if (c->fusedExpect.empty()) c->fusedExpect.assign(kFlagCount, 0u);
-    if (!c->fusedExpectRing && cudaMalloc(&c->fusedExpectRing, sizeof(uint32_t) * kFlagCount * 16) != cudaSuccess) return nullptr;
-    for (int i = lo; i < hi; ++i)
-        if (i < skipLo || i >= skipHi) c->fusedExpect[i] += units;      // [skipLo, skipHi): counters nobody bumps in this call
-    uint32_t *slot = (uint32_t *)c->fusedExpectRing + (size_t)c->fusedExpectNext * kFlagCount;
-    c->fusedExpectNext = (c->fusedExpectNext + 1) % 16;
-    if (cudaMemcpyAsync(slot + lo, c->fusedExpect.data() + lo, sizeof(uint32_t) * (size_t)(hi - lo), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess) return nullptr;
-    return slot;
+    static std::map<void *, bool> attrSet;
+    std::lock_guard<std::mutex> lk(g_ringMu);
+    if (!attrSet[(void *)kernel]) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes);
+        attrSet[(void *)kernel] = true;
+    }
 }
 
 template <typename KernelT>
 HcclResult LaunchFused(Comm *c, KernelT kernel, int smemBytes, const FusedParams &hp, int tiles, int opId, void *stream)
 {
-    static std::map<void *, bool> attrSet;
-    {
-        std::lock_guard<std::mutex> lk(g_ringMu);
-        if (!attrSet[(void *)kernel]) {
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes);
-            attrSet[(void *)kernel] = true;
-        }
-    }
+    SetSmemOnce(kernel, smemBytes);
     if (c->emuSameDevice && c->nRanks > 1) {
         const int ctas = std::max(1, std::min(GemmSmCount() / (int)c->nRanks, tiles));
         return EmuLaunchGeneric(c->identifier + "#fused" + std::to_string(c->group.id), c->nRanks, c->rank, opId, &hp, sizeof(hp), stream,
                                 [=](const void *devTable, uint32_t n, void *st) {
-                                    void *args[] = {(void *)&devTable};
+                                    FusedParams unused;
+                                    memset(&unused, 0, sizeof(unused));
+                                    void *args[] = {(void *)&unused, (void *)&devTable};
                                     cudaError_t e = cudaLaunchCooperativeKernel((void *)kernel, dim3(ctas, n, 1), dim3(kFusedThreads, 1, 1), args, smemBytes, (cudaStream_t)st);
                                     if (e != cudaSuccess) { HCCL_ERROR("fused launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
                                     return HCCL_SUCCESS;
                                 });
     }
-    FusedParams *slot = ParamSlot(c);
-    cudaError_t e = cudaMemcpyAsync(slot, &hp, sizeof(hp), cudaMemcpyHostToDevice, (cudaStream_t)stream);
-    if (e != cudaSuccess) return HCCL_E_RUNTIME;
+    // the parameter block travels as a kernel argument: no copy to order, nothing for the host to wait for
     const int ctas = std::min(GemmSmCount(), tiles);
-    kernel<<<dim3(ctas, 1, 1), kFusedThreads, smemBytes, (cudaStream_t)stream>>>(slot);
-    e = cudaGetLastError();
+    kernel<<<dim3(ctas, 1, 1), kFusedThreads, smemBytes, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
+    cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("fused launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
 }
@@ -398,10 +478,8 @@ bool PairKernelsEnabled()
 
 // CTA pairs of `kernel` (compile-time cluster of two) that can be resident at once; 0 when pairs cannot be scheduled.
 template <typename KernelT>
-int PairCapacityOf(KernelT kernel)
+int PairCapacityOf(KernelT kernel, int smemBytes)
 {
-    constexpr int smemBytes = Config2<256, 7>::kSmemBytes;      // = Config2<256, 6, true>::kSmemBytes
-    static_assert(Config2<256, 7>::kSmemBytes == Config2<256, 6, true>::kSmemBytes, "both fused pair kernels use the same shared-memory size");
     static std::map<void *, int> capacity;
     std::lock_guard<std::mutex> lk(g_ringMu);
     auto it = capacity.find((void *)kernel);
@@ -425,15 +503,12 @@ int PairCapacityOf(KernelT kernel)
 
 // Launches a CTA-pair kernel on as many pairs as can be resident at once.
 template <typename KernelT>
-HcclResult LaunchFusedPair(Comm *c, KernelT kernel, const FusedParams &hp, int tiles, void *stream)
+HcclResult LaunchFusedPair(Comm *c, KernelT kernel, int smemBytes, const FusedParams &hp, int tiles, void *stream)
 {
-    constexpr int smemBytes = Config2<256, 7>::kSmemBytes;
-    const int cap = PairCapacityOf(kernel);
+    const int cap = PairCapacityOf(kernel, smemBytes);
     if (cap <= 0) return HCCL_E_NOT_SUPPORT;
-    FusedParams *slot = ParamSlot(c);
-    if (cudaMemcpyAsync(slot, &hp, sizeof(hp), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess) return HCCL_E_RUNTIME;
     const int pairs = std::min(cap, tiles);
-    kernel<<<dim3(2 * pairs, 1, 1), kFusedThreads, smemBytes, (cudaStream_t)stream>>>(slot);
+    kernel<<<dim3(2 * pairs, 1, 1), kFusedThreads, smemBytes, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("fused launch (CTA pairs) failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
@@ -448,11 +523,44 @@ HcclResult CheckFusable(Comm *c, const char *what)
     return HCCL_SUCCESS;
 }
 
+// 0 = automatic, 1 = one fused kernel, 2 = two launches of this library's kernels
+int ResolveMode(int mode)
+{
+    if (mode == HCOMM_FUSED_MODE_AUTO) {
+        static const int envMode = [] {
+            const char *e = getenv("HCOMM_FUSED_MODE");
+            if (e && !strcmp(e, "split")) return (int)HCOMM_FUSED_MODE_SPLIT;
+            if (e && !strcmp(e, "fused")) return (int)HCOMM_FUSED_MODE_FUSED;
+            return (int)HCOMM_FUSED_MODE_AUTO;
+        }();
+        mode = envMode;
+    }
+    return mode;
+}
+
 }  // namespace
 
 HcclResult LaunchBarrierIfNeeded(Comm *c, void *stream);   // defined in ops.cc
 
-HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *out, int M, int N, int K, int lda, int ldb, int ldOut, void *stream)
+// Tile width of the CTA-pair kernels for an N-column problem with `rowBlocks` 256-row blocks on `pairs` CTA pairs:
+// the width (a divisor of N among 256, 224, 192, 160, 128) with the least work in whole waves.
+int PickPairTileWidth(int rowBlocks, int N, int pairs)
+{
+    static const int forced = [] { const char *e = getenv("HCOMM_GEMM_BN"); return e ? atoi(e) : 0; }();
+    if (forced && N % forced == 0 && forced % 32 == 0 && forced >= 128 && forced <= 256) return forced;
+    int best = 0;
+    long bestCost = 0;
+    for (int bn = 256; bn >= 128; bn -= 32) {
+        if (N % bn) continue;
+        const long tiles = (long)rowBlocks * (N / bn);
+        const long waves = (tiles + pairs - 1) / pairs;
+        const long cost = waves * bn + (bn < 256 ? 4 : 0);      // a narrower tile must win by more than a tie
+        if (!best || cost < bestCost) { best = bn; bestCost = cost; }
+    }
+    return best;
+}
+
+HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *out, int M, int N, int K, int lda, int ldb, int ldOut, void *stream, int mode)
 {
     CHK_RET(CheckFusable(c, "GEMM+ReduceScatter"));
     const int p = (int)c->nRanks;
@@ -462,35 +570,61 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     }
     const int BN = N % 256 == 0 ? 256 : 128;
     const int rowsPer = M / p;
+    mode = ResolveMode(mode);
+    const bool emu = c->emuSameDevice && c->nRanks > 1;
+    const bool usePair = PairKernelsEnabled() && !emu && rowsPer % kPairM == 0 && N % 256 == 0 &&
+                         PairCapacityOf(GemmReduceScatterPairKernel, Config2<256, 6, true>::kSmemBytes) > 0;
+    const int blockRows = usePair ? kPairM : kBlockM;
+    const bool fits = (uint64_t)p * rowsPer * N * 2 <= c->halfBytes && (uint64_t)p * (rowsPer / blockRows) * (N / BN) <= (uint64_t)kRsMaxSrcTiles;
+    if (mode == HCOMM_FUSED_MODE_SPLIT || (!fits && !emu && mode == HCOMM_FUSED_MODE_AUTO)) {
+        // GEMM into a scratch matrix kept by the communicator, then this library's reduce-scatter kernel
+        const size_t need = (size_t)M * N * 2;
+        {
+            std::lock_guard<std::mutex> lk(c->opMu);
+            if (c->fusedTempBytes < need) {
+                if (c->fusedTemp) { cudaStreamSynchronize((cudaStream_t)stream); cudaFree(c->fusedTemp); c->fusedTemp = nullptr; c->fusedTempBytes = 0; }
+                if (cudaMalloc(&c->fusedTemp, need) != cudaSuccess) { cudaGetLastError(); return HCCL_E_MEMORY; }
+                c->fusedTempBytes = need;
+            }
+        }
+        CHK_RET(GemmBf16(A, B, c->fusedTemp, M, N, K, lda, ldb, N, stream));
+        if (ldOut != N) { RPT_ERR("EI0003", "the split GEMM+ReduceScatter writes a contiguous result (ldOut %d, N %d)", ldOut, N); return HCCL_E_PARA; }
+        OpDesc od;
+        od.cmd = HCCL_CMD_REDUCE_SCATTER; od.in = c->fusedTemp; od.out = out; od.count = (uint64_t)rowsPer * N;
+        od.dtype = HCCL_DATA_TYPE_BFP16; od.op = HCCL_REDUCE_SUM; od.stream = (Stream)stream;
+        return RunOp(c, od);
+    }
     if ((uint64_t)p * rowsPer * N * 2 > c->halfBytes) {
         RPT_ERR("EI0003", "GEMM+ReduceScatter staging (%llu MB) exceeds one CCL half (%u MB); raise HCCL_BUFFSIZE", (unsigned long long)((uint64_t)p * rowsPer * N * 2 >> 20), c->cfg.bufferMB);
         return HCCL_E_MEMORY;
     }
-    if ((rowsPer / kBlockM) * (N / BN) > 4096) return HCCL_E_NOT_SUPPORT;
+    if ((uint64_t)p * (rowsPer / blockRows) * (N / BN) > (uint64_t)kRsMaxSrcTiles) return HCCL_E_NOT_SUPPORT;
     std::lock_guard<std::mutex> lk(c->opMu);
     CHK_RET(LaunchBarrierIfNeeded(c, stream));
     FusedParams hp;
     memset(&hp, 0, sizeof(hp));
-    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && rowsPer % kPairM == 0 && N % 256 == 0 &&
-                         PairCapacityOf(GemmReduceScatterPairKernel) > 0;
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, usePair ? 128u : (uint32_t)BN, kBlockK));
-    const int blockRows = usePair ? kPairM : kBlockM;
     hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / blockRows; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
+    hp.shape.phase = usePair ? PhaseBuffer(c, stream) : nullptr;
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / blockRows; hp.rowsPer = rowsPer; hp.K = K;
-    // every peer bumps a tile's counter once per CTA that wrote part of it (two CTAs share a tile in the pair kernel)
-    hp.expect = ExpectTable(c, kRsFlagBase, kRsFlagBase + hp.mbPer * hp.shape.tilesN, (uint32_t)(p - 1) * (usePair ? 2u : 1u), stream);
-    if (!hp.expect) return HCCL_E_RUNTIME;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
-    if (usePair) {
-        return LaunchFusedPair(c, GemmReduceScatterPairKernel, hp, tiles, stream);
-    }
+    c->fusedLastCtas = usePair ? 2 * std::min(PairCapacityOf(GemmReduceScatterPairKernel, Config2<256, 6, true>::kSmemBytes), tiles) : 0;
+    if (usePair) return LaunchFusedPair(c, GemmReduceScatterPairKernel, Config2<256, 6, true>::kSmemBytes, hp, tiles, stream);
     if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
     return LaunchFused(c, GemmReduceScatterKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9002, stream);
 }
 
-HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, int Mshard, int N, int K, int ldx, int ldw, int ldOut, void *stream)
+namespace {
+template <int BN>
+HcclResult LaunchAgPair(Comm *c, const FusedParams &hp, int tiles, void *stream)
+{
+    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN>, Config2<BN, 7>::kSmemBytes, hp, tiles, stream);
+}
+}  // namespace
+
+HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, int Mshard, int N, int K, int ldx, int ldw, int ldOut, void *stream, int mode)
 {
     CHK_RET(CheckFusable(c, "AllGather+GEMM"));
     const int p = (int)c->nRanks;
@@ -498,38 +632,61 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
         RPT_ERR("EI0003", "AllGather+GEMM needs a contiguous shard with rows divisible by %d, N by 128, K by 8 (rows=%d N=%d K=%d)", kBlockM, Mshard, N, K);
         return HCCL_E_PARA;
     }
-    const int BN = N % 256 == 0 ? 256 : 128;
     const int M = Mshard * p;
     if ((uint64_t)M * K * 2 > c->halfBytes) {
         RPT_ERR("EI0003", "AllGather+GEMM staging (%llu MB) exceeds one CCL half (%u MB); raise HCCL_BUFFSIZE", (unsigned long long)((uint64_t)M * K * 2 >> 20), c->cfg.bufferMB);
         return HCCL_E_MEMORY;
     }
-    if (M / kBlockM > 4096) return HCCL_E_NOT_SUPPORT;
+    if (M / kBlockM > kAgMaxBlocks) return HCCL_E_NOT_SUPPORT;
+    mode = ResolveMode(mode);
     std::lock_guard<std::mutex> lk(c->opMu);
     CHK_RET(LaunchBarrierIfNeeded(c, stream));
     FusedParams hp;
     memset(&hp, 0, sizeof(hp));
     // The staging copy of the gathered activations lives in this operator's CCL half; which half is only known on
     // the device (launch parity), so a map is built for each and the kernel picks.
-    const bool usePair = PairKernelsEnabled() && !(c->emuSameDevice && c->nRanks > 1) && Mshard % kPairM == 0 && N % 256 == 0 &&
-                         PairCapacityOf(AllGatherGemmPairKernel) > 0;
+    const bool emu = c->emuSameDevice && c->nRanks > 1;
+    const bool usePair = PairKernelsEnabled() && !emu && Mshard % kPairM == 0 && N % 128 == 0 &&
+                         PairCapacityOf(AllGatherGemmPairKernel<256>, Config2<256, 7>::kSmemBytes) > 0;
+    int BN = N % 256 == 0 ? 256 : 128;
+    if (usePair) BN = PickPairTileWidth(M / kPairM, N, PairCapacityOf(AllGatherGemmPairKernel<256>, Config2<256, 7>::kSmemBytes));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, x, (uint64_t)Mshard, (uint64_t)K, (uint64_t)ldx, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2, c->CclBuffer(), (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2b, c->CclBuffer() + c->halfBytes, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
-    CHK_RET(MakeTensorMap2dBf16(&hp.tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, usePair ? 128u : (uint32_t)BN, kBlockK));
+    CHK_RET(MakeTensorMap2dBf16(&hp.tmB, W, (uint64_t)N, (uint64_t)K, (uint64_t)ldw, usePair ? (uint32_t)(BN / 2) : (uint32_t)BN, kBlockK));
     hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / (usePair ? kPairM : kBlockM); hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
+    hp.shape.phase = usePair ? PhaseBuffer(c, stream) : nullptr;
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = Mshard / kBlockM; hp.rowsPer = Mshard; hp.K = K; hp.xLocal = x;
-    const uint64_t blockBytes = (uint64_t)kBlockM * K * 2;
-    hp.expect = ExpectTable(c, kAgFlagBase, kAgFlagBase + M / kBlockM, (uint32_t)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes), stream,
-                            kAgFlagBase + (int)c->rank * (Mshard / kBlockM), kAgFlagBase + ((int)c->rank + 1) * (Mshard / kBlockM));   // my own blocks are not sent to me
-    if (!hp.expect) return HCCL_E_RUNTIME;
+    char *local = FusedLocal(c);
+    if (!local) return HCCL_E_MEMORY;
+    hp.sent = (uint32_t *)local;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
-    if (usePair) {
-        return LaunchFusedPair(c, AllGatherGemmPairKernel, hp, tiles, stream);
+    if (mode == HCOMM_FUSED_MODE_SPLIT && !emu && p > 1) {
+        // first launch: the push on the whole GPU; the GEMM launched next waits for the peers' flags like the fused form
+        AllGatherPushKernel<<<dim3(GemmSmCount(), 1, 1), 512, 0, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
+        if (cudaGetLastError() != cudaSuccess) return HCCL_E_RUNTIME;
+        hp.xLocal = nullptr;
     }
+    if (usePair) {
+        c->fusedLastCtas = 2 * std::min(PairCapacityOf(AllGatherGemmPairKernel<256>, Config2<256, 7>::kSmemBytes), tiles);
+        switch (BN) {
+            case 256: return LaunchAgPair<256>(c, hp, tiles, stream);
+            case 224: return LaunchAgPair<224>(c, hp, tiles, stream);
+            case 192: return LaunchAgPair<192>(c, hp, tiles, stream);
+            case 160: return LaunchAgPair<160>(c, hp, tiles, stream);
+            default: return LaunchAgPair<128>(c, hp, tiles, stream);
+        }
+    }
+    c->fusedLastCtas = 0;
     if (BN == 256) return LaunchFused(c, AllGatherGemmKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9003, stream);
     return LaunchFused(c, AllGatherGemmKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9004, stream);
+}
+
+// Clears the device-local scratch after a suspension (a call that was cut short leaves counts behind).
+void FusedResetLocal(Comm *c)
+{
+    if (c->fusedLocal) cudaMemset(c->fusedLocal, 0, kLocalBytes);
 }
 
 }  // namespace hc
@@ -540,14 +697,52 @@ int HcommFusedGemmReduceScatterBf16(HcclComm comm, const void *A, const void *B,
 {
     hc::Comm *c = hc::AsComm(comm);
     if (!c) return HCCL_E_PTR;
-    return (int)hc::FusedGemmReduceScatter(c, A, B, out, M, N, K, lda, ldb, ldOut, stream);
+    return (int)hc::FusedGemmReduceScatter(c, A, B, out, M, N, K, lda, ldb, ldOut, stream, HCOMM_FUSED_MODE_AUTO);
 }
 
 int HcommFusedAllGatherGemmBf16(HcclComm comm, const void *x, const void *W, void *out, int Mshard, int N, int K, int ldx, int ldw, int ldOut, void *stream)
 {
     hc::Comm *c = hc::AsComm(comm);
     if (!c) return HCCL_E_PTR;
-    return (int)hc::FusedAllGatherGemm(c, x, W, out, Mshard, N, K, ldx, ldw, ldOut, stream);
+    return (int)hc::FusedAllGatherGemm(c, x, W, out, Mshard, N, K, ldx, ldw, ldOut, stream, HCOMM_FUSED_MODE_AUTO);
+}
+
+int HcommFusedGemmReduceScatterBf16Mode(HcclComm comm, const void *A, const void *B, void *out, int M, int N, int K, int lda, int ldb, int ldOut, void *stream, int mode)
+{
+    hc::Comm *c = hc::AsComm(comm);
+    if (!c) return HCCL_E_PTR;
+    return (int)hc::FusedGemmReduceScatter(c, A, B, out, M, N, K, lda, ldb, ldOut, stream, mode);
+}
+
+int HcommFusedAllGatherGemmBf16Mode(HcclComm comm, const void *x, const void *W, void *out, int Mshard, int N, int K, int ldx, int ldw, int ldOut, void *stream, int mode)
+{
+    hc::Comm *c = hc::AsComm(comm);
+    if (!c) return HCCL_E_PTR;
+    return (int)hc::FusedAllGatherGemm(c, x, W, out, Mshard, N, K, ldx, ldw, ldOut, stream, mode);
+}
+
+// Phase clocks of the CTA-pair fused kernels: when on, every call records per CTA when it started and ended and how long
+// its roles waited (the slots are listed in gemm_sm100.cuh).  Costs a few clock reads per tile; off by default.
+int HcommFusedSetPhaseClocks(HcclComm comm, int on)
+{
+    hc::Comm *c = hc::AsComm(comm);
+    if (!c) return HCCL_E_PTR;
+    c->fusedPhaseClocks = on != 0;
+    return HCCL_SUCCESS;
+}
+
+// Copies the clocks of the most recent fused call (after the caller synchronised its stream): `words` receives
+// ctas x 8 values, *ctas the number of CTAs that call ran on.
+int HcommFusedGetPhaseClocks(HcclComm comm, uint64_t *words, int maxCtas, int *ctas)
+{
+    hc::Comm *c = hc::AsComm(comm);
+    if (!c || !words || !ctas) return HCCL_E_PTR;
+    *ctas = 0;
+    if (!c->fusedLocal || !c->fusedLastCtas) return HCCL_SUCCESS;
+    const int n = std::min(maxCtas, c->fusedLastCtas);
+    if (cudaMemcpy(words, (char *)c->fusedLocal + hc::kLocalSentWords * 4, (size_t)n * hcgemm::kPhaseSlots * 8, cudaMemcpyDeviceToHost) != cudaSuccess) return HCCL_E_RUNTIME;
+    *ctas = n;
+    return HCCL_SUCCESS;
 }
 
 }  // extern "C"

@@ -12,6 +12,8 @@ HcclResult MakeTensorMap2dBf16(CUtensorMap *map, const void *base, uint64_t rows
 // C[M,N] = A[M,K] * B[N,K]^T, bf16 in / bf16 out, fp32 accumulation in tensor memory.
 HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream);
 int GemmSmCount();
+// Tile width (256, 224, 192, 160 or 128, a divisor of N) of the CTA-pair kernels with the least work in whole waves.
+int PickPairTileWidth(int rowBlocks256, int N, int pairs);
 uint32_t *GemmErrorFlag();
 
 }  // namespace hc

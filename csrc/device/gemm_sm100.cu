@@ -43,8 +43,11 @@ int PairClusterCapacity()
 {
     static int cap = -1;
     if (cap >= 0) return cap;
-    cudaFuncSetAttribute(GemmBf16PairKernel<256, 6>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 6>::kSmemBytes);
     cudaFuncSetAttribute(GemmBf16PairKernel<256, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 7>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairKernel<224, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<224, 7>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairKernel<192, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<192, 7>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairKernel<160, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<160, 7>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairKernel<128, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<128, 7>::kSmemBytes);
     cudaFuncSetAttribute(GemmBf16PairStagedKernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 6, true>::kSmemBytes);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148, 1, 1);
@@ -125,38 +128,44 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
         return HCCL_E_PARA;
     }
     static const bool pairEnabled = [] { const char *e = getenv("HCOMM_GEMM_PAIR"); return !(e && e[0] == '0'); }();
-    if (pairEnabled && M % hcgemm::kPairM == 0 && N % 256 == 0 && PairClusterCapacity() > 0) {
+    if (pairEnabled && M % hcgemm::kPairM == 0 && N % 128 == 0 && PairClusterCapacity() > 0) {
+        const int bn = PickPairTileWidth(M / hcgemm::kPairM, N, PairClusterCapacity());
         CUtensorMap tmA, tmB;
         CHK_RET(MakeTensorMap2dBf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, hcgemm::kBlockM, hcgemm::kBlockK));
-        CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, 128, hcgemm::kBlockK));
+        CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)(bn / 2), hcgemm::kBlockK));
         hcgemm::GemmShape shape;
         shape.M = M; shape.N = N; shape.K = K;
         shape.tilesM = M / hcgemm::kPairM;
-        shape.tilesN = N / 256;
+        shape.tilesN = N / bn;
         shape.errFlag = GemmErrorFlag();
+        shape.phase = nullptr;
         hcgemm::StoreBf16 epi{(__nv_bfloat16 *)C, ldc, M, N};
         const int clusters = std::min(PairClusterCapacity(), shape.tilesM * shape.tilesN);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * clusters, 1, 1);
         cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
-        static const int stages = [] { const char *e = getenv("HCOMM_GEMM_STAGES"); return e && atoi(e) == 6 ? 6 : 7; }();
         static const int gm = [] { const char *e = getenv("HCOMM_GEMM_GM"); int v = e ? atoi(e) : 0; return v > 0 ? v : 16; }();
-        cfg.dynamicSmemBytes = stages == 7 ? hcgemm::Config2<256, 7>::kSmemBytes : hcgemm::Config2<256, 6>::kSmemBytes;
         cfg.stream = (cudaStream_t)stream;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
         at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
         static const bool stagedEpilogue = [] { const char *e = getenv("HCOMM_GEMM_STAGED"); return e && e[0] == '1'; }();
-        if (stagedEpilogue && ldc % 8 == 0) {
+        if (stagedEpilogue && ldc % 8 == 0 && bn == 256) {
             cfg.dynamicSmemBytes = hcgemm::Config2<256, 6, true>::kSmemBytes;
             hcgemm::StoreBf16Staged sepi{(__nv_bfloat16 *)C, ldc};
             cudaError_t e2 = cudaLaunchKernelEx(&cfg, GemmBf16PairStagedKernel<256>, tmA, tmB, shape, sepi, gm);
             if (e2 != cudaSuccess) { HCCL_ERROR("GemmBf16 (CTA pairs, staged epilogue) launch failed: %s", cudaGetErrorString(e2)); return HCCL_E_RUNTIME; }
             return HCCL_SUCCESS;
         }
-        cudaError_t e = stages == 7 ? cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 7>, tmA, tmB, shape, epi, gm)
-                                    : cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 6>, tmA, tmB, shape, epi, gm);
+        cudaError_t e;
+        switch (bn) {
+            case 256: cfg.dynamicSmemBytes = hcgemm::Config2<256, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 7>, tmA, tmB, shape, epi, gm); break;
+            case 224: cfg.dynamicSmemBytes = hcgemm::Config2<224, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<224, 7>, tmA, tmB, shape, epi, gm); break;
+            case 192: cfg.dynamicSmemBytes = hcgemm::Config2<192, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<192, 7>, tmA, tmB, shape, epi, gm); break;
+            case 160: cfg.dynamicSmemBytes = hcgemm::Config2<160, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<160, 7>, tmA, tmB, shape, epi, gm); break;
+            default: cfg.dynamicSmemBytes = hcgemm::Config2<128, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<128, 7>, tmA, tmB, shape, epi, gm); break;
+        }
         if (e != cudaSuccess) {
             HCCL_ERROR("GemmBf16 (CTA pairs) launch failed: %s", cudaGetErrorString(e));
             return HCCL_E_RUNTIME;
@@ -172,6 +181,7 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
     shape.tilesM = (M + hcgemm::kBlockM - 1) / hcgemm::kBlockM;
     shape.tilesN = (N + BN - 1) / BN;
     shape.errFlag = GemmErrorFlag();
+    shape.phase = nullptr;
     hcgemm::StoreBf16 epi{(__nv_bfloat16 *)C, ldc, M, N};
     int grid = std::min(GemmSmCount(), shape.tilesM * shape.tilesN);
     cudaError_t e;

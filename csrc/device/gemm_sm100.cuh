@@ -45,7 +45,26 @@ struct GemmShape {
     int M, N, K;
     int tilesM, tilesN;
     uint32_t *errFlag;       // device word, set to non-zero when a wait expired
+    uint64_t *phase;         // optional phase clocks, kPhaseSlots words per CTA (nanoseconds of the GPU's global timer); NULL = off
 };
+
+// Phase clocks of one CTA.  Start / End are time stamps, the others are sums of waiting or working time.
+constexpr int kPhaseSlots = 8;
+constexpr int kPhaseStart = 0;      // the CTA began
+constexpr int kPhaseEnd = 1;        // the CTA left the main loop
+constexpr int kPhaseGateWait = 2;   // TMA producer: waiting for rows that another rank sends (all-gather -> GEMM)
+constexpr int kPhaseAccWait = 3;    // first epilogue warp: waiting for an accumulator
+constexpr int kPhaseTileWait = 4;   // first epilogue warp: waiting for the peers' partial tiles (GEMM -> reduce-scatter)
+constexpr int kPhasePushBusy = 5;   // first communication warp: first to last byte of its share of the push
+constexpr int kPhasePushEnd = 6;    // first communication warp: time stamp of its last signal
+constexpr int kPhaseSignal = 7;     // first communication / epilogue warp: time inside fences and signals
+
+__device__ __forceinline__ uint64_t GlobalTimer()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 
 struct SharedState {
     uint64_t full[8], empty[8], tmemFull[2], tmemEmpty[2];

@@ -25,17 +25,21 @@ constexpr int kPairM = 256;
 constexpr int kStagingBytesPerWarp = 32 * 128 * 2;      // 32 rows x 128 bf16 columns
 constexpr int kStagingBytes = 4 * kStagingBytesPerWarp;  // one slab per epilogue warp
 
+// BN: width of the pair's tile, a multiple of 32 between 128 and 256 (each CTA holds BN / 2 rows of B, whole 8-row
+// swizzle groups, and the epilogue reads 32 columns at a time).  Widths below 256 exist for the tail: a problem whose
+// tile count at 256 columns leaves most of the last wave idle runs faster on narrower tiles.
 template <int BN, int STAGES = 6, bool STAGING = false> struct Config2 {
-    static_assert(BN == 256, "the pair kernel is built for 256 x 256 tiles");
-    static_assert(STAGES >= 2 && STAGES <= 7, "the ring must fit 227 KB of shared memory and the 8-entry barrier arrays");
-    static_assert(!STAGING || STAGES <= 6, "epilogue staging takes the room of the seventh stage");
+    static_assert(BN % 32 == 0 && BN >= 128 && BN <= 256, "tile widths: 128, 160, 192, 224, 256");
+    static_assert(STAGES >= 2 && STAGES <= 8, "the ring must fit 227 KB of shared memory and the 8-entry barrier arrays");
+    static_assert(!STAGING || BN % 128 == 0, "the staged epilogue sends 128-column slabs");
     static constexpr int kStages = STAGES;
     static constexpr int kStaging = STAGING ? kStagingBytes : 0;
     static constexpr int kABytes = kBlockM * kBlockK * 2;          // 128 rows of A per CTA
     static constexpr int kBBytes = (BN / 2) * kBlockK * 2;         // 128 of the 256 B rows per CTA
     static constexpr int kStageBytes = kABytes + kBBytes;
-    static constexpr int kTmemCols = 2 * BN;
+    static constexpr int kTmemCols = 2 * BN <= 256 ? 256 : 512;    // two accumulators; allocations are powers of two
     static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + 1024 + 256;
+    static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 };
 
 // Epilogue policies without a staged path.
@@ -171,6 +175,7 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
     const int firstTile = (int)ClusterId(), tileStep = (int)NumClusters();
 
     if (threadIdx.x == 0) {
+        if (g.phase) g.phase[(size_t)blockIdx.x * kPhaseSlots + kPhaseStart] = GlobalTimer();
         for (int s = 0; s < Cfg::kStages; ++s) { MbarInit(&st->full[s], 1); MbarInit(&st->empty[s], 1); }
         for (int a = 0; a < 2; ++a) { MbarInit(&st->tmemFull[a], 1); MbarInit(&st->tmemEmpty[a], 8); }   // 4 epilogue warps x 2 CTAs
         st->abort = 0;
@@ -253,6 +258,13 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
             int mb, nb;
             order(t, g, &mb, &nb);
             const uint32_t acc = tileIter & 1, accPh = (tileIter >> 1) & 1;
+            if (g.phase && q == 0 && lane == 0) {
+                // phase clock: time this CTA's epilogue spent waiting for an accumulator (main loop or its inputs late)
+                const uint64_t t0 = GlobalTimer();
+                const bool ok = MbarWait(&st->tmemFull[acc], accPh, &st->abort);
+                g.phase[(size_t)blockIdx.x * kPhaseSlots + kPhaseAccWait] += GlobalTimer() - t0;
+                if (!ok) st->abort = 1;
+            }
             if (!MbarWait(&st->tmemFull[acc], accPh, &st->abort)) { alive = false; break; }
             TcFenceAfter();
             const int row = mb * kPairM + (int)ctaRank * kBlockM + q * 32 + lane;
@@ -311,6 +323,7 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
     ClusterSync();
     if (warp == 1) TmemDealloc2(tmemBase, Cfg::kTmemCols);
     if (threadIdx.x == 0 && st->abort && g.errFlag) atomicExch(g.errFlag, 1u);
+    if (threadIdx.x == 0 && g.phase) g.phase[(size_t)blockIdx.x * kPhaseSlots + kPhaseEnd] = GlobalTimer();
 }
 
 }  // namespace hcgemm

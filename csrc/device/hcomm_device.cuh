@@ -41,6 +41,17 @@ __device__ __forceinline__ uint64_t LdAcquireSys64(const uint64_t *p)
     asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
+__device__ __forceinline__ uint32_t LdRelaxedSys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void StRelaxedSys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void FenceAcqRelSys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
 __device__ __forceinline__ void RedReleaseSysAdd64(uint64_t *p, uint64_t v)
 {
     asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
@@ -80,6 +91,31 @@ __device__ __forceinline__ bool WaitFlagGe32(const CommDev *d, const uint32_t *f
             if (GlobalTimerNs() - start > d->timeoutNs) { ReportTimeout(d, peer, kind, slot, target, seen); return false; }
         }
     }
+}
+// The same wait for flags that are polled next to busy tensor-core and copy warps: relaxed loads with a growing
+// sleep between them (a poll costs one L2 access and nothing else), and one acquire fence once the value is there.
+// `waitedNs`, when given, is increased by the time spent here.
+__device__ __forceinline__ bool WaitFlagGe32Quiet(const CommDev *d, const uint32_t *flag, uint32_t target, uint32_t peer, uint32_t kind,
+                                                  uint32_t slot, uint64_t *waitedNs = nullptr)
+{
+    uint32_t seen = LdRelaxedSys(flag);
+    if ((int32_t)(seen - target) < 0) {
+        const uint64_t start = GlobalTimerNs();
+        uint32_t ns = 32;
+        for (uint32_t it = 1;; ++it) {
+            __nanosleep(ns);
+            if (ns < 512) ns *= 2;
+            seen = LdRelaxedSys(flag);
+            if ((int32_t)(seen - target) >= 0) break;
+            if ((it & 31) == 0) {
+                if (Aborted(d)) return false;
+                if (GlobalTimerNs() - start > d->timeoutNs) { ReportTimeout(d, peer, kind, slot, target, seen); return false; }
+            }
+        }
+        if (waitedNs) *waitedNs += GlobalTimerNs() - start;
+    }
+    FenceAcqRelSys();
+    return true;
 }
 __device__ __forceinline__ bool WaitFlagGe64(const CommDev *d, const uint64_t *flag, uint64_t target, uint32_t peer, uint32_t kind,
                                              uint32_t slot)
@@ -135,6 +171,7 @@ __device__ __forceinline__ void CrossRankBarrierMc(const CommDev *d, uint32_t ep
 struct LaunchState {
     uint32_t epoch0;
     uint32_t half;
+    uint32_t seq;      // operators launched on this communicator so far + 1: the same on every rank, never zero in a flag's lifetime
 };
 static_assert(sizeof(CommDev) <= HC_DEV_COUNTERS_OFFSET, "CommDev outgrew its slot");
 __device__ __forceinline__ uint32_t *DevCounters(const CommDev *d) { return (uint32_t *)((char *)d + HC_DEV_COUNTERS_OFFSET); }
@@ -144,7 +181,8 @@ __device__ __forceinline__ LaunchState KernelBegin(const CommDev *d)
     LaunchState s;
     const uint32_t *ctr = DevCounters(d);
     s.epoch0 = *(volatile const uint32_t *)&ctr[0];
-    s.half = *(volatile const uint32_t *)&ctr[1] & 1u;
+    s.seq = *(volatile const uint32_t *)&ctr[1] + 1u;
+    s.half = (s.seq - 1u) & 1u;
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         if (d->profile) {
             // device-side timestamps of the last kernels, read by the host (HcclDiagGetKernelTimes); only when profiling

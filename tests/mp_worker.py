@@ -267,6 +267,51 @@ def main():
         stage("moe dispatch/combine ok")
         moe.destroy()
         dist.destroy_process_group()
+    elif scenario == "fused_bench_shapes":
+        # The tensor-parallel benchmark's shapes (8192 tokens, hidden 8192, intermediate 28672 / world): more tiles than CTA
+        # pairs, every destination / source with many tiles.  Checked on sampled rows against an fp32 product; the
+        # reduce-scatter is also issued several times back to back with one rank held back on the host, so that a fast rank
+        # is a whole call ahead of a slow one.
+        import torch
+        import torch.distributed as dist
+        from hcomm_b200.ops.fused import all_gather_gemm, gemm_reduce_scatter
+        from hcomm_b200.ops.gemm import take_kernel_error
+        dist.init_process_group("gloo", init_method=f"file://{os.environ['HCOMM_ROOT_FILE']}.gloo", rank=rank, world_size=world)
+        tokens, hidden, inter = 8192, 8192, 28672 // world
+        rows = tokens // world
+        g = torch.Generator(device="cuda").manual_seed(50 + rank)
+        x = torch.randn(rows, hidden, device="cuda", generator=g).to(torch.bfloat16)
+        w_up = (torch.randn(inter, hidden, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+        w_down = (torch.randn(hidden, inter, device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+        pick = torch.randperm(rows, generator=torch.Generator().manual_seed(7))[:48].sort().values     # the same local rows on every rank
+        for mode in ("fused", "split"):
+            gathered = [torch.empty(48, hidden, dtype=torch.bfloat16) for _ in range(world)]
+            dist.all_gather(gathered, x[pick.cuda()].cpu())
+            want_h = torch.cat(gathered).cuda().float() @ w_up.float().t()                                # rows (r, pick[i]) of the gathered product
+            for rep in range(2):
+                h = all_gather_gemm(comm, x, w_up, mode=mode)
+                torch.cuda.synchronize()
+                got = torch.cat([h[r * rows + pick.cuda()] for r in range(world)]).float()
+                err = (got - want_h).abs().max().item()
+                assert err <= 2e-2 * max(1.0, want_h.abs().max().item()), ("ag_gemm", mode, rep, err)
+            stage(f"all_gather_gemm {mode} ok at the benchmark's shape")
+            # partial products of the sampled rows of every destination, summed over ranks on the host
+            sel = torch.cat([r * rows + pick for r in range(world)]).cuda()
+            part = (h[sel].float() @ w_down.float().t()).cpu()
+            dist.all_reduce(part)
+            want_y = part[rank * 48:(rank + 1) * 48].cuda()
+            outs = []
+            if rank == world - 1:
+                time.sleep(0.05)                    # this rank starts late: the others are calls ahead of it
+            for rep in range(4):
+                outs.append(gemm_reduce_scatter(comm, h, w_down, mode=mode))
+            torch.cuda.synchronize()
+            for rep, y in enumerate(outs):
+                err = (y[pick.cuda()].float() - want_y).abs().max().item()
+                assert err <= 2e-2 * max(1.0, want_y.abs().max().item()), ("gemm_rs", mode, rep, err)
+            stage(f"gemm_reduce_scatter {mode} ok at the benchmark's shape, four calls back to back")
+        assert take_kernel_error() == 0 and comm.async_error() == 0
+        dist.destroy_process_group()
     elif scenario == "hcom":
         # named groups, rank translation, gradient fusion split and group collectives (the python `hccl` package)
         import ctypes

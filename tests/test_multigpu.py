@@ -30,6 +30,14 @@ def test_fused_kernels_across_gpus(world):
     assert codes == [0] * world, "\n".join(outs)
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_fused_kernels_at_the_benchmark_shapes(world):
+    if cuda_device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    codes, outs = launch("fused_bench_shapes", world, {"HCOMM_TEST_BUFFER_MB": "512", "HCCL_EXEC_TIMEOUT": "30"}, timeout=300)
+    assert codes == [0] * world, "\n".join(outs)
+
+
 @pytest.mark.parametrize("scenario", ["torch_ops", "torch_ddp"])
 def test_torch_backend_across_gpus(scenario):
     if cuda_device_count() < 2:
