@@ -244,7 +244,9 @@ static bool NvlsServes(const SelectInput &in)
 {
     if (!in.cuda || !in.nvlsAvailable) return false;
     if (in.cmd == HCCL_CMD_BROADCAST) return true;
-    if (in.cmd != HCCL_CMD_ALLREDUCE) return false;
+    if (in.cmd == HCCL_CMD_ALLGATHER) return !in.variableCounts;       // multicast stores move bytes of any type
+    if (in.cmd != HCCL_CMD_ALLREDUCE && in.cmd != HCCL_CMD_REDUCE_SCATTER) return false;
+    if (in.variableCounts) return false;
     // multimem.ld_reduce exists for f32/f16/bf16 add and integer min/max/add; keep to what is exercised
     bool typeOk = in.dtype == HCCL_DATA_TYPE_FP32 || in.dtype == HCCL_DATA_TYPE_FP16 || in.dtype == HCCL_DATA_TYPE_BFP16;
     return typeOk && in.op == HCCL_REDUCE_SUM && in.deterministic == 0;

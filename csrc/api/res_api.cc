@@ -636,6 +636,60 @@ HcclResult HcclChannelGetDeviceView(HcclComm comm, ChannelHandle channel, void *
 //   3. otherwise (cudaMalloc memory) -> legacy CUDA IPC handles.
 // All ranks must take the same case; the exchange checks it.
 
+namespace {
+// Gives a window backed by a virtual-memory allocation a multicast alias (multimem loads reduce the ranks' copies in the
+// switch, multimem stores replicate to all of them), the way the communicator's own heap has one.  Needs the same
+// allocation size and the same window offset on every rank; every step is agreed on by all ranks so that they keep
+// or drop the alias together.  Failure leaves the window without alias: operators then use peer loads and stores.
+void WindowSetupMulticast(Comm *c, Window *w, const PhysMem &phys, uint64_t allocBytes, bool sameLayout)
+{
+    Platform *P = c->plat;
+    const uint32_t n = c->nRanks;
+    auto agree = [&](bool ok) {
+        std::vector<Blob> all;
+        Blob mine(1, ok ? 1 : 0);
+        if (c->boot->AllGather(c->group, mine, &all) != HCCL_SUCCESS) return false;
+        for (auto &b : all)
+            if (b.empty() || !b[0]) return false;
+        return true;
+    };
+    const uint64_t gran = P->Granularity();
+    bool want = c->mcBase != nullptr && sameLayout && allocBytes % gran == 0 && P->MulticastSupported();
+    if (!agree(want)) return;
+    const uint64_t tag = ((uint64_t)c->group.id << 32) | 0x4d000000u | (uint32_t)(c->windows.size() & 0xffffff);
+    bool ok = true;
+    if (c->rank == 0) {
+        ok = P->McCreate(allocBytes, (int)n, &w->mcPhys) == HCCL_SUCCESS;
+        for (uint32_t q = 1; q < n && ok; ++q) {
+            int fd = -1;
+            ok = P->PhysExportFd(w->mcPhys, &fd) == HCCL_SUCCESS && c->boot->SendFd(c->worldRanks[q], tag, fd) == HCCL_SUCCESS;
+            if (fd >= 0) ::close(fd);
+        }
+    }
+    if (!agree(ok)) { if (w->mcPhys.bytes) P->PhysRelease(&w->mcPhys); w->mcPhys = PhysMem(); return; }
+    if (c->rank != 0) {
+        int fd = -1;
+        ok = c->boot->RecvFd(c->worldRanks[0], tag, &fd) == HCCL_SUCCESS && P->PhysImportFd(fd, allocBytes, &w->mcPhys) == HCCL_SUCCESS;
+        if (fd >= 0) ::close(fd);
+    }
+    ok = ok && P->McAddDevice(w->mcPhys) == HCCL_SUCCESS;
+    if (!agree(ok)) { if (w->mcPhys.bytes) P->PhysRelease(&w->mcPhys); w->mcPhys = PhysMem(); return; }
+    ok = P->McBind(w->mcPhys, 0, phys, allocBytes) == HCCL_SUCCESS;
+    w->mcBound = ok;
+    void *va = nullptr;
+    ok = ok && P->VaReserve(allocBytes, &va) == HCCL_SUCCESS && P->Map(va, w->mcPhys, allocBytes) == HCCL_SUCCESS;
+    if (!agree(ok)) {
+        if (w->mcBound) { P->McUnbind(w->mcPhys, 0, allocBytes); w->mcBound = false; }
+        if (w->mcPhys.bytes) P->PhysRelease(&w->mcPhys);
+        w->mcPhys = PhysMem();
+        return;
+    }
+    w->mcVa = va;
+    w->mcBytes = allocBytes;
+    w->mcPtr = (char *)va + w->allocOffset;
+}
+}  // namespace
+
 HcclResult HcclCommSymWinRegister(HcclComm comm, void *addr, uint64_t size, HcclCommSymWindow *winHandle, uint32_t flag)
 {
     (void)flag;
@@ -723,6 +777,9 @@ HcclResult HcclCommSymWinRegister(HcclComm comm, void *addr, uint64_t size, Hccl
             CHK_RET(P->Map(va, w->imported[q], descs[q].allocBytes));
             w->peerPtr[q] = va + descs[q].offset;
         }
+        bool sameLayout = true;
+        for (uint32_t q = 0; q < n; ++q) sameLayout = sameLayout && descs[q].allocBytes == mine.allocBytes && descs[q].offset == mine.offset;
+        WindowSetupMulticast(c, w.get(), phys, mine.allocBytes, sameLayout);
         P->PhysRelease(&phys);
     } else {
         w->ipcBases.assign(n, nullptr);
@@ -753,6 +810,10 @@ HcclResult HcclCommSymWinDeregister(HcclCommSymWindow winHandle)
         for (uint32_t q = 0; q < c->nRanks; ++q)
             if (q != c->rank && w->imported[q].bytes) { P->Unmap((char *)w->vaBase + (size_t)q * w->mapStride, w->imported[q].bytes); P->PhysRelease(&w->imported[q]); }
         if (w->vaBase) P->VaFree(w->vaBase, w->vaBytes);
+        if (w->mcVa) { P->Unmap(w->mcVa, w->mcBytes); P->VaFree(w->mcVa, w->mcBytes); }
+        if (w->mcBound) P->McUnbind(w->mcPhys, 0, w->mcBytes);
+        if (w->mcPhys.bytes) P->PhysRelease(&w->mcPhys);
+        w->mcVa = nullptr; w->mcBound = false; w->mcPhys = PhysMem(); w->mcPtr = nullptr;
     } else if (w->kind == Window::IPC) {
         for (void *b : w->ipcBases)
             if (b) P->IpcClose(b);

@@ -155,27 +155,64 @@ bool TrySmallLL(Comm *c, const OpDesc &d, const Selection &sel, HcclResult *res)
 
 // -------------------------------------------------------------------------- fast-kernel drivers
 
+// Zero-copy on registered memory: when a buffer lies inside a window registered with HcclCommSymWinRegister (or an
+// activated HcclCommSetMemoryRange), kernels read the peers' copies of it in place instead of staging through the CCL
+// buffer - what the reference's zero-copy address manager and graph-mode kernels are for
+// (communicator/impl/zero_copy/zero_copy_address_mgr.cc, aiv_all_reduce_910b_bigdata_graph.h).  HCCL_ZERO_COPY=0 turns it off.
+bool ZeroCopyEnabled()
+{
+    static const bool on = [] { const char *e = getenv("HCCL_ZERO_COPY"); return !(e && e[0] == '0'); }();
+    return on;
+}
+// Fills a.inPeer / a.inMc when [in, in + bytes) is registered (and 16-byte aligned); returns whether it is.
+bool RegisteredInput(Comm *c, const void *in, uint64_t bytes, CollArgs &a, bool needMc)
+{
+    if (!ZeroCopyEnabled() || c->emuSameDevice || ((uintptr_t)in & 15) != 0) return false;
+    uint64_t off = 0;
+    Window *w = FindWindow(c, in, bytes, &off);
+    if (!w || (needMc && !w->mcPtr)) return false;
+    for (uint32_t r = 0; r < c->nRanks; ++r) a.inPeer[r] = (const char *)w->peerPtr[r] + off;
+    a.inMc = w->mcPtr ? (const char *)w->mcPtr + off : nullptr;
+    return true;
+}
+void *RegisteredOutputMc(Comm *c, void *out, uint64_t bytes)
+{
+    if (!ZeroCopyEnabled() || c->emuSameDevice || ((uintptr_t)out & 15) != 0) return nullptr;
+    uint64_t off = 0;
+    Window *w = FindWindow(c, out, bytes, &off);
+    return (w && w->mcPtr) ? (char *)w->mcPtr + off : nullptr;
+}
+void ClearRegistered(CollArgs &a)
+{
+    memset(a.inPeer, 0, sizeof(a.inPeer));
+    a.inMc = nullptr;
+    a.outMc = nullptr;
+}
+
 HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
 {
     const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
     CollArgs a;
     FillBase(c, d, a);
     int kind = sel.engine == Engine::NVLS ? FK_ALLREDUCE_NVLS : (sel.algo == Algo::MESH_ONESHOT ? FK_ALLREDUCE_ONESHOT : FK_ALLREDUCE_TWOSHOT);
-    uint64_t maxPerLaunch, oneShotCap = AlignDownElems(c->halfBytes / n / esz, esz);
+    const uint64_t oneShotCap = AlignDownElems(c->halfBytes / n / esz, esz);
     if (kind == FK_ALLREDUCE_ONESHOT && d.count > oneShotCap) kind = FK_ALLREDUCE_TWOSHOT;
-    if (kind == FK_ALLREDUCE_ONESHOT) maxPerLaunch = oneShotCap;
-    else if (kind == FK_ALLREDUCE_TWOSHOT) maxPerLaunch = AlignDownElems(c->halfBytes / (2 * n) / esz, esz) * n;
-    else maxPerLaunch = AlignDownElems(c->halfBytes / esz, esz);
-    for (uint64_t off = 0; off < d.count; off += maxPerLaunch) {
-        uint64_t cnt = std::min(maxPerLaunch, d.count - off);
-        a.in = (const char *)d.in + off * esz;
-        a.out = (char *)d.out + off * esz;
-        a.count = cnt;
-        a.sliceElems = kind == FK_ALLREDUCE_ONESHOT ? oneShotCap : AlignedSliceCount(cnt, n, esz);
-        uint64_t perRank = kind == FK_ALLREDUCE_ONESHOT ? cnt * esz : cnt * esz / n * 2;
-        CHK_RET(Launch(c, kind, a, PickCtas(c, sel, perRank), d.stream));
+    a.in = d.in; a.out = d.out; a.count = d.count;
+    // in-switch reduction straight from the registered input into the registered output: no staging, any size
+    const bool nvlsTypes = d.op == HCCL_REDUCE_SUM && (d.dtype == HCCL_DATA_TYPE_FP32 || d.dtype == HCCL_DATA_TYPE_FP16 || d.dtype == HCCL_DATA_TYPE_BFP16);
+    if (c->mcBase && nvlsTypes && c->cfg.deterministic == 0 && sel.reason != "forced by configuration" && d.count * esz >= 64 * 1024 &&
+        RegisteredInput(c, d.in, d.count * esz, a, true)) {
+        a.outMc = RegisteredOutputMc(c, d.out, d.count * esz);
+        if (a.outMc) return Launch(c, FK_ALLREDUCE_NVLS, a, PickCtas(c, sel, d.count * esz), d.stream);
+        ClearRegistered(a);
     }
-    return HCCL_SUCCESS;
+    // One launch whatever the size: operands beyond the staging are walked in windows inside the kernel.
+    if (kind == FK_ALLREDUCE_ONESHOT) { a.sliceElems = oneShotCap; a.winElems = 0; }
+    else if (kind == FK_ALLREDUCE_TWOSHOT) { a.winElems = AlignDownElems(c->halfBytes / (2 * n) / esz, esz) * n; a.sliceElems = d.count <= a.winElems ? AlignedSliceCount(d.count, n, esz) : 0; }
+    else { a.winElems = AlignDownElems(c->halfBytes / esz, esz); a.sliceElems = 0; }
+    const uint64_t perWin = a.winElems ? std::min<uint64_t>(d.count, a.winElems) : d.count;
+    const uint64_t perRank = kind == FK_ALLREDUCE_ONESHOT ? perWin * esz : (d.count > perWin ? perWin * esz : perWin * esz / n * 2);
+    return Launch(c, kind, a, PickCtas(c, sel, perRank), d.stream);
 }
 
 HcclResult FastReduce(Comm *c, const OpDesc &d, const Selection &sel)
@@ -195,32 +232,36 @@ HcclResult FastReduce(Comm *c, const OpDesc &d, const Selection &sel)
     return HCCL_SUCCESS;
 }
 
-// ReduceScatter and its V form: block q = sendCounts[q] elements at sendDispls[q].
+// ReduceScatter and its V form: block q = sendCounts[q] elements at sendDispls[q].  One launch: blocks longer than a
+// staging slot travel in column windows inside the kernel.
 HcclResult FastReduceScatter(Comm *c, const OpDesc &d, const Selection &sel)
 {
     const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
     CollArgs a;
     FillBase(c, d, a);
-    std::vector<uint64_t> cnt(n), dsp(n);
+    const bool uniform = d.sendCounts.empty();
     uint64_t maxCnt = 0;
     for (uint32_t q = 0; q < n; ++q) {
-        cnt[q] = d.sendCounts.empty() ? d.count : d.sendCounts[q];
-        dsp[q] = d.sendCounts.empty() ? (uint64_t)q * d.count : d.sendDispls[q];
-        maxCnt = std::max(maxCnt, cnt[q]);
+        a.sendCounts[q] = uniform ? d.count : d.sendCounts[q];
+        a.sendDispls[q] = uniform ? (uint64_t)q * d.count : d.sendDispls[q];
+        maxCnt = std::max(maxCnt, a.sendCounts[q]);
     }
-    uint64_t cap = AlignDownElems(c->halfBytes / n / esz, esz);
+    a.in = d.in; a.out = d.out; a.count = maxCnt;
+    const uint64_t cap = AlignDownElems(c->halfBytes / n / esz, esz);
     a.sliceElems = cap;
-    a.in = d.in;
-    for (uint64_t c0 = 0; c0 < maxCnt; c0 += cap) {
-        for (uint32_t q = 0; q < n; ++q) {
-            uint64_t hi = std::min(cnt[q], c0 + cap);
-            a.sendCounts[q] = hi > c0 ? hi - c0 : 0;
-            a.sendDispls[q] = dsp[q] + c0;
-        }
-        a.out = (char *)d.out + c0 * esz;
-        CHK_RET(Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz * std::max(1u, n - 1)), d.stream));   // bytes this rank moves
+    const uint64_t moved = std::min(cap, maxCnt) * esz * std::max(1u, n - 1);       // bytes this rank moves per window
+    const bool vectors = uniform && (d.count * esz) % 16 == 0 && (((uintptr_t)d.in | (uintptr_t)d.out) & 15) == 0;
+    const bool nvlsTypes = d.op == HCCL_REDUCE_SUM && (d.dtype == HCCL_DATA_TYPE_FP32 || d.dtype == HCCL_DATA_TYPE_FP16 || d.dtype == HCCL_DATA_TYPE_BFP16);
+    const bool nvls = sel.engine == Engine::NVLS && c->mcBase && vectors && nvlsTypes && c->cfg.deterministic == 0;
+    if (uniform && sel.reason != "forced by configuration" && d.count * esz >= 16 * 1024 && RegisteredInput(c, d.in, (uint64_t)n * d.count * esz, a, false)) {
+        // registered input: pull the peers' blocks in place (through the switch when the window has a multicast alias)
+        if (a.inMc && nvls) return Launch(c, FK_REDUCE_SCATTER_NVLS, a, PickCtas(c, sel, moved), d.stream);
+        a.inMc = nullptr;
+        return Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, moved), d.stream);
     }
-    return HCCL_SUCCESS;
+    ClearRegistered(a);
+    if (nvls) return Launch(c, FK_REDUCE_SCATTER_NVLS, a, PickCtas(c, sel, moved), d.stream);
+    return Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, moved), d.stream);
 }
 
 HcclResult FastAllGather(Comm *c, const OpDesc &d, const Selection &sel)
@@ -228,25 +269,28 @@ HcclResult FastAllGather(Comm *c, const OpDesc &d, const Selection &sel)
     const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
     CollArgs a;
     FillBase(c, d, a);
-    std::vector<uint64_t> cnt(n), dsp(n);
+    const bool uniform = d.recvCounts.empty();
     uint64_t maxCnt = 0;
     for (uint32_t q = 0; q < n; ++q) {
-        cnt[q] = d.recvCounts.empty() ? d.count : d.recvCounts[q];
-        dsp[q] = d.recvCounts.empty() ? (uint64_t)q * d.count : d.recvDispls[q];
-        maxCnt = std::max(maxCnt, cnt[q]);
+        a.recvCounts[q] = uniform ? d.count : d.recvCounts[q];
+        a.recvDispls[q] = uniform ? (uint64_t)q * d.count : d.recvDispls[q];
+        maxCnt = std::max(maxCnt, a.recvCounts[q]);
     }
-    uint64_t cap = AlignDownElems(c->halfBytes / esz, esz);
-    a.out = d.out;
-    for (uint64_t c0 = 0; c0 < maxCnt; c0 += cap) {
-        for (uint32_t q = 0; q < n; ++q) {
-            uint64_t hi = std::min(cnt[q], c0 + cap);
-            a.recvCounts[q] = hi > c0 ? hi - c0 : 0;
-            a.recvDispls[q] = dsp[q] + c0;
-        }
-        a.in = (const char *)d.in + c0 * esz;
-        CHK_RET(Launch(c, FK_ALLGATHER, a, PickCtas(c, sel, std::min(cap, maxCnt - c0) * esz * std::max(1u, n - 1)), d.stream));   // bytes this rank moves
+    a.in = d.in; a.out = d.out; a.count = maxCnt;
+    const bool vectors = uniform && (d.count * esz) % 16 == 0 && (((uintptr_t)d.in | (uintptr_t)d.out) & 15) == 0;
+    const bool nvls = sel.engine == Engine::NVLS && c->mcBase && vectors;
+    const bool mayZeroCopy = uniform && sel.reason != "forced by configuration" && d.count * esz >= 16 * 1024;
+    if (nvls) {
+        // every rank stores its block once, the switch replicates it: straight into a registered output, else via the staging
+        a.outMc = mayZeroCopy ? RegisteredOutputMc(c, d.out, (uint64_t)n * d.count * esz) : nullptr;
+        a.sliceElems = AlignDownElems(c->halfBytes / n / esz, esz);
+        return Launch(c, FK_ALLGATHER_NVLS, a, PickCtas(c, sel, std::min(a.sliceElems, maxCnt) * esz * std::max(1u, n - 1)), d.stream);
     }
-    return HCCL_SUCCESS;
+    a.sliceElems = AlignDownElems(c->halfBytes / esz, esz);
+    const uint64_t moved = std::min(a.sliceElems, maxCnt) * esz * std::max(1u, n - 1);
+    if (mayZeroCopy && RegisteredInput(c, d.in, d.count * esz, a, false)) { a.inMc = nullptr; return Launch(c, FK_ALLGATHER, a, PickCtas(c, sel, moved), d.stream); }
+    ClearRegistered(a);
+    return Launch(c, FK_ALLGATHER, a, PickCtas(c, sel, moved), d.stream);
 }
 
 HcclResult FastAlltoAll(Comm *c, const OpDesc &d, const Selection &sel)

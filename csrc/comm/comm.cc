@@ -381,6 +381,9 @@ Comm::~Comm()
                 if (r != rank && w->peerPtr[r]) plat->Unmap((char *)w->vaBase + (size_t)r * w->mapStride, w->mapStride);
             for (auto &ph : w->imported) plat->PhysRelease(&ph);
             if (w->vaBase) plat->VaFree(w->vaBase, w->vaBytes);
+            if (w->mcVa) { plat->Unmap(w->mcVa, w->mcBytes); plat->VaFree(w->mcVa, w->mcBytes); }
+            if (w->mcBound) plat->McUnbind(w->mcPhys, 0, w->mcBytes);
+            if (w->mcPhys.bytes) plat->PhysRelease(&w->mcPhys);
         } else if (w->kind == Window::IPC) {
             for (void *b : w->ipcBases)
                 if (b) plat->IpcClose(b);
@@ -419,6 +422,19 @@ void CommDestroy(Comm *c)
     delete c;
     if (world && boot) boot->Close();
     // the hub (if this process owns it) ends when every agent has said goodbye
+}
+
+Window *FindWindow(Comm *c, const void *ptr, uint64_t bytes, uint64_t *offset)
+{
+    std::lock_guard<std::mutex> lk(c->resMu);
+    for (auto &w : c->windows) {
+        const char *b = (const char *)w->localAddr;
+        if ((const char *)ptr >= b && (const char *)ptr + bytes <= b + w->size) {
+            if (offset) *offset = (uint64_t)((const char *)ptr - b);
+            return w.get();
+        }
+    }
+    return nullptr;
 }
 
 void CommSetAsyncError(Comm *c, HcclResult err)

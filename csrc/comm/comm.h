@@ -69,7 +69,16 @@ struct Window {
     std::vector<PhysMem> imported;
     std::vector<void *> ipcBases;
     uint64_t allocOffset = 0;        // offset of localAddr inside its allocation
+    // multicast alias of a virtual-memory window (the heap's own alias serves HEAP windows)
+    PhysMem mcPhys;
+    void *mcVa = nullptr;
+    size_t mcBytes = 0;
+    bool mcBound = false;
 };
+
+// The registered window that holds [ptr, ptr + bytes), or NULL; *offset receives the distance from the window's start.
+struct Comm;
+Window *FindWindow(Comm *c, const void *ptr, uint64_t bytes, uint64_t *offset);
 
 struct ThreadRes {
     uint32_t magic = 0x54485244;     // "THRD"

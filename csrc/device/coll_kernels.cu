@@ -167,6 +167,38 @@ __device__ __forceinline__ uint32_t MaybePreBarrier(const CommDev *d, const Coll
     return 1;
 }
 
+// Operands larger than the staging walk it in windows of a.winElems elements inside ONE launch; window w works in CCL
+// half (first half + w) & 1.  CTAs only ever wait for their namesakes on the other ranks, so CTAs drift apart and the
+// copy-in of one window, the reduction of another and the copy-out of a third overlap - the counter-chasing pipeline
+// of the reference's big-data kernels (aiv_all_reduce_910b_bigdata.h:90-165,262-289) without its progress counters.
+// A half is reused two windows later; by then every peer's namesake CTA has passed a barrier that follows its last
+// access to it (the same argument that lets consecutive operators alternate halves).
+struct Window {
+    uint32_t index, half;
+    uint64_t off, cnt;       // elements
+};
+__device__ __forceinline__ uint32_t WindowCount(const CollArgs &a, uint64_t total)
+{
+    if (a.winElems == 0 || total <= a.winElems) return 1;
+    return (uint32_t)((total + a.winElems - 1) / a.winElems);
+}
+__device__ __forceinline__ Window WindowAt(const CollArgs &a, const LaunchState &ls, uint32_t w, uint64_t total)
+{
+    Window x;
+    x.index = w;
+    x.half = (ls.half + w) & 1u;
+    const uint64_t W = (a.winElems == 0 || total <= a.winElems) ? total : a.winElems;
+    x.off = (uint64_t)w * W;
+    x.cnt = total - x.off < W ? total - x.off : W;
+    return x;
+}
+// Elements per slice when `cnt` elements are cut into n slices of whole 16-byte vectors.
+__device__ __forceinline__ uint64_t SliceElems(uint64_t cnt, int n, uint32_t esz)
+{
+    const uint64_t per = (cnt + n - 1) / n, q = esz >= 16 ? 1 : 16 / esz;
+    return (per + q - 1) / q * q;
+}
+
 // ------------------------------------------------------------------------------------ AllReduce
 
 // count <= sliceElems; staging: n slots of sliceElems elements.
@@ -189,9 +221,9 @@ __global__ void __launch_bounds__(512) KAllReduceOneShot(const __grid_constant__
     KernelEnd(d, ls, used);
 }
 
-// Staging: 2n slots of sliceElems elements: [0,n) partial slices arriving from the peers, [n,2n) reduced slices
-// arriving from their owners.  count <= n * sliceElems.  NVLink carries data in the first two phases (partials
-// out, then reduced slices out while they are being computed); the last phase is a local copy.
+// Staging: 2n slots of S elements: [0,n) partial slices arriving from the peers, [n,2n) reduced slices
+// arriving from their owners.  A window holds at most n * S elements.  NVLink carries data in the first two phases
+// (partials out, then reduced slices out while they are being computed); the last phase is a local copy.
 template <typename T>
 __global__ void __launch_bounds__(512) KAllReduceTwoShot(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
@@ -199,38 +231,79 @@ __global__ void __launch_bounds__(512) KAllReduceTwoShot(const __grid_constant__
     const LaunchState ls = KernelBegin(d);
     uint32_t used = MaybePreBarrier(d, a, ls);
     const int n = d->nRanks, me = d->rank;
-    const uint64_t S = a.sliceElems, slotBytes = S * sizeof(T);
-    uint64_t beg, len;
-    // scatter: my copy of slice q goes to slot `me` of rank q
-    for (int i = 1; i < n; ++i) {
-        int q = (me + i) % n;
-        SliceRange(a.count, S, q, &beg, &len);
-        GridCopy(CclHalf(d, q, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in + beg * sizeof(T), len * sizeof(T), sizeof(T));
+    const uint32_t nWin = WindowCount(a, a.count);
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const Window x = WindowAt(a, ls, w, a.count);
+        const char *in = (const char *)a.in + x.off * sizeof(T);
+        char *out = (char *)a.out + x.off * sizeof(T);
+        const uint64_t S = nWin == 1 && a.sliceElems ? a.sliceElems : SliceElems(x.cnt, n, sizeof(T)), slotBytes = S * sizeof(T);
+        uint64_t beg, len;
+        // scatter: my copy of slice q goes to slot `me` of rank q
+        for (int i = 1; i < n; ++i) {
+            int q = (me + i) % n;
+            SliceRange(x.cnt, S, q, &beg, &len);
+            GridCopy(CclHalf(d, q, x.half) + (uint64_t)me * slotBytes, in + beg * sizeof(T), len * sizeof(T), sizeof(T));
+        }
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        // reduce my slice in rank order; the result goes to my output and to slot n+me of every peer
+        SliceRange(x.cnt, S, me, &beg, &len);
+        {
+            const char *src[HC_KERNEL_MAX_RANKS];
+            char *dst[HC_KERNEL_MAX_RANKS];
+            for (int r = 0; r < n; ++r) src[r] = (r == me) ? in + beg * sizeof(T) : CclHalf(d, me, x.half) + (uint64_t)r * slotBytes;
+            int nd = 0;
+            dst[nd++] = out + beg * sizeof(T);
+            for (int i = 1; i < n; ++i) dst[nd++] = CclHalf(d, (me + i) % n, x.half) + (uint64_t)(n + me) * slotBytes;
+            ReduceFanOut<T>(src, n, dst, nd, len, a.op, a.useScale, a.scale);
+        }
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        // the other slices have landed in my staging: copy them out
+        for (int i = 1; i < n; ++i) {
+            int q = (me + i) % n;
+            SliceRange(x.cnt, S, q, &beg, &len);
+            GridCopy(out + beg * sizeof(T), CclHalf(d, me, x.half) + (uint64_t)(n + q) * slotBytes, len * sizeof(T), sizeof(T));
+        }
     }
-    CrossRankBarrier(d, ls.epoch0 + (++used));
-    // reduce my slice in rank order; the result goes to my output and to slot n+me of every peer
-    SliceRange(a.count, S, me, &beg, &len);
-    {
-        const char *src[HC_KERNEL_MAX_RANKS];
-        char *dst[HC_KERNEL_MAX_RANKS];
-        for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + beg * sizeof(T) : CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes;
-        int nd = 0;
-        dst[nd++] = (char *)a.out + beg * sizeof(T);
-        for (int i = 1; i < n; ++i) dst[nd++] = CclHalf(d, (me + i) % n, ls.half) + (uint64_t)(n + me) * slotBytes;
-        ReduceFanOut<T>(src, n, dst, nd, len, a.op, a.useScale, a.scale);
-    }
-    CrossRankBarrier(d, ls.epoch0 + (++used));
-    // the other slices have landed in my staging: copy them out
-    for (int i = 1; i < n; ++i) {
-        int q = (me + i) % n;
-        SliceRange(a.count, S, q, &beg, &len);
-        GridCopy((char *)a.out + beg * sizeof(T), CclHalf(d, me, ls.half) + (uint64_t)(n + q) * slotBytes, len * sizeof(T), sizeof(T));
-    }
-    KernelEnd(d, ls, used);
+    KernelEnd(d, ls, used, nWin);
 }
 
 // In-switch reduction.  count*sizeof(T) <= halfBytes; the vector lives in the symmetric half,
 // multimem.ld_reduce pulls the sum of all ranks' copies, multimem.st replicates it to all of them.
+//
+// Which thread touches which 16-byte vector is the same in all three phases: vector i belongs to grid thread
+// i % (gridDim * blockDim) - the rule of GridCopy - and, in the reduce phase, to rank (i / (gridDim * blockDim)) % n.
+// The per-CTA barriers between the phases pair CTA b of one rank with CTA b of the others, so a vector must never
+// change its CTA index from one phase to the next.  The ragged last vector (bytes % 16) belongs to CTA 0 of every
+// rank in the copies and to rank 0's CTA 0 in the reduce phase.
+template <typename T>
+__device__ __forceinline__ uint4 ScaleVec(uint4 v, float scale)
+{
+    Pack<T> p; p.v = v;
+#pragma unroll
+    for (int j = 0; j < Pack<T>::N; ++j) p.e[j] = Narrow<T>(Widen<T>(p.e[j]) * scale);
+    return p.v;
+}
+// Reduces, through the switch, the vectors [0, nvec) of `mc` that this rank owns (see above) and hands each sum to sink(i, v).
+template <typename T, typename Sink>
+__device__ __forceinline__ void NvlsReduceOwned(const char *mc, uint64_t nvec, int n, int me, int useScale, float scale, Sink sink)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, step = (uint64_t)n * stride;
+    // A switch round trip takes microseconds: four independent 16-byte reductions per thread are kept in flight.
+    constexpr int kUnroll = 4;
+    uint64_t i = (uint64_t)me * stride + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i + (kUnroll - 1) * step < nvec; i += kUnroll * step) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = Multimem<T>::LdReduceAdd(mc + ((i + u * step) << 4));
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) sink(i + u * step, useScale ? ScaleVec<T>(v[u], scale) : v[u]);
+    }
+    for (; i < nvec; i += step) {
+        uint4 v = Multimem<T>::LdReduceAdd(mc + (i << 4));
+        sink(i, useScale ? ScaleVec<T>(v, scale) : v);
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(512) KAllReduceNvls(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
@@ -238,58 +311,116 @@ __global__ void __launch_bounds__(512) KAllReduceNvls(const __grid_constant__ Co
     const LaunchState ls = KernelBegin(d);
     uint32_t used = MaybePreBarrier(d, a, ls);
     const int n = d->nRanks, me = d->rank;
-    // pad to whole 16-byte vectors: the padding bytes are whatever the half held, harmless
-    const uint64_t bytes = a.count * sizeof(T);
-    char *mine = CclHalf(d, me, ls.half);
-    GridCopy(mine, (const char *)a.in, bytes, sizeof(T));
-    CrossRankBarrier(d, ls.epoch0 + (++used));
-    {
-        const uint64_t nvec = (bytes + 15) >> 4;
-        const uint64_t per = (nvec + n - 1) / n;
-        const uint64_t v0 = per * me < nvec ? per * me : nvec, v1 = (v0 + per < nvec) ? v0 + per : nvec;
-        char *mc = d->mcBase + d->bufOffset + (uint64_t)ls.half * d->halfBytes;
-        const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
-        // A switch round trip takes microseconds: four independent 16-byte reductions per thread are kept in flight.
-        constexpr int kUnroll = 4;
-        uint64_t i = v0 + (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-        for (; i + (kUnroll - 1) * stride < v1; i += kUnroll * stride) {
-            uint4 v[kUnroll];
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) v[u] = Multimem<T>::LdReduceAdd(mc + ((i + u * stride) << 4));
-#pragma unroll
-            for (int u = 0; u < kUnroll; ++u) {
-                if (a.useScale) {
-                    Pack<T> p; p.v = v[u];
-#pragma unroll
-                    for (int j = 0; j < Pack<T>::N; ++j) p.e[j] = Narrow<T>(Widen<T>(p.e[j]) * a.scale);
-                    v[u] = p.v;
-                }
-                MultimemSt16(mc + ((i + u * stride) << 4), v[u]);
-            }
+    if (a.inMc && a.outMc) {
+        // Registered buffers (both inside a window with a multicast alias): the switch reads the ranks' inputs in place
+        // and writes every rank's output in place; nothing is staged.  First barrier: every rank's input is final (its
+        // stream has reached this operator).  Last barrier: nobody reuses its input or reads its output before every
+        // rank has finished pulling / storing.
+        const uint64_t bytes = a.count * sizeof(T), nvec = bytes >> 4;
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        char *omc = (char *)a.outMc;
+        NvlsReduceOwned<T>((const char *)a.inMc, nvec, n, me, a.useScale, a.scale, [&](uint64_t i, uint4 v) { MultimemSt16(omc + (i << 4), v); });
+        if ((bytes & 15) && blockIdx.x == 0 && threadIdx.x < (bytes & 15) / sizeof(T)) {
+            // ragged tail (fewer than 16 bytes): every rank reduces it for itself from the peers' inputs with plain loads
+            const uint64_t e = (nvec << 4) / sizeof(T) + threadIdx.x;
+            typename AccOf<T>::type acc = Widen<T>(*(volatile const T *)((const char *)a.inPeer[0] + e * sizeof(T)));
+            for (int r = 1; r < n; ++r) acc = Combine<typename AccOf<T>::type>(a.op, acc, Widen<T>(*(volatile const T *)((const char *)a.inPeer[r] + e * sizeof(T))));
+            ((T *)a.out)[e] = Narrow<T>(a.useScale ? ScaleAcc<typename AccOf<T>::type>(acc, a.scale) : acc);
         }
-        for (; i < v1; i += stride) {
-            uint4 v = Multimem<T>::LdReduceAdd(mc + (i << 4));
-            if (a.useScale) {
-                Pack<T> p; p.v = v;
-#pragma unroll
-                for (int j = 0; j < Pack<T>::N; ++j) p.e[j] = Narrow<T>(Widen<T>(p.e[j]) * a.scale);
-                v = p.v;
-            }
-            MultimemSt16(mc + (i << 4), v);
-        }
-        // Multicast stores travel through the switch; the barrier's release by another thread of the CTA does not
-        // cover them, so every thread fences its own before the CTA signals.
         __threadfence_system();
+        CrossRankBarrierMc(d, ls.epoch0 + (++used));
+        KernelEnd(d, ls, used, 0);
+        return;
     }
-    CrossRankBarrierMc(d, ls.epoch0 + (++used));
-    GridCopy((char *)a.out, mine, bytes, sizeof(T));
-    KernelEnd(d, ls, used);
+    const uint32_t nWin = WindowCount(a, a.count);
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const Window x = WindowAt(a, ls, w, a.count);
+        const uint64_t bytes = x.cnt * sizeof(T);
+        char *mine = CclHalf(d, me, x.half);
+        GridCopy(mine, (const char *)a.in + x.off * sizeof(T), bytes, sizeof(T));
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        {
+            char *mc = d->mcBase + d->bufOffset + (uint64_t)x.half * d->halfBytes;
+            const uint64_t nvec = bytes >> 4;
+            NvlsReduceOwned<T>(mc, nvec, n, me, a.useScale, a.scale, [&](uint64_t i, uint4 v) { MultimemSt16(mc + (i << 4), v); });
+            if ((bytes & 15) && me == 0 && blockIdx.x == 0 && threadIdx.x == 0) {
+                // the padding bytes of the last vector are whatever the half held on each rank: harmless, they are not copied out
+                uint4 v = Multimem<T>::LdReduceAdd(mc + (nvec << 4));
+                MultimemSt16(mc + (nvec << 4), a.useScale ? ScaleVec<T>(v, a.scale) : v);
+            }
+            // Multicast stores travel through the switch; the barrier's release by another thread of the CTA does not
+            // cover them, so every thread fences its own before the CTA signals.
+            __threadfence_system();
+        }
+        CrossRankBarrierMc(d, ls.epoch0 + (++used));
+        GridCopy((char *)a.out + x.off * sizeof(T), mine, bytes, sizeof(T));
+    }
+    KernelEnd(d, ls, used, nWin);
 }
 
-// -------------------------------------------------------------------------------- ReduceScatter
+// Column window [c0, c0 + cap) of a block of `cnt` elements: how many of its elements fall inside.
+__device__ __forceinline__ uint64_t InWindow(uint64_t cnt, uint64_t c0, uint64_t cap)
+{
+    const uint64_t hi = cnt < c0 + cap ? cnt : c0 + cap;
+    return hi > c0 ? hi - c0 : 0;
+}
 
-// Input: n blocks; block q has sendCounts[q] elements at sendDispls[q]; output recvCounts[me] elements.
-// Staging: n slots of sliceElems elements.
+// In-switch reduce-scatter: every rank parks (a window of) its n blocks in its half, then rank r pulls the sum of
+// block r through the switch straight into its output.  Blocks are whole 16-byte vectors (count * sizeof(T) % 16 == 0,
+// checked by the host).  With a registered input that has a multicast alias nothing is parked at all.
+// Replaces the in-fabric reduce-scatter programs of the reference (alg_ccu_context/.../reduce_scatter mesh1d).
+template <typename T>
+__device__ __forceinline__ void NvlsPullBlock(const char *mc, char *out, uint64_t vecs, int useScale, float scale)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    constexpr int kUnroll = 4;
+    for (; j + (kUnroll - 1) * stride < vecs; j += kUnroll * stride) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) v[u] = Multimem<T>::LdReduceAdd(mc + ((j + u * stride) << 4));
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) St16(out + ((j + u * stride) << 4), useScale ? ScaleVec<T>(v[u], scale) : v[u]);
+    }
+    for (; j < vecs; j += stride) {
+        uint4 v = Multimem<T>::LdReduceAdd(mc + (j << 4));
+        St16(out + (j << 4), useScale ? ScaleVec<T>(v, scale) : v);
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(512) KReduceScatterNvls(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    if (a.inMc) {
+        CrossRankBarrier(d, ls.epoch0 + (++used));           // every rank's input is final
+        NvlsPullBlock<T>((const char *)a.inMc + (uint64_t)me * a.count * sizeof(T), (char *)a.out, a.count * sizeof(T) >> 4, a.useScale, a.scale);
+        CrossRankBarrier(d, ls.epoch0 + (++used));           // nobody reuses its input while a peer still pulls from it
+        KernelEnd(d, ls, used, 0);
+        return;
+    }
+    const uint64_t cap = a.sliceElems;                       // elements of every block per window: n * cap * sizeof(T) <= half
+    const uint32_t nWin = (uint32_t)((a.count + cap - 1) / cap);
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const uint32_t half = (ls.half + w) & 1u;
+        const uint64_t c0 = (uint64_t)w * cap, len = InWindow(a.count, c0, cap), slotBytes = len * sizeof(T);
+        char *mine = CclHalf(d, me, half);
+        // slot q of my half = my contribution to block q; vector j of a slot belongs to grid thread j % (grid size) in both phases
+        for (int q = 0; q < n; ++q) GridCopy(mine + (uint64_t)q * slotBytes, (const char *)a.in + ((uint64_t)q * a.count + c0) * sizeof(T), slotBytes, sizeof(T));
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        const char *mc = d->mcBase + d->bufOffset + (uint64_t)half * d->halfBytes;
+        NvlsPullBlock<T>(mc + (uint64_t)me * slotBytes, (char *)a.out + c0 * sizeof(T), slotBytes >> 4, a.useScale, a.scale);
+        // this half is written again two windows (or two operators) from now; a barrier that every rank reaches only
+        // after leaving this loop lies in between
+    }
+    KernelEnd(d, ls, used, nWin);
+}
+
+// Input: n blocks; block q has sendCounts[q] elements at sendDispls[q]; output sendCounts[me] elements.
+// Staging: n slots of sliceElems elements; longer blocks travel in column windows of sliceElems (a.count = longest block).
+// With a registered input (a.inPeer set) the peers' blocks are read in place: no staging, one pass.
 template <typename T>
 __global__ void __launch_bounds__(512) KReduceScatter(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
@@ -297,16 +428,31 @@ __global__ void __launch_bounds__(512) KReduceScatter(const __grid_constant__ Co
     const LaunchState ls = KernelBegin(d);
     uint32_t used = MaybePreBarrier(d, a, ls);
     const int n = d->nRanks, me = d->rank;
-    const uint64_t slotBytes = a.sliceElems * sizeof(T);
-    for (int i = 1; i < n; ++i) {
-        int q = (me + i) % n;
-        GridCopy(CclHalf(d, q, ls.half) + (uint64_t)me * slotBytes, (const char *)a.in + a.sendDispls[q] * sizeof(T), a.sendCounts[q] * sizeof(T), sizeof(T));
+    if (a.inPeer[0]) {
+        CrossRankBarrier(d, ls.epoch0 + (++used));           // every rank's input is final
+        const char *src[HC_KERNEL_MAX_RANKS];
+        for (int r = 0; r < n; ++r) src[r] = (const char *)a.inPeer[r] + a.sendDispls[me] * sizeof(T);
+        ReduceAuto<T>(src, n, (char *)a.out, nullptr, a.sendCounts[me], a.op, a.useScale, a.scale);
+        CrossRankBarrier(d, ls.epoch0 + (++used));           // nobody reuses its input while a peer still reads it
+        KernelEnd(d, ls, used, 0);
+        return;
     }
-    CrossRankBarrier(d, ls.epoch0 + (++used));
-    const char *src[HC_KERNEL_MAX_RANKS];
-    for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + a.sendDispls[me] * sizeof(T) : CclHalf(d, me, ls.half) + (uint64_t)r * slotBytes;
-    ReduceAuto<T>(src, n, (char *)a.out, nullptr, a.sendCounts[me], a.op, a.useScale, a.scale);
-    KernelEnd(d, ls, used);
+    const uint64_t cap = a.sliceElems, slotBytes = cap * sizeof(T);
+    uint32_t nWin = (uint32_t)((a.count + cap - 1) / cap);
+    if (nWin == 0) nWin = 1;
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const uint32_t half = (ls.half + w) & 1u;
+        const uint64_t c0 = (uint64_t)w * cap;
+        for (int i = 1; i < n; ++i) {
+            int q = (me + i) % n;
+            GridCopy(CclHalf(d, q, half) + (uint64_t)me * slotBytes, (const char *)a.in + (a.sendDispls[q] + c0) * sizeof(T), InWindow(a.sendCounts[q], c0, cap) * sizeof(T), sizeof(T));
+        }
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        const char *src[HC_KERNEL_MAX_RANKS];
+        for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + (a.sendDispls[me] + c0) * sizeof(T) : CclHalf(d, me, half) + (uint64_t)r * slotBytes;
+        ReduceAuto<T>(src, n, (char *)a.out + c0 * sizeof(T), nullptr, InWindow(a.sendCounts[me], c0, cap), a.op, a.useScale, a.scale);
+    }
+    KernelEnd(d, ls, used, nWin);
 }
 
 // --------------------------------------------------------------------------------------- Reduce
@@ -346,8 +492,9 @@ __global__ void __launch_bounds__(512) KReduce(const __grid_constant__ CollArgs 
 
 // ------------------------------------------------------------------------- byte-moving kernels
 
-// AllGather(V): rank r contributes sendCounts[0] elements... expressed in bytes via elemSize:
-// my block has recvCounts[me] elements and lands at recvDispls[q] of everyone's output.
+// AllGather(V): my block has recvCounts[me] elements and lands at recvDispls[q] of everyone's output (counts in
+// elements of elemSize bytes).  Blocks longer than the staging (sliceElems elements) travel in column windows
+// (a.count = longest block).  With a registered input (a.inPeer set) the peers' blocks are pulled from where they are.
 __global__ void __launch_bounds__(512) KAllGather(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
     HC_ARGS;
@@ -355,14 +502,83 @@ __global__ void __launch_bounds__(512) KAllGather(const __grid_constant__ CollAr
     uint32_t used = MaybePreBarrier(d, a, ls);
     const int n = d->nRanks, me = d->rank;
     const uint64_t es = a.elemSize;
-    GridCopy(CclHalf(d, me, ls.half), (const char *)a.in, a.recvCounts[me] * es, a.elemSize);
-    CrossRankBarrier(d, ls.epoch0 + (++used));
-    GridCopy((char *)a.out + a.recvDispls[me] * es, (const char *)a.in, a.recvCounts[me] * es, a.elemSize);
-    for (int i = 1; i < n; ++i) {
-        int q = (me + i) % n;
-        GridCopy((char *)a.out + a.recvDispls[q] * es, CclHalf(d, q, ls.half), a.recvCounts[q] * es, a.elemSize);
+    if (a.inPeer[0]) {
+        CrossRankBarrier(d, ls.epoch0 + (++used));           // every rank's input is final
+        for (int i = 0; i < n; ++i) {
+            int q = (me + i) % n;
+            GridCopy((char *)a.out + a.recvDispls[q] * es, (const char *)a.inPeer[q], a.recvCounts[q] * es, a.elemSize);
+        }
+        CrossRankBarrier(d, ls.epoch0 + (++used));           // nobody reuses its input while a peer still reads it
+        KernelEnd(d, ls, used, 0);
+        return;
     }
-    KernelEnd(d, ls, used);
+    const uint64_t cap = a.sliceElems;
+    uint32_t nWin = (uint32_t)((a.count + cap - 1) / cap);
+    if (nWin == 0) nWin = 1;
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const uint32_t half = (ls.half + w) & 1u;
+        const uint64_t c0 = (uint64_t)w * cap;
+        const char *in = (const char *)a.in + c0 * es;
+        const uint64_t mineBytes = InWindow(a.recvCounts[me], c0, cap) * es;
+        GridCopy(CclHalf(d, me, half), in, mineBytes, a.elemSize);
+        CrossRankBarrier(d, ls.epoch0 + (++used));
+        GridCopy((char *)a.out + (a.recvDispls[me] + c0) * es, in, mineBytes, a.elemSize);
+        for (int i = 1; i < n; ++i) {
+            int q = (me + i) % n;
+            GridCopy((char *)a.out + (a.recvDispls[q] + c0) * es, CclHalf(d, q, half), InWindow(a.recvCounts[q], c0, cap) * es, a.elemSize);
+        }
+    }
+    KernelEnd(d, ls, used, nWin);
+}
+
+// All-gather through the switch: every rank stores its block ONCE to the multicast alias and the switch replicates it
+// into all ranks' memory, so a GPU sends 1/(n-1) of what the unicast form sends.  Equal blocks of whole 16-byte
+// vectors from a 16-byte aligned input (checked by the host).  With a registered output that has a multicast alias the
+// blocks land in the output itself; otherwise in the staging half (windows of sliceElems elements per rank) and a
+// local copy follows.  Replaces the in-fabric all-gather programs of the reference (alg_ccu_context/.../all_gather mesh1d).
+__device__ __forceinline__ void NvlsStoreBlock(char *mc, const char *src, uint64_t vecs)
+{
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x;
+    uint64_t j = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; j + 3 * stride < vecs; j += 4 * stride) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = Ld16(src + ((j + u * stride) << 4));
+#pragma unroll
+        for (int u = 0; u < 4; ++u) MultimemSt16(mc + ((j + u * stride) << 4), v[u]);
+    }
+    for (; j < vecs; j += stride) MultimemSt16(mc + (j << 4), Ld16(src + (j << 4)));
+    __threadfence_system();      // multicast stores are fenced by the thread that issued them
+}
+__global__ void __launch_bounds__(512) KAllGatherNvls(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t es = a.elemSize, blockBytes = a.count * es;
+    if (a.outMc) {
+        CrossRankBarrier(d, ls.epoch0 + (++used));           // every rank has left whatever last touched its output
+        NvlsStoreBlock((char *)a.outMc + (uint64_t)me * blockBytes, (const char *)a.in, blockBytes >> 4);
+        CrossRankBarrierMc(d, ls.epoch0 + (++used));
+        KernelEnd(d, ls, used, 0);
+        return;
+    }
+    const uint64_t cap = a.sliceElems;                       // elements per rank and window: n * cap * es <= half
+    const uint32_t nWin = (uint32_t)((a.count + cap - 1) / cap);
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const uint32_t half = (ls.half + w) & 1u;
+        const uint64_t c0 = (uint64_t)w * cap, slotBytes = InWindow(a.count, c0, cap) * es;
+        char *mc = d->mcBase + d->bufOffset + (uint64_t)half * d->halfBytes;
+        // Peers read this half (their copy-out of two windows / operators ago) only before a barrier that I have passed.
+        NvlsStoreBlock(mc + (uint64_t)me * slotBytes, (const char *)a.in + c0 * es, slotBytes >> 4);
+        CrossRankBarrierMc(d, ls.epoch0 + (++used));
+        for (int i = 0; i < n; ++i) {
+            int q = (me + i) % n;
+            GridCopy((char *)a.out + ((uint64_t)q * a.count + c0) * es, CclHalf(d, me, half) + (uint64_t)q * slotBytes, slotBytes, a.elemSize);
+        }
+    }
+    KernelEnd(d, ls, used, nWin);
 }
 
 // AlltoAll(V/VC): block for rank q has sendCounts[q] elements at sendDispls[q]; block from rank r has
@@ -934,6 +1150,13 @@ void *ReduceKernelFor(int kind, int dtype)
                 case HCCL_DATA_TYPE_BFP16: return (void *)KAllReduceNvls<__nv_bfloat16>;
                 default: return nullptr;
             }
+        case FK_REDUCE_SCATTER_NVLS:
+            switch (dtype) {
+                case HCCL_DATA_TYPE_FP32: return (void *)KReduceScatterNvls<float>;
+                case HCCL_DATA_TYPE_FP16: return (void *)KReduceScatterNvls<__half>;
+                case HCCL_DATA_TYPE_BFP16: return (void *)KReduceScatterNvls<__nv_bfloat16>;
+                default: return nullptr;
+            }
         default: return nullptr;
     }
 #undef HC_PICK
@@ -943,6 +1166,7 @@ void *KernelFor(int kind, int dtype)
 {
     switch (kind) {
         case FK_ALLGATHER: return (void *)KAllGather;
+        case FK_ALLGATHER_NVLS: return (void *)KAllGatherNvls;
         case FK_ALLTOALL: return (void *)KAlltoAll;
         case FK_BROADCAST_PUSH: return (void *)KBroadcastPush;
         case FK_BROADCAST_TWOSHOT: return (void *)KBroadcastTwoShot;
@@ -982,7 +1206,8 @@ void PreloadFastKernels()
 const char *FastKindName(int32_t k)
 {
     static const char *names[] = {"AllReduceOneShot", "AllReduceTwoShot", "AllReduceNvls", "ReduceScatter", "AllGather", "AlltoAll",
-                                  "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier", "SmallLL"};
+                                  "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier", "SmallLL",
+                                  "ReduceScatterNvls", "AllGatherNvls"};
     return (k >= 0 && k < FK_COUNT) ? names[k] : "?";
 }
 
@@ -990,7 +1215,7 @@ uint32_t FastKindBarriers(int32_t kind, int preBarrier)
 {
     uint32_t k = 1;
     switch (kind) {
-        case FK_ALLREDUCE_TWOSHOT: case FK_ALLREDUCE_NVLS: case FK_REDUCE: case FK_BROADCAST_NVLS: k = 2; break;
+        case FK_ALLREDUCE_TWOSHOT: case FK_ALLREDUCE_NVLS: case FK_REDUCE: case FK_BROADCAST_NVLS: k = 2; break;   // per window
         case FK_SEND: case FK_RECV: case FK_SMALL_LL: return 0;
         default: k = 1;
     }

@@ -30,6 +30,8 @@ enum FastKind : int32_t {
     FK_RECV,
     FK_BARRIER,
     FK_SMALL_LL,             // flag-in-data exchange for small all-reduce / all-gather / all-to-all / reduce-scatter
+    FK_REDUCE_SCATTER_NVLS,  // in-switch reduce-scatter (multimem.ld_reduce of the rank's own block)
+    FK_ALLGATHER_NVLS,       // all-gather by multicast stores
     FK_COUNT
 };
 const char *FastKindName(int32_t k);
@@ -54,6 +56,12 @@ struct CollArgs {
     uint64_t sendCounts[HC_KERNEL_MAX_RANKS], sendDispls[HC_KERNEL_MAX_RANKS];
     uint64_t recvCounts[HC_KERNEL_MAX_RANKS], recvDispls[HC_KERNEL_MAX_RANKS];
     uint64_t col0, col1;     // column window of this launch for chunked all-to-all style ops
+    uint64_t winElems;       // all-reduce: elements per in-kernel window (0 = the whole operand is one window)
+    // Registered (zero-copy) buffers: the operand's address in every rank's memory as this rank maps it, and the
+    // multicast alias of the operand; NULL when the buffer is not inside a registered window (or has no alias).
+    const void *inPeer[HC_KERNEL_MAX_RANKS];
+    const void *inMc;
+    void *outMc;
     // point-to-point bookkeeping (values before this operator)
     uint64_t p2pDataBase, p2pAckBase;
     uint64_t p2pOffset;      // offset of the point-to-point landing area in the heap

@@ -55,7 +55,8 @@ namespace {
 
 using namespace hcgemm;
 
-constexpr int kFusedThreads = 256;          // 6 GEMM warps + 2 communication warps
+constexpr int kFusedThreads = 256;          // reduce-scatter kernels: 6 GEMM warps (+ 2 idle)
+constexpr int kAgThreads = 384;             // all-gather kernels: 6 GEMM warps + 6 communication warps
 constexpr size_t kAgChunkBytes = 32 << 10;  // unit of the all-gather push: one warp moves one chunk
 // Flag words (u32) inside the HC_OFF_FUSED region of every rank's heap:
 //   all-gather:      block b (128 rows of the gathered matrix)           -> kAgFlagBase + b * 8            (own 32-byte sector)
@@ -90,14 +91,24 @@ __device__ __forceinline__ uint32_t *FusedFlag(const CommDev *d, int rank, int i
 
 // ------------------------------------------------------------------------ GEMM -> ReduceScatter
 
+// Tile order of a rank: partial tiles for the other ranks first, cycling through the destinations so that the stores
+// of the tiles in flight spread over all NVLink destinations at once (a single destination takes a fraction of a GPU's
+// outgoing bandwidth), then the rank's own tiles.  Inside a destination: column by column, its row blocks share B panels.
 struct RsOrder {
     int rank, nRanks, mbPer;
     __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
     {
         const int perDest = mbPer * g.tilesN;
-        const int i = t / perDest, local = t % perDest;
-        const int q = (rank + 1 + i) % nRanks;
-        *mb = q * mbPer + local % mbPer;      // column by column inside a destination: its row blocks share B panels
+        const int remote = (nRanks - 1) * perDest;
+        int q, local;
+        if (t < remote) {
+            q = (rank + 1 + t % (nRanks - 1)) % nRanks;
+            local = t / (nRanks - 1);
+        } else {
+            q = rank;
+            local = t - remote;
+        }
+        *mb = q * mbPer + local % mbPer;
         *nb = local / mbPer;
     }
 };
@@ -261,15 +272,23 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) Ge
 
 // -------------------------------------------------------------------------- AllGather -> GEMM
 
+// Tile order of a rank: tiles of its own rows first, then the other ranks' rows one row block at a time across ALL
+// sources (block i of every source, then block i + 1, ...), which is the order in which the push delivers them.
 struct AgOrder {
     int rank, nRanks, mbPer;
     __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
     {
         const int perSrc = mbPer * g.tilesN;
-        const int j = t / perSrc, local = t % perSrc;
-        const int src = (rank - j + nRanks) % nRanks;
-        *mb = src * mbPer + local % mbPer;
-        *nb = local / mbPer;
+        if (t < perSrc) {
+            *mb = rank * mbPer + t % mbPer;
+            *nb = t / mbPer;
+            return;
+        }
+        const int u = t - perSrc, perRow = (nRanks - 1) * g.tilesN;
+        const int i = u / perRow, rem = u % perRow;
+        const int src = (rank - 1 - rem % (nRanks - 1) + 2 * nRanks) % nRanks;
+        *mb = src * mbPer + i;
+        *nb = rem / (nRanks - 1);
     }
 };
 
@@ -317,15 +336,16 @@ struct AgPush {
         const size_t rowBytes = (size_t)K * sizeof(__nv_bfloat16);
         const size_t blockBytes = (size_t)kBlockM * rowBytes;                     // a multiple of 2 KB (K is a multiple of 8)
         const int chunksPerBlock = (int)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes);
-        const int perPeer = mbPer * chunksPerBlock;
-        const int items = (n - 1) * perPeer;
-        const bool clocked = phase && w == (int)blockIdx.x * 2;                  // the CTA's first communication warp
+        const int perBlock = (n - 1) * chunksPerBlock;
+        const int items = mbPer * perBlock;
+        const bool clocked = phase && (threadIdx.x >> 5) == 6;                   // the CTA's first communication warp
         const uint64_t tStart = clocked ? GlobalTimer() : 0;
         uint64_t tSignal = 0;
-        // peer-major order: everything for the nearest consumer first; consecutive warps take consecutive chunks
+        // block-major order: block 0 to every peer (nearest consumer first), then block 1, ...; consecutive warps take
+        // consecutive chunks, so the warps in flight write to all peers at once
         for (int it = w; it < items; it += warps) {
-            const int peerIdx = it / perPeer, rem = it % perPeer;
-            const int blk = rem / chunksPerBlock, ch = rem % chunksPerBlock;
+            const int blk = it / perBlock, rem = it % perBlock;
+            const int peerIdx = rem / chunksPerBlock, ch = rem % chunksPerBlock;
             const int peer = (me + 1 + peerIdx) % n;
             const size_t off = (size_t)blk * blockBytes + (size_t)ch * kAgChunkBytes;
             const size_t len = blockBytes - (size_t)ch * kAgChunkBytes < kAgChunkBytes ? blockBytes - (size_t)ch * kAgChunkBytes : kAgChunkBytes;
@@ -365,12 +385,13 @@ struct AgPush {
     }
     __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *) const
     {
-        Run((int)blockIdx.x * 2 + warpInRole, (int)gridDim.x * 2, lane);
+        const int perCta = (int)(blockDim.x >> 5) - 6;
+        Run((int)blockIdx.x * perCta + warpInRole, (int)gridDim.x * perCta, lane);
     }
 };
 
 template <int BN>
-__global__ void __launch_bounds__(kFusedThreads, 1) AllGatherGemmKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
+__global__ void __launch_bounds__(kAgThreads, 1) AllGatherGemmKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
@@ -386,7 +407,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) AllGatherGemmKernel(const __
 // CTA-pair variant: p.mbPer counts 128-row blocks (gate, push and flags keep that unit), the tile order works
 // on 256-row blocks.  BN: tile width (see Config2).
 template <int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) AllGatherGemmPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAgThreads, 1) AllGatherGemmPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
@@ -447,7 +468,7 @@ void SetSmemOnce(KernelT kernel, int smemBytes)
 }
 
 template <typename KernelT>
-HcclResult LaunchFused(Comm *c, KernelT kernel, int smemBytes, const FusedParams &hp, int tiles, int opId, void *stream)
+HcclResult LaunchFused(Comm *c, KernelT kernel, int threads, int smemBytes, const FusedParams &hp, int tiles, int opId, void *stream)
 {
     SetSmemOnce(kernel, smemBytes);
     if (c->emuSameDevice && c->nRanks > 1) {
@@ -457,14 +478,14 @@ HcclResult LaunchFused(Comm *c, KernelT kernel, int smemBytes, const FusedParams
                                     FusedParams unused;
                                     memset(&unused, 0, sizeof(unused));
                                     void *args[] = {(void *)&unused, (void *)&devTable};
-                                    cudaError_t e = cudaLaunchCooperativeKernel((void *)kernel, dim3(ctas, n, 1), dim3(kFusedThreads, 1, 1), args, smemBytes, (cudaStream_t)st);
+                                    cudaError_t e = cudaLaunchCooperativeKernel((void *)kernel, dim3(ctas, n, 1), dim3(threads, 1, 1), args, smemBytes, (cudaStream_t)st);
                                     if (e != cudaSuccess) { HCCL_ERROR("fused launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
                                     return HCCL_SUCCESS;
                                 });
     }
     // the parameter block travels as a kernel argument: no copy to order, nothing for the host to wait for
     const int ctas = std::min(GemmSmCount(), tiles);
-    kernel<<<dim3(ctas, 1, 1), kFusedThreads, smemBytes, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
+    kernel<<<dim3(ctas, 1, 1), threads, smemBytes, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("fused launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
@@ -478,7 +499,7 @@ bool PairKernelsEnabled()
 
 // CTA pairs of `kernel` (compile-time cluster of two) that can be resident at once; 0 when pairs cannot be scheduled.
 template <typename KernelT>
-int PairCapacityOf(KernelT kernel, int smemBytes)
+int PairCapacityOf(KernelT kernel, int threads, int smemBytes)
 {
     static std::map<void *, int> capacity;
     std::lock_guard<std::mutex> lk(g_ringMu);
@@ -487,7 +508,7 @@ int PairCapacityOf(KernelT kernel, int smemBytes)
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smemBytes);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * GemmSmCount(), 1, 1);
-        cfg.blockDim = dim3(kFusedThreads, 1, 1);
+        cfg.blockDim = dim3(threads, 1, 1);
         cfg.dynamicSmemBytes = smemBytes;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
@@ -503,12 +524,12 @@ int PairCapacityOf(KernelT kernel, int smemBytes)
 
 // Launches a CTA-pair kernel on as many pairs as can be resident at once.
 template <typename KernelT>
-HcclResult LaunchFusedPair(Comm *c, KernelT kernel, int smemBytes, const FusedParams &hp, int tiles, void *stream)
+HcclResult LaunchFusedPair(Comm *c, KernelT kernel, int threads, int smemBytes, const FusedParams &hp, int tiles, void *stream)
 {
-    const int cap = PairCapacityOf(kernel, smemBytes);
+    const int cap = PairCapacityOf(kernel, threads, smemBytes);
     if (cap <= 0) return HCCL_E_NOT_SUPPORT;
     const int pairs = std::min(cap, tiles);
-    kernel<<<dim3(2 * pairs, 1, 1), kFusedThreads, smemBytes, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
+    kernel<<<dim3(2 * pairs, 1, 1), threads, smemBytes, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("fused launch (CTA pairs) failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
@@ -573,7 +594,7 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     mode = ResolveMode(mode);
     const bool emu = c->emuSameDevice && c->nRanks > 1;
     const bool usePair = PairKernelsEnabled() && !emu && rowsPer % kPairM == 0 && N % 256 == 0 &&
-                         PairCapacityOf(GemmReduceScatterPairKernel, Config2<256, 6, true>::kSmemBytes) > 0;
+                         PairCapacityOf(GemmReduceScatterPairKernel, kFusedThreads, Config2<256, 6, true>::kSmemBytes) > 0;
     const int blockRows = usePair ? kPairM : kBlockM;
     const bool fits = (uint64_t)p * rowsPer * N * 2 <= c->halfBytes && (uint64_t)p * (rowsPer / blockRows) * (N / BN) <= (uint64_t)kRsMaxSrcTiles;
     if (mode == HCOMM_FUSED_MODE_SPLIT || (!fits && !emu && mode == HCOMM_FUSED_MODE_AUTO)) {
@@ -610,17 +631,17 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / blockRows; hp.rowsPer = rowsPer; hp.K = K;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
-    c->fusedLastCtas = usePair ? 2 * std::min(PairCapacityOf(GemmReduceScatterPairKernel, Config2<256, 6, true>::kSmemBytes), tiles) : 0;
-    if (usePair) return LaunchFusedPair(c, GemmReduceScatterPairKernel, Config2<256, 6, true>::kSmemBytes, hp, tiles, stream);
-    if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
-    return LaunchFused(c, GemmReduceScatterKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9002, stream);
+    c->fusedLastCtas = usePair ? 2 * std::min(PairCapacityOf(GemmReduceScatterPairKernel, kFusedThreads, Config2<256, 6, true>::kSmemBytes), tiles) : 0;
+    if (usePair) return LaunchFusedPair(c, GemmReduceScatterPairKernel, kFusedThreads, Config2<256, 6, true>::kSmemBytes, hp, tiles, stream);
+    if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, kFusedThreads, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
+    return LaunchFused(c, GemmReduceScatterKernel<128>, kFusedThreads, Config<128>::kSmemBytes, hp, tiles, 9002, stream);
 }
 
 namespace {
 template <int BN>
 HcclResult LaunchAgPair(Comm *c, const FusedParams &hp, int tiles, void *stream)
 {
-    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN>, Config2<BN, 7>::kSmemBytes, hp, tiles, stream);
+    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN>, kAgThreads, Config2<BN, 7>::kSmemBytes, hp, tiles, stream);
 }
 }  // namespace
 
@@ -647,9 +668,9 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     // the device (launch parity), so a map is built for each and the kernel picks.
     const bool emu = c->emuSameDevice && c->nRanks > 1;
     const bool usePair = PairKernelsEnabled() && !emu && Mshard % kPairM == 0 && N % 128 == 0 &&
-                         PairCapacityOf(AllGatherGemmPairKernel<256>, Config2<256, 7>::kSmemBytes) > 0;
+                         PairCapacityOf(AllGatherGemmPairKernel<256>, kAgThreads, Config2<256, 7>::kSmemBytes) > 0;
     int BN = N % 256 == 0 ? 256 : 128;
-    if (usePair) BN = PickPairTileWidth(M / kPairM, N, PairCapacityOf(AllGatherGemmPairKernel<256>, Config2<256, 7>::kSmemBytes));
+    if (usePair) BN = PickPairTileWidth(M / kPairM, N, PairCapacityOf(AllGatherGemmPairKernel<256>, kAgThreads, Config2<256, 7>::kSmemBytes));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, x, (uint64_t)Mshard, (uint64_t)K, (uint64_t)ldx, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2, c->CclBuffer(), (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2b, c->CclBuffer() + c->halfBytes, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
@@ -669,7 +690,7 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
         hp.xLocal = nullptr;
     }
     if (usePair) {
-        c->fusedLastCtas = 2 * std::min(PairCapacityOf(AllGatherGemmPairKernel<256>, Config2<256, 7>::kSmemBytes), tiles);
+        c->fusedLastCtas = 2 * std::min(PairCapacityOf(AllGatherGemmPairKernel<256>, kAgThreads, Config2<256, 7>::kSmemBytes), tiles);
         switch (BN) {
             case 256: return LaunchAgPair<256>(c, hp, tiles, stream);
             case 224: return LaunchAgPair<224>(c, hp, tiles, stream);
@@ -679,8 +700,8 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
         }
     }
     c->fusedLastCtas = 0;
-    if (BN == 256) return LaunchFused(c, AllGatherGemmKernel<256>, Config<256>::kSmemBytes, hp, tiles, 9003, stream);
-    return LaunchFused(c, AllGatherGemmKernel<128>, Config<128>::kSmemBytes, hp, tiles, 9004, stream);
+    if (BN == 256) return LaunchFused(c, AllGatherGemmKernel<256>, kAgThreads, Config<256>::kSmemBytes, hp, tiles, 9003, stream);
+    return LaunchFused(c, AllGatherGemmKernel<128>, kAgThreads, Config<128>::kSmemBytes, hp, tiles, 9004, stream);
 }
 
 // Clears the device-local scratch after a suspension (a call that was cut short leaves counts behind).

@@ -76,16 +76,20 @@ static __device__ __noinline__ void ReportTimeout(const CommDev *d, uint32_t pee
     __threadfence_system();
 }
 
-// Spins until *flag reaches `target` (wrap-safe), the abort word is raised, or the time budget ends.
+// Spins until *flag reaches `target` (wrap-safe), the abort word is raised, or the time budget ends.  The first polls
+// come back to back (a barrier between ranks that arrive together costs no more than before); a wait that lasts longer
+// sleeps between polls, so that a kernel waiting for a late peer leaves the memory system to the kernels beside it.
 __device__ __forceinline__ bool WaitFlagGe32(const CommDev *d, const uint32_t *flag, uint32_t target, uint32_t peer, uint32_t kind,
                                              uint32_t slot)
 {
     uint32_t seen = LdAcquireSys(flag);
     if ((int32_t)(seen - target) >= 0) return true;
     uint64_t start = GlobalTimerNs();
+    uint32_t ns = 0;
     for (uint32_t it = 1;; ++it) {
         seen = LdAcquireSys(flag);
         if ((int32_t)(seen - target) >= 0) return true;
+        if (it >= 128) { if (ns < 512) ns += 32; __nanosleep(ns); }
         if ((it & 63) == 0) {
             if (Aborted(d)) return false;
             if (GlobalTimerNs() - start > d->timeoutNs) { ReportTimeout(d, peer, kind, slot, target, seen); return false; }
@@ -123,9 +127,11 @@ __device__ __forceinline__ bool WaitFlagGe64(const CommDev *d, const uint64_t *f
     uint64_t seen = LdAcquireSys64(flag);
     if (seen >= target) return true;
     uint64_t start = GlobalTimerNs();
+    uint32_t ns = 0;
     for (uint32_t it = 1;; ++it) {
         seen = LdAcquireSys64(flag);
         if (seen >= target) return true;
+        if (it >= 128) { if (ns < 512) ns += 32; __nanosleep(ns); }
         if ((it & 63) == 0) {
             if (Aborted(d)) return false;
             if (GlobalTimerNs() - start > d->timeoutNs) { ReportTimeout(d, peer, kind, slot, target, seen); return false; }

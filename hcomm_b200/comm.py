@@ -289,9 +289,49 @@ class Communicator:
     def resume(self):
         check(self._lib.HcclCommResume(self._h), "HcclCommResume")
 
+    # ---------------------------------------------------------------- registered (symmetric) memory
+    def alloc_registered(self, shape, dtype):
+        """Collective: allocates exportable device memory of the given torch shape / dtype on every rank, registers it as a
+        symmetric window and returns it as a torch tensor.  Operators whose buffers lie inside such a window read and
+        write the ranks' copies in place (zero-copy) instead of staging through the CCL buffer.  Every rank must pass the
+        same size.  The memory lives until the communicator is destroyed (or :meth:`free_registered`)."""
+        import torch
+        n = 1
+        for s_ in (shape if isinstance(shape, (tuple, list)) else (shape,)):
+            n *= int(s_)
+        nbytes = max(16, n * torch.tensor([], dtype=dtype).element_size())
+        ptr = ctypes.c_void_p()
+        check(self._lib.HcommMemAlloc(ctypes.byref(ptr), ctypes.c_size_t(nbytes)), "HcommMemAlloc")
+        win = ctypes.c_void_p()
+        rc = self._lib.HcclCommSymWinRegister(self._h, ptr, ctypes.c_uint64(nbytes), ctypes.byref(win), 0)
+        if rc != 0:
+            self._lib.HcommMemFree(ptr)
+            check(rc, "HcclCommSymWinRegister")
+        typestr = {1: "|u1", 2: "<u2", 4: "<u4", 8: "<u8"}[torch.tensor([], dtype=dtype).element_size()]
+
+        class _View:
+            pass
+        v = _View()
+        v.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr.value, False), "version": 3, "strides": None}
+        t = torch.as_tensor(v, device=torch.device("cuda", torch.cuda.current_device())).view(dtype).view(shape)
+        if not hasattr(self, "_registered"):
+            self._registered = {}
+        self._registered[t.data_ptr()] = (ptr, win)
+        return t
+
+    def free_registered(self, tensor):
+        """Collective: deregisters and frees a tensor obtained from :meth:`alloc_registered`."""
+        ptr, win = self._registered.pop(tensor.data_ptr())
+        check(self._lib.HcclCommSymWinDeregister(win), "HcclCommSymWinDeregister")
+        check(self._lib.HcommMemFree(ptr), "HcommMemFree")
+
     def destroy(self):
         if self._h:
+            regs = getattr(self, "_registered", {})
             check(self._lib.HcclCommDestroy(self._h), "HcclCommDestroy")
+            for ptr, _ in regs.values():
+                self._lib.HcommMemFree(ptr)
+            regs.clear()
             self._h = ctypes.c_void_p()
 
 

@@ -28,21 +28,40 @@ def bus_factor(op: str, n: int) -> float:
     return 2.0 * (n - 1) / n if op == "allreduce" else (n - 1) / n
 
 
-def run_sweep(comm: Communicator, ops, sizes, dtype, iters, warmup, with_nccl=True, algo_label="auto"):
+def run_sweep(comm: Communicator, ops, sizes, dtype, iters, warmup, with_nccl=True, algo_label="auto", registered=False):
+    """registered=True: operands live in symmetric windows (``Communicator.alloc_registered``), which lets the kernels work
+    on the ranks' buffers in place."""
     rank, n = comm.rank, comm.size
     results = []
+    reg_pool = {}
+
+    def new(count, like=None, key=""):
+        if not registered:
+            return torch.empty(count, device="cuda", dtype=dtype)
+        # windows are collective and live as long as the communicator: one per (role, size), reused by later rows
+        if (key, count) not in reg_pool:
+            reg_pool[(key, count)] = comm.alloc_registered((count,), dtype)
+        return reg_pool[(key, count)]
+
     for op in ops:
         for nbytes in sizes:
             esz = torch.tensor([], dtype=dtype).element_size()
             count = max(n, nbytes // esz)
             count = (count + n - 1) // n * n
-            x = torch.randn(count, device="cuda", dtype=torch.float32).to(dtype)
+            g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+            if count <= (1 << 28):
+                x0 = torch.randn(count, device="cuda", dtype=torch.float32, generator=g).to(dtype)
+            else:       # N(0,1) values without a 4-byte-per-element temporary for the largest operands
+                x0 = torch.randn(1 << 24, device="cuda", dtype=torch.float32, generator=g).to(dtype).repeat((count + (1 << 24) - 1) >> 24)[:count]
+            x = new(count, key="x")
+            x.copy_(x0)
+            del x0
             if op == "allreduce":
-                y = torch.empty_like(x)
+                y = new(count, key="y")
                 ours = lambda: comm.all_reduce(x, y)
                 nccl = lambda: dist.all_reduce(y)
             elif op == "allgather":
-                xi, y = x[:count // n].contiguous(), torch.empty_like(x)
+                xi, y = x[:count // n], new(count, key="y")
                 ours = lambda: comm.all_gather(xi, y)
                 nccl = lambda: dist.all_gather_into_tensor(y, xi)
             elif op == "reducescatter":
@@ -57,7 +76,7 @@ def run_sweep(comm: Communicator, ops, sizes, dtype, iters, warmup, with_nccl=Tr
                 raise ValueError(op)
             flush = count * esz < (160 << 20)
             it = iters if count * esz <= (256 << 20) else max(3, iters // 3)
-            row = {"op": op, "bytes": count * esz, "dtype": str(dtype).replace("torch.", ""), "n": n, "algo": algo_label}
+            row = {"op": op, "bytes": count * esz, "dtype": str(dtype).replace("torch.", ""), "n": n, "algo": algo_label, "registered": bool(registered)}
             for name, fn in (("ours", ours), ("nccl", nccl)):
                 if name == "nccl" and not with_nccl:
                     continue
@@ -87,6 +106,7 @@ def main():
     ap.add_argument("--buffer-mb", type=int, default=512)
     ap.add_argument("--algo", default=None)
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--registered", action="store_true", help="operands in registered symmetric windows (zero-copy kernels)")
     ap.add_argument("--out", default=None)
     a = ap.parse_args()
     rank, world, local = env_rank()
@@ -106,7 +126,8 @@ def main():
         sizes.append(s)
         s *= a.factor
     dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[a.dtype]
-    res = run_sweep(comm, a.ops.split(","), sizes, dtype, a.iters, a.warmup, with_nccl=(world > 1 and not a.no_nccl), algo_label=a.algo or "auto")
+    res = run_sweep(comm, a.ops.split(","), sizes, dtype, a.iters, a.warmup, with_nccl=(world > 1 and not a.no_nccl), algo_label=a.algo or "auto",
+                    registered=a.registered)
     if rank == 0 and a.out:
         with open(a.out, "w") as f:
             json.dump(res, f, indent=1)

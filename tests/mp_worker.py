@@ -215,6 +215,55 @@ def main():
             g = np.zeros(7 * world, np.int32)
             comm.all_gather(np.full(7, rank, np.int32), g)
             assert np.array_equal(g, np.repeat(np.arange(world), 7))
+    elif scenario == "collectives_big":
+        # Operands larger than the staging (in-kernel windows), the in-switch (NVLS) kernels forced with many CTAs on counts
+        # that do not divide evenly, and zero-copy on registered buffers - each against values computed locally.
+        import torch
+        nvls_ok = world > 1 and os.environ.get("HCCL_NVLS_ENABLE", "1") != "0"
+
+        def pattern(count, r, dtype):
+            return (torch.arange(count, device="cuda", dtype=torch.float32) % 13 + r).to(dtype)
+
+        def check_all(c, tag, dtype, count, registered=False):
+            want_ar = sum(pattern(count, r, torch.float32) for r in range(world)).to(dtype).float()
+            per = count // world
+            if registered:
+                x, y = c.alloc_registered((count,), dtype), c.alloc_registered((count,), dtype)
+                x.copy_(pattern(count, rank, dtype))
+            else:
+                x, y = pattern(count, rank, dtype), torch.empty(count, device="cuda", dtype=dtype)
+            y.zero_()
+            c.all_reduce(x, y)
+            torch.cuda.synchronize()
+            assert torch.allclose(y.float(), want_ar, rtol=2e-2, atol=1e-3), (tag, "all_reduce", dtype, count)
+            if per * world == count and per > 0:
+                rs = torch.zeros(per, device="cuda", dtype=dtype)
+                c.reduce_scatter(x, rs)
+                torch.cuda.synchronize()
+                assert torch.allclose(rs.float(), want_ar[rank * per:(rank + 1) * per], rtol=2e-2, atol=1e-3), (tag, "reduce_scatter", dtype, count)
+                y.zero_()
+                c.all_gather(x[:per], y)
+                torch.cuda.synchronize()
+                want_ag = torch.cat([pattern(count, r, dtype)[:per] for r in range(world)])
+                assert torch.equal(y, want_ag), (tag, "all_gather", dtype, count)
+            assert c.async_error() == 0, (tag, dtype, count)
+            stage(f"{tag}: {dtype} x {count} ok")
+
+        # 16 MB of CCL buffer: these operands take several windows per launch
+        for dtype, count in ((torch.float32, 9_000_000 * world // world // world * world), (torch.bfloat16, 24 * 1024 * 1024 + 16 * world)):
+            check_all(comm, "windows", dtype, count // world * world)
+        check_all(comm, "ragged", torch.float32, 5_000_011)
+        if nvls_ok:
+            forced = comm.split(list(range(world)), sub_id=7, buffer_mb=int(os.environ.get("HCOMM_TEST_BUFFER_MB", "16")),
+                                algo="allreduce=level0:nvls/allgather=level0:nvls/reducescatter=level0:nvls")
+            # 144 CTAs x 512 threads = 73728 vectors per sweep; these counts leave partial sweeps on every rank
+            for dtype, count in ((torch.float32, (73728 * 4 * 3 + 40) * world), (torch.bfloat16, (73728 * 8 * 2 + 4104) * world), (torch.float32, 20_000_000 // world * world)):
+                check_all(forced, "nvls forced", dtype, count)
+            check_all(forced, "nvls forced, ragged", torch.bfloat16, 3_000_001)
+            forced.destroy()
+        for dtype, count in ((torch.float32, 1 << 20), (torch.bfloat16, (6 << 20) + 8 * world), (torch.float32, 12_000_000 // world * world)):
+            check_all(comm, "registered", dtype, count, registered=True)
+        stage("collectives_big ok")
     elif scenario == "fused":
         import torch
         from hcomm_b200.ops.fused import all_gather_gemm, gemm_reduce_scatter

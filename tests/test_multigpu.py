@@ -15,6 +15,14 @@ def test_collectives_across_gpus(world):
     assert codes == [0] * world, "\n".join(outs)
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_windows_nvls_and_registered_buffers_across_gpus(world):
+    if cuda_device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    codes, outs = launch("collectives_big", world, {"HCOMM_TEST_BUFFER_MB": "16", "HCCL_EXEC_TIMEOUT": "30"}, timeout=300)
+    assert codes == [0] * world, "\n".join(outs)
+
+
 def test_peer_exit_between_steps_is_seen_on_the_host():
     if cuda_device_count() < 2:
         pytest.skip("needs 2 GPUs")
