@@ -159,6 +159,14 @@ bool TrySmallLL(Comm *c, const OpDesc &d, const Selection &sel, HcclResult *res)
 // activated HcclCommSetMemoryRange), kernels read the peers' copies of it in place instead of staging through the CCL
 // buffer - what the reference's zero-copy address manager and graph-mode kernels are for
 // (communicator/impl/zero_copy/zero_copy_address_mgr.cc, aiv_all_reduce_910b_bigdata_graph.h).  HCCL_ZERO_COPY=0 turns it off.
+// HCCL_WINDOWS_IN_KERNEL=0: operands beyond the staging are cut into one launch per window by the host instead of
+// being walked inside one launch (kept for comparison).
+bool WindowsInKernel()
+{
+    static const bool on = [] { const char *e = getenv("HCCL_WINDOWS_IN_KERNEL"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 bool ZeroCopyEnabled()
 {
     static const bool on = [] { const char *e = getenv("HCCL_ZERO_COPY"); return !(e && e[0] == '0'); }();
@@ -200,7 +208,8 @@ HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
     a.in = d.in; a.out = d.out; a.count = d.count;
     // in-switch reduction straight from the registered input into the registered output: no staging, any size
     const bool nvlsTypes = d.op == HCCL_REDUCE_SUM && (d.dtype == HCCL_DATA_TYPE_FP32 || d.dtype == HCCL_DATA_TYPE_FP16 || d.dtype == HCCL_DATA_TYPE_BFP16);
-    if (c->mcBase && nvlsTypes && c->cfg.deterministic == 0 && sel.reason != "forced by configuration" && d.count * esz >= 64 * 1024 &&
+    // (up to 4 GPUs the mesh kernels measured faster than in-switch reduction, registered or not)
+    if (c->mcBase && n > 4 && nvlsTypes && c->cfg.deterministic == 0 && sel.reason != "forced by configuration" && d.count * esz >= 64 * 1024 &&
         RegisteredInput(c, d.in, d.count * esz, a, true)) {
         a.outMc = RegisteredOutputMc(c, d.out, d.count * esz);
         if (a.outMc) return Launch(c, FK_ALLREDUCE_NVLS, a, PickCtas(c, sel, d.count * esz), d.stream);
@@ -212,6 +221,18 @@ HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
     else { a.winElems = AlignDownElems(c->halfBytes / esz, esz); a.sliceElems = 0; }
     const uint64_t perWin = a.winElems ? std::min<uint64_t>(d.count, a.winElems) : d.count;
     const uint64_t perRank = kind == FK_ALLREDUCE_ONESHOT ? perWin * esz : (d.count > perWin ? perWin * esz : perWin * esz / n * 2);
+    if (a.winElems && d.count > a.winElems && !WindowsInKernel()) {
+        const uint64_t W = a.winElems;
+        a.winElems = 0;
+        for (uint64_t off = 0; off < d.count; off += W) {
+            const uint64_t cnt = std::min(W, d.count - off);
+            a.in = (const char *)d.in + off * esz; a.out = (char *)d.out + off * esz; a.count = cnt;
+            a.sliceElems = kind == FK_ALLREDUCE_TWOSHOT ? AlignedSliceCount(cnt, n, esz) : 0;
+            CHK_RET(Launch(c, kind, a, PickCtas(c, sel, perRank), d.stream));
+        }
+        return HCCL_SUCCESS;
+    }
+    if (kind == FK_ALLREDUCE_TWOSHOT && d.count > a.winElems) kind = FK_ALLREDUCE_TWOSHOT_WIN;
     return Launch(c, kind, a, PickCtas(c, sel, perRank), d.stream);
 }
 
@@ -257,11 +278,25 @@ HcclResult FastReduceScatter(Comm *c, const OpDesc &d, const Selection &sel)
         // registered input: pull the peers' blocks in place (through the switch when the window has a multicast alias)
         if (a.inMc && nvls) return Launch(c, FK_REDUCE_SCATTER_NVLS, a, PickCtas(c, sel, moved), d.stream);
         a.inMc = nullptr;
-        return Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, moved), d.stream);
+        return Launch(c, FK_REDUCE_SCATTER_INPLACE, a, PickCtas(c, sel, moved), d.stream);
     }
     ClearRegistered(a);
     if (nvls) return Launch(c, FK_REDUCE_SCATTER_NVLS, a, PickCtas(c, sel, moved), d.stream);
-    return Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, moved), d.stream);
+    if (maxCnt > cap && !WindowsInKernel()) {
+        std::vector<uint64_t> cnt(a.sendCounts, a.sendCounts + n), dsp(a.sendDispls, a.sendDispls + n);
+        for (uint64_t c0 = 0; c0 < maxCnt; c0 += cap) {
+            for (uint32_t q = 0; q < n; ++q) {
+                const uint64_t hi = std::min(cnt[q], c0 + cap);
+                a.sendCounts[q] = hi > c0 ? hi - c0 : 0;
+                a.sendDispls[q] = dsp[q] + c0;
+            }
+            a.out = (char *)d.out + c0 * esz;
+            a.count = std::min(cap, maxCnt - c0);
+            CHK_RET(Launch(c, FK_REDUCE_SCATTER, a, PickCtas(c, sel, moved), d.stream));
+        }
+        return HCCL_SUCCESS;
+    }
+    return Launch(c, maxCnt > cap ? FK_REDUCE_SCATTER_WIN : FK_REDUCE_SCATTER, a, PickCtas(c, sel, moved), d.stream);
 }
 
 HcclResult FastAllGather(Comm *c, const OpDesc &d, const Selection &sel)

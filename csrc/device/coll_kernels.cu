@@ -129,8 +129,10 @@ __device__ __forceinline__ void ReduceLoop(const char *const *src, int n, char *
         }
     }
 }
+// Not inlined: a kernel calls it from several places (per window, staged and zero-copy forms) and the four loop
+// variants inside would otherwise be replicated at each call site, which cost the callers half their registers.
 template <typename T>
-__device__ __forceinline__ void ReduceFanOut(const char *const *src, int n, char *const *dst, int nd, uint64_t nElems, int op, int useScale, float scale)
+static __device__ __noinline__ void ReduceFanOut(const char *const *src, int n, char *const *dst, int nd, uint64_t nElems, int op, int useScale, float scale)
 {
     uintptr_t bits = 0;
     for (int r = 0; r < n; ++r) bits |= (uintptr_t)src[r];
@@ -224,45 +226,72 @@ __global__ void __launch_bounds__(512) KAllReduceOneShot(const __grid_constant__
 // Staging: 2n slots of S elements: [0,n) partial slices arriving from the peers, [n,2n) reduced slices
 // arriving from their owners.  A window holds at most n * S elements.  NVLink carries data in the first two phases
 // (partials out, then reduced slices out while they are being computed); the last phase is a local copy.
+// One window of the two-shot all-reduce.  Out of line and fed with values only (no reference to the argument block):
+// inlined into the window loop, the body's loads of the argument block were hoisted and kept alive across the loop,
+// which cost the kernel its registers (spills in the copy and reduction loops).
+template <typename T>
+__device__ __forceinline__ void AllReduceTwoShotBody(const CommDev *d, const char *in, char *out, uint32_t half, uint64_t cnt, uint64_t S, uint32_t epoch,
+                                                     int op, int useScale, float scale)
+{
+    const int n = d->nRanks, me = d->rank;
+    const uint64_t slotBytes = S * sizeof(T);
+    uint64_t beg, len;
+    // scatter: my copy of slice q goes to slot `me` of rank q
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        SliceRange(cnt, S, q, &beg, &len);
+        GridCopy(CclHalf(d, q, half) + (uint64_t)me * slotBytes, in + beg * sizeof(T), len * sizeof(T), sizeof(T));
+    }
+    CrossRankBarrier(d, epoch);
+    // reduce my slice in rank order; the result goes to my output and to slot n+me of every peer
+    SliceRange(cnt, S, me, &beg, &len);
+    {
+        const char *src[HC_KERNEL_MAX_RANKS];
+        char *dst[HC_KERNEL_MAX_RANKS];
+        for (int r = 0; r < n; ++r) src[r] = (r == me) ? in + beg * sizeof(T) : CclHalf(d, me, half) + (uint64_t)r * slotBytes;
+        int nd = 0;
+        dst[nd++] = out + beg * sizeof(T);
+        for (int i = 1; i < n; ++i) dst[nd++] = CclHalf(d, (me + i) % n, half) + (uint64_t)(n + me) * slotBytes;
+        ReduceFanOut<T>(src, n, dst, nd, len, op, useScale, scale);
+    }
+    CrossRankBarrier(d, epoch + 1);
+    // the other slices have landed in my staging: copy them out
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        SliceRange(cnt, S, q, &beg, &len);
+        GridCopy(out + beg * sizeof(T), CclHalf(d, me, half) + (uint64_t)(n + q) * slotBytes, len * sizeof(T), sizeof(T));
+    }
+}
+template <typename T>
+static __device__ __noinline__ void AllReduceTwoShotWindow(const CommDev *d, const char *in, char *out, uint32_t half, uint64_t cnt, uint64_t S, uint32_t epoch,
+                                                           int op, int useScale, float scale)
+{
+    AllReduceTwoShotBody<T>(d, in, out, half, cnt, S, epoch, op, useScale, scale);
+}
+// The operand fits one window (the common case): the body is inlined, nothing is kept across a loop.
 template <typename T>
 __global__ void __launch_bounds__(512) KAllReduceTwoShot(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
     HC_ARGS;
     const LaunchState ls = KernelBegin(d);
     uint32_t used = MaybePreBarrier(d, a, ls);
-    const int n = d->nRanks, me = d->rank;
+    AllReduceTwoShotBody<T>(d, (const char *)a.in, (char *)a.out, ls.half, a.count, a.sliceElems, ls.epoch0 + used + 1, a.op, a.useScale, a.scale);
+    KernelEnd(d, ls, used + 2);
+}
+// Operands beyond one window: the same body, called once per window.
+template <typename T>
+__global__ void __launch_bounds__(512, 1) KAllReduceTwoShotWin(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
     const uint32_t nWin = WindowCount(a, a.count);
     for (uint32_t w = 0; w < nWin; ++w) {
         const Window x = WindowAt(a, ls, w, a.count);
-        const char *in = (const char *)a.in + x.off * sizeof(T);
-        char *out = (char *)a.out + x.off * sizeof(T);
-        const uint64_t S = nWin == 1 && a.sliceElems ? a.sliceElems : SliceElems(x.cnt, n, sizeof(T)), slotBytes = S * sizeof(T);
-        uint64_t beg, len;
-        // scatter: my copy of slice q goes to slot `me` of rank q
-        for (int i = 1; i < n; ++i) {
-            int q = (me + i) % n;
-            SliceRange(x.cnt, S, q, &beg, &len);
-            GridCopy(CclHalf(d, q, x.half) + (uint64_t)me * slotBytes, in + beg * sizeof(T), len * sizeof(T), sizeof(T));
-        }
-        CrossRankBarrier(d, ls.epoch0 + (++used));
-        // reduce my slice in rank order; the result goes to my output and to slot n+me of every peer
-        SliceRange(x.cnt, S, me, &beg, &len);
-        {
-            const char *src[HC_KERNEL_MAX_RANKS];
-            char *dst[HC_KERNEL_MAX_RANKS];
-            for (int r = 0; r < n; ++r) src[r] = (r == me) ? in + beg * sizeof(T) : CclHalf(d, me, x.half) + (uint64_t)r * slotBytes;
-            int nd = 0;
-            dst[nd++] = out + beg * sizeof(T);
-            for (int i = 1; i < n; ++i) dst[nd++] = CclHalf(d, (me + i) % n, x.half) + (uint64_t)(n + me) * slotBytes;
-            ReduceFanOut<T>(src, n, dst, nd, len, a.op, a.useScale, a.scale);
-        }
-        CrossRankBarrier(d, ls.epoch0 + (++used));
-        // the other slices have landed in my staging: copy them out
-        for (int i = 1; i < n; ++i) {
-            int q = (me + i) % n;
-            SliceRange(x.cnt, S, q, &beg, &len);
-            GridCopy(out + beg * sizeof(T), CclHalf(d, me, x.half) + (uint64_t)(n + q) * slotBytes, len * sizeof(T), sizeof(T));
-        }
+        const uint64_t S = nWin == 1 && a.sliceElems ? a.sliceElems : SliceElems(x.cnt, d->nRanks, sizeof(T));
+        AllReduceTwoShotWindow<T>(d, (const char *)a.in + x.off * sizeof(T), (char *)a.out + x.off * sizeof(T), x.half, x.cnt, S, ls.epoch0 + used + 1, a.op,
+                                  a.useScale, a.scale);
+        used += 2;
     }
     KernelEnd(d, ls, used, nWin);
 }
@@ -420,37 +449,76 @@ __global__ void __launch_bounds__(512) KReduceScatterNvls(const __grid_constant_
 
 // Input: n blocks; block q has sendCounts[q] elements at sendDispls[q]; output sendCounts[me] elements.
 // Staging: n slots of sliceElems elements; longer blocks travel in column windows of sliceElems (a.count = longest block).
-// With a registered input (a.inPeer set) the peers' blocks are read in place: no staging, one pass.
+// One column window of the reduce-scatter: block q of this rank's input starts at in + dspBytes[q] and has lenBytes[q]
+// bytes inside the window.  Out of line and fed with values only, like AllReduceTwoShotWindow.
+template <typename T>
+__device__ __forceinline__ void ReduceScatterBody(const CommDev *d, const char *in, char *out, const uint64_t *dspBytes, const uint64_t *lenBytes, uint32_t half,
+                                                  uint64_t slotBytes, uint32_t epoch, int op, int useScale, float scale)
+{
+    const int n = d->nRanks, me = d->rank;
+    for (int i = 1; i < n; ++i) {
+        int q = (me + i) % n;
+        GridCopy(CclHalf(d, q, half) + (uint64_t)me * slotBytes, in + dspBytes[q], lenBytes[q], sizeof(T));
+    }
+    CrossRankBarrier(d, epoch);
+    const char *src[HC_KERNEL_MAX_RANKS];
+    for (int r = 0; r < n; ++r) src[r] = (r == me) ? in + dspBytes[me] : CclHalf(d, me, half) + (uint64_t)r * slotBytes;
+    ReduceAuto<T>(src, n, out, nullptr, lenBytes[me] / sizeof(T), op, useScale, scale);
+}
+template <typename T>
+static __device__ __noinline__ void ReduceScatterWindow(const CommDev *d, const char *in, char *out, const uint64_t *dspBytes, const uint64_t *lenBytes, uint32_t half,
+                                                        uint64_t slotBytes, uint32_t epoch, int op, int useScale, float scale)
+{
+    ReduceScatterBody<T>(d, in, out, dspBytes, lenBytes, half, slotBytes, epoch, op, useScale, scale);
+}
+// Every block fits a staging slot (the common case): one window, body inlined.
 template <typename T>
 __global__ void __launch_bounds__(512) KReduceScatter(const __grid_constant__ CollArgs byval, const CollArgs *emu)
 {
     HC_ARGS;
     const LaunchState ls = KernelBegin(d);
     uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks;
+    uint64_t dsp[HC_KERNEL_MAX_RANKS], len[HC_KERNEL_MAX_RANKS];
+    for (int q = 0; q < n; ++q) { dsp[q] = a.sendDispls[q] * sizeof(T); len[q] = a.sendCounts[q] * sizeof(T); }
+    ReduceScatterBody<T>(d, (const char *)a.in, (char *)a.out, dsp, len, ls.half, a.sliceElems * sizeof(T), ls.epoch0 + (++used), a.op, a.useScale, a.scale);
+    KernelEnd(d, ls, used);
+}
+// Registered input: the peers' blocks are read where they are - no staging, one pass.
+template <typename T>
+__global__ void __launch_bounds__(512) KReduceScatterInPlace(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
     const int n = d->nRanks, me = d->rank;
-    if (a.inPeer[0]) {
-        CrossRankBarrier(d, ls.epoch0 + (++used));           // every rank's input is final
-        const char *src[HC_KERNEL_MAX_RANKS];
-        for (int r = 0; r < n; ++r) src[r] = (const char *)a.inPeer[r] + a.sendDispls[me] * sizeof(T);
-        ReduceAuto<T>(src, n, (char *)a.out, nullptr, a.sendCounts[me], a.op, a.useScale, a.scale);
-        CrossRankBarrier(d, ls.epoch0 + (++used));           // nobody reuses its input while a peer still reads it
-        KernelEnd(d, ls, used, 0);
-        return;
-    }
-    const uint64_t cap = a.sliceElems, slotBytes = cap * sizeof(T);
+    CrossRankBarrier(d, ls.epoch0 + (++used));           // every rank's input is final
+    const char *src[HC_KERNEL_MAX_RANKS];
+    for (int r = 0; r < n; ++r) src[r] = (const char *)a.inPeer[r] + a.sendDispls[me] * sizeof(T);
+    ReduceAuto<T>(src, n, (char *)a.out, nullptr, a.sendCounts[me], a.op, a.useScale, a.scale);
+    CrossRankBarrier(d, ls.epoch0 + (++used));           // nobody reuses its input while a peer still reads it
+    KernelEnd(d, ls, used, 0);
+}
+// Blocks longer than a staging slot: column windows of sliceElems, the body called once per window.
+template <typename T>
+__global__ void __launch_bounds__(512, 1) KReduceScatterWin(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks;
+    const uint64_t cap = a.sliceElems;
     uint32_t nWin = (uint32_t)((a.count + cap - 1) / cap);
     if (nWin == 0) nWin = 1;
     for (uint32_t w = 0; w < nWin; ++w) {
-        const uint32_t half = (ls.half + w) & 1u;
         const uint64_t c0 = (uint64_t)w * cap;
-        for (int i = 1; i < n; ++i) {
-            int q = (me + i) % n;
-            GridCopy(CclHalf(d, q, half) + (uint64_t)me * slotBytes, (const char *)a.in + (a.sendDispls[q] + c0) * sizeof(T), InWindow(a.sendCounts[q], c0, cap) * sizeof(T), sizeof(T));
+        uint64_t dsp[HC_KERNEL_MAX_RANKS], len[HC_KERNEL_MAX_RANKS];
+        for (int q = 0; q < n; ++q) {
+            dsp[q] = (a.sendDispls[q] + c0) * sizeof(T);
+            len[q] = InWindow(a.sendCounts[q], c0, cap) * sizeof(T);
         }
-        CrossRankBarrier(d, ls.epoch0 + (++used));
-        const char *src[HC_KERNEL_MAX_RANKS];
-        for (int r = 0; r < n; ++r) src[r] = (r == me) ? (const char *)a.in + (a.sendDispls[me] + c0) * sizeof(T) : CclHalf(d, me, half) + (uint64_t)r * slotBytes;
-        ReduceAuto<T>(src, n, (char *)a.out + c0 * sizeof(T), nullptr, InWindow(a.sendCounts[me], c0, cap), a.op, a.useScale, a.scale);
+        ReduceScatterWindow<T>(d, (const char *)a.in, (char *)a.out + c0 * sizeof(T), dsp, len, (ls.half + w) & 1u, cap * sizeof(T), ls.epoch0 + (++used), a.op,
+                               a.useScale, a.scale);
     }
     KernelEnd(d, ls, used, nWin);
 }
@@ -1141,6 +1209,9 @@ void *ReduceKernelFor(int kind, int dtype)
         case FK_ALLREDUCE_ONESHOT: HC_PICK(KAllReduceOneShot)
         case FK_ALLREDUCE_TWOSHOT: HC_PICK(KAllReduceTwoShot)
         case FK_REDUCE_SCATTER: HC_PICK(KReduceScatter)
+        case FK_ALLREDUCE_TWOSHOT_WIN: HC_PICK(KAllReduceTwoShotWin)
+        case FK_REDUCE_SCATTER_WIN: HC_PICK(KReduceScatterWin)
+        case FK_REDUCE_SCATTER_INPLACE: HC_PICK(KReduceScatterInPlace)
         case FK_REDUCE: HC_PICK(KReduce)
         case FK_SMALL_LL: HC_PICK(KSmallLL)
         case FK_ALLREDUCE_NVLS:
@@ -1207,7 +1278,7 @@ const char *FastKindName(int32_t k)
 {
     static const char *names[] = {"AllReduceOneShot", "AllReduceTwoShot", "AllReduceNvls", "ReduceScatter", "AllGather", "AlltoAll",
                                   "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier", "SmallLL",
-                                  "ReduceScatterNvls", "AllGatherNvls"};
+                                  "ReduceScatterNvls", "AllGatherNvls", "AllReduceTwoShotWindows", "ReduceScatterWindows", "ReduceScatterInPlace"};
     return (k >= 0 && k < FK_COUNT) ? names[k] : "?";
 }
 

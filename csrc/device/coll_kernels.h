@@ -32,6 +32,9 @@ enum FastKind : int32_t {
     FK_SMALL_LL,             // flag-in-data exchange for small all-reduce / all-gather / all-to-all / reduce-scatter
     FK_REDUCE_SCATTER_NVLS,  // in-switch reduce-scatter (multimem.ld_reduce of the rank's own block)
     FK_ALLGATHER_NVLS,       // all-gather by multicast stores
+    FK_ALLREDUCE_TWOSHOT_WIN,   // two-shot all-reduce of an operand beyond the staging: windows inside one launch
+    FK_REDUCE_SCATTER_WIN,      // reduce-scatter of blocks beyond a staging slot: column windows inside one launch
+    FK_REDUCE_SCATTER_INPLACE,  // reduce-scatter that reads the peers' registered inputs in place
     FK_COUNT
 };
 const char *FastKindName(int32_t k);

@@ -33,7 +33,7 @@
 #include "hccl/hccl_sym_win.h"
 #include "hcomm_res.h"
 #include "hcomm_device.cuh"
-#include "moe_api.h"
+#include "hcomm_moe.h"
 
 namespace hc {
 namespace {
@@ -66,6 +66,9 @@ __device__ __forceinline__ float *Scales(const MoeParams &p, int rank) { return 
 __device__ __forceinline__ uint64_t *Origin(const MoeParams &p, int rank) { return (uint64_t *)(p.peerBuf[rank] + p.lay.offOrigin); }
 __device__ __forceinline__ uint32_t *ExpertOffsets(const MoeParams &p, int rank) { return (uint32_t *)(p.peerBuf[rank] + p.lay.offExpertOffsets); }
 __device__ __forceinline__ __nv_bfloat16 *Comb(const MoeParams &p, int rank) { return (__nv_bfloat16 *)(p.peerBuf[rank] + p.lay.offCombine); }
+// one byte per (token, k) of the LOCAL tokens: 1 when dispatch sent that row, 0 when the expert index was out of range
+// (masked) or the owner's receive capacity was exhausted; combine leaves such rows out of the sum
+__device__ __forceinline__ uint8_t *Valid(const MoeParams &p, int rank) { return (uint8_t *)(p.peerBuf[rank] + p.lay.offValid); }
 
 __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
 {
@@ -111,11 +114,13 @@ __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
         if (tid == 0) {
             uint32_t acc = 0;
             uint32_t *off = ExpertOffsets(p, me);
+            // every entry is clamped to the receive capacity: a grouped GEMM that walks [off[el], off[el + 1]) never leaves the buffer
+            const uint32_t capRows = (uint32_t)p.lay.maxRecvRows;
             for (int el = 0; el < El; ++el) {
-                off[el] = acc;
+                off[el] = acc < capRows ? acc : capRows;
                 acc += sTot[el];
             }
-            off[El] = acc < (uint32_t)p.lay.maxRecvRows ? acc : (uint32_t)p.lay.maxRecvRows;
+            off[El] = acc < capRows ? acc : capRows;
         }
         __syncthreads();
     }
@@ -182,15 +187,19 @@ __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
         }
         for (int k = 0; k < K; ++k) {
             const int e = p.topkIdx[t * K + k];
-            if (e < 0 || e >= E) continue;
+            if (e < 0 || e >= E) {
+                if (lane == 0) Valid(p, me)[t * K + k] = 0;
+                continue;
+            }
             const int owner = e / El;
             uint32_t slot = 0;
             if (lane == 0) slot = sBase[e] + atomicAdd(&cursor[e], 1u);
             slot = __shfl_sync(0xffffffffu, slot, 0);
             if (slot >= (uint32_t)p.lay.maxRecvRows) {
-                if (lane == 0) atomicAdd(p.overflow, 1u);
+                if (lane == 0) { atomicAdd(p.overflow, 1u); Valid(p, me)[t * K + k] = 0; }
                 continue;
             }
+            if (lane == 0) Valid(p, me)[t * K + k] = 1;
             uint8_t *row = Rows(p, owner) + (size_t)slot * H;
             float *srow = Scales(p, owner) + (size_t)slot * blocksPerRow;
             int i = 0;
@@ -239,10 +248,12 @@ __global__ void __launch_bounds__(512) MoeCombineKernel(const MoeParams *table)
     // 2. gate-weighted sum per local token
     for (int t = blockIdx.x * warpsPerCta + warp; t < p.numTokens; t += gridDim.x * warpsPerCta) {
         float g[16];
-        for (int k = 0; k < K; ++k) g[k] = p.gates[t * K + k];
+        bool live[16];
+        for (int k = 0; k < K; ++k) { g[k] = p.gates[t * K + k]; live[k] = Valid(p, me)[t * K + k] != 0; }
         for (int v = lane; v < vecs; v += 32) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
             for (int k = 0; k < K; ++k) {
+                if (!live[k]) continue;                     // nothing was sent for this (token, k): the slot holds an older step's row
                 const uint4 pk = Ld16Volatile((const char *)(Comb(p, me) + ((size_t)t * K + k) * H) + (size_t)v * 16);
                 const __nv_bfloat162 *ph = (const __nv_bfloat162 *)&pk;
 #pragma unroll
@@ -272,6 +283,8 @@ struct MoeCtx {
     HcclCommSymWindow win = nullptr;
     char *peer[HC_KERNEL_MAX_RANKS] = {nullptr};
     uint32_t *scratch = nullptr;
+    uint32_t *staticScratch = nullptr;   // device address of the built-in counter table on this exchange's GPU
+    int device = -1;                     // the GPU this exchange was created on
     uint32_t *overflow = nullptr;
     MoeParams *devParams = nullptr;
     int nextParam = 0;
@@ -314,6 +327,49 @@ HcclResult LaunchBarrierIfNeeded(Comm *c, void *stream);
 
 using namespace hc;
 
+// ------------------------------------------------------------------ built-in scratch of HcommMoeDispatchStaticScratch
+//
+// The dispatch kernel counts rows per expert in a small table of global-memory counters.  HcommMoeDispatch keeps
+// that table in a cudaMalloc'ed block owned by the exchange object.  HcommMoeDispatchStaticScratch runs the SAME kernel
+// with the table placed in the array below, which is part of this library's device image, so that nothing on its path
+// asks any allocator for memory - neither the CUDA runtime's nor a framework's caching one.
+//
+// It exists for callers that must not allocate at the moment they dispatch:
+//   * a serving process whose memory pool has already claimed all of the GPU, where a late cudaMalloc fails;
+//   * a step in which other streams (or other ranks' kernels waiting on this rank) are in flight, where the
+//     implicit device-wide synchronisation of cudaMalloc / cudaFree stalls them or lengthens a peer's wait;
+//   * code that owns no handle it could hang a buffer on and would otherwise allocate and free around each call.
+//
+// Limits and rules:
+//   * at most kStaticScratchExperts experts (2 counters each, kStaticScratchBytes of device memory per process and
+//     GPU, reserved when the library is loaded); larger exchanges are refused with HCCL_E_PARA;
+//   * the array's device address is looked up (cudaGetSymbolAddress) by HcommMoeCreate, which runs at set-up on the
+//     exchange's GPU; the dispatch call itself does no look-up, and it refuses (HCCL_E_PARA, before anything is queued)
+//     a call made while another device is current - the address belongs to the exchange's GPU only;
+//   * the array is shared by every call from this process on the same GPU and keeps whatever the previous call
+//     left (a call that ran out of time leaves counts behind); each call therefore zeroes the part it uses, on
+//     the caller's stream, before the kernel runs;
+//   * because the array is shared, two calls that overlap in time on one GPU (different streams, different
+//     exchange objects) race on it: keep calls of this entry point ordered one after another per GPU;
+//   * ranks of one process that share a GPU (the single-GPU test arrangement) are refused: their launches are
+//     merged through a table that is created on demand, which this entry point promises not to do.
+constexpr int kStaticScratchExperts = 256;
+constexpr size_t kStaticScratchBytes = sizeof(uint32_t) * 2 * kStaticScratchExperts;
+static __device__ __align__(256) uint32_t g_staticDispatchScratch[2 * kStaticScratchExperts];
+
+// Device address of the table on the CURRENT device (in host code the array's name is only a stand-in for it).
+static uint32_t *ResolveStaticScratch()
+{
+    uint32_t *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void **)&ptr, g_staticDispatchScratch);
+    if (e != cudaSuccess || !ptr) {
+        HCCL_WARNING("built-in dispatch scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        cudaGetLastError();
+        return nullptr;
+    }
+    return ptr;
+}
+
 extern "C" {
 
 // Collective: every rank allocates the same symmetric buffer and maps its peers'.
@@ -339,6 +395,7 @@ int HcommMoeCreate(HcclComm comm, int numExperts, int topk, int hidden, int maxT
     L.offScales = off; off = Align256(off + (uint64_t)L.maxRecvRows * (hidden / 128) * 4);
     L.offRows = off; off = Align256(off + (uint64_t)L.maxRecvRows * hidden);
     L.offCombine = off; off = Align256(off + (uint64_t)maxTokens * topk * hidden * 2);
+    L.offValid = off; off = Align256(off + (uint64_t)maxTokens * topk);
     L.totalBytes = off;
     HcclResult r = (HcclResult)HcommMemAlloc(&m->buf, L.totalBytes);
     if (r != HCCL_SUCCESS) { delete m; return r; }
@@ -355,6 +412,8 @@ int HcommMoeCreate(HcclComm comm, int numExperts, int topk, int hidden, int maxT
     cudaMalloc(&m->overflow, sizeof(uint32_t));
     cudaMemset(m->overflow, 0, sizeof(uint32_t));
     cudaMalloc(&m->devParams, sizeof(MoeParams) * 32);
+    cudaGetDevice(&m->device);
+    m->staticScratch = ResolveStaticScratch();       // set-up time, the exchange's GPU is current
     cudaFuncAttributes fa;
     cudaFuncGetAttributes(&fa, MoeDispatchKernel);
     cudaFuncGetAttributes(&fa, MoeCombineKernel);
@@ -441,62 +500,7 @@ int HcommMoeCombine(void *handle, const void *y, const float *gates, void *out, 
 
 // ------------------------------------------------------------------ dispatch without any allocation
 //
-// The dispatch kernel counts rows per expert in a small table of global-memory counters.  HcommMoeDispatch keeps
-// that table in a cudaMalloc'ed block owned by the exchange object.  The entry point below runs the SAME kernel
-// with the table placed in an array that is part of this library's device image instead, so that nothing on its
-// path asks any allocator for memory - neither the CUDA runtime's nor a framework's caching one.
-//
-// It exists for callers that must not allocate at the moment they dispatch:
-//   * a serving process whose memory pool has already claimed all of the GPU, where a late cudaMalloc fails;
-//   * a step in which other streams (or other ranks' kernels waiting on this rank) are in flight, where the
-//     implicit device-wide synchronisation of cudaMalloc / cudaFree stalls them or lengthens a peer's wait;
-//   * code that owns no handle it could hang a buffer on and would otherwise allocate and free around each call.
-//
-// Limits and rules:
-//   * at most kStaticScratchExperts experts (2 counters each, kStaticScratchBytes of device memory per process and
-//     GPU, reserved when the library is loaded); larger exchanges are refused with HCCL_E_PARA;
-//   * the array is shared by every call from this process on the same GPU and keeps whatever the previous call
-//     left (a call that ran out of time leaves counts behind); each call therefore zeroes the part it uses, on
-//     the caller's stream, before the kernel runs;
-//   * because the array is shared, two calls that overlap in time on one GPU (different streams, different
-//     exchange objects) race on it: keep calls of this entry point ordered one after another per GPU;
-//   * the first call on a device looks up the array's address (cudaGetSymbolAddress) and remembers it; make that
-//     first call during start-up, with the device current and before any stream capture begins;
-//   * ranks of one process that share a GPU (the single-GPU test arrangement) are refused: their launches are
-//     merged through a table that is created on demand, which this entry point promises not to do.
-constexpr int kStaticScratchExperts = 256;
-constexpr size_t kStaticScratchBytes = sizeof(uint32_t) * 2 * kStaticScratchExperts;
-static __device__ __align__(256) uint32_t g_staticDispatchScratch[2 * kStaticScratchExperts];
-
-namespace {
-constexpr int kMaxDevicesTracked = 64;
-uint32_t *g_staticScratchAddr[kMaxDevicesTracked];   // per device, filled on first use
-std::mutex g_staticScratchMu;
-
-// Address of the built-in table on the current device; looked up once per device.
-HcclResult StaticScratchForCurrentDevice(uint32_t **out)
-{
-    int dev = -1;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevicesTracked) {
-        HCCL_ERROR("built-in dispatch scratch: no usable current device (%s)", e == cudaSuccess ? "index out of range" : cudaGetErrorString(e));
-        return HCCL_E_RUNTIME;
-    }
-    std::lock_guard<std::mutex> lk(g_staticScratchMu);
-    if (!g_staticScratchAddr[dev]) {
-        uint32_t *ptr = nullptr;
-        e = cudaGetSymbolAddress((void **)&ptr, g_staticDispatchScratch);
-        if (e != cudaSuccess || !ptr) {
-            HCCL_ERROR("built-in dispatch scratch: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
-            return HCCL_E_RUNTIME;
-        }
-        g_staticScratchAddr[dev] = ptr;
-    }
-    *out = g_staticScratchAddr[dev];
-    return HCCL_SUCCESS;
-}
-}  // namespace
-
+// See the comment at g_staticDispatchScratch (top of the host section) for what this entry point is for and its rules.
 int HcommMoeDispatchStaticScratch(void *handle, const void *x, const int32_t *topkIdx, int numTokens, void *stream)
 {
     MoeCtx *m = (MoeCtx *)handle;
@@ -512,20 +516,29 @@ int HcommMoeDispatchStaticScratch(void *handle, const void *x, const int32_t *to
         RPT_ERR("EI0003", "HcommMoeDispatchStaticScratch does not serve several ranks of one process on one GPU - use HcommMoeDispatch");
         return HCCL_E_NOT_SUPPORT;
     }
+    // The table's address belongs to the GPU the exchange was created on; with another device current the launch
+    // below would go elsewhere.  Checked before anything is queued or counted.
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev != m->device) {
+        RPT_ERR("EI0003", "HcommMoeDispatchStaticScratch called with device %d current; the exchange lives on device %d", dev, m->device);
+        return HCCL_E_PARA;
+    }
+    if (!m->staticScratch) {
+        RPT_ERR("EI0003", "the built-in dispatch scratch could not be resolved when this exchange was created - use HcommMoeDispatch");
+        return HCCL_E_NOT_SUPPORT;
+    }
     std::lock_guard<std::mutex> lk(c->opMu);
     int st = c->state.load();
     if (st == (int)CommState::SUSPENDING || st == (int)CommState::SUSPENDED) return HCCL_E_SUSPENDING;
-    uint32_t *scratch = nullptr;
-    CHK_RET(StaticScratchForCurrentDevice(&scratch));
     CHK_RET(LaunchBarrierIfNeeded(c, stream));
     // the kernel expects both counter rows at zero and the array may hold a previous call's leftovers
-    if (cudaMemsetAsync(scratch, 0, sizeof(uint32_t) * 2 * (size_t)m->lay.numExperts, (cudaStream_t)stream) != cudaSuccess) {
+    if (cudaMemsetAsync(m->staticScratch, 0, sizeof(uint32_t) * 2 * (size_t)m->lay.numExperts, (cudaStream_t)stream) != cudaSuccess) {
         HCCL_ERROR("built-in dispatch scratch: clearing failed: %s", cudaGetErrorString(cudaGetLastError()));
         return HCCL_E_RUNTIME;
     }
     MoeParams hp;
     FillCommon(m, hp);
-    hp.scratch = scratch;
+    hp.scratch = m->staticScratch;
     hp.x = (const __nv_bfloat16 *)x; hp.topkIdx = topkIdx; hp.numTokens = numTokens;
     ++c->opSeq;
     return LaunchMoe(m, (void *)MoeDispatchKernel, hp, 9103, stream);

@@ -24,7 +24,7 @@ class MoeLayout(ctypes.Structure):
     _fields_ = [("numExperts", ctypes.c_int32), ("topk", ctypes.c_int32), ("hidden", ctypes.c_int32), ("maxTokens", ctypes.c_int32),
                 ("maxRecvRows", ctypes.c_int32), ("reserved", ctypes.c_int32), ("offCounts", ctypes.c_uint64), ("offExpertOffsets", ctypes.c_uint64),
                 ("offOrigin", ctypes.c_uint64), ("offScales", ctypes.c_uint64), ("offRows", ctypes.c_uint64), ("offCombine", ctypes.c_uint64),
-                ("totalBytes", ctypes.c_uint64)]
+                ("totalBytes", ctypes.c_uint64), ("offValid", ctypes.c_uint64)]
 
 
 class _DevView:
