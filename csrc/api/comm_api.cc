@@ -441,20 +441,16 @@ HcclResult HcclCommSuspend(HcclComm comm)
     return HCCL_SUCCESS;
 }
 
-// Collective over the ranks that are still alive: clears the flag pages and counters so that the
-// next operator starts from a consistent state, then reopens the communicator.
-HcclResult HcclCommResume(HcclComm comm)
+}  // extern "C"
+
+namespace hc {
+// Collective (two barriers on `g`): puts every synchronisation value of the communicator back to its initial state -
+// flag pages, device counters, host-side expectations, the abort word and the recorded failure.  The caller holds
+// the operator lock and nothing of this communicator is in flight on any rank.
+HcclResult CommClearSyncState(Comm *c, Bootstrap::Group &g)
 {
-    Comm *c = AsComm(comm);
-    CHK_PTR_NULL(c);
-    if (c->state.load() != (int)CommState::SUSPENDED) {
-        RPT_ERR("EI0003", "HcclCommResume on a communicator that is not suspended");
-        return HCCL_E_PARA;
-    }
-    FireState(c, HCCL_COMM_STATE_PHASE_RESUME_PRE);
-    std::lock_guard<std::mutex> lk(c->opMu);
     Platform *P = c->plat;
-    CHK_RET(c->boot->Barrier(c->group));            // everyone is quiescent
+    CHK_RET(c->boot->Barrier(g));            // everyone is quiescent
     CHK_RET(P->MemsetSync(c->LocalHeap(), 0, HC_CTRL_BYTES));
     CHK_RET(P->MemsetSync(c->LocalHeap() + c->llOffset, 0, c->llBytes));
     CHK_RET(P->MemsetSync(c->devCounters, 0, 128 * sizeof(uint32_t)));
@@ -469,12 +465,31 @@ HcclResult HcclCommResume(HcclComm comm)
     }
     c->hostLaunches = 0;
     c->lastOpOnHost = true;
-    FusedResetLocal(c);
+    if (P->kind() == PlatKind::CUDA) FusedResetLocal(c);
     memset(c->waitStatus, 0, sizeof(HcclDeviceWaitStatus));
     __atomic_store_n(c->abortWord, 0u, __ATOMIC_RELEASE);
     c->asyncError.store(0);
     c->boot->ClearRemoteError();
-    CHK_RET(c->boot->Barrier(c->group));            // nobody signals into a page that is still being cleared
+    CHK_RET(c->boot->Barrier(g));            // nobody signals into a page that is still being cleared
+    return HCCL_SUCCESS;
+}
+}  // namespace hc
+
+extern "C" {
+
+// Collective over the ranks that are still alive: clears the flag pages and counters so that the
+// next operator starts from a consistent state, then reopens the communicator.
+HcclResult HcclCommResume(HcclComm comm)
+{
+    Comm *c = AsComm(comm);
+    CHK_PTR_NULL(c);
+    if (c->state.load() != (int)CommState::SUSPENDED) {
+        RPT_ERR("EI0003", "HcclCommResume on a communicator that is not suspended");
+        return HCCL_E_PARA;
+    }
+    FireState(c, HCCL_COMM_STATE_PHASE_RESUME_PRE);
+    std::lock_guard<std::mutex> lk(c->opMu);
+    CHK_RET(CommClearSyncState(c, c->group));
     c->state.store((int)CommState::READY);
     FireState(c, HCCL_COMM_STATE_PHASE_RESUME_POST);
     HCCL_RUN_INFO("communicator \"%s\" rank %u resumed", c->cfg.name.c_str(), c->rank);

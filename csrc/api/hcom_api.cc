@@ -401,5 +401,14 @@ HcclResult HcomAllToAll(const void *in, uint64_t sendCount, HcclDataType sendTyp
 HcclResult HcomAlltoAllV(const void *in, const void *sendCounts, const void *sdispls, HcclDataType sendType, const void *out, const void *recvCounts,
                          const void *rdispls, HcclDataType recvType, const char *group, aclrtStream stream, const char *tag)
 { HCOM_COMM(group); return HcclAlltoAllV(in, sendCounts, sdispls, sendType, out, recvCounts, rdispls, recvType, (HcclComm)c, stream); }
+HcclResult HcomAllGatherV(const char *tag, const void *sendBuf, uint64_t sendCount, const void *recvBuf, const void *recvCounts, const void *rdispls,
+                          HcclDataType dataType, const char *group, aclrtStream stream)
+{ HCOM_COMM(group); return HcclAllGatherV((void *)sendBuf, sendCount, (void *)recvBuf, recvCounts, rdispls, dataType, (HcclComm)c, stream); }
+HcclResult HcomReduceScatterV(const char *tag, void *sendBuf, const void *sendCounts, const void *sdispls, void *recvBuf, uint64_t recvCount, HcclDataType dataType,
+                              HcclReduceOp op, const char *group, aclrtStream stream)
+{ HCOM_COMM(group); return HcclReduceScatterV(sendBuf, sendCounts, sdispls, recvBuf, recvCount, dataType, op, (HcclComm)c, stream); }
+HcclResult HcomAlltoAllVC(const void *sendBuf, const void *sendCountMatrix, HcclDataType sendType, const void *recvBuf, HcclDataType recvType, const char *group,
+                          aclrtStream stream, const char *tag)
+{ HCOM_COMM(group); return HcclAlltoAllVC(sendBuf, sendCountMatrix, sendType, recvBuf, recvType, (HcclComm)c, stream); }
 
 }  // extern "C"

@@ -9,6 +9,7 @@
 #include "../alg/templates.h"
 #include "../core/env.h"
 #include "../core/log.h"
+#include "../plat/platform.h"
 #include "../topo/nvml_topo.h"
 #include "../topo/rank_graph.h"
 
@@ -141,6 +142,10 @@ int HcommToolSelect(int cmd, uint32_t nRanks, uint64_t bytes, int dtype, int op,
     Out(out, outLen, sel.name);
     return 0;
 }
+
+// Simulator ranks of this process lose their next n flag writes (a message that the test drops): the peers' waits
+// then run out, which is how the timeout and operator-retry paths are exercised without touching a GPU.
+void HcommToolSimWithholdFlags(int n) { hc::SimWithholdFlagWrites(n); }
 
 void HcommToolReloadEnv(void)
 {

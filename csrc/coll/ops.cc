@@ -57,6 +57,7 @@ void Record(Comm *c, const OpDesc &d, const Selection &sel, uint64_t t0)
     r.hostStartNs = t0;
     r.hostEndNs = NowNs();
     ++c->opRingNext;
+    if (c->profiling) DfxReportOp(c, r.algName, r.hostStartNs, r.hostEndNs);
 }
 
 // CTAs per rank.  Small transfers are latency bound (few CTAs keep the barrier cheap); large ones need many CTAs
@@ -677,13 +678,27 @@ bool GroupActive() { return t_groupDepth > 0; }
 
 HcclResult RunOp(Comm *c, const OpDesc &d)
 {
-    std::lock_guard<std::mutex> lk(c->opMu);
+    HcclResult r;
+    uint64_t seq;
+    {
+        std::lock_guard<std::mutex> lk(c->opMu);
+        r = RunOpLocked(c, d);
+        seq = c->opSeq;
+    }
+    // an expired wait that a host engine reports synchronously: the retry rounds run the operator again
+    if (r == HCCL_E_TIMEOUT && c->retry) r = RetryAfterTimeout(c, seq);
+    return r;
+}
+
+HcclResult RunOpLocked(Comm *c, const OpDesc &d)
+{
     int st = c->state.load();
     if (st == (int)CommState::SUSPENDING || st == (int)CommState::SUSPENDED) return HCCL_E_SUSPENDING;
     if (st == (int)CommState::DESTROYED) return HCCL_E_PARA;
     if (c->asyncError.load() != 0) return (HcclResult)c->asyncError.load();
     uint64_t t0 = NowNs();
     ++c->opSeq;
+    RetryNoteOp(c, d);
     const bool cuda = c->plat->kind() == PlatKind::CUDA;
     const uint32_t esz = DtypeSize(d.dtype);
 

@@ -1,6 +1,10 @@
 // ops.h - operator front end: validation, group deferral, selection, dispatch to an engine.
 #pragma once
+#include <atomic>
+#include <condition_variable>
 #include <functional>
+#include <mutex>
+#include <thread>
 #include <vector>
 
 #include "../alg/selector.h"
@@ -27,8 +31,32 @@ struct OpDesc {
 
 // Runs (or, inside HcclGroupStart/End, queues) one operator.
 HcclResult SubmitOp(Comm *c, const OpDesc &d);
-// Executes immediately; used by SubmitOp and by HcclGroupEnd.
+// Executes immediately; used by SubmitOp and by HcclGroupEnd.  With operator retry on, an operator that ends with an
+// expired wait is run again by the retry rounds before the caller sees a result.
 HcclResult RunOp(Comm *c, const OpDesc &d);
+// The same for a caller that already holds the communicator's operator lock (the retry agent).
+HcclResult RunOpLocked(Comm *c, const OpDesc &d);
+
+// Operator retry (retry.cc): per-communicator state of the agent thread.
+struct RetryState {
+    uint32_t maxCnt = 1, holdMs = 5000, intervalMs = 1000;
+    Bootstrap::Group group;                  // the agents' own gather group on the control plane
+    std::thread agent;
+    std::atomic<bool> stop{false};
+    // last operator issued on this communicator (guarded by the operator lock)
+    OpDesc lastOp;
+    uint64_t lastSeq = 0;
+    bool lastValid = false;
+    // request / verdict hand-over between the caller and the agent
+    std::mutex mu;
+    std::condition_variable cv;
+    bool requested = false;
+    uint64_t verdictSeq = 0, servedSeq = 0;
+    int verdict = 0;
+    uint64_t requests = 0, rounds = 0, succeeded = 0, failed = 0;
+};
+void RetryNoteOp(Comm *c, const OpDesc &d);
+HcclResult RetryAfterTimeout(Comm *c, uint64_t seq);
 uint64_t OpDataVolume(const Comm *c, const OpDesc &d);
 
 // Group bookkeeping (thread local).

@@ -356,6 +356,7 @@ HcclResult CommCreate(const CommInitArgs &args, Comm **out)
     CHK_RET(c->boot->Barrier(c->group));
     HCCL_RUN_INFO("communicator \"%s\" ready: rank %u/%u on %s device %d, CCL buffer 2x%u MB, NVLS %s, %s", c->cfg.name.c_str(), c->rank,
                   c->nRanks, c->plat->name(), c->device, c->cfg.bufferMB, c->mcBase ? "on" : "off", c->graph.Describe().c_str());
+    RetrySetup(c.get());
     *out = c.release();
     return HCCL_SUCCESS;
 }
@@ -412,6 +413,7 @@ Comm::~Comm()
 void CommDestroy(Comm *c)
 {
     if (!c) return;
+    RetryTeardown(c);
     RegistryRemove(c);
     // Peers must stop touching my heap before it disappears.
     if (c->boot && c->state.load() != (int)CommState::DESTROYED) c->boot->Barrier(c->group, 10000);
@@ -443,6 +445,7 @@ void CommSetAsyncError(Comm *c, HcclResult err)
     if (c->asyncError.compare_exchange_strong(expected, (int)err)) {
         HCCL_ERROR("communicator \"%s\" rank %u: asynchronous error %d", c->cfg.name.c_str(), c->rank, (int)err);
         if (c->boot) c->boot->NotifyError(err);
+        DfxFireException(c, err);
     }
 }
 
@@ -452,7 +455,8 @@ HcclResult CommPollDeviceStatus(Comm *c)
         const HcclDeviceWaitStatus &s = *c->waitStatus;
         RPT_ERR("EI0002", "rank %u gave up waiting for rank %u (kind %u slot %u block %u): expected %llu, saw %llu, operator #%llu", s.rank,
                 s.peer, s.kind, s.slot, s.block, (unsigned long long)s.expected, (unsigned long long)s.seen, (unsigned long long)s.seq);
-        CommSetAsyncError(c, HCCL_E_TIMEOUT);
+        // with operator retry on, the retry rounds own the failure: it becomes the communicator's error only if they give up
+        if (!c->retry) CommSetAsyncError(c, HCCL_E_TIMEOUT);
         return HCCL_E_TIMEOUT;
     }
     return HCCL_SUCCESS;

@@ -116,6 +116,7 @@ struct ChannelRes {
 };
 
 enum class CommState { READY = 0, SUSPENDING = 1, SUSPENDED = 2, DESTROYED = 3 };
+struct RetryState;       // coll/ops.h
 
 struct Comm {
     uint32_t magic = 0x434f4d4d;     // "COMM"
@@ -189,6 +190,14 @@ struct Comm {
     uint32_t subCommSeq = 0;
 
     // ---- diagnostics
+    std::shared_ptr<RetryState> retry;       // operator retry agent, when switched on
+    // what the caller attached for diagnostics (HcommRegOpInfo / HcommRegOpTaskException / HcclDfxRegOpInfoByCommId)
+    std::vector<uint8_t> userOpInfo;
+    void (*userOpInfoFormatter)(const void *, char *, size_t) = nullptr;
+    std::vector<uint8_t> exchangeInfo;                       // HcclCommAddExchangeInfo: this rank's extra bytes
+    std::vector<std::vector<uint8_t>> peerExchangeInfo;      // what the peers contributed, filled by the channel exchange
+    std::map<std::string, int32_t (*)(uint64_t, int32_t)> taskCallbacks;
+    std::map<std::string, std::pair<void *, uint64_t>> taggedDevMem;
     std::mutex diagMu;
     std::vector<HcclOpRecord> opRing;
     uint64_t opRingNext = 0;
@@ -233,6 +242,16 @@ HcclResult RegistryAdd(Comm *c);
 void RegistryRemove(Comm *c);
 Comm *RegistryFind(const std::string &name);
 void RegistryForEach(const std::function<void(Comm *)> &fn);
+
+// Operator retry agent (coll/retry.cc).
+void RetrySetup(Comm *c);
+void RetryTeardown(Comm *c);
+// Collective (two barriers on `g`): every synchronisation value of the communicator back to its initial state.
+HcclResult CommClearSyncState(Comm *c, Bootstrap::Group &g);
+// Diagnostics hooks (api/dfx_api.cc): exception callbacks fire when a communicator records a failure, the profiling
+// sink receives one report per operator while profiling is on.
+void DfxFireException(Comm *c, HcclResult err);
+void DfxReportOp(Comm *c, const char *name, uint64_t beginNs, uint64_t endNs);
 
 // Clears the device-local scratch of the fused GEMM kernels (fused_gemm.cu) when a communicator resumes.
 void FusedResetLocal(Comm *c);

@@ -113,6 +113,8 @@ Platform *SimInstance();
 Platform *CudaInstance();
 // Applies HCCL_SIM: 1 -> simulator, 0 -> CUDA or failure, unset -> CUDA when available else simulator.
 Platform *DefaultPlatform();
+// Simulator only, for tests of the failure paths: the next n flag writes issued by this process are dropped.
+void SimWithholdFlagWrites(int n);
 // CUDA only: load the stream-engine helper kernels on the current device (see cuda_platform.cu).
 void PreloadPlatformKernels();
 

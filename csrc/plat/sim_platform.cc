@@ -24,6 +24,8 @@
 
 namespace hc {
 namespace {
+std::atomic<int> g_withhold{0};     // flag writes still to be dropped (tests)
+
 
 class SimStream {
 public:
@@ -243,6 +245,10 @@ public:
     }
     HcclResult FlagAddAsync(uint64_t *flag, uint64_t v, Stream s) override
     {
+        // host-side fault injection for tests: the next g_withhold flag writes of this process are lost
+        int left = g_withhold.load();
+        while (left > 0 && !g_withhold.compare_exchange_weak(left, left - 1)) {}
+        if (left > 0) return HCCL_SUCCESS;
         Run(s, [=] { __atomic_fetch_add(flag, v, __ATOMIC_RELEASE); });
         return HCCL_SUCCESS;
     }
@@ -285,6 +291,8 @@ private:
 };
 
 }  // namespace
+
+void SimWithholdFlagWrites(int n) { g_withhold.store(n > 0 ? n : 0); }
 
 Platform *SimInstance()
 {

@@ -68,6 +68,12 @@ HcclResult HcomAllToAll(const void *in, uint64_t sendCount, HcclDataType sendTyp
 HcclResult HcomAlltoAllV(const void *in, const void *sendCounts, const void *sdispls, HcclDataType sendType,
                          const void *out, const void *recvCounts, const void *rdispls, HcclDataType recvType,
                          const char *group, aclrtStream stream, const char *tag);
+HcclResult HcomAllGatherV(const char *tag, const void *sendBuf, uint64_t sendCount, const void *recvBuf, const void *recvCounts,
+                          const void *rdispls, HcclDataType dataType, const char *group, aclrtStream stream);
+HcclResult HcomReduceScatterV(const char *tag, void *sendBuf, const void *sendCounts, const void *sdispls, void *recvBuf,
+                              uint64_t recvCount, HcclDataType dataType, HcclReduceOp op, const char *group, aclrtStream stream);
+HcclResult HcomAlltoAllVC(const void *sendBuf, const void *sendCountMatrix, HcclDataType sendType, const void *recvBuf,
+                          HcclDataType recvType, const char *group, aclrtStream stream, const char *tag);
 
 #ifdef __cplusplus
 }

@@ -486,6 +486,87 @@ def main():
             stage(f"{algo} ok")
             c2.destroy()
         comm.barrier()
+    elif scenario == "op_retry":
+        # A flag write of one rank is lost on the host (the simulator drops it): a peer's wait runs out, the retry agents agree
+        # on the operator, clear the synchronisation state and run it again.  Exception callback, operator description and
+        # profiling sink are registered on the way.
+        import ctypes
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+
+        class RetryStats(ctypes.Structure):
+            _fields_ = [("enabled", ctypes.c_uint32), ("maxCnt", ctypes.c_uint32), ("holdTimeMs", ctypes.c_uint32), ("intervalMs", ctypes.c_uint32),
+                        ("requests", ctypes.c_uint64), ("rounds", ctypes.c_uint64), ("succeeded", ctypes.c_uint64), ("failed", ctypes.c_uint64)]
+
+        def stats():
+            st = RetryStats()
+            assert lib.HcclCommGetOpRetryStats(ctypes.c_void_p(comm.handle), ctypes.byref(st)) == 0
+            return st
+
+        seen = {"exceptions": [], "reports": []}
+        EXC = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_void_p)
+        SINK = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_void_p)
+        FMT = ctypes.CFUNCTYPE(None, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t)
+        exc_cb = EXC(lambda info, user: seen["exceptions"].append(ctypes.cast(info, ctypes.POINTER(ctypes.c_uint32))[9]))   # retCode
+        sink_cb = SINK(lambda kind, group, name, b, e, user: seen["reports"].append((kind, name.decode())))
+
+        def fmt(op_info, out, size):
+            ctypes.memmove(out, b"step 7 gradient bucket 3\0", 25)
+        fmt_cb = FMT(fmt)
+        assert lib.HcommExceptionRegisterCallback(exc_cb, None) == 0
+        assert lib.HcclProfilingSetSink(sink_cb, None) == 0
+        name = comm.name.encode()
+        blob = ctypes.create_string_buffer(b"opaque operator description", 64)
+        assert lib.HcommRegOpInfo(name, blob, 64) == 0
+        assert lib.HcommRegOpTaskException(name, fmt_cb) == 0
+        comm.set_profiling(True)
+        assert stats().enabled == 1 and stats().maxCnt == 2
+
+        x = np.full(5000, rank + 1, np.float32)
+        y = np.zeros_like(x)
+        comm.all_reduce(x, y)
+        assert (y == world * (world + 1) / 2).all()
+        assert any(k == 0 for k, _ in seen["reports"]), "the profiling sink saw no operator"
+        # --- the fault: rank 1 loses one flag write of the next operator
+        if rank == 1:
+            lib.HcommToolSimWithholdFlags(1)
+        y[:] = 0
+        comm.all_reduce(x, y)                       # a rank whose wait ran out returns only after the retry rounds
+        deadline = time.time() + 60
+        while stats().succeeded < 1 and stats().failed < 1 and time.time() < deadline:
+            time.sleep(0.05)                        # ranks whose own part had completed wait here for the agents' round
+        st = stats()
+        assert st.rounds >= 1 and st.succeeded >= 1 and st.failed == 0, (st.rounds, st.succeeded, st.failed)
+        assert (y == world * (world + 1) / 2).all(), y[:4]
+        assert comm.async_error() == 0
+        stage(f"retry ok after {st.rounds} round(s), {st.requests} request(s) from this rank")
+        # the communicator keeps working
+        comm.all_reduce(x, y)
+        assert (y == world * (world + 1) / 2).all()
+        # --- an operator that cannot be run again (in-place reduction): the failure surfaces, callbacks fire
+        if rank == 1:
+            lib.HcommToolSimWithholdFlags(1)
+        z = x.copy()
+        failed = 0
+        try:
+            comm.all_reduce(z)
+        except hb.HcclError as e:
+            failed = e.code
+        deadline = time.time() + 30
+        codes = [None]
+        while time.time() < deadline:
+            codes[0] = comm.async_error()
+            if failed or codes[0]:
+                break
+            time.sleep(0.05)
+        # at least one rank saw the expired wait; every rank ends up with an error of its own or a remote one
+        print(f"rank {rank}: in-place operator ended with {failed}, async error {codes[0]}, callbacks {seen['exceptions']}", flush=True)
+        if failed:
+            assert failed == 9, failed
+            assert seen["exceptions"] == [9], seen["exceptions"]          # the callback saw HCCL_E_TIMEOUT once
+        lib.HcommExceptionUnregisterCallback(exc_cb)
+        lib.HcclProfilingSetSink(None, None)
+        return 0
     elif scenario == "peer_exit":
         # One rank leaves between steps; the others learn it from the control plane before their next launch.
         x = np.ones(10, np.float32) if not use_cuda else None

@@ -44,3 +44,11 @@ def test_suspend_resume_snapshot_and_diagnostics():
 def test_forced_algorithm_families_on_sub_communicators():
     codes, outs = launch("forced_algos", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=180)
     assert codes == [0, 0, 0], "\n".join(outs)
+
+
+def test_operator_retry_after_a_withheld_flag_and_the_dfx_callbacks():
+    env = {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCCL_OP_RETRY_ENABLE": "1", "HCCL_OP_RETRY_PARAMS": "MaxCnt:2,HoldTime:300,IntervalTime:100",
+           "HCCL_EXEC_TIMEOUT": "2"}
+    codes, outs = launch("op_retry", 3, env, timeout=180)
+    assert codes == [0, 0, 0], "\n".join(outs)
+    assert any("retry ok after" in o for o in outs)
