@@ -279,6 +279,7 @@ static HcclResult SetupDeviceState(Comm *c)
     d.opCounters = c->opCounters;
     d.timeoutNs = (uint64_t)c->TimeoutMs() * 1000000ull;
     d.llOffset = c->llOffset;
+    d.heapMB = (uint32_t)((c->heapBytes + (1u << 20) - 1) >> 20);
     static_assert(sizeof(CommDev) <= HC_DEV_COUNTERS_OFFSET, "CommDev outgrew its slot");
     CHK_RET(P->MemcpySync(c->devStruct, &d, sizeof(CommDev)));
     return HCCL_SUCCESS;

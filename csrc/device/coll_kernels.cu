@@ -135,8 +135,8 @@ template <typename T>
 static __device__ __noinline__ void ReduceFanOut(const char *const *src, int n, char *const *dst, int nd, uint64_t nElems, int op, int useScale, float scale)
 {
     uintptr_t bits = 0;
-    for (int r = 0; r < n; ++r) bits |= (uintptr_t)src[r];
-    for (int k = 0; k < nd; ++k) bits |= (uintptr_t)dst[k];
+    for (int r = 0; r < n; ++r) { HC_BOUNDS_OR_RETURN(src[r], nElems * sizeof(T)); bits |= (uintptr_t)src[r]; }
+    for (int k = 0; k < nd; ++k) { HC_BOUNDS_OR_RETURN(dst[k], nElems * sizeof(T)); bits |= (uintptr_t)dst[k]; }
     if ((bits & 15) == 0) {
         if (n <= 2) ReduceLoop<T, true, 2, 4>(src, n, dst, nd, nElems, op, useScale, scale);
         else if (n <= 4) ReduceLoop<T, true, 4, 2>(src, n, dst, nd, nElems, op, useScale, scale);

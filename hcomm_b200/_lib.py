@@ -85,7 +85,9 @@ class HcclSendRecvItem(ctypes.Structure):
 
 
 def lib_path() -> Path:
-    return Path(__file__).resolve().parent / "lib" / "libhcomm.so"
+    # HCOMM_LIBRARY=bounds selects the bounds-checking build (hcomm_b200.build.build_core(bounds=True))
+    name = "libhcomm_bounds.so" if os.environ.get("HCOMM_LIBRARY") == "bounds" else "libhcomm.so"
+    return Path(__file__).resolve().parent / "lib" / name
 
 
 def load() -> ctypes.CDLL:
@@ -96,7 +98,7 @@ def load() -> ctypes.CDLL:
     path = lib_path()
     if not path.exists() or os.environ.get("HCOMM_REBUILD") == "1":
         from . import build
-        build.build_core()
+        build.build_core(bounds=os.environ.get("HCOMM_LIBRARY") == "bounds")
     _LIB = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
     _LIB.HcclGetErrorString.restype = ctypes.c_char_p
     return _LIB

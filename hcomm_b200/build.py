@@ -56,20 +56,20 @@ def _core_sources():
     return srcs
 
 
-def _obj_for(src: Path) -> Path:
+def _obj_for(src: Path, variant: str = "") -> Path:
     rel = src.relative_to(CSRC)
-    return BUILD / "obj" / (str(rel).replace("/", "__") + ".o")
+    return BUILD / ("obj" + ("-" + variant if variant else "")) / (str(rel).replace("/", "__") + ".o")
 
 
-def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=()) -> Path:
-    obj = _obj_for(src)
+def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=(), variant: str = "", defines=()) -> Path:
+    obj = _obj_for(src, variant)
     obj.parent.mkdir(parents=True, exist_ok=True)
     if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_mtime):
         return obj
     if src.suffix == ".cu":
-        cmd = [NVCC, *NVCC_FLAGS, *extra_nvcc, "-c", str(src), "-o", str(obj)]
+        cmd = [NVCC, *NVCC_FLAGS, *extra_nvcc, *defines, "-c", str(src), "-o", str(obj)]
     else:
-        cmd = ["g++", *CXX_FLAGS, "-c", str(src), "-o", str(obj)]
+        cmd = ["g++", *CXX_FLAGS, *defines, "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -80,15 +80,21 @@ def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=()) -> Path:
     return obj
 
 
-def build_core(verbose: bool = False, jobs: int | None = None) -> Path:
-    """Builds ``libhcomm.so`` and returns its path."""
+def build_core(verbose: bool = False, jobs: int | None = None, bounds: bool = False) -> Path:
+    """Builds ``libhcomm.so`` and returns its path.
+
+    ``bounds=True`` builds ``libhcomm_bounds.so`` instead: the same library compiled with ``-DHCOMM_DEBUG_BOUNDS``, in
+    which every grid copy and reduction of the collective kernels checks its address ranges against the symmetric heap
+    and the CCL halves and records a violation in the status block instead of touching memory out of range.  Select it
+    at run time with ``HCOMM_LIBRARY=bounds``."""
     LIBDIR.mkdir(parents=True, exist_ok=True)
-    out = LIBDIR / "libhcomm.so"
+    out = LIBDIR / ("libhcomm_bounds.so" if bounds else "libhcomm.so")
     srcs = _core_sources()
     hdr = _headers_mtime()
     jobs = jobs or min(8, os.cpu_count() or 4)
+    variant, defines = ("bounds", ("-DHCOMM_DEBUG_BOUNDS",)) if bounds else ("", ())
     with ThreadPoolExecutor(max_workers=jobs) as ex:
-        objs = list(ex.map(lambda s: _compile(s, hdr, verbose), srcs))
+        objs = list(ex.map(lambda s: _compile(s, hdr, verbose, variant=variant, defines=defines), srcs))
     newest_obj = max(o.stat().st_mtime for o in objs)
     if out.exists() and out.stat().st_mtime >= newest_obj:
         return out
@@ -164,4 +170,6 @@ def build_all(verbose: bool = False) -> None:
 
 if __name__ == "__main__":
     build_all(verbose="-v" in sys.argv)
+    if "--bounds" in sys.argv:
+        build_core(verbose="-v" in sys.argv, bounds=True)
     print("built:", *sorted(p.name for p in LIBDIR.glob("*.so")))
