@@ -18,6 +18,7 @@ const char *AlgoName(Algo a)
         case Algo::RING: return "ring"; case Algo::HD: return "H-D_R"; case Algo::BRUCK: return "NB";
         case Algo::PAIRWISE: return "pairwise"; case Algo::TREE: return "tree"; case Algo::NVLS: return "nvls";
         case Algo::STAR: return "star";
+        case Algo::NHR: return "NHR";
     }
     return "?";
 }
@@ -29,7 +30,8 @@ bool ParseAlgoName(const std::string &raw, Algo *out)
     if (s == "ring") *out = Algo::RING;
     else if (s == "fullmesh" || s == "mesh" || s == "pipeline") *out = Algo::MESH;
     else if (s == "mesh_oneshot" || s == "oneshot") *out = Algo::MESH_ONESHOT;
-    else if (s == "h-d_r" || s == "hd" || s == "rhd" || s == "nhr" || s == "nhr_v1" || s == "ahc" || s == "ahc_broke") *out = Algo::HD;
+    else if (s == "h-d_r" || s == "hd" || s == "rhd" || s == "ahc" || s == "ahc_broke") *out = Algo::HD;
+    else if (s == "nhr" || s == "nhr_v1") *out = Algo::NHR;
     else if (s == "nb" || s == "bruck") *out = Algo::BRUCK;
     else if (s == "pairwise") *out = Algo::PAIRWISE;
     else if (s == "tree") *out = Algo::TREE;
@@ -485,6 +487,161 @@ void AllGatherBruck(const CollShape &sh, Schedule &s)
     }
 }
 
+// ------------------------------------------------------------------------------------------ NHR
+//
+// Non-uniform hierarchical ring (reference: alg_template/nonuniform_hierarchical_ring_base.cc:20-62 and the step tables
+// of temp_reduce_scatter/reduce_scatter_nhr.cc:552-590, temp_all_gather/all_gather_nhr.cc:228-260): a ring walked in
+// ceil(log2 p) steps of doubling distance that works for ANY rank count.  Reduce-scatter step k (distance d = 2^k):
+// rank r sends to r - d the partial sums of the slices  r - d, r - d - 2d, r - d - 4d, ...  (floor((p - 1 + d) / 2d)
+// of them) and receives from r + d the slices  r, r - 2d, r - 4d, ...  which it adds to its own partials; after the last
+// step slice r is complete on rank r.  All-gather runs the same steps backwards with the roles of the two lists swapped.
+uint32_t NhrSteps(uint32_t p) { uint32_t k = 0; while ((1u << k) < p) ++k; return k; }
+void NhrSlices(uint32_t p, uint32_t r, uint32_t k, std::vector<uint32_t> *sent, std::vector<uint32_t> *received)
+{
+    const uint32_t d = 1u << k, n = (p - 1 + d) / (2 * d);
+    sent->clear(); received->clear();
+    for (uint32_t i = 0; i < n; ++i) {
+        const uint64_t back = (uint64_t)i * 2 * d;
+        sent->push_back((uint32_t)(((uint64_t)r + (uint64_t)p * (back / p + 2) - d - back) % p));
+        received->push_back((uint32_t)(((uint64_t)r + (uint64_t)p * (back / p + 2) - back) % p));
+    }
+}
+
+// Reduce-scatter on accumulators in scratch: slots [0, p) hold this rank's partial sum of every block, slots from p
+// on receive (a fresh range per step, so nothing is reused inside one call).
+void ReduceScatterNhr(const CollShape &sh, Schedule &s)
+{
+    const uint32_t p = sh.nRanks, steps = NhrSteps(p);
+    s.name = "ReduceScatterNHR";
+    SetRsLayouts(sh, s);
+    FinishScratch(s, 2 * p, sh.elemSize);
+    for (uint32_t r = 0; r < p; ++r) {
+        if (!WantRank(sh, r)) continue;
+        Emit e(s.ranks[r]);
+        if (p == 1) { e.Copy(IN, 0, OUT, 0, 1, OUT, 0); continue; }
+        for (uint32_t k = 0; k < steps; ++k) e.Post((r + (1u << k)) % p, N_READY);        // to the ranks that will write into my scratch
+        e.Copy(IN, 0, SCR, 0, p, IN, 0);
+        uint32_t slot = p;
+        std::vector<uint32_t> tx, rx;
+        for (uint32_t k = 0; k < steps; ++k) {
+            e.step = (uint8_t)(1 + k);
+            const uint32_t d = 1u << k, to = (r + p - d % p) % p, from = (r + d) % p;
+            NhrSlices(p, r, k, &tx, &rx);
+            e.Wait(to, N_READY);
+            for (uint32_t i = 0; i < tx.size(); ++i) e.Write(to, SCR, tx[i], slot + i, 1, IN, tx[i]);
+            e.Post(to, N_DATA);
+            e.Wait(from, N_DATA);
+            for (uint32_t i = 0; i < rx.size(); ++i) e.Reduce(SCR, slot + i, SCR, rx[i], 1, IN, rx[i]);
+            slot += (uint32_t)tx.size();
+        }
+        e.Copy(SCR, r, OUT, 0, 1, OUT, 0);
+    }
+}
+
+// All-gather in the caller's output: the steps of the reduce-scatter backwards, data flowing the other way.
+void AllGatherNhr(const CollShape &sh, Schedule &s)
+{
+    const uint32_t p = sh.nRanks, steps = NhrSteps(p);
+    s.name = "AllGatherNHR";
+    SetAgLayouts(sh, s);
+    FinishScratch(s, p, sh.elemSize);
+    for (uint32_t r = 0; r < p; ++r) {
+        if (!WantRank(sh, r)) continue;
+        Emit e(s.ranks[r]);
+        e.Copy(IN, 0, OUT, r, 1, OUT, r);
+        if (p == 1) continue;
+        for (uint32_t k = 0; k < steps; ++k) e.Post((r + p - (1u << k) % p) % p, N_READY);
+        uint32_t slot = 0;
+        std::vector<uint32_t> have, get;
+        for (uint32_t k = steps; k-- > 0;) {
+            e.step = (uint8_t)(steps - k);
+            const uint32_t d = 1u << k, to = (r + d) % p, from = (r + p - d % p) % p;
+            NhrSlices(p, r, k, &get, &have);                 // what I received in the reduce-scatter I now own and send
+            e.Wait(to, N_READY);
+            for (uint32_t i = 0; i < have.size(); ++i) e.Write(to, OUT, have[i], slot + i, 1, OUT, have[i]);
+            e.Post(to, N_DATA);
+            e.Wait(from, N_DATA);
+            for (uint32_t i = 0; i < get.size(); ++i) e.Copy(SCR, slot + i, OUT, get[i], 1, OUT, get[i]);
+            slot += (uint32_t)have.size();
+        }
+    }
+}
+
+// All-reduce = NHR reduce-scatter on the output's slices followed by NHR all-gather.
+void AllReduceNhr(const CollShape &sh, Schedule &s)
+{
+    const uint32_t p = sh.nRanks, steps = NhrSteps(p);
+    s.name = "AllReduceNHR";
+    s.input.resize(1); s.output.resize(1);
+    Uniform(s.input[0], p, sh.count, sh.elemSize); Uniform(s.output[0], p, sh.count, sh.elemSize);
+    FinishScratch(s, 2 * p, sh.elemSize);
+    for (uint32_t r = 0; r < p; ++r) {
+        if (!WantRank(sh, r)) continue;
+        Emit e(s.ranks[r]);
+        e.Copy(IN, 0, OUT, 0, p, OUT, 0);
+        if (p == 1) continue;
+        for (uint32_t k = 0; k < steps; ++k) { e.Post((r + (1u << k)) % p, N_READY); e.Post((r + p - (1u << k) % p) % p, N_READY); }
+        uint32_t slot = 0;
+        std::vector<uint32_t> tx, rx;
+        for (uint32_t k = 0; k < steps; ++k) {
+            e.step = (uint8_t)(1 + k);
+            const uint32_t d = 1u << k, to = (r + p - d % p) % p, from = (r + d) % p;
+            NhrSlices(p, r, k, &tx, &rx);
+            e.Wait(to, N_READY);
+            for (uint32_t i = 0; i < tx.size(); ++i) e.Write(to, OUT, tx[i], slot + i, 1, OUT, tx[i]);
+            e.Post(to, N_DATA);
+            e.Wait(from, N_DATA);
+            for (uint32_t i = 0; i < rx.size(); ++i) e.Reduce(SCR, slot + i, OUT, rx[i], 1, OUT, rx[i]);
+            slot += (uint32_t)tx.size();
+        }
+        for (uint32_t k = steps; k-- > 0;) {
+            e.step = (uint8_t)(2 * steps - k);
+            const uint32_t d = 1u << k, to = (r + d) % p, from = (r + p - d % p) % p;
+            NhrSlices(p, r, k, &rx, &tx);
+            e.Wait(to, N_READY);
+            for (uint32_t i = 0; i < tx.size(); ++i) e.Write(to, OUT, tx[i], slot + i, 1, OUT, tx[i]);
+            e.Post(to, N_DATA);
+            e.Wait(from, N_DATA);
+            for (uint32_t i = 0; i < rx.size(); ++i) e.Copy(SCR, slot + i, OUT, rx[i], 1, OUT, rx[i]);
+            slot += (uint32_t)tx.size();
+        }
+    }
+}
+
+// Reduce-scatter along the Bruck tree, the all-gather's dissemination run backwards: accumulator slot j of rank r holds
+// the partial sum of block (r + j) mod p; for d = largest power of two below p down to 1, slots [d, d + min(d, p - d))
+// go to rank r + d, which adds them to its slots [0, min(d, p - d)).  Slot 0 ends as the complete block r.
+void ReduceScatterBruck(const CollShape &sh, Schedule &s)
+{
+    const uint32_t p = sh.nRanks;
+    s.name = "ReduceScatterBruck";
+    SetRsLayouts(sh, s);
+    FinishScratch(s, 2 * p, sh.elemSize);
+    for (uint32_t r = 0; r < p; ++r) {
+        if (!WantRank(sh, r)) continue;
+        Emit e(s.ranks[r]);
+        if (p == 1) { e.Copy(IN, 0, OUT, 0, 1, OUT, 0); continue; }
+        for (uint32_t d = 1; d < p; d *= 2) e.Post((r + p - d) % p, N_READY);
+        for (uint32_t j = 0; j < p; ++j) e.Copy(IN, (r + j) % p, SCR, j, 1, IN, (r + j) % p);
+        uint32_t top = 1;
+        while (top * 2 < p) top *= 2;
+        uint32_t slot = p;
+        uint8_t st = 1;
+        for (uint32_t d = top; d >= 1; d /= 2, ++st) {
+            e.step = st;
+            const uint32_t cnt = std::min(d, p - d), to = (r + d) % p, from = (r + p - d) % p;
+            e.Wait(to, N_READY);
+            for (uint32_t j = 0; j < cnt; ++j) e.Write(to, SCR, d + j, slot + j, 1, IN, (r + d + j) % p);
+            e.Post(to, N_DATA);
+            e.Wait(from, N_DATA);
+            for (uint32_t j = 0; j < cnt; ++j) e.Reduce(SCR, slot + j, SCR, j, 1, IN, (r + j) % p);
+            slot += cnt;
+            if (d == 1) break;
+        }
+        e.Copy(SCR, 0, OUT, 0, 1, OUT, 0);
+    }
+}
+
 // ------------------------------------------------------------------------------------- AlltoAll
 
 void SetA2aLayouts(const CollShape &sh, Schedule &s)
@@ -843,12 +1000,12 @@ std::vector<Algo> AlgosFor(HcclCMDType cmd, uint32_t nRanks)
 {
     bool pow2 = nRanks != 0 && (nRanks & (nRanks - 1)) == 0;
     switch (cmd) {
-        case HCCL_CMD_ALLREDUCE: return {Algo::MESH, Algo::MESH_ONESHOT, Algo::RING, Algo::HD};
+        case HCCL_CMD_ALLREDUCE: return {Algo::MESH, Algo::MESH_ONESHOT, Algo::RING, Algo::HD, Algo::NHR};
         case HCCL_CMD_REDUCE_SCATTER:
-            return pow2 ? std::vector<Algo>{Algo::MESH, Algo::RING, Algo::HD} : std::vector<Algo>{Algo::MESH, Algo::RING};
-        case HCCL_CMD_REDUCE_SCATTER_V: return {Algo::MESH, Algo::RING};
+            return pow2 ? std::vector<Algo>{Algo::MESH, Algo::RING, Algo::HD, Algo::NHR, Algo::BRUCK} : std::vector<Algo>{Algo::MESH, Algo::RING, Algo::NHR, Algo::BRUCK};
+        case HCCL_CMD_REDUCE_SCATTER_V: return {Algo::MESH, Algo::RING, Algo::NHR, Algo::BRUCK};
         case HCCL_CMD_ALLGATHER: case HCCL_CMD_ALLGATHER_V:
-            return pow2 ? std::vector<Algo>{Algo::MESH, Algo::RING, Algo::HD, Algo::BRUCK} : std::vector<Algo>{Algo::MESH, Algo::RING, Algo::BRUCK};
+            return pow2 ? std::vector<Algo>{Algo::MESH, Algo::RING, Algo::HD, Algo::BRUCK, Algo::NHR} : std::vector<Algo>{Algo::MESH, Algo::RING, Algo::BRUCK, Algo::NHR};
         case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC: return {Algo::MESH, Algo::PAIRWISE};
         case HCCL_CMD_BROADCAST: return {Algo::MESH, Algo::MESH_ONESHOT, Algo::RING, Algo::TREE};
         case HCCL_CMD_REDUCE: return {Algo::MESH, Algo::RING, Algo::TREE};
@@ -877,12 +1034,15 @@ bool BuildSchedule(const CollShape &sh, Algo algo, Schedule *out, std::string *w
             else if (algo == Algo::MESH || algo == Algo::AUTO) AllReduceTwoShot(sh, s);
             else if (algo == Algo::RING) AllReduceRing(sh, s);
             else if (algo == Algo::HD) AllReduceHD(sh, s);
+            else if (algo == Algo::NHR) AllReduceNhr(sh, s);
             else unsupported();
             break;
         case HCCL_CMD_REDUCE_SCATTER: case HCCL_CMD_REDUCE_SCATTER_V:
             if (algo == Algo::MESH || algo == Algo::AUTO) ReduceScatterMesh(sh, s);
             else if (algo == Algo::RING) ReduceScatterRing(sh, s);
             else if (algo == Algo::HD) ok = ReduceScatterHD(sh, s, why);
+            else if (algo == Algo::NHR) ReduceScatterNhr(sh, s);
+            else if (algo == Algo::BRUCK) ReduceScatterBruck(sh, s);
             else unsupported();
             break;
         case HCCL_CMD_ALLGATHER: case HCCL_CMD_ALLGATHER_V:
@@ -890,6 +1050,7 @@ bool BuildSchedule(const CollShape &sh, Algo algo, Schedule *out, std::string *w
             else if (algo == Algo::RING) AllGatherRing(sh, s);
             else if (algo == Algo::HD) ok = AllGatherHD(sh, s, why);
             else if (algo == Algo::BRUCK) AllGatherBruck(sh, s);
+            else if (algo == Algo::NHR) AllGatherNhr(sh, s);
             else unsupported();
             break;
         case HCCL_CMD_ALLTOALL: case HCCL_CMD_ALLTOALLV: case HCCL_CMD_ALLTOALLVC:
@@ -901,13 +1062,13 @@ bool BuildSchedule(const CollShape &sh, Algo algo, Schedule *out, std::string *w
             if (algo == Algo::MESH_ONESHOT || algo == Algo::STAR) BroadcastOneShot(sh, s);
             else if (algo == Algo::MESH || algo == Algo::AUTO) BroadcastTwoShot(sh, s);
             else if (algo == Algo::RING) BroadcastRing(sh, s);
-            else if (algo == Algo::TREE || algo == Algo::HD || algo == Algo::BRUCK) BroadcastTree(sh, s);
+            else if (algo == Algo::TREE || algo == Algo::HD || algo == Algo::BRUCK || algo == Algo::NHR) BroadcastTree(sh, s);
             else unsupported();
             break;
         case HCCL_CMD_REDUCE:
             if (algo == Algo::MESH || algo == Algo::AUTO) ReduceMesh(sh, s);
             else if (algo == Algo::RING) ReduceRing(sh, s);
-            else if (algo == Algo::TREE || algo == Algo::HD) ReduceTree(sh, s);
+            else if (algo == Algo::TREE || algo == Algo::HD || algo == Algo::NHR) ReduceTree(sh, s);
             else unsupported();
             break;
         case HCCL_CMD_SCATTER:

@@ -29,7 +29,7 @@ namespace hc {
 
 enum Notify : uint16_t { N_READY = 0, N_DATA = 1, N_FIN = 2, N_DONE = 3, N_COUNT = 4 };
 
-enum class Algo : uint8_t { AUTO = 0, MESH, MESH_ONESHOT, RING, HD, BRUCK, PAIRWISE, TREE, NVLS, STAR };
+enum class Algo : uint8_t { AUTO = 0, MESH, MESH_ONESHOT, RING, HD, BRUCK, PAIRWISE, TREE, NVLS, STAR, NHR };
 const char *AlgoName(Algo a);
 // Accepts the reference's spellings: ring, fullmesh, H-D_R, pairwise, NHR, NHR_V1, NB, AHC, AHC_BROKE, pipeline, null.
 bool ParseAlgoName(const std::string &s, Algo *out);

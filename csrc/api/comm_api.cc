@@ -454,7 +454,7 @@ HcclResult CommClearSyncState(Comm *c, Bootstrap::Group &g)
     CHK_RET(P->MemsetSync(c->LocalHeap(), 0, HC_CTRL_BYTES));
     CHK_RET(P->MemsetSync(c->LocalHeap() + c->llOffset, 0, c->llBytes));
     CHK_RET(P->MemsetSync(c->devCounters, 0, 128 * sizeof(uint32_t)));
-    CHK_RET(P->MemsetSync(c->devIrCounters, 0, 2ull * HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY * sizeof(uint64_t)));
+    CHK_RET(P->MemsetSync(c->devIrCounters, 0, 2ull * HC_IR_MAX_CTAS * HC_IR_RANKS * HC_IR_NOTIFY * sizeof(uint64_t)));
     std::fill(c->chanWaited.begin(), c->chanWaited.end(), 0);
     std::fill(c->p2pSent.begin(), c->p2pSent.end(), 0);
     std::fill(c->p2pRecvd.begin(), c->p2pRecvd.end(), 0);

@@ -253,7 +253,7 @@ static HcclResult SetupDeviceState(Comm *c)
     c->devStruct = (CommDev *)p;
     c->devCounters = (uint32_t *)((char *)p + HC_DEV_COUNTERS_OFFSET);
     c->opCounters = (uint64_t *)((char *)p + HC_DEV_OPCOUNTERS_OFFSET);
-    size_t irBytes = 2ull * HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY * sizeof(uint64_t);
+    size_t irBytes = 2ull * HC_IR_MAX_CTAS * HC_IR_RANKS * HC_IR_NOTIFY * sizeof(uint64_t);
     CHK_RET(P->DevAlloc(irBytes, &p));
     c->devIrCounters = (uint64_t *)p;
     CHK_RET(P->MemsetSync(p, 0, irBytes));
@@ -273,7 +273,7 @@ static HcclResult SetupDeviceState(Comm *c)
     d.epoch = c->devCounters;
     d.launches = c->devCounters + 1;
     d.blocksDone = c->devCounters + 2;
-    d.irConsumed = c->devIrCounters + (size_t)HC_IR_MAX_CTAS * HC_MAX_RANKS * HC_IR_NOTIFY;
+    d.irConsumed = c->devIrCounters + (size_t)HC_IR_MAX_CTAS * HC_IR_RANKS * HC_IR_NOTIFY;
     d.abortWord = c->abortWord;
     d.status = c->waitStatus;
     d.opCounters = c->opCounters;

@@ -1037,87 +1037,80 @@ __global__ void __launch_bounds__(512) KSmallLL(const __grid_constant__ CollArgs
 // [cta][from][slot] in the control region and consumes posts with device-resident counters (they survive the launch,
 // a wait expects one more post than the previous wait on that word).  Primitives run in program order, which is the
 // order the host engine runs them in on one stream.
+// Moves (or reduces into dst) n elements.  CTA c owns the blocks b with b % gridDim.x == c, a block being kIrBlock
+// elements counted from the start of the slice (so ownership does not depend on buffer alignment and is the same in every
+// primitive of a program).  A CTA walks its blocks kIrUnroll at a time: every thread keeps one 16-byte load (two when it
+// reduces) per block of the batch in flight, which is what hides NVLink and HBM latency with the few CTAs these
+// kernels run on.
+constexpr uint64_t kIrBlock = 4096;
+constexpr int kIrUnroll = 4;
+template <typename T> struct IrBits { using type = T; };
+template <> struct IrBits<__half> { using type = unsigned short; };
+template <> struct IrBits<__nv_bfloat16> { using type = unsigned short; };
+template <typename T>
+__device__ __forceinline__ T IrCombineBits(int op, typename IrBits<T>::type d, typename IrBits<T>::type s)
+{
+    using A = typename AccOf<T>::type;
+    T dv, sv;
+    memcpy(&dv, &d, sizeof(T)); memcpy(&sv, &s, sizeof(T));
+    return Narrow<T>(Combine<A>(op, Widen<T>(dv), Widen<T>(sv)));
+}
 template <typename T>
 __device__ __forceinline__ void IrMove(char *dst, const char *src, uint64_t n, bool reduce, int op)
 {
     using A = typename AccOf<T>::type;
-    constexpr uint64_t kBlock = 2048;
+    using B = typename IrBits<T>::type;
     constexpr int N = Pack<T>::N;
-    const uint64_t nBlocks = (n + kBlock - 1) / kBlock;
-    for (uint64_t b = blockIdx.x; b < nBlocks; b += gridDim.x) {
-        const uint64_t e0 = b * kBlock, cnt = n - e0 < kBlock ? n - e0 : kBlock;
-        const char *ps = src + e0 * sizeof(T);
-        char *pd = dst + e0 * sizeof(T);
-        uint64_t done = 0;
-        if ((((uintptr_t)ps | (uintptr_t)pd) & 15) == 0) {
-            const uint64_t nvec = cnt / N;
-            for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
-                Pack<T> s;
-                s.v = Ld16Volatile(ps + (v << 4));
-                if (reduce) {
-                    Pack<T> t;
-                    t.v = Ld16Volatile(pd + (v << 4));
+    HC_BOUNDS_OR_RETURN(dst, n * sizeof(T));
+    HC_BOUNDS_OR_RETURN(src, n * sizeof(T));
+    const uint64_t nBlocks = (n + kIrBlock - 1) / kIrBlock;
+    const bool aligned = ((((uintptr_t)src | (uintptr_t)dst) & 15) == 0) && (kIrBlock * sizeof(T)) % 16 == 0;
+    for (uint64_t b0 = blockIdx.x; b0 < nBlocks; b0 += (uint64_t)kIrUnroll * gridDim.x) {
+        if (aligned) {
+            // vectors of the batch's blocks, thread-strided inside each block
+            constexpr uint64_t kVecs = kIrBlock / N;
+            for (uint64_t v = threadIdx.x; v < kVecs; v += blockDim.x) {
+                Pack<T> s[kIrUnroll], t[kIrUnroll];
+                bool live[kIrUnroll];
 #pragma unroll
-                    for (int j = 0; j < N; ++j) t.e[j] = Narrow<T>(Combine<A>(op, Widen<T>(t.e[j]), Widen<T>(s.e[j])));
-                    s = t;
+                for (int u = 0; u < kIrUnroll; ++u) {
+                    const uint64_t b = b0 + (uint64_t)u * gridDim.x, e = b * kIrBlock + v * N;
+                    live[u] = b < nBlocks && e + N <= n;
+                    if (live[u]) {
+                        s[u].v = Ld16Volatile(src + e * sizeof(T));
+                        if (reduce) t[u].v = Ld16Volatile(dst + e * sizeof(T));
+                    }
                 }
-                St16(pd + (v << 4), s.v);
+#pragma unroll
+                for (int u = 0; u < kIrUnroll; ++u) {
+                    if (!live[u]) continue;
+                    const uint64_t e = (b0 + (uint64_t)u * gridDim.x) * kIrBlock + v * N;
+                    if (reduce) {
+#pragma unroll
+                        for (int j = 0; j < N; ++j) s[u].e[j] = Narrow<T>(Combine<A>(op, Widen<T>(t[u].e[j]), Widen<T>(s[u].e[j])));
+                    }
+                    St16(dst + e * sizeof(T), s[u].v);
+                }
             }
-            done = nvec * N;
         }
-        for (uint64_t e = done + threadIdx.x; e < cnt; e += blockDim.x) {
-            T s = *(volatile const T *)(ps + e * sizeof(T));
-            if (reduce) s = Narrow<T>(Combine<A>(op, Widen<T>(*(volatile const T *)(pd + e * sizeof(T))), Widen<T>(s)));
-            *(T *)(pd + e * sizeof(T)) = s;
+        // elements no vector covered: everything when the buffers are not 16-byte aligned, else the ragged end of the slice
+        for (int u = 0; u < kIrUnroll; ++u) {
+            const uint64_t b = b0 + (uint64_t)u * gridDim.x;
+            if (b >= nBlocks) break;
+            const uint64_t e0 = b * kIrBlock, cnt = n - e0 < kIrBlock ? n - e0 : kIrBlock;
+            const uint64_t done = aligned ? cnt / N * N : 0;
+            for (uint64_t e = e0 + done + threadIdx.x; e < e0 + cnt; e += blockDim.x) {
+                B sb = *(volatile const B *)(src + e * sizeof(T));
+                if (reduce) {
+                    const B db = *(volatile const B *)(dst + e * sizeof(T));
+                    T r = IrCombineBits<T>(op, db, sb);
+                    memcpy(&sb, &r, sizeof(T));
+                }
+                *(B *)(dst + e * sizeof(T)) = sb;
+            }
         }
     }
 }
-template <> __device__ __forceinline__ void IrMove<__half>(char *dst, const char *src, uint64_t n, bool reduce, int op);
-template <> __device__ __forceinline__ void IrMove<__nv_bfloat16>(char *dst, const char *src, uint64_t n, bool reduce, int op);
-
-// 16-bit floating types: the scalar tail goes through their bit patterns (volatile class-type loads do not compile)
-template <typename T>
-__device__ __forceinline__ void IrMoveHalfLike(char *dst, const char *src, uint64_t n, bool reduce, int op)
-{
-    constexpr uint64_t kBlock = 2048;
-    constexpr int N = 8;
-    const uint64_t nBlocks = (n + kBlock - 1) / kBlock;
-    for (uint64_t b = blockIdx.x; b < nBlocks; b += gridDim.x) {
-        const uint64_t e0 = b * kBlock, cnt = n - e0 < kBlock ? n - e0 : kBlock;
-        const char *ps = src + e0 * 2;
-        char *pd = dst + e0 * 2;
-        uint64_t done = 0;
-        if ((((uintptr_t)ps | (uintptr_t)pd) & 15) == 0) {
-            const uint64_t nvec = cnt / N;
-            for (uint64_t v = threadIdx.x; v < nvec; v += blockDim.x) {
-                Pack<T> s;
-                s.v = Ld16Volatile(ps + (v << 4));
-                if (reduce) {
-                    Pack<T> t;
-                    t.v = Ld16Volatile(pd + (v << 4));
-#pragma unroll
-                    for (int j = 0; j < N; ++j) t.e[j] = Narrow<T>(Combine<float>(op, Widen<T>(t.e[j]), Widen<T>(s.e[j])));
-                    s = t;
-                }
-                St16(pd + (v << 4), s.v);
-            }
-            done = nvec * N;
-        }
-        for (uint64_t e = done + threadIdx.x; e < cnt; e += blockDim.x) {
-            unsigned short sb = *(volatile const unsigned short *)(ps + e * 2);
-            if (reduce) {
-                unsigned short db = *(volatile const unsigned short *)(pd + e * 2);
-                T sv, dv;
-                memcpy(&sv, &sb, 2); memcpy(&dv, &db, 2);
-                T r = Narrow<T>(Combine<float>(op, Widen<T>(dv), Widen<T>(sv)));
-                memcpy(&sb, &r, 2);
-            }
-            *(unsigned short *)(pd + e * 2) = sb;
-        }
-    }
-}
-template <> __device__ __forceinline__ void IrMove<__half>(char *dst, const char *src, uint64_t n, bool reduce, int op) { IrMoveHalfLike<__half>(dst, src, n, reduce, op); }
-template <> __device__ __forceinline__ void IrMove<__nv_bfloat16>(char *dst, const char *src, uint64_t n, bool reduce, int op) { IrMoveHalfLike<__nv_bfloat16>(dst, src, n, reduce, op); }
 
 template <typename T>
 __global__ void __launch_bounds__(512) KIrInterp(const __grid_constant__ IrArgs byval, const IrArgs *emu)
@@ -1131,7 +1124,7 @@ __global__ void __launch_bounds__(512) KIrInterp(const __grid_constant__ IrArgs 
     const DevPrim *prims = (const DevPrim *)a.prims;
     const uint32_t esz = a.elemSize;
     auto Word = [&](int owner, int from, uint32_t slot) {
-        return (uint64_t *)(HcPeerHeap(d, owner) + HC_OFF_IR_NOTIFY) + ((uint64_t)blockIdx.x * HC_MAX_RANKS + (uint64_t)from) * HC_IR_NOTIFY + slot;
+        return (uint64_t *)(HcPeerHeap(d, owner) + HC_OFF_IR_NOTIFY) + ((uint64_t)blockIdx.x * HC_IR_RANKS + (uint64_t)from) * HC_IR_NOTIFY + slot;
     };
     auto Count = [&](uint32_t buf, uint32_t slice) -> uint64_t {      // elements of a slice inside the column window
         const IrLayoutDev &L = a.lay[buf];
@@ -1160,7 +1153,7 @@ __global__ void __launch_bounds__(512) KIrInterp(const __grid_constant__ IrArgs 
             case 7: {   // WAIT
                 __shared__ int okFlag;
                 if (threadIdx.x == 0) {
-                    uint64_t *consumed = d->irConsumed + ((uint64_t)blockIdx.x * HC_MAX_RANKS + (uint64_t)p.peer) * HC_IR_NOTIFY + p.notify;
+                    uint64_t *consumed = d->irConsumed + ((uint64_t)blockIdx.x * HC_IR_RANKS + (uint64_t)p.peer) * HC_IR_NOTIFY + p.notify;
                     const uint64_t expect = *consumed + 1;
                     *consumed = expect;
                     okFlag = WaitFlagGe64(d, Word(me, p.peer, p.notify), expect, (uint32_t)p.peer, HC_WAIT_CHAN_NOTIFY, p.notify) ? 1 : 0;

@@ -16,13 +16,14 @@
 #define HC_MAX_RANKS 64          /* sizing of flag tables */
 #define HC_KERNEL_MAX_RANKS 16   /* rank count the SM kernels accept (one NVLink domain) */
 #define HC_MAX_CTAS 256          /* CTAs per rank that can take part in a cross-rank barrier */
-#define HC_IR_MAX_CTAS 64        /* CTAs of the schedule-interpreter kernel */
+#define HC_IR_MAX_CTAS 128       /* CTAs of the schedule-interpreter kernel */
+#define HC_IR_RANKS 16           /* ranks the interpreter's notify tables are laid out for (= HC_KERNEL_MAX_RANKS) */
 #define HC_IR_NOTIFY 8           /* notify slots per (CTA, peer) in the interpreter */
 #define HC_CHAN_NOTIFY 64        /* notify slots per channel on the host engines */
 
 #define HC_CTRL_BYTES (4ull << 20)
 #define HC_OFF_BARRIER 0ull                       /* u32  [HC_MAX_CTAS][HC_MAX_RANKS]                */
-#define HC_OFF_IR_NOTIFY (64ull << 10)            /* u64  [HC_IR_MAX_CTAS][HC_MAX_RANKS][HC_IR_NOTIFY] */
+#define HC_OFF_IR_NOTIFY (64ull << 10)            /* u64  [HC_IR_MAX_CTAS][HC_IR_RANKS][HC_IR_NOTIFY]: 128 KB */
 #define HC_OFF_CHAN_NOTIFY (384ull << 10)         /* u64  [HC_MAX_RANKS][HC_CHAN_NOTIFY]              */
 #define HC_OFF_P2P (448ull << 10)                 /* u64  [HC_MAX_RANKS][8] send/recv handshakes      */
 #define HC_OFF_META (480ull << 10)                /* u64  [HC_MAX_RANKS] per-operator values agreed in-kernel */
@@ -53,7 +54,7 @@ struct CommDev {
     uint32_t *blocksDone;    /* device-local scratch counter */
     uint32_t profile;        /* non-zero: kernels record start / end timestamps in the ring at HC_DEV_TIMES_OFFSET */
     uint32_t heapMB;         /* size of one rank's heap in MB (range checks of the bounds-checking build) */
-    uint64_t *irConsumed;    /* device-local [HC_IR_MAX_CTAS][HC_MAX_RANKS][HC_IR_NOTIFY]: posts consumed by the interpreter's waits */
+    uint64_t *irConsumed;    /* device-local [HC_IR_MAX_CTAS][HC_IR_RANKS][HC_IR_NOTIFY]: posts consumed by the interpreter's waits */
     uint32_t *abortWord;     /* host-pinned: non-zero makes every wait return immediately */
     HcclDeviceWaitStatus *status; /* host-pinned record of the first wait that expired */
     uint64_t *opCounters;    /* device-local {head, tail}: bumped at kernel start / end (the host peeks at them to tell which operator hangs) */

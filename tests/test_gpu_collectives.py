@@ -310,3 +310,13 @@ def test_kernel_time_ring_reports_device_durations(n=2):
         assert "allreduce" in comms[0].dump().lower().replace("_", "")
     finally:
         _destroy(comms)
+
+
+def test_single_rank_operator_in_a_captured_cuda_graph():
+    """The demo of examples/02_graphs on one GPU (one rank): capture, replay with new data."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    res = subprocess.run([sys.executable, str(root / "examples" / "02_graphs" / "allreduce_cuda_graph_demo.py")], capture_output=True, text=True, timeout=240)
+    assert res.returncode == 0 and "5 replays ok" in res.stdout, res.stdout[-2000:] + res.stderr[-3000:]

@@ -60,3 +60,18 @@ def test_forced_algorithm_families_across_gpus():
         pytest.skip("needs 2 GPUs")
     codes, outs = launch("forced_algos", 2, {"HCOMM_TEST_BUFFER_MB": "8", "HCCL_EXEC_TIMEOUT": "20"}, timeout=200)
     assert codes == [0, 0], "\n".join(outs)
+
+
+def test_all_reduce_in_a_captured_cuda_graph_across_gpus():
+    """examples/02_graphs/allreduce_cuda_graph_demo.py on two GPUs: five replays of one captured all-reduce."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    if cuda_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    root = Path(__file__).resolve().parent.parent
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29671",
+           str(root / "examples" / "02_graphs" / "allreduce_cuda_graph_demo.py")]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=dict(os.environ, HCCL_EXEC_TIMEOUT="20"))
+    assert res.returncode == 0 and "5 replays ok" in res.stdout, res.stdout[-2000:] + res.stderr[-3000:]

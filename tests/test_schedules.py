@@ -50,3 +50,19 @@ def test_unsupported_combinations_are_refused():
 def test_schedule_dump_is_readable():
     rc, text = tool_str(_lib().HcommToolDumpSchedule, CMD["allreduce"], 4, b"ring", 1024, 0, 1)
     assert rc == 0 and "AllReduceRing rank 1/4" in text and "WRITE" in text and "WAIT" in text
+
+
+def test_nhr_and_bruck_reduce_scatter_are_schedules_of_their_own():
+    lib = _lib()
+    for n in range(2, 9):
+        for cmd, want in (("allreduce", "AllReduceNHR"), ("reducescatter", "ReduceScatterNHR"), ("allgather", "AllGatherNHR")):
+            rc, text = tool_str(lib.HcommToolDumpSchedule, CMD[cmd], n, b"NHR", 4096, 0, n - 1)
+            assert rc == 0 and want in text, text[:200]
+            rc, rep = tool_str(lib.HcommToolCheckSchedule, CMD[cmd], n, b"NHR", 4096 + n, 0, 0, 0)
+            assert rc == 0, rep
+        rc, text = tool_str(lib.HcommToolDumpSchedule, CMD["reducescatter"], n, b"NB", 4096, 0, 0)
+        assert rc == 0 and "ReduceScatterBruck" in text
+    # log-step: an 8-rank NHR all-reduce has 3 + 3 exchange steps where the ring has 7 + 7
+    _, nhr = tool_str(lib.HcommToolDumpSchedule, CMD["allreduce"], 8, b"NHR", 4096, 0, 0)
+    _, ring = tool_str(lib.HcommToolDumpSchedule, CMD["allreduce"], 8, b"ring", 4096, 0, 0)
+    assert nhr.count("WAIT") < ring.count("WAIT")

@@ -27,7 +27,7 @@ def test_allreduce_8_ranks_1mi_fp32_exact_sum(monkeypatch):
     destroy(comms)
 
 
-@pytest.mark.parametrize("algo", ["", "level0:ring", "level0:H-D_R", "level0:fullmesh", "allreduce=level0:mesh_oneshot/others=level0:ring"])
+@pytest.mark.parametrize("algo", ["", "level0:ring", "level0:H-D_R", "level0:NHR", "level0:fullmesh", "allreduce=level0:mesh_oneshot/others=level0:ring"])
 @pytest.mark.parametrize("n", [2, 3, 5, 8])
 def test_allreduce_algorithms(monkeypatch, algo, n):
     sim_env(monkeypatch, HCCL_ALGO=algo)
@@ -56,7 +56,7 @@ def test_allreduce_ops_in_place(monkeypatch, op, fn):
     destroy(comms)
 
 
-@pytest.mark.parametrize("algo", ["", "level0:ring", "level0:NB", "level0:pairwise"])
+@pytest.mark.parametrize("algo", ["", "level0:ring", "level0:NB", "level0:NHR", "level0:pairwise"])
 @pytest.mark.parametrize("n", [1, 4, 7])
 def test_all_collectives(monkeypatch, algo, n):
     sim_env(monkeypatch, HCCL_ALGO=algo)
