@@ -567,7 +567,7 @@ HcclResult LaunchBarrierIfNeeded(Comm *c, void *stream);   // defined in ops.cc
 // the width (a divisor of N among 256, 224, 192, 160, 128) with the least work in whole waves.
 int PickPairTileWidth(int rowBlocks, int N, int pairs)
 {
-    static const int forced = [] { const char *e = getenv("HCOMM_GEMM_BN"); return e ? atoi(e) : 0; }();
+    const int forced = ForcedPairTileWidth();
     if (forced && N % forced == 0 && forced % 32 == 0 && forced >= 128 && forced <= 256) return forced;
     int best = 0;
     long bestCost = 0;

@@ -14,6 +14,8 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
 int GemmSmCount();
 // Tile width (256, 224, 192, 160 or 128, a divisor of N) of the CTA-pair kernels with the least work in whole waves.
 int PickPairTileWidth(int rowBlocks256, int N, int pairs);
+int PairGroupRows(int K);        // rasterisation group of the CTA-pair kernels (row blocks of 256 rows)
+int ForcedPairTileWidth();       // HCOMM_GEMM_BN / HcommGemmSetTuning, 0 = automatic
 uint32_t *GemmErrorFlag();
 
 }  // namespace hc

@@ -2,6 +2,7 @@
 // used by every kernel that loads tiles with TMA.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "../core/log.h"
@@ -95,6 +96,38 @@ HcclResult MakeTensorMap2dBf16(CUtensorMap *map, const void *base, uint64_t rows
     return HCCL_SUCCESS;
 }
 
+// Row blocks (256 rows) per rasterisation group of the CTA-pair kernels.  The tiles in flight cover gm row blocks by
+// pairs / gm column blocks; the gm A panels are what consecutive waves share, so they should stay in L2.  The L2 is two
+// partitions and a panel that both halves of the chip read occupies both, so the budget is about half the nominal 126 MB.
+// HCOMM_GEMM_GM or HcommGemmSetTuning override the choice.
+namespace {
+std::atomic<int> g_forceGm{-1}, g_forceBn{-1};
+}
+int PairGroupRows(int K)
+{
+    int forced = g_forceGm.load();
+    if (forced < 0) {
+        const char *e = getenv("HCOMM_GEMM_GM");
+        forced = e ? atoi(e) : 0;
+        g_forceGm.store(forced);
+    }
+    if (forced > 0) return forced;
+    const double panelMB = 256.0 * K * 2 / (1 << 20);
+    int gm = 16;
+    while (gm > 4 && gm * panelMB > 40.0) gm /= 2;
+    return gm;
+}
+int ForcedPairTileWidth()
+{
+    int forced = g_forceBn.load();
+    if (forced < 0) {
+        const char *e = getenv("HCOMM_GEMM_BN");
+        forced = e ? atoi(e) : 0;
+        g_forceBn.store(forced);
+    }
+    return forced;
+}
+
 int GemmSmCount()
 {
     static int sms = 0;
@@ -144,7 +177,7 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * clusters, 1, 1);
         cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
-        static const int gm = [] { const char *e = getenv("HCOMM_GEMM_GM"); int v = e ? atoi(e) : 0; return v > 0 ? v : 16; }();
+        const int gm = PairGroupRows(K);
         cfg.stream = (cudaStream_t)stream;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension;
@@ -210,6 +243,12 @@ extern "C" int HcommGemmBf16(const void *A, const void *B, void *C, int M, int N
     return (int)hc::GemmBf16(A, B, C, M, N, K, lda, ldb, ldc, stream);
 }
 // Reads and clears the "a bounded wait expired inside a GEMM kernel" flag of the current device.
+// Overrides the rasterisation group (row blocks of 256 rows) and the tile width of the CTA-pair GEMM kernels; 0 = automatic.
+extern "C" void HcommGemmSetTuning(int groupRows, int tileWidth)
+{
+    hc::g_forceGm.store(groupRows > 0 ? groupRows : 0);
+    hc::g_forceBn.store(tileWidth > 0 ? tileWidth : 0);
+}
 extern "C" int HcommGemmTakeError(void)
 {
     uint32_t v = 0, zero = 0;

@@ -4,21 +4,21 @@
 // all traffic is remote stores into symmetric buffers.  The reference only offers AlltoAll(V/VC) for this
 // (pkg_inc/legacy/hccl/hccl_inner.h:55-66); routing, quantisation and the weighted sum are fused here.
 //
-// Dispatch, rank r:
-//   1. histogram of the experts its tokens chose                                  (all CTAs, grid barrier)
-//   2. publish the counts to the rank that owns each expert                       (CTA 0, cross-rank barrier)
-//   3. every CTA reads the owners' count tables and derives, for each expert, where this rank's rows start
-//      in the owner's receive buffer: rows are grouped by expert, inside an expert by source rank
-//   4. one warp per token: load 7168 bf16, per 128-value block absmax -> scale -> e4m3, then for each of
-//      the token's k experts claim a row (local atomic) and store row, scales and origin to the owner
-//   5. cross-rank barrier; the owner writes the per-expert offsets for its grouped GEMM
-// Combine, rank r (owner of experts):
-//   1. one warp per received row: send the bf16 expert output to slot (token, k) of the token's rank
-//   2. cross-rank barrier
-//   3. one warp per local token: out = sum_k gate[k] * slot(token, k), fp32 accumulation
+// Dispatch, rank r - two ordinary launches (no CTA of a launch waits for another CTA of it, so they can share the GPU
+// with expert GEMMs on other streams):
+//   route    (1 CTA)  histogram of the experts its tokens chose, the counts published to the rank that owns each expert,
+//                     one cross-rank barrier, the per-expert offsets of this rank's own experts for its grouped GEMM
+//   dispatch (N CTAs) every CTA reads the owners' count tables and derives, for each expert, where this rank's rows
+//                     start in the owner's receive buffer (rows are grouped by expert, inside an expert by source rank);
+//                     one warp per token: load 7168 bf16, per 128-value block absmax -> scale -> e4m3, lanes 0..k-1
+//                     claim the rows of the token's k experts in parallel (local atomics), then the k rows, scales and
+//                     origins leave back to back; each CTA ends with one cross-rank barrier with its namesakes
+// Combine, rank r (owner of experts) - two ordinary launches:
+//   send  one warp per received row: the bf16 expert output goes to slot (token, k) of the token's rank; cross-rank barrier
+//   sum   one warp per local token: out = sum_k gate[k] * slot(token, k) over the k that were sent, fp32 accumulation
 //
-// Device scratch (beyond inputs and outputs): per call, 2 * numExperts u32 counters (histogram and row
-// cursors) that the kernel leaves zeroed for the next call.
+// Device scratch (beyond inputs and outputs): numExperts u32 row cursors (second half of a 2 * numExperts table), cleared
+// by the route launch.
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -70,65 +70,69 @@ __device__ __forceinline__ __nv_bfloat16 *Comb(const MoeParams &p, int rank) { r
 // (masked) or the owner's receive capacity was exhausted; combine leaves such rows out of the sum
 __device__ __forceinline__ uint8_t *Valid(const MoeParams &p, int rank) { return (uint8_t *)(p.peerBuf[rank] + p.lay.offValid); }
 
+// Dispatch, first launch (one CTA per rank): routing histogram, counts published to the experts' owners, one cross-rank
+// barrier, the offsets of this rank's own experts, row cursors cleared for the second launch.
+__global__ void __launch_bounds__(1024) MoeRouteKernel(const MoeParams *table)
+{
+    const MoeParams &p = table[blockIdx.y];
+    const CommDev *d = p.dev;
+    const LaunchState ls = KernelBegin(d);
+    const int n = d->nRanks, me = d->rank;
+    const int E = p.lay.numExperts, El = E / n, K = p.lay.topk;
+    const int tid = threadIdx.x;
+    __shared__ uint32_t sHist[kMaxExperts], sTot[kMaxExperts];
+    uint32_t *cursor = p.scratch + E;
+    for (int e = tid; e < E; e += blockDim.x) { sHist[e] = 0; cursor[e] = 0; }
+    __syncthreads();
+    for (int i = tid; i < p.numTokens * K; i += blockDim.x) {
+        int e = p.topkIdx[i];
+        if (e >= 0 && e < E) atomicAdd(&sHist[e], 1u);
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += blockDim.x) Counts(p, e / El)[me * El + (e % El)] = sHist[e];
+    CrossRankBarrier(d, ls.epoch0 + 1);
+    // the offsets of my own experts for the grouped GEMM that follows (the table may be overwritten by a peer's next
+    // dispatch as soon as the second launch's barrier is passed, so derive them now): one thread per local expert sums
+    // its column, thread 0 turns the sums into a prefix
+    for (int el = tid; el < El; el += blockDim.x) {
+        const volatile uint32_t *c = Counts(p, me);
+        uint32_t sum = 0;
+        for (int s = 0; s < n; ++s) sum += c[s * El + el];
+        sTot[el] = sum;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        // every entry is clamped to the receive capacity: a grouped GEMM that walks [off[el], off[el + 1]) never leaves the buffer
+        const uint32_t capRows = (uint32_t)p.lay.maxRecvRows;
+        uint32_t acc = 0;
+        uint32_t *off = ExpertOffsets(p, me);
+        for (int el = 0; el < El; ++el) {
+            off[el] = acc < capRows ? acc : capRows;
+            acc += sTot[el];
+        }
+        off[El] = acc < capRows ? acc : capRows;
+    }
+    KernelEnd(d, ls, 1, 0);
+}
+
+// Dispatch, second launch (any number of CTAs, an ordinary launch that can share the GPU with expert GEMMs): every CTA
+// derives from the owners' count tables where this rank's rows of each expert start, then quantises and sends its
+// tokens, one warp per token, and meets its namesakes on the other ranks once all of its rows are on their way.
 __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
 {
     const MoeParams &p = table[blockIdx.y];
     const CommDev *d = p.dev;
-    cg::grid_group grid = cg::this_grid();
     const LaunchState ls = KernelBegin(d);
     const int n = d->nRanks, me = d->rank;
     const int E = p.lay.numExperts, El = E / n, K = p.lay.topk, H = p.lay.hidden;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int warpsPerCta = blockDim.x >> 5;
     __shared__ uint32_t sBase[kMaxExperts], sTot[kMaxExperts];
-    uint32_t *hist = p.scratch, *cursor = p.scratch + E;
+    uint32_t *cursor = p.scratch + E;
 
-    // 1. histogram
-    for (int e = tid; e < E; e += blockDim.x) sBase[e] = 0;
-    __syncthreads();
-    for (int i = blockIdx.x * blockDim.x + tid; i < p.numTokens * K; i += gridDim.x * blockDim.x) {
-        int e = p.topkIdx[i];
-        if (e >= 0 && e < E) atomicAdd(&sBase[e], 1u);
-    }
-    __syncthreads();
-    for (int e = tid; e < E; e += blockDim.x)
-        if (sBase[e]) atomicAdd(&hist[e], sBase[e]);
-    grid.sync();
-
-    // 2. publish my counts to the owners; CTA 0 of every rank meets, then releases the rest of its grid
-    uint32_t used = 0;
-    ++used;
-    if (blockIdx.x == 0) {
-        for (int e = tid; e < E; e += blockDim.x) Counts(p, e / El)[me * El + (e % El)] = hist[e];
-        CrossRankBarrier(d, ls.epoch0 + used);
-        // the offsets of my own experts for the grouped GEMM that follows (the table may be overwritten by a
-        // peer's next dispatch as soon as this kernel's last barrier is passed, so derive them now): one thread per
-        // local expert sums its column, thread 0 turns the sums into a prefix
-        for (int el = tid; el < El; el += blockDim.x) {
-            const volatile uint32_t *c = Counts(p, me);
-            uint32_t sum = 0;
-            for (int s = 0; s < n; ++s) sum += c[s * El + el];
-            sTot[el] = sum;
-        }
-        __syncthreads();
-        if (tid == 0) {
-            uint32_t acc = 0;
-            uint32_t *off = ExpertOffsets(p, me);
-            // every entry is clamped to the receive capacity: a grouped GEMM that walks [off[el], off[el + 1]) never leaves the buffer
-            const uint32_t capRows = (uint32_t)p.lay.maxRecvRows;
-            for (int el = 0; el < El; ++el) {
-                off[el] = acc < capRows ? acc : capRows;
-                acc += sTot[el];
-            }
-            off[El] = acc < capRows ? acc : capRows;
-        }
-        __syncthreads();
-    }
-    grid.sync();
-
-    // 3. where do my rows of expert e start at its owner?  before them: all rows of the owner's earlier experts,
-    //    and the rows of this expert that come from lower ranks.  One thread per expert fetches that expert's n
-    //    counts from the owner (independent loads, one NVLink round trip), then the prefix runs on shared memory.
+    // where do my rows of expert e start at its owner?  before them: all rows of the owner's earlier experts,
+    // and the rows of this expert that come from lower ranks.  One thread per expert fetches that expert's n
+    // counts from the owner (independent loads, one NVLink round trip), then the prefix runs on shared memory.
     for (int e = tid; e < E; e += blockDim.x) {
         const int owner = e / El, el = e % El;
         const volatile uint32_t *c = Counts(p, owner);
@@ -150,15 +154,28 @@ __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
     }
     __syncthreads();
 
-    // 4. quantise and send, one warp per token
+    // quantise and send, one warp per token
     const int chunks = H / 16;                       // 16 values (32 bytes in, 16 bytes out) per lane step
     const int blocksPerRow = H / kBlock;
     for (int t = blockIdx.x * warpsPerCta + warp; t < p.numTokens; t += gridDim.x * warpsPerCta) {
+        // lane k claims the row of the token's k-th expert while the other lanes already load the token
+        int myExpert = -1;
+        uint32_t mySlot = 0xffffffffu;
+        if (lane < K) {
+            myExpert = p.topkIdx[t * K + lane];
+            if (myExpert >= 0 && myExpert < E) {
+                mySlot = sBase[myExpert] + atomicAdd(&cursor[myExpert], 1u);
+                if (mySlot >= (uint32_t)p.lay.maxRecvRows) { atomicAdd(p.overflow, 1u); mySlot = 0xffffffffu; }
+            }
+            Valid(p, me)[t * K + lane] = mySlot != 0xffffffffu ? 1 : 0;
+        }
         const __nv_bfloat16 *src = p.x + (size_t)t * H;
-        uint4 q[16];                                 // up to 16 chunks per lane: hidden <= 8192
+        uint4 q[16];                                 // up to 16 chunks per lane: hidden <= 8192; fully unrolled so that they stay in registers
         float sc[16];
-        int nq = 0;
-        for (int c = lane; c < chunks; c += 32, ++nq) {
+#pragma unroll
+        for (int nq = 0; nq < 16; ++nq) {
+            const int c = lane + 32 * nq;
+            if (c >= chunks) break;
             const uint4 a = *(const uint4 *)(src + c * 16), b = *(const uint4 *)(src + c * 16 + 8);
             float v[16];
             const __nv_bfloat162 *pa = (const __nv_bfloat162 *)&a, *pb = (const __nv_bfloat162 *)&b;
@@ -185,82 +202,99 @@ __global__ void __launch_bounds__(512) MoeDispatchKernel(const MoeParams *table)
             }
             q[nq] = make_uint4(w[0], w[1], w[2], w[3]);
         }
+        // the token's rows leave back to back: nothing but stores between the first and the last
         for (int k = 0; k < K; ++k) {
-            const int e = p.topkIdx[t * K + k];
-            if (e < 0 || e >= E) {
-                if (lane == 0) Valid(p, me)[t * K + k] = 0;
-                continue;
-            }
+            const int e = __shfl_sync(0xffffffffu, myExpert, k);
+            const uint32_t slot = __shfl_sync(0xffffffffu, mySlot, k);
+            if (slot == 0xffffffffu) continue;
             const int owner = e / El;
-            uint32_t slot = 0;
-            if (lane == 0) slot = sBase[e] + atomicAdd(&cursor[e], 1u);
-            slot = __shfl_sync(0xffffffffu, slot, 0);
-            if (slot >= (uint32_t)p.lay.maxRecvRows) {
-                if (lane == 0) { atomicAdd(p.overflow, 1u); Valid(p, me)[t * K + k] = 0; }
-                continue;
-            }
-            if (lane == 0) Valid(p, me)[t * K + k] = 1;
             uint8_t *row = Rows(p, owner) + (size_t)slot * H;
             float *srow = Scales(p, owner) + (size_t)slot * blocksPerRow;
-            int i = 0;
-            for (int c = lane; c < chunks; c += 32, ++i) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int c = lane + 32 * i;
+                if (c >= chunks) break;
                 *(uint4 *)(row + c * 16) = q[i];
                 if ((lane & 7) == 0) srow[c / 8] = sc[i];
             }
             if (lane == 0) Origin(p, owner)[slot] = ((uint64_t)me << 32) | (uint32_t)(t * K + k);
         }
     }
-
-    // 5. all rows have landed everywhere; scratch back to zero for the next call
-    CrossRankBarrier(d, ls.epoch0 + (++used));
-    grid.sync();
-    if (blockIdx.x == 0)
-        for (int e = tid; e < 2 * E; e += blockDim.x) p.scratch[e] = 0;
-    KernelEnd(d, ls, used);
+    // all rows of this CTA are on their way; once every local CTA has passed its barrier (= the kernel has ended) all
+    // CTAs of all ranks have sent
+    CrossRankBarrier(d, ls.epoch0 + 1);
+    KernelEnd(d, ls, 1);
 }
 
-__global__ void __launch_bounds__(512) MoeCombineKernel(const MoeParams *table)
+// Combine, first launch: every expert output row goes home, into slot (token, k) of the token's rank; each CTA then
+// meets its namesakes on the other ranks.  When the kernel has ended on a rank, every rank's rows for it have landed.
+__global__ void __launch_bounds__(512) MoeCombineSendKernel(const MoeParams *table)
 {
     const MoeParams &p = table[blockIdx.y];
     const CommDev *d = p.dev;
     const LaunchState ls = KernelBegin(d);
     const int n = d->nRanks, me = d->rank;
-    const int El = p.lay.numExperts / n, K = p.lay.topk, H = p.lay.hidden;
+    const int El = p.lay.numExperts / n, H = p.lay.hidden;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warpsPerCta = blockDim.x >> 5;
     const int rows = (int)ExpertOffsets(p, me)[El];
     const int vecs = H / 8;                          // 16-byte vectors of bf16 per row
-
-    // 1. send every expert output row home
     for (int r = blockIdx.x * warpsPerCta + warp; r < rows; r += gridDim.x * warpsPerCta) {
         const uint64_t o = Origin(p, me)[r];
         const int src = (int)(o >> 32);
         const uint32_t tk = (uint32_t)o;
         const uint4 *in = (const uint4 *)(p.y + (size_t)r * H);
         uint4 *dst = (uint4 *)(Comb(p, src) + (size_t)tk * H);
-        for (int v = lane; v < vecs; v += 32) dst[v] = in[v];
+        // eight loads of the row in flight per lane, then their stores back to back
+        for (int v0 = lane; v0 < vecs; v0 += 32 * 8) {
+            uint4 buf[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (v0 + 32 * u < vecs) buf[u] = in[v0 + 32 * u];
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (v0 + 32 * u < vecs) dst[v0 + 32 * u] = buf[u];
+        }
     }
-    uint32_t used = 0;
-    CrossRankBarrier(d, ls.epoch0 + (++used));
-    // A CTA's barrier only pairs it with the same-index CTA of the other ranks, but the rows of one token come from
-    // arbitrary CTAs of their owners: once ALL local CTAs have passed their barrier, all CTAs of all ranks have sent.
-    cg::this_grid().sync();
+    CrossRankBarrier(d, ls.epoch0 + 1);
+    KernelEnd(d, ls, 1);
+}
 
-    // 2. gate-weighted sum per local token
+// Combine, second launch (local): gate-weighted sum of the K landing slots of every local token, fp32 accumulation.
+__global__ void __launch_bounds__(512) MoeCombineSumKernel(const MoeParams *table)
+{
+    const MoeParams &p = table[blockIdx.y];
+    const int me = p.dev->rank;
+    const int K = p.lay.topk, H = p.lay.hidden;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warpsPerCta = blockDim.x >> 5;
+    const int vecs = H / 8;
     for (int t = blockIdx.x * warpsPerCta + warp; t < p.numTokens; t += gridDim.x * warpsPerCta) {
         float g[16];
         bool live[16];
-        for (int k = 0; k < K; ++k) { g[k] = p.gates[t * K + k]; live[k] = Valid(p, me)[t * K + k] != 0; }
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            live[k] = k < K && Valid(p, me)[t * K + k] != 0;
+            g[k] = live[k] ? p.gates[t * K + k] : 0.f;
+        }
         for (int v = lane; v < vecs; v += 32) {
             float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            for (int k = 0; k < K; ++k) {
-                if (!live[k]) continue;                     // nothing was sent for this (token, k): the slot holds an older step's row
-                const uint4 pk = Ld16Volatile((const char *)(Comb(p, me) + ((size_t)t * K + k) * H) + (size_t)v * 16);
-                const __nv_bfloat162 *ph = (const __nv_bfloat162 *)&pk;
+            // eight rows of this column at a time: eight independent loads in flight (fully unrolled: registers, not local memory)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    float2 f = __bfloat1622float2(ph[j]);
-                    acc[2 * j] += g[k] * f.x;
-                    acc[2 * j + 1] += g[k] * f.y;
+            for (int kb = 0; kb < 16; kb += 8) {
+                if (kb >= K) break;
+                uint4 pk[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (live[kb + k]) pk[k] = Ld16Volatile((const char *)(Comb(p, me) + ((size_t)t * K + kb + k) * H) + (size_t)v * 16);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    if (!live[kb + k]) continue;            // nothing was sent for this (token, k): the slot holds an older step's row
+                    const __nv_bfloat162 *ph = (const __nv_bfloat162 *)&pk[k];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float2 f = __bfloat1622float2(ph[j]);
+                        acc[2 * j] += g[kb + k] * f.x;
+                        acc[2 * j + 1] += g[kb + k] * f.y;
+                    }
                 }
             }
             uint4 outv;
@@ -273,7 +307,6 @@ __global__ void __launch_bounds__(512) MoeCombineKernel(const MoeParams *table)
             *(uint4 *)((char *)(p.out + (size_t)t * H) + (size_t)v * 16) = outv;
         }
     }
-    KernelEnd(d, ls, used);
 }
 
 struct MoeCtx {
@@ -294,18 +327,28 @@ std::map<void *, MoeCtx *> g_ctx;
 
 uint64_t Align256(uint64_t v) { return (v + 255) & ~255ull; }
 
-HcclResult LaunchMoe(MoeCtx *m, void *kernel, const MoeParams &hp, int id, void *stream)
+// CTAs of the data-moving launches: all SMs unless HCOMM_MOE_CTAS leaves some to kernels running beside them.
+int MoeCtas(int sms)
+{
+    static const int forced = [] { const char *e = getenv("HCOMM_MOE_CTAS"); return e ? atoi(e) : 0; }();
+    return forced > 0 ? std::min(forced, HC_MAX_CTAS) : std::min(sms, HC_MAX_CTAS);
+}
+
+// One launch of `kernel` with `ctas` CTAs of `threads` threads (ctas <= 0: the data-moving default).  Ordinary launches:
+// nothing in these kernels waits for another CTA of the same launch.  Ranks that share a GPU (tests) are merged into one
+// cooperative launch, because their kernels wait for each other.
+HcclResult LaunchMoe(MoeCtx *m, void *kernel, const MoeParams &hp, int id, void *stream, int ctas = 0, int threads = 512)
 {
     Comm *c = m->comm;
     int dev = 0, sms = 148;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (c->emuSameDevice && c->nRanks > 1) {
-        const int ctas = std::max(1, sms / (int)c->nRanks);
+        const int perRank = ctas > 0 ? ctas : std::max(1, sms / (int)c->nRanks);
         return EmuLaunchGeneric(c->identifier + "#moe" + std::to_string(c->group.id), c->nRanks, c->rank, id, &hp, sizeof(hp), stream,
                                 [=](const void *devTable, uint32_t n, void *st) {
                                     void *args[] = {(void *)&devTable};
-                                    cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(ctas, n, 1), dim3(512, 1, 1), args, 0, (cudaStream_t)st);
+                                    cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(perRank, n, 1), dim3(threads, 1, 1), args, 0, (cudaStream_t)st);
                                     if (e != cudaSuccess) { HCCL_ERROR("MoE launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
                                     return HCCL_SUCCESS;
                                 });
@@ -314,7 +357,7 @@ HcclResult LaunchMoe(MoeCtx *m, void *kernel, const MoeParams &hp, int id, void 
     m->nextParam = (m->nextParam + 1) % 32;
     if (cudaMemcpyAsync(slot, &hp, sizeof(hp), cudaMemcpyHostToDevice, (cudaStream_t)stream) != cudaSuccess) return HCCL_E_RUNTIME;
     void *args[] = {(void *)&slot};
-    cudaError_t e = cudaLaunchCooperativeKernel(kernel, dim3(sms, 1, 1), dim3(512, 1, 1), args, 0, (cudaStream_t)stream);
+    cudaError_t e = cudaLaunchKernel(kernel, dim3(ctas > 0 ? ctas : MoeCtas(sms), 1, 1), dim3(threads, 1, 1), args, 0, (cudaStream_t)stream);
     if (e != cudaSuccess) { HCCL_ERROR("MoE launch failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
     return HCCL_SUCCESS;
 }
@@ -415,8 +458,10 @@ int HcommMoeCreate(HcclComm comm, int numExperts, int topk, int hidden, int maxT
     cudaGetDevice(&m->device);
     m->staticScratch = ResolveStaticScratch();       // set-up time, the exchange's GPU is current
     cudaFuncAttributes fa;
+    cudaFuncGetAttributes(&fa, MoeRouteKernel);
     cudaFuncGetAttributes(&fa, MoeDispatchKernel);
-    cudaFuncGetAttributes(&fa, MoeCombineKernel);
+    cudaFuncGetAttributes(&fa, MoeCombineSendKernel);
+    cudaFuncGetAttributes(&fa, MoeCombineSumKernel);
     cudaDeviceSynchronize();
     *handle = m;
     if (layoutOut) *layoutOut = L;
@@ -478,6 +523,7 @@ int HcommMoeDispatch(void *handle, const void *x, const int32_t *topkIdx, int nu
     FillCommon(m, hp);
     hp.x = (const __nv_bfloat16 *)x; hp.topkIdx = topkIdx; hp.numTokens = numTokens;
     ++c->opSeq;
+    CHK_RET(LaunchMoe(m, (void *)MoeRouteKernel, hp, 9100, stream, 1, 1024));
     return LaunchMoe(m, (void *)MoeDispatchKernel, hp, 9101, stream);
 }
 
@@ -495,7 +541,8 @@ int HcommMoeCombine(void *handle, const void *y, const float *gates, void *out, 
     FillCommon(m, hp);
     hp.y = (const __nv_bfloat16 *)y; hp.gates = gates; hp.out = (__nv_bfloat16 *)out; hp.numTokens = numTokens;
     ++c->opSeq;
-    return LaunchMoe(m, (void *)MoeCombineKernel, hp, 9102, stream);
+    CHK_RET(LaunchMoe(m, (void *)MoeCombineSendKernel, hp, 9102, stream));
+    return LaunchMoe(m, (void *)MoeCombineSumKernel, hp, 9104, stream);
 }
 
 // ------------------------------------------------------------------ dispatch without any allocation
@@ -541,6 +588,7 @@ int HcommMoeDispatchStaticScratch(void *handle, const void *x, const int32_t *to
     hp.scratch = m->staticScratch;
     hp.x = (const __nv_bfloat16 *)x; hp.topkIdx = topkIdx; hp.numTokens = numTokens;
     ++c->opSeq;
+    CHK_RET(LaunchMoe(m, (void *)MoeRouteKernel, hp, 9105, stream, 1, 1024));
     return LaunchMoe(m, (void *)MoeDispatchKernel, hp, 9103, stream);
 }
 

@@ -73,6 +73,8 @@ class MoeExchange:
         self._scales = _view(ptrs[1].value, (cap, hidden // 128), torch.float32, dev)
         self._origin = _view(ptrs[2].value, (cap,), torch.int64, dev)
         self._offsets = _view(ptrs[3].value, (epr + 1,), torch.int32, dev)
+        # one byte per (local token, k): 1 when the last dispatch sent that row, 0 when the index was masked or the row was dropped
+        self.sent = _view(ptrs[0].value - self.layout.offRows + self.layout.offValid, (max_tokens, topk), torch.uint8, dev)
 
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor) -> Received:
         assert x.dtype == torch.bfloat16 and x.is_contiguous() and x.shape[1] == self.hidden

@@ -25,6 +25,8 @@ extern "C" {
 
 /* C[M,N] = A[M,K] * B[N,K]^T on the current device.  N, K and ldc multiples of 8, C 16-byte aligned. */
 int HcommGemmBf16(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream);
+/* Tuning overrides of the CTA-pair GEMM kernels (0 = automatic): rasterisation group in 256-row blocks, tile width (128..256, multiple of 32). */
+void HcommGemmSetTuning(int groupRows, int tileWidth);
 /* Reads and clears the "a bounded wait expired inside a GEMM kernel" flag of the current device (0 = none). */
 int HcommGemmTakeError(void);
 

@@ -74,3 +74,64 @@ def test_dispatch_and_combine(n, experts, topk, hidden, tokens):
     finally:
         run_ranks(n, lambda r: moes[r].destroy())
         run_ranks(n, lambda r: comms[r].destroy())
+
+
+@pytest.mark.parametrize("capacity_factor,masked", [(2.0, True), (0.3, False)])
+def test_masked_experts_and_dropped_rows_stay_out_of_the_sum(capacity_factor, masked):
+    """An expert index outside the range masks that choice, and rows beyond the receive capacity are dropped: combine must
+    add neither - the landing slot of such a (token, k) holds whatever an earlier step left there."""
+    import hcomm_b200 as hb
+    from hcomm_b200.ops.moe import MoeExchange, quantize_e4m3_1x128
+    n, experts, topk, hidden, tokens = 2, 8, 4, 512, 64
+    info = hb.get_root_info()
+
+    def init(r):
+        torch.cuda.set_device(0)
+        return hb.Communicator(n, info, r, buffer_mb=8)
+    comms = run_ranks(n, init)
+    moes = run_ranks(n, lambda r: (torch.cuda.set_device(0), MoeExchange(comms[r], experts, topk, hidden, tokens, capacity_factor=capacity_factor))[1])
+    try:
+        g = torch.Generator(device="cuda").manual_seed(3)
+        xs = [torch.randn(tokens, hidden, device="cuda", generator=g).to(torch.bfloat16) for _ in range(n)]
+        gates = [torch.rand(tokens, topk, device="cuda", generator=g).float().contiguous() for _ in range(n)]
+        outs, sent = [None] * n, [None] * n
+        for step in range(2):
+            # step 0 fills every landing slot with large values (nothing masked), step 1 is the one that is checked
+            idx = [torch.stack([torch.randperm(experts, device="cuda", generator=g)[:topk] for _ in range(tokens)]).to(torch.int32).contiguous() for _ in range(n)]
+            if masked and step == 1:
+                for r in range(n):
+                    idx[r][::3, 1] = -1
+                    idx[r][1::5, 3] = experts + 7
+            scale = 1000.0 if step == 0 else 1.0
+
+            def op(r):
+                torch.cuda.set_device(0)
+                rec = moes[r].dispatch(xs[r], idx[r])
+                torch.cuda.synchronize()
+                nrows = rec.num_rows
+                offs = rec.expert_offsets.tolist()
+                assert all(0 <= o <= moes[r].layout.maxRecvRows for o in offs) and offs == sorted(offs)
+                y = (rec.dequantized(nrows) * scale).to(torch.bfloat16)
+                outs[r] = moes[r].combine(y, gates[r])
+                torch.cuda.synchronize()
+                sent[r] = moes[r].sent[:tokens].clone()
+            run_ranks(n, op)
+            dropped = sum(m.overflow() for m in moes)
+            if step == 0:
+                continue
+            if capacity_factor < 1:
+                assert dropped > 0, "the capacity was meant to overflow"
+            for r in range(n):
+                in_range = (idx[r] >= 0) & (idx[r] < experts)
+                assert torch.all(sent[r].bool() <= in_range), "a masked choice was marked as sent"
+                if capacity_factor >= 1:
+                    assert torch.equal(sent[r].bool(), in_range)
+                q, sc = quantize_e4m3_1x128(xs[r])
+                deq = (q.float().view(tokens, -1, 128) * sc.unsqueeze(-1)).view(tokens, hidden).to(torch.bfloat16).float()
+                ref = deq * (gates[r] * sent[r].float()).sum(dim=1, keepdim=True)
+                assert torch.isfinite(outs[r].float()).all()
+                err = (outs[r].float() - ref).abs().max().item()
+                assert err <= 3e-2 * max(1.0, ref.abs().max().item()), (r, err)
+    finally:
+        run_ranks(n, lambda r: moes[r].destroy())
+        run_ranks(n, lambda r: comms[r].destroy())

@@ -50,9 +50,13 @@ def test_static_scratch_dispatch_matches_allocating_dispatch():
             cases.append((x, idx, _snapshot(moe, rec)))
         received = Received(moe._rows, moe._scales, moe._origin, moe._offsets)
         for x, idx, want in cases:          # two calls of the new entry point in a row
+            torch.cuda.synchronize()
+            free_before, allocated_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
             rc = fn(moe._h, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(idx.data_ptr()), tokens, ctypes.c_void_p(stream))
             assert rc == 0
             torch.cuda.synchronize()
+            # the call took no memory from the driver nor from torch's allocator
+            assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == allocated_before
             got = _snapshot(moe, received)
             assert torch.equal(got[0], want[0]), "expert offsets"
             assert torch.equal(got[1], want[1]), "origins"
@@ -64,6 +68,14 @@ def test_static_scratch_dispatch_matches_allocating_dispatch():
         x = torch.zeros(8, 512, device="cuda", dtype=torch.bfloat16)
         idx = torch.zeros(8, 2, device="cuda", dtype=torch.int32)
         assert fn(big._h, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(idx.data_ptr()), 8, ctypes.c_void_p(stream)) == HCCL_E_PARA
+        # called with another device current: the built-in table belongs to the exchange's GPU, the call is refused before anything is queued
+        if torch.cuda.device_count() > 1:
+            x2, idx2 = cases[0][0], cases[0][1]
+            torch.cuda.set_device(1)
+            try:
+                assert fn(moe._h, ctypes.c_void_p(x2.data_ptr()), ctypes.c_void_p(idx2.data_ptr()), tokens, ctypes.c_void_p(stream)) == HCCL_E_PARA
+            finally:
+                torch.cuda.set_device(0)
     finally:
         big.destroy()
         moe.destroy()
