@@ -57,6 +57,7 @@ using namespace hcgemm;
 
 constexpr int kFusedThreads = 256;          // reduce-scatter kernels: 6 GEMM warps (+ 2 idle)
 constexpr int kAgThreads = 384;             // all-gather kernels: 6 GEMM warps + 6 communication warps
+constexpr int kAgBulkThreads = 224;         // all-gather CTA-pair kernel with the push on the copy engine: 6 GEMM warps + 1
 constexpr size_t kAgChunkBytes = 32 << 10;  // unit of the all-gather push: one warp moves one chunk
 // Flag words (u32) inside the HC_OFF_FUSED region of every rank's heap:
 //   all-gather:      block b (128 rows of the gathered matrix)           -> kAgFlagBase + b * 8            (own 32-byte sector)
@@ -114,9 +115,12 @@ struct RsOrder {
 };
 
 // TILE_ROWS: 128 (one CTA per tile) or 256 (CTA pair).  A row group is the 32 rows one epilogue warp owns.
-template <int BN, int TILE_ROWS>
+// BULK: partial rows leave through the SM's copy engine (one 256-byte bulk copy per row and 128 columns) instead of
+// the epilogue warps' own stores; the tile is then published when the warp returns for its next tile.
+template <int BN, int TILE_ROWS, bool BULK = false>
 struct RsEpilogue {
     static constexpr bool kStaged = true;      // the CTA-pair main loop sends partial tiles out as whole 256-byte row segments
+    static constexpr bool kBulk = BULK;
     const CommDev *d;
     __nv_bfloat16 *out;
     int ldOut, N, mbPer, rowsPer, tilesN;
@@ -132,6 +136,12 @@ struct RsEpilogue {
         return FusedFlag(d, owner, kRsFlagBase + ((src * mbPer + mb % mbPer) * tilesN + nb) * 8 + group);
     }
     __device__ __forceinline__ bool StagedTile(int mb) const { return mb / mbPer != d->rank; }
+    // where 128 columns of the calling thread's row of a partial tile go on the owner
+    __device__ __forceinline__ char *RowDst(int mb, int row, int col) const
+    {
+        const int q = mb / mbPer;
+        return Slot(q, d->rank) + ((size_t)(row - q * rowsPer) * N + col) * sizeof(__nv_bfloat16);
+    }
     // 32 rows x 128 columns of a partial tile, parked in shared memory by the calling warp, go to the owner's staging
     __device__ __forceinline__ void StoreStaged(int mb, int, int rowBase, int colBase, const uint8_t *slab, int lane) const
     {
@@ -147,12 +157,14 @@ struct RsEpilogue {
         // my own rows: every peer's partial of this row group must have landed; lane s waits for source s
         const int lane = threadIdx.x & 31;
         const int group = (row - lane - mb * TILE_ROWS) >> 5;
+        const bool clocked = phase && (threadIdx.x >> 5) == 2 && lane == 0;
+        const uint64_t t0 = clocked ? GlobalTimer() : 0;
         if (lane < d->nRanks && lane != me) {
             uint64_t waited = 0;
             hcdev::WaitFlagGe32Quiet(d, TileFlag(me, lane, mb, nb, group), seq, (uint32_t)lane, HC_WAIT_TILE_FLAG, (uint32_t)(mb * tilesN + nb), &waited);
-            if (phase && (threadIdx.x >> 5) == 2 && lane == (me == 0 ? 1 : 0)) phase[kPhaseTileWait] += waited;   // one lane speaks for the warp
         }
         __syncwarp();
+        if (clocked) phase[kPhaseTileWait] += GlobalTimer() - t0;      // until the slowest source's flag was seen
     }
     __device__ __forceinline__ void Fragment(int mb, int, int row, int col, const uint32_t (&f)[32]) const
     {
@@ -259,13 +271,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(cons
 }
 
 // The same on CTA pairs (256 x 256 tiles): row blocks and blocks per rank count 256 rows; a tile has eight row groups.
+template <bool BULK>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) GemmReduceScatterPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
-    RsEpilogue<256, kPairM> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, PhaseOfCta(p.shape)};
+    RsEpilogue<256, kPairM, BULK> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, PhaseOfCta(p.shape)};
     GemmMainLoopPair<256, 6>(&p.tmA, &p.tmB, p.shape, order, epi);
     hcdev::KernelEnd(d, ls, 0);
 }
@@ -383,10 +396,116 @@ struct AgPush {
             phase[kPhaseSignal] = tSignal;
         }
     }
-    __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *) const
+    static constexpr int kSmemBytes = 0;
+    __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *, uint8_t * = nullptr) const
     {
         const int perCta = (int)(blockDim.x >> 5) - 6;
         Run((int)blockIdx.x * perCta + warpInRole, (int)gridDim.x * perCta, lane);
+    }
+};
+
+// The push through the SM's copy engine.  One thread per worker moves the worker's chunks: a bulk load brings a
+// chunk of the shard into a ring slot in shared memory, p-1 bulk stores send the slot to every peer's staging (the
+// shard is read once, not once per peer), and no register or load/store unit of the SM touches the payload.
+// Loads run two chunks ahead; a slot is loaded again once the stores that read it have left shared memory; a chunk is
+// counted once its stores are complete, three chunks later, so the thread never sits out a round trip.
+// Counters: sent[block]; the thread whose count completes a 128-row block writes the block's flag on every peer.
+constexpr int kBulkSlots = 4;
+constexpr uint32_t kBulkChunk = 8 << 10;
+struct AgPushBulk {
+    static constexpr int kSmemBytes = 128 + kBulkSlots * (int)kBulkChunk;     // per worker: mbarriers, then the ring
+    const CommDev *d;
+    const char *x;         // my shard [rowsPer, K] bf16; NULL: nothing to push from this launch
+    int mbPer, K;
+    uint32_t half, seq;
+    uint32_t *sent;
+    uint64_t *phase;
+
+    __device__ __forceinline__ void Count(int item, int chunksPerBlock, uint64_t *tSignal, bool clocked) const
+    {
+        const uint64_t t0 = clocked ? GlobalTimer() : 0;
+        const int n = d->nRanks, me = d->rank, blk = item / chunksPerBlock;
+        // the chunk's stores are complete; order them before the count (see AgPush for the pairing of fences)
+        hcdev::FenceAcqRelSys();
+        uint32_t *ctr = sent + blk;
+        if (atomicAdd(ctr, 1u) + 1u == (uint32_t)chunksPerBlock) {
+            *(volatile uint32_t *)ctr = 0u;                                       // next used by a later launch
+            hcdev::FenceAcqRelSys();
+            for (int pi = 0; pi < n - 1; ++pi)
+                hcdev::StRelaxedSys(FusedFlag(d, (me + 1 + pi) % n, kAgFlagBase + (me * mbPer + blk) * 8), seq);
+        }
+        if (clocked) *tSignal += GlobalTimer() - t0;
+    }
+    // Called by ONE thread per worker; `smem` is the worker's own kSmemBytes (128-byte aligned).
+    __device__ __forceinline__ void Run(int worker, int workers, uint8_t *smem, volatile uint32_t *abortFlag, bool clocked) const
+    {
+        if (!x) return;
+        clocked = clocked && phase;
+        const int n = d->nRanks, me = d->rank;
+        uint64_t *bars = (uint64_t *)smem;
+        uint8_t *ring = smem + 128;
+        const size_t blockBytes = (size_t)kBlockM * K * sizeof(__nv_bfloat16);      // a multiple of 2 KB (K is a multiple of 8)
+        const int chunksPerBlock = (int)((blockBytes + kBulkChunk - 1) / kBulkChunk);
+        const int items = mbPer * chunksPerBlock;
+        const int count = worker < items ? (items - worker + workers - 1) / workers : 0;
+        const uint64_t tStart = clocked ? GlobalTimer() : 0;
+        uint64_t tSignal = 0;
+        for (int s = 0; s < kBulkSlots; ++s) MbarInit(&bars[s], 1);
+        MbarFenceInit();
+        // chunk k of this worker: item worker + k * workers, block-major (all workers are on block 0 first)
+        auto offOf = [&](int k, uint32_t *len) {
+            const int item = worker + k * workers, blk = item / chunksPerBlock, ch = item % chunksPerBlock;
+            const size_t inBlock = (size_t)ch * kBulkChunk;
+            *len = (uint32_t)(blockBytes - inBlock < kBulkChunk ? blockBytes - inBlock : kBulkChunk);
+            return (size_t)blk * blockBytes + inBlock;
+        };
+        auto load = [&](int k) {
+            uint32_t len;
+            const size_t off = offOf(k, &len);
+            const int s = k % kBulkSlots;
+            MbarExpectTx(&bars[s], len);
+            BulkLoad(ring + (size_t)s * kBulkChunk, x + off, len, &bars[s]);
+        };
+        for (int k = 0; k < 2 && k < count; ++k) load(k);
+        int sentOut = 0, counted = 0;
+        for (int k = 0; k < count; ++k) {
+            const int s = k % kBulkSlots;
+            if (!MbarWait(&bars[s], (uint32_t)(k / kBulkSlots) & 1u, abortFlag)) break;
+            uint32_t len;
+            const size_t off = offOf(k, &len);
+            for (int pi = 0; pi < n - 1; ++pi) {
+                char *dst = hcdev::CclHalf(d, (me + 1 + pi) % n, half) + (size_t)me * mbPer * blockBytes + off;
+                BulkStore(dst, ring + (size_t)s * kBulkChunk, len);
+            }
+            TmaStoreCommit();
+            sentOut = k + 1;
+            if (k + 2 < count) {
+                TmaStoreWaitRead<2>();               // the stores of chunk k - 2 have read the slot chunk k + 2 lands in
+                load(k + 2);
+            }
+            if (k >= 3) {
+                TmaStoreWait<3>();                   // the stores of chunk k - 3 are complete
+                Count(worker + (k - 3) * workers, chunksPerBlock, &tSignal, clocked);
+                counted = k - 2;
+            }
+        }
+        TmaStoreWait<0>();
+        for (int k = counted; k < sentOut; ++k) Count(worker + k * workers, chunksPerBlock, &tSignal, clocked);
+        if (sentOut < count) {
+            // a load that did not arrive in time may still land in the ring: stay (bounded) until it has
+            for (int k = sentOut; k < count && k < sentOut + 2; ++k)
+                for (uint32_t i = 0; i < (1u << 20) && !MbarTryWait(&bars[k % kBulkSlots], (uint32_t)(k / kBulkSlots) & 1u); ++i) {}
+        }
+        if (clocked) {
+            const uint64_t now = GlobalTimer();
+            phase[kPhasePushBusy] = now - tStart;
+            phase[kPhasePushEnd] = now;
+            phase[kPhaseSignal] = tSignal;
+        }
+    }
+    __device__ __forceinline__ void operator()(int warpInRole, int, volatile uint32_t *abortFlag, uint8_t *smem) const
+    {
+        if (warpInRole == 0 && ElectOne()) Run((int)blockIdx.x, (int)gridDim.x, smem, abortFlag, true);
     }
 };
 
@@ -405,23 +524,31 @@ __global__ void __launch_bounds__(kAgThreads, 1) AllGatherGemmKernel(const __gri
 }
 
 // CTA-pair variant: p.mbPer counts 128-row blocks (gate, push and flags keep that unit), the tile order works
-// on 256-row blocks.  BN: tile width (see Config2).
-template <int BN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAgThreads, 1) AllGatherGemmPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
+// on 256-row blocks.  BN: tile width (see Config2).  BULK: the push runs on the copy engine (one extra warp, six
+// ring stages) instead of six communication warps (seven stages).
+template <int BN, bool BULK>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(BULK ? kAgBulkThreads : kAgThreads, 1)
+    AllGatherGemmPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     AgOrder order{d->rank, d->nRanks, p.mbPer / 2};
     AgGate gate{d, p.mbPer, ls.seq, PhaseOfCta(p.shape)};
-    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape)};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
-    GemmMainLoopPair<BN, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
+    if constexpr (BULK) {
+        AgPushBulk push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape)};
+        GemmMainLoopPair<BN, 6>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
+    } else {
+        AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape)};
+        GemmMainLoopPair<BN, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
+    }
     hcdev::KernelEnd(d, ls, 0);
 }
 
-// The push alone, on every warp of the grid: first launch of the split form.  It leaves the launch count alone so that
-// the GEMM launched next sees the same sequence number and CCL half.
+// The push alone: first launch of the split form.  It leaves the launch count alone so that the GEMM launched next
+// sees the same sequence number and CCL half.  This form moves the shard with load and store instructions on
+// every warp of the grid ...
 __global__ void __launch_bounds__(512, 1) AllGatherPushKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
@@ -430,6 +557,24 @@ __global__ void __launch_bounds__(512, 1) AllGatherPushKernel(const __grid_const
     AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr};
     const int warpsPerCta = blockDim.x >> 5;
     push.Run((int)blockIdx.x * warpsPerCta + (int)(threadIdx.x >> 5), (int)gridDim.x * warpsPerCta, threadIdx.x & 31);
+    hcdev::KernelEnd(d, ls, 0, 0);
+}
+// ... and this one with the copy engine: four workers per CTA (one thread each), every worker with its own ring.
+constexpr int kPushBulkWorkers = 4;
+__global__ void __launch_bounds__(kPushBulkWorkers * 32, 1) AllGatherPushBulkKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
+{
+    extern __shared__ __align__(128) uint8_t pushSmem[];
+    __shared__ uint32_t abortFlag;
+    const FusedParams &p = table ? table[blockIdx.y] : own;
+    const CommDev *d = p.dev;
+    const hcdev::LaunchState ls = hcdev::KernelBegin(d);
+    if (threadIdx.x == 0) abortFlag = 0;
+    __syncthreads();
+    AgPushBulk push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr};
+    const int w = threadIdx.x >> 5;
+    if (ElectOne()) push.Run((int)blockIdx.x * kPushBulkWorkers + w, (int)gridDim.x * kPushBulkWorkers, pushSmem + (size_t)w * AgPushBulk::kSmemBytes, &abortFlag, false);
+    __syncthreads();
+    if (threadIdx.x == 0 && abortFlag && p.shape.errFlag) atomicExch(p.shape.errFlag, 1u);
     hcdev::KernelEnd(d, ls, 0, 0);
 }
 
@@ -494,6 +639,14 @@ HcclResult LaunchFused(Comm *c, KernelT kernel, int threads, int smemBytes, cons
 bool PairKernelsEnabled()
 {
     static const bool on = [] { const char *e = getenv("HCOMM_GEMM_PAIR"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+// Remote rows leave through the SM's copy engine (bulk copies) unless HCOMM_FUSED_BULK=0 asks for the kernels that
+// move them with their own load and store instructions.
+bool BulkEnabled()
+{
+    static const bool on = [] { const char *e = getenv("HCOMM_FUSED_BULK"); return !(e && e[0] == '0'); }();
     return on;
 }
 
@@ -593,8 +746,10 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     const int rowsPer = M / p;
     mode = ResolveMode(mode);
     const bool emu = c->emuSameDevice && c->nRanks > 1;
-    const bool usePair = PairKernelsEnabled() && !emu && rowsPer % kPairM == 0 && N % 256 == 0 &&
-                         PairCapacityOf(GemmReduceScatterPairKernel, kFusedThreads, Config2<256, 6, true>::kSmemBytes) > 0;
+    const bool bulk = BulkEnabled();
+    auto pairKernel = bulk ? GemmReduceScatterPairKernel<true> : GemmReduceScatterPairKernel<false>;
+    constexpr int pairSmem = Config2<256, 6, true>::kSmemBytes;
+    const bool usePair = PairKernelsEnabled() && !emu && rowsPer % kPairM == 0 && N % 256 == 0 && PairCapacityOf(pairKernel, kFusedThreads, pairSmem) > 0;
     const int blockRows = usePair ? kPairM : kBlockM;
     const bool fits = (uint64_t)p * rowsPer * N * 2 <= c->halfBytes && (uint64_t)p * (rowsPer / blockRows) * (N / BN) <= (uint64_t)kRsMaxSrcTiles;
     if (mode == HCOMM_FUSED_MODE_SPLIT || (!fits && !emu && mode == HCOMM_FUSED_MODE_AUTO)) {
@@ -631,8 +786,8 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / blockRows; hp.rowsPer = rowsPer; hp.K = K;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
-    c->fusedLastCtas = usePair ? 2 * std::min(PairCapacityOf(GemmReduceScatterPairKernel, kFusedThreads, Config2<256, 6, true>::kSmemBytes), tiles) : 0;
-    if (usePair) return LaunchFusedPair(c, GemmReduceScatterPairKernel, kFusedThreads, Config2<256, 6, true>::kSmemBytes, hp, tiles, stream);
+    c->fusedLastCtas = usePair ? 2 * std::min(PairCapacityOf(pairKernel, kFusedThreads, pairSmem), tiles) : 0;
+    if (usePair) return LaunchFusedPair(c, pairKernel, kFusedThreads, pairSmem, hp, tiles, stream);
     if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, kFusedThreads, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
     return LaunchFused(c, GemmReduceScatterKernel<128>, kFusedThreads, Config<128>::kSmemBytes, hp, tiles, 9002, stream);
 }
@@ -641,7 +796,15 @@ namespace {
 template <int BN>
 HcclResult LaunchAgPair(Comm *c, const FusedParams &hp, int tiles, void *stream)
 {
-    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN>, kAgThreads, Config2<BN, 7>::kSmemBytes, hp, tiles, stream);
+    if (BulkEnabled())
+        return LaunchFusedPair(c, AllGatherGemmPairKernel<BN, true>, kAgBulkThreads, Config2<BN, 6, false, AgPushBulk::kSmemBytes>::kSmemBytes, hp, tiles, stream);
+    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN, false>, kAgThreads, Config2<BN, 7>::kSmemBytes, hp, tiles, stream);
+}
+// pairs of the widest all-gather kernel that can be resident (the narrower ones need less shared memory)
+int AgPairCapacity()
+{
+    if (BulkEnabled()) return PairCapacityOf(AllGatherGemmPairKernel<256, true>, kAgBulkThreads, Config2<256, 6, false, AgPushBulk::kSmemBytes>::kSmemBytes);
+    return PairCapacityOf(AllGatherGemmPairKernel<256, false>, kAgThreads, Config2<256, 7>::kSmemBytes);
 }
 }  // namespace
 
@@ -667,10 +830,9 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     // The staging copy of the gathered activations lives in this operator's CCL half; which half is only known on
     // the device (launch parity), so a map is built for each and the kernel picks.
     const bool emu = c->emuSameDevice && c->nRanks > 1;
-    const bool usePair = PairKernelsEnabled() && !emu && Mshard % kPairM == 0 && N % 128 == 0 &&
-                         PairCapacityOf(AllGatherGemmPairKernel<256>, kAgThreads, Config2<256, 7>::kSmemBytes) > 0;
+    const bool usePair = PairKernelsEnabled() && !emu && Mshard % kPairM == 0 && N % 128 == 0 && AgPairCapacity() > 0;
     int BN = N % 256 == 0 ? 256 : 128;
-    if (usePair) BN = PickPairTileWidth(M / kPairM, N, PairCapacityOf(AllGatherGemmPairKernel<256>, kAgThreads, Config2<256, 7>::kSmemBytes));
+    if (usePair) BN = PickPairTileWidth(M / kPairM, N, AgPairCapacity());
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, x, (uint64_t)Mshard, (uint64_t)K, (uint64_t)ldx, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2, c->CclBuffer(), (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2b, c->CclBuffer() + c->halfBytes, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
@@ -685,12 +847,18 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     if (mode == HCOMM_FUSED_MODE_SPLIT && !emu && p > 1) {
         // first launch: the push on the whole GPU; the GEMM launched next waits for the peers' flags like the fused form
-        AllGatherPushKernel<<<dim3(GemmSmCount(), 1, 1), 512, 0, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
+        if (BulkEnabled()) {
+            constexpr int smem = kPushBulkWorkers * AgPushBulk::kSmemBytes;
+            SetSmemOnce(AllGatherPushBulkKernel, smem);
+            AllGatherPushBulkKernel<<<dim3(GemmSmCount(), 1, 1), kPushBulkWorkers * 32, smem, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
+        } else {
+            AllGatherPushKernel<<<dim3(GemmSmCount(), 1, 1), 512, 0, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
+        }
         if (cudaGetLastError() != cudaSuccess) return HCCL_E_RUNTIME;
         hp.xLocal = nullptr;
     }
     if (usePair) {
-        c->fusedLastCtas = 2 * std::min(PairCapacityOf(AllGatherGemmPairKernel<256>, kAgThreads, Config2<256, 7>::kSmemBytes), tiles);
+        c->fusedLastCtas = 2 * std::min(AgPairCapacity(), tiles);
         switch (BN) {
             case 256: return LaunchAgPair<256>(c, hp, tiles, stream);
             case 224: return LaunchAgPair<224>(c, hp, tiles, stream);

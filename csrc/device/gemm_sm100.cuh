@@ -72,8 +72,11 @@ struct SharedState {
     volatile uint32_t abort;
 };
 
+// Extra policies run on the warps after the six GEMM warps; kSmemBytes of shared memory (after the operand ring
+// and the epilogue staging) are theirs in the CTA-pair main loop.
 struct NoExtra {
-    __device__ __forceinline__ void operator()(int, int, volatile uint32_t *) const {}
+    static constexpr int kSmemBytes = 0;
+    __device__ __forceinline__ void operator()(int, int, volatile uint32_t *, uint8_t * = nullptr) const {}
 };
 
 // tmA2: optional second tensor map for A; the Gate policy decides per tile which one the producer reads
@@ -231,6 +234,7 @@ struct NoGate {
 // Writes bf16 rows of C; each thread stores its 32 columns as four 16-byte vectors.
 struct StoreBf16 {
     static constexpr bool kStaged = false;
+    static constexpr bool kBulk = false;
     __nv_bfloat16 *C;
     int ldc, M, N;
     __device__ __forceinline__ void BeginTile(int, int, int) const {}

@@ -102,7 +102,8 @@ def main():
     ap.add_argument("--factor", type=int, default=4)
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--prespin", type=float, default=1.0, help="seconds of GEMMs before the first measurement (clocks ramp up from idle)")
     ap.add_argument("--buffer-mb", type=int, default=512)
     ap.add_argument("--algo", default=None)
     ap.add_argument("--no-nccl", action="store_true")
@@ -126,6 +127,15 @@ def main():
         sizes.append(s)
         s *= a.factor
     dtype = {"bf16": torch.bfloat16, "fp32": torch.float32, "fp16": torch.float16}[a.dtype]
+    if a.prespin > 0:
+        import time
+        w = torch.randn(4096, 4096, device="cuda", dtype=torch.bfloat16)
+        t0 = time.time()
+        while time.time() - t0 < a.prespin:
+            for _ in range(20):
+                w @ w
+            torch.cuda.synchronize()
+        del w
     res = run_sweep(comm, a.ops.split(","), sizes, dtype, a.iters, a.warmup, with_nccl=(world > 1 and not a.no_nccl), algo_label=a.algo or "auto",
                     registered=a.registered)
     if rank == 0 and a.out:
