@@ -10,6 +10,7 @@
 #include <time.h>
 
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 
 #include "../core/dtype.h"
@@ -198,6 +199,19 @@ void ClearRegistered(CollArgs &a)
     a.outMc = nullptr;
 }
 
+static bool NvlsPipelineEnabled()
+{
+    static const bool on = [] { const char *e = getenv("HCCL_NVLS_PIPELINE"); return !(e && e[0] == '0'); }();
+    return on;
+}
+// Smallest operand that takes the pipelined kernel (HCCL_NVLS_PIPELINE_MIN_MB, default 96 MB): below it the extra
+// barriers cost more than the overlapped copies save.
+static uint64_t NvlsPipelineMinBytes()
+{
+    static const uint64_t v = [] { const char *e = getenv("HCCL_NVLS_PIPELINE_MIN_MB"); return (uint64_t)(e ? std::max(1, atoi(e)) : 96) << 20; }();
+    return v;
+}
+
 HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
 {
     const uint32_t n = c->nRanks, esz = DtypeSize(d.dtype);
@@ -219,7 +233,18 @@ HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
     // One launch whatever the size: operands beyond the staging are walked in windows inside the kernel.
     if (kind == FK_ALLREDUCE_ONESHOT) { a.sliceElems = oneShotCap; a.winElems = 0; }
     else if (kind == FK_ALLREDUCE_TWOSHOT) { a.winElems = AlignDownElems(c->halfBytes / (2 * n) / esz, esz) * n; a.sliceElems = d.count <= a.winElems ? AlignedSliceCount(d.count, n, esz) : 0; }
-    else { a.winElems = AlignDownElems(c->halfBytes / esz, esz); a.sliceElems = 0; }
+    else {
+        a.winElems = AlignDownElems(c->halfBytes / esz, esz);
+        a.sliceElems = 0;
+        // Large operands: eight or more windows, with copy-in, in-switch reduction and copy-out of neighbouring windows
+        // overlapped inside the kernel (HCCL_NVLS_PIPELINE=0 keeps the phase-by-phase kernel).
+        const uint64_t bytes = d.count * esz;
+        if (NvlsPipelineEnabled() && WindowsInKernel() && bytes >= NvlsPipelineMinBytes() && bytes % 16 == 0 && (((uintptr_t)d.in | (uintptr_t)d.out) & 15) == 0) {
+            const uint64_t winBytes = std::min<uint64_t>(c->halfBytes & ~(uint64_t)4095, std::max<uint64_t>(8ull << 20, ((bytes / 8 + 4095) & ~(uint64_t)4095)));
+            a.winElems = winBytes / esz;
+            return Launch(c, FK_ALLREDUCE_NVLS_PIPE, a, PickCtas(c, sel, bytes), d.stream);
+        }
+    }
     const uint64_t perWin = a.winElems ? std::min<uint64_t>(d.count, a.winElems) : d.count;
     const uint64_t perRank = kind == FK_ALLREDUCE_ONESHOT ? perWin * esz : (d.count > perWin ? perWin * esz : perWin * esz / n * 2);
     if (a.winElems && d.count > a.winElems && !WindowsInKernel()) {

@@ -387,6 +387,86 @@ __global__ void __launch_bounds__(512) KAllReduceNvls(const __grid_constant__ Co
     KernelEnd(d, ls, used, nWin);
 }
 
+// The same for a large operand that is not registered, as a software pipeline over windows: while window w is reduced
+// and replicated through the switch in one CCL half, the same threads copy the result of window w - 1 out of the other
+// half and the input of window w + 1 into it.  The link-bound phase and the two HBM-bound copies then run at the same
+// time instead of one after the other, and there is one cross-rank barrier per window instead of two.
+//   * A "row" is n * gridsize vectors; thread g of the grid owns column g of every row: it reduces the vector of
+//     sub-row `me` (the ownership rule above) and copies the vectors of all n sub-rows.  A vector keeps its thread, hence
+//     its CTA, in every phase, which is what the per-CTA barriers need.
+//   * Copy-out and copy-in of the other half touch the same addresses: a thread reads a vector's old contents (result
+//     of window w - 1) before it overwrites them (input of window w + 1).
+//   * The barrier at the end of step w orders: results of w on every rank before anyone copies them out (step w + 1);
+//     input of w + 1 on every rank before anyone reduces it; everybody's reads of half (w & 1) before window w + 2
+//     is copied into it.
+// Needs count * sizeof(T) and the window to be whole 16-byte vectors (the host checks).  The reference's big-data
+// all-reduce (aiv_all_reduce_910b_bigdata.h:90-165,262-289) overlaps the same three stages with progress counters.
+template <typename T>
+__global__ void __launch_bounds__(512) KAllReduceNvlsPipe(const __grid_constant__ CollArgs byval, const CollArgs *emu)
+{
+    HC_ARGS;
+    const LaunchState ls = KernelBegin(d);
+    uint32_t used = MaybePreBarrier(d, a, ls);
+    const int n = d->nRanks, me = d->rank;
+    const uint32_t nWin = WindowCount(a, a.count);
+    const uint64_t stride = (uint64_t)gridDim.x * blockDim.x, g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t rowVecs = (uint64_t)n * stride;
+    {
+        const Window x0 = WindowAt(a, ls, 0, a.count);
+        GridCopy(CclHalf(d, me, x0.half), (const char *)a.in + x0.off * sizeof(T), x0.cnt * sizeof(T), sizeof(T));
+    }
+    CrossRankBarrier(d, ls.epoch0 + (++used));
+    for (uint32_t w = 0; w < nWin; ++w) {
+        const Window x = WindowAt(a, ls, w, a.count);
+        char *mc = d->mcBase + d->bufOffset + (uint64_t)x.half * d->halfBytes;
+        char *other = CclHalf(d, me, x.half ^ 1u);
+        const uint64_t nvec = (x.cnt * sizeof(T)) >> 4;
+        uint64_t ovec = 0, ivec = 0;
+        char *outp = nullptr;
+        const char *inp = nullptr;
+        if (w > 0) {
+            const Window xo = WindowAt(a, ls, w - 1, a.count);
+            ovec = (xo.cnt * sizeof(T)) >> 4;
+            outp = (char *)a.out + xo.off * sizeof(T);
+        }
+        if (w + 1 < nWin) {
+            const Window xi = WindowAt(a, ls, w + 1, a.count);
+            ivec = (xi.cnt * sizeof(T)) >> 4;
+            inp = (const char *)a.in + xi.off * sizeof(T);
+        }
+        uint64_t most = nvec > ovec ? nvec : ovec;
+        if (ivec > most) most = ivec;
+        for (uint64_t row = 0; row < most; row += rowVecs) {
+            const uint64_t base = row + g, mine = base + (uint64_t)me * stride;
+            uint4 red = make_uint4(0, 0, 0, 0);
+            if (mine < nvec) red = Multimem<T>::LdReduceAdd(mc + (mine << 4));          // in flight while the copies run
+            for (int r0 = 0; r0 < n; r0 += 4) {
+                uint4 o[4], c[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint64_t idx = base + (uint64_t)(r0 + u) * stride;
+                    if (r0 + u < n && idx < ovec) o[u] = Ld16Volatile(other + (idx << 4));
+                    if (r0 + u < n && idx < ivec) c[u] = Ld16Volatile(inp + (idx << 4));
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint64_t idx = base + (uint64_t)(r0 + u) * stride;
+                    if (r0 + u < n && idx < ovec) St16(outp + (idx << 4), o[u]);
+                    if (r0 + u < n && idx < ivec) St16(other + (idx << 4), c[u]);
+                }
+            }
+            if (mine < nvec) MultimemSt16(mc + (mine << 4), a.useScale ? ScaleVec<T>(red, a.scale) : red);
+        }
+        __threadfence_system();      // multicast stores travel through the switch: every thread fences its own
+        CrossRankBarrierMc(d, ls.epoch0 + (++used));
+    }
+    {
+        const Window xl = WindowAt(a, ls, nWin - 1, a.count);
+        GridCopy((char *)a.out + xl.off * sizeof(T), CclHalf(d, me, xl.half), xl.cnt * sizeof(T), sizeof(T));
+    }
+    KernelEnd(d, ls, used, nWin);
+}
+
 // Column window [c0, c0 + cap) of a block of `cnt` elements: how many of its elements fall inside.
 __device__ __forceinline__ uint64_t InWindow(uint64_t cnt, uint64_t c0, uint64_t cap)
 {
@@ -1214,6 +1294,13 @@ void *ReduceKernelFor(int kind, int dtype)
                 case HCCL_DATA_TYPE_BFP16: return (void *)KAllReduceNvls<__nv_bfloat16>;
                 default: return nullptr;
             }
+        case FK_ALLREDUCE_NVLS_PIPE:
+            switch (dtype) {
+                case HCCL_DATA_TYPE_FP32: return (void *)KAllReduceNvlsPipe<float>;
+                case HCCL_DATA_TYPE_FP16: return (void *)KAllReduceNvlsPipe<__half>;
+                case HCCL_DATA_TYPE_BFP16: return (void *)KAllReduceNvlsPipe<__nv_bfloat16>;
+                default: return nullptr;
+            }
         case FK_REDUCE_SCATTER_NVLS:
             switch (dtype) {
                 case HCCL_DATA_TYPE_FP32: return (void *)KReduceScatterNvls<float>;
@@ -1271,7 +1358,7 @@ const char *FastKindName(int32_t k)
 {
     static const char *names[] = {"AllReduceOneShot", "AllReduceTwoShot", "AllReduceNvls", "ReduceScatter", "AllGather", "AlltoAll",
                                   "BroadcastPush", "BroadcastTwoShot", "BroadcastNvls", "Reduce", "Scatter", "Gather", "Send", "Recv", "Barrier", "SmallLL",
-                                  "ReduceScatterNvls", "AllGatherNvls", "AllReduceTwoShotWindows", "ReduceScatterWindows", "ReduceScatterInPlace"};
+                                  "ReduceScatterNvls", "AllGatherNvls", "AllReduceTwoShotWindows", "ReduceScatterWindows", "ReduceScatterInPlace", "AllReduceNvlsPipeline"};
     return (k >= 0 && k < FK_COUNT) ? names[k] : "?";
 }
 

@@ -35,6 +35,7 @@ enum FastKind : int32_t {
     FK_ALLREDUCE_TWOSHOT_WIN,   // two-shot all-reduce of an operand beyond the staging: windows inside one launch
     FK_REDUCE_SCATTER_WIN,      // reduce-scatter of blocks beyond a staging slot: column windows inside one launch
     FK_REDUCE_SCATTER_INPLACE,  // reduce-scatter that reads the peers' registered inputs in place
+    FK_ALLREDUCE_NVLS_PIPE,     // in-switch all-reduce of a large unregistered operand: copy-in / reduce / copy-out of different windows overlap
     FK_COUNT
 };
 const char *FastKindName(int32_t k);

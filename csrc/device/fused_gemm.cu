@@ -2,22 +2,25 @@
 // moving over NVLink peer memory tile by tile while the tensor cores work on other tiles.
 //
 // GEMM -> ReduceScatter  (row-parallel linear:  Y[M,N] = sum_r A_r[M,K_r] * B_r[N,K_r]^T, rank q keeps rows q*M/p ..)
-//   Rank r computes its partial tiles in destination order r+1, r+2, ..., r-1, r.  The epilogue of a
-//   tile owned by another rank converts the fp32 accumulator to bf16, stores it into slot r of the owner's
-//   staging (remote stores, whole 256-byte row segments) and then publishes it: every epilogue warp owns 32 rows
-//   of the tile and writes the operator's sequence number into the flag word of (source rank, tile, row group)
-//   on the owner.  Tiles of the rank's own rows come last: the warp that owns a row group waits for the p-1
-//   flags of that same row group (one lane per source), adds the partials to the accumulator still in registers
-//   in ascending rank order (fp32) and writes the final bf16 rows.  There is no separate reduction pass, no
-//   CTA-wide barrier on the way and nothing goes through a library collective.
+//   Rank r computes its partial tiles in an order that cycles through the destinations r+1, r+2, ..., r-1 and takes
+//   its own tiles last.  The epilogue of a tile owned by another rank converts the fp32 accumulator to bf16 and
+//   stores it into slot r of the owner's staging (remote stores, whole 256-byte row segments).  Every epilogue warp
+//   owns 32 rows of the tile (a row group); the operator's sequence number in the flag word of (source rank, tile,
+//   row group) on the owner says that the rows have landed.  In the CTA-pair kernel the epilogue warps only count
+//   their finished tiles in shared memory and a signaller thread publishes them (see RsSignaller); in the
+//   single-CTA kernel each warp publishes its own rows.  Tiles of the rank's own rows: the warp that owns a row group
+//   waits for the p-1 flags of that same row group (one lane per source), adds the partials to the accumulator
+//   still in registers in ascending rank order (fp32) and writes the final bf16 rows.  There is no separate
+//   reduction pass, no CTA-wide barrier on the way and nothing goes through a library collective.
 //
 // AllGather -> GEMM  (column-parallel linear:  Y_r[M,N_r] = concat_q(x_q)[M,K] * W_r[N_r,K]^T)
-//   Two extra warps per CTA push this rank's activation shard into every peer's staging (nearest consumer
-//   first, 32 KB chunks), while the GEMM starts on the local shard.  The warp that completes a 128-row block
-//   (counted on this GPU) writes the sequence number into the block's flag on the consumer.  The TMA producer of
-//   a tile whose rows come from rank q waits for that flag, then loads from the local staging copy - TMA never
-//   reads peer memory.  Blocks are consumed in the order own, r-1, r-2, ... which is the order in which peers
-//   send them.
+//   Extra warps in every CTA push this rank's activation shard into every peer's staging (block-major: block 0 to
+//   all peers, then block 1, ...; 32 KB chunks), while the GEMM starts on the local shard.  Finished chunks are
+//   counted on this GPU; the thread whose count completes a 128-row block writes the sequence number into the
+//   block's flag on the consumer.  In the CTA-pair kernel six warps push and a seventh counts and publishes for
+//   them (AgPush::Signal), so the pushing warps never execute a fence.  The TMA producer of a tile whose rows come
+//   from rank q waits for that flag, then loads from the local staging copy - TMA never reads peer memory.  Blocks
+//   are consumed in the order own, then block i of every source for i = 0, 1, ..., the order in which they arrive.
 //
 // Flags hold the sequence number of the operator that wrote them (the communicator's launch count, the same on
 // every rank and kept on the device) and are compared with >=, so a flag names its call: a fast rank that is
@@ -56,8 +59,8 @@ namespace {
 using namespace hcgemm;
 
 constexpr int kFusedThreads = 256;          // reduce-scatter kernels: 6 GEMM warps (+ 2 idle)
-constexpr int kAgThreads = 384;             // all-gather kernels: 6 GEMM warps + 6 communication warps
-constexpr int kAgBulkThreads = 224;         // all-gather CTA-pair kernel with the push on the copy engine: 6 GEMM warps + 1
+constexpr int kAgThreads = 384;             // all-gather kernel on single CTAs: 6 GEMM warps + 6 communication warps
+constexpr int kAgPairThreads = 416;         // all-gather kernel on CTA pairs: 6 GEMM warps + 6 pushing warps + the signaller
 constexpr size_t kAgChunkBytes = 32 << 10;  // unit of the all-gather push: one warp moves one chunk
 // Flag words (u32) inside the HC_OFF_FUSED region of every rank's heap:
 //   all-gather:      block b (128 rows of the gathered matrix)           -> kAgFlagBase + b * 8            (own 32-byte sector)
@@ -83,6 +86,8 @@ struct FusedParams {
     int rowsPer;              // rows per rank
     int K;
     uint32_t *sent;           // AG: device-local chunk counters [peer index][block]
+    int pushWarps;            // AG, CTA-pair kernel: pushing warps per CTA that take part (1..6)
+    int signaller;            // AG, CTA-pair kernel: a seventh warp publishes the chunks (1) or every pushing warp its own (0)
 };
 
 __device__ __forceinline__ uint32_t *FusedFlag(const CommDev *d, int rank, int idx)
@@ -114,13 +119,24 @@ struct RsOrder {
     }
 };
 
+// A fence at system scope costs 15 - 20 us while the SM has remote stores in flight (measured on NVLink; it appears
+// to wait for all of them, not just the caller's), so the warps that move data never execute one.  In the CTA-pair
+// kernels they hand their progress to a signaller warp through shared memory (release / acquire at CTA scope), and
+// the signaller publishes whatever has accumulated with ONE fence: the cost is paid off the data path and
+// is shared by all tiles (chunks) that completed meanwhile.
+constexpr uint32_t kSignallerPolls = 1u << 23;   // x 128 ns of sleep: about a second without progress, then the kernel gives up
+
+__device__ __forceinline__ uint32_t *RsTileFlag(const CommDev *d, int owner, int src, int mbPer, int tilesN, int mb, int nb, int group)
+{
+    return FusedFlag(d, owner, kRsFlagBase + ((src * mbPer + mb % mbPer) * tilesN + nb) * 8 + group);
+}
+
 // TILE_ROWS: 128 (one CTA per tile) or 256 (CTA pair).  A row group is the 32 rows one epilogue warp owns.
-// BULK: partial rows leave through the SM's copy engine (one 256-byte bulk copy per row and 128 columns) instead of
-// the epilogue warps' own stores; the tile is then published when the warp returns for its next tile.
-template <int BN, int TILE_ROWS, bool BULK = false>
+// SIGNALLED: the warp does not publish its row groups itself (RsSignaller does).
+template <int BN, int TILE_ROWS, bool SIGNALLED = false>
 struct RsEpilogue {
     static constexpr bool kStaged = true;      // the CTA-pair main loop sends partial tiles out as whole 256-byte row segments
-    static constexpr bool kBulk = BULK;
+    static constexpr bool kReportsTiles = SIGNALLED;
     const CommDev *d;
     __nv_bfloat16 *out;
     int ldOut, N, mbPer, rowsPer, tilesN;
@@ -133,15 +149,9 @@ struct RsEpilogue {
     }
     __device__ __forceinline__ uint32_t *TileFlag(int owner, int src, int mb, int nb, int group) const
     {
-        return FusedFlag(d, owner, kRsFlagBase + ((src * mbPer + mb % mbPer) * tilesN + nb) * 8 + group);
+        return RsTileFlag(d, owner, src, mbPer, tilesN, mb, nb, group);
     }
     __device__ __forceinline__ bool StagedTile(int mb) const { return mb / mbPer != d->rank; }
-    // where 128 columns of the calling thread's row of a partial tile go on the owner
-    __device__ __forceinline__ char *RowDst(int mb, int row, int col) const
-    {
-        const int q = mb / mbPer;
-        return Slot(q, d->rank) + ((size_t)(row - q * rowsPer) * N + col) * sizeof(__nv_bfloat16);
-    }
     // 32 rows x 128 columns of a partial tile, parked in shared memory by the calling warp, go to the owner's staging
     __device__ __forceinline__ void StoreStaged(int mb, int, int rowBase, int colBase, const uint8_t *slab, int lane) const
     {
@@ -241,7 +251,7 @@ struct RsEpilogue {
     __device__ __forceinline__ void EndTile(int mb, int nb, int row) const
     {
         const int q = mb / mbPer;
-        if (q == d->rank) return;
+        if (SIGNALLED || q == d->rank) return;
         __syncwarp();
         const int lane = threadIdx.x & 31;
         if (lane == 0) {
@@ -250,6 +260,63 @@ struct RsEpilogue {
             hcdev::StReleaseSys(TileFlag(q, d->rank, mb, nb, group), seq);
             if (phase && (threadIdx.x >> 5) == 2) phase[kPhaseSignal] += GlobalTimer() - t0;
         }
+    }
+    // Epilogue warp `quarter` has issued every store of its first `count` tiles (own tiles included).
+    __device__ __forceinline__ void TileDone(int quarter, uint32_t count, uint8_t *shared, int lane) const
+    {
+        __syncwarp();
+        if (lane == 0) hcdev::StReleaseCtaShared((uint32_t *)shared + quarter, count);
+    }
+};
+
+// The signaller of the CTA-pair reduce-scatter kernel: one thread per CTA follows the four epilogue warps' tile counts
+// and publishes the row groups of every partial tile all four have stored - one fence for all tiles that completed
+// since it last looked, then one flag word per row group.
+struct RsSignaller {
+    static constexpr int kSmemBytes = 64;
+    const CommDev *d;
+    RsOrder order;
+    const GemmShape *shapePtr;
+    int mbPer;
+    uint32_t seq;
+    uint64_t *phase;
+    __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *abortFlag, uint8_t *shared) const
+    {
+        if (warpInRole != 0 || lane != 0) return;
+        const GemmShape &shape = *shapePtr;
+        const uint32_t *done = (const uint32_t *)shared;
+        const int me = d->rank, numTiles = shape.tilesM * shape.tilesN;
+        const int first = (int)pair::ClusterId(), step = (int)pair::NumClusters(), ctaRank = (int)pair::ClusterCtaRank();
+        const int mine = first < numTiles ? (numTiles - first + step - 1) / step : 0;
+        int k = 0;
+        uint32_t idle = 0;
+        uint64_t tSignal = 0;
+        while (k < mine) {
+            uint32_t c = hcdev::LdAcquireCtaShared(done);
+#pragma unroll
+            for (int w = 1; w < 4; ++w) { const uint32_t v = hcdev::LdAcquireCtaShared(done + w); c = v < c ? v : c; }
+            if ((int)c <= k) {
+                if (*abortFlag) return;
+                if (++idle > kSignallerPolls) { *abortFlag = 1; return; }
+                __nanosleep(128);
+                continue;
+            }
+            idle = 0;
+            const uint64_t t0 = phase ? GlobalTimer() : 0;
+            bool fenced = false;
+            for (int j = k; j < (int)c; ++j) {
+                int mb, nb;
+                order(first + j * step, shape, &mb, &nb);
+                const int q = mb / mbPer;
+                if (q == me) continue;
+                if (!fenced) { hcdev::FenceAcqRelSys(); fenced = true; }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) hcdev::StRelaxedSys(RsTileFlag(d, q, me, mbPer, shape.tilesN, mb, nb, ctaRank * 4 + g), seq);
+            }
+            if (phase && fenced) tSignal += GlobalTimer() - t0;
+            k = (int)c;
+        }
+        if (phase) phase[kPhaseSignal] = tSignal;
     }
 };
 
@@ -271,15 +338,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(cons
 }
 
 // The same on CTA pairs (256 x 256 tiles): row blocks and blocks per rank count 256 rows; a tile has eight row groups.
-template <bool BULK>
+template <bool SIGNALLED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) GemmReduceScatterPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
-    RsEpilogue<256, kPairM, BULK> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, PhaseOfCta(p.shape)};
-    GemmMainLoopPair<256, 6>(&p.tmA, &p.tmB, p.shape, order, epi);
+    RsEpilogue<256, kPairM, SIGNALLED> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, PhaseOfCta(p.shape)};
+    if constexpr (SIGNALLED) {
+        RsSignaller signaller{d, order, &p.shape, p.mbPer, ls.seq, PhaseOfCta(p.shape)};
+        GemmMainLoopPair<256, 6>(&p.tmA, &p.tmB, p.shape, order, epi, NoGate(), nullptr, signaller);
+    } else {
+        GemmMainLoopPair<256, 6>(&p.tmA, &p.tmB, p.shape, order, epi);
+    }
     hcdev::KernelEnd(d, ls, 0);
 }
 
@@ -333,27 +405,54 @@ struct AgGate {
     }
 };
 
-// Communication warps: push my shard to the peers' staging, nearest consumer first.  `warps` warps share the work,
-// this one is number `w`.
+// Communication warps: push my shard to the peers' staging, block-major.  `warps` warps share the work, this one is
+// number `w`; its items are w, w + warps, w + 2 * warps, ...  With `report` (a word in shared memory) the warp only
+// counts the chunks it has stored there and AgPush::Signal, on another warp of the CTA, publishes them; without, the
+// warp fences and counts each chunk itself.
 struct AgPush {
+    static constexpr int kPushers = 6;         // pushing warps per CTA in the fused CTA-pair kernel, followed by one signaller
+    static constexpr int kSmemBytes = 64;
     const CommDev *d;
     const char *x;         // my shard [rowsPer, K] bf16; NULL: nothing to push from this launch
     int mbPer, K;
     uint32_t half, seq;
     uint32_t *sent;
     uint64_t *phase;
-    __device__ __forceinline__ void Run(int w, int warps, int lane) const
+    int pushWarps, signaller;
+
+    __device__ __forceinline__ int ChunksPerBlock() const
+    {
+        const size_t blockBytes = (size_t)kBlockM * K * sizeof(__nv_bfloat16);
+        return (int)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes);
+    }
+    __device__ __forceinline__ int Items() const { return mbPer * (d->nRanks - 1) * ChunksPerBlock(); }
+    // Chunk `it` is on the peers' side: count it; the caller has ordered the chunk before the count (fence).  The
+    // thread whose count completes a block has seen every chunk of it ordered (fence, atomic on one side - atomic,
+    // fence on the other) and names the block on the consumer.
+    __device__ __forceinline__ void Count(int it) const
+    {
+        const int n = d->nRanks, me = d->rank, chunksPerBlock = ChunksPerBlock(), perBlock = (n - 1) * chunksPerBlock;
+        const int blk = it / perBlock, peerIdx = (it % perBlock) / chunksPerBlock;
+        uint32_t *ctr = sent + peerIdx * mbPer + blk;
+        if (atomicAdd(ctr, 1u) + 1u == (uint32_t)chunksPerBlock) {
+            *(volatile uint32_t *)ctr = 0u;                               // next used by a later launch
+            hcdev::FenceAcqRelSys();
+            hcdev::StRelaxedSys(FusedFlag(d, (me + 1 + peerIdx) % n, kAgFlagBase + (me * mbPer + blk) * 8), seq);
+        }
+    }
+    __device__ __forceinline__ void Run(int w, int warps, int lane, uint32_t *report = nullptr, bool clocked = false) const
     {
         if (!x) return;
         const int n = d->nRanks, me = d->rank;
         const size_t rowBytes = (size_t)K * sizeof(__nv_bfloat16);
         const size_t blockBytes = (size_t)kBlockM * rowBytes;                     // a multiple of 2 KB (K is a multiple of 8)
-        const int chunksPerBlock = (int)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes);
+        const int chunksPerBlock = ChunksPerBlock();
         const int perBlock = (n - 1) * chunksPerBlock;
         const int items = mbPer * perBlock;
-        const bool clocked = phase && (threadIdx.x >> 5) == 6;                   // the CTA's first communication warp
+        clocked = clocked && phase;
         const uint64_t tStart = clocked ? GlobalTimer() : 0;
         uint64_t tSignal = 0;
+        uint32_t stored = 0;
         // block-major order: block 0 to every peer (nearest consumer first), then block 1, ...; consecutive warps take
         // consecutive chunks, so the warps in flight write to all peers at once
         for (int it = w; it < items; it += warps) {
@@ -376,136 +475,81 @@ struct AgPush {
             }
             __syncwarp();
             if (lane == 0) {
-                const uint64_t t0 = clocked ? GlobalTimer() : 0;
-                // The chunk is ordered before the count; the warp whose count completes the block has therefore
-                // seen every chunk of it ordered (fence, atomic on one side - atomic, fence on the other) and names it.
-                hcdev::FenceAcqRelSys();
-                uint32_t *ctr = sent + peerIdx * mbPer + blk;
-                if (atomicAdd(ctr, 1u) + 1u == (uint32_t)chunksPerBlock) {
-                    *(volatile uint32_t *)ctr = 0u;                               // next used by a later launch
+                if (report) {
+                    hcdev::StReleaseCtaShared(report, ++stored);
+                } else {
+                    const uint64_t t0 = clocked ? GlobalTimer() : 0;
                     hcdev::FenceAcqRelSys();
-                    hcdev::StRelaxedSys(FusedFlag(d, peer, kAgFlagBase + (me * mbPer + blk) * 8), seq);
+                    Count(it);
+                    if (clocked) tSignal += GlobalTimer() - t0;
                 }
-                if (clocked) tSignal += GlobalTimer() - t0;
             }
         }
         if (clocked && lane == 0) {
             const uint64_t now = GlobalTimer();
             phase[kPhasePushBusy] = now - tStart;
-            phase[kPhasePushEnd] = now;
-            phase[kPhaseSignal] = tSignal;
+            if (!report) { phase[kPhasePushEnd] = now; phase[kPhaseSignal] = tSignal; }
         }
     }
-    static constexpr int kSmemBytes = 0;
-    __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *, uint8_t * = nullptr) const
-    {
-        const int perCta = (int)(blockDim.x >> 5) - 6;
-        Run((int)blockIdx.x * perCta + warpInRole, (int)gridDim.x * perCta, lane);
-    }
-};
-
-// The push through the SM's copy engine.  One thread per worker moves the worker's chunks: a bulk load brings a
-// chunk of the shard into a ring slot in shared memory, p-1 bulk stores send the slot to every peer's staging (the
-// shard is read once, not once per peer), and no register or load/store unit of the SM touches the payload.
-// Loads run two chunks ahead; a slot is loaded again once the stores that read it have left shared memory; a chunk is
-// counted once its stores are complete, three chunks later, so the thread never sits out a round trip.
-// Counters: sent[block]; the thread whose count completes a 128-row block writes the block's flag on every peer.
-constexpr int kBulkSlots = 4;
-constexpr uint32_t kBulkChunk = 8 << 10;
-struct AgPushBulk {
-    static constexpr int kSmemBytes = 128 + kBulkSlots * (int)kBulkChunk;     // per worker: mbarriers, then the ring
-    const CommDev *d;
-    const char *x;         // my shard [rowsPer, K] bf16; NULL: nothing to push from this launch
-    int mbPer, K;
-    uint32_t half, seq;
-    uint32_t *sent;
-    uint64_t *phase;
-
-    __device__ __forceinline__ void Count(int item, int chunksPerBlock, uint64_t *tSignal, bool clocked) const
-    {
-        const uint64_t t0 = clocked ? GlobalTimer() : 0;
-        const int n = d->nRanks, me = d->rank, blk = item / chunksPerBlock;
-        // the chunk's stores are complete; order them before the count (see AgPush for the pairing of fences)
-        hcdev::FenceAcqRelSys();
-        uint32_t *ctr = sent + blk;
-        if (atomicAdd(ctr, 1u) + 1u == (uint32_t)chunksPerBlock) {
-            *(volatile uint32_t *)ctr = 0u;                                       // next used by a later launch
-            hcdev::FenceAcqRelSys();
-            for (int pi = 0; pi < n - 1; ++pi)
-                hcdev::StRelaxedSys(FusedFlag(d, (me + 1 + pi) % n, kAgFlagBase + (me * mbPer + blk) * 8), seq);
-        }
-        if (clocked) *tSignal += GlobalTimer() - t0;
-    }
-    // Called by ONE thread per worker; `smem` is the worker's own kSmemBytes (128-byte aligned).
-    __device__ __forceinline__ void Run(int worker, int workers, uint8_t *smem, volatile uint32_t *abortFlag, bool clocked) const
+    // One thread follows the counts of NP pushing warps (global numbers firstWarp .. firstWarp + NP - 1 of `warps`) and
+    // counts, after ONE fence, all chunks they have stored since it last looked.
+    template <int NP>
+    __device__ __forceinline__ void Signal(int firstWarp, int warps, const uint32_t *reports, volatile uint32_t *abortFlag, bool clocked, int active = NP) const
     {
         if (!x) return;
+        const int items = Items();
         clocked = clocked && phase;
-        const int n = d->nRanks, me = d->rank;
-        uint64_t *bars = (uint64_t *)smem;
-        uint8_t *ring = smem + 128;
-        const size_t blockBytes = (size_t)kBlockM * K * sizeof(__nv_bfloat16);      // a multiple of 2 KB (K is a multiple of 8)
-        const int chunksPerBlock = (int)((blockBytes + kBulkChunk - 1) / kBulkChunk);
-        const int items = mbPer * chunksPerBlock;
-        const int count = worker < items ? (items - worker + workers - 1) / workers : 0;
-        const uint64_t tStart = clocked ? GlobalTimer() : 0;
-        uint64_t tSignal = 0;
-        for (int s = 0; s < kBulkSlots; ++s) MbarInit(&bars[s], 1);
-        MbarFenceInit();
-        // chunk k of this worker: item worker + k * workers, block-major (all workers are on block 0 first)
-        auto offOf = [&](int k, uint32_t *len) {
-            const int item = worker + k * workers, blk = item / chunksPerBlock, ch = item % chunksPerBlock;
-            const size_t inBlock = (size_t)ch * kBulkChunk;
-            *len = (uint32_t)(blockBytes - inBlock < kBulkChunk ? blockBytes - inBlock : kBulkChunk);
-            return (size_t)blk * blockBytes + inBlock;
-        };
-        auto load = [&](int k) {
-            uint32_t len;
-            const size_t off = offOf(k, &len);
-            const int s = k % kBulkSlots;
-            MbarExpectTx(&bars[s], len);
-            BulkLoad(ring + (size_t)s * kBulkChunk, x + off, len, &bars[s]);
-        };
-        for (int k = 0; k < 2 && k < count; ++k) load(k);
-        int sentOut = 0, counted = 0;
-        for (int k = 0; k < count; ++k) {
-            const int s = k % kBulkSlots;
-            if (!MbarWait(&bars[s], (uint32_t)(k / kBulkSlots) & 1u, abortFlag)) break;
-            uint32_t len;
-            const size_t off = offOf(k, &len);
-            for (int pi = 0; pi < n - 1; ++pi) {
-                char *dst = hcdev::CclHalf(d, (me + 1 + pi) % n, half) + (size_t)me * mbPer * blockBytes + off;
-                BulkStore(dst, ring + (size_t)s * kBulkChunk, len);
-            }
-            TmaStoreCommit();
-            sentOut = k + 1;
-            if (k + 2 < count) {
-                TmaStoreWaitRead<2>();               // the stores of chunk k - 2 have read the slot chunk k + 2 lands in
-                load(k + 2);
-            }
-            if (k >= 3) {
-                TmaStoreWait<3>();                   // the stores of chunk k - 3 are complete
-                Count(worker + (k - 3) * workers, chunksPerBlock, &tSignal, clocked);
-                counted = k - 2;
-            }
+        uint32_t published[NP], total[NP];
+        int remaining = 0;
+#pragma unroll
+        for (int w = 0; w < NP; ++w) {
+            published[w] = 0;
+            total[w] = (w < active && firstWarp + w < items) ? (uint32_t)((items - (firstWarp + w) + warps - 1) / warps) : 0u;
+            remaining += (int)total[w];
         }
-        TmaStoreWait<0>();
-        for (int k = counted; k < sentOut; ++k) Count(worker + k * workers, chunksPerBlock, &tSignal, clocked);
-        if (sentOut < count) {
-            // a load that did not arrive in time may still land in the ring: stay (bounded) until it has
-            for (int k = sentOut; k < count && k < sentOut + 2; ++k)
-                for (uint32_t i = 0; i < (1u << 20) && !MbarTryWait(&bars[k % kBulkSlots], (uint32_t)(k / kBulkSlots) & 1u); ++i) {}
+        uint32_t idle = 0;
+        uint64_t tSignal = 0;
+        while (remaining > 0) {
+            uint32_t c[NP];
+            bool any = false;
+#pragma unroll
+            for (int w = 0; w < NP; ++w) { c[w] = hcdev::LdAcquireCtaShared(reports + w); any = any || c[w] > published[w]; }
+            if (!any) {
+                if (abortFlag && *abortFlag) return;
+                if (++idle > kSignallerPolls) { if (abortFlag) *abortFlag = 1; return; }
+                __nanosleep(128);
+                continue;
+            }
+            idle = 0;
+            const uint64_t t0 = clocked ? GlobalTimer() : 0;
+            hcdev::FenceAcqRelSys();
+#pragma unroll
+            for (int w = 0; w < NP; ++w) {
+                for (uint32_t k = published[w]; k < c[w]; ++k) Count(firstWarp + w + (int)k * warps);
+                remaining -= (int)(c[w] - published[w]);
+                published[w] = c[w];
+            }
+            if (clocked) tSignal += GlobalTimer() - t0;
         }
         if (clocked) {
-            const uint64_t now = GlobalTimer();
-            phase[kPhasePushBusy] = now - tStart;
-            phase[kPhasePushEnd] = now;
+            phase[kPhasePushEnd] = GlobalTimer();
             phase[kPhaseSignal] = tSignal;
         }
     }
-    __device__ __forceinline__ void operator()(int warpInRole, int, volatile uint32_t *abortFlag, uint8_t *smem) const
+    // Extra-warp entry of the GEMM main loops.  With shared memory (CTA-pair kernel): kPushers pushing warps and one
+    // signaller; without (single-CTA kernel): every extra warp pushes and publishes its own chunks.
+    __device__ __forceinline__ void operator()(int warpInRole, int lane, volatile uint32_t *abortFlag, uint8_t *shared = nullptr) const
     {
-        if (warpInRole == 0 && ElectOne()) Run((int)blockIdx.x, (int)gridDim.x, smem, abortFlag, true);
+        if (!shared) {
+            const int perCta = (int)(blockDim.x >> 5) - 6;
+            Run((int)blockIdx.x * perCta + warpInRole, (int)gridDim.x * perCta, lane);
+            return;
+        }
+        uint32_t *reports = (uint32_t *)shared;
+        const int active = pushWarps >= 1 && pushWarps <= kPushers ? pushWarps : kPushers;
+        const int first = (int)blockIdx.x * active, warps = (int)gridDim.x * active;
+        if (warpInRole < active) Run(first + warpInRole, warps, lane, signaller ? reports + warpInRole : nullptr, warpInRole == 0);
+        else if (warpInRole == kPushers && lane == 0 && signaller) Signal<kPushers>(first, warps, reports, abortFlag, true, active);
     }
 };
 
@@ -517,64 +561,49 @@ __global__ void __launch_bounds__(kAgThreads, 1) AllGatherGemmKernel(const __gri
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     AgOrder order{d->rank, d->nRanks, p.mbPer};
     AgGate gate{d, p.mbPer, ls.seq, nullptr};
-    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr};
+    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr, p.pushWarps, p.signaller};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
     GemmMainLoop<BN>(&p.tmA, &p.tmB, p.shape, order, gate, epi, ls.half ? &p.tmA2b : &p.tmA2, push);
     hcdev::KernelEnd(d, ls, 0);
 }
 
 // CTA-pair variant: p.mbPer counts 128-row blocks (gate, push and flags keep that unit), the tile order works
-// on 256-row blocks.  BN: tile width (see Config2).  BULK: the push runs on the copy engine (one extra warp, six
-// ring stages) instead of six communication warps (seven stages).
-template <int BN, bool BULK>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(BULK ? kAgBulkThreads : kAgThreads, 1)
-    AllGatherGemmPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
+// on 256-row blocks.  BN: tile width (see Config2).
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAgPairThreads, 1) AllGatherGemmPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     AgOrder order{d->rank, d->nRanks, p.mbPer / 2};
     AgGate gate{d, p.mbPer, ls.seq, PhaseOfCta(p.shape)};
+    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape), p.pushWarps, p.signaller};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
-    if constexpr (BULK) {
-        AgPushBulk push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape)};
-        GemmMainLoopPair<BN, 6>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
-    } else {
-        AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape)};
-        GemmMainLoopPair<BN, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
-    }
+    GemmMainLoopPair<BN, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
     hcdev::KernelEnd(d, ls, 0);
 }
 
-// The push alone: first launch of the split form.  It leaves the launch count alone so that the GEMM launched next
-// sees the same sequence number and CCL half.  This form moves the shard with load and store instructions on
-// every warp of the grid ...
+// The push alone, on every SM: first launch of the split form.  It leaves the launch count alone so that the GEMM
+// launched next sees the same sequence number and CCL half.  Fifteen warps push, the sixteenth publishes.
+constexpr int kPushKernelPushers = 15;
 __global__ void __launch_bounds__(512, 1) AllGatherPushKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
+    __shared__ uint32_t reports[kPushKernelPushers + 1];
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
-    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr};
-    const int warpsPerCta = blockDim.x >> 5;
-    push.Run((int)blockIdx.x * warpsPerCta + (int)(threadIdx.x >> 5), (int)gridDim.x * warpsPerCta, threadIdx.x & 31);
-    hcdev::KernelEnd(d, ls, 0, 0);
-}
-// ... and this one with the copy engine: four workers per CTA (one thread each), every worker with its own ring.
-constexpr int kPushBulkWorkers = 4;
-__global__ void __launch_bounds__(kPushBulkWorkers * 32, 1) AllGatherPushBulkKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
-{
-    extern __shared__ __align__(128) uint8_t pushSmem[];
-    __shared__ uint32_t abortFlag;
-    const FusedParams &p = table ? table[blockIdx.y] : own;
-    const CommDev *d = p.dev;
-    const hcdev::LaunchState ls = hcdev::KernelBegin(d);
-    if (threadIdx.x == 0) abortFlag = 0;
+    if (threadIdx.x <= kPushKernelPushers) reports[threadIdx.x] = 0;
     __syncthreads();
-    AgPushBulk push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr};
-    const int w = threadIdx.x >> 5;
-    if (ElectOne()) push.Run((int)blockIdx.x * kPushBulkWorkers + w, (int)gridDim.x * kPushBulkWorkers, pushSmem + (size_t)w * AgPushBulk::kSmemBytes, &abortFlag, false);
-    __syncthreads();
-    if (threadIdx.x == 0 && abortFlag && p.shape.errFlag) atomicExch(p.shape.errFlag, 1u);
+    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr, p.pushWarps, p.signaller};
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int first = (int)blockIdx.x * kPushKernelPushers, warps = (int)gridDim.x * kPushKernelPushers;
+    if (w < kPushKernelPushers) {
+        push.Run(first + w, warps, lane, p.signaller ? &reports[w] : nullptr);
+    } else if (lane == 0 && p.signaller) {
+        volatile uint32_t *abortFlag = &reports[kPushKernelPushers];
+        push.Signal<kPushKernelPushers>(first, warps, reports, abortFlag, false);
+        if (*abortFlag && p.shape.errFlag) atomicExch(p.shape.errFlag, 1u);
+    }
     hcdev::KernelEnd(d, ls, 0, 0);
 }
 
@@ -642,12 +671,16 @@ bool PairKernelsEnabled()
     return on;
 }
 
-// Remote rows leave through the SM's copy engine (bulk copies) unless HCOMM_FUSED_BULK=0 asks for the kernels that
-// move them with their own load and store instructions.
-bool BulkEnabled()
+// The signaller warps are on unless HCOMM_FUSED_SIGNALLER=0 (then every warp that moves data fences and publishes its own).
+bool SignallerEnabled()
 {
-    static const bool on = [] { const char *e = getenv("HCOMM_FUSED_BULK"); return !(e && e[0] == '0'); }();
+    static const bool on = [] { const char *e = getenv("HCOMM_FUSED_SIGNALLER"); return !(e && e[0] == '0'); }();
     return on;
+}
+int PushWarps()
+{
+    static const int v = [] { const char *e = getenv("HCOMM_FUSED_PUSH_WARPS"); const int n = e ? atoi(e) : 6; return n >= 1 && n <= 6 ? n : 6; }();
+    return v;
 }
 
 // CTA pairs of `kernel` (compile-time cluster of two) that can be resident at once; 0 when pairs cannot be scheduled.
@@ -746,9 +779,8 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     const int rowsPer = M / p;
     mode = ResolveMode(mode);
     const bool emu = c->emuSameDevice && c->nRanks > 1;
-    const bool bulk = BulkEnabled();
-    auto pairKernel = bulk ? GemmReduceScatterPairKernel<true> : GemmReduceScatterPairKernel<false>;
-    constexpr int pairSmem = Config2<256, 6, true>::kSmemBytes;
+    auto pairKernel = SignallerEnabled() ? GemmReduceScatterPairKernel<true> : GemmReduceScatterPairKernel<false>;
+    constexpr int pairSmem = Config2<256, 6, true, RsSignaller::kSmemBytes>::kSmemBytes;      // enough for both forms
     const bool usePair = PairKernelsEnabled() && !emu && rowsPer % kPairM == 0 && N % 256 == 0 && PairCapacityOf(pairKernel, kFusedThreads, pairSmem) > 0;
     const int blockRows = usePair ? kPairM : kBlockM;
     const bool fits = (uint64_t)p * rowsPer * N * 2 <= c->halfBytes && (uint64_t)p * (rowsPer / blockRows) * (N / BN) <= (uint64_t)kRsMaxSrcTiles;
@@ -796,15 +828,7 @@ namespace {
 template <int BN>
 HcclResult LaunchAgPair(Comm *c, const FusedParams &hp, int tiles, void *stream)
 {
-    if (BulkEnabled())
-        return LaunchFusedPair(c, AllGatherGemmPairKernel<BN, true>, kAgBulkThreads, Config2<BN, 6, false, AgPushBulk::kSmemBytes>::kSmemBytes, hp, tiles, stream);
-    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN, false>, kAgThreads, Config2<BN, 7>::kSmemBytes, hp, tiles, stream);
-}
-// pairs of the widest all-gather kernel that can be resident (the narrower ones need less shared memory)
-int AgPairCapacity()
-{
-    if (BulkEnabled()) return PairCapacityOf(AllGatherGemmPairKernel<256, true>, kAgBulkThreads, Config2<256, 6, false, AgPushBulk::kSmemBytes>::kSmemBytes);
-    return PairCapacityOf(AllGatherGemmPairKernel<256, false>, kAgThreads, Config2<256, 7>::kSmemBytes);
+    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN>, kAgPairThreads, Config2<BN, 7, false, AgPush::kSmemBytes>::kSmemBytes, hp, tiles, stream);
 }
 }  // namespace
 
@@ -830,9 +854,10 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     // The staging copy of the gathered activations lives in this operator's CCL half; which half is only known on
     // the device (launch parity), so a map is built for each and the kernel picks.
     const bool emu = c->emuSameDevice && c->nRanks > 1;
-    const bool usePair = PairKernelsEnabled() && !emu && Mshard % kPairM == 0 && N % 128 == 0 && AgPairCapacity() > 0;
+    const bool usePair = PairKernelsEnabled() && !emu && Mshard % kPairM == 0 && N % 128 == 0 &&
+                         PairCapacityOf(AllGatherGemmPairKernel<256>, kAgPairThreads, Config2<256, 7, false, AgPush::kSmemBytes>::kSmemBytes) > 0;
     int BN = N % 256 == 0 ? 256 : 128;
-    if (usePair) BN = PickPairTileWidth(M / kPairM, N, AgPairCapacity());
+    if (usePair) BN = PickPairTileWidth(M / kPairM, N, PairCapacityOf(AllGatherGemmPairKernel<256>, kAgPairThreads, Config2<256, 7, false, AgPush::kSmemBytes>::kSmemBytes));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, x, (uint64_t)Mshard, (uint64_t)K, (uint64_t)ldx, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2, c->CclBuffer(), (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2b, c->CclBuffer() + c->halfBytes, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
@@ -843,22 +868,17 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     char *local = FusedLocal(c);
     if (!local) return HCCL_E_MEMORY;
     hp.sent = (uint32_t *)local;
+    hp.pushWarps = PushWarps(); hp.signaller = SignallerEnabled() ? 1 : 0;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     if (mode == HCOMM_FUSED_MODE_SPLIT && !emu && p > 1) {
         // first launch: the push on the whole GPU; the GEMM launched next waits for the peers' flags like the fused form
-        if (BulkEnabled()) {
-            constexpr int smem = kPushBulkWorkers * AgPushBulk::kSmemBytes;
-            SetSmemOnce(AllGatherPushBulkKernel, smem);
-            AllGatherPushBulkKernel<<<dim3(GemmSmCount(), 1, 1), kPushBulkWorkers * 32, smem, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
-        } else {
-            AllGatherPushKernel<<<dim3(GemmSmCount(), 1, 1), 512, 0, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
-        }
+        AllGatherPushKernel<<<dim3(GemmSmCount(), 1, 1), 512, 0, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
         if (cudaGetLastError() != cudaSuccess) return HCCL_E_RUNTIME;
         hp.xLocal = nullptr;
     }
     if (usePair) {
-        c->fusedLastCtas = 2 * std::min(AgPairCapacity(), tiles);
+        c->fusedLastCtas = 2 * std::min(PairCapacityOf(AllGatherGemmPairKernel<256>, kAgPairThreads, Config2<256, 7, false, AgPush::kSmemBytes>::kSmemBytes), tiles);
         switch (BN) {
             case 256: return LaunchAgPair<256>(c, hp, tiles, stream);
             case 224: return LaunchAgPair<224>(c, hp, tiles, stream);

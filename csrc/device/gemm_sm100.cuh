@@ -72,8 +72,8 @@ struct SharedState {
     volatile uint32_t abort;
 };
 
-// Extra policies run on the warps after the six GEMM warps; kSmemBytes of shared memory (after the operand ring
-// and the epilogue staging) are theirs in the CTA-pair main loop.
+// Extra policies run on the warps after the six GEMM warps.  In the CTA-pair main loop kSmemBytes of shared memory
+// (a multiple of 16, zeroed before any role starts) are theirs; epilogue policies with kReportsTiles see it too.
 struct NoExtra {
     static constexpr int kSmemBytes = 0;
     __device__ __forceinline__ void operator()(int, int, volatile uint32_t *, uint8_t * = nullptr) const {}
@@ -234,7 +234,7 @@ struct NoGate {
 // Writes bf16 rows of C; each thread stores its 32 columns as four 16-byte vectors.
 struct StoreBf16 {
     static constexpr bool kStaged = false;
-    static constexpr bool kBulk = false;
+    static constexpr bool kReportsTiles = false;
     __nv_bfloat16 *C;
     int ldc, M, N;
     __device__ __forceinline__ void BeginTile(int, int, int) const {}

@@ -22,8 +22,8 @@ namespace hcgemm {
 
 constexpr int kPairM = 256;
 
-constexpr int kStagingBytesPerWarp = 32 * 128 * 2 + 128;   // 32 rows x 128 bf16 columns, 16 bytes of padding after every 4th row
-constexpr int kStagingBytes = 4 * kStagingBytesPerWarp;     // one slab per epilogue warp
+constexpr int kStagingBytesPerWarp = 32 * 128 * 2;      // 32 rows x 128 bf16 columns
+constexpr int kStagingBytes = 4 * kStagingBytesPerWarp;  // one slab per epilogue warp
 
 // BN: width of the pair's tile, a multiple of 32 between 128 and 256 (each CTA holds BN / 2 rows of B, whole 8-row
 // swizzle groups, and the epilogue reads 32 columns at a time).  Widths below 256 exist for the tail: a problem whose
@@ -38,13 +38,13 @@ template <int BN, int STAGES = 6, bool STAGING = false, int EXTRA = 0> struct Co
     static constexpr int kBBytes = (BN / 2) * kBlockK * 2;         // 128 of the 256 B rows per CTA
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kTmemCols = 2 * BN <= 256 ? 256 : 512;    // two accumulators; allocations are powers of two
-    static constexpr int kExtra = EXTRA;                           // shared memory of the Extra policy (a multiple of 16)
+    static constexpr int kExtra = EXTRA;                           // shared memory of the Extra policy
     static constexpr int kSmemBytes = kStages * kStageBytes + kStaging + kExtra + 1024 + 256;
     static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 };
 
 // Epilogue policies without a staged path.
-struct NoStaging { static constexpr bool kStaged = false; static constexpr bool kBulk = false; };
+struct NoStaging { static constexpr bool kStaged = false; };
 
 namespace pair {
 
@@ -126,10 +126,6 @@ __device__ __forceinline__ uint4 StageGet(const uint8_t *slab, int row, int chun
 {
     return *(const uint4 *)(slab + row * 256 + ((chunk ^ (row & 15)) << 4));
 }
-// The other layout of a slab, for rows that leave through the SM's copy engine: every row is 256 contiguous
-// bytes (a bulk copy moves a linear range), and 16 bytes of padding after every fourth row put the 32 lanes of a
-// row-wise write on all banks (lane l: bank group (l / 4 + chunk) % 8, four lanes each - the minimum for 512 bytes).
-__device__ __forceinline__ uint8_t *StageRowLinear(uint8_t *slab, int row) { return slab + row * 256 + ((row >> 2) << 4); }
 // Writes the slab to dst[row * pitchBytes + 0..255] for rows 0..31 (dst may be peer memory).
 __device__ __forceinline__ void StageFlushRows(const uint8_t *slab, char *dst, size_t pitchBytes, int lane)
 {
@@ -147,7 +143,7 @@ __device__ __forceinline__ void StageFlushRows(const uint8_t *slab, char *dst, s
 // For shapes whose tiles are complete (M a multiple of 256, N a multiple of 256).
 struct StoreBf16Staged {
     static constexpr bool kStaged = true;
-    static constexpr bool kBulk = false;
+    static constexpr bool kReportsTiles = false;
     __nv_bfloat16 *C;
     int ldc;
     __device__ __forceinline__ bool StagedTile(int) const { return true; }
@@ -186,6 +182,7 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
         for (int s = 0; s < Cfg::kStages; ++s) { MbarInit(&st->full[s], 1); MbarInit(&st->empty[s], 1); }
         for (int a = 0; a < 2; ++a) { MbarInit(&st->tmemFull[a], 1); MbarInit(&st->tmemEmpty[a], 8); }   // 4 epilogue warps x 2 CTAs
         st->abort = 0;
+        for (int i = 0; i < Cfg::kExtra / 4; ++i) ((volatile uint32_t *)extraSmem)[i] = 0;
         MbarFenceInit();
         TmaPrefetchDescriptor(tmA);
         TmaPrefetchDescriptor(tmB);
@@ -261,10 +258,6 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
         const int q = warp & 3;
         uint32_t tileIter = 0;
         bool alive = true;
-        // A tile whose rows left through bulk copies is published (EndTile) once the copies are complete; the warp
-        // does not wait for that at the end of the tile but when it comes back for the next one.
-        bool owed = false;
-        int owedMb = 0, owedNb = 0, owedRow = 0;
         for (int t = firstTile; t < numTiles && alive; t += tileStep, ++tileIter) {
             int mb, nb;
             order(t, g, &mb, &nb);
@@ -278,47 +271,12 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
             }
             if (!MbarWait(&st->tmemFull[acc], accPh, &st->abort)) { alive = false; break; }
             TcFenceAfter();
-            if constexpr (Epilogue::kBulk) {
-                if (owed) {
-                    TmaStoreWait<0>();
-                    __syncwarp();
-                    epi.EndTile(owedMb, owedNb, owedRow);
-                    owed = false;
-                }
-            }
             const int row = mb * kPairM + (int)ctaRank * kBlockM + q * 32 + lane;
             epi.BeginTile(mb, nb, row);
             bool staged = false;
             if constexpr (Epilogue::kStaged) staged = epi.StagedTile(mb);
             if (staged) {
-                if constexpr (Epilogue::kBulk) {
-                    // every lane parks its own row (256 bytes per 128 columns) and sends it with one bulk copy
-                    uint8_t *mine = StageRowLinear(staging + q * kStagingBytesPerWarp, lane);
-#pragma unroll 1
-                    for (int c0 = 0; c0 < BN; c0 += 128) {
-#pragma unroll 1
-                        for (int c = 0; c < 128; c += 32) {
-                            uint32_t frag[32];
-                            TmemLoad32x32(tmemBase + ((uint32_t)(q * 32) << 16) + acc * BN + c0 + c, frag);
-                            TmemLoadWait();
-                            if (c == 0) TmaStoreWaitRead<0>();          // the row's previous contents have left shared memory
-#pragma unroll
-                            for (int v = 0; v < 4; ++v) {
-                                uint4 pk;
-                                uint32_t *pw = (uint32_t *)&pk;
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(frag[v * 8 + 2 * j]), __uint_as_float(frag[v * 8 + 2 * j + 1]));
-                                    pw[j] = *(uint32_t *)&h;
-                                }
-                                *(uint4 *)(mine + (((c >> 3) + v) << 4)) = pk;
-                            }
-                        }
-                        FenceProxyAsyncShared();                          // my writes, before the copy engine reads them
-                        BulkStore(epi.RowDst(mb, row, nb * BN + c0), mine, 256);
-                        TmaStoreCommit();
-                    }
-                } else if constexpr (Epilogue::kStaged) {
+                if constexpr (Epilogue::kStaged) {
                     uint8_t *slab = staging + q * kStagingBytesPerWarp;
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 128) {
@@ -359,17 +317,9 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
                 if (leader) MbarArrive(&st->tmemEmpty[acc]);
                 else RemoteArrive(MapToCta(&st->tmemEmpty[acc], 0));
             }
-            if (Epilogue::kBulk && staged) {
-                owed = true; owedMb = mb; owedNb = nb; owedRow = row;
-            } else {
-                epi.EndTile(mb, nb, row);
-            }
-        }
-        if constexpr (Epilogue::kBulk) {
-            // also after a wait that ran out: this thread's copies still read its shared memory
-            TmaStoreWait<0>();
-            __syncwarp();
-            if (owed) epi.EndTile(owedMb, owedNb, owedRow);
+            epi.EndTile(mb, nb, row);
+            // epilogues that leave the publication of their tiles to another warp count them here
+            if constexpr (Epilogue::kReportsTiles) epi.TileDone(q, tileIter + 1, extraSmem, lane);
         }
     }
     // Nobody leaves while the peer may still read this CTA's shared memory, signal its barriers or use its

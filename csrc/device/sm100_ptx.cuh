@@ -86,18 +86,6 @@ __device__ __forceinline__ void TmaStoreCommit() { asm volatile("cp.async.bulk.c
 template <int N> __device__ __forceinline__ void TmaStoreWaitRead() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
 template <int N> __device__ __forceinline__ void TmaStoreWait() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void FenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-// Untiled bulk copies (the copy engine of the SM moves a linear range): both addresses 16-byte aligned, the size a
-// multiple of 16 bytes.  The store belongs to the issuing thread's bulk group (TmaStoreCommit / TmaStoreWait*); its
-// destination may be another GPU's memory.  The load completes on an mbarrier and only ever reads this GPU's memory.
-__device__ __forceinline__ void BulkStore(void *globalDst, const void *smemSrc, uint32_t bytes)
-{
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(globalDst), "r"(SmemAddr(smemSrc)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void BulkLoad(void *smemDst, const void *globalSrc, uint32_t bytes, uint64_t *bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(SmemAddr(smemDst)), "l"(globalSrc), "r"(bytes), "r"(SmemAddr(bar)) : "memory");
-}
 
 // ------------------------------------------------------------------------------ tensor memory
 

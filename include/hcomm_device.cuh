@@ -57,6 +57,18 @@ __device__ __forceinline__ void StRelaxedSys(uint32_t *p, uint32_t v)
     asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void FenceAcqRelSys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
+// Hand-off inside a CTA through a word in shared memory: the writer's earlier accesses (and those it has observed, e.g.
+// its warp's after __syncwarp) are ordered before whatever the reader does after it has seen the value.
+__device__ __forceinline__ void StReleaseCtaShared(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t LdAcquireCtaShared(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"((uint32_t)__cvta_generic_to_shared(p)) : "memory");
+    return v;
+}
 __device__ __forceinline__ void RedReleaseSysAdd64(uint64_t *p, uint64_t v)
 {
     asm volatile("red.release.sys.global.add.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");

@@ -257,7 +257,9 @@ def main():
             forced = comm.split(list(range(world)), sub_id=7, buffer_mb=int(os.environ.get("HCOMM_TEST_BUFFER_MB", "16")),
                                 algo="allreduce=level0:nvls/allgather=level0:nvls/reducescatter=level0:nvls")
             # 144 CTAs x 512 threads = 73728 vectors per sweep; these counts leave partial sweeps on every rank
-            for dtype, count in ((torch.float32, (73728 * 4 * 3 + 40) * world), (torch.bfloat16, (73728 * 8 * 2 + 4104) * world), (torch.float32, 20_000_000 // world * world)):
+            for dtype, count in ((torch.float32, (73728 * 4 * 3 + 40) * world), (torch.bfloat16, (73728 * 8 * 2 + 4104) * world), (torch.float32, 20_000_000 // world * world),
+                                 (torch.bfloat16, 40_000_000 // (8 * world) * (8 * world))):
+                # the two 80 MB operands take the pipelined kernel (the test lowers its threshold to 32 MB): ten windows
                 check_all(forced, "nvls forced", dtype, count)
             check_all(forced, "nvls forced, ragged", torch.bfloat16, 3_000_001)
             forced.destroy()

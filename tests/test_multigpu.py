@@ -19,7 +19,7 @@ def test_collectives_across_gpus(world):
 def test_windows_nvls_and_registered_buffers_across_gpus(world):
     if cuda_device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    codes, outs = launch("collectives_big", world, {"HCOMM_TEST_BUFFER_MB": "16", "HCCL_EXEC_TIMEOUT": "30"}, timeout=300)
+    codes, outs = launch("collectives_big", world, {"HCOMM_TEST_BUFFER_MB": "16", "HCCL_EXEC_TIMEOUT": "30", "HCCL_NVLS_PIPELINE_MIN_MB": "32"}, timeout=300)
     assert codes == [0] * world, "\n".join(outs)
 
 
