@@ -73,7 +73,10 @@ static_assert((size_t)(kRsFlagBase + kRsMaxSrcTiles * 8) * 4 <= HC_OFF_TEAM_SYNC
 // Device-local scratch of a communicator (Comm::fusedLocal): chunk counters of the push, then the phase clocks.
 constexpr size_t kLocalSentWords = kAgMaxBlocks;
 constexpr size_t kLocalPhaseWords = 2 * 160 * kPhaseSlots;     // u64, two CTAs per SM pair slot, up to 160 SMs
-constexpr size_t kLocalBytes = kLocalSentWords * 4 + kLocalPhaseWords * 8;
+constexpr int kRsMaxLocalTiles = 4096;                            // tiles of a reduce-scatter whose partial tiles go through the outbox
+constexpr size_t kLocalReadyWords = (size_t)kRsMaxLocalTiles * 8;  // u32: (tile, row group) of my partial product is in the outbox
+constexpr size_t kLocalReadyOffset = kLocalSentWords * 4 + kLocalPhaseWords * 8;
+constexpr size_t kLocalBytes = kLocalReadyOffset + kLocalReadyWords * 4;
 
 struct FusedParams {
     CUtensorMap tmA, tmB, tmA2, tmA2b;   // tmA2 / tmA2b: staging copy of A in CCL half 0 / 1
@@ -86,6 +89,8 @@ struct FusedParams {
     int rowsPer;              // rows per rank
     int K;
     uint32_t *sent;           // AG: device-local chunk counters [peer index][block]
+    char *outbox;             // RS with communication CTAs: my partial product [M, N] bf16 in local memory
+    uint32_t *ready;          // RS with communication CTAs: device-local flags, (tile, row group) is in the outbox
     int pushWarps;            // AG, CTA-pair kernel: pushing warps per CTA that take part (1..6)
     int signaller;            // AG, CTA-pair kernel: a seventh warp publishes the chunks (1) or every pushing warp its own (0)
 };
@@ -132,16 +137,22 @@ __device__ __forceinline__ uint32_t *RsTileFlag(const CommDev *d, int owner, int
 }
 
 // TILE_ROWS: 128 (one CTA per tile) or 256 (CTA pair).  A row group is the 32 rows one epilogue warp owns.
-// SIGNALLED: the warp does not publish its row groups itself (RsSignaller does).
-template <int BN, int TILE_ROWS, bool SIGNALLED = false>
+// MODE: who publishes a partial tile.  kRsDirect: the epilogue warp itself, after a fence.  kRsSignalled: RsSignaller,
+// a warp of the same CTA.  kRsOutbox: the partial tile does not leave the GPU here at all - it goes to a local matrix (the
+// outbox) with a local "ready" flag, and the communication CTAs (RsForward) carry it to its owner.
+constexpr int kRsDirect = 0, kRsSignalled = 1, kRsOutbox = 2;
+template <int BN, int TILE_ROWS, int MODE = kRsDirect>
 struct RsEpilogue {
     static constexpr bool kStaged = true;      // the CTA-pair main loop sends partial tiles out as whole 256-byte row segments
-    static constexpr bool kReportsTiles = SIGNALLED;
+    static constexpr bool kReportsTiles = MODE == kRsSignalled;
+    static constexpr bool SIGNALLED = MODE == kRsSignalled;
     const CommDev *d;
     __nv_bfloat16 *out;
     int ldOut, N, mbPer, rowsPer, tilesN;
     uint32_t half, seq;
     uint64_t *phase;                           // this CTA's phase clocks or NULL
+    char *outbox;                              // kRsOutbox only
+    uint32_t *ready;
 
     __device__ __forceinline__ char *Slot(int owner, int src) const
     {
@@ -156,7 +167,8 @@ struct RsEpilogue {
     __device__ __forceinline__ void StoreStaged(int mb, int, int rowBase, int colBase, const uint8_t *slab, int lane) const
     {
         const int q = mb / mbPer;
-        char *dst = Slot(q, d->rank) + ((size_t)(rowBase - q * rowsPer) * N + colBase) * sizeof(__nv_bfloat16);
+        char *dst = MODE == kRsOutbox ? outbox + ((size_t)rowBase * N + colBase) * sizeof(__nv_bfloat16)
+                                      : Slot(q, d->rank) + ((size_t)(rowBase - q * rowsPer) * N + colBase) * sizeof(__nv_bfloat16);
         hcgemm::pair::StageFlushRows(slab, dst, (size_t)N * sizeof(__nv_bfloat16), lane);
     }
     // `row` is the calling thread's row; the warp's 32 rows form row group (row of lane 0 - tile start) / 32.
@@ -254,6 +266,14 @@ struct RsEpilogue {
         if (SIGNALLED || q == d->rank) return;
         __syncwarp();
         const int lane = threadIdx.x & 31;
+        if (MODE == kRsOutbox) {
+            // local hand-over to the communication CTAs: release at GPU scope, nothing waits for NVLink
+            if (lane == 0) {
+                const int group = (row - mb * TILE_ROWS) >> 5;
+                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(ready + ((size_t)mb * tilesN + nb) * 8 + group), "r"(seq) : "memory");
+            }
+            return;
+        }
         if (lane == 0) {
             const int group = (row - mb * TILE_ROWS) >> 5;
             const uint64_t t0 = phase ? GlobalTimer() : 0;
@@ -286,7 +306,7 @@ struct RsSignaller {
         const GemmShape &shape = *shapePtr;
         const uint32_t *done = (const uint32_t *)shared;
         const int me = d->rank, numTiles = shape.tilesM * shape.tilesN;
-        const int first = (int)pair::ClusterId(), step = (int)pair::NumClusters(), ctaRank = (int)pair::ClusterCtaRank();
+        const int first = (int)pair::ClusterId(), step = shape.clusters > 0 ? shape.clusters : (int)pair::NumClusters(), ctaRank = (int)pair::ClusterCtaRank();
         const int mine = first < numTiles ? (numTiles - first + step - 1) / step : 0;
         int k = 0;
         uint32_t idle = 0;
@@ -320,6 +340,105 @@ struct RsSignaller {
     }
 };
 
+// Communication CTAs of the reduce-scatter (kRsOutbox): forwarding warps take the (partial tile, row group) units in
+// the order the GEMM CTAs produce them, wait for the unit's local ready flag, copy its 32 rows x 256 columns from the
+// outbox into this rank's slot on the owner and count it in shared memory; the CTA's last warp publishes the counted
+// units - one fence for all that were forwarded since it last looked, then the owner's flag word of each.
+// NF forwarding warps per CTA; their global numbers are firstWarp .. firstWarp + NF - 1 of `warps`.
+template <int NF>
+struct RsForward {
+    const CommDev *d;
+    RsOrder order;
+    const GemmShape *shapePtr;
+    int mbPer, rowsPer;
+    uint32_t half, seq;
+    const char *outbox;
+    const uint32_t *ready;
+    uint64_t *phase;
+
+    __device__ __forceinline__ int Units() const { return (d->nRanks - 1) * mbPer * shapePtr->tilesN * 8; }   // remote tiles come first in the order
+    __device__ __forceinline__ void Forward(int w, int warps, int lane, uint32_t *report, volatile uint32_t *abortFlag) const
+    {
+        const GemmShape &shape = *shapePtr;
+        const int units = Units(), me = d->rank, N = shape.N;
+        const size_t pitch = (size_t)N * sizeof(__nv_bfloat16);
+        uint32_t forwarded = 0;
+        for (int u = w; u < units; u += warps) {
+            int mb, nb;
+            order(u >> 3, shape, &mb, &nb);
+            const int g = u & 7, q = mb / mbPer;
+            const uint32_t *flag = ready + ((size_t)mb * shape.tilesN + nb) * 8 + g;
+            uint32_t polls = 0;
+            for (;;) {
+                uint32_t v;
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                if ((int32_t)(v - seq) >= 0) break;
+                if (*abortFlag) return;
+                if (++polls > kSignallerPolls) { *abortFlag = 1; return; }
+                __nanosleep(128);
+            }
+            const int row0 = mb * kPairM + g * 32;
+            const char *src = outbox + ((size_t)row0 * N + (size_t)nb * 256) * sizeof(__nv_bfloat16) + (size_t)lane * 16;
+            char *dst = hcdev::CclHalf(d, q, half) + (size_t)me * rowsPer * pitch + ((size_t)(row0 - q * rowsPer) * N + (size_t)nb * 256) * sizeof(__nv_bfloat16) +
+                        (size_t)lane * 16;
+            // a row of the unit is 512 bytes: one 16-byte access per lane; sixteen rows in flight per lane
+#pragma unroll 1
+            for (int r0 = 0; r0 < 32; r0 += 16) {
+                uint4 v[16];
+#pragma unroll
+                for (int r = 0; r < 16; ++r) v[r] = hcdev::Ld16Volatile(src + (size_t)(r0 + r) * pitch);
+#pragma unroll
+                for (int r = 0; r < 16; ++r) hcdev::St16(dst + (size_t)(r0 + r) * pitch, v[r]);
+            }
+            __syncwarp();
+            if (lane == 0) hcdev::StReleaseCtaShared(report, ++forwarded);
+        }
+    }
+    __device__ __forceinline__ void Publish(int firstWarp, int warps, const uint32_t *reports, volatile uint32_t *abortFlag) const
+    {
+        const GemmShape &shape = *shapePtr;
+        const int units = Units(), me = d->rank;
+        uint32_t published[NF], total[NF];
+        int remaining = 0;
+#pragma unroll
+        for (int w = 0; w < NF; ++w) {
+            published[w] = 0;
+            total[w] = firstWarp + w < units ? (uint32_t)((units - (firstWarp + w) + warps - 1) / warps) : 0u;
+            remaining += (int)total[w];
+        }
+        uint32_t idle = 0;
+        uint64_t tSignal = 0;
+        while (remaining > 0) {
+            uint32_t c[NF];
+            bool any = false;
+#pragma unroll
+            for (int w = 0; w < NF; ++w) { c[w] = hcdev::LdAcquireCtaShared(reports + w); any = any || c[w] > published[w]; }
+            if (!any) {
+                if (*abortFlag) return;
+                if (++idle > kSignallerPolls) { *abortFlag = 1; return; }
+                __nanosleep(128);
+                continue;
+            }
+            idle = 0;
+            const uint64_t t0 = phase ? GlobalTimer() : 0;
+            hcdev::FenceAcqRelSys();
+#pragma unroll
+            for (int w = 0; w < NF; ++w) {
+                for (uint32_t k = published[w]; k < c[w]; ++k) {
+                    const int u = firstWarp + w + (int)k * warps;
+                    int mb, nb;
+                    order(u >> 3, shape, &mb, &nb);
+                    hcdev::StRelaxedSys(RsTileFlag(d, mb / mbPer, me, mbPer, shape.tilesN, mb, nb, u & 7), seq);
+                }
+                remaining -= (int)(c[w] - published[w]);
+                published[w] = c[w];
+            }
+            if (phase) tSignal += GlobalTimer() - t0;
+        }
+        if (phase) { phase[kPhaseSignal] = tSignal; phase[kPhasePushEnd] = GlobalTimer(); }
+    }
+};
+
 __device__ __forceinline__ uint64_t *PhaseOfCta(const GemmShape &g)
 {
     return g.phase ? g.phase + (size_t)blockIdx.x * kPhaseSlots : nullptr;
@@ -332,21 +451,46 @@ __global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(cons
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
-    RsEpilogue<BN, kBlockM> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, nullptr};
+    RsEpilogue<BN, kBlockM> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, nullptr, nullptr, nullptr};
     GemmMainLoop<BN>(&p.tmA, &p.tmB, p.shape, order, NoGate(), epi);
     hcdev::KernelEnd(d, ls, 0);
 }
 
 // The same on CTA pairs (256 x 256 tiles): row blocks and blocks per rank count 256 rows; a tile has eight row groups.
-template <bool SIGNALLED>
+template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) GemmReduceScatterPairKernel(const __grid_constant__ FusedParams own, const FusedParams *table)
 {
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
     RsOrder order{d->rank, d->nRanks, p.mbPer};
-    RsEpilogue<256, kPairM, SIGNALLED> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, PhaseOfCta(p.shape)};
-    if constexpr (SIGNALLED) {
+    if constexpr (MODE == kRsOutbox) {
+        const int gemmCtas = p.shape.clusters > 0 ? 2 * p.shape.clusters : (int)gridDim.x;
+        if ((int)blockIdx.x >= gemmCtas) {
+            // communication CTA: seven warps forward, the eighth publishes
+            constexpr int NF = kFusedThreads / 32 - 1;
+            __shared__ uint32_t reports[NF + 1];
+            uint64_t *phase = PhaseOfCta(p.shape);
+            if (threadIdx.x <= NF) reports[threadIdx.x] = 0;
+            if (threadIdx.x == 0 && phase) phase[kPhaseStart] = GlobalTimer();
+            __syncthreads();
+            RsForward<NF> fwd{d, order, &p.shape, p.mbPer, p.rowsPer, ls.half, ls.seq, p.outbox, p.ready, phase};
+            const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            const int first = ((int)blockIdx.x - gemmCtas) * NF, warps = ((int)gridDim.x - gemmCtas) * NF;
+            volatile uint32_t *abortFlag = &reports[NF];
+            if (w < NF) fwd.Forward(first + w, warps, lane, &reports[w], abortFlag);
+            else if (lane == 0) fwd.Publish(first, warps, reports, abortFlag);
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                if (*abortFlag && p.shape.errFlag) atomicExch(p.shape.errFlag, 1u);
+                if (phase) phase[kPhaseEnd] = GlobalTimer();
+            }
+            hcdev::KernelEnd(d, ls, 0);
+            return;
+        }
+    }
+    RsEpilogue<256, kPairM, MODE> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, PhaseOfCta(p.shape), p.outbox, p.ready};
+    if constexpr (MODE == kRsSignalled) {
         RsSignaller signaller{d, order, &p.shape, p.mbPer, ls.seq, PhaseOfCta(p.shape)};
         GemmMainLoopPair<256, 6>(&p.tmA, &p.tmB, p.shape, order, epi, NoGate(), nullptr, signaller);
     } else {
@@ -575,9 +719,36 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAgPairThreads, 1) A
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
+    const int gemmCtas = p.shape.clusters > 0 ? 2 * p.shape.clusters : (int)gridDim.x;
+    if ((int)blockIdx.x >= gemmCtas) {
+        // Communication CTA (the last pairs of the grid when the host sets some aside): twelve warps push, the
+        // thirteenth publishes; no tile is computed here, so the stores that queue up behind a busy NVLink hold up
+        // nobody's operand loads.
+        constexpr int NP = kAgPairThreads / 32 - 1;
+        __shared__ uint32_t reports[NP + 1];
+        uint64_t *phase = PhaseOfCta(p.shape);
+        if (threadIdx.x <= NP) reports[threadIdx.x] = 0;
+        if (threadIdx.x == 0 && phase) phase[kPhaseStart] = GlobalTimer();
+        __syncthreads();
+        AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, phase, NP, 1};
+        const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        const int first = ((int)blockIdx.x - gemmCtas) * NP, warps = ((int)gridDim.x - gemmCtas) * NP;
+        if (w < NP) {
+            push.Run(first + w, warps, lane, &reports[w], w == 0);
+        } else if (lane == 0) {
+            volatile uint32_t *abortFlag = &reports[NP];
+            push.Signal<NP>(first, warps, reports, abortFlag, true);
+            if (*abortFlag && p.shape.errFlag) atomicExch(p.shape.errFlag, 1u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0 && phase) phase[kPhaseEnd] = GlobalTimer();
+        hcdev::KernelEnd(d, ls, 0);
+        return;
+    }
     AgOrder order{d->rank, d->nRanks, p.mbPer / 2};
     AgGate gate{d, p.mbPer, ls.seq, PhaseOfCta(p.shape)};
-    AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape), p.pushWarps, p.signaller};
+    // with communication CTAs the extra warps of the GEMM CTAs have nothing to push
+    AgPush push{d, gemmCtas < (int)gridDim.x ? nullptr : (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape), p.pushWarps, p.signaller};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
     GemmMainLoopPair<BN, 7>(&p.tmA, &p.tmB, p.shape, order, epi, gate, ls.half ? &p.tmA2b : &p.tmA2, push);
     hcdev::KernelEnd(d, ls, 0);
@@ -677,6 +848,19 @@ bool SignallerEnabled()
     static const bool on = [] { const char *e = getenv("HCOMM_FUSED_SIGNALLER"); return !(e && e[0] == '0'); }();
     return on;
 }
+// CTAs of the all-gather CTA-pair kernel set aside for communication (HCOMM_FUSED_COMM_CTAS, even; 0 = the extra warps
+// of every CTA push).
+int CommCtas()
+{
+    static const int v = [] { const char *e = getenv("HCOMM_FUSED_COMM_CTAS"); const int n = e ? atoi(e) : 0; return n > 0 && n <= 64 ? (n + 1) / 2 * 2 : 0; }();
+    return v;
+}
+// The same for the reduce-scatter kernel (HCOMM_FUSED_RS_COMM_CTAS; 0 = the epilogue warps store to the owners themselves).
+int RsCommCtas()
+{
+    static const int v = [] { const char *e = getenv("HCOMM_FUSED_RS_COMM_CTAS"); const int n = e ? atoi(e) : 0; return n > 0 && n <= 64 ? (n + 1) / 2 * 2 : 0; }();
+    return v;
+}
 int PushWarps()
 {
     static const int v = [] { const char *e = getenv("HCOMM_FUSED_PUSH_WARPS"); const int n = e ? atoi(e) : 6; return n >= 1 && n <= 6 ? n : 6; }();
@@ -710,11 +894,11 @@ int PairCapacityOf(KernelT kernel, int threads, int smemBytes)
 
 // Launches a CTA-pair kernel on as many pairs as can be resident at once.
 template <typename KernelT>
-HcclResult LaunchFusedPair(Comm *c, KernelT kernel, int threads, int smemBytes, const FusedParams &hp, int tiles, void *stream)
+HcclResult LaunchFusedPair(Comm *c, KernelT kernel, int threads, int smemBytes, const FusedParams &hp, int tiles, void *stream, int pairsWanted = 0)
 {
     const int cap = PairCapacityOf(kernel, threads, smemBytes);
-    if (cap <= 0) return HCCL_E_NOT_SUPPORT;
-    const int pairs = std::min(cap, tiles);
+    if (cap <= 0 || pairsWanted > cap) return HCCL_E_NOT_SUPPORT;
+    const int pairs = pairsWanted > 0 ? pairsWanted : std::min(cap, tiles);
     kernel<<<dim3(2 * pairs, 1, 1), threads, smemBytes, (cudaStream_t)stream>>>(hp, (const FusedParams *)nullptr);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) { HCCL_ERROR("fused launch (CTA pairs) failed: %s", cudaGetErrorString(e)); return HCCL_E_RUNTIME; }
@@ -779,8 +963,10 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     const int rowsPer = M / p;
     mode = ResolveMode(mode);
     const bool emu = c->emuSameDevice && c->nRanks > 1;
-    auto pairKernel = SignallerEnabled() ? GemmReduceScatterPairKernel<true> : GemmReduceScatterPairKernel<false>;
-    constexpr int pairSmem = Config2<256, 6, true, RsSignaller::kSmemBytes>::kSmemBytes;      // enough for both forms
+    constexpr int pairSmem = Config2<256, 6, true, RsSignaller::kSmemBytes>::kSmemBytes;      // enough for every form
+    // communication CTAs (the outbox form) need the whole partial product in local memory and a ready flag per tile
+    const int commWanted = (p > 1 && mode != HCOMM_FUSED_MODE_SPLIT && (M / kPairM) * (N / 256) <= kRsMaxLocalTiles) ? RsCommCtas() : 0;
+    auto pairKernel = commWanted > 0 ? GemmReduceScatterPairKernel<kRsOutbox> : (SignallerEnabled() ? GemmReduceScatterPairKernel<kRsSignalled> : GemmReduceScatterPairKernel<kRsDirect>);
     const bool usePair = PairKernelsEnabled() && !emu && rowsPer % kPairM == 0 && N % 256 == 0 && PairCapacityOf(pairKernel, kFusedThreads, pairSmem) > 0;
     const int blockRows = usePair ? kPairM : kBlockM;
     const bool fits = (uint64_t)p * rowsPer * N * 2 <= c->halfBytes && (uint64_t)p * (rowsPer / blockRows) * (N / BN) <= (uint64_t)kRsMaxSrcTiles;
@@ -816,19 +1002,35 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / blockRows; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
     hp.shape.phase = usePair ? PhaseBuffer(c, stream) : nullptr;
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / blockRows; hp.rowsPer = rowsPer; hp.K = K;
-    ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
-    c->fusedLastCtas = usePair ? 2 * std::min(PairCapacityOf(pairKernel, kFusedThreads, pairSmem), tiles) : 0;
-    if (usePair) return LaunchFusedPair(c, pairKernel, kFusedThreads, pairSmem, hp, tiles, stream);
+    int pairsWanted = 0;
+    if (usePair && commWanted > 0) {
+        const int cap = PairCapacityOf(pairKernel, kFusedThreads, pairSmem), commPairs = std::min(commWanted / 2, cap / 2);
+        const size_t need = (size_t)M * N * 2;
+        if (c->fusedTempBytes < need) {
+            if (c->fusedTemp) { cudaStreamSynchronize((cudaStream_t)stream); cudaFree(c->fusedTemp); c->fusedTemp = nullptr; c->fusedTempBytes = 0; }
+            if (cudaMalloc(&c->fusedTemp, need) != cudaSuccess) { cudaGetLastError(); return HCCL_E_MEMORY; }
+            c->fusedTempBytes = need;
+        }
+        char *local = FusedLocal(c);
+        if (!local) return HCCL_E_MEMORY;
+        hp.outbox = (char *)c->fusedTemp;
+        hp.ready = (uint32_t *)(local + kLocalReadyOffset);
+        hp.shape.clusters = std::min(cap - commPairs, tiles);
+        pairsWanted = hp.shape.clusters + commPairs;
+    }
+    ++c->opSeq;
+    c->fusedLastCtas = usePair ? (pairsWanted > 0 ? 2 * pairsWanted : 2 * std::min(PairCapacityOf(pairKernel, kFusedThreads, pairSmem), tiles)) : 0;
+    if (usePair) return LaunchFusedPair(c, pairKernel, kFusedThreads, pairSmem, hp, tiles, stream, pairsWanted);
     if (BN == 256) return LaunchFused(c, GemmReduceScatterKernel<256>, kFusedThreads, Config<256>::kSmemBytes, hp, tiles, 9001, stream);
     return LaunchFused(c, GemmReduceScatterKernel<128>, kFusedThreads, Config<128>::kSmemBytes, hp, tiles, 9002, stream);
 }
 
 namespace {
 template <int BN>
-HcclResult LaunchAgPair(Comm *c, const FusedParams &hp, int tiles, void *stream)
+HcclResult LaunchAgPair(Comm *c, const FusedParams &hp, int tiles, void *stream, int pairs)
 {
-    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN>, kAgPairThreads, Config2<BN, 7, false, AgPush::kSmemBytes>::kSmemBytes, hp, tiles, stream);
+    return LaunchFusedPair(c, AllGatherGemmPairKernel<BN>, kAgPairThreads, Config2<BN, 7, false, AgPush::kSmemBytes>::kSmemBytes, hp, tiles, stream, pairs);
 }
 }  // namespace
 
@@ -857,7 +1059,11 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     const bool usePair = PairKernelsEnabled() && !emu && Mshard % kPairM == 0 && N % 128 == 0 &&
                          PairCapacityOf(AllGatherGemmPairKernel<256>, kAgPairThreads, Config2<256, 7, false, AgPush::kSmemBytes>::kSmemBytes) > 0;
     int BN = N % 256 == 0 ? 256 : 128;
-    if (usePair) BN = PickPairTileWidth(M / kPairM, N, PairCapacityOf(AllGatherGemmPairKernel<256>, kAgPairThreads, Config2<256, 7, false, AgPush::kSmemBytes>::kSmemBytes));
+    // pairs that compute tiles: all that can be resident, less the ones set aside for communication
+    const int pairCap = usePair ? PairCapacityOf(AllGatherGemmPairKernel<256>, kAgPairThreads, Config2<256, 7, false, AgPush::kSmemBytes>::kSmemBytes) : 0;
+    const int commPairs = (usePair && p > 1 && mode != HCOMM_FUSED_MODE_SPLIT) ? std::min(CommCtas() / 2, pairCap / 2) : 0;
+    const int gemmPairs = pairCap - commPairs;
+    if (usePair) BN = PickPairTileWidth(M / kPairM, N, gemmPairs);
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA, x, (uint64_t)Mshard, (uint64_t)K, (uint64_t)ldx, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2, c->CclBuffer(), (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
     CHK_RET(MakeTensorMap2dBf16(&hp.tmA2b, c->CclBuffer() + c->halfBytes, (uint64_t)M, (uint64_t)K, (uint64_t)K, kBlockM, kBlockK));
@@ -878,13 +1084,15 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
         hp.xLocal = nullptr;
     }
     if (usePair) {
-        c->fusedLastCtas = 2 * std::min(PairCapacityOf(AllGatherGemmPairKernel<256>, kAgPairThreads, Config2<256, 7, false, AgPush::kSmemBytes>::kSmemBytes), tiles);
+        // with communication pairs the grid is always full: the first `clusters` pairs share the tiles, the rest push
+        if (commPairs > 0) hp.shape.clusters = std::min(gemmPairs, tiles);
+        c->fusedLastCtas = commPairs > 0 ? 2 * (hp.shape.clusters + commPairs) : 2 * std::min(pairCap, tiles);
         switch (BN) {
-            case 256: return LaunchAgPair<256>(c, hp, tiles, stream);
-            case 224: return LaunchAgPair<224>(c, hp, tiles, stream);
-            case 192: return LaunchAgPair<192>(c, hp, tiles, stream);
-            case 160: return LaunchAgPair<160>(c, hp, tiles, stream);
-            default: return LaunchAgPair<128>(c, hp, tiles, stream);
+            case 256: return LaunchAgPair<256>(c, hp, tiles, stream, c->fusedLastCtas / 2);
+            case 224: return LaunchAgPair<224>(c, hp, tiles, stream, c->fusedLastCtas / 2);
+            case 192: return LaunchAgPair<192>(c, hp, tiles, stream, c->fusedLastCtas / 2);
+            case 160: return LaunchAgPair<160>(c, hp, tiles, stream, c->fusedLastCtas / 2);
+            default: return LaunchAgPair<128>(c, hp, tiles, stream, c->fusedLastCtas / 2);
         }
     }
     c->fusedLastCtas = 0;

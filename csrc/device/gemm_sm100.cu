@@ -3,6 +3,8 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <map>
+#include <vector>
 #include <mutex>
 
 #include "../core/log.h"
@@ -153,6 +155,136 @@ uint32_t *GemmErrorFlag()
     return flag[dev];
 }
 
+namespace {
+
+// One launch of the CTA-pair kernel with tile width bn and rasterisation group gm.
+HcclResult LaunchPairGemm(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, int bn, int gm, void *stream)
+{
+    CUtensorMap tmA, tmB;
+    CHK_RET(MakeTensorMap2dBf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, hcgemm::kBlockM, hcgemm::kBlockK));
+    CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)(bn / 2), hcgemm::kBlockK));
+    hcgemm::GemmShape shape;
+    shape.M = M; shape.N = N; shape.K = K;
+    shape.tilesM = M / hcgemm::kPairM;
+    shape.tilesN = N / bn;
+    shape.errFlag = GemmErrorFlag();
+    shape.phase = nullptr;
+    hcgemm::StoreBf16 epi{(__nv_bfloat16 *)C, ldc, M, N};
+    const int clusters = std::min(PairClusterCapacity(), shape.tilesM * shape.tilesN);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
+    cfg.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    static const bool stagedEpilogue = [] { const char *e = getenv("HCOMM_GEMM_STAGED"); return e && e[0] == '1'; }();
+    if (stagedEpilogue && ldc % 8 == 0 && bn == 256) {
+        cfg.dynamicSmemBytes = hcgemm::Config2<256, 6, true>::kSmemBytes;
+        hcgemm::StoreBf16Staged sepi{(__nv_bfloat16 *)C, ldc};
+        cudaError_t e2 = cudaLaunchKernelEx(&cfg, GemmBf16PairStagedKernel<256>, tmA, tmB, shape, sepi, gm);
+        if (e2 != cudaSuccess) { HCCL_ERROR("GemmBf16 (CTA pairs, staged epilogue) launch failed: %s", cudaGetErrorString(e2)); return HCCL_E_RUNTIME; }
+        return HCCL_SUCCESS;
+    }
+    cudaError_t e;
+    switch (bn) {
+        case 256: cfg.dynamicSmemBytes = hcgemm::Config2<256, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 7>, tmA, tmB, shape, epi, gm); break;
+        case 224: cfg.dynamicSmemBytes = hcgemm::Config2<224, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<224, 7>, tmA, tmB, shape, epi, gm); break;
+        case 192: cfg.dynamicSmemBytes = hcgemm::Config2<192, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<192, 7>, tmA, tmB, shape, epi, gm); break;
+        case 160: cfg.dynamicSmemBytes = hcgemm::Config2<160, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<160, 7>, tmA, tmB, shape, epi, gm); break;
+        default: cfg.dynamicSmemBytes = hcgemm::Config2<128, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<128, 7>, tmA, tmB, shape, epi, gm); break;
+    }
+    if (e != cudaSuccess) {
+        HCCL_ERROR("GemmBf16 (CTA pairs) launch failed: %s", cudaGetErrorString(e));
+        return HCCL_E_RUNTIME;
+    }
+    return HCCL_SUCCESS;
+}
+
+// Tile width and rasterisation group of the CTA-pair kernel for a shape.  The wave model (PickPairTileWidth) and the L2
+// budget (PairGroupRows) give the starting point; for a large shape seen for the first time the candidates around it
+// are timed once on the caller's stream - two interleaved rounds, so that a clock that drifts under the power cap
+// touches all of them alike - and the fastest is kept for the process.  Measured on B200 the model alone misses by up
+// to 15 % (8192 x 28672 x 8192: 224-wide tiles beat 256-wide ones although both need the same number of tile columns
+// per wave).  Not done while the stream is being captured into a graph, nor when a width or group is forced.
+struct ShapeKey {
+    int M, N, K;
+    bool operator<(const ShapeKey &o) const { return M != o.M ? M < o.M : (N != o.N ? N < o.N : K < o.K); }
+};
+std::mutex g_tuneMu;
+std::map<ShapeKey, std::pair<int, int>> g_tuned;
+
+bool AutotuneEnabled()
+{
+    static const bool on = [] { const char *e = getenv("HCOMM_GEMM_AUTOTUNE"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
+void PairChoice(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream, int *bnOut, int *gmOut)
+{
+    const int pairs = PairClusterCapacity();
+    const int bn0 = PickPairTileWidth(M / hcgemm::kPairM, N, pairs), gm0 = PairGroupRows(K);
+    *bnOut = bn0; *gmOut = gm0;
+    const bool forced = ForcedPairTileWidth() > 0 || g_forceGm.load() > 0;
+    const double flops = 2.0 * M * N * K;
+    if (forced || !AutotuneEnabled() || flops < 2e11) return;
+    const ShapeKey key{M, N, K};
+    {
+        std::lock_guard<std::mutex> lk(g_tuneMu);
+        auto it = g_tuned.find(key);
+        if (it != g_tuned.end()) { *bnOut = it->second.first; *gmOut = it->second.second; return; }
+    }
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing((cudaStream_t)stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return; }
+    // candidates: widths whose whole-wave cost is within 15 % of the best, each with the group halved, kept and doubled
+    struct Cand { int bn, gm; float best; };
+    std::vector<Cand> cands;
+    const int rowBlocks = M / hcgemm::kPairM;
+    long bestCost = 0;
+    for (int bn = 256; bn >= 128; bn -= 32) {
+        if (N % bn) continue;
+        const long tiles = (long)rowBlocks * (N / bn), cost = (tiles + pairs - 1) / pairs * bn;
+        if (!bestCost || cost < bestCost) bestCost = cost;
+    }
+    for (int bn = 256; bn >= 128; bn -= 32) {
+        if (N % bn) continue;
+        const long tiles = (long)rowBlocks * (N / bn), cost = (tiles + pairs - 1) / pairs * bn;
+        if (cost * 100 > bestCost * 115) continue;
+        for (int gm : {gm0 / 2, gm0, gm0 * 2})
+            if (gm >= 2 && gm <= 32) cands.push_back({bn, gm, 1e30f});
+    }
+    if (cands.size() < 2) return;
+    cudaEvent_t ev[2];
+    if (cudaEventCreate(&ev[0]) != cudaSuccess || cudaEventCreate(&ev[1]) != cudaSuccess) { cudaGetLastError(); return; }
+    bool ok = true;
+    for (int round = 0; round < 3 && ok; ++round) {           // round 0 warms every variant up (module load, L2), rounds 1 and 2 count
+        for (auto &cd : cands) {
+            cudaEventRecord(ev[0], (cudaStream_t)stream);
+            if (LaunchPairGemm(A, B, C, M, N, K, lda, ldb, ldc, cd.bn, cd.gm, stream) != HCCL_SUCCESS) { ok = false; break; }
+            cudaEventRecord(ev[1], (cudaStream_t)stream);
+            if (cudaEventSynchronize(ev[1]) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+            float ms = 0;
+            cudaEventElapsedTime(&ms, ev[0], ev[1]);
+            if (round > 0 && ms < cd.best) cd.best = ms;
+        }
+    }
+    cudaEventDestroy(ev[0]);
+    cudaEventDestroy(ev[1]);
+    if (!ok) return;
+    const Cand *win = &cands[0];
+    for (auto &cd : cands)
+        if (cd.best < win->best) win = &cd;
+    HCCL_INFO("GEMM %d x %d x %d: tile width %d, group %d chosen by measurement (%.3f ms; model said %d / %d)", M, N, K, win->bn, win->gm, win->best, bn0, gm0);
+    {
+        std::lock_guard<std::mutex> lk(g_tuneMu);
+        g_tuned[key] = {win->bn, win->gm};
+    }
+    *bnOut = win->bn; *gmOut = win->gm;
+}
+
+}  // namespace
+
 HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream)
 {
     if (M <= 0 || N <= 0 || K <= 0) return HCCL_SUCCESS;
@@ -162,48 +294,9 @@ HcclResult GemmBf16(const void *A, const void *B, void *C, int M, int N, int K, 
     }
     static const bool pairEnabled = [] { const char *e = getenv("HCOMM_GEMM_PAIR"); return !(e && e[0] == '0'); }();
     if (pairEnabled && M % hcgemm::kPairM == 0 && N % 128 == 0 && PairClusterCapacity() > 0) {
-        const int bn = PickPairTileWidth(M / hcgemm::kPairM, N, PairClusterCapacity());
-        CUtensorMap tmA, tmB;
-        CHK_RET(MakeTensorMap2dBf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, hcgemm::kBlockM, hcgemm::kBlockK));
-        CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)(bn / 2), hcgemm::kBlockK));
-        hcgemm::GemmShape shape;
-        shape.M = M; shape.N = N; shape.K = K;
-        shape.tilesM = M / hcgemm::kPairM;
-        shape.tilesN = N / bn;
-        shape.errFlag = GemmErrorFlag();
-        shape.phase = nullptr;
-        hcgemm::StoreBf16 epi{(__nv_bfloat16 *)C, ldc, M, N};
-        const int clusters = std::min(PairClusterCapacity(), shape.tilesM * shape.tilesN);
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * clusters, 1, 1);
-        cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
-        const int gm = PairGroupRows(K);
-        cfg.stream = (cudaStream_t)stream;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-        cfg.attrs = at; cfg.numAttrs = 1;
-        static const bool stagedEpilogue = [] { const char *e = getenv("HCOMM_GEMM_STAGED"); return e && e[0] == '1'; }();
-        if (stagedEpilogue && ldc % 8 == 0 && bn == 256) {
-            cfg.dynamicSmemBytes = hcgemm::Config2<256, 6, true>::kSmemBytes;
-            hcgemm::StoreBf16Staged sepi{(__nv_bfloat16 *)C, ldc};
-            cudaError_t e2 = cudaLaunchKernelEx(&cfg, GemmBf16PairStagedKernel<256>, tmA, tmB, shape, sepi, gm);
-            if (e2 != cudaSuccess) { HCCL_ERROR("GemmBf16 (CTA pairs, staged epilogue) launch failed: %s", cudaGetErrorString(e2)); return HCCL_E_RUNTIME; }
-            return HCCL_SUCCESS;
-        }
-        cudaError_t e;
-        switch (bn) {
-            case 256: cfg.dynamicSmemBytes = hcgemm::Config2<256, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 7>, tmA, tmB, shape, epi, gm); break;
-            case 224: cfg.dynamicSmemBytes = hcgemm::Config2<224, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<224, 7>, tmA, tmB, shape, epi, gm); break;
-            case 192: cfg.dynamicSmemBytes = hcgemm::Config2<192, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<192, 7>, tmA, tmB, shape, epi, gm); break;
-            case 160: cfg.dynamicSmemBytes = hcgemm::Config2<160, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<160, 7>, tmA, tmB, shape, epi, gm); break;
-            default: cfg.dynamicSmemBytes = hcgemm::Config2<128, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<128, 7>, tmA, tmB, shape, epi, gm); break;
-        }
-        if (e != cudaSuccess) {
-            HCCL_ERROR("GemmBf16 (CTA pairs) launch failed: %s", cudaGetErrorString(e));
-            return HCCL_E_RUNTIME;
-        }
-        return HCCL_SUCCESS;
+        int bn = 0, gm = 0;
+        PairChoice(A, B, C, M, N, K, lda, ldb, ldc, stream, &bn, &gm);
+        return LaunchPairGemm(A, B, C, M, N, K, lda, ldb, ldc, bn, gm, stream);
     }
     const int BN = (N % 256 == 0 || N >= 2048) ? 256 : 128;
     CUtensorMap tmA, tmB;

@@ -46,6 +46,7 @@ struct GemmShape {
     int tilesM, tilesN;
     uint32_t *errFlag;       // device word, set to non-zero when a wait expired
     uint64_t *phase;         // optional phase clocks, kPhaseSlots words per CTA (nanoseconds of the GPU's global timer); NULL = off
+    int clusters = 0;        // CTA-pair main loop: pairs that share the tiles (the first `clusters` of the grid); 0 = all of them
 };
 
 // Phase clocks of one CTA.  Start / End are time stamps, the others are sums of waiting or working time.

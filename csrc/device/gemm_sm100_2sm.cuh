@@ -175,7 +175,7 @@ __device__ __forceinline__ void GemmMainLoopPair(const CUtensorMap *tmA, const C
     const bool leader = ctaRank == 0;
     const int numTiles = g.tilesM * g.tilesN;
     const int kBlocks = (g.K + kBlockK - 1) / kBlockK;
-    const int firstTile = (int)ClusterId(), tileStep = (int)NumClusters();
+    const int firstTile = (int)ClusterId(), tileStep = g.clusters > 0 ? g.clusters : (int)NumClusters();
 
     if (threadIdx.x == 0) {
         if (g.phase) g.phase[(size_t)blockIdx.x * kPhaseSlots + kPhaseStart] = GlobalTimer();
