@@ -945,7 +945,9 @@ int PickPairTileWidth(int rowBlocks, int N, int pairs)
         if (N % bn) continue;
         const long tiles = (long)rowBlocks * (N / bn);
         const long waves = (tiles + pairs - 1) / pairs;
-        const long cost = waves * bn + (bn < 256 ? 4 : 0);      // a narrower tile must win by more than a tie
+        // ties: 224 columns before 256 (measured equal or faster on every shape that both divide: 3584, 7168, 14336 and
+        // 28672 columns at K = 8192), anything narrower must win by more than a tie
+        const long cost = waves * bn * 8 + (bn == 224 ? 0 : (bn == 256 ? 1 : 32));
         if (!best || cost < bestCost) { best = bn; bestCost = cost; }
     }
     return best;
@@ -959,6 +961,8 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
         RPT_ERR("EI0003", "GEMM+ReduceScatter needs M divisible by %d, N by 128, K by 8 (M=%d N=%d K=%d)", p * kBlockM, M, N, K);
         return HCCL_E_PARA;
     }
+    // a single rank has nobody to exchange with: the plain GEMM (its tile shape tuned per problem) is the whole operator
+    if (p == 1 && !c->emuSameDevice) return GemmBf16(A, B, out, M, N, K, lda, ldb, ldOut, stream);
     const int BN = N % 256 == 0 ? 256 : 128;
     const int rowsPer = M / p;
     mode = ResolveMode(mode);
@@ -1042,6 +1046,7 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
         RPT_ERR("EI0003", "AllGather+GEMM needs a contiguous shard with rows divisible by %d, N by 128, K by 8 (rows=%d N=%d K=%d)", kBlockM, Mshard, N, K);
         return HCCL_E_PARA;
     }
+    if (p == 1 && !c->emuSameDevice) return GemmBf16(x, W, out, Mshard, N, K, ldx, ldw, ldOut, stream);
     const int M = Mshard * p;
     if ((uint64_t)M * K * 2 > c->halfBytes) {
         RPT_ERR("EI0003", "AllGather+GEMM staging (%llu MB) exceeds one CCL half (%u MB); raise HCCL_BUFFSIZE", (unsigned long long)((uint64_t)M * K * 2 >> 20), c->cfg.bufferMB);

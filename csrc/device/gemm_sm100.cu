@@ -2,6 +2,7 @@
 // used by every kernel that loads tiles with TMA.
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <atomic>
 #include <map>
 #include <vector>
@@ -255,23 +256,35 @@ void PairChoice(const void *A, const void *B, void *C, int M, int N, int K, int 
             if (gm >= 2 && gm <= 32) cands.push_back({bn, gm, 1e30f});
     }
     if (cands.size() < 2) return;
+    // Five rounds over all candidates, two back-to-back launches each; the first round only warms up (module load, L2,
+    // clocks).  Odd rounds walk the list backwards so that a drift over a round does not favour one end of it, and a
+    // candidate's figure is the median of its four counted rounds, not its luckiest one.
     cudaEvent_t ev[2];
     if (cudaEventCreate(&ev[0]) != cudaSuccess || cudaEventCreate(&ev[1]) != cudaSuccess) { cudaGetLastError(); return; }
     bool ok = true;
-    for (int round = 0; round < 3 && ok; ++round) {           // round 0 warms every variant up (module load, L2), rounds 1 and 2 count
-        for (auto &cd : cands) {
+    const int nc = (int)cands.size();
+    std::vector<std::vector<float>> samples(nc);
+    for (int round = 0; round < 5 && ok; ++round) {
+        for (int i = 0; i < nc && ok; ++i) {
+            const int ci = (round & 1) ? nc - 1 - i : i;
+            const Cand &cd = cands[ci];
             cudaEventRecord(ev[0], (cudaStream_t)stream);
-            if (LaunchPairGemm(A, B, C, M, N, K, lda, ldb, ldc, cd.bn, cd.gm, stream) != HCCL_SUCCESS) { ok = false; break; }
+            for (int rep = 0; rep < 2 && ok; ++rep)
+                if (LaunchPairGemm(A, B, C, M, N, K, lda, ldb, ldc, cd.bn, cd.gm, stream) != HCCL_SUCCESS) ok = false;
             cudaEventRecord(ev[1], (cudaStream_t)stream);
-            if (cudaEventSynchronize(ev[1]) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
+            if (!ok || cudaEventSynchronize(ev[1]) != cudaSuccess) { cudaGetLastError(); ok = false; break; }
             float ms = 0;
             cudaEventElapsedTime(&ms, ev[0], ev[1]);
-            if (round > 0 && ms < cd.best) cd.best = ms;
+            if (round > 0) samples[ci].push_back(ms * 0.5f);
         }
     }
     cudaEventDestroy(ev[0]);
     cudaEventDestroy(ev[1]);
     if (!ok) return;
+    for (int i = 0; i < nc; ++i) {
+        std::sort(samples[i].begin(), samples[i].end());
+        cands[i].best = samples[i].empty() ? 1e30f : 0.5f * (samples[i][(samples[i].size() - 1) / 2] + samples[i][samples[i].size() / 2]);
+    }
     const Cand *win = &cands[0];
     for (auto &cd : cands)
         if (cd.best < win->best) win = &cd;
@@ -341,6 +354,14 @@ extern "C" void HcommGemmSetTuning(int groupRows, int tileWidth)
 {
     hc::g_forceGm.store(groupRows > 0 ? groupRows : 0);
     hc::g_forceBn.store(tileWidth > 0 ? tileWidth : 0);
+}
+// Tile width and rasterisation group the measurement at first use chose for a shape (0 / 0: none was made).
+extern "C" void HcommGemmGetTuned(int M, int N, int K, int *tileWidth, int *groupRows)
+{
+    std::lock_guard<std::mutex> lk(hc::g_tuneMu);
+    auto it = hc::g_tuned.find(hc::ShapeKey{M, N, K});
+    if (tileWidth) *tileWidth = it == hc::g_tuned.end() ? 0 : it->second.first;
+    if (groupRows) *groupRows = it == hc::g_tuned.end() ? 0 : it->second.second;
 }
 extern "C" int HcommGemmTakeError(void)
 {

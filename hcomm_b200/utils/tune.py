@@ -16,8 +16,8 @@ import os
 
 CANDIDATES = {
     "allreduce": [("mesh_oneshot", "sm"), ("mesh", "sm"), ("nvls", "nvls")],
-    "allgather": [("mesh", "sm")],
-    "reducescatter": [("mesh", "sm")],
+    "allgather": [("mesh", "sm"), ("nvls", "nvls")],
+    "reducescatter": [("mesh", "sm"), ("nvls", "nvls")],
     "alltoall": [("mesh", "sm")],
     "broadcast": [("mesh_oneshot", "sm"), ("mesh", "sm"), ("nvls", "nvls")],
 }
