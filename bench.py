@@ -378,6 +378,15 @@ def main():
         del h
         extra["cublas_ms_per_step"] = cublas_ms
         extra["speedup_vs_cublas"] = cublas_ms / ms_per_step
+        # what the library's measurement at first use kept for the two GEMM shapes (tile width, rasterisation group)
+        import ctypes
+        from hcomm_b200 import _lib
+        tuned = {}
+        for name, (m, n, k) in (("up", (TOKENS, INTER, HIDDEN)), ("down", (TOKENS, HIDDEN, INTER))):
+            bn, gm = ctypes.c_int(0), ctypes.c_int(0)
+            _lib.load().HcommGemmGetTuned(m, n, k, ctypes.byref(bn), ctypes.byref(gm))
+            tuned[name] = {"tile_width": bn.value, "group_rows": gm.value}
+        extra["gemm_tuning"] = tuned
     roof, basis, t_gemm, t_link = roofline_ms(world)
     extra["roofline_ms"] = roof
     extra["fraction_of_roofline"] = roof / ms_per_step

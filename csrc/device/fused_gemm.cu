@@ -91,6 +91,7 @@ struct FusedParams {
     uint32_t *sent;           // AG: device-local chunk counters [peer index][block]
     char *outbox;             // RS with communication CTAs: my partial product [M, N] bf16 in local memory
     uint32_t *ready;          // RS with communication CTAs: device-local flags, (tile, row group) is in the outbox
+    int orderGroup;           // row blocks per group of the tile order (see RsOrder / AgOrder), at least 1
     int pushWarps;            // AG, CTA-pair kernel: pushing warps per CTA that take part (1..6)
     int signaller;            // AG, CTA-pair kernel: a seventh warp publishes the chunks (1) or every pushing warp its own (0)
 };
@@ -102,11 +103,23 @@ __device__ __forceinline__ uint32_t *FusedFlag(const CommDev *d, int rank, int i
 
 // ------------------------------------------------------------------------ GEMM -> ReduceScatter
 
+// Walks `rows` x tilesN tiles in groups of `group` rows, column by column inside a group (the rows of a group share
+// B panels, the group's A panels stay in L2 while its columns pass): index -> (row, column).
+__device__ __forceinline__ void GroupedWalk(int index, int rows, int tilesN, int group, int *row, int *col)
+{
+    const int perGroup = group * tilesN, gi = index / perGroup, r = index - gi * perGroup;
+    const int here = rows - gi * group < group ? rows - gi * group : group;       // the last group may be shorter
+    *col = r / here;
+    *row = gi * group + r % here;
+}
+
 // Tile order of a rank: partial tiles for the other ranks first, cycling through the destinations so that the stores
 // of the tiles in flight spread over all NVLink destinations at once (a single destination takes a fraction of a GPU's
-// outgoing bandwidth), then the rank's own tiles.  Inside a destination: column by column, its row blocks share B panels.
+// outgoing bandwidth), then the rank's own tiles.  Inside a destination: row groups of `group` row blocks, column by
+// column; with p - 1 destinations in flight the A panels that are live at once are group x (p - 1), which the host sizes
+// for the L2 (a destination's 16 row blocks of K = 14336 at two ranks would not fit).
 struct RsOrder {
-    int rank, nRanks, mbPer;
+    int rank, nRanks, mbPer, group;
     __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
     {
         const int perDest = mbPer * g.tilesN;
@@ -119,8 +132,9 @@ struct RsOrder {
             q = rank;
             local = t - remote;
         }
-        *mb = q * mbPer + local % mbPer;
-        *nb = local / mbPer;
+        int row;
+        GroupedWalk(local, mbPer, g.tilesN, group, &row, nb);
+        *mb = q * mbPer + row;
     }
 };
 
@@ -450,7 +464,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) GemmReduceScatterKernel(cons
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
-    RsOrder order{d->rank, d->nRanks, p.mbPer};
+    RsOrder order{d->rank, d->nRanks, p.mbPer, p.orderGroup};
     RsEpilogue<BN, kBlockM> epi{d, (__nv_bfloat16 *)p.out, p.ldOut, p.shape.N, p.mbPer, p.rowsPer, p.shape.tilesN, ls.half, ls.seq, nullptr, nullptr, nullptr};
     GemmMainLoop<BN>(&p.tmA, &p.tmB, p.shape, order, NoGate(), epi);
     hcdev::KernelEnd(d, ls, 0);
@@ -463,7 +477,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) Ge
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
-    RsOrder order{d->rank, d->nRanks, p.mbPer};
+    RsOrder order{d->rank, d->nRanks, p.mbPer, p.orderGroup};
     if constexpr (MODE == kRsOutbox) {
         const int gemmCtas = p.shape.clusters > 0 ? 2 * p.shape.clusters : (int)gridDim.x;
         if ((int)blockIdx.x >= gemmCtas) {
@@ -501,23 +515,28 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) Ge
 
 // -------------------------------------------------------------------------- AllGather -> GEMM
 
-// Tile order of a rank: tiles of its own rows first, then the other ranks' rows one row block at a time across ALL
-// sources (block i of every source, then block i + 1, ...), which is the order in which the push delivers them.
+// Tile order of a rank: tiles of its own rows first, then the other ranks' rows, `group` row blocks of every source at a
+// time (blocks i .. i + group - 1 of every source, then the next group), which follows the order in which the push
+// delivers them (block-major).  Inside a group: column by column, so its (p - 1) x group A panels stay in L2 while the B
+// panels pass once per group; one row block per group (the arrival order exactly) re-reads all of B for every block.
 struct AgOrder {
-    int rank, nRanks, mbPer;
+    int rank, nRanks, mbPer, group;
     __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
     {
         const int perSrc = mbPer * g.tilesN;
         if (t < perSrc) {
-            *mb = rank * mbPer + t % mbPer;
-            *nb = t / mbPer;
+            int row;
+            GroupedWalk(t, mbPer, g.tilesN, group * (nRanks - 1) > 0 ? group * (nRanks - 1) : 1, &row, nb);
+            *mb = rank * mbPer + row;
             return;
         }
-        const int u = t - perSrc, perRow = (nRanks - 1) * g.tilesN;
-        const int i = u / perRow, rem = u % perRow;
-        const int src = (rank - 1 - rem % (nRanks - 1) + 2 * nRanks) % nRanks;
-        *mb = src * mbPer + i;
-        *nb = rem / (nRanks - 1);
+        const int u = t - perSrc, others = nRanks - 1;
+        const int perGroup = group * others * g.tilesN, gi = u / perGroup, r = u - gi * perGroup;
+        const int here = (mbPer - gi * group < group ? mbPer - gi * group : group) * others;     // rows of this group over all sources
+        const int w = r % here;
+        const int src = (rank - 1 - w % others + 2 * nRanks) % nRanks;
+        *nb = r / here;
+        *mb = src * mbPer + gi * group + w / others;
     }
 };
 
@@ -703,7 +722,7 @@ __global__ void __launch_bounds__(kAgThreads, 1) AllGatherGemmKernel(const __gri
     const FusedParams &p = table ? table[blockIdx.y] : own;
     const CommDev *d = p.dev;
     const hcdev::LaunchState ls = hcdev::KernelBegin(d);
-    AgOrder order{d->rank, d->nRanks, p.mbPer};
+    AgOrder order{d->rank, d->nRanks, p.mbPer, p.orderGroup};
     AgGate gate{d, p.mbPer, ls.seq, nullptr};
     AgPush push{d, (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, nullptr, p.pushWarps, p.signaller};
     StoreBf16 epi{(__nv_bfloat16 *)p.out, p.ldOut, p.shape.M, p.shape.N};
@@ -745,7 +764,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kAgPairThreads, 1) A
         hcdev::KernelEnd(d, ls, 0);
         return;
     }
-    AgOrder order{d->rank, d->nRanks, p.mbPer / 2};
+    AgOrder order{d->rank, d->nRanks, p.mbPer / 2, p.orderGroup};
     AgGate gate{d, p.mbPer, ls.seq, PhaseOfCta(p.shape)};
     // with communication CTAs the extra warps of the GEMM CTAs have nothing to push
     AgPush push{d, gemmCtas < (int)gridDim.x ? nullptr : (const char *)p.xLocal, p.mbPer, p.K, ls.half, ls.seq, p.sent, PhaseOfCta(p.shape), p.pushWarps, p.signaller};
@@ -842,12 +861,17 @@ bool PairKernelsEnabled()
     return on;
 }
 
-// The signaller warps are on unless HCOMM_FUSED_SIGNALLER=0 (then every warp that moves data fences and publishes its own).
-bool SignallerEnabled()
+// Signaller warps (HCOMM_FUSED_SIGNALLER=1 / 0 forces both on / off).  Measured on 8 GPUs at the benchmark shapes: the
+// reduce-scatter kernel gains from it (456 us against 465 us, and its epilogue then waits for accumulators instead of
+// for fences), the all-gather kernel loses (532 us against 499 us: pushing warps that never fence finish their share
+// earlier but disturb the operand loads of the GEMM more while they do), so by default only the reduce-scatter has one.
+int SignallerSetting()
 {
-    static const bool on = [] { const char *e = getenv("HCOMM_FUSED_SIGNALLER"); return !(e && e[0] == '0'); }();
-    return on;
+    static const int v = [] { const char *e = getenv("HCOMM_FUSED_SIGNALLER"); return e ? (e[0] == '0' ? 0 : 1) : -1; }();
+    return v;
 }
+bool RsSignallerEnabled() { return SignallerSetting() != 0; }
+bool AgSignallerEnabled() { return SignallerSetting() == 1; }
 // CTAs of the all-gather CTA-pair kernel set aside for communication (HCOMM_FUSED_COMM_CTAS, even; 0 = the extra warps
 // of every CTA push).
 int CommCtas()
@@ -970,7 +994,7 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     constexpr int pairSmem = Config2<256, 6, true, RsSignaller::kSmemBytes>::kSmemBytes;      // enough for every form
     // communication CTAs (the outbox form) need the whole partial product in local memory and a ready flag per tile
     const int commWanted = (p > 1 && mode != HCOMM_FUSED_MODE_SPLIT && (M / kPairM) * (N / 256) <= kRsMaxLocalTiles) ? RsCommCtas() : 0;
-    auto pairKernel = commWanted > 0 ? GemmReduceScatterPairKernel<kRsOutbox> : (SignallerEnabled() ? GemmReduceScatterPairKernel<kRsSignalled> : GemmReduceScatterPairKernel<kRsDirect>);
+    auto pairKernel = commWanted > 0 ? GemmReduceScatterPairKernel<kRsOutbox> : (RsSignallerEnabled() ? GemmReduceScatterPairKernel<kRsSignalled> : GemmReduceScatterPairKernel<kRsDirect>);
     const bool usePair = PairKernelsEnabled() && !emu && rowsPer % kPairM == 0 && N % 256 == 0 && PairCapacityOf(pairKernel, kFusedThreads, pairSmem) > 0;
     const int blockRows = usePair ? kPairM : kBlockM;
     const bool fits = (uint64_t)p * rowsPer * N * 2 <= c->halfBytes && (uint64_t)p * (rowsPer / blockRows) * (N / BN) <= (uint64_t)kRsMaxSrcTiles;
@@ -1006,6 +1030,8 @@ HcclResult FusedGemmReduceScatter(Comm *c, const void *A, const void *B, void *o
     hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / blockRows; hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
     hp.shape.phase = usePair ? PhaseBuffer(c, stream) : nullptr;
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = rowsPer / blockRows; hp.rowsPer = rowsPer; hp.K = K;
+    // A panels live at once: (p - 1) destinations x orderGroup row blocks, sized like the plain GEMM's raster group
+    hp.orderGroup = std::min(hp.mbPer, std::max(1, PairGroupRows(K) * (kPairM / blockRows) / std::max(1, p - 1)));
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     int pairsWanted = 0;
     if (usePair && commWanted > 0) {
@@ -1076,10 +1102,14 @@ HcclResult FusedAllGatherGemm(Comm *c, const void *x, const void *W, void *out, 
     hp.shape.M = M; hp.shape.N = N; hp.shape.K = K; hp.shape.tilesM = M / (usePair ? kPairM : kBlockM); hp.shape.tilesN = N / BN; hp.shape.errFlag = GemmErrorFlag();
     hp.shape.phase = usePair ? PhaseBuffer(c, stream) : nullptr;
     hp.dev = c->devStruct; hp.out = out; hp.ldOut = ldOut; hp.mbPer = Mshard / kBlockM; hp.rowsPer = Mshard; hp.K = K; hp.xLocal = x;
+    {
+        const int blocksPerSrc = usePair ? Mshard / kPairM : Mshard / kBlockM;
+        hp.orderGroup = std::min(blocksPerSrc, std::max(1, PairGroupRows(K) * (usePair ? 1 : 2) / std::max(1, p - 1)));
+    }
     char *local = FusedLocal(c);
     if (!local) return HCCL_E_MEMORY;
     hp.sent = (uint32_t *)local;
-    hp.pushWarps = PushWarps(); hp.signaller = SignallerEnabled() ? 1 : 0;
+    hp.pushWarps = PushWarps(); hp.signaller = AgSignallerEnabled() ? 1 : 0;
     ++c->opSeq;
     const int tiles = hp.shape.tilesM * hp.shape.tilesN;
     if (mode == HCOMM_FUSED_MODE_SPLIT && !emu && p > 1) {

@@ -115,9 +115,12 @@ int PairGroupRows(int K)
         g_forceGm.store(forced);
     }
     if (forced > 0) return forced;
+    // Never below 8: a wave of 74 tiles laid out as r rows x c columns loads r + c panels, least at r = c = 8.6, and DRAM
+    // counters on B200 confirm it for deep K too, where the group's A panels exceed the L2 anyway (8192 x 8192 x 28672:
+    // 6.5 GB read at 8 or 16 row blocks per group, 8.8 GB at 4, 9.7 GB at 2; ideal 0.9 GB).
     const double panelMB = 256.0 * K * 2 / (1 << 20);
     int gm = 16;
-    while (gm > 4 && gm * panelMB > 40.0) gm /= 2;
+    while (gm > 8 && gm * panelMB > 40.0) gm /= 2;
     return gm;
 }
 int ForcedPairTileWidth()
@@ -203,12 +206,14 @@ HcclResult LaunchPairGemm(const void *A, const void *B, void *C, int M, int N, i
     return HCCL_SUCCESS;
 }
 
-// Tile width and rasterisation group of the CTA-pair kernel for a shape.  The wave model (PickPairTileWidth) and the L2
-// budget (PairGroupRows) give the starting point; for a large shape seen for the first time the candidates around it
-// are timed once on the caller's stream - two interleaved rounds, so that a clock that drifts under the power cap
-// touches all of them alike - and the fastest is kept for the process.  Measured on B200 the model alone misses by up
-// to 15 % (8192 x 28672 x 8192: 224-wide tiles beat 256-wide ones although both need the same number of tile columns
-// per wave).  Not done while the stream is being captured into a graph, nor when a width or group is forced.
+// Tile width and rasterisation group of the CTA-pair kernel for a shape.  The wave model (PickPairTileWidth) and the
+// group rule (PairGroupRows) decide.  With HCOMM_GEMM_AUTOTUNE=1 a large shape seen for the first time is also timed
+// once with the candidates around that choice on the caller's stream - interleaved rounds, medians - and the fastest
+// is kept for the process.  It is off by default: on a GPU at its power cap the variants differ mostly through the
+// clock they leave the chip at (the cycle counts of the 256- and 224-wide variants are within 1 % for every group size;
+// the DRAM traffic, 4 to 10 GB for the benchmark's projections, sets the power), and timings of a few launches each
+// were not stable enough to rank them - repeated runs of one process kept different winners.
+// Never done while the stream is being captured into a graph, nor when a width or group is forced.
 struct ShapeKey {
     int M, N, K;
     bool operator<(const ShapeKey &o) const { return M != o.M ? M < o.M : (N != o.N ? N < o.N : K < o.K); }
@@ -218,7 +223,7 @@ std::map<ShapeKey, std::pair<int, int>> g_tuned;
 
 bool AutotuneEnabled()
 {
-    static const bool on = [] { const char *e = getenv("HCOMM_GEMM_AUTOTUNE"); return !(e && e[0] == '0'); }();
+    static const bool on = [] { const char *e = getenv("HCOMM_GEMM_AUTOTUNE"); return e && e[0] == '1'; }();
     return on;
 }
 

@@ -4,8 +4,9 @@
 
 C[M, N] = A[M, K] * B[N, K]^T.  The two implementations take turns (``rounds`` rounds of ``iters`` back-to-back calls
 each, CUDA events around every round), so a clock that drifts under the power cap touches both alike; the figure per
-implementation is the median of its rounds.  Before the first round one untimed call lets the library measure and pick its
-tile width and rasterisation group for the shape; the choice is printed.  Operands of the default shapes exceed the L2.
+implementation is the median of its rounds.  With HCOMM_GEMM_AUTOTUNE=1 the first, untimed call lets the library measure
+and pick its tile width and rasterisation group for the shape and the choice is printed (0 / 0 otherwise: the model
+decided).  Operands of the default shapes exceed the L2.
 """
 from __future__ import annotations
 

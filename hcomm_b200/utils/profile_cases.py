@@ -1,6 +1,8 @@
 """Small, self-terminating workloads for kernel profilers (one GPU, one process).
 
     python -m hcomm_b200.utils.profile_cases gemm            tcgen05 GEMM 8192^3 bf16 (operands larger than L2)
+    python -m hcomm_b200.utils.profile_cases gemm_up         the benchmark's up projection 8192 x 28672 x 8192: this library's GEMM twice, then cuBLAS twice
+    python -m hcomm_b200.utils.profile_cases gemm_raster      both benchmark projections once per (tile width, rasterisation group) pair, for counter sweeps
     python -m hcomm_b200.utils.profile_cases fused           GEMM->ReduceScatter and AllGather->GEMM, two ranks sharing the GPU
     python -m hcomm_b200.utils.profile_cases allreduce       one-shot, two-shot all-reduce and all-gather kernels, two ranks sharing the GPU
     python -m hcomm_b200.utils.profile_cases fused_pair      the CTA-pair variants of the two fused kernels on a one-rank communicator
@@ -44,6 +46,40 @@ def case_gemm(reps=3):
     for _ in range(reps):
         gemm_bf16(a, w, out)
     torch.cuda.synchronize()
+    assert take_kernel_error() == 0
+
+
+def case_gemm_up(reps=2):
+    """1.1 GB of operands and result.  The tile width and group come from HCOMM_GEMM_BN / HCOMM_GEMM_GM or the model."""
+    from ..ops.gemm import gemm_bf16, take_kernel_error
+    a = torch.randn(8192, 8192, device="cuda").to(torch.bfloat16)
+    w = (torch.randn(28672, 8192, device="cuda") * 0.02).to(torch.bfloat16)
+    out = torch.empty(8192, 28672, device="cuda", dtype=torch.bfloat16)
+    for _ in range(reps):
+        gemm_bf16(a, w, out)
+    for _ in range(reps):
+        torch.matmul(a, w.t(), out=out)
+    torch.cuda.synchronize()
+    assert take_kernel_error() == 0
+
+
+def case_gemm_raster():
+    """One launch per (shape, tile width, group): 2 shapes x 2 widths x 5 groups = 20 launches of the CTA-pair kernel, in the
+    order of the loops below, so that a profiler's per-launch counters (DRAM bytes, cycles) can be read as a table."""
+    from .. import _lib
+    from ..ops.gemm import gemm_bf16, take_kernel_error
+    lib = _lib.load()
+    for (m, n, k) in ((8192, 28672, 8192), (8192, 8192, 28672)):
+        a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+        w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
+        out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
+        for bn in (256, 224) if n % 224 == 0 else (256, 128):
+            for gm in (2, 4, 8, 16, 32):
+                lib.HcommGemmSetTuning(gm, bn)
+                gemm_bf16(a, w, out)
+        torch.cuda.synchronize()
+        del a, w, out
+    lib.HcommGemmSetTuning(0, 0)
     assert take_kernel_error() == 0
 
 
@@ -133,7 +169,7 @@ def case_moe(reps=2):
 def main():
     torch.cuda.set_device(0)
     which = sys.argv[1] if len(sys.argv) > 1 else "gemm"
-    {"gemm": case_gemm, "fused": case_fused, "fused_pair": case_fused_pair, "allreduce": case_allreduce, "moe": case_moe}[which]()
+    {"gemm": case_gemm, "gemm_up": case_gemm_up, "gemm_raster": case_gemm_raster, "fused": case_fused, "fused_pair": case_fused_pair, "allreduce": case_allreduce, "moe": case_moe}[which]()
     print(f"profile case {which}: done", flush=True)
 
 

@@ -27,8 +27,8 @@ extern "C" {
 int HcommGemmBf16(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream);
 /* Tuning overrides of the CTA-pair GEMM kernels (0 = automatic): rasterisation group in 256-row blocks, tile width (128..256, multiple of 32). */
 void HcommGemmSetTuning(int groupRows, int tileWidth);
-/* Large shapes (2 * M * N * K >= 2e11) seen for the first time are timed once with the candidate tile widths and groups
- * on the caller's stream (not while it is being captured; HCOMM_GEMM_AUTOTUNE=0 turns this off) and the fastest is kept.
+/* With HCOMM_GEMM_AUTOTUNE=1, large shapes (2 * M * N * K >= 2e11) seen for the first time are timed once with the candidate
+ * tile widths and groups on the caller's stream (not while it is being captured) and the fastest is kept for the process.
  * Returns what was chosen for a shape, 0 / 0 if nothing was measured. */
 void HcommGemmGetTuned(int M, int N, int K, int *tileWidth, int *groupRows);
 /* Reads and clears the "a bounded wait expired inside a GEMM kernel" flag of the current device (0 = none). */

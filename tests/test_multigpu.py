@@ -46,6 +46,18 @@ def test_fused_kernels_at_the_benchmark_shapes(world):
     assert codes == [0] * world, "\n".join(outs)
 
 
+@pytest.mark.parametrize("form", ["communication_ctas", "no_signaller", "signaller_everywhere"])
+def test_fused_kernels_in_their_other_forms(form):
+    # the same shapes with CTAs set aside for communication (all-gather pushers; reduce-scatter outbox and forwarders),
+    # with every data-moving warp publishing its own tiles, and with a signaller warp in both kernels
+    if cuda_device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    extra = {"communication_ctas": {"HCOMM_FUSED_COMM_CTAS": "16", "HCOMM_FUSED_RS_COMM_CTAS": "16"}, "no_signaller": {"HCOMM_FUSED_SIGNALLER": "0"},
+             "signaller_everywhere": {"HCOMM_FUSED_SIGNALLER": "1"}}[form]
+    codes, outs = launch("fused_bench_shapes", 2, {"HCOMM_TEST_BUFFER_MB": "512", "HCCL_EXEC_TIMEOUT": "30", **extra}, timeout=300)
+    assert codes == [0, 0], "\n".join(outs)
+
+
 @pytest.mark.parametrize("scenario", ["torch_ops", "torch_ddp"])
 def test_torch_backend_across_gpus(scenario):
     if cuda_device_count() < 2:
