@@ -12,6 +12,7 @@
 #include "gemm_api.h"
 #include "gemm_sm100.cuh"
 #include "gemm_sm100_2sm.cuh"
+#include "gemm_sm100_2sm_wide.cuh"
 
 namespace hc {
 
@@ -42,6 +43,13 @@ GemmBf16PairKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     hcgemm::GemmMainLoopPair<BN, STAGES>(&tmA, &tmB, shape, hcgemm::GroupedOrder{shape.tilesM < gm ? shape.tilesM : gm}, epi);
 }
 
+// 256 x 512 tiles, one accumulator per CTA (see gemm_sm100_2sm_wide.cuh).
+__global__ void __launch_bounds__(hcgemm::kWideThreads, 1)
+GemmBf16PairWideKernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const __grid_constant__ CUtensorMap tmC, hcgemm::GemmShape shape, int gm)
+{
+    hcgemm::GemmMainLoopPairWide<4>(&tmA, &tmB, &tmC, shape, hcgemm::GroupedOrder{shape.tilesM < gm ? shape.tilesM : gm});
+}
+
 // Clusters of two CTAs that can be resident at once (0 when the query fails).
 int PairClusterCapacity()
 {
@@ -53,6 +61,7 @@ int PairClusterCapacity()
     cudaFuncSetAttribute(GemmBf16PairKernel<160, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<160, 7>::kSmemBytes);
     cudaFuncSetAttribute(GemmBf16PairKernel<128, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<128, 7>::kSmemBytes);
     cudaFuncSetAttribute(GemmBf16PairStagedKernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::Config2<256, 6, true>::kSmemBytes);
+    cudaFuncSetAttribute(GemmBf16PairWideKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, hcgemm::ConfigWide<4>::kSmemBytes);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148, 1, 1);
     cfg.blockDim = dim3(hcgemm::kThreads, 1, 1);
@@ -166,7 +175,7 @@ HcclResult LaunchPairGemm(const void *A, const void *B, void *C, int M, int N, i
 {
     CUtensorMap tmA, tmB;
     CHK_RET(MakeTensorMap2dBf16(&tmA, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, hcgemm::kBlockM, hcgemm::kBlockK));
-    CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, (uint32_t)(bn / 2), hcgemm::kBlockK));
+    CHK_RET(MakeTensorMap2dBf16(&tmB, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, bn == hcgemm::kWideN ? 128u : (uint32_t)(bn / 2), hcgemm::kBlockK));
     hcgemm::GemmShape shape;
     shape.M = M; shape.N = N; shape.K = K;
     shape.tilesM = M / hcgemm::kPairM;
@@ -193,6 +202,14 @@ HcclResult LaunchPairGemm(const void *A, const void *B, void *C, int M, int N, i
     }
     cudaError_t e;
     switch (bn) {
+        case hcgemm::kWideN: {
+            CUtensorMap tmC;            // result tiles leave through TMA stores: boxes of 32 rows x 64 columns
+            CHK_RET(MakeTensorMap2dBf16(&tmC, C, (uint64_t)M, (uint64_t)N, (uint64_t)ldc, 32, 64));
+            cfg.dynamicSmemBytes = hcgemm::ConfigWide<4>::kSmemBytes;
+            cfg.blockDim = dim3(hcgemm::kWideThreads, 1, 1);
+            e = cudaLaunchKernelEx(&cfg, GemmBf16PairWideKernel, tmA, tmB, tmC, shape, gm);
+            break;
+        }
         case 256: cfg.dynamicSmemBytes = hcgemm::Config2<256, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<256, 7>, tmA, tmB, shape, epi, gm); break;
         case 224: cfg.dynamicSmemBytes = hcgemm::Config2<224, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<224, 7>, tmA, tmB, shape, epi, gm); break;
         case 192: cfg.dynamicSmemBytes = hcgemm::Config2<192, 7>::kSmemBytes; e = cudaLaunchKernelEx(&cfg, GemmBf16PairKernel<192, 7>, tmA, tmB, shape, epi, gm); break;
@@ -221,6 +238,13 @@ struct ShapeKey {
 std::mutex g_tuneMu;
 std::map<ShapeKey, std::pair<int, int>> g_tuned;
 
+// HCOMM_GEMM_WIDE=0 keeps the tiles at 256 columns or fewer.
+bool WideTilesEnabled()
+{
+    static const bool on = [] { const char *e = getenv("HCOMM_GEMM_WIDE"); return !(e && e[0] == '0'); }();
+    return on;
+}
+
 bool AutotuneEnabled()
 {
     static const bool on = [] { const char *e = getenv("HCOMM_GEMM_AUTOTUNE"); return e && e[0] == '1'; }();
@@ -230,7 +254,20 @@ bool AutotuneEnabled()
 void PairChoice(const void *A, const void *B, void *C, int M, int N, int K, int lda, int ldb, int ldc, void *stream, int *bnOut, int *gmOut)
 {
     const int pairs = PairClusterCapacity();
-    const int bn0 = PickPairTileWidth(M / hcgemm::kPairM, N, pairs), gm0 = PairGroupRows(K);
+    int bn0 = PickPairTileWidth(M / hcgemm::kPairM, N, pairs), gm0 = PairGroupRows(K);
+    // 256 x 512 tiles (a quarter less operand traffic, one accumulator) when N allows and whole waves of them cost at most
+    // 5 % more columns than the best narrower width; a wave of 74 such tiles loads the fewest panels at 12 rows x 6 columns
+    if (N % hcgemm::kWideN == 0 && WideTilesEnabled()) {
+        const long rowBlocks = M / hcgemm::kPairM;
+        const long wide = (rowBlocks * (N / hcgemm::kWideN) + pairs - 1) / pairs * hcgemm::kWideN;
+        const long narrow = (rowBlocks * (N / bn0) + pairs - 1) / pairs * bn0;
+        const int forcedBn = ForcedPairTileWidth();
+        if (forcedBn == hcgemm::kWideN || (forcedBn == 0 && wide * 100 <= narrow * 105)) {
+            *bnOut = hcgemm::kWideN;
+            *gmOut = g_forceGm.load() > 0 ? g_forceGm.load() : (gm0 >= 16 ? 16 : 12);
+            return;
+        }
+    }
     *bnOut = bn0; *gmOut = gm0;
     const bool forced = ForcedPairTileWidth() > 0 || g_forceGm.load() > 0;
     const double flops = 2.0 * M * N * K;

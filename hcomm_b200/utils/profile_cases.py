@@ -2,7 +2,7 @@
 
     python -m hcomm_b200.utils.profile_cases gemm            tcgen05 GEMM 8192^3 bf16 (operands larger than L2)
     python -m hcomm_b200.utils.profile_cases gemm_up         the benchmark's up projection 8192 x 28672 x 8192: this library's GEMM twice, then cuBLAS twice
-    python -m hcomm_b200.utils.profile_cases gemm_raster      both benchmark projections once per (tile width, rasterisation group) pair, for counter sweeps
+    python -m hcomm_b200.utils.profile_cases gemm_raster      both benchmark projections once per (tile width 512 / 256, rasterisation group) pair, for counter sweeps
     python -m hcomm_b200.utils.profile_cases fused           GEMM->ReduceScatter and AllGather->GEMM, two ranks sharing the GPU
     python -m hcomm_b200.utils.profile_cases allreduce       one-shot, two-shot all-reduce and all-gather kernels, two ranks sharing the GPU
     python -m hcomm_b200.utils.profile_cases fused_pair      the CTA-pair variants of the two fused kernels on a one-rank communicator
@@ -63,8 +63,11 @@ def case_gemm_up(reps=2):
     assert take_kernel_error() == 0
 
 
+GEMM_RASTER_WIDTHS, GEMM_RASTER_GROUPS = (512, 256), (4, 6, 8, 12, 16, 24)
+
+
 def case_gemm_raster():
-    """One launch per (shape, tile width, group): 2 shapes x 2 widths x 5 groups = 20 launches of the CTA-pair kernel, in the
+    """One launch per (shape, tile width, group): 2 shapes x 2 widths x 6 groups = 24 launches of the CTA-pair kernels, in the
     order of the loops below, so that a profiler's per-launch counters (DRAM bytes, cycles) can be read as a table."""
     from .. import _lib
     from ..ops.gemm import gemm_bf16, take_kernel_error
@@ -73,8 +76,8 @@ def case_gemm_raster():
         a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
         w = (torch.randn(n, k, device="cuda") * 0.02).to(torch.bfloat16)
         out = torch.empty(m, n, device="cuda", dtype=torch.bfloat16)
-        for bn in (256, 224) if n % 224 == 0 else (256, 128):
-            for gm in (2, 4, 8, 16, 32):
+        for bn in GEMM_RASTER_WIDTHS:
+            for gm in GEMM_RASTER_GROUPS:
                 lib.HcommGemmSetTuning(gm, bn)
                 gemm_bf16(a, w, out)
         torch.cuda.synchronize()
