@@ -347,6 +347,7 @@ HcclResult HcclGetCommAsyncError(HcclComm comm, HcclResult *asyncError)
     if (e == 0 && c->boot) {
         if (c->boot->RemoteError() != HCCL_SUCCESS) e = HCCL_E_REMOTE;
         else if (c->boot->LostMask() != 0) e = HCCL_E_REMOTE;   // a peer stopped answering heartbeats
+        else if (c->boot->HubGone()) e = HCCL_E_REMOTE;         // rank 0's process, which hosts the hub, is gone
     }
     *asyncError = (HcclResult)e;
     return HCCL_SUCCESS;

@@ -106,6 +106,9 @@ public:
     void StartHeartbeat(int intervalMs);
     void StopHeartbeat();   // also what a test uses to make this rank fall silent
     uint64_t LostMask() const { return lostMask_.load(); }
+    // The connection to the hub (rank 0's process) broke without this side closing it: that process is gone, and with
+    // it the heartbeat view, the relays and the retry rounds.
+    bool HubGone() const { return hubGone_.load(); }
     // Milliseconds since rank r was last heard by the hub, as of the newest state broadcast.
     void HeartbeatAges(std::vector<uint64_t> *ages) const;
     // Async error fan-out.

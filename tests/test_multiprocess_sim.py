@@ -21,6 +21,12 @@ def test_peer_exit_is_reported_as_remote_error():
     assert codes[0] == 0 and codes[1] == 0, "\n".join(outs)
 
 
+def test_exit_of_the_rank_that_hosts_the_hub_is_reported_too():
+    # rank 0's process carries the hub of the control plane; when it goes the others lose heartbeats and relays at once
+    codes, outs = launch("peer_exit", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_HUB_EXIT": "1"}, timeout=90)
+    assert codes[1] == 0 and codes[2] == 0, "\n".join(outs)
+
+
 def test_torch_backend_operators_on_the_simulator():
     codes, outs = launch("torch_ops", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "2", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29641"}, timeout=240)
     assert codes == [0, 0, 0], "\n".join(outs)
