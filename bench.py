@@ -103,12 +103,33 @@ class ClockSampler:
                 "samples_under_load": len(load), "power_w_max": round(pmax, 1)}
 
 
+def bind_near_gpu(local):
+    """Runs this process on the CPUs NVML names as closest to its GPU (both arms do), so that the pinned buffers of the
+    end-to-end step are allocated on that GPU's side of the host.  Returns the number of CPUs kept, 0 when nothing changed."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        near = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        keep = near & allowed
+        if keep and keep != allowed:
+            os.sched_setaffinity(0, keep)
+            return len(keep)
+    except Exception:
+        pass
+    return 0
+
+
 def setup_dist(torch, dist, a):
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     if world != a.gpus and world == 1:
         print(f"bench.py --gpus {a.gpus} must be launched with torch.distributed.run --nproc-per-node {a.gpus}", file=sys.stderr)
         sys.exit(2)
+    a.cpus_bound = 0 if a.no_bind else bind_near_gpu(local)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -279,7 +300,7 @@ def reference_arm(a):
             "impl": "nccl+cublas (reference is Ascend-only)", "reference_unavailable": REFERENCE_WHY,
             "metric": "tp_mlp_fused_tokens_per_s", "value": TOKENS / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_block(world), "clocks": clocks.summary(), "prespin_s": round(spin_s, 2),
+            "config": config_block(world), "clocks": clocks.summary(), "prespin_s": round(spin_s, 2), "cpus_bound_near_gpu": a.cpus_bound,
             "e2e": {"value": TOKENS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo},
             "gpu_launches": 0, "roofline_ms": roof, "fraction_of_roofline": roof / ms, "roofline_basis": basis}))
     if world > 1:
@@ -295,6 +316,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--prespin", type=float, default=1.5, help="seconds of GEMMs before the warm-up steps")
     ap.add_argument("--no-collectives", action="store_true", help="skip the all-reduce table")
+    ap.add_argument("--no-bind", action="store_true", help="leave the process on whatever CPUs it was started on")
     ap.add_argument("--mode", default="auto", choices=["auto", "fused", "split"], help="how the GEMM + collective operators run")
     ap.add_argument("--phases", default="", help="write the fused kernels' per-CTA phase clocks of one step to this JSON file (rank 0)")
     a = ap.parse_args()
@@ -429,7 +451,7 @@ def main():
             "metric": "tp_mlp_fused_tokens_per_s", "value": TOKENS / (ms_per_step * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
             "warmup": a.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "tflops_per_gpu": flops / world / (ms_per_step * 1e-3) / 1e12, "config": config_block(world),
-            "clocks": clocks.summary(), "prespin_s": round(spin_s, 2), "max_err_vs_cublas_nccl": max_err, "mode": a.mode,
+            "clocks": clocks.summary(), "prespin_s": round(spin_s, 2), "cpus_bound_near_gpu": a.cpus_bound, "max_err_vs_cublas_nccl": max_err, "mode": a.mode,
             "e2e": {"value": TOKENS / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": bi, "d2h_bytes_per_step": bo,
                     "note": "every step copies its input from pinned host memory and its whole result back to pinned host memory; the copies run on "
                             "copy streams beside the neighbouring steps' compute"},
