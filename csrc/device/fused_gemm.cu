@@ -58,7 +58,7 @@ namespace {
 
 using namespace hcgemm;
 
-constexpr int kFusedThreads = 256;          // reduce-scatter kernels: 6 GEMM warps (+ 2 idle)
+constexpr int kFusedThreads = 256;          // reduce-scatter kernels: 6 GEMM warps, the signaller and an idle warp (communication CTAs: 7 forwarding warps + publisher)
 constexpr int kAgThreads = 384;             // all-gather kernel on single CTAs: 6 GEMM warps + 6 communication warps
 constexpr int kAgPairThreads = 416;         // all-gather kernel on CTA pairs: 6 GEMM warps + 6 pushing warps + the signaller
 constexpr size_t kAgChunkBytes = 32 << 10;  // unit of the all-gather push: one warp moves one chunk
@@ -70,7 +70,7 @@ constexpr int kAgMaxBlocks = 1024;
 constexpr int kRsFlagBase = 16384;
 constexpr int kRsMaxSrcTiles = 8192;        // nRanks * tiles per rank
 static_assert((size_t)(kRsFlagBase + kRsMaxSrcTiles * 8) * 4 <= HC_OFF_TEAM_SYNC - HC_OFF_FUSED, "fused flags outgrew their region");
-// Device-local scratch of a communicator (Comm::fusedLocal): chunk counters of the push, then the phase clocks.
+// Device-local scratch of a communicator (Comm::fusedLocal): chunk counters of the push, the phase clocks, then the ready flags of the outbox.
 constexpr size_t kLocalSentWords = kAgMaxBlocks;
 constexpr size_t kLocalPhaseWords = 2 * 160 * kPhaseSlots;     // u64, two CTAs per SM pair slot, up to 160 SMs
 constexpr int kRsMaxLocalTiles = 4096;                            // tiles of a reduce-scatter whose partial tiles go through the outbox
@@ -105,7 +105,7 @@ __device__ __forceinline__ uint32_t *FusedFlag(const CommDev *d, int rank, int i
 
 // Walks `rows` x tilesN tiles in groups of `group` rows, column by column inside a group (the rows of a group share
 // B panels, the group's A panels stay in L2 while its columns pass): index -> (row, column).
-__device__ __forceinline__ void GroupedWalk(int index, int rows, int tilesN, int group, int *row, int *col)
+__host__ __device__ __forceinline__ void GroupedWalk(int index, int rows, int tilesN, int group, int *row, int *col)
 {
     const int perGroup = group * tilesN, gi = index / perGroup, r = index - gi * perGroup;
     const int here = rows - gi * group < group ? rows - gi * group : group;       // the last group may be shorter
@@ -120,7 +120,7 @@ __device__ __forceinline__ void GroupedWalk(int index, int rows, int tilesN, int
 // for the L2 (a destination's 16 row blocks of K = 14336 at two ranks would not fit).
 struct RsOrder {
     int rank, nRanks, mbPer, group;
-    __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
+    __host__ __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
     {
         const int perDest = mbPer * g.tilesN;
         const int remote = (nRanks - 1) * perDest;
@@ -521,7 +521,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFusedThreads, 1) Ge
 // panels pass once per group; one row block per group (the arrival order exactly) re-reads all of B for every block.
 struct AgOrder {
     int rank, nRanks, mbPer, group;
-    __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
+    __host__ __device__ __forceinline__ void operator()(int t, const GemmShape &g, int *mb, int *nb) const
     {
         const int perSrc = mbPer * g.tilesN;
         if (t < perSrc) {
@@ -1171,6 +1171,19 @@ int HcommFusedAllGatherGemmBf16Mode(HcclComm comm, const void *x, const void *W,
     hc::Comm *c = hc::AsComm(comm);
     if (!c) return HCCL_E_PTR;
     return (int)hc::FusedAllGatherGemm(c, x, W, out, Mshard, N, K, ldx, ldw, ldOut, stream, mode);
+}
+
+// Tile t of the fused kernels' schedules, evaluated on the host: kind 0 = GEMM -> reduce-scatter, 1 = all-gather -> GEMM;
+// `mbPer` row blocks per rank, `tilesN` tile columns, `group` row blocks per group.  The kernels run the same functions;
+// tests check on the CPU that every schedule visits every tile once and in the order the flags are produced.
+int HcommToolFusedTileOrder(int kind, int rank, int nRanks, int mbPer, int tilesN, int group, int t, int *mb, int *nb)
+{
+    if (!mb || !nb || nRanks < 1 || rank < 0 || rank >= nRanks || mbPer < 1 || tilesN < 1 || group < 1 || t < 0 || t >= nRanks * mbPer * tilesN) return HCCL_E_PARA;
+    hcgemm::GemmShape g;
+    g.M = g.N = g.K = 0; g.tilesM = nRanks * mbPer; g.tilesN = tilesN; g.errFlag = nullptr; g.phase = nullptr;
+    if (kind == 0) hc::RsOrder{rank, nRanks, mbPer, group}(t, g, mb, nb);
+    else hc::AgOrder{rank, nRanks, mbPer, group}(t, g, mb, nb);
+    return HCCL_SUCCESS;
 }
 
 // Phase clocks of the CTA-pair fused kernels: when on, every call records per CTA when it started and ended and how long
