@@ -568,6 +568,32 @@ struct AgGate {
     }
 };
 
+// Item `it` of the all-gather push of a rank with p - 1 peers: which 128-row block, which peer (index 0 = the next
+// rank), which byte range of the shard.  Items are block-major: all chunks of block 0 for every peer, then block 1, ...
+struct AgItem {
+    int blk, peerIdx, ch;
+    size_t off, len;
+};
+__host__ __device__ __forceinline__ int AgChunksPerBlock(int K)
+{
+    const size_t blockBytes = (size_t)kBlockM * K * 2;                          // bf16; a multiple of 2 KB (K is a multiple of 8)
+    return (int)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes);
+}
+__host__ __device__ __forceinline__ AgItem AgDecode(int it, int nRanks, int K)
+{
+    const size_t blockBytes = (size_t)kBlockM * K * 2;
+    const int chunksPerBlock = AgChunksPerBlock(K), perBlock = (nRanks - 1) * chunksPerBlock;
+    AgItem a;
+    a.blk = it / perBlock;
+    const int rem = it % perBlock;
+    a.peerIdx = rem / chunksPerBlock;
+    a.ch = rem % chunksPerBlock;
+    const size_t inBlock = (size_t)a.ch * kAgChunkBytes;
+    a.off = (size_t)a.blk * blockBytes + inBlock;
+    a.len = blockBytes - inBlock < kAgChunkBytes ? blockBytes - inBlock : kAgChunkBytes;
+    return a;
+}
+
 // Communication warps: push my shard to the peers' staging, block-major.  `warps` warps share the work, this one is
 // number `w`; its items are w, w + warps, w + 2 * warps, ...  With `report` (a word in shared memory) the warp only
 // counts the chunks it has stored there and AgPush::Signal, on another warp of the CTA, publishes them; without, the
@@ -583,35 +609,28 @@ struct AgPush {
     uint64_t *phase;
     int pushWarps, signaller;
 
-    __device__ __forceinline__ int ChunksPerBlock() const
-    {
-        const size_t blockBytes = (size_t)kBlockM * K * sizeof(__nv_bfloat16);
-        return (int)((blockBytes + kAgChunkBytes - 1) / kAgChunkBytes);
-    }
+    __device__ __forceinline__ int ChunksPerBlock() const { return AgChunksPerBlock(K); }
     __device__ __forceinline__ int Items() const { return mbPer * (d->nRanks - 1) * ChunksPerBlock(); }
     // Chunk `it` is on the peers' side: count it; the caller has ordered the chunk before the count (fence).  The
     // thread whose count completes a block has seen every chunk of it ordered (fence, atomic on one side - atomic,
     // fence on the other) and names the block on the consumer.
     __device__ __forceinline__ void Count(int it) const
     {
-        const int n = d->nRanks, me = d->rank, chunksPerBlock = ChunksPerBlock(), perBlock = (n - 1) * chunksPerBlock;
-        const int blk = it / perBlock, peerIdx = (it % perBlock) / chunksPerBlock;
-        uint32_t *ctr = sent + peerIdx * mbPer + blk;
-        if (atomicAdd(ctr, 1u) + 1u == (uint32_t)chunksPerBlock) {
+        const int n = d->nRanks, me = d->rank;
+        const AgItem a = AgDecode(it, n, K);
+        uint32_t *ctr = sent + a.peerIdx * mbPer + a.blk;
+        if (atomicAdd(ctr, 1u) + 1u == (uint32_t)ChunksPerBlock()) {
             *(volatile uint32_t *)ctr = 0u;                               // next used by a later launch
             hcdev::FenceAcqRelSys();
-            hcdev::StRelaxedSys(FusedFlag(d, (me + 1 + peerIdx) % n, kAgFlagBase + (me * mbPer + blk) * 8), seq);
+            hcdev::StRelaxedSys(FusedFlag(d, (me + 1 + a.peerIdx) % n, kAgFlagBase + (me * mbPer + a.blk) * 8), seq);
         }
     }
     __device__ __forceinline__ void Run(int w, int warps, int lane, uint32_t *report = nullptr, bool clocked = false) const
     {
         if (!x) return;
         const int n = d->nRanks, me = d->rank;
-        const size_t rowBytes = (size_t)K * sizeof(__nv_bfloat16);
-        const size_t blockBytes = (size_t)kBlockM * rowBytes;                     // a multiple of 2 KB (K is a multiple of 8)
-        const int chunksPerBlock = ChunksPerBlock();
-        const int perBlock = (n - 1) * chunksPerBlock;
-        const int items = mbPer * perBlock;
+        const size_t blockBytes = (size_t)kBlockM * K * sizeof(__nv_bfloat16);
+        const int items = Items();
         clocked = clocked && phase;
         const uint64_t tStart = clocked ? GlobalTimer() : 0;
         uint64_t tSignal = 0;
@@ -619,13 +638,11 @@ struct AgPush {
         // block-major order: block 0 to every peer (nearest consumer first), then block 1, ...; consecutive warps take
         // consecutive chunks, so the warps in flight write to all peers at once
         for (int it = w; it < items; it += warps) {
-            const int blk = it / perBlock, rem = it % perBlock;
-            const int peerIdx = rem / chunksPerBlock, ch = rem % chunksPerBlock;
-            const int peer = (me + 1 + peerIdx) % n;
-            const size_t off = (size_t)blk * blockBytes + (size_t)ch * kAgChunkBytes;
-            const size_t len = blockBytes - (size_t)ch * kAgChunkBytes < kAgChunkBytes ? blockBytes - (size_t)ch * kAgChunkBytes : kAgChunkBytes;
-            const char *src = x + off;
-            char *dst = hcdev::CclHalf(d, peer, half) + (size_t)me * mbPer * blockBytes + off;
+            const AgItem a = AgDecode(it, n, K);
+            const int peer = (me + 1 + a.peerIdx) % n;
+            const size_t len = a.len;
+            const char *src = x + a.off;
+            char *dst = hcdev::CclHalf(d, peer, half) + (size_t)me * mbPer * blockBytes + a.off;
             // eight 16-byte loads per lane in flight (4 KB per warp and step)
             for (size_t b = (size_t)lane * 16; b < len; b += 32 * 16 * 8) {
                 uint4 v[8];
@@ -1183,6 +1200,21 @@ int HcommToolFusedTileOrder(int kind, int rank, int nRanks, int mbPer, int tiles
     g.M = g.N = g.K = 0; g.tilesM = nRanks * mbPer; g.tilesN = tilesN; g.errFlag = nullptr; g.phase = nullptr;
     if (kind == 0) hc::RsOrder{rank, nRanks, mbPer, group}(t, g, mb, nb);
     else hc::AgOrder{rank, nRanks, mbPer, group}(t, g, mb, nb);
+    return HCCL_SUCCESS;
+}
+
+// Item `item` of the all-gather push (see AgDecode), evaluated on the host; *items receives the number of items of a rank.
+int HcommToolFusedPushItem(int nRanks, int mbPer, int K, int item, int *items, int *blk, int *peerIdx, unsigned long long *off, unsigned long long *len)
+{
+    if (nRanks < 2 || mbPer < 1 || K < 8 || K % 8) return HCCL_E_PARA;
+    const int total = mbPer * (nRanks - 1) * hc::AgChunksPerBlock(K);
+    if (items) *items = total;
+    if (item < 0 || item >= total) return item == -1 ? HCCL_SUCCESS : HCCL_E_PARA;
+    const hc::AgItem a = hc::AgDecode(item, nRanks, K);
+    if (blk) *blk = a.blk;
+    if (peerIdx) *peerIdx = a.peerIdx;
+    if (off) *off = a.off;
+    if (len) *len = a.len;
     return HCCL_SUCCESS;
 }
 

@@ -57,3 +57,36 @@ def test_all_gather_order_starts_with_own_rows_and_follows_the_arrival_of_blocks
         order_of_first_use = [b for b, _ in sorted(first_use.items(), key=lambda kv: kv[1])]
         groups = [b // group for b in order_of_first_use]
         assert groups == sorted(groups)
+
+
+@pytest.mark.parametrize("n,mb_per,k", [(2, 8, 8192), (8, 8, 8192), (4, 3, 1000), (8, 2, 72), (3, 5, 16392)])
+def test_all_gather_push_items_cover_every_byte_for_every_peer_once_block_by_block(n, mb_per, k):
+    from hcomm_b200 import _lib
+    fn = _lib.load().HcommToolFusedPushItem
+    fn.restype = ctypes.c_int
+    items = ctypes.c_int(0)
+    assert fn(n, mb_per, k, -1, ctypes.byref(items), None, None, None, None) == 0
+    block_bytes = 128 * k * 2
+    covered = {p: [] for p in range(n - 1)}
+    per_block = {}
+    last_blk = 0
+    for it in range(items.value):
+        blk, peer = ctypes.c_int(), ctypes.c_int()
+        off, ln = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+        assert fn(n, mb_per, k, it, None, ctypes.byref(blk), ctypes.byref(peer), ctypes.byref(off), ctypes.byref(ln)) == 0
+        assert 0 <= peer.value < n - 1 and 0 <= blk.value < mb_per
+        assert blk.value >= last_blk                      # block-major: the consumers take blocks in this order
+        last_blk = blk.value
+        assert off.value % 16 == 0 and ln.value % 16 == 0 and ln.value > 0
+        assert off.value // block_bytes == blk.value and (off.value + ln.value - 1) // block_bytes == blk.value
+        covered[peer.value].append((off.value, ln.value))
+        per_block[(peer.value, blk.value)] = per_block.get((peer.value, blk.value), 0) + 1
+    chunks = (block_bytes + (32 << 10) - 1) // (32 << 10)
+    assert all(v == chunks for v in per_block.values()) and len(per_block) == (n - 1) * mb_per
+    for p, ranges in covered.items():
+        ranges.sort()
+        pos = 0
+        for off, ln in ranges:
+            assert off == pos
+            pos += ln
+        assert pos == mb_per * block_bytes
