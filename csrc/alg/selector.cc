@@ -152,9 +152,10 @@ void Builtin(TuneTable &t)
                                        {UINT64_MAX, Algo::NVLS, Engine::NVLS, 0}};
         t.buckets["broadcast/" + n] = {{1 * MB, Algo::MESH_ONESHOT, Engine::SM_FAST, 0}, {UINT64_MAX, Algo::NVLS, Engine::NVLS, 0}};
         // all-gather (bytes per rank): multicast stores win in the middle range on 8 GPUs (4 MB in total: 39 us against 54,
-        // 16 MB: 57 against 72), lose below (32 - 35 us against 22 - 25) and above 64 MB in total (152 us against 143);
-        // on 2 and 4 GPUs the mesh kernel is faster at every size
-        if (p >= 6) t.buckets["allgather/" + n] = {{128 * KB, Algo::MESH, Engine::SM_FAST, 0}, {4 * MB, Algo::NVLS, Engine::NVLS, 0}, {UINT64_MAX, Algo::MESH, Engine::SM_FAST, 0}};
+        // 16 MB: 57 against 72), lose below (32 - 35 us against 22 - 25) and at 64 MB in total (152 us against 143);
+        // on 2 and 4 GPUs the mesh kernel is faster at every size.  The buckets are what `python -m hcomm_b200.utils.tune
+        // --from-sweeps` makes of the 8-GPU sweeps of the two families (hcomm_b200/utils/tune_tables/).
+        if (p >= 6) t.buckets["allgather/" + n] = {{128 * KB, Algo::MESH, Engine::SM_FAST, 0}, {2 * MB, Algo::NVLS, Engine::NVLS, 0}, {UINT64_MAX, Algo::MESH, Engine::SM_FAST, 0}};
         else t.buckets["allgather/" + n] = {{UINT64_MAX, Algo::MESH, Engine::SM_FAST, 0}};
         t.buckets["reducescatter/" + n] = {{UINT64_MAX, Algo::MESH, Engine::SM_FAST, 0}};
         t.buckets["alltoall/" + n] = {{UINT64_MAX, Algo::MESH, Engine::SM_FAST, 0}};

@@ -6,7 +6,14 @@
 For every collective and message size the candidates (mesh one-shot, mesh two-shot, in-switch reduction, each with
 a few CTA counts) are timed with the same rules as the benchmarks (CUDA events, L2 flush, maximum over ranks); the
 fastest candidate per size wins and neighbouring sizes with the same winner are merged into one bucket.
-The file format is what ``HCCL_TUNE_FILE`` expects: {op: {ranks: [{"max_bytes", "algo", "engine", "ctas"}, ...]}}.
+The file format is what ``HCCL_TUNE_FILE`` expects: {op: {ranks: [{"max_bytes", "algo", "engine", "ctas"}, ...]}};
+``max_bytes`` counts what the selector sees: the whole vector for all-reduce and broadcast, one rank's block for
+all-gather, reduce-scatter and all-to-all.
+
+The same table can be built without a GPU from sweeps that ``coll_bench --out`` wrote earlier, one file per forced
+algorithm (a file whose rows say ``auto`` stands for the family given with ``--auto-is``):
+
+    python -m hcomm_b200.utils.tune --from-sweeps mesh.json nvls.json --auto-is mesh --ops allgather,reducescatter --out tune_8.json
 """
 from __future__ import annotations
 
@@ -57,6 +64,42 @@ def pick_winners(measurements):
     return winners
 
 
+def selector_bytes(op, nbytes, world):
+    """The size the selector compares with ``max_bytes`` for an operand of `nbytes` as the benchmarks count them."""
+    return nbytes // world if op in ("allgather", "reducescatter", "alltoall") else nbytes
+
+
+def family_of(label, op, auto_is):
+    """(algo, engine) of a sweep row's ``algo`` label, e.g. ``allgather=level0:nvls/reducescatter=level0:nvls``."""
+    name = auto_is
+    if label and label != "auto":
+        for part in label.split("/"):
+            key, _, val = part.partition("=")
+            if not val:                                   # "level0:ring" applies to every operator
+                key, val = op, part
+            if key.strip() == op:
+                name = val.split(":")[-1].strip().lower()
+    name = {"fullmesh": "mesh", "oneshot": "mesh_oneshot"}.get(name, name)
+    return name, ("nvls" if name == "nvls" else "sm")
+
+
+def table_from_sweeps(paths, ops, auto_is="mesh"):
+    """Builds the bucket table from ``coll_bench --out`` files (lists of rows with op, bytes, n, algo, ours_us)."""
+    meas = {}
+    for path in paths:
+        with open(path) as f:
+            for row in json.load(f):
+                if row["op"] not in ops or row.get("registered"):
+                    continue
+                algo, engine = family_of(row.get("algo", "auto"), row["op"], auto_is)
+                key = (row["op"], str(row["n"]))
+                meas.setdefault(key, {}).setdefault(selector_bytes(row["op"], row["bytes"], row["n"]), {})[(algo, engine, 0)] = row["ours_us"]
+    table = {}
+    for (op, ranks), by_size in sorted(meas.items()):
+        table.setdefault(op, {})[ranks] = merge_buckets(pick_winners(by_size))
+    return table
+
+
 def algo_config(op, algo, engine):
     level0 = {"mesh": "fullmesh", "mesh_oneshot": "fullmesh", "nvls": "nvls"}[algo]
     return f"{op}=level0:{level0}"
@@ -77,7 +120,15 @@ def main():
     ap.add_argument("--factor", type=int, default=4)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--out", default="hccl_tune.json")
+    ap.add_argument("--from-sweeps", nargs="+", default=None, help="build the table from coll_bench --out files instead of measuring")
+    ap.add_argument("--auto-is", default="mesh", help="family that rows labelled 'auto' stand for (with --from-sweeps)")
     a = ap.parse_args()
+    if a.from_sweeps:
+        table = table_from_sweeps(a.from_sweeps, a.ops.split(","), a.auto_is)
+        with open(a.out, "w") as f:
+            json.dump(table, f, indent=1)
+        print(json.dumps(table))
+        return
     rank, world, local = env_rank()
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -116,7 +167,7 @@ def main():
                         continue
                     t = torch.tensor([med], device="cuda", dtype=torch.float64)
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                    meas.setdefault(nbytes, {})[(algo, engine, ctas)] = t.item() * 1e3
+                    meas.setdefault(selector_bytes(op, nbytes, world), {})[(algo, engine, ctas)] = t.item() * 1e3
                 torch.cuda.synchronize()
                 comm.destroy()
         table[op] = {str(world): merge_buckets(pick_winners(meas))}
