@@ -220,7 +220,7 @@ HcclResult HcclCommGetOpRetryStats(HcclComm comm, HcclOpRetryStats *stats)
     if (!r) return HCCL_SUCCESS;
     std::lock_guard<std::mutex> lk(r->mu);
     stats->enabled = 1; stats->maxCnt = r->maxCnt; stats->holdTimeMs = r->holdMs; stats->intervalMs = r->intervalMs;
-    stats->requests = r->requests; stats->rounds = r->rounds; stats->succeeded = r->succeeded; stats->failed = r->failed;
+    stats->requests = r->requests.load(); stats->rounds = r->rounds.load(); stats->succeeded = r->succeeded.load(); stats->failed = r->failed.load();
     return HCCL_SUCCESS;
 }
 

@@ -53,7 +53,7 @@ struct RetryState {
     bool requested = false;
     uint64_t verdictSeq = 0, servedSeq = 0;
     int verdict = 0;
-    uint64_t requests = 0, rounds = 0, succeeded = 0, failed = 0;
+    std::atomic<uint64_t> requests{0}, rounds{0}, succeeded{0}, failed{0};   // read by HcclCommGetOpRetryStats from any thread
 };
 void RetryNoteOp(Comm *c, const OpDesc &d);
 HcclResult RetryAfterTimeout(Comm *c, uint64_t seq);

@@ -62,6 +62,7 @@ def _obj_for(src: Path, variant: str = "") -> Path:
 
 
 ASAN_HOST_FLAGS = ["-fsanitize=address", "-fno-omit-frame-pointer", "-g"]
+TSAN_HOST_FLAGS = ["-fsanitize=thread", "-fno-omit-frame-pointer", "-g"]
 
 
 def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=(), variant: str = "", defines=()) -> Path:
@@ -69,12 +70,12 @@ def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=(), variant:
     obj.parent.mkdir(parents=True, exist_ok=True)
     if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_mtime):
         return obj
-    asan = variant == "asan"
+    san = {"asan": ASAN_HOST_FLAGS, "tsan": TSAN_HOST_FLAGS}.get(variant, [])
     if src.suffix == ".cu":
-        host = ["-Xcompiler", ",".join(ASAN_HOST_FLAGS)] if asan else []       # host side of the file only; device code has no such tool
+        host = ["-Xcompiler", ",".join(san)] if san else []       # host side of the file only; device code has no such tool
         cmd = [NVCC, *NVCC_FLAGS, *extra_nvcc, *host, *defines, "-c", str(src), "-o", str(obj)]
     else:
-        cmd = ["g++", *CXX_FLAGS, *(ASAN_HOST_FLAGS if asan else []), *defines, "-c", str(src), "-o", str(obj)]
+        cmd = ["g++", *CXX_FLAGS, *san, *defines, "-c", str(src), "-o", str(obj)]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -85,31 +86,32 @@ def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=(), variant:
     return obj
 
 
-def build_core(verbose: bool = False, jobs: int | None = None, bounds: bool = False, asan: bool = False) -> Path:
+def build_core(verbose: bool = False, jobs: int | None = None, bounds: bool = False, asan: bool = False, tsan: bool = False) -> Path:
     """Builds ``libhcomm.so`` and returns its path.
 
     ``asan=True`` builds ``libhcomm_asan.so``: the host runtime (and the host side of the ``.cu`` files) compiled with
     AddressSanitizer.  Load it with ``HCOMM_LIBRARY=asan`` in a process started with ``LD_PRELOAD`` set to the compiler's
     ``libasan.so`` (``g++ -print-file-name=libasan.so``) and ``ASAN_OPTIONS=detect_leaks=0`` (the interpreter leaks by design);
     the simulator platform (``HCCL_SIM=1``) then runs the control plane, the host engine and the schedule interpreter under it.
+    ``tsan=True`` builds ``libhcomm_tsan.so`` the same way with ThreadSanitizer (``HCOMM_LIBRARY=tsan``, preload ``libtsan.so``).
 
     ``bounds=True`` builds ``libhcomm_bounds.so`` instead: the same library compiled with ``-DHCOMM_DEBUG_BOUNDS``, in
     which every grid copy and reduction of the collective kernels checks its address ranges against the symmetric heap
     and the CCL halves and records a violation in the status block instead of touching memory out of range.  Select it
     at run time with ``HCOMM_LIBRARY=bounds``."""
     LIBDIR.mkdir(parents=True, exist_ok=True)
-    out = LIBDIR / ("libhcomm_bounds.so" if bounds else ("libhcomm_asan.so" if asan else "libhcomm.so"))
+    out = LIBDIR / ("libhcomm_bounds.so" if bounds else ("libhcomm_asan.so" if asan else ("libhcomm_tsan.so" if tsan else "libhcomm.so")))
     srcs = _core_sources()
     hdr = _headers_mtime()
     jobs = jobs or min(8, os.cpu_count() or 4)
-    variant, defines = ("bounds", ("-DHCOMM_DEBUG_BOUNDS",)) if bounds else (("asan", ()) if asan else ("", ()))
+    variant, defines = ("bounds", ("-DHCOMM_DEBUG_BOUNDS",)) if bounds else (("asan", ()) if asan else (("tsan", ()) if tsan else ("", ())))
     with ThreadPoolExecutor(max_workers=jobs) as ex:
         objs = list(ex.map(lambda s: _compile(s, hdr, verbose, variant=variant, defines=defines), srcs))
     newest_obj = max(o.stat().st_mtime for o in objs)
     if out.exists() and out.stat().st_mtime >= newest_obj:
         return out
     link = ["g++", "-shared", "-o", str(out), *map(str, objs), f"-L{CUDA_HOME / 'lib64'}", "-lcudart_static",
-            "-lpthread", "-ldl", "-lrt"] + (["-fsanitize=address"] if asan else ["-Wl,--no-undefined"])
+            "-lpthread", "-ldl", "-lrt"] + (["-fsanitize=address"] if asan else (["-fsanitize=thread"] if tsan else ["-Wl,--no-undefined"]))
     if verbose:
         print(" ".join(link), flush=True)
     res = subprocess.run(link, capture_output=True, text=True)
@@ -184,4 +186,6 @@ if __name__ == "__main__":
         build_core(verbose="-v" in sys.argv, bounds=True)
     if "--asan" in sys.argv:
         build_core(verbose="-v" in sys.argv, asan=True)
+    if "--tsan" in sys.argv:
+        build_core(verbose="-v" in sys.argv, tsan=True)
     print("built:", *sorted(p.name for p in LIBDIR.glob("*.so")))
