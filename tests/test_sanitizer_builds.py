@@ -1,5 +1,5 @@
-"""The AddressSanitizer and ThreadSanitizer builds of the host runtime (``python -m hcomm_b200.build --asan`` / ``--tsan``) under
-the simulator platform.
+"""The AddressSanitizer, ThreadSanitizer and UndefinedBehaviorSanitizer builds of the host runtime
+(``python -m hcomm_b200.build --asan`` / ``--tsan`` / ``--ubsan``) under the simulator platform.
 
 Skipped when the library has not been built.  Every scenario runs as separate processes with the sanitizer's runtime
 preloaded; an address report of any kind, or a data race, fails the test."""
@@ -12,6 +12,7 @@ from mp_launch import launch
 
 LIBDIR = Path(__file__).resolve().parent.parent / "hcomm_b200" / "lib"
 needs_asan = pytest.mark.skipif(not (LIBDIR / "libhcomm_asan.so").exists(), reason="libhcomm_asan.so not built (python -m hcomm_b200.build --asan)")
+needs_ubsan = pytest.mark.skipif(not (LIBDIR / "libhcomm_ubsan.so").exists(), reason="libhcomm_ubsan.so not built (python -m hcomm_b200.build --ubsan)")
 needs_tsan = pytest.mark.skipif(not (LIBDIR / "libhcomm_tsan.so").exists(), reason="libhcomm_tsan.so not built (python -m hcomm_b200.build --tsan)")
 
 SCENARIOS = [
@@ -59,4 +60,18 @@ def test_simulator_scenarios_have_no_data_race_under_thread_sanitizer(scenario, 
     codes, outs = launch(scenario, world, _tsan_env(extra), timeout=600)
     text = "\n".join(outs)
     assert "ThreadSanitizer: data race" not in text and "ThreadSanitizer: lock-order-inversion" not in text, text[-6000:]
+    assert codes == [0] * world, text[-4000:]
+
+
+@needs_ubsan
+@pytest.mark.parametrize("scenario,world,extra", SCENARIOS[:3])
+def test_simulator_scenarios_have_no_undefined_behaviour(scenario, world, extra):
+    runtime = subprocess.run(["g++", "-print-file-name=libubsan.so"], capture_output=True, text=True).stdout.strip()
+    if not runtime or not Path(runtime).exists():
+        pytest.skip("the compiler's libubsan.so was not found")
+    env = {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_LIBRARY": "ubsan", "LD_PRELOAD": runtime, "UBSAN_OPTIONS": "print_stacktrace=1:halt_on_error=0"}
+    env.update(extra)
+    codes, outs = launch(scenario, world, env, timeout=300)
+    text = "\n".join(outs)
+    assert "runtime error" not in text, text[-4000:]
     assert codes == [0] * world, text[-4000:]
