@@ -92,6 +92,14 @@ HcclResult HcclDiagGetHeartbeat(HcclComm comm, uint64_t *ageMs, uint32_t capacit
     return HCCL_SUCCESS;
 }
 
+HcclResult HcclDiagPauseHeartbeat(HcclComm comm)
+{
+    Comm *c = AsComm(comm);
+    CHK_PTR_NULL(c);
+    c->boot->StopHeartbeat();
+    return HCCL_SUCCESS;
+}
+
 HcclResult HcclDiagSetProfiling(HcclComm comm, int enable)
 {
     Comm *c = AsComm(comm);

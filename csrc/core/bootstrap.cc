@@ -17,6 +17,10 @@ namespace {
 constexpr uint32_t kMsgMagic = 0x4d434348;  // "HCCM"
 constexpr uint64_t kMaxMsgBytes = 100ull << 20;  // same cap as the reference's rank-table buffer
 
+// Messages of the ring monitor travel over the descriptor-passing sockets without a descriptor: the header's second
+// word says which kind, the set of ranks the sender holds for lost rides in its tag.
+constexpr uint32_t kRingPing = 1, kRingBye = 2;
+
 enum MsgType : uint16_t {
     MSG_HELLO = 1,
     MSG_TABLE = 2,
@@ -374,7 +378,16 @@ HcclResult Bootstrap::Connect(const RootHandle &root, uint32_t rank, uint32_t nR
 void Bootstrap::Close()
 {
     if (closing_.exchange(true)) return;
+    const bool monitored = heart_.joinable();
     StopHeartbeat();
+    if (monitored && nRanks_ >= 2 && nRanks_ <= 64) {
+        // Leave the ring: every rank still there skips this one from now on instead of finding its socket closed.
+        // Everyone is told, not only the neighbours, because two neighbours that leave at the same moment would
+        // otherwise each tell only the other.  One connection attempt per rank: a rank that is gone costs nothing.
+        const uint64_t skip = LostMask() | ringLeft_.load();
+        for (uint32_t r = 0; r < nRanks_; ++r)
+            if (r != rank_ && !((skip >> r) & 1)) RingSend(r, kRingBye, 0);
+    }
     if (sock_ >= 0) {
         {
             std::lock_guard<std::mutex> lk(sendMu_);
@@ -462,9 +475,13 @@ void Bootstrap::FdAcceptLoop()
         struct { uint32_t src; uint32_t pad; uint64_t tag; } meta;
         int fd = -1;
         if (net::UdsRecvFd(c, &meta, sizeof(meta), &fd, net::NowMs() + 5000) == HCCL_SUCCESS) {
-            std::lock_guard<std::mutex> lk(mu_);
-            fdInbox_[Key{meta.src, meta.tag}].push_back(fd);
-            cv_.notify_all();
+            if (fd < 0) {
+                RingHeard(meta.src, meta.pad, meta.tag);      // no descriptor: a message of the ring monitor
+            } else {
+                std::lock_guard<std::mutex> lk(mu_);
+                fdInbox_[Key{meta.src, meta.tag}].push_back(fd);
+                cv_.notify_all();
+            }
         }
         ::close(c);
     }
@@ -572,13 +589,88 @@ HcclResult Bootstrap::RecvFd(uint32_t srcRank, uint64_t tag, int *fd, int timeou
     return HCCL_SUCCESS;
 }
 
+// ---- ring monitor
+
+// Nearest rank in direction dir (+1 / -1) that is neither lost nor gone; -1 if there is none.
+int Bootstrap::RingNeighbour(int dir) const
+{
+    const uint64_t skip = LostMask() | ringLeft_.load();
+    for (uint32_t k = 1; k < nRanks_; ++k) {
+        const uint32_t r = (rank_ + nRanks_ + (dir > 0 ? k : nRanks_ - k)) % nRanks_;
+        if (r == rank_) break;
+        if (nRanks_ <= 64 && (skip >> r) & 1) continue;
+        return (int)r;
+    }
+    return -1;
+}
+
+bool Bootstrap::RingSend(uint32_t dst, uint32_t kind, int deadlineMs)
+{
+    int c = -1;
+    if (net::UdsConnect("hccl-" + identifier_ + "-" + std::to_string(dst), net::NowMs() + deadlineMs, &c) != HCCL_SUCCESS) return false;
+    struct { uint32_t src; uint32_t pad; uint64_t tag; } meta{rank_, kind, LostMask()};
+    ssize_t n;
+    do { n = send(c, &meta, sizeof(meta), MSG_NOSIGNAL); } while (n < 0 && errno == EINTR);
+    ::close(c);
+    return n == (ssize_t)sizeof(meta);
+}
+
+void Bootstrap::RingHeard(uint32_t src, uint32_t kind, uint64_t lostSeen)
+{
+    if (src >= nRanks_ || nRanks_ > 64) return;
+    if (kind == kRingBye) { ringLeft_.fetch_or(1ull << src); return; }
+    if (kind != kRingPing) return;
+    {
+        std::lock_guard<std::mutex> lk(hbMu_);
+        if (src < ringHeardMs_.size()) ringHeardMs_[src] = net::NowMs();
+    }
+    // what the sender knows travels on; nobody talks this rank, or the sender itself, into being lost
+    ringLost_.fetch_or(lostSeen & ~(1ull << rank_) & ~(1ull << src));
+}
+
+void Bootstrap::RingTick(int lostAfterMs)
+{
+    if (nRanks_ < 2 || nRanks_ > 64) return;
+    const int64_t now = net::NowMs();
+    int done = -1;
+    for (int dir : {+1, -1}) {
+        const int nb = RingNeighbour(dir);
+        if (nb < 0 || nb == done) continue;         // two ranks: both directions meet the same neighbour
+        done = nb;
+        if (RingSend((uint32_t)nb, kRingPing, 100)) {
+            ringRefused_[nb] = 0;
+        } else if (++ringRefused_[nb] >= 2) {
+            // nobody listens on the neighbour's socket any more: its process is gone
+            ringLost_.fetch_or(1ull << nb);
+            HCCL_WARNING("ring monitor: rank %d does not accept connections, marked LOST by rank %u", nb, rank_);
+            continue;
+        }
+        int64_t heard;
+        {
+            std::lock_guard<std::mutex> lk(hbMu_);
+            heard = ringHeardMs_[nb];
+        }
+        if (now - heard > lostAfterMs) {
+            ringLost_.fetch_or(1ull << nb);
+            HCCL_WARNING("ring monitor: rank %d silent for %lld ms, marked LOST by rank %u", nb, (long long)(now - heard), rank_);
+        }
+    }
+}
+
 void Bootstrap::StartHeartbeat(int intervalMs)
 {
     if (heart_.joinable()) return;
     heartStop_.store(false);
-    heart_ = std::thread([this, intervalMs] {
+    {
+        std::lock_guard<std::mutex> lk(hbMu_);
+        ringHeardMs_.assign(nRanks_, net::NowMs());        // silence counts from now
+    }
+    ringRefused_.assign(nRanks_, 0);
+    const int lostAfterMs = EnvConfig::Get().heartbeatLostMs.value;
+    heart_ = std::thread([this, intervalMs, lostAfterMs] {
         while (!heartStop_.load() && !closing_.load()) {
-            SendMsg(MSG_HEARTBEAT, 0, 0, nullptr, 0);
+            if (!hubGone_.load()) SendMsg(MSG_HEARTBEAT, 0, 0, nullptr, 0);
+            RingTick(lostAfterMs);
             for (int waited = 0; waited < intervalMs && !heartStop_.load(); waited += 10) usleep(10000);
         }
     });

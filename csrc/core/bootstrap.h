@@ -13,6 +13,13 @@
 //     a connection that closes without a goodbye marks the rank lost at once,
 //   - asynchronous error broadcast (a rank that hits a device timeout tells everyone).
 // File descriptors (exported memory) travel rank-to-rank over abstract Unix sockets.
+//
+// Beside the star, when heartbeats are on, the ranks watch each other in a ring that does not need the hub (the
+// reference's cluster monitor is a double ring, src/coll_communicator_mgr/dfx/cluster_monitor/README_en.md:9-20):
+// every interval a rank pings its nearest live neighbour in both directions over that neighbour's Unix socket.  A
+// neighbour whose socket refuses connections (its process is gone) or that has been silent for the lost time is marked
+// lost; every ping carries the sender's set of lost ranks, so the news travels round the ring also after the hub's
+// process has died.  A rank that closes its communicator says goodbye first and is skipped from then on.
 #pragma once
 #include <atomic>
 #include <condition_variable>
@@ -105,7 +112,7 @@ public:
     // Heartbeat: starts a thread that pings the hub every intervalMs.
     void StartHeartbeat(int intervalMs);
     void StopHeartbeat();   // also what a test uses to make this rank fall silent
-    uint64_t LostMask() const { return lostMask_.load(); }
+    uint64_t LostMask() const { return lostMask_.load() | ringLost_.load(); }
     // The connection to the hub (rank 0's process) broke without this side closing it: that process is gone, and with
     // it the heartbeat view, the relays and the retry rounds.
     bool HubGone() const { return hubGone_.load(); }
@@ -126,6 +133,11 @@ private:
     };
     void ReaderLoop();
     void FdAcceptLoop();
+    // ring monitor (runs on the heartbeat thread; messages arrive on the descriptor-accept thread)
+    void RingTick(int lostAfterMs);
+    void RingHeard(uint32_t src, uint32_t kind, uint64_t lostSeen);
+    bool RingSend(uint32_t dst, uint32_t kind, int deadlineMs);
+    int RingNeighbour(int dir) const;
     HcclResult SendMsg(uint16_t type, uint32_t dst, uint64_t tag, const void *data, size_t len);
 
     uint32_t rank_ = 0, nRanks_ = 0;
@@ -147,6 +159,9 @@ private:
     std::atomic<int> remoteError_{0};
     mutable std::mutex hbMu_;
     std::vector<uint64_t> ages_;
+    std::atomic<uint64_t> ringLost_{0}, ringLeft_{0};
+    std::vector<int64_t> ringHeardMs_;       // guarded by hbMu_: when each rank's ping last arrived
+    std::vector<int> ringRefused_;           // heartbeat thread only: consecutive refused connections per rank
 };
 
 }  // namespace hc

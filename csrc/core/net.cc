@@ -278,7 +278,10 @@ HcclResult UdsRecvFd(int sock, void *meta, size_t metaLen, int *fdOut, int64_t d
     do { n = recvmsg(sock, &msg, MSG_CMSG_CLOEXEC); } while (n < 0 && errno == EINTR);
     if (n != (ssize_t)metaLen) return HCCL_E_SYSCALL;
     struct cmsghdr *c = CMSG_FIRSTHDR(&msg);
-    if (!c || c->cmsg_level != SOL_SOCKET || c->cmsg_type != SCM_RIGHTS) return HCCL_E_SYSCALL;
+    if (!c || c->cmsg_level != SOL_SOCKET || c->cmsg_type != SCM_RIGHTS) {
+        *fdOut = -1;              // a message without a descriptor (the ring monitor's pings)
+        return HCCL_SUCCESS;
+    }
     memcpy(fdOut, CMSG_DATA(c), sizeof(int));
     return HCCL_SUCCESS;
 }

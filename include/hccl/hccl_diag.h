@@ -47,8 +47,13 @@ HcclResult HcclDiagGetOpCounters(HcclComm comm, uint64_t *launched, uint64_t *he
 HcclResult HcclDiagGetKernelTimes(HcclComm comm, uint64_t *startNs, uint64_t *endNs, uint32_t capacity, uint32_t *written);
 HcclResult HcclDiagGetWaitStatus(HcclComm comm, HcclDeviceWaitStatus *status);
 HcclResult HcclDiagClearWaitStatus(HcclComm comm);
-/* rank -> milliseconds since its last heartbeat (UINT64_MAX: never seen); lostMask bit r = LOST. */
+/* rank -> milliseconds since its last heartbeat (UINT64_MAX: never seen); lostMask bit r = LOST.  The mask joins
+ * what the control plane's hub reports with what the ring monitor found (each rank pings its nearest live
+ * neighbours and passes on the losses it knows of), so it keeps growing after the hub's own process is gone. */
 HcclResult HcclDiagGetHeartbeat(HcclComm comm, uint64_t *ageMs, uint32_t capacity, uint64_t *lostMask);
+/* Stops this rank's heartbeat thread: to the others it looks like a rank that hangs (its sockets stay open).  For
+ * tests of the lost-rank paths; the thread is not started again. */
+HcclResult HcclDiagPauseHeartbeat(HcclComm comm);
 HcclResult HcclDiagSetProfiling(HcclComm comm, int enable);
 /* Human-readable dump of the newest operator records and the wait status. */
 HcclResult HcclDiagDump(HcclComm comm, char *buf, uint32_t bufLen);

@@ -601,6 +601,69 @@ def main():
         err = comm.async_error()
         print(f"rank {rank}: async error {err}", flush=True)
         return 0 if err == 21 else 3
+    elif scenario == "ring_monitor":
+        # Five ranks watch each other in a ring.  The hub's process (rank 0) vanishes, then rank 2; the ranks that are
+        # left learn of both without the hub, rank 4 (no neighbour of rank 2) from what its neighbours pass on.  Rank 3
+        # then leaves in good order and is not taken for lost.
+        import ctypes
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+        assert world == 5
+        comm.all_reduce(np.ones(10, np.float32))
+
+        def lost_mask():
+            lost = ctypes.c_uint64()
+            assert lib.HcclDiagGetHeartbeat(ctypes.c_void_p(comm.handle), None, ctypes.c_uint32(0), ctypes.byref(lost)) == 0
+            return lost.value
+
+        def wait_for(bits, seconds):
+            deadline = time.time() + seconds
+            while lost_mask() & bits != bits and time.time() < deadline:
+                time.sleep(0.05)
+            return lost_mask()
+
+        if rank == 0:
+            os._exit(0)
+        seen = wait_for(0b00001, 15)
+        print(f"rank {rank}: lost after the hub went {seen:#x}", flush=True)
+        if seen != 0b00001:
+            return 3
+        time.sleep(1.0)                   # every survivor has seen the first loss before the second one happens
+        if rank == 2:
+            os._exit(0)
+        seen = wait_for(0b00101, 15)
+        print(f"rank {rank}: lost after rank 2 went {seen:#x}", flush=True)
+        if seen != 0b00101:
+            return 4
+        time.sleep(1.0)
+        if rank == 3:
+            comm.destroy()                # says goodbye round the ring
+            return 0
+        time.sleep(2.0)                   # many intervals: a rank taken for lost would show by now
+        seen = lost_mask()
+        print(f"rank {rank}: lost after rank 3 left in good order {seen:#x}", flush=True)
+        return 0 if seen == 0b00101 and comm.async_error() == 21 else 5
+    elif scenario == "silent_rank":
+        # A rank that hangs: its process and sockets stay, only its heartbeats stop.  The others mark it lost after the
+        # silence limit, by the hub's count and by the ring's.
+        import ctypes
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+        comm.all_reduce(np.ones(10, np.float32))
+        silent = world - 1
+        if rank == silent:
+            assert lib.HcclDiagPauseHeartbeat(ctypes.c_void_p(comm.handle)) == 0
+            time.sleep(6.0)
+            os._exit(0)
+        lost = ctypes.c_uint64()
+        deadline = time.time() + 15
+        while time.time() < deadline:
+            assert lib.HcclDiagGetHeartbeat(ctypes.c_void_p(comm.handle), None, ctypes.c_uint32(0), ctypes.byref(lost)) == 0
+            if lost.value:
+                break
+            time.sleep(0.05)
+        print(f"rank {rank}: lost {lost.value:#x}, async error {comm.async_error()}", flush=True)
+        return 0 if lost.value == 1 << silent and comm.async_error() == 21 else 3
     comm.destroy()
     print(f"rank {rank}: ok", flush=True)
     return 0

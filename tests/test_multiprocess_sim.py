@@ -27,6 +27,19 @@ def test_exit_of_the_rank_that_hosts_the_hub_is_reported_too():
     assert codes[1] == 0 and codes[2] == 0, "\n".join(outs)
 
 
+def test_ring_monitor_reports_losses_after_the_hub_is_gone():
+    env = {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCCL_HEARTBEAT_INTERVAL_MS": "100", "HCCL_HEARTBEAT_LOST_MS": "5000"}
+    codes, outs = launch("ring_monitor", 5, env, timeout=120)
+    assert codes[1] == 0 and codes[3] == 0 and codes[4] == 0, "\n".join(outs)
+    assert "lost after rank 2 went 0x5" in outs[4], outs[4]
+
+
+def test_rank_that_falls_silent_is_marked_lost():
+    env = {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCCL_HEARTBEAT_INTERVAL_MS": "100", "HCCL_HEARTBEAT_LOST_MS": "1500"}
+    codes, outs = launch("silent_rank", 3, env, timeout=120)
+    assert codes[0] == 0 and codes[1] == 0, "\n".join(outs)
+
+
 def test_torch_backend_operators_on_the_simulator():
     codes, outs = launch("torch_ops", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "2", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "29641"}, timeout=240)
     assert codes == [0, 0, 0], "\n".join(outs)

@@ -22,6 +22,11 @@ SCENARIOS = [
     ("hcom", 3, {}),
     ("op_retry", 3, {"HCCL_OP_RETRY_ENABLE": "1", "HCCL_OP_RETRY_PARAMS": "MaxCnt:2,HoldTime:300,IntervalTime:100", "HCCL_EXEC_TIMEOUT": "6"}),
 ]
+# the heartbeat thread and the ring monitor beside the descriptor-accept thread, with ranks that vanish or fall silent
+MONITOR_SCENARIOS = [
+    ("ring_monitor", 5, {"HCCL_HEARTBEAT_INTERVAL_MS": "100", "HCCL_HEARTBEAT_LOST_MS": "8000"}),
+    ("silent_rank", 3, {"HCCL_HEARTBEAT_INTERVAL_MS": "100", "HCCL_HEARTBEAT_LOST_MS": "1500"}),
+]
 
 
 def _asan_env(extra=None):
@@ -35,7 +40,7 @@ def _asan_env(extra=None):
 
 
 @needs_asan
-@pytest.mark.parametrize("scenario,world,extra", SCENARIOS)
+@pytest.mark.parametrize("scenario,world,extra", SCENARIOS + MONITOR_SCENARIOS)
 def test_simulator_scenarios_are_clean_under_address_sanitizer(scenario, world, extra):
     codes, outs = launch(scenario, world, _asan_env(extra), timeout=300)
     text = "\n".join(outs)
@@ -54,7 +59,7 @@ def _tsan_env(extra=None):
 
 
 @needs_tsan
-@pytest.mark.parametrize("scenario,world,extra", SCENARIOS)
+@pytest.mark.parametrize("scenario,world,extra", SCENARIOS + MONITOR_SCENARIOS)
 def test_simulator_scenarios_have_no_data_race_under_thread_sanitizer(scenario, world, extra):
     # agents, reader threads, heartbeats, retry rounds and the simulator's stream workers all run in these scenarios
     codes, outs = launch(scenario, world, _tsan_env(extra), timeout=600)
