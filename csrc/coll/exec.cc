@@ -111,10 +111,17 @@ HcclResult ExecuteOnHost(Comm *c, const Schedule &s, const ExecArgs &a)
     uint64_t q = esz >= 16 ? 1 : 16 / esz;
     uint64_t chunk = cap / q * q;
     uint64_t passes = maxSlice == 0 ? 1 : (maxSlice + chunk - 1) / chunk;
+    // Collectives alternate between the two CCL halves, pass by pass: every rank runs the same collectives in the same
+    // order, so the ranks agree on the half without talking.  A send or receive involves two ranks only and must not
+    // advance that count (the ranks would disagree from then on, first of all the two partners when one of them has
+    // sent or received more often than the other).  It lands in the half that the next collective will use, which
+    // is idle: a rank that has finished collective k knows that every rank has entered k and so has finished k-1.  Its
+    // passes need no alternation, each one starts with the receiver's READY.
+    const bool pointToPoint = s.cmd == HCCL_CMD_SEND || s.cmd == HCCL_CMD_RECEIVE;
     for (uint64_t pass = 0; pass < passes; ++pass) {
         Walker w{c, s, a, esz, cap, pass * chunk, (pass + 1) * chunk, c->hostLaunches & 1u};
         CHK_RET(w.Run());
-        ++c->hostLaunches;
+        if (!pointToPoint) ++c->hostLaunches;
     }
     return HCCL_SUCCESS;
 }

@@ -521,7 +521,9 @@ HcclResult HostBatchSendRecv(Comm *c, const OpDesc &d)
     auto notify = [&](uint32_t owner, uint32_t from, uint32_t idx) {
         return (uint64_t *)(c->PeerHeap(owner) + HC_OFF_CHAN_NOTIFY) + (uint64_t)from * HC_CHAN_NOTIFY + idx;
     };
-    auto slot = [&](uint32_t owner, uint32_t from) { return c->PeerHeap(owner) + HC_CTRL_BYTES + (uint64_t)from * slotBytes; };
+    // landing slots in the CCL half that the next collective will use (idle now; see ExecuteOnHost)
+    const uint64_t halfOff = (uint64_t)(c->hostLaunches & 1u) * c->halfBytes;
+    auto slot = [&](uint32_t owner, uint32_t from) { return c->PeerHeap(owner) + HC_CTRL_BYTES + halfOff + (uint64_t)from * slotBytes; };
     auto wait = [&](uint32_t peer, uint32_t idx) -> HcclResult {
         uint64_t &w = c->chanWaited[(size_t)peer * HC_CHAN_NOTIFY + idx];
         ++w;

@@ -87,7 +87,7 @@ class HcclSendRecvItem(ctypes.Structure):
 def lib_path() -> Path:
     # HCOMM_LIBRARY=bounds selects the bounds-checking build, HCOMM_LIBRARY=asan the AddressSanitizer build of the host runtime
     # (hcomm_b200.build.build_core(bounds=True) / (asan=True))
-    name = {"bounds": "libhcomm_bounds.so", "asan": "libhcomm_asan.so", "tsan": "libhcomm_tsan.so", "ubsan": "libhcomm_ubsan.so"}.get(os.environ.get("HCOMM_LIBRARY", ""), "libhcomm.so")
+    name = {"bounds": "libhcomm_bounds.so", "asan": "libhcomm_asan.so", "tsan": "libhcomm_tsan.so", "ubsan": "libhcomm_ubsan.so", "cov": "libhcomm_cov.so"}.get(os.environ.get("HCOMM_LIBRARY", ""), "libhcomm.so")
     return Path(__file__).resolve().parent / "lib" / name
 
 
@@ -100,7 +100,8 @@ def load() -> ctypes.CDLL:
     if not path.exists() or os.environ.get("HCOMM_REBUILD") == "1":
         from . import build
         build.build_core(bounds=os.environ.get("HCOMM_LIBRARY") == "bounds", asan=os.environ.get("HCOMM_LIBRARY") == "asan",
-                         tsan=os.environ.get("HCOMM_LIBRARY") == "tsan", ubsan=os.environ.get("HCOMM_LIBRARY") == "ubsan")
+                         tsan=os.environ.get("HCOMM_LIBRARY") == "tsan", ubsan=os.environ.get("HCOMM_LIBRARY") == "ubsan",
+                         cov=os.environ.get("HCOMM_LIBRARY") == "cov")
     _LIB = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
     _LIB.HcclGetErrorString.restype = ctypes.c_char_p
     return _LIB

@@ -64,6 +64,7 @@ def _obj_for(src: Path, variant: str = "") -> Path:
 ASAN_HOST_FLAGS = ["-fsanitize=address", "-fno-omit-frame-pointer", "-g"]
 TSAN_HOST_FLAGS = ["-fsanitize=thread", "-fno-omit-frame-pointer", "-g"]
 UBSAN_HOST_FLAGS = ["-fsanitize=undefined", "-fno-sanitize-recover=undefined", "-fno-omit-frame-pointer", "-g"]
+COV_HOST_FLAGS = ["--coverage", "-O0", "-g", "-fprofile-update=atomic"]      # gcov counters, updated atomically (many threads)
 
 
 def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=(), variant: str = "", defines=()) -> Path:
@@ -71,7 +72,7 @@ def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=(), variant:
     obj.parent.mkdir(parents=True, exist_ok=True)
     if obj.exists() and obj.stat().st_mtime >= max(src.stat().st_mtime, hdr_mtime):
         return obj
-    san = {"asan": ASAN_HOST_FLAGS, "tsan": TSAN_HOST_FLAGS, "ubsan": UBSAN_HOST_FLAGS}.get(variant, [])
+    san = {"asan": ASAN_HOST_FLAGS, "tsan": TSAN_HOST_FLAGS, "ubsan": UBSAN_HOST_FLAGS, "cov": COV_HOST_FLAGS}.get(variant, [])
     if src.suffix == ".cu":
         host = ["-Xcompiler", ",".join(san)] if san else []       # host side of the file only; device code has no such tool
         cmd = [NVCC, *NVCC_FLAGS, *extra_nvcc, *host, *defines, "-c", str(src), "-o", str(obj)]
@@ -87,7 +88,8 @@ def _compile(src: Path, hdr_mtime: float, verbose: bool, extra_nvcc=(), variant:
     return obj
 
 
-def build_core(verbose: bool = False, jobs: int | None = None, bounds: bool = False, asan: bool = False, tsan: bool = False, ubsan: bool = False) -> Path:
+def build_core(verbose: bool = False, jobs: int | None = None, bounds: bool = False, asan: bool = False, tsan: bool = False, ubsan: bool = False,
+               cov: bool = False) -> Path:
     """Builds ``libhcomm.so`` and returns its path.
 
     ``asan=True`` builds ``libhcomm_asan.so``: the host runtime (and the host side of the ``.cu`` files) compiled with
@@ -96,23 +98,28 @@ def build_core(verbose: bool = False, jobs: int | None = None, bounds: bool = Fa
     the simulator platform (``HCCL_SIM=1``) then runs the control plane, the host engine and the schedule interpreter under it.
     ``tsan=True`` builds ``libhcomm_tsan.so`` the same way with ThreadSanitizer (``HCOMM_LIBRARY=tsan``, preload ``libtsan.so``).
 
+    ``cov=True`` builds ``libhcomm_cov.so`` with gcov counters in the host code (``HCOMM_LIBRARY=cov``); the counters
+    land beside the objects in ``build/obj-cov`` when a process exits, and ``python -m hcomm_b200.utils.coverage`` runs
+    the CPU tests on that library and prints line coverage per source file.
+
     ``bounds=True`` builds ``libhcomm_bounds.so`` instead: the same library compiled with ``-DHCOMM_DEBUG_BOUNDS``, in
     which every grid copy and reduction of the collective kernels checks its address ranges against the symmetric heap
     and the CCL halves and records a violation in the status block instead of touching memory out of range.  Select it
     at run time with ``HCOMM_LIBRARY=bounds``."""
     LIBDIR.mkdir(parents=True, exist_ok=True)
-    out = LIBDIR / ("libhcomm_bounds.so" if bounds else ("libhcomm_asan.so" if asan else ("libhcomm_tsan.so" if tsan else ("libhcomm_ubsan.so" if ubsan else "libhcomm.so"))))
+    variant = "bounds" if bounds else "asan" if asan else "tsan" if tsan else "ubsan" if ubsan else "cov" if cov else ""
+    out = LIBDIR / ("libhcomm_" + variant + ".so" if variant else "libhcomm.so")
     srcs = _core_sources()
     hdr = _headers_mtime()
     jobs = jobs or min(8, os.cpu_count() or 4)
-    variant, defines = ("bounds", ("-DHCOMM_DEBUG_BOUNDS",)) if bounds else (("asan", ()) if asan else (("tsan", ()) if tsan else (("ubsan", ()) if ubsan else ("", ()))))
+    defines = ("-DHCOMM_DEBUG_BOUNDS",) if bounds else ()
     with ThreadPoolExecutor(max_workers=jobs) as ex:
         objs = list(ex.map(lambda s: _compile(s, hdr, verbose, variant=variant, defines=defines), srcs))
     newest_obj = max(o.stat().st_mtime for o in objs)
     if out.exists() and out.stat().st_mtime >= newest_obj:
         return out
     link = ["g++", "-shared", "-o", str(out), *map(str, objs), f"-L{CUDA_HOME / 'lib64'}", "-lcudart_static",
-            "-lpthread", "-ldl", "-lrt"] + (["-fsanitize=address"] if asan else (["-fsanitize=thread"] if tsan else (["-fsanitize=undefined"] if ubsan else ["-Wl,--no-undefined"])))
+            "-lpthread", "-ldl", "-lrt"] + (["-fsanitize=address"] if asan else ["-fsanitize=thread"] if tsan else ["-fsanitize=undefined"] if ubsan else ["--coverage"] if cov else ["-Wl,--no-undefined"])
     if verbose:
         print(" ".join(link), flush=True)
     res = subprocess.run(link, capture_output=True, text=True)
@@ -191,4 +198,6 @@ if __name__ == "__main__":
         build_core(verbose="-v" in sys.argv, tsan=True)
     if "--ubsan" in sys.argv:
         build_core(verbose="-v" in sys.argv, ubsan=True)
+    if "--cov" in sys.argv:
+        build_core(verbose="-v" in sys.argv, cov=True)
     print("built:", *sorted(p.name for p in LIBDIR.glob("*.so")))

@@ -418,6 +418,122 @@ def main():
         manage.destroy_world_group()
         stage("hcom ok")
         return 0        # the world group adopted and released the communicator
+    elif scenario == "hcom_ops":
+        # every operator and query that is addressed by group name, on the world group and on a sub group
+        import ctypes
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+        V, U64, U32 = ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint32
+        P = lambda a: a.ctypes.data_as(V)                                     # noqa: E731
+        FP32, I32, U64T, SUM, MAX = 4, 2, 6, 0, 2
+        W = b"hccl_world_group"
+        started = ctypes.c_bool(True)
+        assert lib.HcomGetInitStatus(ctypes.byref(started)) == 0 and not started.value
+        assert lib.HcomInitByComm(V(comm.handle)) == 0
+        assert lib.HcomInitByComm(V(comm.handle)) == 1                        # twice: HCCL_E_PARA
+        assert lib.HcomGetInitStatus(ctypes.byref(started)) == 0 and started.value
+        handle = V()
+        assert lib.HcomGetCommHandleByGroup(W, ctypes.byref(handle)) == 0 and handle.value == comm.handle
+        assert lib.HcomGetCommHandleByGroup(b"no_such_group", ctypes.byref(handle)) == 6       # HCCL_E_NOT_FOUND
+        # buffers and constants of the world group
+        buf_in, buf_out, size_in, size_out, half = V(), V(), U64(), U64(), U64()
+        assert lib.HcomGetInCCLbuffer(W, ctypes.byref(buf_in), ctypes.byref(size_in)) == 0
+        assert lib.HcomGetOutCCLbuffer(W, ctypes.byref(buf_out), ctypes.byref(size_out)) == 0
+        assert lib.HcomGetCommCCLBufferSize(W, ctypes.byref(half)) == 0
+        assert size_in.value == size_out.value == half.value == 1 << 20 and buf_out.value == buf_in.value + half.value
+        bw = ctypes.c_float()
+        assert lib.HcomGetBandWidthPerNPU(U32(0), ctypes.byref(bw)) == 0 and bw.value == 900.0
+        assert lib.HcomGetBandWidthPerNPU(U32(3), ctypes.byref(bw)) == 1
+        servers, per_server, per_agg = U32(), U32(), U32()
+        assert lib.HcomGetServerNumAndDeviceNumPerServer(ctypes.byref(servers), ctypes.byref(per_server), ctypes.byref(per_agg)) == 0
+        assert servers.value == 1 and per_server.value == world and per_agg.value == world
+        algo = ctypes.c_char_p()
+        assert lib.HcomGetAlgorithm(U32(0), ctypes.byref(algo)) == 0 and algo.value == b"fullmesh"
+        assert lib.HcomGetAlgorithm(U32(1), ctypes.byref(algo)) == 0 and algo.value == b"NA"
+        topo = ctypes.c_int(-1)
+        assert lib.HcomGetL0TopoTypeEx(W, ctypes.byref(topo), U32(0)) == 0 and topo.value >= 0
+        det = ctypes.c_bool(False)
+        assert lib.HcomSupportDeterministicOptim(W, ctypes.byref(det)) == 0 and det.value
+        # a sub group of the first world-1 ranks; the last rank stays outside
+        members = list(range(world - 1))
+        inside = rank in members
+        G = b"front"
+        if inside:
+            ids = (U32 * len(members))(*members)
+            assert lib.HcomCreateGroup(G, U32(len(members)), ids) == 0
+        for group, ranks in ((W, list(range(world))), (G, members)):
+            if rank not in ranks:
+                continue
+            n, me = len(ranks), ranks.index(rank)
+            x = (np.arange(n * 8, dtype=np.float32) + 100 * rank)
+            # all-gather
+            out = np.zeros(n * 8 * n, np.float32)
+            assert lib.HcomAllGather(b"t", P(x), P(out), U64(x.size), FP32, group, None) == 0
+            want = np.concatenate([np.arange(n * 8, dtype=np.float32) + 100 * r for r in ranks])
+            assert (out == want).all()
+            # reduce-scatter
+            out = np.zeros(8, np.float32)
+            assert lib.HcomReduceScatter(b"t", P(x), P(out), U64(8), FP32, SUM, group, None) == 0
+            total = sum(np.arange(n * 8, dtype=np.float32) + 100 * r for r in ranks)
+            assert (out == total[me * 8:(me + 1) * 8]).all()
+            # broadcast from the last rank of the group, reduce (max) to rank 0 of the group
+            b = x.copy() if me == n - 1 else np.zeros_like(x)
+            assert lib.HcomBroadcast(b"t", P(b), U64(b.size), FP32, U32(n - 1), group, None) == 0
+            assert (b == np.arange(n * 8, dtype=np.float32) + 100 * ranks[-1]).all()
+            out = np.zeros_like(x)
+            assert lib.HcomReduce(b"t", P(x), P(out), U64(x.size), FP32, MAX, U32(0), group, None) == 0
+            if me == 0:
+                assert (out == np.arange(n * 8, dtype=np.float32) + 100 * ranks[-1]).all()
+            # send / receive round the ring of the group: even positions send first
+            if n > 1:
+                got = np.zeros(5, np.int32)
+                msg = np.full(5, rank, np.int32)
+                right, left = (me + 1) % n, (me - 1) % n
+                if me % 2 == 0:
+                    assert lib.HcomSend(b"t", P(msg), U64(5), I32, U32(right), U32(0), group, None) == 0
+                    assert lib.HcomReceive(b"t", P(got), U64(5), I32, U32(left), U32(0), group, None) == 0
+                else:
+                    assert lib.HcomReceive(b"t", P(got), U64(5), I32, U32(left), U32(0), group, None) == 0
+                    assert lib.HcomSend(b"t", P(msg), U64(5), I32, U32(right), U32(0), group, None) == 0
+                assert (got == ranks[left]).all(), (group, me, got)
+            # all-to-all: block j of rank i is i*1000+j
+            a = np.repeat(np.arange(n, dtype=np.float32) + 1000 * rank, 4)
+            out = np.zeros_like(a)
+            assert lib.HcomAllToAll(P(a), U64(4), FP32, P(out), U64(4), FP32, group, None, b"t") == 0
+            assert (out == np.repeat(np.array([1000 * r + me for r in ranks], np.float32), 4)).all()
+            # all-to-all with per-peer counts: rank i sends i+1 elements to everybody
+            cnt = me + 1
+            sc = np.full(n, cnt, np.uint64)
+            sd = np.arange(n, dtype=np.uint64) * cnt
+            rc_ = np.arange(1, n + 1, dtype=np.uint64)
+            rd = np.concatenate([[0], np.cumsum(rc_)[:-1]]).astype(np.uint64)
+            a = np.full(n * cnt, rank, np.float32)
+            out = np.zeros(int(rc_.sum()), np.float32)
+            assert lib.HcomAlltoAllV(P(a), P(sc), P(sd), FP32, P(out), P(rc_), P(rd), FP32, group, None, b"t") == 0
+            assert (out == np.concatenate([np.full(i + 1, ranks[i], np.float32) for i in range(n)])).all()
+            # the same exchange described by the full count matrix
+            matrix = np.repeat(np.arange(1, n + 1, dtype=np.uint64), n).reshape(n, n)      # row i: what rank i sends to each
+            out = np.zeros(int(rc_.sum()), np.float32)
+            assert lib.HcomAlltoAllVC(P(a), P(matrix), FP32, P(out), FP32, group, None, b"t") == 0
+            assert (out == np.concatenate([np.full(i + 1, ranks[i], np.float32) for i in range(n)])).all()
+            # all-gather with per-rank counts (rank i contributes i+1 elements)
+            mine = np.full(me + 1, rank, np.float32)
+            out = np.zeros(int(rc_.sum()), np.float32)
+            assert lib.HcomAllGatherV(b"t", P(mine), U64(me + 1), P(out), P(rc_), P(rd), FP32, group, None) == 0
+            assert (out == np.concatenate([np.full(i + 1, ranks[i], np.float32) for i in range(n)])).all()
+            # reduce-scatter with per-rank counts (rank i receives i+1 elements)
+            full = np.arange(int(rc_.sum()), dtype=np.float32) + rank
+            out = np.zeros(me + 1, np.float32)
+            assert lib.HcomReduceScatterV(b"t", P(full), P(rc_), P(rd), P(out), U64(me + 1), FP32, SUM, group, None) == 0
+            want = sum(np.arange(int(rc_.sum()), dtype=np.float32) + r for r in ranks)[int(rd[me]):int(rd[me]) + me + 1]
+            assert (out == want).all()
+        if inside:
+            assert lib.HcomDestroyGroup(G) == 0
+            assert lib.HcomDestroyGroup(G) == 6
+        comm.barrier()
+        assert lib.HcomDestroy() == 0
+        stage("hcom operators ok")
+        return 0        # the world group adopted and released the communicator
     elif scenario == "lifecycle":
         # suspend / resume, snapshot, diagnostics
         import ctypes

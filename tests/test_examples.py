@@ -30,8 +30,10 @@ def library():
 @pytest.mark.parametrize("src,args", EXAMPLES)
 def test_example_runs_on_the_simulator(src, args, library, tmp_path):
     exe = tmp_path / (Path(src).stem + "_" + "_".join(args))
+    # HCOMM_LIBRARY=cov (the coverage run of hcomm_b200.utils.coverage) links the examples to that build of the library
+    name = "hcomm_cov" if os.environ.get("HCOMM_LIBRARY") == "cov" else "hcomm"
     cmd = ["g++", "-std=c++17", "-O1", "-pthread", f"-I{ROOT / 'include'}", str(ROOT / "examples" / src), "-o", str(exe),
-           f"-L{library}", "-lhcomm", f"-Wl,-rpath,{library}"]
+           f"-L{library}", "-l" + name, f"-Wl,-rpath,{library}"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-4000:]
     env = dict(os.environ, HCCL_SIM="1", HCCL_BUFFSIZE="2", HCCL_EXEC_TIMEOUT="20")

@@ -55,6 +55,11 @@ def test_named_groups_and_gradient_split_through_the_python_package():
     assert codes == [0, 0, 0, 0], "\n".join(outs)
 
 
+def test_operators_and_queries_addressed_by_group_name():
+    codes, outs = launch("hcom_ops", 4, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=120)
+    assert codes == [0, 0, 0, 0], "\n".join(outs)
+
+
 def test_suspend_resume_snapshot_and_diagnostics():
     codes, outs = launch("lifecycle", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=120)
     assert codes == [0, 0, 0], "\n".join(outs)

@@ -136,6 +136,47 @@ def test_alltoallvc_and_batch_send_recv(monkeypatch):
     destroy(comms)
 
 
+def test_sends_between_two_ranks_leave_the_collectives_of_all_ranks_intact(monkeypatch):
+    """Point-to-point operators involve two ranks; the others do not count them.  Collectives before, between and after
+    them must still meet in the same half of the communication buffer on every rank, and a rank that sends before it
+    receives must meet a partner that has done neither yet."""
+    sim_env(monkeypatch, buffsize=1)
+    n = 3
+    comms = make_comms(n)
+    x = [np.arange(3000, dtype=np.float32) + 10 * r for r in range(n)]
+    want = sum(x)
+    big = np.arange(700_000, dtype=np.int32)        # larger than one landing slot: several passes
+    out = [dict() for _ in range(n)]
+
+    def body(r):
+        c = comms[r]
+        out[r]["a"] = c.all_reduce(x[r], np.zeros_like(x[r]))
+        if r == 0:                                   # one message 0 -> 1: rank 2 knows nothing of it
+            c.send(big, 1)
+        elif r == 1:
+            out[r]["big"] = c.recv(np.zeros_like(big), 0)
+        out[r]["b"] = c.all_reduce(x[r], np.zeros_like(x[r]))
+        # a ring in which ranks 0 and 2 send first and rank 1 receives first
+        msg, got = np.full(100, r, np.int32), np.zeros(100, np.int32)
+        if r % 2 == 0:
+            c.send(msg, (r + 1) % n)
+            c.recv(got, (r - 1) % n)
+        else:
+            c.recv(got, (r - 1) % n)
+            c.send(msg, (r + 1) % n)
+        out[r]["ring"] = got
+        out[r]["c"] = c.all_reduce(x[r], np.zeros_like(x[r]))
+        out[r]["g"] = c.all_gather(x[r], np.zeros(n * 3000, np.float32))
+    run_ranks(n, body)
+    for r in range(n):
+        for key in "abc":
+            assert np.array_equal(out[r][key], want), (r, key)
+        assert np.array_equal(out[r]["g"], np.concatenate(x))
+        assert (out[r]["ring"] == (r - 1) % n).all(), (r, out[r]["ring"][:4])
+    assert np.array_equal(out[1]["big"], big)
+    destroy(comms)
+
+
 def test_sub_communicator_and_argument_checks(monkeypatch):
     sim_env(monkeypatch)
     from hcomm_b200 import HcclError
