@@ -287,7 +287,8 @@ HcclResult HcclSetConfig(HcclConfig config, union HcclConfigValue configValue)
     if (config != HCCL_DETERMINISTIC) return HCCL_E_NOT_SUPPORT;
     if (configValue.value < 0 || configValue.value > 2) return HCCL_E_PARA;
     g_processDeterministic.store(configValue.value);
-    RegistryForEach([&](Comm *c) { c->cfg.deterministic = (uint32_t)configValue.value; });
+    // operators of other threads may be reading the setting right now
+    RegistryForEach([&](Comm *c) { __atomic_store_n(&c->cfg.deterministic, (uint32_t)configValue.value, __ATOMIC_RELAXED); });
     return HCCL_SUCCESS;
 }
 

@@ -224,7 +224,7 @@ HcclResult FastAllReduce(Comm *c, const OpDesc &d, const Selection &sel)
     // in-switch reduction straight from the registered input into the registered output: no staging, any size
     const bool nvlsTypes = d.op == HCCL_REDUCE_SUM && (d.dtype == HCCL_DATA_TYPE_FP32 || d.dtype == HCCL_DATA_TYPE_FP16 || d.dtype == HCCL_DATA_TYPE_BFP16);
     // (up to 4 GPUs the mesh kernels measured faster than in-switch reduction, registered or not)
-    if (c->mcBase && n > 4 && nvlsTypes && c->cfg.deterministic == 0 && sel.reason != "forced by configuration" && d.count * esz >= 64 * 1024 &&
+    if (c->mcBase && n > 4 && nvlsTypes && __atomic_load_n(&c->cfg.deterministic, __ATOMIC_RELAXED) == 0 && sel.reason != "forced by configuration" && d.count * esz >= 64 * 1024 &&
         RegisteredInput(c, d.in, d.count * esz, a, true)) {
         a.outMc = RegisteredOutputMc(c, d.out, d.count * esz);
         if (a.outMc) return Launch(c, FK_ALLREDUCE_NVLS, a, PickCtas(c, sel, d.count * esz), d.stream);
@@ -299,7 +299,7 @@ HcclResult FastReduceScatter(Comm *c, const OpDesc &d, const Selection &sel)
     const uint64_t moved = std::min(cap, maxCnt) * esz * std::max(1u, n - 1);       // bytes this rank moves per window
     const bool vectors = uniform && (d.count * esz) % 16 == 0 && (((uintptr_t)d.in | (uintptr_t)d.out) & 15) == 0;
     const bool nvlsTypes = d.op == HCCL_REDUCE_SUM && (d.dtype == HCCL_DATA_TYPE_FP32 || d.dtype == HCCL_DATA_TYPE_FP16 || d.dtype == HCCL_DATA_TYPE_BFP16);
-    const bool nvls = sel.engine == Engine::NVLS && c->mcBase && vectors && nvlsTypes && c->cfg.deterministic == 0;
+    const bool nvls = sel.engine == Engine::NVLS && c->mcBase && vectors && nvlsTypes && __atomic_load_n(&c->cfg.deterministic, __ATOMIC_RELAXED) == 0;
     if (uniform && sel.reason != "forced by configuration" && d.count * esz >= 16 * 1024 && RegisteredInput(c, d.in, (uint64_t)n * d.count * esz, a, false)) {
         // registered input: pull the peers' blocks in place (through the switch when the window has a multicast alias)
         if (a.inMc && nvls) return Launch(c, FK_REDUCE_SCATTER_NVLS, a, PickCtas(c, sel, moved), d.stream);
@@ -733,7 +733,7 @@ HcclResult RunOpLocked(Comm *c, const OpDesc &d)
     si.cmd = d.cmd; si.nRanks = c->nRanks; si.dtype = d.dtype; si.op = d.op;
     si.bytes = d.count * esz;
     si.opExpansionMode = c->cfg.opExpansionMode;
-    si.deterministic = c->cfg.deterministic;
+    si.deterministic = __atomic_load_n(&c->cfg.deterministic, __ATOMIC_RELAXED);
     si.cuda = cuda;
     si.singleDomain = c->nRanks <= HC_KERNEL_MAX_RANKS && c->graph.SingleNvlinkDomain();
     si.nvlsAvailable = c->mcBase != nullptr;

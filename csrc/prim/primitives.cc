@@ -10,8 +10,10 @@
 //   task cache  between TaskCacheStart/End verbs are recorded under a tag with their pointer
 //               arguments expressed relative to the caller's address table; TaskCacheExecute replays
 //               the list with a new table (the role the reference's AICPU task cache plays)
+#include <atomic>
 #include <cstring>
 #include <map>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -58,7 +60,7 @@ struct Op {
     uint64_t dstOff = 0, srcOff = 0;
 };
 
-float g_defaultWaitTimeout = 0.0f;   // seconds; 0 = communicator exec timeout
+std::atomic<float> g_defaultWaitTimeout{0.0f};   // seconds; 0 = communicator exec timeout
 std::mutex g_mu;
 
 struct Recording {
@@ -74,7 +76,8 @@ std::map<std::string, Recording> g_taskCache;
 uint32_t TimeoutMs(const Op &op)
 {
     if (op.timeoutSec) return op.timeoutSec * 1000u;
-    if (g_defaultWaitTimeout > 0) return (uint32_t)(g_defaultWaitTimeout * 1000.0f);
+    const float dflt = g_defaultWaitTimeout.load(std::memory_order_relaxed);
+    if (dflt > 0) return (uint32_t)(dflt * 1000.0f);
     Comm *c = op.thread ? op.thread->comm : (op.chan ? op.chan->comm : nullptr);
     return c ? c->TimeoutMs() : 1836000u;
 }
@@ -122,8 +125,11 @@ HcclResult Submit(const Op &op)
             rep.kind = HC_WAIT_THREAD_NOTIFY; rep.slot = 0xffff;
             uint64_t *w = (uint64_t *)(uintptr_t)op.rawId;
             static std::map<uint64_t, uint64_t> waited;
-            std::lock_guard<std::mutex> lk(g_mu);
-            uint64_t expect = ++waited[op.rawId];
+            uint64_t expect;
+            {
+                std::lock_guard<std::mutex> lk(g_mu);        // the count only: the wait itself may block (simulator)
+                expect = ++waited[op.rawId];
+            }
             return P->FlagWaitGeAsync(w, expect, TimeoutMs(op), rep, s);
         }
     }
@@ -303,6 +309,17 @@ int32_t HcommReadReduceOnThread(ThreadHandle thread, ChannelHandle channel, void
 static ThreadRes *NbiThread(ChannelRes *ch)
 {
     Comm *c = ch->comm;
+    if (!c) {
+        // a base-level channel (no communicator): the side thread belongs to the channel and lives as long as the process
+        static std::map<ChannelRes *, std::unique_ptr<ThreadRes>> sides;
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = sides.find(ch);
+        if (it != sides.end()) return it->second.get();
+        std::unique_ptr<ThreadRes> t(new ThreadRes());
+        t->plat = ch->plat; t->engine = ch->engine;
+        if (ch->plat->kind() == PlatKind::CUDA) { if (ch->plat->StreamCreate(&t->stream) != HCCL_SUCCESS) return nullptr; t->ownsStream = true; }
+        return (sides[ch] = std::move(t)).get();
+    }
     std::lock_guard<std::mutex> lk(c->resMu);
     auto it = c->dedicatedThreads.find(1000 + (int)ch->remoteRank);
     if (it != c->dedicatedThreads.end()) return it->second;
@@ -401,7 +418,7 @@ int32_t HcommChannelNotifyWait(ChannelHandle channel, uint32_t localNotifyIdx, u
     int32_t r = HcommChannelNotifyWaitOnThread((ThreadHandle)(uintptr_t)t, channel, localNotifyIdx, timeOut);
     if (r) return r;
     if (t->stream) CHK_RET(t->plat->StreamSync(t->stream));   // the thread-less form is synchronous for the caller
-    return (int32_t)CommPollDeviceStatus(ch->comm);
+    return ch->comm ? (int32_t)CommPollDeviceStatus(ch->comm) : HCCL_SUCCESS;
 }
 
 int32_t HcommThreadSynchronize(ThreadHandle thread)
@@ -449,13 +466,13 @@ int32_t HcommChannelDrainOnThread(ThreadHandle thread, ChannelHandle channel)
     ThreadRes *s = NbiThread(ch);
     if (s && s->stream) CHK_RET(s->plat->StreamSync(s->stream));
     if (t->stream) CHK_RET(t->plat->StreamSync(t->stream));
-    return (int32_t)CommPollDeviceStatus(ch->comm);
+    return ch->comm ? (int32_t)CommPollDeviceStatus(ch->comm) : HCCL_SUCCESS;
 }
 
 int32_t HcommSetNotifyWaitTimeOut(float timeOut)
 {
     if (timeOut < 0) return HCCL_E_PARA;
-    g_defaultWaitTimeout = timeOut;
+    g_defaultWaitTimeout.store(timeOut, std::memory_order_relaxed);
     return HCCL_SUCCESS;
 }
 int32_t HcommThreadResAcquireTimeOut(float timeOut) { return timeOut < 0 ? HCCL_E_PARA : HCCL_SUCCESS; }

@@ -12,16 +12,19 @@ namespace hc {
 
 uint32_t Crc32(const void *data, size_t len, uint32_t seed)
 {
-    static uint32_t table[256];
-    static bool init = false;
-    if (!init) {
-        for (uint32_t i = 0; i < 256; ++i) {
-            uint32_t c = i;
-            for (int k = 0; k < 8; ++k) c = (c & 1) ? (0xEDB88320u ^ (c >> 1)) : (c >> 1);
-            table[i] = c;
+    struct Table {
+        uint32_t v[256];
+        Table()
+        {
+            for (uint32_t i = 0; i < 256; ++i) {
+                uint32_t c = i;
+                for (int k = 0; k < 8; ++k) c = (c & 1) ? (0xEDB88320u ^ (c >> 1)) : (c >> 1);
+                v[i] = c;
+            }
         }
-        init = true;
-    }
+    };
+    static const Table built;                 // built once, also when several ranks of a process get here together
+    const uint32_t *table = built.v;
     uint32_t c = ~seed;
     const uint8_t *p = (const uint8_t *)data;
     for (size_t i = 0; i < len; ++i) c = table[(c ^ p[i]) & 0xff] ^ (c >> 8);

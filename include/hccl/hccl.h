@@ -51,9 +51,11 @@ HcclResult HcclReduce(void *sendBuf, void *recvBuf, uint64_t count, HcclDataType
                       uint32_t root, HcclComm comm, aclrtStream stream);
 
 /*
- * B200 extension: AllReduce with the reduction fused with a scale and a dtype cast.
- * recv[i] = cast<outType>( scale * sum_r send_r[i] ); accumulation is fp32.  Used by the
- * data-parallel gradient hook (divide by world size and keep bf16) without a second kernel.
+ * B200 extension: AllReduce with a scale fused into the reduction.
+ * recv[i] = scale * sum_r send_r[i]; the sum and the product are formed in fp32 and rounded once to the
+ * operand type.  inType and outType must be the same floating-point type (fp16, bf16, fp32, fp64); a
+ * conversion on the way is not offered.  Used by the data-parallel gradient hook (divide by the world
+ * size and keep bf16) without a second kernel.
  */
 HcclResult HcclAllReduceScaled(void *sendBuf, void *recvBuf, uint64_t count, HcclDataType inType,
                                HcclDataType outType, float scale, HcclComm comm, aclrtStream stream);

@@ -3,6 +3,7 @@
 
 Skipped when the library has not been built.  Every scenario runs as separate processes with the sanitizer's runtime
 preloaded; an address report of any kind, or a data race, fails the test."""
+import os
 import subprocess
 from pathlib import Path
 
@@ -80,3 +81,36 @@ def test_simulator_scenarios_have_no_undefined_behaviour(scenario, world, extra)
     text = "\n".join(outs)
     assert "runtime error" not in text, text[-4000:]
     assert codes == [0] * world, text[-4000:]
+
+
+def _build_sweep(tmp_path, variant):
+    """tests/api_sweep.cc linked against a sanitizer build of the library (with ThreadSanitizer the program is instrumented too)."""
+    root = LIBDIR.parent.parent
+    exe = tmp_path / ("api_sweep_" + variant)
+    extra = ["-fsanitize=thread"] if variant == "tsan" else ["-Wl,--allow-shlib-undefined"]
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-pthread", f"-I{root / 'include'}", str(root / "tests" / "api_sweep.cc"), "-o", str(exe),
+           f"-L{LIBDIR}", "-lhcomm_" + variant, "-ldl", f"-Wl,-rpath,{LIBDIR}", *extra]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr[-6000:]
+    return exe
+
+
+@needs_asan
+def test_api_sweep_is_clean_under_address_sanitizer(tmp_path):
+    exe = _build_sweep(tmp_path, "asan")
+    env = dict(os.environ, **_asan_env({"HCCL_BUFFSIZE": "2", "HCCL_EXEC_TIMEOUT": "60"}))
+    run = subprocess.run([str(exe), "4"], capture_output=True, text=True, env=env, timeout=300)
+    text = run.stdout + run.stderr
+    assert "AddressSanitizer" not in text, text[-6000:]
+    assert run.returncode == 0 and "4 ranks ok" in run.stdout, text[-4000:]
+
+
+@needs_tsan
+def test_api_sweep_has_no_data_race_under_thread_sanitizer(tmp_path):
+    # ranks are threads of one process here, so the registries, the control plane and the simulator's memory are shared
+    exe = _build_sweep(tmp_path, "tsan")
+    env = dict(os.environ, **_tsan_env({"HCCL_BUFFSIZE": "2", "HCCL_EXEC_TIMEOUT": "120"}))
+    run = subprocess.run([str(exe), "4"], capture_output=True, text=True, env=env, timeout=600)
+    text = run.stdout + run.stderr
+    assert "ThreadSanitizer: data race" not in text and "ThreadSanitizer: lock-order-inversion" not in text, text[-8000:]
+    assert run.returncode == 0 and "4 ranks ok" in run.stdout, text[-4000:]
