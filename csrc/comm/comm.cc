@@ -411,20 +411,76 @@ Comm::~Comm()
     if (abortWord) plat->HostFree(abortWord);
 }
 
-void CommDestroy(Comm *c)
+namespace {
+// Communicators whose HcclCommDestroy has returned although other ranks had not arrived yet (see CommDestroy); keyed by
+// rendezvous identifier and group.  They are freed by the rank of this process whose own barrier completes.
+std::mutex g_parkedMu;
+std::map<std::string, std::vector<Comm *>> g_parked;
+
+std::string FamilyKey(const Comm *c) { return c->identifier + "/" + std::to_string(c->group.id); }
+
+// Another rank of the same communicator lives in this process and has not entered its destroy yet.
+bool HasLiveSibling(const Comm *c)
 {
-    if (!c) return;
-    RetryTeardown(c);
-    RegistryRemove(c);
-    // Peers must stop touching my heap before it disappears.
-    if (c->boot && c->state.load() != (int)CommState::DESTROYED) c->boot->Barrier(c->group, 10000);
-    c->state.store((int)CommState::DESTROYED);
+    const std::string key = FamilyKey(c);
+    std::lock_guard<std::mutex> lk(g_regMu);
+    for (auto &kv : g_registry)
+        if (kv.second != c && FamilyKey(kv.second) == key) return true;
+    return false;
+}
+
+void Release(Comm *c)
+{
     std::shared_ptr<Bootstrap> boot = c->boot;
     std::shared_ptr<BootstrapHub> hub = c->hub;
     bool world = c->group.id == 0;
     delete c;
     if (world && boot) boot->Close();
     // the hub (if this process owns it) ends when every agent has said goodbye
+}
+}  // namespace
+
+// Peers must stop touching a rank's heap before it disappears, so destruction meets the other ranks in a barrier.  When
+// several ranks of the communicator are objects of one process and one thread destroys them one after the other
+// (the usual way after HcclCommInitAll), the first call cannot wait for ranks whose destroy only that same thread will
+// ever call.  Such a rank says that it has arrived, waits briefly, and if the others are not there yet its resources
+// are parked; the rank of this process that sees the barrier complete frees them with its own.
+void CommDestroy(Comm *c)
+{
+    if (!c) return;
+    RetryTeardown(c);
+    RegistryRemove(c);
+    bool met = true;
+    if (c->boot && c->state.load() != (int)CommState::DESTROYED) {
+        uint64_t ticket = 0;
+        if (c->boot->BarrierArrive(c->group, &ticket) == HCCL_SUCCESS) {
+            const bool siblings = HasLiveSibling(c);
+            HcclResult r = c->boot->BarrierWait(ticket, siblings ? 50 : 10000, siblings);
+            met = !(siblings && r == HCCL_E_TIMEOUT);
+        }
+    }
+    c->state.store((int)CommState::DESTROYED);
+    const std::string key = FamilyKey(c);
+    if (!met) {
+        c->magic = 0x5a4f4d42;           // the handle is dead for the caller
+        std::lock_guard<std::mutex> lk(g_parkedMu);
+        g_parked[key].push_back(c);
+        return;
+    }
+    std::vector<Comm *> parked;
+    {
+        std::lock_guard<std::mutex> lk(g_parkedMu);
+        auto it = g_parked.find(key);
+        if (it != g_parked.end()) { parked.swap(it->second); g_parked.erase(it); }
+    }
+    Platform *plat = c->plat;
+    const int device = c->device;
+    Release(c);
+    for (Comm *z : parked) {
+        if (plat) plat->SetDevice(z->device);
+        Release(z);
+    }
+    if (plat && !parked.empty()) plat->SetDevice(device);
 }
 
 Window *FindWindow(Comm *c, const void *ptr, uint64_t bytes, uint64_t *offset)

@@ -533,6 +533,32 @@ HcclResult Bootstrap::AllGather(Group &g, const Blob &mine, std::vector<Blob> *a
 
 HcclResult Bootstrap::Barrier(Group &g, int timeoutMs) { return AllGather(g, Blob(), nullptr, timeoutMs); }
 
+HcclResult Bootstrap::BarrierArrive(Group &g, uint64_t *ticket)
+{
+    if (g.myIndex == ~0u || !ticket) return HCCL_E_PARA;
+    *ticket = ((uint64_t)g.id << 32) | (uint64_t)(g.seq++);
+    Blob msg;
+    Put32(msg, (uint32_t)g.ranks.size());
+    Put32(msg, g.myIndex);
+    PutBlob(msg, Blob());
+    return SendMsg(MSG_GATHER, 0, *ticket, msg.data(), msg.size());
+}
+
+HcclResult Bootstrap::BarrierWait(uint64_t ticket, int timeoutMs, bool quiet)
+{
+    if (timeoutMs < 0) timeoutMs = timeoutMs_;
+    std::unique_lock<std::mutex> lk(mu_);
+    cv_.wait_for(lk, std::chrono::milliseconds(timeoutMs), [&] { return gatherDone_.count(ticket) || hubGone_.load(); });
+    if (gatherDone_.count(ticket)) {
+        gatherDone_.erase(ticket);
+        return HCCL_SUCCESS;
+    }
+    if (!quiet)
+        HCCL_ERROR("rank %u: control-plane barrier (group %u, seq %u) did not complete: %s", rank_, (uint32_t)(ticket >> 32), (uint32_t)ticket,
+                   hubGone_.load() ? "rendezvous server is gone" : "timeout");
+    return hubGone_.load() ? HCCL_E_NETWORK : HCCL_E_TIMEOUT;
+}
+
 HcclResult Bootstrap::Broadcast(Group &g, uint32_t rootIndex, Blob *data, int timeoutMs)
 {
     std::vector<Blob> all;

@@ -101,6 +101,10 @@ public:
 
     HcclResult AllGather(Group &g, const Blob &mine, std::vector<Blob> *all, int timeoutMs = -1);
     HcclResult Barrier(Group &g, int timeoutMs = -1);
+    // The barrier in two steps: Arrive tells the others that this rank is there and returns at once; Wait returns when all
+    // have arrived.  A Wait that ran out of time (HCCL_E_TIMEOUT) leaves the barrier pending and may be repeated.
+    HcclResult BarrierArrive(Group &g, uint64_t *ticket);
+    HcclResult BarrierWait(uint64_t ticket, int timeoutMs, bool quiet = false);
     HcclResult Broadcast(Group &g, uint32_t rootIndex, Blob *data, int timeoutMs = -1);
     // Relayed datagrams; (src, tag) streams are FIFO.
     HcclResult Send(uint32_t dstRank, uint64_t tag, const Blob &data);

@@ -4,6 +4,7 @@
 #include <unistd.h>
 
 #include <atomic>
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <fstream>
@@ -671,6 +672,288 @@ static void BaseLevel(uint32_t rank, uint32_t n, HcclComm comm)
     EX_CHECK(HcclBarrier(comm, nullptr));
 }
 
+// ------------------------------------------------------------------------- teams below the world team, team channels
+
+static void Teams(uint32_t rank, uint32_t n, HcclComm comm)
+{
+    HcclTeamCreateDesc td;
+    EX_CHECK(HcclTeamCreateDescInit(&td));
+    td.selfRankId = rank;
+    td.requirement.signalCount = 1;
+    td.requirement.barrierCount = 1;
+    HcommTeamHandle world = nullptr;
+    EX_CHECK(HcclWorldTeamCreate(comm, &td, &world));
+    // the even ranks form a team of their own; an odd rank cannot create it
+    std::vector<uint32_t> evens;
+    for (uint32_t r = 0; r < n; r += 2) evens.push_back(r);
+    HcclTeamCreateDesc sd = td;
+    sd.rankIds = evens.data();
+    sd.rankNum = (uint32_t)evens.size();
+    HcommTeamHandle sub = nullptr;
+    if (rank % 2 == 0) {
+        EX_CHECK(HcclSubTeamCreate(world, &sd, &sub));
+        uint32_t members = 0, myIdx = 99;
+        EX_CHECK(HcclTeamGetInfo(sub, &members, &myIdx));
+        EX_EXPECT(members == evens.size() && myIdx == rank / 2);
+        for (int round = 1; round <= 3; ++round) EX_CHECK(HcclTeamBarrier(sub, 0, nullptr));
+        const uint32_t next = (myIdx + 1) % members, prev = (myIdx + members - 1) % members;
+        EX_CHECK(HcclTeamSignal(sub, next, 0, 5, nullptr));
+        EX_CHECK(HcclTeamSignalWait(sub, prev, 0, 5, nullptr));
+        EX_CHECK(HcclTeamDestroy(sub));
+    } else {
+        EXPECT_RC(HcclSubTeamCreate(world, &sd, &sub), HCCL_E_PARA);
+    }
+    uint32_t outside = n;
+    HcclTeamCreateDesc bad = td;
+    bad.rankIds = &outside;
+    bad.rankNum = 1;
+    EXPECT_RC(HcclSubTeamCreate(world, &bad, &sub), HCCL_E_PARA);
+    bad.rankIds = nullptr;
+    bad.rankNum = 0;
+    EXPECT_RC(HcclSubTeamCreate(world, &bad, &sub), HCCL_E_PARA);      // a sub team names its members
+    // channels between all members of the world team, found again by a query
+    HcclTeamCreateChannelsDesc cd;
+    EX_CHECK(HcclTeamCreateChannelsDescInit(&cd));
+    cd.notifyNum = 3;
+    EX_CHECK(HcclTeamChannelsCreate(comm, world, &cd));
+    cd.header.magicWord = 0;
+    EXPECT_RC(HcclTeamChannelsCreate(comm, world, &cd), HCCL_E_PARA);
+    for (uint32_t q = 0; q < n; ++q) {
+        if (q == rank) continue;
+        HcclChannelDesc d;
+        EX_CHECK(HcclChannelDescInit(&d, 1));
+        d.remoteRank = q;
+        d.notifyNum = 3;
+        ChannelHandle h = 0;
+        EX_CHECK(HcclChannelQuery(comm, COMM_ENGINE_CPU_TS, &d, 1, &h));
+        EX_EXPECT(h != 0);
+    }
+    EX_CHECK(HcclTeamBarrier(world, 0, nullptr));
+    EX_CHECK(HcclTeamDestroy(world));
+    EXPECT_RC(HcclTeamDestroy(world), HCCL_E_PTR);
+}
+
+// ------------------------------------------------------------------- operator records, wait status, heartbeat switch
+
+static void Diagnostics(uint32_t rank, uint32_t n, HcclComm comm)
+{
+    EX_CHECK(HcclDiagSetProfiling(comm, 1));
+    std::vector<int32_t> v(777, (int32_t)rank), out(777, 0);
+    EX_CHECK(HcclAllReduce(v.data(), out.data(), 777, HCCL_DATA_TYPE_INT32, HCCL_REDUCE_MAX, comm, nullptr));
+    EX_EXPECT(out[776] == (int32_t)(n - 1));
+    HcclOpRecord recs[8];
+    uint32_t written = 0;
+    EX_CHECK(HcclDiagGetOpRecords(comm, recs, 8, &written));
+    EX_EXPECT(written >= 1);
+    const HcclOpRecord &last = recs[written - 1];
+    EX_EXPECT(last.cmdType == (uint32_t)HCCL_CMD_ALLREDUCE && last.count == 777 && last.dataType == (uint32_t)HCCL_DATA_TYPE_INT32 &&
+              last.reduceOp == (uint32_t)HCCL_REDUCE_MAX && last.hostEndNs >= last.hostStartNs && last.algName[0] != 0);
+    uint64_t launched = 0;
+    EX_CHECK(HcclDiagGetOpCounters(comm, &launched, nullptr, nullptr));
+    EX_EXPECT(launched == last.seq);
+    uint64_t starts[4], ends[4];
+    written = 99;
+    EX_CHECK(HcclDiagGetKernelTimes(comm, starts, ends, 4, &written));
+    EX_EXPECT(written == 0);                               // the simulator runs no kernels
+    HcclDeviceWaitStatus ws;
+    std::memset(&ws, 0xff, sizeof(ws));
+    EX_CHECK(HcclDiagGetWaitStatus(comm, &ws));
+    EX_EXPECT(ws.valid == 0);
+    EX_CHECK(HcclDiagClearWaitStatus(comm));
+    uint64_t lost = 99;
+    std::vector<uint64_t> ages(n);
+    EX_CHECK(HcclDiagGetHeartbeat(comm, ages.data(), n, &lost));
+    EX_EXPECT(lost == 0);
+    EX_CHECK(HcclDiagPauseHeartbeat(comm));                // heartbeats are off here: nothing to stop, nothing breaks
+    char text[4096];
+    EX_CHECK(HcclDiagDump(comm, text, sizeof(text)));
+    EX_EXPECT(std::strstr(text, "AllReduce") != nullptr || std::strstr(text, "allreduce") != nullptr);
+    HcclOpRetryStats stats;
+    EX_CHECK(HcclCommGetOpRetryStats(comm, &stats));
+    EX_EXPECT(stats.enabled == 0 && stats.requests == 0);
+    EX_CHECK(HcclDiagSetProfiling(comm, 0));
+
+    // the hooks around a snapshot of the process: Pre suspends every communicator of the process, each rank resumes its own
+    EX_CHECK(HcclBarrier(comm, nullptr));
+    if (rank == 0) EX_CHECK(HcclSnapshotPre());
+    static std::atomic<int> suspendedSeen{0};
+    if (rank == 0) suspendedSeen.store(1);
+    while (suspendedSeen.load() == 0) usleep(1000);
+    EXPECT_RC(HcclAllReduce(v.data(), out.data(), 777, HCCL_DATA_TYPE_INT32, HCCL_REDUCE_MAX, comm, nullptr), HCCL_E_SUSPENDING);
+    EX_CHECK(HcclCommResume(comm));
+    EX_CHECK(HcclAllReduce(v.data(), out.data(), 777, HCCL_DATA_TYPE_INT32, HCCL_REDUCE_SUM, comm, nullptr));
+    EX_EXPECT(out[0] == (int32_t)(n * (n - 1) / 2));
+    EX_CHECK(HcclBarrier(comm, nullptr));
+    if (rank == 0) EX_CHECK(HcclSnapshotPost());           // nothing is suspended any more: a no-op
+    EX_CHECK(HcclBarrier(comm, nullptr));
+}
+
+// ---------------------------------------------------------------- a host function launched in the communicator's order
+
+struct SweepKernelArgs { std::atomic<int> *calls; int add; };
+extern "C" int SweepKernel(void *args, uint32_t argSize, void *stream)
+{
+    if (argSize != sizeof(SweepKernelArgs) || stream != nullptr) return 7;
+    SweepKernelArgs *a = (SweepKernelArgs *)args;
+    a->calls->fetch_add(a->add);
+    return 0;
+}
+extern "C" int SweepKernelFails(void *, uint32_t, void *) { return 3; }
+
+static void Launch(uint32_t rank, uint32_t n, HcclComm comm)
+{
+    static std::atomic<int> calls{0};
+    HcclOpDesc op;
+    EX_CHECK(HcclOpDescInit(&op));
+    std::snprintf(op.opName, sizeof(op.opName), "sweep");
+    HcclKernelFuncInfo fi;
+    std::memset(&fi, 0, sizeof(fi));
+    std::snprintf(fi.kernelFuncName, sizeof(fi.kernelFuncName), "SweepKernel");       // in this program: no library name
+    SweepKernelArgs args{&calls, (int)rank + 1};
+    fi.args = &args;
+    fi.argSize = sizeof(args);
+    HcclKernelLaunchCfg cfg;
+    EX_CHECK(HcclKernelLaunchCfgInit(&cfg));
+    ThreadHandle t = 0;
+    EX_CHECK(HcclThreadAcquire(comm, COMM_ENGINE_CPU_TS, 1, 1, &t));
+    EX_CHECK(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, &cfg));
+    EX_CHECK(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, nullptr));
+    std::snprintf(fi.kernelFuncName, sizeof(fi.kernelFuncName), "SweepKernelFails");
+    EXPECT_RC(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, &cfg), HCCL_E_INTERNAL);
+    std::snprintf(fi.kernelFuncName, sizeof(fi.kernelFuncName), "NoSuchKernel");
+    EXPECT_RC(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, &cfg), HCCL_E_NOT_FOUND);
+    std::snprintf(fi.kernelSoName, sizeof(fi.kernelSoName), "/nonexistent/libsweep.so");
+    EXPECT_RC(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, &cfg), HCCL_E_OPEN_FILE_FAILURE);
+    op.header.magicWord = 0;
+    EXPECT_RC(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, &cfg), HCCL_E_PARA);
+    EX_CHECK(HcclBarrier(comm, nullptr));
+    EX_EXPECT(calls.load() == (int)(n * (n + 1)));         // every rank launched twice with rank + 1
+    EX_CHECK(HcclBarrier(comm, nullptr));
+    if (rank == 0) calls.store(0);
+}
+
+// ------------------------------------------------------------------------- the other ways to create a communicator
+
+static std::string MakeRankTable(uint32_t n, const char *instance)
+{
+    std::ostringstream os;
+    os << "{\"version\": \"2.0\", \"rank_count\": " << n << ", \"status\": \"completed\", \"rank_list\": [";
+    for (uint32_t r = 0; r < n; ++r) {
+        os << (r ? ", " : "") << "{\"rank_id\": " << r << ", \"device_id\": " << r << ", \"local_id\": " << r
+           << ", \"level_list\": [{\"net_layer\": 0, \"net_instance_id\": \"" << instance << "\", \"net_type\": \"TOPO_FILE_DESC\", \"net_attr\": \"\", "
+           << "\"rank_addr_list\": [{\"addr_type\": \"IPV4\", \"addr\": \"127.0.0.1\", \"ports\": [\"0/" << r << "\"]}]}]}";
+    }
+    os << "]}";
+    return os.str();
+}
+
+static void SumOverRanks(uint32_t n, const std::vector<HcclComm> &comms)
+{
+    std::vector<std::thread> ts;
+    for (uint32_t r = 0; r < n; ++r)
+        ts.emplace_back([&, r] {
+            double x = (double)(r + 1), sum = 0;
+            EX_CHECK(HcclAllReduce(&x, &sum, 1, HCCL_DATA_TYPE_FP64, HCCL_REDUCE_SUM, comms[r], nullptr));
+            EX_EXPECT(sum == (double)n * (n + 1) / 2);
+        });
+    for (auto &t : ts) t.join();
+}
+
+static void OtherWaysToStart(uint32_t n)
+{
+    // all ranks from one call
+    std::vector<int32_t> devices(n);
+    std::iota(devices.begin(), devices.end(), 0);
+    std::vector<HcclComm> comms(n, nullptr);
+    EX_CHECK(HcclCommInitAll(n, devices.data(), comms.data()));
+    EXPECT_RC(HcclCommInitAll(0, devices.data(), comms.data()), HCCL_E_PARA);
+    SumOverRanks(n, comms);
+    // one thread destroys them one after the other: no call may wait for ranks that only this thread can bring along
+    const auto before = std::chrono::steady_clock::now();
+    for (HcclComm c : comms) EX_CHECK(HcclCommDestroy(c));
+    EX_EXPECT(std::chrono::steady_clock::now() - before < std::chrono::seconds(3));
+
+    // root info with a configuration: a name of the caller's choice, a buffer size, a deterministic setting
+    HcclRootInfo info;
+    EX_CHECK(HcclGetRootInfo(&info));
+    std::vector<std::thread> ts;
+    for (uint32_t r = 0; r < n; ++r)
+        ts.emplace_back([&, r] {
+            HcclCommConfig cfg;
+            HcclCommConfigInit(&cfg);
+            std::snprintf(cfg.hcclCommName, sizeof(cfg.hcclCommName), "sweep_named");
+            cfg.hcclBufferSize = 1;
+            cfg.hcclDeterministic = 1;
+            EX_CHECK(HcclCommInitRootInfoConfig(n, &info, r, &cfg, &comms[r]));
+            char name[COMM_NAME_MAX_LENGTH] = "";
+            EX_CHECK(HcclGetCommName(comms[r], name));
+            EX_EXPECT(std::string(name) == "sweep_named");
+            void *buf = nullptr;
+            uint64_t size = 0;
+            EX_CHECK(HcclGetHcclBuffer(comms[r], &buf, &size));
+            EX_EXPECT(size == 2u << 20);
+        });
+    for (auto &t : ts) t.join();
+    ts.clear();
+    SumOverRanks(n, comms);
+    for (HcclComm c : comms) EX_CHECK(HcclCommDestroy(c));
+
+    // a rank table: every rank reads the same file, nothing else is exchanged beforehand
+    const std::string path = "/tmp/hccl_sweep_table_" + std::to_string((long)getpid()) + ".json";
+    {
+        std::ofstream f(path);
+        f << MakeRankTable(n, "sweep_node");
+    }
+    for (uint32_t r = 0; r < n; ++r)
+        ts.emplace_back([&, r] {
+            if (r % 2 == 0) {
+                EX_CHECK(HcclCommInitClusterInfo(path.c_str(), r, &comms[r]));
+            } else {
+                HcclCommConfig cfg;
+                HcclCommConfigInit(&cfg);
+                EX_CHECK(HcclCommInitClusterInfoConfig(path.c_str(), r, &cfg, &comms[r]));
+            }
+        });
+    for (auto &t : ts) t.join();
+    ts.clear();
+    SumOverRanks(n, comms);
+    HcclComm none = nullptr;
+    EXPECT_RC(HcclCommInitClusterInfo(path.c_str(), n, &none), HCCL_E_PARA);              // not in the table
+    EX_EXPECT(HcclCommInitClusterInfo("/nonexistent/table.json", 0, &none) != HCCL_SUCCESS);
+    for (HcclComm c : comms) EX_CHECK(HcclCommDestroy(c));
+    unlink(path.c_str());
+
+    // the world group from a rank table (one rank: the group is process-wide)
+    const std::string solo = "/tmp/hccl_sweep_solo_" + std::to_string((long)getpid()) + ".json";
+    {
+        std::ofstream f(solo);
+        f << MakeRankTable(1, "sweep_solo");
+    }
+    EX_CHECK(HcomInitByRankTable(solo.c_str(), 0));
+    EXPECT_RC(HcomInitByRankTable(solo.c_str(), 0), HCCL_E_PARA);                          // already there
+    uint32_t size = 0, id = 9;
+    EX_CHECK(HcomGetRankSize(HCCL_WORLD_GROUP, &size));
+    EX_CHECK(HcomGetRankId(HCCL_WORLD_GROUP, &id));
+    EX_EXPECT(size == 1 && id == 0);
+    float one = 3.f, res = 0.f;
+    EX_CHECK(HcomAllReduce("t", &one, &res, 1, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, HCCL_WORLD_GROUP, nullptr));
+    EX_EXPECT(res == 3.f);
+    EX_CHECK(HcomDestroy());
+    unlink(solo.c_str());
+
+    // a restored process image: what is left of its communicators is invalid
+    HcclComm last = nullptr;
+    EX_CHECK(HcclGetRootInfo(&info));
+    EX_CHECK(HcclCommInitRootInfo(1, &info, 0, &last));
+    char name[COMM_NAME_MAX_LENGTH] = "";
+    EX_CHECK(HcclGetCommName(last, name));
+    EX_CHECK(HcclSnapshotRestore());
+    EXPECT_RC(HcclAllReduce(&one, &res, 1, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, last, nullptr), HCCL_E_PARA);
+    HcclCommStatus status = HCCL_COMM_STATUS_READY;
+    EX_CHECK(HcclCommGetStatus(name, &status));
+    EX_EXPECT(status == HCCL_COMM_STATUS_INVALID);
+}
+
 int main(int argc, char **argv)
 {
     const uint32_t n = argc > 1 ? (uint32_t)std::atoi(argv[1]) : 4;
@@ -680,7 +963,11 @@ int main(int argc, char **argv)
         InnerOperators(rank, n, comm);
         Resources(rank, n, comm);
         BaseLevel(rank, n, comm);
+        Teams(rank, n, comm);
+        Diagnostics(rank, n, comm);
+        Launch(rank, n, comm);
     });
+    OtherWaysToStart(n);
     std::printf("api_sweep: %u ranks ok\n", n);
     return 0;
 }

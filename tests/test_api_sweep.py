@@ -17,7 +17,7 @@ def sweep(tmp_path_factory):
     name = "hcomm_cov" if os.environ.get("HCOMM_LIBRARY") == "cov" else "hcomm"      # the coverage run links that build
     exe = tmp_path_factory.mktemp("sweep") / "api_sweep"
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-pthread", f"-I{ROOT / 'include'}", str(ROOT / "tests" / "api_sweep.cc"), "-o", str(exe),
-           f"-L{libdir}", "-l" + name, "-ldl", f"-Wl,-rpath,{libdir}"]
+           f"-L{libdir}", "-l" + name, "-ldl", "-rdynamic", f"-Wl,-rpath,{libdir}"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-6000:]
     return exe

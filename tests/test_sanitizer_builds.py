@@ -89,7 +89,7 @@ def _build_sweep(tmp_path, variant):
     exe = tmp_path / ("api_sweep_" + variant)
     extra = ["-fsanitize=thread"] if variant == "tsan" else ["-Wl,--allow-shlib-undefined"]
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-pthread", f"-I{root / 'include'}", str(root / "tests" / "api_sweep.cc"), "-o", str(exe),
-           f"-L{LIBDIR}", "-lhcomm_" + variant, "-ldl", f"-Wl,-rpath,{LIBDIR}", *extra]
+           f"-L{LIBDIR}", "-lhcomm_" + variant, "-ldl", "-rdynamic", f"-Wl,-rpath,{LIBDIR}", *extra]
     res = subprocess.run(cmd, capture_output=True, text=True)
     assert res.returncode == 0, res.stderr[-6000:]
     return exe
