@@ -954,6 +954,79 @@ static void OtherWaysToStart(uint32_t n)
     EX_EXPECT(status == HCCL_COMM_STATUS_INVALID);
 }
 
+// ------------------------------------------------- bring-up inside a group, channel requests that cannot be served
+
+extern "C" void HcommToolReloadEnv(void);       // re-reads the environment variables (exported for tests)
+static void SumOverRanks(uint32_t n, const std::vector<HcclComm> &comms);
+
+static void EdgeCases(uint32_t n)
+{
+    // communicators whose creation is queued by a group: nothing exists before the group ends
+    HcclRootInfo info;
+    EX_CHECK(HcclGetRootInfo(&info));
+    std::vector<HcclComm> comms(n, nullptr);
+    std::vector<std::thread> ts;
+    for (uint32_t r = 0; r < n; ++r)
+        ts.emplace_back([&, r] {
+            EX_CHECK(HcclGroupStart());
+            EX_CHECK(HcclCommInitRootInfo(n, &info, r, &comms[r]));
+            EX_EXPECT(comms[r] == nullptr);
+            EX_CHECK(HcclGroupEnd());
+            EX_EXPECT(comms[r] != nullptr);
+        });
+    for (auto &t : ts) t.join();
+    ts.clear();
+    SumOverRanks(n, comms);
+    if (n >= 2) {
+        // more notify slots than a pair of ranks has: the whole request is rolled back, a smaller one is served
+        for (uint32_t r = 0; r < 2; ++r)
+            ts.emplace_back([&, r] {
+                HcclChannelDesc d[2];
+                EX_CHECK(HcclChannelDescInit(d, 2));
+                d[0].remoteRank = d[1].remoteRank = 1 - r;
+                d[0].notifyNum = 40;
+                d[1].notifyNum = 30;
+                ChannelHandle h[2] = {7, 7};
+                EXPECT_RC(HcclChannelAcquire(comms[r], COMM_ENGINE_CPU_TS, d, 2, h), HCCL_E_UNAVAIL);
+                EX_EXPECT(h[0] == 0 && h[1] == 0);
+                EX_CHECK(HcclChannelQuery(comms[r], COMM_ENGINE_CPU_TS, d, 1, h));
+                EX_EXPECT(h[0] == 0);                      // the first channel of the failed request is gone too
+                EX_CHECK(HcclChannelAcquire(comms[r], COMM_ENGINE_CPU_TS, d, 1, h));
+                EX_EXPECT(h[0] != 0);
+                EX_CHECK(HcommChannelNotifyRecord(h[0], 39));
+                EX_CHECK(HcommChannelNotifyWait(h[0], 39, 10));
+                d[0].notifyNum = 65;
+                EXPECT_RC(HcclChannelAcquire(comms[r], COMM_ENGINE_CPU_TS, d, 1, h), HCCL_E_PARA);     // more than a channel can hold
+                d[0].notifyNum = 1;
+                d[0].remoteRank = r;
+                EXPECT_RC(HcclChannelAcquire(comms[r], COMM_ENGINE_CPU_TS, d, 1, h), HCCL_E_PARA);     // a channel to oneself
+                d[0].remoteRank = 1 - r;
+                d[0].channelProtocol = COMM_PROTOCOL_ROCE;
+                EXPECT_RC(HcclChannelAcquire(comms[r], COMM_ENGINE_CPU_TS, d, 1, h), HCCL_E_NOT_SUPPORT);
+                d[0].header.magicWord = 0;
+                EXPECT_RC(HcclChannelAcquire(comms[r], COMM_ENGINE_CPU_TS, d, 1, h), HCCL_E_PARA);
+            });
+        for (auto &t : ts) t.join();
+        ts.clear();
+        // a peer that never asks for its end of the channel: the request gives up after the connect timeout
+        setenv("HCCL_CONNECT_TIMEOUT", "2", 1);
+        HcommToolReloadEnv();
+        HcclChannelDesc d;
+        EX_CHECK(HcclChannelDescInit(&d, 1));
+        d.remoteRank = 1;
+        d.notifyNum = 2;
+        ChannelHandle h = 0;
+        const auto before = std::chrono::steady_clock::now();
+        EXPECT_RC(HcclChannelAcquire(comms[0], COMM_ENGINE_CPU_TS, &d, 1, &h), HCCL_E_TIMEOUT);
+        const auto took = std::chrono::steady_clock::now() - before;
+        EX_EXPECT(took >= std::chrono::milliseconds(1900) && took < std::chrono::seconds(8));
+        unsetenv("HCCL_CONNECT_TIMEOUT");
+        HcommToolReloadEnv();
+    }
+    for (uint32_t r = 0; r < n; ++r) ts.emplace_back([&, r] { EX_CHECK(HcclCommDestroy(comms[r])); });
+    for (auto &t : ts) t.join();
+}
+
 int main(int argc, char **argv)
 {
     const uint32_t n = argc > 1 ? (uint32_t)std::atoi(argv[1]) : 4;
@@ -967,6 +1040,7 @@ int main(int argc, char **argv)
         Diagnostics(rank, n, comm);
         Launch(rank, n, comm);
     });
+    EdgeCases(n);
     OtherWaysToStart(n);
     std::printf("api_sweep: %u ranks ok\n", n);
     return 0;
