@@ -130,3 +130,15 @@ def test_nvml_discovery_through_a_fake_table():
     rc, s = tool_str(lib.HcommToolFakeNvmlProbe, 2, 0)
     assert rc == 0 and "links 18 switch 0 peers 18 fabric 0" in s
     tool_str(lib.HcommToolFakeNvmlProbe, 0, 0)
+
+
+def test_parsers_survive_damaged_input():
+    """tests/fuzz_parsers.py: a few thousand rank tables and algorithm settings with values replaced, removed, duplicated,
+    bytes flipped, cut and nested far too deep.  Every one is answered with a return code; what is accepted parses again."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    run = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "fuzz_parsers.py"), "2500", "11"], capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0 and "fuzz: 2500 inputs" in run.stdout, run.stdout[-2000:] + run.stderr[-4000:]
+    rc, _, sm = _parse(b'{"a":' + b"[" * 200000 + b"]" * 200000 + b"}")
+    assert rc != 0 and "nesting too deep" in sm
