@@ -167,7 +167,9 @@ void BootstrapHub::Run()
         }
         MsgHdr h;
         Blob pl;
-        if (ReadMsg(fd, &h, &pl, deadline) != HCCL_SUCCESS || h.type != MSG_HELLO) { net::Close(fd); continue; }
+        // A rank sends its HELLO right after connecting.  Whatever else connects (a port scan, a health check) and stays
+        // silent must not hold up the ranks that queue behind it: it gets a few seconds, not the rendezvous' whole time.
+        if (ReadMsg(fd, &h, &pl, std::min<int64_t>(deadline, net::NowMs() + 3000)) != HCCL_SUCCESS || h.type != MSG_HELLO) { net::Close(fd); continue; }
         Reader rd(pl);
         uint32_t size = rd.u32(), rank = rd.u32();
         Blob agentId = rd.blob();

@@ -203,3 +203,31 @@ def test_sub_communicator_and_argument_checks(monkeypatch):
         comms[0].send(x, 0)                                                     # send to self
     run_ranks(n, lambda r: subs[r].destroy() if subs[r] else None)
     destroy(comms)
+
+
+def test_rendezvous_survives_connections_that_are_not_ranks(monkeypatch):
+    """Whatever connects to the rendezvous port without being a rank - silent, talking nonsense, or announcing an absurd
+    message length - is dropped and does not hold up the ranks for long."""
+    import socket
+    import struct
+    import time
+    import hcomm_b200 as hb
+    sim_env(monkeypatch)
+    info = hb.get_root_info()
+    ip = info[:64].split(b"\0")[0].decode()
+    port = struct.unpack_from("<I", info, 64)[0]
+    strays = []
+    for payload in (None, b"GET / HTTP/1.0\r\n\r\n", struct.pack("<IHHIQQ", 0x4d434348, 1, 0, 0, 0, 1 << 60)[:24]):
+        s = socket.create_connection((ip, port), timeout=5)
+        if payload:
+            s.sendall(payload)
+        strays.append(s)            # kept open: the hub has to give up on the silent one by itself
+    t0 = time.time()
+    n = 3
+    comms = run_ranks(n, lambda r: hb.Communicator(n, info, r))
+    assert time.time() - t0 < 20
+    out = run_ranks(n, lambda r: comms[r].all_reduce(np.full(100, r + 1, np.float32), np.zeros(100, np.float32)))
+    assert all((o == 6).all() for o in out)
+    for s in strays:
+        s.close()
+    destroy(comms)
