@@ -34,3 +34,18 @@ def test_kernels_that_spin_have_a_bound():
             continue
         for i, line in enumerate(p.read_text(errors="ignore").splitlines(), 1):
             assert not bare.search(line), f"{p}:{i}: unbounded spin: {line.strip()}"
+
+
+def test_every_exported_entry_point_is_in_the_api_reference():
+    """docs/api_reference.md names every function the shared library exports under the API's prefixes."""
+    import subprocess
+    lib = ROOT / "hcomm_b200" / "lib" / "libhcomm.so"
+    if not lib.exists():
+        import hcomm_b200
+        hcomm_b200.load_library()
+    out = subprocess.run(["nm", "-D", "--defined-only", str(lib)], capture_output=True, text=True).stdout
+    names = sorted({ln.split()[2] for ln in out.splitlines() if len(ln.split()) == 3 and ln.split()[1] == "T" and ln.split()[2].startswith(("Hccl", "Hcom"))})
+    assert len(names) > 250
+    doc = (ROOT / "docs" / "api_reference.md").read_text()
+    missing = [n for n in names if f"`{n}`" not in doc]
+    assert not missing, missing
