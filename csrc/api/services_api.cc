@@ -15,6 +15,7 @@
 #include "../core/dtype.h"
 #include "../core/log.h"
 #include "hccl/hccl_launch.h"
+#include "hccl/hccl_mc2.h"
 #include "hccl/hccl_one_sided.h"
 #include "hccl/hccl_res.h"
 #include "hcomm_res.h"
@@ -220,6 +221,55 @@ HcclResult HcclCommPrepare(HcclComm comm, const HcclPrepareConfig *prepareConfig
     CHK_PTR_NULL(c); CHK_PTR_NULL(prepareConfig);
     if (prepareConfig->topoType != HCCL_TOPO_FULLMESH) return HCCL_E_NOT_SUPPORT;
     return c->boot->Barrier(c->group, timeout > 0 ? timeout * 1000 : -1);
+}
+
+// ------------------------------------------------- resources of fused compute + communication kernels
+
+static HcclResult ContextOf(Comm *c, void **commContext)
+{
+    CHK_PTR_NULL(c); CHK_PTR_NULL(commContext);
+    *commContext = c->devStruct ? c->devStruct : (void *)&c->hostDev;
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclAllocComResource(HcclComm comm, uint32_t streamMode, void **commContext)
+{
+    (void)streamMode;
+    return ContextOf(AsComm(comm), commContext);
+}
+HcclResult HcclAllocComResourceByTiling(HcclComm comm, void *stream, void *mc2Tiling, void **commContext)
+{
+    (void)stream; (void)mc2Tiling;
+    return ContextOf(AsComm(comm), commContext);
+}
+HcclResult HcclCreateComResource(const char *commName, uint32_t streamMode, void **commContext)
+{
+    (void)streamMode;
+    CHK_PTR_NULL(commName);
+    Comm *c = RegistryFind(commName);
+    if (!c) return HCCL_E_NOT_FOUND;
+    return ContextOf(c, commContext);
+}
+
+HcclResult HcclGetAicpuOpStreamAndNotify(HcclComm comm, aclrtStream *opStream, uint8_t aicpuNotifyNum, void **aicpuNotify)
+{
+    Comm *c = AsComm(comm);
+    CHK_PTR_NULL(c); CHK_PTR_NULL(opStream);
+    if (aicpuNotifyNum && !aicpuNotify) return HCCL_E_PTR;
+    ThreadHandle h = 0;
+    CHK_RET(HcclDedicatedThreadAcquire(comm, HCCL_DED_THREAD_TYPE_AICPU_LAUNCH, aicpuNotifyNum, &h));
+    ThreadRes *t = AsThread(h);
+    CHK_PTR_NULL(t);
+    *opStream = t->stream;
+    for (uint32_t i = 0; i < aicpuNotifyNum; ++i) aicpuNotify[i] = t->notify + i;
+    return HCCL_SUCCESS;
+}
+HcclResult HcclGetAicpuOpStreamNotify(const char *commName, aclrtStream *opStream, void **aicpuNotify)
+{
+    CHK_PTR_NULL(commName);
+    Comm *c = RegistryFind(commName);
+    if (!c) return HCCL_E_NOT_FOUND;
+    return HcclGetAicpuOpStreamAndNotify((HcclComm)c, opStream, aicpuNotify ? 1 : 0, aicpuNotify);
 }
 
 // ------------------------------------------------------------------------------ kernel launch

@@ -591,6 +591,23 @@ HcclResult Bootstrap::Recv(uint32_t srcRank, uint64_t tag, Blob *data, int timeo
     return HCCL_SUCCESS;
 }
 
+HcclResult Bootstrap::TryRecv(uint32_t srcRank, uint64_t want, uint64_t mask, Blob *data, uint32_t *fromRank, uint64_t *fromTag)
+{
+    std::lock_guard<std::mutex> lk(mu_);
+    for (auto it = inbox_.begin(); it != inbox_.end(); ++it) {
+        if (it->second.empty()) continue;
+        if (srcRank != ~0u && it->first.src != srcRank) continue;
+        if ((it->first.tag & mask) != (want & mask)) continue;
+        if (data) *data = std::move(it->second.front());
+        if (fromRank) *fromRank = it->first.src;
+        if (fromTag) *fromTag = it->first.tag;
+        it->second.pop_front();
+        if (it->second.empty()) inbox_.erase(it);
+        return HCCL_SUCCESS;
+    }
+    return hubGone_.load() ? HCCL_E_NETWORK : HCCL_E_AGAIN;
+}
+
 HcclResult Bootstrap::SendFd(uint32_t dstRank, uint64_t tag, int fd)
 {
     int c = -1;

@@ -110,6 +110,9 @@ public:
     HcclResult Send(uint32_t dstRank, uint64_t tag, const Blob &data);
     HcclResult Recv(uint32_t srcRank, uint64_t tag, Blob *data, int timeoutMs = -1);
     // File descriptor passing.  The received descriptor belongs to the caller.
+    // Takes the oldest queued relay message from `srcRank` (~0u: from anybody) whose tag agrees with `want` in the bits
+    // of `mask`, without waiting.  HCCL_E_AGAIN when there is none.
+    HcclResult TryRecv(uint32_t srcRank, uint64_t want, uint64_t mask, Blob *data, uint32_t *fromRank, uint64_t *fromTag);
     HcclResult SendFd(uint32_t dstRank, uint64_t tag, int fd);
     HcclResult RecvFd(uint32_t srcRank, uint64_t tag, int *fd, int timeoutMs = -1);
 

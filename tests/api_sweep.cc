@@ -17,6 +17,8 @@
 #include "hccl/hccl_dfx.h"
 #include "hccl/hccl_diag.h"
 #include "hccl/hccl_launch.h"
+#include "hccl/hccl_mc2.h"
+#include "hccl/hccl_msg.h"
 #include "hccl/hccl_one_sided.h"
 #include "hccl/hccl_rank_graph.h"
 #include "hccl/hccl_res.h"
@@ -826,6 +828,22 @@ static void Launch(uint32_t rank, uint32_t n, HcclComm comm)
     EXPECT_RC(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, &cfg), HCCL_E_OPEN_FILE_FAILURE);
     op.header.magicWord = 0;
     EXPECT_RC(HcclAicpuKernelLaunch(comm, &op, &fi, 0, nullptr, &cfg), HCCL_E_PARA);
+    // what a fused compute + communication kernel is given: the communicator's device block, the launch stream, notifies
+    void *ctx = nullptr, *ctx2 = nullptr, *ctx3 = nullptr;
+    EX_CHECK(HcclAllocComResource(comm, 0, &ctx));
+    EX_CHECK(HcclAllocComResourceByTiling(comm, nullptr, nullptr, &ctx2));
+    char commName[COMM_NAME_MAX_LENGTH] = "";
+    EX_CHECK(HcclGetCommName(comm, commName));
+    EX_CHECK(HcclCreateComResource(commName, 0, &ctx3));
+    EX_EXPECT(ctx != nullptr && ctx == ctx2 && ctx3 != nullptr);
+    EXPECT_RC(HcclCreateComResource("no such communicator", 0, &ctx3), HCCL_E_NOT_FOUND);
+    aclrtStream opStream = (aclrtStream)1;
+    void *notifies[2] = {nullptr, nullptr};
+    EX_CHECK(HcclGetAicpuOpStreamAndNotify(comm, &opStream, 2, notifies));
+    EX_EXPECT(notifies[0] != nullptr && (char *)notifies[1] == (char *)notifies[0] + 8);
+    void *one = nullptr;
+    EX_CHECK(HcclGetAicpuOpStreamNotify(commName, &opStream, &one));
+    EXPECT_RC(HcclGetAicpuOpStreamNotify("no such communicator", &opStream, &one), HCCL_E_NOT_FOUND);
     EX_CHECK(HcclBarrier(comm, nullptr));
     EX_EXPECT(calls.load() == (int)(n * (n + 1)));         // every rank launched twice with rank + 1
     EX_CHECK(HcclBarrier(comm, nullptr));
@@ -922,6 +940,22 @@ static void OtherWaysToStart(uint32_t n)
     EX_EXPECT(HcclCommInitClusterInfo("/nonexistent/table.json", 0, &none) != HCCL_SUCCESS);
     for (HcclComm c : comms) EX_CHECK(HcclCommDestroy(c));
     unlink(path.c_str());
+
+    // the same table handed over as text in memory
+    {
+        const std::string text = MakeRankTable(n, "sweep_text");
+        for (uint32_t r = 0; r < n; ++r)
+            ts.emplace_back([&, r] {
+                CommAttr attr{HCCL_MODE_ANY, r};
+                EX_CHECK(HcclInitComm(text.c_str(), r, &attr, &comms[r]));
+            });
+        for (auto &t : ts) t.join();
+        ts.clear();
+        SumOverRanks(n, comms);
+        for (uint32_t r = 0; r < n; ++r) ts.emplace_back([&, r] { EX_CHECK(HcclFinalizeComm(comms[r])); });
+        for (auto &t : ts) t.join();
+        ts.clear();
+    }
 
     // the world group from a rank table (one rank: the group is process-wide)
     const std::string solo = "/tmp/hccl_sweep_solo_" + std::to_string((long)getpid()) + ".json";
@@ -1027,6 +1061,145 @@ static void EdgeCases(uint32_t n)
     for (auto &t : ts) t.join();
 }
 
+// --------------------------------------------------- tagged host messages with matched probe, also over a connection
+
+static std::atomic<uint32_t> g_rawPort{0};
+
+static void Messages(uint32_t rank, uint32_t n, HcclComm comm)
+{
+    if (n < 2) return;
+    const int right = (int)((rank + 1) % n), left = (int)((rank + n - 1) % n);
+    // two messages with different tags to the right neighbour; the receiver takes the second tag first
+    std::vector<int32_t> a(100, (int32_t)rank), b(7, (int32_t)(rank + 1000));
+    HcclRequest reqs[4] = {nullptr, nullptr, nullptr, nullptr};
+    EX_CHECK(HcclIsend(a.data(), 100, HCCL_DATA_TYPE_INT32, right, 5, comm, &reqs[0]));
+    EX_CHECK(HcclIsend(b.data(), 7, HCCL_DATA_TYPE_INT32, right, 6, comm, &reqs[1]));
+    EXPECT_RC(HcclIsend(a.data(), 1, HCCL_DATA_TYPE_INT32, (int)n, 5, comm, &reqs[2]), HCCL_E_PARA);
+    EXPECT_RC(HcclIsend(a.data(), 1, HCCL_DATA_TYPE_INT32, right, -2, comm, &reqs[2]), HCCL_E_PARA);
+    int flag = 0, count = -1;
+    HcclMessage msg = nullptr;
+    HcclStatus st;
+    for (int spin = 0; spin < 20000 && !flag; ++spin) {
+        EX_CHECK(HcclImprobe(left, 6, comm, &flag, &msg, &st));
+        if (!flag) usleep(500);
+    }
+    EX_EXPECT(flag == 1 && st.srcRank == left && st.tag == 6 && st.error == 0);
+    EX_CHECK(HcclGetCount(&st, HCCL_DATA_TYPE_INT32, &count));
+    EX_EXPECT(count == 7);
+    EXPECT_RC(HcclGetCount(&st, HCCL_DATA_TYPE_INT64, &count), HCCL_E_PARA);       // 28 bytes are no whole number of those
+    std::vector<int32_t> got(7, -1);
+    std::vector<int32_t> tooSmall(3);
+    EXPECT_RC(HcclImrecv(tooSmall.data(), 3, HCCL_DATA_TYPE_INT32, &msg, &reqs[2]), HCCL_E_MEMORY);
+    EX_EXPECT(msg != nullptr);                             // still the caller's
+    EX_CHECK(HcclImrecv(got.data(), 7, HCCL_DATA_TYPE_INT32, &msg, &reqs[2]));
+    EX_EXPECT(msg == nullptr && got[0] == left + 1000 && got[6] == left + 1000);
+    // the first message is still queued: found by a probe that names neither source nor tag
+    flag = 0;
+    for (int spin = 0; spin < 20000 && !flag; ++spin) {
+        EX_CHECK(HcclImprobe(HCCL_ANY_SOURCE, HCCL_ANY_TAG, comm, &flag, &msg, &st));
+        if (!flag) usleep(500);
+    }
+    EX_EXPECT(flag == 1 && st.srcRank == left && st.tag == 5 && st.count == 400);
+    std::vector<int32_t> big(100, -1);
+    EX_CHECK(HcclImrecv(big.data(), 100, HCCL_DATA_TYPE_INT32, &msg, &reqs[3]));
+    EX_EXPECT(big[99] == left);
+    EX_CHECK(HcclImprobe(left, 5, comm, &flag, &msg, &st));
+    EX_EXPECT(flag == 0 && msg == nullptr);                // nothing left
+    int done = 0, idx[4];
+    HcclStatus sts[4];
+    EX_CHECK(HcclTestSome(4, reqs, &done, idx, sts));
+    EX_EXPECT(done == 4 && reqs[0] == nullptr && reqs[3] == nullptr && sts[0].count == 400 && sts[3].srcRank == left);
+    EX_CHECK(HcclTestSome(4, reqs, &done, idx, sts));
+    EX_EXPECT(done == 0);                                  // each completion is reported once
+    EXPECT_RC(HcclImprobe((int)n, 5, comm, &flag, &msg, &st), HCCL_E_PARA);
+    EX_CHECK(HcclBarrier(comm, nullptr));                  // the wildcard probes above must not meet what follows
+    // an empty message is a message
+    EX_CHECK(HcclIsend(nullptr, 0, HCCL_DATA_TYPE_INT8, left, 9, comm, &reqs[0]));
+    flag = 0;
+    for (int spin = 0; spin < 20000 && !flag; ++spin) {
+        EX_CHECK(HcclImprobe(right, 9, comm, &flag, &msg, &st));
+        if (!flag) usleep(500);
+    }
+    EX_EXPECT(flag == 1 && st.count == 0);
+    EX_CHECK(HcclImrecv(nullptr, 0, HCCL_DATA_TYPE_INT8, &msg, &reqs[1]));
+    EX_CHECK(HcclTestSome(2, reqs, &done, idx, sts));
+    EX_EXPECT(done == 2);
+    int buffer[16];
+    EX_CHECK(HcclRegisterMemory(comm, buffer, sizeof(buffer)));
+    EX_CHECK(HcclUnregisterMemory(comm, buffer));
+    EXPECT_RC(HcclUnregisterMemory(comm, buffer), HCCL_E_NOT_FOUND);
+    if (rank == 0) {
+        EX_CHECK(HcclRegisterGlobalMemory(buffer, sizeof(buffer)));
+        EXPECT_RC(HcclRegisterGlobalMemory(buffer, sizeof(buffer)), HCCL_E_PARA);
+        EX_CHECK(HcclUnregisterGlobalMemory(buffer));
+        EXPECT_RC(HcclUnregisterGlobalMemory(buffer), HCCL_E_NOT_FOUND);
+    }
+    EX_CHECK(HcclBarrier(comm, nullptr));
+
+    // ---- the same between two endpoints without a communicator: rank 0 listens, rank 1 connects
+    if (rank == 0) {
+        HcclConn listener = nullptr, peer = nullptr;
+        EX_CHECK(HcclRawOpen(&listener));
+        EXPECT_RC(HcclRawListen(listener, 4), HCCL_E_PARA);                        // not bound yet
+        HcclAddr addr;
+        std::memset(&addr, 0, sizeof(addr));
+        addr.type = HCCL_ADDR_TYPE_ROCE;
+        EX_CHECK(HcclRawBind(listener, &addr));
+        EX_EXPECT(addr.info.tcp.port != 0);
+        EX_CHECK(HcclRawListen(listener, 4));
+        g_rawPort.store(addr.info.tcp.port);
+        HcclAddr from;
+        EX_CHECK(HcclRawAccept(listener, &from, &peer));
+        EX_EXPECT(from.info.tcp.ipv4Addr != 0);
+        flag = 0;
+        for (int spin = 0; spin < 20000 && !flag; ++spin) {
+            EX_CHECK(HcclRawImprobe(peer, &flag, &msg, &st));
+            if (!flag) usleep(500);
+        }
+        EX_EXPECT(flag == 1 && st.count == 40);
+        EX_CHECK(HcclRawGetCount(&st, HCCL_DATA_TYPE_FP32, &count));
+        EX_EXPECT(count == 10);
+        float head[4] = {0}, tail[6] = {0};
+        void *bufs[2] = {head, tail};
+        int counts[2] = {4, 6};
+        HcclRequest rr = nullptr;
+        EX_CHECK(HcclRawImrecvScatter(bufs, counts, 2, HCCL_DATA_TYPE_FP32, &msg, &rr));
+        EX_EXPECT(head[3] == 3.f && tail[0] == 4.f && tail[5] == 9.f);
+        EX_CHECK(HcclRawIsend(tail, 6, HCCL_DATA_TYPE_FP32, peer, &reqs[0]));      // an answer
+        reqs[1] = rr;
+        EX_CHECK(HcclRawTestSome(2, reqs, &done, idx, sts));
+        EX_EXPECT(done == 2);
+        EX_CHECK(HcclRawClose(peer));
+        EX_CHECK(HcclRawForceClose(listener));
+        EXPECT_RC(HcclRawClose(nullptr), HCCL_E_PTR);
+    } else if (rank == 1) {
+        while (g_rawPort.load() == 0) usleep(1000);
+        HcclConn conn = nullptr;
+        EX_CHECK(HcclRawOpen(&conn));
+        HcclAddr addr;
+        std::memset(&addr, 0, sizeof(addr));
+        addr.type = HCCL_ADDR_TYPE_ROCE;
+        addr.info.tcp.port = (uint16_t)g_rawPort.load();                           // address 0: this host
+        EX_CHECK(HcclRawConnect(conn, &addr));
+        float ten[10];
+        for (int i = 0; i < 10; ++i) ten[i] = (float)i;
+        EX_CHECK(HcclRawIsend(ten, 10, HCCL_DATA_TYPE_FP32, conn, &reqs[0]));
+        flag = 0;
+        for (int spin = 0; spin < 20000 && !flag; ++spin) {
+            EX_CHECK(HcclRawImprobe(conn, &flag, &msg, &st));
+            if (!flag) usleep(500);
+        }
+        EX_EXPECT(flag == 1 && st.count == 24);
+        float back[6] = {0};
+        EX_CHECK(HcclRawImrecv(back, 6, HCCL_DATA_TYPE_FP32, &msg, &reqs[1]));
+        EX_EXPECT(back[0] == 4.f && back[5] == 9.f);
+        EX_CHECK(HcclRawTestSome(2, reqs, &done, idx, sts));
+        EX_EXPECT(done == 2);
+        EX_CHECK(HcclRawClose(conn));
+    }
+    EX_CHECK(HcclBarrier(comm, nullptr));
+}
+
 int main(int argc, char **argv)
 {
     const uint32_t n = argc > 1 ? (uint32_t)std::atoi(argv[1]) : 4;
@@ -1039,6 +1212,7 @@ int main(int argc, char **argv)
         Teams(rank, n, comm);
         Diagnostics(rank, n, comm);
         Launch(rank, n, comm);
+        Messages(rank, n, comm);
     });
     EdgeCases(n);
     OtherWaysToStart(n);
