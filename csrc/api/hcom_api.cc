@@ -2,6 +2,9 @@
 // translation, gradient-fusion split strategies and operators addressed by group name.
 // Reference: framework/hcom/hcom.cc, hcom_common.cc, gradient_segment/gradient_segment.cc.
 #include <cstring>
+#include <vector>
+#include <string>
+#include <atomic>
 #include <map>
 #include <mutex>
 
@@ -9,6 +12,10 @@
 #include "../core/log.h"
 #include "hccl/hccl.h"
 #include "hccl/hccl_res.h"
+#include "../coll/ops.h"
+#include "hccl/hccl_diag.h"
+#include "hccl/hccl_mc2.h"
+#include "hccl/hccl_msg.h"
 #include "hccl/hcom.h"
 
 using namespace hc;
@@ -410,5 +417,160 @@ HcclResult HcomReduceScatterV(const char *tag, void *sendBuf, const void *sendCo
 HcclResult HcomAlltoAllVC(const void *sendBuf, const void *sendCountMatrix, HcclDataType sendType, const void *recvBuf, HcclDataType recvType, const char *group,
                           aclrtStream stream, const char *tag)
 { HCOM_COMM(group); return HcclAlltoAllVC(sendBuf, sendCountMatrix, sendType, recvBuf, recvType, (HcclComm)c, stream); }
+
+// ------------------------------------------------------------------ further calls with a meaning here
+
+HcclResult HcomInitByString(const char *rankTableM, const char *identify)
+{
+    CHK_PTR_NULL(rankTableM); CHK_PTR_NULL(identify);
+    char *end = nullptr;
+    unsigned long rank = strtoul(identify, &end, 10);
+    if (end == identify || *end != 0) { RPT_ERR("EI0003", "HcomInitByString: \"%s\" is not a rank id", identify); return HCCL_E_PARA; }
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (g_groups.count(HCCL_WORLD_GROUP)) return HCCL_E_PARA;
+    }
+    HcclComm comm = nullptr;
+    CHK_RET(HcclInitComm(rankTableM, (uint32_t)rank, nullptr, &comm));
+    CHK_RET(HcomInitByComm(comm));
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_groups[HCCL_WORLD_GROUP].owned = true;
+    return HCCL_SUCCESS;
+}
+
+bool HcomFindGroup(const char *group)
+{
+    if (!group) return false;
+    std::lock_guard<std::mutex> lk(g_mu);
+    return g_groups.count(group) != 0;
+}
+
+HcclResult HcomGetRankSizeEx(const char *group, uint32_t *rankSize, uint32_t flag)
+{
+    (void)flag;
+    return HcomGetRankSize(group, rankSize);
+}
+
+HcclResult HcomReleaseSubComms(void)
+{
+    std::vector<GroupRec> gone;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        for (auto it = g_groups.begin(); it != g_groups.end();) {
+            if (it->first == HCCL_WORLD_GROUP) { ++it; continue; }
+            gone.push_back(it->second);
+            it = g_groups.erase(it);
+        }
+    }
+    HcclResult first = HCCL_SUCCESS;
+    for (auto &g : gone)
+        if (g.owned) { HcclResult r = HcclCommDestroy((HcclComm)g.comm); if (r != HCCL_SUCCESS && first == HCCL_SUCCESS) first = r; }
+    return first;
+}
+
+HcclResult HcomCreateCommCCLbuffer(const char *group)
+{
+    Comm *c;
+    CHK_RET(CommOf(group, &c));
+    return c->CclBuffer() ? HCCL_SUCCESS : HCCL_E_MEMORY;
+}
+
+static std::atomic<int> g_workflowMode{(int)HCCL_WORKFLOW_MODE_OP_BASE};
+HcclWorkflowMode HcomGetWorkflowMode(void) { return (HcclWorkflowMode)g_workflowMode.load(); }
+HcclResult HcomSetWorkflowMode(HcclWorkflowMode mode)
+{
+    if (mode != HCCL_WORKFLOW_MODE_OPS_KERNEL_INFO_LIB && mode != HCCL_WORKFLOW_MODE_OP_BASE) return HCCL_E_PARA;
+    g_workflowMode.store((int)mode);
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcomSetProfilingMode(HcomProfilingMode profilingMode, const char *profilingOption)
+{
+    (void)profilingOption;
+    if (profilingMode != PROFILING_CLOSE && profilingMode != PROFILING_OPEN) return HCCL_E_PARA;
+    std::vector<Comm *> comms;
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        for (auto &kv : g_groups) comms.push_back(kv.second.comm);
+    }
+    for (Comm *c : comms) CHK_RET(HcclDiagSetProfiling((HcclComm)c, profilingMode == PROFILING_OPEN));
+    return HCCL_SUCCESS;
+}
+
+static HcclResult Describe(int64_t comm, const char *group, uint64_t count, void *counts, HcclDataType dataType, HcclReduceOp op, HcclCMDType opType,
+                           int32_t aivCoreLimit, Selection *sel, int *ctas)
+{
+    Comm *c = comm ? AsComm((HcclComm)(intptr_t)comm) : nullptr;
+    if (!c) CHK_RET(CommOf(group, &c));
+    CHK_RET(DescribeSelection(c, opType, count, dataType, op, counts != nullptr, sel, ctas));
+    if (ctas && aivCoreLimit > 0 && *ctas > aivCoreLimit) *ctas = aivCoreLimit;
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcomSelectAlg(int64_t comm, const char *group, uint64_t count, void *counts, HcclDataType dataType, HcclReduceOp op, HcclCMDType opType,
+                         int32_t aivCoreLimit, bool *ifAiv, char *algName)
+{
+    CHK_PTR_NULL(ifAiv); CHK_PTR_NULL(algName);
+    Selection sel;
+    CHK_RET(Describe(comm, group, count, counts, dataType, op, opType, aivCoreLimit, &sel, nullptr));
+    *ifAiv = sel.engine != Engine::HOST;
+    snprintf(algName, 128, "%s", sel.name.c_str());
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcomCalcAivCoreNum(const char *group, HcclCMDType opType, uint64_t count, void *counts, HcclDataType dataType, int32_t aivCoreLimit, char *algName,
+                              uint32_t *numBlocks)
+{
+    CHK_PTR_NULL(numBlocks);
+    Selection sel;
+    int ctas = 0;
+    CHK_RET(Describe(0, group, count, counts, dataType, HCCL_REDUCE_SUM, opType, aivCoreLimit, &sel, &ctas));
+    if (algName) snprintf(algName, 128, "%s", sel.name.c_str());
+    *numBlocks = (uint32_t)ctas;
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcomSetAivCoreLimit(const char *group, uint32_t aivCoreLimit)
+{
+    Comm *c;
+    CHK_RET(CommOf(group, &c));
+    __atomic_store_n(&c->ctaLimit, aivCoreLimit, __ATOMIC_RELAXED);
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcomGenerateCclOpTag(const char *opType, int64_t hcomComm, const char *group, char *sTag)
+{
+    CHK_PTR_NULL(opType); CHK_PTR_NULL(sTag);
+    (void)hcomComm;
+    static std::mutex mu;
+    static std::map<std::string, uint64_t> next;        // every rank issues its operators in the same order: the counters agree
+    const std::string key = std::string(opType) + "_" + (group ? group : HCCL_WORLD_GROUP);
+    uint64_t n;
+    {
+        std::lock_guard<std::mutex> lk(mu);
+        n = next[key]++;
+    }
+    snprintf(sTag, 256, "%s_%llu", key.c_str(), (unsigned long long)n);
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcomCreateComResourceByComm(HcclComm comm, uint32_t streamMode, bool isOpbaseMode, void **commContext)
+{
+    (void)isOpbaseMode;
+    return HcclAllocComResource(comm, streamMode, commContext);
+}
+HcclResult HcomGetAicpuOpStreamNotify(const char *group, aclrtStream *opStream, uint8_t aicpuNotifyNum, void **aicpuNotify)
+{
+    Comm *c;
+    CHK_RET(CommOf(group, &c));
+    return HcclGetAicpuOpStreamAndNotify((HcclComm)c, opStream, aicpuNotifyNum, aicpuNotify);
+}
+HcclResult HcomMc2AiCpuStreamAllocAndGet(const char *group, uint32_t streamMode, aclrtStream *aiCpuStream)
+{
+    (void)streamMode;
+    Comm *c;
+    CHK_RET(CommOf(group, &c));
+    return HcclGetAicpuOpStreamAndNotify((HcclComm)c, aiCpuStream, 0, nullptr);
+}
 
 }  // extern "C"

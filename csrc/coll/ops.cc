@@ -74,6 +74,8 @@ int PickCtas(Comm *c, const Selection &sel, uint64_t bytesPerRank)
     else if (bytesPerRank >= (2ull << 20)) ctas = 48;
     else ctas = (int)std::min<uint64_t>(32, std::max<uint64_t>(1, (bytesPerRank + (16 << 10) - 1) / (16 << 10)));
     if (cap > 0) ctas = std::min(ctas, cap);
+    const uint32_t own = __atomic_load_n(&c->ctaLimit, __ATOMIC_RELAXED);     // this communicator's share of the SMs
+    if (own > 0) ctas = std::min(ctas, (int)own);
     if (forced > 0) ctas = forced;
     if (c->emuSameDevice) ctas = std::min(ctas, 4);
     return std::max(1, std::min(ctas, HC_MAX_CTAS));
@@ -669,6 +671,22 @@ HcclResult LaunchBarrierIfNeeded(Comm *c, void *stream)
     CollArgs a;
     FillBase(c, d, a);
     return Launch(c, FK_BARRIER, a, 1, stream);
+}
+
+HcclResult DescribeSelection(Comm *c, HcclCMDType cmd, uint64_t count, HcclDataType dtype, HcclReduceOp op, bool variableCounts, Selection *sel, int *ctas)
+{
+    SelectInput si;
+    si.cmd = cmd; si.nRanks = c->nRanks; si.dtype = dtype; si.op = op;
+    si.bytes = count * DtypeSize(dtype);
+    si.opExpansionMode = c->cfg.opExpansionMode;
+    si.deterministic = __atomic_load_n(&c->cfg.deterministic, __ATOMIC_RELAXED);
+    si.cuda = c->plat->kind() == PlatKind::CUDA;
+    si.singleDomain = c->nRanks <= HC_KERNEL_MAX_RANKS && c->graph.SingleNvlinkDomain();
+    si.nvlsAvailable = c->mcBase != nullptr;
+    si.variableCounts = variableCounts;
+    CHK_RET(SelectAlgorithm(si, AlgoConfigOf(c), sel));
+    if (ctas) *ctas = (sel->engine == Engine::HOST) ? 0 : PickCtas(c, *sel, si.bytes);
+    return HCCL_SUCCESS;
 }
 
 const AlgoConfig &AlgoConfigOf(Comm *c)

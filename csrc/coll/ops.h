@@ -66,6 +66,9 @@ void GroupQueue(std::function<HcclResult()> job, uint64_t volume, bool isP2p, Co
 // Parsed per-communicator algorithm configuration (cached on the communicator name).
 const AlgoConfig &AlgoConfigOf(Comm *c);
 
+// What the communicator would do with such an operator: the selector's choice and the CTAs its kernel would use.
+HcclResult DescribeSelection(Comm *c, HcclCMDType cmd, uint64_t count, HcclDataType dtype, HcclReduceOp op, bool variableCounts, Selection *sel, int *ctas);
+
 // Launches one specialised kernel for this rank, handling the shared-GPU rendezvous.
 struct FastLaunch;
 HcclResult LaunchForRank(Comm *c, FastLaunch &l);

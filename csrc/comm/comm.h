@@ -187,6 +187,7 @@ struct Comm {
     std::vector<std::unique_ptr<RegMem>> regMems;
     std::vector<std::unique_ptr<Window>> windows;
     uint64_t teamSyncUsed = 0;               // bytes of HC_OFF_TEAM_SYNC handed out
+    uint32_t ctaLimit = 0;                   // upper bound of CTAs per collective kernel of this communicator (HcomSetAivCoreLimit); 0 = none
     uint32_t subCommSeq = 0;
 
     // ---- diagnostics

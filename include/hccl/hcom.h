@@ -6,6 +6,8 @@
 #ifndef HCOM_H_
 #define HCOM_H_
 
+#include <stdbool.h>
+
 #include "hccl_rank_graph.h"
 #include "hccl_types.h"
 
@@ -74,6 +76,45 @@ HcclResult HcomReduceScatterV(const char *tag, void *sendBuf, const void *sendCo
                               uint64_t recvCount, HcclDataType dataType, HcclReduceOp op, const char *group, aclrtStream stream);
 HcclResult HcomAlltoAllVC(const void *sendBuf, const void *sendCountMatrix, HcclDataType sendType, const void *recvBuf,
                           HcclDataType recvType, const char *group, aclrtStream stream, const char *tag);
+
+/* ---- further calls of the reference's hcom.h that have a meaning here (pkg_inc/legacy/hccl/hcom.h:205-352) ---- */
+
+/* The world group from a rank table held in memory; `identify` is this process's rank as a decimal string. */
+HcclResult HcomInitByString(const char *rankTableM, const char *identify);
+bool HcomFindGroup(const char *group);
+HcclResult HcomGetRankSizeEx(const char *group, uint32_t *rankSize, uint32_t flag);
+HcclResult HcomReleaseSubComms(void);                 /* destroys every group but the world group */
+HcclResult HcomCreateCommCCLbuffer(const char *group); /* the buffer exists with the group: checks the name */
+
+/* How operators are issued: one by one by the caller (operator base) or from a compiled graph.  Kept per process. */
+typedef enum {
+    HCCL_WORKFLOW_MODE_OPS_KERNEL_INFO_LIB = 0,
+    HCCL_WORKFLOW_MODE_OP_BASE = 1,
+    HCCL_WORKFLOW_MODE_RESERVED = 255
+} HcclWorkflowMode;
+HcclWorkflowMode HcomGetWorkflowMode(void);
+HcclResult HcomSetWorkflowMode(HcclWorkflowMode mode);
+
+typedef enum { PROFILING_CLOSE = 0, PROFILING_OPEN = 1, PROFILING_RESERVED } HcomProfilingMode;
+/* Switches operator records and device timestamps on or off for every group. */
+HcclResult HcomSetProfilingMode(HcomProfilingMode profilingMode, const char *profilingOption);
+
+/* What the selector would pick for such an operator on the group: ifAiv tells whether a kernel of the SM engine runs it,
+ * algName (at least 128 bytes) receives "operator/algorithm@engine".  counts != NULL marks a variable-count operator. */
+HcclResult HcomSelectAlg(int64_t comm, const char *group, uint64_t count, void *counts, HcclDataType dataType, HcclReduceOp op,
+                         HcclCMDType opType, int32_t aivCoreLimit, bool *ifAiv, char *algName);
+/* The CTAs that kernel would be launched with (0 on the host engine). */
+HcclResult HcomCalcAivCoreNum(const char *group, HcclCMDType opType, uint64_t count, void *counts, HcclDataType dataType,
+                              int32_t aivCoreLimit, char *algName, uint32_t *numBlocks);
+/* Upper bound of CTAs per collective kernel of the group, so that compute kernels keep their share of the SMs; 0 lifts it. */
+HcclResult HcomSetAivCoreLimit(const char *group, uint32_t aivCoreLimit);
+/* A tag that is the same on every rank for the n-th operator of a kind on a group: "<opType>_<group>_<n>". */
+HcclResult HcomGenerateCclOpTag(const char *opType, int64_t hcomComm, const char *group, char *sTag);
+
+/* Resources of fused compute + communication kernels, by group name (hccl_mc2.h). */
+HcclResult HcomCreateComResourceByComm(HcclComm comm, uint32_t streamMode, bool isOpbaseMode, void **commContext);
+HcclResult HcomGetAicpuOpStreamNotify(const char *group, aclrtStream *opStream, uint8_t aicpuNotifyNum, void **aicpuNotify);
+HcclResult HcomMc2AiCpuStreamAllocAndGet(const char *group, uint32_t streamMode, aclrtStream *aiCpuStream);
 
 #ifdef __cplusplus
 }

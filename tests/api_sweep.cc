@@ -974,6 +974,13 @@ static void OtherWaysToStart(uint32_t n)
     EX_EXPECT(res == 3.f);
     EX_CHECK(HcomDestroy());
     unlink(solo.c_str());
+    // and from the table as text, with the rank as a string
+    const std::string soloText = MakeRankTable(1, "sweep_solo_text");
+    EXPECT_RC(HcomInitByString(soloText.c_str(), "zero"), HCCL_E_PARA);
+    EX_CHECK(HcomInitByString(soloText.c_str(), "0"));
+    EX_EXPECT(HcomFindGroup(HCCL_WORLD_GROUP));
+    EX_CHECK(HcomDestroy());
+    EX_EXPECT(!HcomFindGroup(HCCL_WORLD_GROUP));
 
     // a restored process image: what is left of its communicators is invalid
     HcclComm last = nullptr;

@@ -527,8 +527,42 @@ def main():
             assert lib.HcomReduceScatterV(b"t", P(full), P(rc_), P(rd), P(out), U64(me + 1), FP32, SUM, group, None) == 0
             want = sum(np.arange(int(rc_.sum()), dtype=np.float32) + r for r in ranks)[int(rd[me]):int(rd[me]) + me + 1]
             assert (out == want).all()
+        # what the selector would do, CTA budget, tags, workflow and profiling switches, resources by group name
+        lib.HcomFindGroup.restype = ctypes.c_bool
+        assert lib.HcomFindGroup(W) and not lib.HcomFindGroup(b"nowhere") and lib.HcomFindGroup(G) == inside
+        size = U32()
+        assert lib.HcomGetRankSizeEx(W, ctypes.byref(size), U32(0)) == 0 and size.value == world
+        is_kernel, alg = ctypes.c_bool(True), ctypes.create_string_buffer(128)
+        assert lib.HcomSelectAlg(ctypes.c_int64(0), W, U64(1 << 20), None, FP32, SUM, 2, ctypes.c_int32(0), ctypes.byref(is_kernel), alg) == 0
+        assert not is_kernel.value and alg.value.startswith(b"allreduce/") and alg.value.endswith(b"@host"), alg.value      # the simulator
+        assert lib.HcomSelectAlg(ctypes.c_int64(comm.handle), None, U64(100), None, FP32, SUM, 6, ctypes.c_int32(0), ctypes.byref(is_kernel), alg) == 0
+        assert alg.value.startswith(b"allgather/")
+        blocks = U32(77)
+        assert lib.HcomCalcAivCoreNum(W, 2, U64(1 << 20), None, FP32, ctypes.c_int32(8), alg, ctypes.byref(blocks)) == 0 and blocks.value == 0
+        assert lib.HcomSetAivCoreLimit(W, U32(16)) == 0 and lib.HcomSetAivCoreLimit(W, U32(0)) == 0
+        assert lib.HcomSetAivCoreLimit(b"nowhere", U32(16)) == 6
+        t0, t1 = ctypes.create_string_buffer(256), ctypes.create_string_buffer(256)
+        assert lib.HcomGenerateCclOpTag(b"HcomAllReduce", ctypes.c_int64(0), W, t0) == 0
+        assert lib.HcomGenerateCclOpTag(b"HcomAllReduce", ctypes.c_int64(0), W, t1) == 0
+        assert t0.value == b"HcomAllReduce_hccl_world_group_0" and t1.value == b"HcomAllReduce_hccl_world_group_1"
+        lib.HcomGetWorkflowMode.restype = ctypes.c_int
+        assert lib.HcomGetWorkflowMode() == 1
+        assert lib.HcomSetWorkflowMode(0) == 0 and lib.HcomGetWorkflowMode() == 0
+        assert lib.HcomSetWorkflowMode(7) == 1 and lib.HcomSetWorkflowMode(1) == 0
+        assert lib.HcomSetProfilingMode(1, None) == 0
+        x = np.ones(16, np.float32)
+        assert lib.HcomAllReduce(b"t", P(x), P(x), U64(16), FP32, SUM, W, None) == 0 and (x == world).all()
+        assert "allreduce" in comm.dump().lower()
+        assert lib.HcomSetProfilingMode(0, None) == 0 and lib.HcomSetProfilingMode(2, None) == 1
+        assert lib.HcomCreateCommCCLbuffer(W) == 0 and lib.HcomCreateCommCCLbuffer(b"nowhere") == 6
+        ctx, stream = V(), V(1)
+        assert lib.HcomCreateComResourceByComm(V(comm.handle), U32(0), ctypes.c_bool(True), ctypes.byref(ctx)) == 0 and ctx.value
+        notify = (V * 2)()
+        assert lib.HcomGetAicpuOpStreamNotify(W, ctypes.byref(stream), ctypes.c_uint8(2), notify) == 0 and notify[0] and notify[1] == notify[0] + 8
+        assert lib.HcomMc2AiCpuStreamAllocAndGet(W, U32(0), ctypes.byref(stream)) == 0
         if inside:
-            assert lib.HcomDestroyGroup(G) == 0
+            assert lib.HcomReleaseSubComms() == 0              # collective over the members: the group's communicator goes
+            assert not lib.HcomFindGroup(G)
             assert lib.HcomDestroyGroup(G) == 6
         comm.barrier()
         assert lib.HcomDestroy() == 0
