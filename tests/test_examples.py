@@ -11,6 +11,7 @@ EXAMPLES = [
     ("01_communicators/root_info_threads.cc", ["4"]),
     ("01_communicators/root_info_processes.cc", ["3"]),
     ("01_communicators/rank_table_processes.cc", ["3"]),
+    ("01_communicators/init_all_one_process.cc", ["4"]),
     ("03_op_dev/mesh_send_recv.cc", ["4"]),
     ("03_op_dev/mesh_send_recv.cc", ["2"]),
     ("04_team_one_sided/team_signal_put.cc", ["4"]),
