@@ -325,6 +325,44 @@ class Communicator:
         check(self._lib.HcclCommSymWinDeregister(win), "HcclCommSymWinDeregister")
         check(self._lib.HcommMemFree(ptr), "HcommMemFree")
 
+    # ---------------------------------------------------------------- host messages over the control plane
+    def send_bytes(self, data: bytes, dst: int, tag: int = 0):
+        """Sends a small host message (control data, not tensors) to rank ``dst``; complete when the call returns."""
+        buf = (ctypes.c_char * max(1, len(data))).from_buffer_copy(data if data else b"\0")
+        req = ctypes.c_void_p()
+        check(self._lib.HcclIsend(buf, len(data), _lib.INT8, dst, tag, self._h, ctypes.byref(req)), "HcclIsend")
+        done = ctypes.c_int()
+        check(self._lib.HcclTestSome(1, ctypes.byref(req), ctypes.byref(done), None, None), "HcclTestSome")
+
+    def probe_bytes(self, src: Optional[int] = None, tag: Optional[int] = None):
+        """Takes the oldest queued message from ``src`` with ``tag`` (``None``: any) without waiting.  Returns
+        ``(source, tag, bytes)`` or ``None`` when nothing has arrived."""
+        class _Status(ctypes.Structure):
+            _fields_ = [("srcRank", ctypes.c_int), ("tag", ctypes.c_int), ("error", ctypes.c_int), ("cancelled", ctypes.c_int), ("count", ctypes.c_int)]
+        flag, msg, st = ctypes.c_int(), ctypes.c_void_p(), _Status()
+        check(self._lib.HcclImprobe(-1 if src is None else src, -1 if tag is None else tag, self._h, ctypes.byref(flag), ctypes.byref(msg), ctypes.byref(st)),
+              "HcclImprobe")
+        if not flag.value:
+            return None
+        buf = ctypes.create_string_buffer(max(1, st.count))
+        req = ctypes.c_void_p()
+        check(self._lib.HcclImrecv(buf, st.count, _lib.INT8, ctypes.byref(msg), ctypes.byref(req)), "HcclImrecv")
+        done = ctypes.c_int()
+        check(self._lib.HcclTestSome(1, ctypes.byref(req), ctypes.byref(done), None, None), "HcclTestSome")
+        return st.srcRank, st.tag, buf.raw[:st.count]
+
+    def recv_bytes(self, src: Optional[int] = None, tag: Optional[int] = None, timeout: float = 30.0):
+        """Waits for a message as :meth:`probe_bytes` describes it; ``TimeoutError`` after ``timeout`` seconds."""
+        import time
+        deadline = time.time() + timeout
+        while True:
+            got = self.probe_bytes(src, tag)
+            if got is not None:
+                return got
+            if time.time() > deadline:
+                raise TimeoutError(f"no message from rank {src} with tag {tag} within {timeout} s")
+            time.sleep(0.0005)
+
     def destroy(self):
         if self._h:
             regs = getattr(self, "_registered", {})

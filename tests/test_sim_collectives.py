@@ -231,3 +231,31 @@ def test_rendezvous_survives_connections_that_are_not_ranks(monkeypatch):
     for s in strays:
         s.close()
     destroy(comms)
+
+
+def test_host_messages_between_ranks(monkeypatch):
+    """Control messages over the control plane: exact and wildcard probes, order per (source, tag), an empty message."""
+    import pickle
+    sim_env(monkeypatch)
+    n = 4
+    comms = make_comms(n)
+    out = [None] * n
+
+    def body(r):
+        c = comms[r]
+        if r == 0:
+            got = sorted(c.recv_bytes() for _ in range(2 * (n - 1)))            # from anybody, any tag
+            out[r] = got
+            for q in range(1, n):
+                c.send_bytes(pickle.dumps({"to": q, "plan": [q] * 3}), q, tag=7)
+        else:
+            c.send_bytes(b"first from %d" % r, 0, tag=1)
+            c.send_bytes(b"", 0, tag=2)
+            assert c.probe_bytes(src=(r % (n - 1)) + 1 if (r % (n - 1)) + 1 != r else None, tag=99) is None     # nothing with that tag
+            src, tag, data = c.recv_bytes(src=0, tag=7)
+            out[r] = (src, tag, pickle.loads(data))
+    run_ranks(n, body)
+    assert out[0] == sorted([(q, 1, b"first from %d" % q) for q in range(1, n)] + [(q, 2, b"") for q in range(1, n)])
+    for q in range(1, n):
+        assert out[q] == (0, 7, {"to": q, "plan": [q] * 3})
+    destroy(comms)
