@@ -732,6 +732,48 @@ def main():
         lib.HcommExceptionUnregisterCallback(exc_cb)
         lib.HcclProfilingSetSink(None, None)
         return 0
+    elif scenario == "op_retry_exhausted":
+        # Every attempt loses a flag write: after the configured number of rounds the agents give up and the operator
+        # ends with HCCL_E_OPRETRY_FAIL on every rank.
+        import ctypes
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+
+        class RetryStats(ctypes.Structure):
+            _fields_ = [("enabled", ctypes.c_uint32), ("maxCnt", ctypes.c_uint32), ("holdTimeMs", ctypes.c_uint32), ("intervalMs", ctypes.c_uint32),
+                        ("requests", ctypes.c_uint64), ("rounds", ctypes.c_uint64), ("succeeded", ctypes.c_uint64), ("failed", ctypes.c_uint64)]
+
+        def stats():
+            st = RetryStats()
+            assert lib.HcclCommGetOpRetryStats(ctypes.c_void_p(comm.handle), ctypes.byref(st)) == 0
+            return st
+        x = np.full(3000, rank + 1, np.float32)
+        y = np.zeros_like(x)
+        comm.all_reduce(x, y)
+        assert (y == world * (world + 1) / 2).all()
+        if rank == 1:
+            lib.HcommToolSimWithholdFlags(100000)
+        failed = 0
+        try:
+            comm.all_reduce(x, y)
+        except hb.HcclError as e:
+            failed = e.code
+        deadline = time.time() + 90
+        while stats().failed < 1 and comm.async_error() == 0 and time.time() < deadline:
+            time.sleep(0.05)
+        if rank == 1:
+            lib.HcommToolSimWithholdFlags(0)
+        st = stats()
+        print(f"rank {rank}: operator ended with {failed}, async error {comm.async_error()}, rounds {st.rounds}, failed {st.failed}, succeeded {st.succeeded}", flush=True)
+        assert st.failed >= 1 and st.succeeded == 0 and st.rounds >= 2, (st.rounds, st.failed, st.succeeded)
+        assert comm.async_error() == 23, comm.async_error()            # HCCL_E_OPRETRY_FAIL
+        assert failed in (0, 23), failed                               # the rank whose own part completed returned before the verdict
+        try:
+            comm.all_reduce(x, y)
+            raise AssertionError("an operator ran on a communicator whose retries were exhausted")
+        except hb.HcclError as e:
+            assert e.code == 23, e.code
+        return 0
     elif scenario == "peer_exit":
         # One rank leaves between steps; the others learn it from the control plane before their next launch.
         x = np.ones(10, np.float32) if not use_cuda else None

@@ -76,3 +76,11 @@ def test_operator_retry_after_a_withheld_flag_and_the_dfx_callbacks():
     codes, outs = launch("op_retry", 3, env, timeout=180)
     assert codes == [0, 0, 0], "\n".join(outs)
     assert any("retry ok after" in o for o in outs)
+
+
+def test_operator_retry_gives_up_after_the_configured_rounds():
+    env = {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCCL_OP_RETRY_ENABLE": "1", "HCCL_OP_RETRY_PARAMS": "MaxCnt:2,HoldTime:200,IntervalTime:100",
+           "HCCL_EXEC_TIMEOUT": "2"}
+    codes, outs = launch("op_retry_exhausted", 3, env, timeout=180)
+    assert codes == [0, 0, 0], "\n".join(outs)
+    assert all("failed 1, succeeded 0" in o for o in outs)
