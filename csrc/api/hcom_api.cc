@@ -1,6 +1,9 @@
 // hcom_api.cc - named-group API (include/hccl/hcom.h): the world group, sub groups by name, rank
 // translation, gradient-fusion split strategies and operators addressed by group name.
 // Reference: framework/hcom/hcom.cc, hcom_common.cc, gradient_segment/gradient_segment.cc.
+#include <arpa/inet.h>
+#include <unistd.h>
+#include <algorithm>
 #include <cstring>
 #include <vector>
 #include <string>
@@ -9,7 +12,10 @@
 #include <mutex>
 
 #include "../comm/comm.h"
+#include "../core/env.h"
 #include "../core/log.h"
+#include "../core/net.h"
+#include "../plat/platform.h"
 #include "hccl/hccl.h"
 #include "hccl/hccl_res.h"
 #include "../coll/ops.h"
@@ -432,6 +438,104 @@ HcclResult HcomInitByString(const char *rankTableM, const char *identify)
     }
     HcclComm comm = nullptr;
     CHK_RET(HcclInitComm(rankTableM, (uint32_t)rank, nullptr, &comm));
+    CHK_RET(HcomInitByComm(comm));
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_groups[HCCL_WORLD_GROUP].owned = true;
+    return HCCL_SUCCESS;
+}
+
+namespace {
+struct MasterJoin { uint32_t magic; uint32_t ip; int32_t device; uint32_t pid; };
+struct MasterAnswer { uint32_t magic; uint32_t rank; HcclRootInfo info; };
+constexpr uint32_t kJoinMagic = 0x4e494f4a, kAnswerMagic = 0x57534e41;   // "JOIN", "ANSW"
+
+bool ParseNumber(const char *s, long lo, long hi, long *out)
+{
+    if (!s || !*s) return false;
+    char *end = nullptr;
+    long v = strtol(s, &end, 10);
+    if (*end != 0 || v < lo || v > hi) return false;
+    *out = v;
+    return true;
+}
+}  // namespace
+
+HcclResult HcomInitByMasterInfo(const char *masterIp, const char *masterPort, const char *masterDeviceId, const char *rankSize, const char *rankIp)
+{
+    CHK_PTR_NULL(masterIp); CHK_PTR_NULL(masterPort); CHK_PTR_NULL(masterDeviceId); CHK_PTR_NULL(rankSize); CHK_PTR_NULL(rankIp);
+    long port = 0, masterDev = 0, n = 0;
+    struct in_addr mine4, master4;
+    if (!ParseNumber(masterPort, 1, 65535, &port) || !ParseNumber(masterDeviceId, 0, 1 << 20, &masterDev) || !ParseNumber(rankSize, 1, 1 << 20, &n) ||
+        inet_pton(AF_INET, masterIp, &master4) != 1 || inet_pton(AF_INET, rankIp, &mine4) != 1) {
+        RPT_ERR("EI0003", "HcomInitByMasterInfo: master %s:%s device %s, %s ranks, own address %s - not all of these are numbers and IPv4 addresses", masterIp,
+                masterPort, masterDeviceId, rankSize, rankIp);
+        return HCCL_E_PARA;
+    }
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (g_groups.count(HCCL_WORLD_GROUP)) { RPT_ERR("EI0003", "the world group is already initialised"); return HCCL_E_PARA; }
+    }
+    Platform *P = DefaultPlatform();
+    MasterJoin me{kJoinMagic, mine4.s_addr, P ? P->CurrentDevice() : 0, (uint32_t)getpid()};
+    const int64_t deadline = net::NowMs() + (int64_t)EnvConfig::Get().connectTimeoutSec.value * 1000;
+    MasterAnswer answer;
+    memset(&answer, 0, sizeof(answer));
+
+    int listenFd = -1, listenPort = 0;
+    // Whoever sits at the master's address on the master's device serves; if the port is taken there, somebody else does.
+    if (mine4.s_addr == master4.s_addr && me.device == (int32_t)masterDev) {
+        if (net::TcpListen(masterIp, (int)port, (int)port, &listenFd, &listenPort) != HCCL_SUCCESS) listenFd = -1;
+    }
+    if (listenFd >= 0) {
+        struct Entry { MasterJoin join; int fd; uint32_t arrival; };
+        std::vector<Entry> entries{{me, -1, 0}};
+        HcclResult r = HCCL_SUCCESS;
+        while (entries.size() < (size_t)n && r == HCCL_SUCCESS) {
+            int fd = -1;
+            r = net::TcpAccept(listenFd, deadline, &fd, nullptr);
+            if (r != HCCL_SUCCESS) break;
+            MasterJoin j;
+            if (net::RecvAll(fd, &j, sizeof(j), net::NowMs() + 3000) != HCCL_SUCCESS || j.magic != kJoinMagic) { net::Close(fd); continue; }   // not one of ours
+            entries.push_back({j, fd, (uint32_t)entries.size()});
+        }
+        if (r == HCCL_SUCCESS) r = HcclGetRootInfo(&answer.info);
+        if (r == HCCL_SUCCESS) {
+            std::stable_sort(entries.begin(), entries.end(), [](const Entry &a, const Entry &b) {
+                if (a.join.ip != b.join.ip) return ntohl(a.join.ip) < ntohl(b.join.ip);
+                if (a.join.device != b.join.device) return a.join.device < b.join.device;
+                return a.arrival < b.arrival;
+            });
+            answer.magic = kAnswerMagic;
+            uint32_t myRank = 0;
+            for (uint32_t i = 0; i < entries.size(); ++i) {
+                if (entries[i].fd < 0) { myRank = i; continue; }
+                answer.rank = i;
+                if (net::SendAll(entries[i].fd, &answer, sizeof(answer)) != HCCL_SUCCESS) r = HCCL_E_TCP_TRANSFER;
+            }
+            answer.rank = myRank;
+        } else {
+            RPT_ERR("EI0015", "HcomInitByMasterInfo: %zu of %ld processes reached the master at %s:%ld in time", entries.size(), n, masterIp, port);
+        }
+        for (auto &e : entries) net::Close(e.fd);
+        net::Close(listenFd);
+        if (r != HCCL_SUCCESS) return r;
+    } else {
+        int fd = -1;
+        HcclResult r = net::TcpConnect(masterIp, (int)port, deadline, &fd);
+        if (r != HCCL_SUCCESS) { RPT_ERR("EI0006", "HcomInitByMasterInfo: nobody answers at %s:%ld", masterIp, port); return HCCL_E_TIMEOUT; }
+        r = net::SendAll(fd, &me, sizeof(me));
+        if (r == HCCL_SUCCESS) r = net::RecvAll(fd, &answer, sizeof(answer), deadline);
+        net::Close(fd);
+        if (r != HCCL_SUCCESS || answer.magic != kAnswerMagic) {
+            RPT_ERR("EI0015", "HcomInitByMasterInfo: the master at %s:%ld did not hand out a rank", masterIp, port);
+            return r != HCCL_SUCCESS ? r : HCCL_E_INTERNAL;
+        }
+    }
+    HcclComm comm = nullptr;
+    HcclCommConfig cfg;
+    HcclCommConfigInit(&cfg);
+    snprintf(cfg.hcclCommName, sizeof(cfg.hcclCommName), "%s", HCCL_WORLD_GROUP);
+    CHK_RET(HcclCommInitRootInfoConfig((uint32_t)n, &answer.info, answer.rank, &cfg, &comm));
     CHK_RET(HcomInitByComm(comm));
     std::lock_guard<std::mutex> lk(g_mu);
     g_groups[HCCL_WORLD_GROUP].owned = true;

@@ -81,6 +81,13 @@ HcclResult HcomAlltoAllVC(const void *sendBuf, const void *sendCountMatrix, Hccl
 
 /* The world group from a rank table held in memory; `identify` is this process's rank as a decimal string. */
 HcclResult HcomInitByString(const char *rankTableM, const char *identify);
+/* The world group when only the master's address is known: every process calls this with the same master address, port,
+ * master device and rank count, and with its own address.  The process that sits at the master's address on the master's
+ * device collects the others, numbers all of them (by address, then device, then arrival) and hands out the ranks together
+ * with a root-info ticket; then everybody joins as with HcclCommInitRootInfo.  All arguments are decimal strings or
+ * dotted addresses, as the reference passes them (pkg_inc/legacy/hccl/hcom.h:244). */
+HcclResult HcomInitByMasterInfo(const char *masterIp, const char *masterPort, const char *masterDeviceId, const char *rankSize,
+                                const char *rankIp);
 bool HcomFindGroup(const char *group);
 HcclResult HcomGetRankSizeEx(const char *group, uint32_t *rankSize, uint32_t flag);
 HcclResult HcomReleaseSubComms(void);                 /* destroys every group but the world group */

@@ -156,6 +156,28 @@ def main():
         return 0   # this rank never joins the rendezvous
     if scenario.startswith("torch_"):
         return torch_scenario(scenario, rank, world, local, use_cuda)
+    if scenario == "hcom_master_info":
+        # Nobody is given a rank: every process knows the master's address only.  The process that gets the port serves.
+        import ctypes
+        from hcomm_b200 import _lib
+        lib = _lib.load()
+        port = os.environ["HCOMM_TEST_MASTER_PORT"].encode()
+        assert lib.HcomInitByMasterInfo(b"127.0.0.1", b"notaport", b"0", str(world).encode(), b"127.0.0.1") == 1
+        rc = lib.HcomInitByMasterInfo(b"127.0.0.1", port, b"0", str(world).encode(), b"127.0.0.1")
+        assert rc == 0, rc
+        size, me = ctypes.c_uint32(), ctypes.c_uint32()
+        assert lib.HcomGetRankSize(b"hccl_world_group", ctypes.byref(size)) == 0 and size.value == world
+        assert lib.HcomGetRankId(b"hccl_world_group", ctypes.byref(me)) == 0 and me.value < world
+        x = np.zeros(world, np.float32)
+        x[me.value] = 1.0                                  # every rank marks its own slot: the ranks handed out are all different
+        y = np.zeros_like(x)
+        V = ctypes.c_void_p
+        assert lib.HcomAllReduce(b"t", x.ctypes.data_as(V), y.ctypes.data_as(V), ctypes.c_uint64(world), 4, 0, b"hccl_world_group", None) == 0
+        assert (y == 1).all(), y
+        assert lib.HcomInitByMasterInfo(b"127.0.0.1", port, b"0", str(world).encode(), b"127.0.0.1") == 1      # already there
+        assert lib.HcomDestroy() == 0
+        print(f"process {rank}: was rank {me.value}, ok", flush=True)
+        return 0
     kw = {}
     if os.environ.get("HCOMM_TEST_BUFFER_MB"):
         kw["buffer_mb"] = int(os.environ["HCOMM_TEST_BUFFER_MB"])

@@ -84,3 +84,13 @@ def test_operator_retry_gives_up_after_the_configured_rounds():
     codes, outs = launch("op_retry_exhausted", 3, env, timeout=180)
     assert codes == [0, 0, 0], "\n".join(outs)
     assert all("failed 1, succeeded 0" in o for o in outs)
+
+
+def test_world_group_from_the_master_address_alone():
+    import socket
+    with socket.socket() as probe:                           # a port that is free right now
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
+    codes, outs = launch("hcom_master_info", 4, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_MASTER_PORT": str(port)}, timeout=120)
+    assert codes == [0, 0, 0, 0], "\n".join(outs)
+    assert sorted(int(o.split("was rank ")[1].split(",")[0]) for o in outs) == [0, 1, 2, 3]
