@@ -6,6 +6,7 @@
 #include <cstring>
 #include <fstream>
 
+#include "../alg/selector.h"
 #include "../core/env.h"
 #include "../core/log.h"
 #include "../device/coll_kernels.h"
@@ -102,6 +103,16 @@ HcclResult ResolveConfig(const HcclCommConfig *cfg, const std::string &defaultNa
         if (covers(cfg->hcclRetryParams, HCCL_COMM_RETRY_PARAMS_MAX_LENGTH) && cfg->hcclRetryParams[0]) r.retryParams = cfg->hcclRetryParams;
         if (covers(cfg->hcclBufferName, BUFFER_NAME_MAX_LENGTH) && cfg->hcclBufferName[0]) r.bufferName = cfg->hcclBufferName;
         if (covers(&cfg->hcclSymWinMaxMemSizePerRank, 8) && cfg->hcclSymWinMaxMemSizePerRank != 0) r.symStrideGB = cfg->hcclSymWinMaxMemSizePerRank;
+    }
+    if (r.execTimeoutSec < 0) { RPT_ERR("EI0003", "the execution timeout (%d s) must not be negative", r.execTimeoutSec); return HCCL_E_PARA; }
+    if (!r.algo.empty()) {
+        // a setting that does not parse is refused here, where the caller sees it, not ignored at the first operator
+        AlgoConfig probe;
+        std::string why;
+        if (!probe.Parse(r.algo, &why)) {
+            RPT_ERR("EI0003", "algorithm configuration \"%s\" (hcclAlgo / HCCL_ALGO): %s", r.algo.c_str(), why.c_str());
+            return HCCL_E_PARA;
+        }
     }
     *out = r;
     return HCCL_SUCCESS;

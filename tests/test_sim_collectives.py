@@ -259,3 +259,24 @@ def test_host_messages_between_ranks(monkeypatch):
     for q in range(1, n):
         assert out[q] == (0, 7, {"to": q, "plan": [q] * 3})
     destroy(comms)
+
+
+def test_configuration_values_that_make_no_sense_are_refused_at_creation(monkeypatch):
+    import hcomm_b200 as hb
+    sim_env(monkeypatch)
+    for kw in (dict(buffer_mb=0), dict(deterministic=7), dict(op_expansion_mode=99), dict(algo="level9:zzz;;;==//"), dict(algo="level0:nosuch"),
+               dict(exec_timeout=-5)):
+        with pytest.raises(hb.HcclError) as err:
+            hb.Communicator(1, hb.get_root_info(), 0, **kw)
+        assert err.value.code == 1, kw                     # HCCL_E_PARA
+    c = hb.Communicator(1, hb.get_root_info(), 0, algo="allreduce=level0:ring/others=level0:fullmesh", deterministic=1, exec_timeout=30, name="x" * 127)
+    assert c.name == "x" * 127
+    c.destroy()
+    # the same rule for the environment variable
+    monkeypatch.setenv("HCCL_ALGO", "level0:nosuch")
+    from hcomm_b200 import _lib
+    _lib.load().HcommToolReloadEnv()
+    with pytest.raises(hb.HcclError):
+        hb.Communicator(1, hb.get_root_info(), 0)
+    monkeypatch.delenv("HCCL_ALGO")
+    _lib.load().HcommToolReloadEnv()
