@@ -1207,6 +1207,61 @@ static void Messages(uint32_t rank, uint32_t n, HcclComm comm)
     EX_CHECK(HcclBarrier(comm, nullptr));
 }
 
+// ---------------------------------------------------------------------------------- argument rules of the operators
+
+static void ArgumentRules(uint32_t rank, uint32_t n, HcclComm comm)
+{
+    float x[8] = {1, 2, 3, 4, 5, 6, 7, 8}, y[8] = {0};
+    // nothing to do is not an error, whatever the pointers say
+    EX_CHECK(HcclAllReduce(nullptr, nullptr, 0, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, comm, nullptr));
+    EX_CHECK(HcclBroadcast(nullptr, 0, HCCL_DATA_TYPE_FP32, 0, comm, nullptr));
+    EX_CHECK(HcclAllGather(nullptr, nullptr, 0, HCCL_DATA_TYPE_FP32, comm, nullptr));
+    // missing communicator or buffers
+    EXPECT_RC(HcclAllReduce(x, y, 8, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, nullptr, nullptr), HCCL_E_PTR);
+    EXPECT_RC(HcclAllReduce(nullptr, y, 8, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, comm, nullptr), HCCL_E_PTR);
+    EXPECT_RC(HcclAllReduce(x, nullptr, 8, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, comm, nullptr), HCCL_E_PTR);
+    EXPECT_RC(HcclBroadcast(nullptr, 8, HCCL_DATA_TYPE_FP32, 0, comm, nullptr), HCCL_E_PTR);
+    int notAComm[64] = {0};
+    EXPECT_RC(HcclAllReduce(x, y, 8, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, (HcclComm)notAComm, nullptr), HCCL_E_PTR);
+    // counts beyond the limit, undefined reductions and types, roots and peers outside the communicator
+    EXPECT_RC(HcclAllReduce(x, y, 0x800000000ull, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, comm, nullptr), HCCL_E_PARA);
+    EXPECT_RC(HcclAllReduce(x, y, 8, HCCL_DATA_TYPE_FP32, (HcclReduceOp)9, comm, nullptr), HCCL_E_PARA);
+    EX_EXPECT(HcclAllReduce(x, y, 8, (HcclDataType)77, HCCL_REDUCE_SUM, comm, nullptr) != HCCL_SUCCESS);
+    EXPECT_RC(HcclBroadcast(x, 8, HCCL_DATA_TYPE_FP32, n, comm, nullptr), HCCL_E_PARA);
+    EXPECT_RC(HcclReduce(x, y, 8, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, n + 3, comm, nullptr), HCCL_E_PARA);
+    EX_EXPECT(HcclSend(x, 8, HCCL_DATA_TYPE_FP32, n, comm, nullptr) != HCCL_SUCCESS);
+    EX_EXPECT(HcclSend(x, 8, HCCL_DATA_TYPE_FP32, rank, comm, nullptr) != HCCL_SUCCESS);        // to oneself
+    EX_EXPECT(HcclRecv(y, 8, HCCL_DATA_TYPE_FP32, n + 1, comm, nullptr) != HCCL_SUCCESS);
+    // variable counts: the list must agree with the own count
+    std::vector<uint64_t> counts(n, 2), displs(n);
+    for (uint32_t q = 0; q < n; ++q) displs[q] = 2 * q;
+    std::vector<float> in(2 * n, 1.f), out(2, 0.f);
+    EXPECT_RC(HcclReduceScatterV(in.data(), counts.data(), displs.data(), out.data(), 3, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, comm, nullptr), HCCL_E_PARA);
+    EXPECT_RC(HcclReduceScatterV(in.data(), nullptr, displs.data(), out.data(), 2, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, comm, nullptr), HCCL_E_PTR);
+    HcclSendRecvItem item;
+    item.sendRecvType = HCCL_SEND; item.buf = x; item.count = 8; item.dataType = HCCL_DATA_TYPE_FP32; item.remoteRank = n;
+    EX_EXPECT(HcclBatchSendRecv(&item, 1, comm, nullptr) != HCCL_SUCCESS);
+    EX_EXPECT(HcclBatchSendRecv(nullptr, 1, comm, nullptr) != HCCL_SUCCESS);
+    // none of the refusals has left anything behind: the next operator runs
+    EX_CHECK(HcclAllReduce(x, y, 8, HCCL_DATA_TYPE_FP32, HCCL_REDUCE_SUM, comm, nullptr));
+    EX_EXPECT(y[7] == 8.f * (float)n);
+    HcclResult err = HCCL_E_INTERNAL;
+    EX_CHECK(HcclGetCommAsyncError(comm, &err));
+    EX_EXPECT(err == HCCL_SUCCESS);
+    // a second communicator of the same name for the same rank in one process is refused
+    if (n == 1) {
+        char name[COMM_NAME_MAX_LENGTH] = "";
+        EX_CHECK(HcclGetCommName(comm, name));
+        HcclRootInfo info;
+        EX_CHECK(HcclGetRootInfo(&info));
+        HcclCommConfig cfg;
+        HcclCommConfigInit(&cfg);
+        std::snprintf(cfg.hcclCommName, sizeof(cfg.hcclCommName), "%s", name);
+        HcclComm twin = nullptr;
+        EXPECT_RC(HcclCommInitRootInfoConfig(1, &info, 0, &cfg, &twin), HCCL_E_PARA);
+    }
+}
+
 int main(int argc, char **argv)
 {
     const uint32_t n = argc > 1 ? (uint32_t)std::atoi(argv[1]) : 4;
@@ -1220,6 +1275,7 @@ int main(int argc, char **argv)
         Diagnostics(rank, n, comm);
         Launch(rank, n, comm);
         Messages(rank, n, comm);
+        ArgumentRules(rank, n, comm);
     });
     EdgeCases(n);
     OtherWaysToStart(n);
