@@ -124,3 +124,16 @@ def test_parsers_survive_damaged_input_under_address_sanitizer():
     text = run.stdout + run.stderr
     assert "AddressSanitizer" not in text, text[-6000:]
     assert run.returncode == 0 and "fuzz: 4000 inputs" in run.stdout, text[-4000:]
+
+
+@needs_ubsan
+def test_api_sweep_has_no_undefined_behaviour(tmp_path):
+    runtime = subprocess.run(["g++", "-print-file-name=libubsan.so"], capture_output=True, text=True).stdout.strip()
+    if not runtime or not Path(runtime).exists():
+        pytest.skip("the compiler's libubsan.so was not found")
+    exe = _build_sweep(tmp_path, "ubsan")
+    env = dict(os.environ, HCCL_SIM="1", HCCL_BUFFSIZE="2", HCCL_EXEC_TIMEOUT="60", LD_PRELOAD=runtime, UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=0")
+    run = subprocess.run([str(exe), "4"], capture_output=True, text=True, env=env, timeout=300)
+    text = run.stdout + run.stderr
+    assert "runtime error" not in text, text[-6000:]
+    assert run.returncode == 0 and "4 ranks ok" in run.stdout, text[-4000:]
