@@ -347,8 +347,14 @@ HcclResult HcclGetCommAsyncError(HcclComm comm, HcclResult *asyncError)
     int e = c->asyncError.load();
     if (e == 0 && c->boot) {
         if (c->boot->RemoteError() != HCCL_SUCCESS) e = HCCL_E_REMOTE;
-        else if (c->boot->LostMask() != 0) e = HCCL_E_REMOTE;   // a peer stopped answering heartbeats
-        else if (c->boot->HubGone()) e = HCCL_E_REMOTE;         // rank 0's process, which hosts the hub, is gone
+        else {
+            // a member of this communicator stopped answering heartbeats or went away (ranks that are lost but do not
+            // belong to it - a communicator over the survivors of its parent - do not count)
+            const uint64_t lost = c->boot->LostMask();
+            for (uint32_t w : c->worldRanks)
+                if (w < 64 && ((lost >> w) & 1)) e = HCCL_E_REMOTE;
+        }
+        if (e == 0 && c->boot->HubGone()) e = HCCL_E_REMOTE;    // rank 0's process, which hosts the hub, is gone
     }
     *asyncError = (HcclResult)e;
     return HCCL_SUCCESS;

@@ -814,7 +814,22 @@ def main():
             time.sleep(0.05)
         err = comm.async_error()
         print(f"rank {rank}: async error {err}", flush=True)
-        return 0 if err == 21 else 3
+        if err != 21:
+            return 3
+        if leaver != 0 and not use_cuda:
+            # The ranks that are left go on without it: a communicator over the survivors, derived from the one that lost a
+            # member (the hub of the control plane is alive, only a peer is gone).
+            survivors = [r for r in range(world) if r != leaver]
+            sub = comm.split(survivors, sub_id=77)
+            assert sub is not None and sub.size == world - 1 and sub.rank == survivors.index(rank)
+            v = np.full(1000, rank + 1, np.float32)
+            out = np.zeros_like(v)
+            sub.all_reduce(v, out)
+            assert (out == sum(r + 1 for r in survivors)).all(), out[:3]
+            assert sub.async_error() == 0
+            print(f"rank {rank}: the survivors' communicator works", flush=True)
+            sub.destroy()
+        return 0
     elif scenario == "ring_monitor":
         # Five ranks watch each other in a ring.  The hub's process (rank 0) vanishes, then rank 2; the ranks that are
         # left learn of both without the hub, rank 4 (no neighbour of rank 2) from what its neighbours pass on.  Rank 3

@@ -19,6 +19,7 @@ def test_rank_that_never_joins_times_out_with_a_report():
 def test_peer_exit_is_reported_as_remote_error():
     codes, outs = launch("peer_exit", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1"}, timeout=90)
     assert codes[0] == 0 and codes[1] == 0, "\n".join(outs)
+    assert "the survivors' communicator works" in outs[0] and "the survivors' communicator works" in outs[1]
 
 
 def test_exit_of_the_rank_that_hosts_the_hub_is_reported_too():
