@@ -2,6 +2,7 @@
 // (declared in include/hccl/hccl_comm.h).
 #include <unistd.h>
 
+#include <algorithm>
 #include <cstring>
 #include <thread>
 
@@ -9,6 +10,7 @@
 #include "../comm/comm.h"
 #include "../core/env.h"
 #include "../core/log.h"
+#include "../core/net.h"
 #include "hccl/hccl.h"
 #include "hccl/hccl_comm.h"
 
@@ -149,7 +151,14 @@ HcclResult HcclCommInitClusterInfoConfig(const char *clusterInfo, uint32_t rank,
     snprintf(root.identifier, sizeof(root.identifier), "ranktable_%08x_%d", table.Crc(), port);
     if (rank == 0) {
         auto hub = std::make_shared<BootstrapHub>();
+        // The port follows from the table, so the hub of an earlier communicator from a table with the same port (or
+        // from this one) may still be winding down there: try for a few seconds before giving up.
         r = hub->Start(ip, port, root.identifier);
+        for (int attempt = 0; r != HCCL_SUCCESS && attempt < 50; ++attempt) {
+            usleep(100000);
+            hub = std::make_shared<BootstrapHub>();
+            r = hub->Start(ip, port, root.identifier);
+        }
         if (r != HCCL_SUCCESS) {
             RPT_ERR("EI0019", "rank 0 cannot listen on %s:%d for the rank-table rendezvous (set HCCL_IF_BASE_PORT to move it)", ip.c_str(), port);
             return r;
@@ -501,6 +510,74 @@ HcclResult HcclCommResume(HcclComm comm)
     c->state.store((int)CommState::READY);
     FireState(c, HCCL_COMM_STATE_PHASE_RESUME_POST);
     HCCL_RUN_INFO("communicator \"%s\" rank %u resumed", c->cfg.name.c_str(), c->rank);
+    return HCCL_SUCCESS;
+}
+
+HcclResult HcclCommRecover(HcclComm comm, uint32_t timeoutSec, HcclComm *newComm, uint32_t *newSize, uint32_t *oldRanks)
+{
+    Comm *c = AsComm(comm);
+    CHK_PTR_NULL(c); CHK_PTR_NULL(newComm);
+    if (!c->boot) return HCCL_E_NOT_SUPPORT;
+    if (timeoutSec == 0) timeoutSec = (uint32_t)EnvConfig::Get().connectTimeoutSec.value;
+    const int64_t deadline = net::NowMs() + (int64_t)timeoutSec * 1000;
+    constexpr uint8_t kProbe = 'P', kTicket = 'T';
+    struct Ticket { uint8_t kind; uint8_t pad[3]; uint32_t count; HcclRootInfo info; };      // followed by `count` old ranks
+    std::vector<uint32_t> members;          // old ranks of the new communicator, ascending
+    HcclRootInfo info;
+    for (;;) {
+        if (net::NowMs() >= deadline) { RPT_ERR("EI0015", "HcclCommRecover: the survivors of \"%s\" did not find each other within %u s", c->cfg.name.c_str(), timeoutSec); return HCCL_E_TIMEOUT; }
+        uint64_t lost = c->boot->LostMask();
+        if (c->boot->HubGone()) lost |= 1ull;                   // the hub lives in world rank 0's process
+        std::vector<uint32_t> alive;
+        for (uint32_t i = 0; i < c->nRanks; ++i)
+            if (c->worldRanks[i] >= 64 || !((lost >> c->worldRanks[i]) & 1)) alive.push_back(i);
+        if (alive.empty() || std::find(alive.begin(), alive.end(), c->rank) == alive.end()) return HCCL_E_INTERNAL;
+        const uint32_t leader = alive[0];
+        if (leader == c->rank) {
+            // who of them answers on its local socket right now?  (a rank that is gone refuses the connection)
+            members.assign(1, c->rank);
+            for (uint32_t i : alive)
+                if (i != c->rank && c->boot->SendDirect(c->worldRanks[i], Blob(1, kProbe)) == HCCL_SUCCESS) members.push_back(i);
+            std::sort(members.begin(), members.end());
+            CHK_RET(HcclGetRootInfo(&info));
+            Blob msg(sizeof(Ticket) + members.size() * 4);
+            Ticket t;
+            memset(&t, 0, sizeof(t));
+            t.kind = kTicket; t.count = (uint32_t)members.size(); t.info = info;
+            memcpy(msg.data(), &t, sizeof(t));
+            memcpy(msg.data() + sizeof(t), members.data(), members.size() * 4);
+            for (uint32_t i : members)
+                if (i != c->rank) CHK_RET(c->boot->SendDirect(c->worldRanks[i], msg));
+            break;
+        }
+        Blob msg;
+        HcclResult r = c->boot->RecvDirect(c->worldRanks[leader], &msg, 500);
+        if (r == HCCL_E_TIMEOUT) continue;                      // look at the lost set again: the leader may be gone as well
+        if (r != HCCL_SUCCESS) return r;
+        if (msg.size() < sizeof(Ticket) || msg[0] != kTicket) continue;      // a probe
+        Ticket t;
+        memcpy(&t, msg.data(), sizeof(t));
+        if (msg.size() != sizeof(Ticket) + (size_t)t.count * 4 || t.count == 0 || t.count > c->nRanks) return HCCL_E_INTERNAL;
+        members.resize(t.count);
+        memcpy(members.data(), msg.data() + sizeof(t), (size_t)t.count * 4);
+        info = t.info;
+        break;
+    }
+    auto me = std::find(members.begin(), members.end(), c->rank);
+    if (me == members.end()) { RPT_ERR("EI0015", "HcclCommRecover: rank %u is not among the survivors the leader found", c->rank); return HCCL_E_INTERNAL; }
+    HcclCommConfig cfg;
+    HcclCommConfigInit(&cfg);
+    snprintf(cfg.hcclCommName, sizeof(cfg.hcclCommName), "%.100s_recovered", c->cfg.name.c_str());
+    cfg.hcclBufferSize = c->cfg.bufferMB;
+    cfg.hcclDeterministic = __atomic_load_n(&c->cfg.deterministic, __ATOMIC_RELAXED);
+    cfg.hcclOpExpansionMode = c->cfg.opExpansionMode;
+    cfg.hcclExecTimeOut = c->cfg.execTimeoutSec;
+    snprintf(cfg.hcclAlgo, sizeof(cfg.hcclAlgo), "%s", c->cfg.algo.c_str());
+    CHK_RET(HcclCommInitRootInfoConfig((uint32_t)members.size(), &info, (uint32_t)(me - members.begin()), &cfg, newComm));
+    if (newSize) *newSize = (uint32_t)members.size();
+    if (oldRanks) memcpy(oldRanks, members.data(), members.size() * 4);
+    HCCL_RUN_INFO("communicator \"%s\": %zu of %u ranks go on as \"%s\", this one as rank %u", c->cfg.name.c_str(), members.size(), c->nRanks, cfg.hcclCommName,
+                  (uint32_t)(me - members.begin()));
     return HCCL_SUCCESS;
 }
 

@@ -20,6 +20,9 @@ constexpr uint64_t kMaxMsgBytes = 100ull << 20;  // same cap as the reference's 
 // Messages of the ring monitor travel over the descriptor-passing sockets without a descriptor: the header's second
 // word says which kind, the set of ranks the sender holds for lost rides in its tag.
 constexpr uint32_t kRingPing = 1, kRingBye = 2;
+// The same sockets carry rank-to-rank bytes that must not depend on the hub (Bootstrap::SendDirect).
+constexpr uint32_t kDirectBytes = 3;
+constexpr uint64_t kMaxDirectBytes = 1 << 20;
 
 enum MsgType : uint16_t {
     MSG_HELLO = 1,
@@ -477,7 +480,15 @@ void Bootstrap::FdAcceptLoop()
         struct { uint32_t src; uint32_t pad; uint64_t tag; } meta;
         int fd = -1;
         if (net::UdsRecvFd(c, &meta, sizeof(meta), &fd, net::NowMs() + 5000) == HCCL_SUCCESS) {
-            if (fd < 0) {
+            if (fd < 0 && meta.pad == kDirectBytes) {
+                // bytes for this rank: the length rides in the tag, the payload follows on the same connection
+                Blob data(meta.tag <= kMaxDirectBytes ? (size_t)meta.tag : 0);
+                if (meta.tag <= kMaxDirectBytes && (data.empty() || net::RecvAll(c, data.data(), data.size(), net::NowMs() + 5000) == HCCL_SUCCESS)) {
+                    std::lock_guard<std::mutex> lk(mu_);
+                    directInbox_[meta.src].push_back(std::move(data));
+                    cv_.notify_all();
+                }
+            } else if (fd < 0) {
                 RingHeard(meta.src, meta.pad, meta.tag);      // no descriptor: a message of the ring monitor
             } else {
                 std::lock_guard<std::mutex> lk(mu_);
@@ -606,6 +617,30 @@ HcclResult Bootstrap::TryRecv(uint32_t srcRank, uint64_t want, uint64_t mask, Bl
         return HCCL_SUCCESS;
     }
     return hubGone_.load() ? HCCL_E_NETWORK : HCCL_E_AGAIN;
+}
+
+HcclResult Bootstrap::SendDirect(uint32_t dstRank, const Blob &data)
+{
+    if (data.size() > kMaxDirectBytes) return HCCL_E_PARA;
+    int c = -1;
+    HcclResult r = net::UdsConnect("hccl-" + identifier_ + "-" + std::to_string(dstRank), net::NowMs() + 2000, &c);
+    if (r != HCCL_SUCCESS) return r;
+    struct { uint32_t src; uint32_t pad; uint64_t tag; } meta{rank_, kDirectBytes, (uint64_t)data.size()};
+    r = net::SendAll(c, &meta, sizeof(meta));
+    if (r == HCCL_SUCCESS && !data.empty()) r = net::SendAll(c, data.data(), data.size());
+    ::close(c);
+    return r;
+}
+
+HcclResult Bootstrap::RecvDirect(uint32_t srcRank, Blob *data, int timeoutMs)
+{
+    std::unique_lock<std::mutex> lk(mu_);
+    bool ok = cv_.wait_for(lk, std::chrono::milliseconds(timeoutMs), [&] { auto it = directInbox_.find(srcRank); return it != directInbox_.end() && !it->second.empty(); });
+    if (!ok) return HCCL_E_TIMEOUT;
+    auto it = directInbox_.find(srcRank);
+    *data = std::move(it->second.front());
+    it->second.pop_front();
+    return HCCL_SUCCESS;
 }
 
 HcclResult Bootstrap::SendFd(uint32_t dstRank, uint64_t tag, int fd)

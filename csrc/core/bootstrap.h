@@ -113,6 +113,9 @@ public:
     // Takes the oldest queued relay message from `srcRank` (~0u: from anybody) whose tag agrees with `want` in the bits
     // of `mask`, without waiting.  HCCL_E_AGAIN when there is none.
     HcclResult TryRecv(uint32_t srcRank, uint64_t want, uint64_t mask, Blob *data, uint32_t *fromRank, uint64_t *fromTag);
+    // Rank-to-rank bytes over the ranks' Unix sockets, without the hub (ranks of one host).  Used where the hub is gone.
+    HcclResult SendDirect(uint32_t dstRank, const Blob &data);
+    HcclResult RecvDirect(uint32_t srcRank, Blob *data, int timeoutMs);
     HcclResult SendFd(uint32_t dstRank, uint64_t tag, int fd);
     HcclResult RecvFd(uint32_t srcRank, uint64_t tag, int *fd, int timeoutMs = -1);
 
@@ -158,6 +161,7 @@ private:
     std::map<uint64_t, std::vector<Blob>> gatherDone_;
     std::map<Key, std::deque<Blob>> inbox_;
     std::map<Key, std::deque<int>> fdInbox_;
+    std::map<uint32_t, std::deque<Blob>> directInbox_;   // guarded by mu_: SendDirect messages by sender
     std::thread reader_, fdAcceptor_, heart_;
     std::atomic<bool> closing_{false};
     std::atomic<bool> heartStop_{false};

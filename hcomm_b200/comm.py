@@ -289,6 +289,14 @@ class Communicator:
     def resume(self):
         check(self._lib.HcclCommResume(self._h), "HcclCommResume")
 
+    def recover(self, timeout: int = 30):
+        """Collective over the ranks that are left after others were lost (the rank that hosted the rendezvous among them
+        or not): returns ``(communicator over the survivors, old rank of every new rank)``.  This communicator stays as it is."""
+        h, size = ctypes.c_void_p(), ctypes.c_uint32()
+        old = (ctypes.c_uint32 * self.size)()
+        check(self._lib.HcclCommRecover(self._h, ctypes.c_uint32(timeout), ctypes.byref(h), ctypes.byref(size), old), "HcclCommRecover")
+        return Communicator.from_handle(h.value), list(old[:size.value])
+
     # ---------------------------------------------------------------- registered (symmetric) memory
     def alloc_registered(self, shape, dtype):
         """Collective: allocates exportable device memory of the given torch shape / dtype on every rank, registers it as a

@@ -79,6 +79,12 @@ static inline void HcclCommConfigInit(HcclCommConfig *config)
  * Suspend stops new launches (operators return HCCL_E_SUSPENDING), Resume re-synchronises the
  * flag pages of all ranks and re-opens the communicator.  Both are collective over live ranks.
  */
+/* B200 extension: after ranks of `comm` were lost - the rank that hosted the rendezvous among them or not - the ranks
+ * that are left call this together and get a new communicator over themselves, numbered in their old order.  It needs
+ * neither the old rendezvous nor a ticket passed around by the caller: the lowest survivor opens a new rendezvous and
+ * hands the ticket to the others over the ranks' local sockets (ranks of one host).  `oldRanks` (optional, room for the
+ * old size) receives the old rank of every new rank.  The old communicator is left as it is; destroy it afterwards. */
+HcclResult HcclCommRecover(HcclComm comm, uint32_t timeoutSec, HcclComm *newComm, uint32_t *newSize, uint32_t *oldRanks);
 HcclResult HcclCommSuspend(HcclComm comm);
 HcclResult HcclCommResume(HcclComm comm);
 typedef HcclResult (*HcclCommStateCallback)(HcclComm comm, HcclCommStatePhase state, void *args);

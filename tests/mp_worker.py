@@ -816,6 +816,19 @@ def main():
         print(f"rank {rank}: async error {err}", flush=True)
         if err != 21:
             return 3
+        if leaver == 0 and not use_cuda:
+            # The rank that hosted the rendezvous is gone, and with it the control plane of this communicator.  The ranks
+            # that are left find each other over their local sockets and start a new one.
+            fresh, old_ranks = comm.recover(timeout=30)
+            assert old_ranks == [r for r in range(world) if r != 0], old_ranks
+            assert fresh.size == world - 1 and fresh.rank == rank - 1
+            v = np.full(1000, rank + 1, np.float32)
+            out = np.zeros_like(v)
+            fresh.all_reduce(v, out)
+            assert (out == sum(r + 1 for r in old_ranks)).all(), out[:3]
+            assert fresh.async_error() == 0
+            print(f"rank {rank}: goes on as rank {fresh.rank} of {fresh.size}", flush=True)
+            fresh.destroy()
         if leaver != 0 and not use_cuda:
             # The ranks that are left go on without it: a communicator over the survivors, derived from the one that lost a
             # member (the hub of the control plane is alive, only a peer is gone).

@@ -24,8 +24,10 @@ def test_peer_exit_is_reported_as_remote_error():
 
 def test_exit_of_the_rank_that_hosts_the_hub_is_reported_too():
     # rank 0's process carries the hub of the control plane; when it goes the others lose heartbeats and relays at once
-    codes, outs = launch("peer_exit", 3, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_HUB_EXIT": "1"}, timeout=90)
-    assert codes[1] == 0 and codes[2] == 0, "\n".join(outs)
+    codes, outs = launch("peer_exit", 4, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_HUB_EXIT": "1"}, timeout=90)
+    assert codes[1] == 0 and codes[2] == 0 and codes[3] == 0, "\n".join(outs)
+    # ... and the survivors start over among themselves without it
+    assert "goes on as rank 0 of 3" in outs[1] and "goes on as rank 2 of 3" in outs[3], "\n".join(outs)
 
 
 def test_ring_monitor_reports_losses_after_the_hub_is_gone():
