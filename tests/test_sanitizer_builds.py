@@ -27,6 +27,8 @@ SCENARIOS = [
 MONITOR_SCENARIOS = [
     ("ring_monitor", 5, {"HCCL_HEARTBEAT_INTERVAL_MS": "100", "HCCL_HEARTBEAT_LOST_MS": "8000"}),
     ("silent_rank", 3, {"HCCL_HEARTBEAT_INTERVAL_MS": "100", "HCCL_HEARTBEAT_LOST_MS": "1500"}),
+    ("peer_exit", 3, {}),                                  # the survivors derive a communicator from the old one
+    ("peer_exit", 4, {"HCOMM_TEST_HUB_EXIT": "1"}),        # the hub's process is gone: the survivors start over among themselves
 ]
 
 
