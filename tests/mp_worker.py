@@ -807,7 +807,8 @@ def main():
             import torch
             torch.cuda.synchronize()
         leaver = 0 if os.environ.get("HCOMM_TEST_HUB_EXIT") == "1" else world - 1      # rank 0 hosts the control plane's hub
-        if rank == leaver:
+        also = int(os.environ.get("HCOMM_TEST_ALSO_EXIT", "-1"))       # a second rank that vanishes at the same time
+        if rank == leaver or rank == also:
             os._exit(0)   # vanishes without destroying the communicator
         deadline = time.time() + 20
         while comm.async_error() == 0 and time.time() < deadline:
@@ -820,8 +821,8 @@ def main():
             # The rank that hosted the rendezvous is gone, and with it the control plane of this communicator.  The ranks
             # that are left find each other over their local sockets and start a new one.
             fresh, old_ranks = comm.recover(timeout=30)
-            assert old_ranks == [r for r in range(world) if r != 0], old_ranks
-            assert fresh.size == world - 1 and fresh.rank == rank - 1
+            assert old_ranks == [r for r in range(world) if r not in (0, also)], old_ranks
+            assert fresh.size == len(old_ranks) and fresh.rank == old_ranks.index(rank)
             v = np.full(1000, rank + 1, np.float32)
             out = np.zeros_like(v)
             fresh.all_reduce(v, out)

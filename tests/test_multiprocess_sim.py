@@ -97,3 +97,10 @@ def test_world_group_from_the_master_address_alone():
     codes, outs = launch("hcom_master_info", 4, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_MASTER_PORT": str(port)}, timeout=120)
     assert codes == [0, 0, 0, 0], "\n".join(outs)
     assert sorted(int(o.split("was rank ")[1].split(",")[0]) for o in outs) == [0, 1, 2, 3]
+
+
+def test_survivors_start_over_after_the_hub_and_another_rank_vanished():
+    # nobody has told the survivors that rank 2 is gone as well: the leader finds out when it asks around
+    codes, outs = launch("peer_exit", 5, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_HUB_EXIT": "1", "HCOMM_TEST_ALSO_EXIT": "2"}, timeout=90)
+    assert codes[1] == 0 and codes[3] == 0 and codes[4] == 0, "\n".join(outs)
+    assert "goes on as rank 0 of 3" in outs[1] and "goes on as rank 1 of 3" in outs[3] and "goes on as rank 2 of 3" in outs[4], "\n".join(outs)
