@@ -1018,6 +1018,26 @@ static void EdgeCases(uint32_t n)
     for (auto &t : ts) t.join();
     ts.clear();
     SumOverRanks(n, comms);
+    {
+        // nobody is lost: the "survivors" are all ranks, and the new communicator is a second one of the same size
+        std::vector<HcclComm> fresh(n, nullptr);
+        for (uint32_t r = 0; r < n; ++r)
+            ts.emplace_back([&, r] {
+                uint32_t size = 0;
+                std::vector<uint32_t> old(n, 99);
+                EX_CHECK(HcclCommRecover(comms[r], 20, &fresh[r], &size, old.data()));
+                EX_EXPECT(size == n && old[r] == r);
+                uint32_t id = 99;
+                EX_CHECK(HcclGetRankId(fresh[r], &id));
+                EX_EXPECT(id == r);
+            });
+        for (auto &t : ts) t.join();
+        ts.clear();
+        SumOverRanks(n, fresh);
+        for (uint32_t r = 0; r < n; ++r) ts.emplace_back([&, r] { EX_CHECK(HcclCommDestroy(fresh[r])); });
+        for (auto &t : ts) t.join();
+        ts.clear();
+    }
     if (n >= 2) {
         // more notify slots than a pair of ranks has: the whole request is rolled back, a smaller one is served
         for (uint32_t r = 0; r < 2; ++r)
