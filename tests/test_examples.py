@@ -18,6 +18,7 @@ EXAMPLES = [
     ("04_team_one_sided/team_signal_put.cc", ["2"]),
     ("05_resources/reduce_scatter_primitives.cc", ["4"]),
     ("05_resources/reduce_scatter_primitives.cc", ["3"]),
+    ("06_recovery/survivors_go_on.cc", ["4"]),
 ]
 
 
