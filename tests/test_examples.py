@@ -19,6 +19,8 @@ EXAMPLES = [
     ("05_resources/reduce_scatter_primitives.cc", ["4"]),
     ("05_resources/reduce_scatter_primitives.cc", ["3"]),
     ("06_recovery/survivors_go_on.cc", ["4"]),
+    ("07_messages/plan_exchange.cc", ["4"]),
+    ("07_messages/plan_exchange.cc", ["2"]),
 ]
 
 
