@@ -280,3 +280,46 @@ def test_configuration_values_that_make_no_sense_are_refused_at_creation(monkeyp
         hb.Communicator(1, hb.get_root_info(), 0)
     monkeypatch.delenv("HCCL_ALGO")
     _lib.load().HcommToolReloadEnv()
+
+
+@pytest.mark.parametrize("heartbeat", [False, True])
+def test_communicators_destroyed_in_any_order_leave_nothing_behind(monkeypatch, heartbeat):
+    """Ranks of one process, destroyed one after the other by one thread (forwards, backwards), all at once, or one first
+    and the rest together: no call stalls, and descriptors and threads are back where they were."""
+    import os
+    import random
+    import time
+    import hcomm_b200 as hb
+    extra = {"HCCL_HEARTBEAT_INTERVAL_MS": 50, "HCCL_HEARTBEAT_LOST_MS": 4000} if heartbeat else {}
+    sim_env(monkeypatch, buffsize=1, **extra)
+    rng = random.Random(5)
+
+    def census():
+        return len(os.listdir("/proc/self/fd")), len(os.listdir("/proc/self/task"))
+    base = None
+    t0 = time.time()
+    for it in range(14):
+        n = rng.choice([2, 3, 4, 5])
+        info = hb.get_root_info()
+        comms = run_ranks(n, lambda r: hb.Communicator(n, info, r))
+        out = run_ranks(n, lambda r: comms[r].all_reduce(np.full(10, r + 1, np.float32), np.zeros(10, np.float32)))
+        assert all((o == n * (n + 1) / 2).all() for o in out)
+        mode = ("forwards", "backwards", "together", "one_first")[it % 4]
+        if mode == "forwards":
+            for c in comms:
+                c.destroy()
+        elif mode == "backwards":
+            for c in reversed(comms):
+                c.destroy()
+        elif mode == "together":
+            run_ranks(n, lambda r: comms[r].destroy())
+        else:
+            comms[0].destroy()
+            run_ranks(n - 1, lambda r: comms[r + 1].destroy())
+        if it == 3:
+            time.sleep(0.3)
+            base = census()
+    time.sleep(0.3)
+    assert time.time() - t0 < 60
+    fds, threads = census()
+    assert fds <= base[0] + 2 and threads <= base[1] + 2, (base, (fds, threads))
