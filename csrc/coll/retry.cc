@@ -190,6 +190,8 @@ void AgentLoop(Comm *c)
     RetryState *r = c->retry.get();
     const uint32_t n = c->nRanks;
     while (!r->stop.load()) {
+        // without the hub there are no rounds: its calls return at once, so do not spin on them
+        if (c->boot->HubGone()) { usleep(50000); continue; }
         // a wait that ran out on this rank's GPU (the host engines report theirs to the caller, who asks)
         if (c->plat->kind() == PlatKind::CUDA && c->abortWord && __atomic_load_n(c->abortWord, __ATOMIC_ACQUIRE) != 0 &&
             c->state.load() == (int)CommState::READY && c->asyncError.load() == 0)

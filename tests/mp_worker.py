@@ -817,6 +817,13 @@ def main():
         print(f"rank {rank}: async error {err}", flush=True)
         if err != 21:
             return 3
+        if leaver == 0 and os.environ.get("HCCL_OP_RETRY_ENABLE") == "1":
+            # with the hub gone its calls return at once: the threads that serve the control plane must not spin on them
+            busy0 = time.process_time()
+            time.sleep(1.0)
+            busy = time.process_time() - busy0
+            print(f"rank {rank}: {busy:.2f} s of processor time in one idle second", flush=True)
+            assert busy < 0.5, busy
         if leaver == 0 and not use_cuda:
             # The rank that hosted the rendezvous is gone, and with it the control plane of this communicator.  The ranks
             # that are left find each other over their local sockets and start a new one.

@@ -104,3 +104,10 @@ def test_survivors_start_over_after_the_hub_and_another_rank_vanished():
     codes, outs = launch("peer_exit", 5, {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_HUB_EXIT": "1", "HCOMM_TEST_ALSO_EXIT": "2"}, timeout=90)
     assert codes[1] == 0 and codes[3] == 0 and codes[4] == 0, "\n".join(outs)
     assert "goes on as rank 0 of 3" in outs[1] and "goes on as rank 1 of 3" in outs[3] and "goes on as rank 2 of 3" in outs[4], "\n".join(outs)
+
+
+def test_nothing_spins_after_the_hub_is_gone():
+    env = {"HCCL_SIM": "1", "HCCL_BUFFSIZE": "1", "HCOMM_TEST_HUB_EXIT": "1", "HCCL_OP_RETRY_ENABLE": "1", "HCCL_HEARTBEAT_INTERVAL_MS": "100"}
+    codes, outs = launch("peer_exit", 3, env, timeout=90)
+    assert codes[1] == 0 and codes[2] == 0, "\n".join(outs)
+    assert "of processor time in one idle second" in outs[1]
