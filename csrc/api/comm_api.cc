@@ -573,6 +573,8 @@ HcclResult HcclCommRecover(HcclComm comm, uint32_t timeoutSec, HcclComm *newComm
     cfg.hcclOpExpansionMode = c->cfg.opExpansionMode;
     cfg.hcclExecTimeOut = c->cfg.execTimeoutSec;
     snprintf(cfg.hcclAlgo, sizeof(cfg.hcclAlgo), "%s", c->cfg.algo.c_str());
+    snprintf(cfg.hcclRetryEnable, sizeof(cfg.hcclRetryEnable), "%s", c->cfg.retryEnable.c_str());
+    snprintf(cfg.hcclRetryParams, sizeof(cfg.hcclRetryParams), "%s", c->cfg.retryParams.c_str());
     CHK_RET(HcclCommInitRootInfoConfig((uint32_t)members.size(), &info, (uint32_t)(me - members.begin()), &cfg, newComm));
     if (newSize) *newSize = (uint32_t)members.size();
     if (oldRanks) memcpy(oldRanks, members.data(), members.size() * 4);

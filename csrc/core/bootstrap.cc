@@ -479,7 +479,9 @@ void Bootstrap::FdAcceptLoop()
         if (c < 0) continue;
         struct { uint32_t src; uint32_t pad; uint64_t tag; } meta;
         int fd = -1;
-        if (net::UdsRecvFd(c, &meta, sizeof(meta), &fd, net::NowMs() + 5000) == HCCL_SUCCESS) {
+        // the sender writes its header right after connecting: a connection that stays silent is dropped soon, because
+        // descriptors, pings and direct messages of the other ranks queue behind it
+        if (net::UdsRecvFd(c, &meta, sizeof(meta), &fd, net::NowMs() + 2000) == HCCL_SUCCESS) {
             if (fd < 0 && meta.pad == kDirectBytes) {
                 // bytes for this rank: the length rides in the tag, the payload follows on the same connection
                 Blob data(meta.tag <= kMaxDirectBytes ? (size_t)meta.tag : 0);
