@@ -138,7 +138,15 @@ def test_parsers_survive_damaged_input():
     import subprocess
     import sys
     from pathlib import Path
-    run = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "fuzz_parsers.py"), "2500", "11"], capture_output=True, text=True, timeout=600)
+    run = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "fuzz_parsers.py"), "2500", "11"], capture_output=True, text=True, errors="replace", timeout=600)
     assert run.returncode == 0 and "fuzz: 2500 inputs" in run.stdout, run.stdout[-2000:] + run.stderr[-4000:]
     rc, _, sm = _parse(b'{"a":' + b"[" * 200000 + b"]" * 200000 + b"}")
     assert rc != 0 and "nesting too deep" in sm
+
+
+def test_communicator_creation_survives_damaged_configuration_structures():
+    import subprocess
+    import sys
+    from pathlib import Path
+    run = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "fuzz_config.py"), "120", "3"], capture_output=True, text=True, errors="replace", timeout=600)
+    assert run.returncode == 0 and "config fuzz: 120 structures" in run.stdout, run.stdout[-2000:] + run.stderr[-4000:]

@@ -122,7 +122,7 @@ def test_api_sweep_has_no_data_race_under_thread_sanitizer(tmp_path):
 def test_parsers_survive_damaged_input_under_address_sanitizer():
     import sys
     env = dict(os.environ, **_asan_env())
-    run = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "fuzz_parsers.py"), "4000", "23"], capture_output=True, text=True, env=env, timeout=900)
+    run = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "fuzz_parsers.py"), "4000", "23"], capture_output=True, text=True, errors="replace", env=env, timeout=900)
     text = run.stdout + run.stderr
     assert "AddressSanitizer" not in text, text[-6000:]
     assert run.returncode == 0 and "fuzz: 4000 inputs" in run.stdout, text[-4000:]
@@ -139,3 +139,13 @@ def test_api_sweep_has_no_undefined_behaviour(tmp_path):
     text = run.stdout + run.stderr
     assert "runtime error" not in text, text[-6000:]
     assert run.returncode == 0 and "4 ranks ok" in run.stdout, text[-4000:]
+
+
+@needs_asan
+def test_communicator_creation_survives_damaged_configuration_under_address_sanitizer():
+    import sys
+    env = dict(os.environ, **_asan_env())
+    run = subprocess.run([sys.executable, str(Path(__file__).resolve().parent / "fuzz_config.py"), "150", "9"], capture_output=True, text=True, errors="replace", env=env, timeout=900)
+    text = run.stdout + run.stderr
+    assert "AddressSanitizer" not in text, text[-6000:]
+    assert run.returncode == 0 and "config fuzz: 150 structures" in run.stdout, text[-4000:]
