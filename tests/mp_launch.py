@@ -14,7 +14,7 @@ def launch(scenario, world, env_extra=None, timeout=180):
         for r in range(world):
             env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), HCOMM_ROOT_FILE=str(Path(tmp) / "root.bin"))
             env.update(env_extra or {})
-            procs.append(subprocess.Popen([sys.executable, WORKER, scenario], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+            procs.append(subprocess.Popen([sys.executable, WORKER, scenario], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, errors="replace"))
         codes, outs = [], []
         for p in procs:
             try:
