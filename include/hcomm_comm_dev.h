@@ -78,8 +78,11 @@ struct CommDev {
 
 #ifdef __CUDACC__
 #define HC_HD __host__ __device__ __forceinline__
-#else
+#elif defined(__cplusplus)
 #define HC_HD inline
+#else
+#define HC_HD static inline
+typedef struct CommDev CommDev;   /* C programs read the layout too */
 #endif
 
 HC_HD char *HcPeerHeap(const CommDev *d, int r) { return d->heapBase + (uint64_t)r * d->heapStride; }

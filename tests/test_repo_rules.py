@@ -49,3 +49,15 @@ def test_every_exported_entry_point_is_in_the_api_reference():
     doc = (ROOT / "docs" / "api_reference.md").read_text()
     missing = [n for n in names if f"`{n}`" not in doc]
     assert not missing, missing
+
+
+def test_public_headers_compile_as_c():
+    """The API is a C ABI: every header under include/ except the CUDA one is accepted by a C compiler on its own."""
+    import subprocess
+    inc = ROOT / "include"
+    cuda = "/usr/local/cuda/include"
+    for header in sorted(inc.rglob("*.h")):
+        rel = header.relative_to(inc)
+        res = subprocess.run(["gcc", "-std=c11", "-fsyntax-only", "-Wall", f"-I{inc}", f"-I{cuda}", "-x", "c", "-"], input=f'#include "{rel}"\n',
+                             capture_output=True, text=True)
+        assert res.returncode == 0, f"{rel}:\n{res.stderr[-2000:]}"
